@@ -1,0 +1,254 @@
+/*
+ * sofie_cuda.h -- C ABI of libSOFIE_cuda, the sm_100a (B200) back end of SOFIE's dense-contraction
+ * inference path.
+ *
+ * This header is what the code emitted by RModel::Generate() includes in place of the block of
+ * Fortran BLAS prototypes the reference writes into every generated header
+ * (reference: src/SOFIE_core/src/RModel_Base.cxx:40-58). It is plain C: no CUDA types, no C++
+ * types, pointers and sizes only. Every function returns an int status (0 = success); nothing
+ * throws across this boundary. The emitted Session turns a non-zero status into
+ * std::runtime_error, which is the reference's own error convention
+ * (reference: src/SOFIE_core/src/RModel.cxx:975-1013).
+ *
+ * Conventions
+ *   - "device pointer" = address in the memory of the GPU the call runs on. Host pointers are
+ *     marked "host".
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream). All compute
+ *     entry points only enqueue work; they do not synchronise.
+ *   - Tensors are dense and row-major. Activations of convolutions are NCHW (the reference's only
+ *     layout) or NHWC (the layout the tensor-core path keeps between fused layers); the descriptor
+ *     says which.
+ *   - There is no CPU fallback: without a usable GPU every compute entry point fails.
+ */
+#ifndef SOFIE_CUDA_H
+#define SOFIE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ status ------------------ */
+#define SOFIE_CUDA_OK 0
+#define SOFIE_CUDA_ERR_INVALID 1     /* bad argument, shape or alignment                          */
+#define SOFIE_CUDA_ERR_UNSUPPORTED 2 /* valid request this build has no kernel for                */
+#define SOFIE_CUDA_ERR_CUDA 3        /* the CUDA runtime / driver reported an error               */
+#define SOFIE_CUDA_ERR_NOMEM 4       /* arena slice out of range or allocation failure            */
+#define SOFIE_CUDA_ERR_DEVICE 5      /* a kernel set its status word (a bounded wait ran out)     */
+
+/* Short text for a status code. Never NULL. */
+const char *sofie_cuda_strerror(int status);
+/* Detail of the last failure on the calling thread ("" if none). Never NULL. */
+const char *sofie_cuda_last_error(void);
+/* ABI version of the loaded library (SOFIE_CUDA_ABI_VERSION of the build). */
+#define SOFIE_CUDA_ABI_VERSION 1
+int sofie_cuda_abi_version(void);
+/* Number of visible CUDA devices (0 and SOFIE_CUDA_ERR_CUDA when there is no driver). */
+int sofie_cuda_device_count(int *count);
+
+/* ------------------------------------------------------------------ context ----------------- */
+/*
+ * One context per emitted Session and GPU. It replaces the Session members the reference emits:
+ * the per-weight std::vector<float> (reference: src/SOFIE_core/src/RModel.cxx:574-595) and the
+ * `new char[]` intermediate pool (reference: src/SOFIE_core/src/RModel.cxx:597-604), which the
+ * reference never frees. The context owns one stream, one device arena allocated once, the
+ * uploaded weights, a pinned staging buffer and, optionally, one captured CUDA graph of infer().
+ */
+typedef struct sofie_cuda_ctx sofie_cuda_ctx;
+
+/* device < 0: take the device from the environment variable SOFIE_CUDA_DEVICE, else device 0. */
+int sofie_cuda_ctx_create(sofie_cuda_ctx **ctx, int device, size_t arena_bytes);
+int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx);
+int sofie_cuda_ctx_stream(sofie_cuda_ctx *ctx, void **stream);
+int sofie_cuda_ctx_device(sofie_cuda_ctx *ctx, int *device);
+/* Bounds-checked pointer to arena bytes [offset, offset+bytes). Offsets are 256-byte aligned. */
+int sofie_cuda_ctx_arena(sofie_cuda_ctx *ctx, size_t offset, size_t bytes, void **dptr);
+/* Persistent device allocation owned by the context (weights, packed weights, scale tables). */
+int sofie_cuda_ctx_alloc(sofie_cuda_ctx *ctx, size_t bytes, void **dptr);
+/* Allocate and fill from host memory; replaces the text-file weight read into fTensor_* vectors
+ * (reference: src/SOFIE_core/src/RModel.cxx:970-1018 reads, this uploads what was read). */
+int sofie_cuda_ctx_upload(sofie_cuda_ctx *ctx, const void *host, size_t bytes, void **dptr);
+/* Host -> device through the context's pinned staging buffer, asynchronous on the context stream
+ * (first statement of the emitted infer()). */
+int sofie_cuda_ctx_h2d(sofie_cuda_ctx *ctx, void *dst_device, const void *src_host, size_t bytes);
+/* Device -> host; returns after the data has arrived (last statement of the emitted infer(),
+ * replaces `return std::vector<float>(tensor_y, tensor_y + n)`,
+ * reference: src/SOFIE_core/src/RModel.cxx:717-740). */
+int sofie_cuda_ctx_d2h(sofie_cuda_ctx *ctx, void *dst_host, const void *src_device, size_t bytes);
+int sofie_cuda_ctx_sync(sofie_cuda_ctx *ctx);
+/* Read and clear the device-side status word that kernels with bounded waits set on give-up. */
+int sofie_cuda_ctx_check(sofie_cuda_ctx *ctx);
+/* Capture of the kernel sequence of one infer() into a CUDA graph: begin, run the launchers on
+ * the context stream, end; then launch replays it. */
+int sofie_cuda_ctx_graph_begin(sofie_cuda_ctx *ctx);
+int sofie_cuda_ctx_graph_end(sofie_cuda_ctx *ctx);
+int sofie_cuda_ctx_graph_launch(sofie_cuda_ctx *ctx);
+int sofie_cuda_ctx_graph_ready(sofie_cuda_ctx *ctx, int *ready);
+
+/* ------------------------------------------------------------------ fp32 contractions ------- */
+#define SOFIE_LAYOUT_NCHW 0
+#define SOFIE_LAYOUT_NHWC 1
+
+/* Which kernel family served the last call of a contraction entry point on this thread:
+ * 0 = none yet, 1 = CUDA-core kernel, 2 = tcgen05 tensor-core kernel. For tests and logs. */
+#define SOFIE_ENGINE_NONE 0
+#define SOFIE_ENGINE_SIMT 1
+#define SOFIE_ENGINE_TCGEN05 2
+int sofie_cuda_last_engine(void);
+/* Force the kernel family for later calls on every thread: 0 = automatic (default),
+ * 1 = CUDA cores only, 2 = tcgen05 only (calls with no tcgen05 kernel then fail UNSUPPORTED). */
+int sofie_cuda_set_engine(int engine);
+
+/*
+ * Y[M,N] = alpha * op(A) * op(B) + beta * broadcast(C), optional Relu. ONNX Gemm / MatMul.
+ * Replaces the text emitted by ROperator_Gemm<float>::Generate
+ * (reference: src/SOFIE_core/inc/SOFIE/ROperator_Gemm.hxx:292-390): std::copy of the pre-broadcast
+ * bias into Y, BLAS::sgemm_, and the separate Relu loop. fp32 in, fp32 out; the tensor-core path
+ * evaluates the product as 3 TF32 products of a hi/lo split with fp32 accumulation.
+ */
+typedef struct sofie_gemm_f32_desc {
+   int32_t M, N, K;
+   int32_t transA;    /* 0: A is [M,K]; 1: A is [K,M]                                    */
+   int32_t transB;    /* 0: B is [K,N]; 1: B is [N,K] (what PyTorch's Linear exports)     */
+   float alpha, beta;
+   int32_t bias_kind; /* 0: no C (beta ignored); 1: C is [N], broadcast over rows; 2: C is [M,N] */
+   int32_t relu;      /* 1: y = y > 0 ? y : 0                                             */
+} sofie_gemm_f32_desc;
+int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *desc, const float *A, const float *B,
+                        const float *C, float *Y);
+
+/* out[cols,rows] = in[rows,cols]^T, used once per Session to bring a [K,N] weight to [N,K]. */
+int sofie_cuda_transpose_f32(void *stream, const float *in, float *out, int32_t rows, int32_t cols);
+
+/*
+ * 2-D convolution (cross-correlation) + per-channel bias, optional Relu, optional fused
+ * MaxPool 2x2 stride 2. Replaces the text emitted by ROperator_Conv<float>::Generate
+ * (reference: src/SOFIE_core/inc/SOFIE/ROperator_Conv.hxx:302-522: weight repack, per-image
+ * UTILITY::Im2col (reference: src/SOFIE_core/inc/SOFIE/SOFIE_common.hxx:485-518), sgemm_, saxpy_)
+ * and, when relu/pool are set, the following ROperator_Relu and ROperator_Pool sweeps
+ * (reference: ROperator_Relu.hxx:54-66, ROperator_Pool.hxx:371-416). No im2col buffer exists.
+ * Pads are symmetric as in the reference (ROperator_Conv.hxx:387-410 averages asymmetric pads).
+ */
+typedef struct sofie_conv2d_desc {
+   int32_t N, C, H, W;     /* input  [N,C,H,W]                                            */
+   int32_t Cout, kH, kW;   /* weight [Cout, C/group, kH, kW]                              */
+   int32_t pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, group;
+   int32_t x_layout;       /* SOFIE_LAYOUT_* of X                                          */
+   int32_t y_layout;       /* SOFIE_LAYOUT_* of Y                                          */
+   int32_t w_packed;       /* 0: W as in ONNX [Cout,C/g,kH,kW]; 1: packed by sofie_cuda_conv2d_pack_* */
+   int32_t relu;           /* fused Relu                                                   */
+   int32_t pool;           /* 0: none; 2: fused MaxPool kernel 2x2 stride 2 (after Relu)   */
+} sofie_conv2d_desc;
+int sofie_cuda_conv2d_f32(void *stream, const sofie_conv2d_desc *desc, const float *X, const float *W,
+                          const float *bias, float *Y);
+/* Repack ONNX weights [Cout,C,kH,kW] to the tensor-core layout [Cout][kH][kW][C] (group 1). */
+int sofie_cuda_conv2d_pack_f32(void *stream, const sofie_conv2d_desc *desc, const float *W, float *Wpacked);
+
+/* ------------------------------------------------------------------ fp32 memory-bound ops --- */
+/* y = x > 0 ? x : 0 (reference: ROperator_Relu.hxx:54-66). In place allowed. */
+int sofie_cuda_relu_f32(void *stream, const float *X, float *Y, size_t n);
+
+/* MaxPool / AveragePool 2-D (reference: ROperator_Pool.hxx:266-476). `pads` are used exactly as
+ * the reference uses the ONNX attribute: rows span [-pads[0], H+pads[1]-kH], columns
+ * [-pads[2], W+pads[3]-kW] (ROperator_Pool.hxx:283-289). */
+typedef struct sofie_pool2d_desc {
+   int32_t mode;            /* 0 max, 1 average                                            */
+   int32_t N, C, H, W;
+   int32_t kH, kW, stride_h, stride_w;
+   int32_t pads[4];
+   int32_t count_include_pad;
+   int32_t layout;          /* SOFIE_LAYOUT_* of both X and Y                               */
+} sofie_pool2d_desc;
+int sofie_cuda_pool2d_f32(void *stream, const sofie_pool2d_desc *desc, const float *X, float *Y);
+
+/* Softmax along one axis of a tensor viewed as [outer, axis_len, inner]
+ * (reference: ROperator_Softmax.hxx:53-184). */
+int sofie_cuda_softmax_f32(void *stream, const float *X, float *Y, size_t outer, size_t axis_len, size_t inner);
+
+/* NCHW <-> NHWC copies for tensors that cross a layout boundary un-fused. */
+int sofie_cuda_nchw_to_nhwc_f32(void *stream, const float *X, float *Y, int32_t N, int32_t C, int32_t H, int32_t W);
+int sofie_cuda_nhwc_to_nchw_f32(void *stream, const float *X, float *Y, int32_t N, int32_t C, int32_t H, int32_t W);
+
+/* ------------------------------------------------------------------ int8 -------------------- */
+/* The reference has no quantised operators (src/SOFIE_parsers/src/RModelParser_ONNX.cxx:154-236
+ * registers none); these follow the ONNX operator definitions with int32 accumulation and
+ * q = clamp(rne((float)acc * mult[n])) + y_zp, bit-exactly reproducible on a CPU. */
+
+/* QuantizeLinear to uint8: y = saturate(rne(x / scale) + zp). */
+int sofie_cuda_quantize_u8(void *stream, const float *X, uint8_t *Y, size_t n, float scale, int32_t zp);
+/* DequantizeLinear from uint8: y = (x - zp) * scale. */
+int sofie_cuda_dequantize_u8(void *stream, const uint8_t *X, float *Y, size_t n, float scale, int32_t zp);
+
+/*
+ * Host-side, once per Session: from HOST int8 weights computes, in a fixed fp32 order,
+ *   mult[n] = (a_scale * w_scale[n]) / y_scale     and
+ *   corr[n] = bias[n] - a_zp * sum_k W[n][k]       (int32; bias may be NULL)
+ * and writes both to the given DEVICE buffers of N elements each. `rows_per_n` is the number of
+ * weights per output channel (K for a matmul, C*kH*kW for a convolution).
+ */
+int sofie_cuda_qlinear_prepare(void *stream, int32_t N, int32_t rows_per_n, const int8_t *W_host, int32_t w_is_nk,
+                               float a_scale, int32_t a_zp, const float *w_scale_host, float y_scale,
+                               const int32_t *bias_host, float *mult_device, int32_t *corr_device);
+
+/* QLinearMatMul: Y = requant(A[M,K] (uint8) x W (int8), per-output-channel multiplier). */
+typedef struct sofie_qgemm_desc {
+   int32_t M, N, K;
+   int32_t w_is_nk;  /* 1: W is [N,K]; 0: W is [K,N] as ONNX stores it                        */
+   int32_t y_zp;
+   int32_t relu;     /* q = max(q, y_zp)                                                     */
+} sofie_qgemm_desc;
+int sofie_cuda_qlinear_matmul(void *stream, const sofie_qgemm_desc *desc, const uint8_t *A, const int8_t *W,
+                              const float *mult, const int32_t *corr, uint8_t *Y);
+/* out[N,K] = in[K,N]^T for int8 weights. */
+int sofie_cuda_transpose_i8(void *stream, const int8_t *in, int8_t *out, int32_t rows, int32_t cols);
+
+/* QLinearConv 2-D: uint8 activations (zero point x_zp; padding contributes nothing), int8 weights,
+ * per-Cout multiplier, optional Relu and fused MaxPool 2x2. `corr` is bias only (int32, may be
+ * NULL); the zero-point term is applied per output position because it depends on which taps fall
+ * inside the image. */
+typedef struct sofie_qconv2d_desc {
+   int32_t N, C, H, W, Cout, kH, kW, pad_h, pad_w, stride_h, stride_w;
+   int32_t x_layout, y_layout, w_packed;
+   int32_t x_zp, y_zp;
+   int32_t relu, pool;
+} sofie_qconv2d_desc;
+int sofie_cuda_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *desc, const uint8_t *X, const int8_t *W,
+                              const float *mult, const int32_t *bias, uint8_t *Y);
+int sofie_cuda_qconv2d_pack_i8(void *stream, const sofie_qconv2d_desc *desc, const int8_t *W, int8_t *Wpacked);
+/* MaxPool 2-D on uint8 (integer max), no padding. */
+int sofie_cuda_maxpool2d_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W,
+                            int32_t kH, int32_t kW, int32_t stride_h, int32_t stride_w, int32_t layout);
+/* uint8 NCHW <-> NHWC. */
+int sofie_cuda_nchw_to_nhwc_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W);
+int sofie_cuda_nhwc_to_nchw_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W);
+
+/* ------------------------------------------------------------------ FP8 E4M3 ---------------- */
+/* Also absent from the reference. E4M3 is the "FN" encoding (max 448, no infinities); bf16 and
+ * E4M3 values cross this ABI as raw uint16_t / uint8_t bit patterns. */
+
+/* y = e4m3(x / scale), round to nearest even, saturating. */
+int sofie_cuda_quantize_e4m3_f32(void *stream, const float *X, uint8_t *Y, size_t n, float scale);
+int sofie_cuda_quantize_e4m3_bf16(void *stream, const uint16_t *X, uint8_t *Y, size_t n, float scale);
+int sofie_cuda_cast_bf16_f32(void *stream, const uint16_t *X, float *Y, size_t n);
+int sofie_cuda_cast_f32_bf16(void *stream, const float *X, uint16_t *Y, size_t n);
+/* max |x| over n values, written to one device float (per-tensor FP8 scale = amax / 448). */
+int sofie_cuda_amax_f32(void *stream, const float *X, size_t n, float *amax_device);
+
+/* Y = bf16( relu( (A x W^T) * (a_scale*w_scale) + bias ) ), A [M,K] and W [N,K] E4M3, fp32
+ * accumulation. When q_scale > 0 the same pass also writes Yq = e4m3(bf16 result / q_scale), the
+ * quantised input of the next FP8 layer, so the activation does not make another trip to HBM. */
+typedef struct sofie_fp8_gemm_desc {
+   int32_t M, N, K;
+   float a_scale, w_scale;
+   int32_t relu;
+   float q_scale;
+} sofie_fp8_gemm_desc;
+int sofie_cuda_gemm_e4m3(void *stream, const sofie_fp8_gemm_desc *desc, const uint8_t *A, const uint8_t *W,
+                         const float *bias, uint16_t *Ybf16, uint8_t *Yq);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SOFIE_CUDA_H */

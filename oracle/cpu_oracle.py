@@ -1,0 +1,211 @@
+"""ctypes binding of liboracle.so (oracle/sofie_oracle.c). TEST INFRASTRUCTURE ONLY.
+
+Only tests, the smoke check and the CPU-baseline leg of the benchmark import this module; the
+product never does. Arrays are numpy; every function returns a new array.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB = HERE / "liboracle.so"
+_lib = None
+
+
+def build(force: bool = False) -> Path:
+    src = HERE / "sofie_oracle.c"
+    if force or not LIB.exists() or LIB.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(HERE), "-B", "liboracle.so"], check=True, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT)
+    return LIB
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(str(build()))
+        _lib.oracle_e4m3_to_f32.restype = C.c_float
+        _lib.oracle_e4m3_to_f32.argtypes = [C.c_uint8]
+        _lib.oracle_f32_to_e4m3.restype = C.c_uint8
+        _lib.oracle_f32_to_e4m3.argtypes = [C.c_float]
+        _lib.oracle_f32_to_bf16.restype = C.c_uint16
+        _lib.oracle_f32_to_bf16.argtypes = [C.c_float]
+        _lib.oracle_bf16_to_f32.restype = C.c_float
+        _lib.oracle_bf16_to_f32.argtypes = [C.c_uint16]
+        _lib.oracle_num_threads.restype = C.c_int
+    return _lib
+
+
+def _f(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def num_threads() -> int:
+    return lib().oracle_num_threads()
+
+
+def gemm_f32(A, B, C_=None, transA=0, transB=0, alpha=1.0, beta=1.0, relu=False):
+    A, B = _f(A), _f(B)
+    M = A.shape[1] if transA else A.shape[0]
+    K = A.shape[0] if transA else A.shape[1]
+    N = B.shape[0] if transB else B.shape[1]
+    kind = 0
+    if C_ is not None:
+        C_ = _f(C_)
+        kind = 1 if C_.size == N else 2
+    Y = np.empty((M, N), np.float32)
+    lib().oracle_gemm_f32(C.c_int(transA), C.c_int(transB), C.c_int(M), C.c_int(N), C.c_int(K), C.c_float(alpha),
+                          _ptr(A), _ptr(B), C.c_float(beta), _ptr(C_), C.c_int(kind), C.c_int(int(relu)), _ptr(Y))
+    return Y
+
+
+def conv2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), group=1, relu=False):
+    X, W = _f(X), _f(W)
+    N, Cin, H, Wd = X.shape
+    Cout, _, kh, kw = W.shape
+    oH = (H + 2 * pad[0] - (dil[0] * (kh - 1) + 1)) // stride[0] + 1
+    oW = (Wd + 2 * pad[1] - (dil[1] * (kw - 1) + 1)) // stride[1] + 1
+    if bias is not None:
+        bias = _f(bias)
+    Y = np.empty((N, Cout, oH, oW), np.float32)
+    ints = [N, Cin, H, Wd, Cout, kh, kw, pad[0], pad[1], stride[0], stride[1], dil[0], dil[1], group]
+    lib().oracle_conv2d_f32(*[C.c_int(v) for v in ints], _ptr(X), _ptr(W), _ptr(bias), C.c_int(int(relu)), _ptr(Y))
+    return Y
+
+
+def relu_f32(X):
+    X = _f(X)
+    Y = np.empty_like(X)
+    lib().oracle_relu_f32(_ptr(X), C.c_size_t(X.size), _ptr(Y))
+    return Y
+
+
+def pool2d_f32(X, mode=0, kernel=(2, 2), stride=(2, 2), pads=(0, 0, 0, 0), count_include_pad=0):
+    X = _f(X)
+    N, Cc, H, W = X.shape
+    oH = -(-(H + pads[0] + pads[1] - kernel[0] + 1) // stride[0])
+    oW = -(-(W + pads[2] + pads[3] - kernel[1] + 1) // stride[1])
+    Y = np.empty((N, Cc, oH, oW), np.float32)
+    p = (C.c_int * 4)(*pads)
+    lib().oracle_pool2d_f32(C.c_int(mode), C.c_size_t(N * Cc), C.c_int(H), C.c_int(W), C.c_int(kernel[0]),
+                            C.c_int(kernel[1]), p, C.c_int(stride[0]), C.c_int(stride[1]),
+                            C.c_int(count_include_pad), _ptr(X), _ptr(Y))
+    return Y
+
+
+def softmax_f32(X, axis=-1):
+    X = _f(X)
+    axis = axis % X.ndim
+    outer = int(np.prod(X.shape[:axis], dtype=np.int64))
+    inner = int(np.prod(X.shape[axis + 1:], dtype=np.int64))
+    Y = np.empty_like(X)
+    lib().oracle_softmax_f32(C.c_size_t(outer), C.c_size_t(X.shape[axis]), C.c_size_t(inner), _ptr(X), _ptr(Y))
+    return Y
+
+
+def requant_multiplier(a_scale, w_scale, y_scale):
+    w_scale = _f(w_scale)
+    m = np.empty_like(w_scale)
+    lib().oracle_requant_multiplier(C.c_float(a_scale), _ptr(w_scale), C.c_int(w_scale.size), C.c_float(y_scale),
+                                    _ptr(m))
+    return m
+
+
+def quantize_u8(X, scale, zp):
+    X = _f(X)
+    Y = np.empty(X.shape, np.uint8)
+    lib().oracle_quantize_u8(_ptr(X), C.c_size_t(X.size), C.c_float(scale), C.c_int32(zp), _ptr(Y))
+    return Y
+
+
+def dequantize_u8(X, scale, zp):
+    X = np.ascontiguousarray(X, np.uint8)
+    Y = np.empty(X.shape, np.float32)
+    lib().oracle_dequantize_u8(_ptr(X), C.c_size_t(X.size), C.c_float(scale), C.c_int32(zp), _ptr(Y))
+    return Y
+
+
+def qlinear_matmul(A, a_scale, a_zp, W, w_scale, y_scale, y_zp, bias=None, w_is_nk=True, relu=False):
+    A = np.ascontiguousarray(A, np.uint8)
+    W = np.ascontiguousarray(W, np.int8)
+    w_scale = _f(w_scale)
+    M, K = A.shape
+    N = W.shape[0] if w_is_nk else W.shape[1]
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, np.int32)
+    Y = np.empty((M, N), np.uint8)
+    lib().oracle_qlinear_matmul(C.c_int(M), C.c_int(N), C.c_int(K), _ptr(A), C.c_float(a_scale), C.c_int32(a_zp),
+                                _ptr(W), C.c_int(int(w_is_nk)), _ptr(w_scale), _ptr(bias), C.c_float(y_scale),
+                                C.c_int32(y_zp), C.c_int(int(relu)), _ptr(Y))
+    return Y
+
+
+def qlinear_conv2d(X, x_scale, x_zp, W, w_scale, y_scale, y_zp, bias=None, pad=(0, 0), stride=(1, 1), relu=False):
+    X = np.ascontiguousarray(X, np.uint8)
+    W = np.ascontiguousarray(W, np.int8)
+    w_scale = _f(w_scale)
+    N, Cin, H, Wd = X.shape
+    Cout, _, kh, kw = W.shape
+    oH = (H + 2 * pad[0] - kh) // stride[0] + 1
+    oW = (Wd + 2 * pad[1] - kw) // stride[1] + 1
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, np.int32)
+    Y = np.empty((N, Cout, oH, oW), np.uint8)
+    ints = [N, Cin, H, Wd, Cout, kh, kw, pad[0], pad[1], stride[0], stride[1]]
+    lib().oracle_qlinear_conv2d(*[C.c_int(v) for v in ints], _ptr(X), C.c_float(x_scale), C.c_int32(x_zp), _ptr(W),
+                                _ptr(w_scale), _ptr(bias), C.c_float(y_scale), C.c_int32(y_zp), C.c_int(int(relu)),
+                                _ptr(Y))
+    return Y
+
+
+def maxpool2d_u8(X, kernel=(2, 2), stride=(2, 2)):
+    X = np.ascontiguousarray(X, np.uint8)
+    N, Cc, H, W = X.shape
+    oH, oW = (H - kernel[0]) // stride[0] + 1, (W - kernel[1]) // stride[1] + 1
+    Y = np.empty((N, Cc, oH, oW), np.uint8)
+    lib().oracle_maxpool2d_u8(C.c_size_t(N * Cc), C.c_int(H), C.c_int(W), C.c_int(kernel[0]), C.c_int(kernel[1]),
+                              C.c_int(stride[0]), C.c_int(stride[1]), _ptr(X), _ptr(Y))
+    return Y
+
+
+def quantize_e4m3(X, scale):
+    X = _f(X)
+    Y = np.empty(X.shape, np.uint8)
+    lib().oracle_quantize_e4m3(_ptr(X), C.c_size_t(X.size), C.c_float(scale), _ptr(Y))
+    return Y
+
+
+def e4m3_table():
+    return np.array([lib().oracle_e4m3_to_f32(i) for i in range(256)], np.float32)
+
+
+def f32_to_bf16_bits(X):
+    X = _f(X)
+    return np.array([lib().oracle_f32_to_bf16(float(v)) for v in X.ravel()], np.uint16).reshape(X.shape)
+
+
+def bf16_bits_to_f32(B):
+    B = np.ascontiguousarray(B, np.uint16)
+    return (B.astype(np.uint32) << 16).view(np.float32)
+
+
+def gemm_e4m3(A, a_scale, W, w_scale, bias=None, relu=False):
+    """A [M,K], W [N,K] uint8 E4M3 codes -> bf16 bits [M,N] (uint16)."""
+    A = np.ascontiguousarray(A, np.uint8)
+    W = np.ascontiguousarray(W, np.uint8)
+    M, K = A.shape
+    N = W.shape[0]
+    if bias is not None:
+        bias = _f(bias)
+    Y = np.empty((M, N), np.uint16)
+    lib().oracle_gemm_e4m3(C.c_int(M), C.c_int(N), C.c_int(K), _ptr(A), C.c_float(a_scale), _ptr(W),
+                           C.c_float(w_scale), _ptr(bias), C.c_int(int(relu)), _ptr(Y))
+    return Y

@@ -1,0 +1,85 @@
+// Shared host/device helpers of libSOFIE_cuda: status handling, launch checks, small math.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+#include "sofie_cuda.h"
+
+namespace sofie {
+
+// Thread-local text of the last failure, returned by sofie_cuda_last_error().
+char *last_error_buffer();
+int fail(int status, const char *fmt, ...);
+void set_last_engine(int engine);
+int forced_engine();
+
+// Device-side status word shared by all kernels that have bounded waits. A kernel that gives up
+// stores a non-zero code here and returns normally, so the context stays usable; the host reads
+// it with sofie_cuda_ctx_check().
+uint32_t *device_status_word(); // device pointer (per current device), nullptr on failure
+
+#define SOFIE_CUDA_TRY(expr)                                                                         \
+   do {                                                                                              \
+      cudaError_t err__ = (expr);                                                                    \
+      if (err__ != cudaSuccess)                                                                      \
+         return ::sofie::fail(SOFIE_CUDA_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                   \
+                              cudaGetErrorString(err__), __FILE__, __LINE__);                        \
+   } while (0)
+
+#define SOFIE_LAUNCH_CHECK(name)                                                                     \
+   do {                                                                                              \
+      cudaError_t err__ = cudaGetLastError();                                                        \
+      if (err__ != cudaSuccess)                                                                      \
+         return ::sofie::fail(SOFIE_CUDA_ERR_CUDA, "launch of %s failed: %s", name,                  \
+                              cudaGetErrorString(err__));                                            \
+   } while (0)
+
+#define SOFIE_REQUIRE(cond, ...)                                                                     \
+   do {                                                                                              \
+      if (!(cond)) return ::sofie::fail(SOFIE_CUDA_ERR_INVALID, __VA_ARGS__);                        \
+   } while (0)
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+constexpr int kNumSMs = 148; // B200
+
+template <typename T>
+__host__ __device__ constexpr T ceil_div(T a, T b)
+{
+   return (a + b - 1) / b;
+}
+
+// ---- requantisation recipe shared by every int8 kernel -------------------------------------------
+// q = clamp(rne((float)acc * mult), qmin - zp, qmax - zp) + zp, with no FMA contraction, so a CPU
+// evaluating nearbyintf((float)acc * mult) under the default rounding mode gets the same bits.
+__device__ __forceinline__ int requant_u8(int acc, float mult, int y_zp, int relu)
+{
+   float r = rintf(__fmul_rn(__int2float_rn(acc), mult));
+   float lo = (float)(0 - y_zp), hi = (float)(255 - y_zp);
+   r = fminf(fmaxf(r, lo), hi);
+   int q = __float2int_rn(r) + y_zp;
+   if (relu && q < y_zp) q = y_zp;
+   return q;
+}
+
+__device__ __forceinline__ float relu_ref(float v)
+{
+   // The reference's `x > 0 ? x : 0`: NaN and -0 both become +0.
+   return v > 0.f ? v : 0.f;
+}
+
+__device__ __forceinline__ uint16_t f32_to_bf16_rne(float x)
+{
+   uint32_t u = __float_as_uint(x);
+   if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40);
+   u += 0x7FFFu + ((u >> 16) & 1u);
+   return (uint16_t)(u >> 16);
+}
+
+__device__ __forceinline__ float bf16_to_f32(uint16_t v) { return __uint_as_float((uint32_t)v << 16); }
+
+} // namespace sofie

@@ -1,0 +1,33 @@
+// Internal launcher interface between api.cu (validation, dispatch) and the kernel files.
+#pragma once
+#include "common.cuh"
+
+namespace sofie {
+
+struct ConvGeom {
+   int N, C, H, W, Cout, kH, kW, pad_h, pad_w, sh, sw, dh, dw, group;
+   int oH, oW;    // convolution output extent
+   int pH, pW;    // stored output extent (halved when pool == 2)
+   int x_nhwc, y_nhwc, w_packed, relu, pool;
+};
+
+int launch_gemm_f32_simt(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *, float *);
+int launch_gemm_f32_umma(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *, float *);
+int launch_qgemm_simt(cudaStream_t, const sofie_qgemm_desc &, const uint8_t *, const int8_t *, const float *,
+                      const int32_t *, uint8_t *);
+int launch_qgemm_umma(cudaStream_t, const sofie_qgemm_desc &, const uint8_t *, const int8_t *, const float *,
+                      const int32_t *, uint8_t *);
+int launch_gemm_e4m3_simt(cudaStream_t, const sofie_fp8_gemm_desc &, const uint8_t *, const uint8_t *, const float *,
+                          uint16_t *, uint8_t *);
+int launch_gemm_e4m3_umma(cudaStream_t, const sofie_fp8_gemm_desc &, const uint8_t *, const uint8_t *, const float *,
+                          uint16_t *, uint8_t *);
+int launch_conv2d_f32_simt(cudaStream_t, const ConvGeom &, const float *, const float *, const float *, float *);
+int launch_conv2d_f32_umma(cudaStream_t, const ConvGeom &, const float *, const float *, const float *, float *);
+int launch_qconv2d_simt(cudaStream_t, const ConvGeom &, const uint8_t *, const int8_t *, const float *, const int32_t *,
+                        int x_zp, int y_zp, uint8_t *);
+int launch_qconv2d_umma(cudaStream_t, const ConvGeom &, const uint8_t *, const int8_t *, const float *, const int32_t *,
+                        int x_zp, int y_zp, uint8_t *);
+template <typename T>
+int launch_pack_ohwi(cudaStream_t, const T *, T *, int Cout, int C, int kH, int kW);
+
+} // namespace sofie

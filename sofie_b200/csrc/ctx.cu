@@ -1,0 +1,360 @@
+// Context of one emitted Session on one GPU: stream, device arena, persistent allocations (weights),
+// pinned staging for host<->device traffic, optional CUDA graph of the infer() kernel sequence.
+//
+// Replaces what the reference emits as Session data members: one std::vector<float> per weight
+// (reference: src/SOFIE_core/src/RModel.cxx:574-595) and the `new char[]` intermediate pool
+// (reference: src/SOFIE_core/src/RModel.cxx:597-604).
+#include "common.cuh"
+
+#include <cstdlib>
+#include <mutex>
+#include <vector>
+
+namespace sofie {
+
+static thread_local char g_last_error[512] = "";
+static thread_local int g_last_engine = SOFIE_ENGINE_NONE;
+static int g_forced_engine = 0;
+
+char *last_error_buffer() { return g_last_error; }
+
+int fail(int status, const char *fmt, ...)
+{
+   va_list ap;
+   va_start(ap, fmt);
+   vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+   va_end(ap);
+   return status;
+}
+
+void set_last_engine(int engine) { g_last_engine = engine; }
+int forced_engine() { return g_forced_engine; }
+
+// One status word per device, allocated on first use with that device current.
+static std::mutex g_status_mutex;
+static uint32_t *g_status_words[64] = {nullptr};
+
+uint32_t *device_status_word()
+{
+   int dev = 0;
+   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+   std::lock_guard<std::mutex> lock(g_status_mutex);
+   if (!g_status_words[dev]) {
+      uint32_t *p = nullptr;
+      if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+      if (cudaMemset(p, 0, 256) != cudaSuccess) return nullptr;
+      g_status_words[dev] = p;
+   }
+   return g_status_words[dev];
+}
+
+} // namespace sofie
+
+struct sofie_cuda_ctx {
+   int device = 0;
+   cudaStream_t stream = nullptr;
+   char *arena = nullptr;
+   size_t arena_bytes = 0;
+   std::vector<void *> owned;
+   void *staging = nullptr; // pinned
+   size_t staging_bytes = 0;
+   cudaGraph_t graph = nullptr;
+   cudaGraphExec_t graph_exec = nullptr;
+   bool capturing = false;
+};
+
+using namespace sofie;
+
+namespace {
+struct DeviceGuard {
+   int prev = -1;
+   explicit DeviceGuard(int dev)
+   {
+      cudaGetDevice(&prev);
+      if (prev != dev) cudaSetDevice(dev);
+      else prev = -1;
+   }
+   ~DeviceGuard()
+   {
+      if (prev >= 0) cudaSetDevice(prev);
+   }
+};
+constexpr size_t kStagingBytes = size_t(64) << 20;
+} // namespace
+
+extern "C" {
+
+const char *sofie_cuda_strerror(int status)
+{
+   switch (status) {
+   case SOFIE_CUDA_OK: return "success";
+   case SOFIE_CUDA_ERR_INVALID: return "invalid argument";
+   case SOFIE_CUDA_ERR_UNSUPPORTED: return "unsupported configuration";
+   case SOFIE_CUDA_ERR_CUDA: return "CUDA error";
+   case SOFIE_CUDA_ERR_NOMEM: return "out of device memory or arena range";
+   case SOFIE_CUDA_ERR_DEVICE: return "kernel reported a device-side failure";
+   default: return "unknown status";
+   }
+}
+
+const char *sofie_cuda_last_error(void) { return last_error_buffer(); }
+int sofie_cuda_abi_version(void) { return SOFIE_CUDA_ABI_VERSION; }
+int sofie_cuda_last_engine(void) { return g_last_engine; }
+
+int sofie_cuda_set_engine(int engine)
+{
+   SOFIE_REQUIRE(engine >= 0 && engine <= 2, "engine must be 0, 1 or 2");
+   g_forced_engine = engine;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_device_count(int *count)
+{
+   SOFIE_REQUIRE(count != nullptr, "count is NULL");
+   *count = 0;
+   cudaError_t err = cudaGetDeviceCount(count);
+   if (err != cudaSuccess) {
+      *count = 0;
+      cudaGetLastError();
+      return fail(SOFIE_CUDA_ERR_CUDA, "cudaGetDeviceCount: %s", cudaGetErrorString(err));
+   }
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_create(sofie_cuda_ctx **out, int device, size_t arena_bytes)
+{
+   SOFIE_REQUIRE(out != nullptr, "ctx output pointer is NULL");
+   *out = nullptr;
+   if (device < 0) {
+      const char *env = std::getenv("SOFIE_CUDA_DEVICE");
+      device = env ? std::atoi(env) : 0;
+   }
+   int count = 0;
+   int rc = sofie_cuda_device_count(&count);
+   if (rc) return rc;
+   if (device >= count) return fail(SOFIE_CUDA_ERR_INVALID, "device %d requested, %d visible", device, count);
+   DeviceGuard guard(device);
+   auto *ctx = new sofie_cuda_ctx();
+   ctx->device = device;
+   cudaError_t err = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+   if (err == cudaSuccess && arena_bytes) {
+      ctx->arena_bytes = (arena_bytes + 255) & ~size_t(255);
+      err = cudaMalloc(&ctx->arena, ctx->arena_bytes);
+   }
+   if (err != cudaSuccess) {
+      if (ctx->stream) cudaStreamDestroy(ctx->stream);
+      delete ctx;
+      cudaGetLastError();
+      return fail(err == cudaErrorMemoryAllocation ? SOFIE_CUDA_ERR_NOMEM : SOFIE_CUDA_ERR_CUDA,
+                  "context creation on device %d (arena %zu bytes): %s", device, arena_bytes, cudaGetErrorString(err));
+   }
+   *out = ctx;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx)
+{
+   if (!ctx) return SOFIE_CUDA_OK;
+   DeviceGuard guard(ctx->device);
+   cudaStreamSynchronize(ctx->stream);
+   if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
+   if (ctx->graph) cudaGraphDestroy(ctx->graph);
+   for (void *p : ctx->owned) cudaFree(p);
+   if (ctx->arena) cudaFree(ctx->arena);
+   if (ctx->staging) cudaFreeHost(ctx->staging);
+   cudaStreamDestroy(ctx->stream);
+   delete ctx;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_stream(sofie_cuda_ctx *ctx, void **stream)
+{
+   SOFIE_REQUIRE(ctx && stream, "NULL argument");
+   *stream = ctx->stream;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_device(sofie_cuda_ctx *ctx, int *device)
+{
+   SOFIE_REQUIRE(ctx && device, "NULL argument");
+   *device = ctx->device;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_arena(sofie_cuda_ctx *ctx, size_t offset, size_t bytes, void **dptr)
+{
+   SOFIE_REQUIRE(ctx && dptr, "NULL argument");
+   SOFIE_REQUIRE((offset & 255) == 0, "arena offset %zu is not 256-byte aligned", offset);
+   if (offset > ctx->arena_bytes || bytes > ctx->arena_bytes - offset)
+      return fail(SOFIE_CUDA_ERR_NOMEM, "arena slice [%zu, +%zu) exceeds arena of %zu bytes", offset, bytes,
+                  ctx->arena_bytes);
+   *dptr = ctx->arena + offset;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_alloc(sofie_cuda_ctx *ctx, size_t bytes, void **dptr)
+{
+   SOFIE_REQUIRE(ctx && dptr, "NULL argument");
+   DeviceGuard guard(ctx->device);
+   void *p = nullptr;
+   cudaError_t err = cudaMalloc(&p, bytes ? bytes : 256);
+   if (err != cudaSuccess) {
+      cudaGetLastError();
+      return fail(SOFIE_CUDA_ERR_NOMEM, "cudaMalloc of %zu bytes: %s", bytes, cudaGetErrorString(err));
+   }
+   ctx->owned.push_back(p);
+   *dptr = p;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_upload(sofie_cuda_ctx *ctx, const void *host, size_t bytes, void **dptr)
+{
+   SOFIE_REQUIRE(ctx && dptr && (host || bytes == 0), "NULL argument");
+   int rc = sofie_cuda_ctx_alloc(ctx, bytes, dptr);
+   if (rc) return rc;
+   DeviceGuard guard(ctx->device);
+   if (bytes) {
+      SOFIE_CUDA_TRY(cudaMemcpyAsync(*dptr, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+      SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+   }
+   return SOFIE_CUDA_OK;
+}
+
+static int ensure_staging(sofie_cuda_ctx *ctx)
+{
+   if (ctx->staging) return SOFIE_CUDA_OK;
+   SOFIE_CUDA_TRY(cudaMallocHost(&ctx->staging, kStagingBytes));
+   ctx->staging_bytes = kStagingBytes;
+   return SOFIE_CUDA_OK;
+}
+
+// Pageable host memory is staged through one pinned buffer in chunks; memory the caller already
+// pinned (cudaHostRegister / cudaMallocHost) is copied directly and stays asynchronous.
+static bool is_pinned(const void *p)
+{
+   cudaPointerAttributes attr;
+   if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+   }
+   return attr.type == cudaMemoryTypeHost;
+}
+
+int sofie_cuda_ctx_h2d(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t bytes)
+{
+   SOFIE_REQUIRE(ctx && dst && src, "NULL argument");
+   DeviceGuard guard(ctx->device);
+   if (is_pinned(src)) {
+      SOFIE_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+      return SOFIE_CUDA_OK;
+   }
+   int rc = ensure_staging(ctx);
+   if (rc) return rc;
+   size_t done = 0;
+   while (done < bytes) {
+      size_t chunk = bytes - done < ctx->staging_bytes ? bytes - done : ctx->staging_bytes;
+      // The staging buffer is reused: wait for the previous chunk's copy before overwriting it.
+      SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+      std::memcpy(ctx->staging, static_cast<const char *>(src) + done, chunk);
+      SOFIE_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(dst) + done, ctx->staging, chunk, cudaMemcpyHostToDevice,
+                                     ctx->stream));
+      done += chunk;
+   }
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_d2h(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t bytes)
+{
+   SOFIE_REQUIRE(ctx && dst && src, "NULL argument");
+   DeviceGuard guard(ctx->device);
+   if (is_pinned(dst)) {
+      SOFIE_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+      SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+      return SOFIE_CUDA_OK;
+   }
+   int rc = ensure_staging(ctx);
+   if (rc) return rc;
+   size_t done = 0;
+   while (done < bytes) {
+      size_t chunk = bytes - done < ctx->staging_bytes ? bytes - done : ctx->staging_bytes;
+      SOFIE_CUDA_TRY(cudaMemcpyAsync(ctx->staging, static_cast<const char *>(src) + done, chunk, cudaMemcpyDeviceToHost,
+                                     ctx->stream));
+      SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+      std::memcpy(static_cast<char *>(dst) + done, ctx->staging, chunk);
+      done += chunk;
+   }
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_sync(sofie_cuda_ctx *ctx)
+{
+   SOFIE_REQUIRE(ctx, "NULL ctx");
+   DeviceGuard guard(ctx->device);
+   SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_check(sofie_cuda_ctx *ctx)
+{
+   SOFIE_REQUIRE(ctx, "NULL ctx");
+   DeviceGuard guard(ctx->device);
+   uint32_t *word = device_status_word();
+   if (!word) return fail(SOFIE_CUDA_ERR_CUDA, "no device status word");
+   uint32_t host_word[4] = {0, 0, 0, 0};
+   SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+   SOFIE_CUDA_TRY(cudaMemcpy(host_word, word, sizeof(host_word), cudaMemcpyDeviceToHost));
+   if (host_word[0]) {
+      SOFIE_CUDA_TRY(cudaMemset(word, 0, 256));
+      return fail(SOFIE_CUDA_ERR_DEVICE, "device status 0x%x (detail 0x%x 0x%x 0x%x)", host_word[0], host_word[1],
+                  host_word[2], host_word[3]);
+   }
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_graph_begin(sofie_cuda_ctx *ctx)
+{
+   SOFIE_REQUIRE(ctx, "NULL ctx");
+   SOFIE_REQUIRE(!ctx->capturing, "graph capture already in progress");
+   DeviceGuard guard(ctx->device);
+   device_status_word(); // allocate outside of capture
+   if (ctx->graph_exec) {
+      cudaGraphExecDestroy(ctx->graph_exec);
+      ctx->graph_exec = nullptr;
+   }
+   if (ctx->graph) {
+      cudaGraphDestroy(ctx->graph);
+      ctx->graph = nullptr;
+   }
+   SOFIE_CUDA_TRY(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+   ctx->capturing = true;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_graph_end(sofie_cuda_ctx *ctx)
+{
+   SOFIE_REQUIRE(ctx, "NULL ctx");
+   SOFIE_REQUIRE(ctx->capturing, "no graph capture in progress");
+   DeviceGuard guard(ctx->device);
+   ctx->capturing = false;
+   SOFIE_CUDA_TRY(cudaStreamEndCapture(ctx->stream, &ctx->graph));
+   SOFIE_CUDA_TRY(cudaGraphInstantiate(&ctx->graph_exec, ctx->graph, 0));
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_graph_launch(sofie_cuda_ctx *ctx)
+{
+   SOFIE_REQUIRE(ctx, "NULL ctx");
+   SOFIE_REQUIRE(ctx->graph_exec != nullptr, "no captured graph");
+   DeviceGuard guard(ctx->device);
+   SOFIE_CUDA_TRY(cudaGraphLaunch(ctx->graph_exec, ctx->stream));
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_graph_ready(sofie_cuda_ctx *ctx, int *ready)
+{
+   SOFIE_REQUIRE(ctx && ready, "NULL argument");
+   *ready = ctx->graph_exec != nullptr;
+   return SOFIE_CUDA_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,442 @@
+// Memory-bound operators between the contractions: Relu, pooling, softmax, layout changes,
+// (de)quantisation and casts. One read and one write per element, 128-bit accesses where the
+// pointers allow it, grids sized as a multiple of the SM count.
+#include "common.cuh"
+
+#include <cuda_fp8.h>
+#include <cfloat>
+
+using namespace sofie;
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_for(size_t work_items, int per_block = kThreads, int waves = 8)
+{
+   size_t blocks = ceil_div<size_t>(work_items, per_block);
+   size_t cap = size_t(kNumSMs) * waves;
+   if (blocks > cap) blocks = cap;
+   if (blocks == 0) blocks = 1;
+   return (int)blocks;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---------------------------------------------------------------- relu ---------------------------
+__global__ void relu_f32_vec4(const float4 *__restrict__ X, float4 *__restrict__ Y, size_t n4)
+{
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+      float4 v = X[i];
+      v.x = relu_ref(v.x);
+      v.y = relu_ref(v.y);
+      v.z = relu_ref(v.z);
+      v.w = relu_ref(v.w);
+      Y[i] = v;
+   }
+}
+__global__ void relu_f32_scalar(const float *__restrict__ X, float *__restrict__ Y, size_t begin, size_t n)
+{
+   for (size_t i = begin + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+      Y[i] = relu_ref(X[i]);
+}
+
+// ---------------------------------------------------------------- pooling ------------------------
+template <bool NHWC>
+__global__ void pool2d_f32_kernel(sofie_pool2d_desc d, int oH, int oW, const float *__restrict__ X,
+                                  float *__restrict__ Y)
+{
+   const size_t total = (size_t)d.N * d.C * oH * oW;
+   const bool do_pad = d.pads[0] || d.pads[1] || d.pads[2] || d.pads[3];
+   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+        idx += (size_t)gridDim.x * blockDim.x) {
+      int n, c, oh, ow;
+      size_t t = idx;
+      if (NHWC) {
+         c = t % d.C; t /= d.C;
+         ow = t % oW; t /= oW;
+         oh = t % oH; n = t / oH;
+      } else {
+         ow = t % oW; t /= oW;
+         oh = t % oH; t /= oH;
+         c = t % d.C; n = t / d.C;
+      }
+      const int i0 = -d.pads[0] + oh * d.stride_h, j0 = -d.pads[2] + ow * d.stride_w;
+      float value = d.mode == 0 ? -INFINITY : 0.f;
+      int nsum = (d.count_include_pad || !do_pad) ? d.kH * d.kW : 0;
+      for (int l = i0; l < i0 + d.kH; l++) {
+         if (l < 0 || l >= d.H) continue;
+         for (int m = j0; m < j0 + d.kW; m++) {
+            if (m < 0 || m >= d.W) continue;
+            size_t xi = NHWC ? (((size_t)n * d.H + l) * d.W + m) * d.C + c : (((size_t)n * d.C + c) * d.H + l) * d.W + m;
+            float v = X[xi];
+            if (d.mode == 0) {
+               if (v > value) value = v;
+            } else {
+               value += v;
+               if (!d.count_include_pad && do_pad) nsum++;
+            }
+         }
+      }
+      if (d.mode == 1) value /= (float)nsum;
+      Y[idx] = value;
+   }
+}
+
+template <bool NHWC>
+__global__ void maxpool2d_u8_kernel(int N, int C, int H, int W, int kH, int kW, int sh, int sw, int oH, int oW,
+                                    const uint8_t *__restrict__ X, uint8_t *__restrict__ Y)
+{
+   const size_t total = (size_t)N * C * oH * oW;
+   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total;
+        idx += (size_t)gridDim.x * blockDim.x) {
+      int n, c, oh, ow;
+      size_t t = idx;
+      if (NHWC) {
+         c = t % C; t /= C;
+         ow = t % oW; t /= oW;
+         oh = t % oH; n = t / oH;
+      } else {
+         ow = t % oW; t /= oW;
+         oh = t % oH; t /= oH;
+         c = t % C; n = t / C;
+      }
+      unsigned v = 0;
+      for (int l = oh * sh; l < oh * sh + kH; l++)
+         for (int m = ow * sw; m < ow * sw + kW; m++) {
+            size_t xi = NHWC ? (((size_t)n * H + l) * W + m) * C + c : (((size_t)n * C + c) * H + l) * W + m;
+            v = max(v, (unsigned)X[xi]);
+         }
+      Y[idx] = (uint8_t)v;
+   }
+}
+
+// ---------------------------------------------------------------- softmax ------------------------
+// inner == 1: one warp per row, values kept in registers when the row is short, else re-read.
+__global__ void softmax_rows_kernel(const float *__restrict__ X, float *__restrict__ Y, size_t rows, size_t len)
+{
+   const int lane = threadIdx.x & 31;
+   const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+   const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+   for (size_t r = warp; r < rows; r += nwarps) {
+      const float *x = X + r * len;
+      float *y = Y + r * len;
+      float vmax = -INFINITY;
+      for (size_t i = lane; i < len; i += 32) vmax = fmaxf(vmax, x[i]);
+      for (int o = 16; o; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+      float sum = 0.f;
+      for (size_t i = lane; i < len; i += 32) {
+         float e = expf(x[i] - vmax);
+         y[i] = e;
+         sum += e;
+      }
+      for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      for (size_t i = lane; i < len; i += 32) y[i] = y[i] / sum;
+   }
+}
+// inner > 1: one thread per (outer, inner) line, strided walk; neighbouring threads touch
+// neighbouring addresses, so the accesses stay coalesced.
+__global__ void softmax_strided_kernel(const float *__restrict__ X, float *__restrict__ Y, size_t outer, size_t len,
+                                       size_t inner)
+{
+   const size_t lines = outer * inner;
+   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < lines;
+        idx += (size_t)gridDim.x * blockDim.x) {
+      size_t o = idx / inner, in = idx % inner;
+      const float *x = X + o * len * inner + in;
+      float *y = Y + o * len * inner + in;
+      float vmax = x[0];
+      for (size_t i = 1; i < len; i++) vmax = fmaxf(vmax, x[i * inner]);
+      float sum = 0.f;
+      for (size_t i = 0; i < len; i++) {
+         float e = expf(x[i * inner] - vmax);
+         y[i * inner] = e;
+         sum += e;
+      }
+      for (size_t i = 0; i < len; i++) y[i * inner] = y[i * inner] / sum;
+   }
+}
+
+// ---------------------------------------------------------------- layout -------------------------
+// Tiled transpose of the [C, H*W] plane of every image: NCHW -> NHWC is a [C,P] -> [P,C] transpose.
+template <typename T>
+__global__ void transpose_batched_kernel(const T *__restrict__ in, T *__restrict__ out, int rows, int cols)
+{
+   __shared__ T tile[32][33];
+   const size_t img = blockIdx.z;
+   const T *src = in + img * (size_t)rows * cols;
+   T *dst = out + img * (size_t)rows * cols;
+   int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+   for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+      int r = r0 + j, c = c0 + threadIdx.x;
+      if (r < rows && c < cols) tile[j][threadIdx.x] = src[(size_t)r * cols + c];
+   }
+   __syncthreads();
+   for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+      int c = c0 + j, r = r0 + threadIdx.x;
+      if (r < rows && c < cols) dst[(size_t)c * rows + r] = tile[threadIdx.x][j];
+   }
+}
+
+template <typename T>
+int launch_transpose(cudaStream_t s, const T *in, T *out, int batch, int rows, int cols)
+{
+   if (batch <= 0 || rows <= 0 || cols <= 0) return SOFIE_CUDA_OK;
+   SOFIE_REQUIRE(batch <= 65535 * 64, "batch too large for transpose");
+   // gridDim.z is limited to 65535: fold the batch in chunks
+   for (int b0 = 0; b0 < batch; b0 += 65535) {
+      int nb = batch - b0 < 65535 ? batch - b0 : 65535;
+      dim3 grid(ceil_div(cols, 32), ceil_div(rows, 32), nb), block(32, 8);
+      transpose_batched_kernel<T><<<grid, block, 0, s>>>(in + (size_t)b0 * rows * cols, out + (size_t)b0 * rows * cols,
+                                                         rows, cols);
+   }
+   SOFIE_LAUNCH_CHECK("transpose_batched_kernel");
+   return SOFIE_CUDA_OK;
+}
+
+// ---------------------------------------------------------------- (de)quantise, casts ------------
+__device__ __forceinline__ uint8_t quant_u8(float x, float scale, int zp)
+{
+   float r = rintf(__fdiv_rn(x, scale));
+   r = fminf(fmaxf(r, (float)(0 - zp)), (float)(255 - zp));
+   return (uint8_t)(__float2int_rn(r) + zp);
+}
+
+__global__ void quantize_u8_kernel(const float *__restrict__ X, uint8_t *__restrict__ Y, size_t n, float scale, int zp,
+                                   bool vec)
+{
+   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
+   size_t n4 = vec ? n / 4 : 0;
+   for (size_t i = tid; i < n4; i += nthreads) {
+      float4 v = reinterpret_cast<const float4 *>(X)[i];
+      uchar4 q = make_uchar4(quant_u8(v.x, scale, zp), quant_u8(v.y, scale, zp), quant_u8(v.z, scale, zp),
+                             quant_u8(v.w, scale, zp));
+      reinterpret_cast<uchar4 *>(Y)[i] = q;
+   }
+   for (size_t i = n4 * 4 + tid; i < n; i += nthreads) Y[i] = quant_u8(X[i], scale, zp);
+}
+
+__global__ void dequantize_u8_kernel(const uint8_t *__restrict__ X, float *__restrict__ Y, size_t n, float scale,
+                                     int zp, bool vec)
+{
+   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
+   size_t n4 = vec ? n / 4 : 0;
+   for (size_t i = tid; i < n4; i += nthreads) {
+      uchar4 q = reinterpret_cast<const uchar4 *>(X)[i];
+      float4 v = make_float4(__fmul_rn((float)((int)q.x - zp), scale), __fmul_rn((float)((int)q.y - zp), scale),
+                             __fmul_rn((float)((int)q.z - zp), scale), __fmul_rn((float)((int)q.w - zp), scale));
+      reinterpret_cast<float4 *>(Y)[i] = v;
+   }
+   for (size_t i = n4 * 4 + tid; i < n; i += nthreads) Y[i] = __fmul_rn((float)((int)X[i] - zp), scale);
+}
+
+__device__ __forceinline__ uint8_t to_e4m3(float x)
+{
+   return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+
+template <typename In>
+__global__ void quantize_e4m3_kernel(const In *__restrict__ X, uint8_t *__restrict__ Y, size_t n, float scale)
+{
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+      float x;
+      if constexpr (sizeof(In) == 2) x = bf16_to_f32(X[i]);
+      else x = X[i];
+      Y[i] = to_e4m3(__fdiv_rn(x, scale));
+   }
+}
+
+__global__ void cast_bf16_f32_kernel(const uint16_t *__restrict__ X, float *__restrict__ Y, size_t n)
+{
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+      Y[i] = bf16_to_f32(X[i]);
+}
+__global__ void cast_f32_bf16_kernel(const float *__restrict__ X, uint16_t *__restrict__ Y, size_t n)
+{
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+      Y[i] = f32_to_bf16_rne(X[i]);
+}
+
+// |x| as an unsigned integer orders like the float for non-NaN values, so atomicMax on the bit
+// pattern gives the exact maximum without a second pass.
+__global__ void amax_f32_kernel(const float *__restrict__ X, size_t n, unsigned *__restrict__ out)
+{
+   unsigned m = 0;
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+      unsigned u = __float_as_uint(X[i]) & 0x7FFFFFFFu;
+      if (u <= 0x7F800000u) m = max(m, u);
+   }
+   for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+   if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
+} // namespace
+
+extern "C" {
+
+int sofie_cuda_relu_f32(void *stream, const float *X, float *Y, size_t n)
+{
+   SOFIE_REQUIRE(X && Y, "NULL tensor");
+   if (n == 0) return SOFIE_CUDA_OK;
+   cudaStream_t s = as_stream(stream);
+   size_t done = 0;
+   if (aligned16(X) && aligned16(Y) && n >= 4) {
+      size_t n4 = n / 4;
+      relu_f32_vec4<<<grid_for(n4), kThreads, 0, s>>>(reinterpret_cast<const float4 *>(X),
+                                                       reinterpret_cast<float4 *>(Y), n4);
+      done = n4 * 4;
+   }
+   if (done < n) relu_f32_scalar<<<grid_for(n - done), kThreads, 0, s>>>(X, Y, done, n);
+   SOFIE_LAUNCH_CHECK("relu_f32");
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_pool2d_f32(void *stream, const sofie_pool2d_desc *d, const float *X, float *Y)
+{
+   SOFIE_REQUIRE(d && X && Y, "NULL argument");
+   SOFIE_REQUIRE(d->mode == 0 || d->mode == 1, "pool mode must be 0 (max) or 1 (average)");
+   SOFIE_REQUIRE(d->N >= 0 && d->C > 0 && d->H > 0 && d->W > 0 && d->kH > 0 && d->kW > 0 && d->stride_h > 0 &&
+                    d->stride_w > 0,
+                 "bad pooling shape");
+   // number of window positions, as the reference's loops count them (ROperator_Pool.hxx:371-373)
+   const int hspan = d->H + d->pads[0] + d->pads[1] - d->kH + 1, wspan = d->W + d->pads[2] + d->pads[3] - d->kW + 1;
+   SOFIE_REQUIRE(hspan > 0 && wspan > 0, "pooling window larger than padded input");
+   const int oH = ceil_div(hspan, d->stride_h), oW = ceil_div(wspan, d->stride_w);
+   size_t total = (size_t)d->N * d->C * oH * oW;
+   if (total == 0) return SOFIE_CUDA_OK;
+   cudaStream_t s = as_stream(stream);
+   if (d->layout == SOFIE_LAYOUT_NHWC)
+      pool2d_f32_kernel<true><<<grid_for(total), kThreads, 0, s>>>(*d, oH, oW, X, Y);
+   else
+      pool2d_f32_kernel<false><<<grid_for(total), kThreads, 0, s>>>(*d, oH, oW, X, Y);
+   SOFIE_LAUNCH_CHECK("pool2d_f32_kernel");
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_maxpool2d_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W,
+                            int32_t kH, int32_t kW, int32_t sh, int32_t sw, int32_t layout)
+{
+   SOFIE_REQUIRE(X && Y, "NULL tensor");
+   SOFIE_REQUIRE(N >= 0 && C > 0 && H >= kH && W >= kW && kH > 0 && kW > 0 && sh > 0 && sw > 0, "bad pooling shape");
+   const int oH = (H - kH) / sh + 1, oW = (W - kW) / sw + 1;
+   size_t total = (size_t)N * C * oH * oW;
+   if (total == 0) return SOFIE_CUDA_OK;
+   cudaStream_t s = as_stream(stream);
+   if (layout == SOFIE_LAYOUT_NHWC)
+      maxpool2d_u8_kernel<true><<<grid_for(total), kThreads, 0, s>>>(N, C, H, W, kH, kW, sh, sw, oH, oW, X, Y);
+   else
+      maxpool2d_u8_kernel<false><<<grid_for(total), kThreads, 0, s>>>(N, C, H, W, kH, kW, sh, sw, oH, oW, X, Y);
+   SOFIE_LAUNCH_CHECK("maxpool2d_u8_kernel");
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_softmax_f32(void *stream, const float *X, float *Y, size_t outer, size_t axis_len, size_t inner)
+{
+   SOFIE_REQUIRE(X && Y, "NULL tensor");
+   SOFIE_REQUIRE(axis_len > 0, "softmax along an axis with zero elements");
+   if (outer == 0 || inner == 0) return SOFIE_CUDA_OK;
+   cudaStream_t s = as_stream(stream);
+   if (inner == 1)
+      softmax_rows_kernel<<<grid_for(outer * 32), kThreads, 0, s>>>(X, Y, outer, axis_len);
+   else
+      softmax_strided_kernel<<<grid_for(outer * inner), kThreads, 0, s>>>(X, Y, outer, axis_len, inner);
+   SOFIE_LAUNCH_CHECK("softmax");
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_transpose_f32(void *stream, const float *in, float *out, int32_t rows, int32_t cols)
+{
+   SOFIE_REQUIRE(in && out && rows >= 0 && cols >= 0, "bad transpose arguments");
+   return launch_transpose<float>(as_stream(stream), in, out, 1, rows, cols);
+}
+int sofie_cuda_transpose_i8(void *stream, const int8_t *in, int8_t *out, int32_t rows, int32_t cols)
+{
+   SOFIE_REQUIRE(in && out && rows >= 0 && cols >= 0, "bad transpose arguments");
+   return launch_transpose<int8_t>(as_stream(stream), in, out, 1, rows, cols);
+}
+int sofie_cuda_nchw_to_nhwc_f32(void *stream, const float *X, float *Y, int32_t N, int32_t C, int32_t H, int32_t W)
+{
+   SOFIE_REQUIRE(X && Y && N >= 0 && C > 0 && H > 0 && W > 0, "bad layout-change arguments");
+   return launch_transpose<float>(as_stream(stream), X, Y, N, C, H * W);
+}
+int sofie_cuda_nhwc_to_nchw_f32(void *stream, const float *X, float *Y, int32_t N, int32_t C, int32_t H, int32_t W)
+{
+   SOFIE_REQUIRE(X && Y && N >= 0 && C > 0 && H > 0 && W > 0, "bad layout-change arguments");
+   return launch_transpose<float>(as_stream(stream), X, Y, N, H * W, C);
+}
+int sofie_cuda_nchw_to_nhwc_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W)
+{
+   SOFIE_REQUIRE(X && Y && N >= 0 && C > 0 && H > 0 && W > 0, "bad layout-change arguments");
+   return launch_transpose<uint8_t>(as_stream(stream), X, Y, N, C, H * W);
+}
+int sofie_cuda_nhwc_to_nchw_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W)
+{
+   SOFIE_REQUIRE(X && Y && N >= 0 && C > 0 && H > 0 && W > 0, "bad layout-change arguments");
+   return launch_transpose<uint8_t>(as_stream(stream), X, Y, N, H * W, C);
+}
+
+int sofie_cuda_quantize_u8(void *stream, const float *X, uint8_t *Y, size_t n, float scale, int32_t zp)
+{
+   SOFIE_REQUIRE(X && Y, "NULL tensor");
+   SOFIE_REQUIRE(scale > 0.f && zp >= 0 && zp <= 255, "bad quantisation parameters");
+   if (n == 0) return SOFIE_CUDA_OK;
+   bool vec = aligned16(X) && (reinterpret_cast<uintptr_t>(Y) & 3) == 0;
+   quantize_u8_kernel<<<grid_for(vec ? n / 4 + 1 : n), kThreads, 0, as_stream(stream)>>>(X, Y, n, scale, zp, vec);
+   SOFIE_LAUNCH_CHECK("quantize_u8_kernel");
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_dequantize_u8(void *stream, const uint8_t *X, float *Y, size_t n, float scale, int32_t zp)
+{
+   SOFIE_REQUIRE(X && Y, "NULL tensor");
+   if (n == 0) return SOFIE_CUDA_OK;
+   bool vec = aligned16(Y) && (reinterpret_cast<uintptr_t>(X) & 3) == 0;
+   dequantize_u8_kernel<<<grid_for(vec ? n / 4 + 1 : n), kThreads, 0, as_stream(stream)>>>(X, Y, n, scale, zp, vec);
+   SOFIE_LAUNCH_CHECK("dequantize_u8_kernel");
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_quantize_e4m3_f32(void *stream, const float *X, uint8_t *Y, size_t n, float scale)
+{
+   SOFIE_REQUIRE(X && Y && scale > 0.f, "bad arguments");
+   if (n == 0) return SOFIE_CUDA_OK;
+   quantize_e4m3_kernel<float><<<grid_for(n), kThreads, 0, as_stream(stream)>>>(X, Y, n, scale);
+   SOFIE_LAUNCH_CHECK("quantize_e4m3_kernel");
+   return SOFIE_CUDA_OK;
+}
+int sofie_cuda_quantize_e4m3_bf16(void *stream, const uint16_t *X, uint8_t *Y, size_t n, float scale)
+{
+   SOFIE_REQUIRE(X && Y && scale > 0.f, "bad arguments");
+   if (n == 0) return SOFIE_CUDA_OK;
+   quantize_e4m3_kernel<uint16_t><<<grid_for(n), kThreads, 0, as_stream(stream)>>>(X, Y, n, scale);
+   SOFIE_LAUNCH_CHECK("quantize_e4m3_kernel");
+   return SOFIE_CUDA_OK;
+}
+int sofie_cuda_cast_bf16_f32(void *stream, const uint16_t *X, float *Y, size_t n)
+{
+   SOFIE_REQUIRE(X && Y, "NULL tensor");
+   if (n == 0) return SOFIE_CUDA_OK;
+   cast_bf16_f32_kernel<<<grid_for(n), kThreads, 0, as_stream(stream)>>>(X, Y, n);
+   SOFIE_LAUNCH_CHECK("cast_bf16_f32_kernel");
+   return SOFIE_CUDA_OK;
+}
+int sofie_cuda_cast_f32_bf16(void *stream, const float *X, uint16_t *Y, size_t n)
+{
+   SOFIE_REQUIRE(X && Y, "NULL tensor");
+   if (n == 0) return SOFIE_CUDA_OK;
+   cast_f32_bf16_kernel<<<grid_for(n), kThreads, 0, as_stream(stream)>>>(X, Y, n);
+   SOFIE_LAUNCH_CHECK("cast_f32_bf16_kernel");
+   return SOFIE_CUDA_OK;
+}
+int sofie_cuda_amax_f32(void *stream, const float *X, size_t n, float *amax_device)
+{
+   SOFIE_REQUIRE(X && amax_device, "NULL tensor");
+   cudaStream_t s = as_stream(stream);
+   SOFIE_CUDA_TRY(cudaMemsetAsync(amax_device, 0, sizeof(float), s));
+   if (n == 0) return SOFIE_CUDA_OK;
+   amax_f32_kernel<<<grid_for(n), kThreads, 0, s>>>(X, n, reinterpret_cast<unsigned *>(amax_device));
+   SOFIE_LAUNCH_CHECK("amax_f32_kernel");
+   return SOFIE_CUDA_OK;
+}
+
+} // extern "C"

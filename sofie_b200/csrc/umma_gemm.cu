@@ -1,0 +1,421 @@
+// Tensor-core GEMM for sm_100a: D[M,N] = A[M,K] * B[N,K]^T with both operands K-major in global
+// memory, TMA-tiled into 128B-swizzled shared memory, multiplied by tcgen05.mma into a TMEM
+// accumulator and finished by a fused epilogue. Three instantiations share one main loop:
+//   kTF32 : fp32 in / fp32 out. Each operand tile is split on chip into hi = tf32(x) and
+//           lo = x - hi, and the product is accumulated as lo*hi + hi*lo + hi*hi in fp32 (3xTF32).
+//   kI8   : uint8 x int8 -> int32, epilogue requantises to uint8.
+//   kF8   : E4M3 x E4M3 -> fp32, epilogue scales, adds bias, Relu, writes bf16 and/or E4M3.
+//
+// CTA = 6 warps: warp 0 issues TMA, warp 1 allocates TMEM and issues MMA, warps 2-5 split the
+// fp32 tiles (kTF32 only) during the main loop and afterwards drain the accumulator (each warp owns
+// the 32 TMEM lanes its warp id modulo 4 selects). One CTA computes one 128 x BN output tile.
+#include "umma.cuh"
+#include "contract.cuh"
+
+#include <cuda_fp8.h>
+#include <mutex>
+
+namespace sofie {
+namespace umma {
+
+EncodeTiledFn encode_tiled_fn()
+{
+   static EncodeTiledFn fn = nullptr;
+   static std::once_flag once;
+   std::call_once(once, [] {
+      void *p = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+          q == cudaDriverEntryPointSuccess)
+         fn = reinterpret_cast<EncodeTiledFn>(p);
+      else
+         cudaGetLastError();
+   });
+   return fn;
+}
+
+int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank, const void *base, const uint64_t *dims,
+                    const uint64_t *strides_bytes, const uint32_t *box, int swizzle_bytes)
+{
+   EncodeTiledFn fn = encode_tiled_fn();
+   if (!fn) return fail(SOFIE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+   cuuint64_t gdims[5], gstrides[5];
+   cuuint32_t gbox[5], estrides[5];
+   for (int i = 0; i < rank; i++) {
+      gdims[i] = dims[i];
+      gbox[i] = box[i];
+      estrides[i] = 1;
+      if (i > 0) gstrides[i - 1] = strides_bytes[i - 1];
+   }
+   CUtensorMapSwizzle sw = swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                           : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                           : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                 : CU_TENSOR_MAP_SWIZZLE_NONE;
+   CUresult r = fn(map, dtype, (cuuint32_t)rank, const_cast<void *>(base), gdims, gstrides, gbox, estrides,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+   if (r != CUDA_SUCCESS) return fail(SOFIE_CUDA_ERR_INVALID, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+   return SOFIE_CUDA_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+struct GemmEpilogue {
+   // kTF32
+   float alpha, beta;
+   const float *C;
+   int bias_kind;
+   float *Yf;
+   // kI8
+   const float *mult;
+   const int32_t *corr;
+   int y_zp;
+   uint8_t *Yu8;
+   // kF8
+   float scale, q_scale;
+   const float *bias;
+   uint16_t *Ybf16;
+   uint8_t *Yq;
+   // all
+   int relu;
+};
+
+constexpr int kBM = 128;        // rows of the output tile = TMEM lanes
+constexpr int kStageK = 128;    // bytes of K per pipeline stage = one 128B swizzle row
+constexpr int kMmaK = 32;       // bytes of K per tcgen05.mma
+constexpr int kGemmThreads = 192;
+
+template <int KIND, int BN>
+struct GemmSmem {
+   static constexpr int kATile = kBM * kStageK;                  // 16 KB
+   static constexpr int kBTile = BN * kStageK;
+   static constexpr int kCopies = (KIND == kTF32) ? 2 : 1;       // hi and lo
+   static constexpr int kStageBytes = kCopies * (kATile + kBTile);
+   static constexpr int stages(int budget) { return budget / kStageBytes; }
+};
+
+template <int KIND, int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmEpilogue ep,
+                 int M, int N, int K, uint32_t *status)
+{
+   using L = GemmSmem<KIND, BN>;
+   constexpr int ES = (KIND == kTF32) ? 4 : 1;           // element size in bytes
+   constexpr int KE = kStageK / ES;                      // elements of K per stage
+   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;     // power of two >= 32
+   extern __shared__ unsigned char smem_raw[];
+   // 1024-byte alignment: the 128B swizzle pattern repeats every 1024 bytes and is address based.
+   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+   __shared__ uint64_t full_bar[STAGES], conv_bar[STAGES], empty_bar[STAGES], accum_bar;
+   __shared__ uint32_t tmem_base_holder;
+   __shared__ volatile uint32_t abort_flag;
+
+   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+   const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
+   const int num_kb = (K * ES + kStageK - 1) / kStageK;
+
+   auto a_hi = [&](int s) { return smem + (size_t)s * L::kStageBytes; };
+   auto b_hi = [&](int s) { return smem + (size_t)s * L::kStageBytes + L::kATile; };
+   auto a_lo = [&](int s) { return smem + (size_t)s * L::kStageBytes + L::kATile + L::kBTile; };
+   auto b_lo = [&](int s) { return smem + (size_t)s * L::kStageBytes + 2 * L::kATile + L::kBTile; };
+
+   if (threadIdx.x == 0) {
+      for (int s = 0; s < STAGES; s++) {
+         mbar_init(&full_bar[s], 1);
+         mbar_init(&conv_bar[s], 128);
+         mbar_init(&empty_bar[s], 1);
+      }
+      mbar_init(&accum_bar, 1);
+      abort_flag = 0;
+      fence_mbar_init();
+      prefetch_tensormap(&tmA);
+      prefetch_tensormap(&tmB);
+   }
+   if (warp == 1) {
+      tmem_alloc(&tmem_base_holder, TMEM_COLS);
+      tmem_relinquish();
+   }
+   tc_fence_before();
+   __syncthreads();
+   tc_fence_after();
+   const uint32_t tmem_base = tmem_base_holder;
+
+   if (warp == 0) {
+      // ---------------- TMA producer ----------------
+      if (lane == 0) {
+         for (int kb = 0; kb < num_kb; kb++) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, kb)) break;
+            mbar_expect_tx(&full_bar[s], L::kATile + L::kBTile);
+            tma_load_2d(a_hi(s), &tmA, kb * KE, m0, &full_bar[s]);
+            tma_load_2d(b_hi(s), &tmB, kb * KE, n0, &full_bar[s]);
+         }
+      }
+   } else if (warp == 1) {
+      // ---------------- MMA issuer ----------------
+      if (lane == 0) {
+         constexpr uint32_t idesc = make_idesc<KIND>(kBM, BN);
+         uint32_t accumulate = 0;
+         for (int kb = 0; kb < num_kb; kb++) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            bool ok = (KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, kb)
+                                      : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, kb);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t da = make_smem_desc(smem_u32(a_hi(s)), kStageK);
+            const uint64_t db = make_smem_desc(smem_u32(b_hi(s)), kStageK);
+#pragma unroll
+            for (int k = 0; k < kStageK / kMmaK; k++) {
+               // advancing K inside the swizzle row: +32 bytes = +2 in the (>>4) address field
+               const uint64_t koff = (uint64_t)(k * (kMmaK >> 4));
+               if constexpr (KIND == kTF32) {
+                  const uint64_t dal = make_smem_desc(smem_u32(a_lo(s)), kStageK);
+                  const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)), kStageK);
+                  tc_mma<KIND>(tmem_base, dal + koff, db + koff, idesc, accumulate);
+                  tc_mma<KIND>(tmem_base, da + koff, dbl + koff, idesc, 1);
+                  tc_mma<KIND>(tmem_base, da + koff, db + koff, idesc, 1);
+               } else {
+                  tc_mma<KIND>(tmem_base, da + koff, db + koff, idesc, accumulate);
+               }
+               accumulate = 1;
+            }
+            tc_commit(&empty_bar[s]); // the stage is free once these MMAs have read it
+         }
+         tc_commit(&accum_bar);
+      }
+   } else {
+      // ---------------- converter (kTF32) then epilogue: warps 2..5 ----------------
+      const int t = threadIdx.x - 64; // 0..127
+      if constexpr (KIND == kTF32) {
+         for (int kb = 0; kb < num_kb; kb++) {
+            const int s = kb % STAGES;
+            const uint32_t ph = (kb / STAGES) & 1;
+            if (!mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, kb)) break;
+            // The split is elementwise, so the swizzled placement does not matter: the lo tile is
+            // written at the same offsets as the hi tile. A and B tiles are contiguous.
+            float4 *hi = reinterpret_cast<float4 *>(a_hi(s));
+            float4 *lo = reinterpret_cast<float4 *>(a_lo(s));
+            constexpr int n4 = (L::kATile + L::kBTile) / 16;
+#pragma unroll 4
+            for (int i = t; i < n4; i += 128) {
+               float4 v = hi[i], h, l;
+               uint32_t u;
+               asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.x)); h.x = __uint_as_float(u); l.x = v.x - h.x;
+               asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.y)); h.y = __uint_as_float(u); l.y = v.y - h.y;
+               asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.z)); h.z = __uint_as_float(u); l.z = v.z - h.z;
+               asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.w)); h.w = __uint_as_float(u); l.w = v.w - h.w;
+               hi[i] = h;
+               lo[i] = l;
+            }
+            fence_proxy_async(); // make the generic-proxy writes visible to the tensor-core (async) proxy
+            mbar_arrive(&conv_bar[s]);
+         }
+      }
+      // ---- epilogue ----
+      if (mbar_wait(&accum_bar, 0, &abort_flag, status, kStatusWaitAccum, 0)) {
+         tc_fence_after();
+         const int lane_base = (warp & 3) * 32;
+         const int row = m0 + lane_base + lane;
+#pragma unroll 1
+         for (int c0 = 0; c0 < BN; c0 += 32) {
+            if (n0 + c0 >= N) break;
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
+            tmem_ld_wait();
+            if (row < M) {
+               const int col0 = n0 + c0;
+               const int ncols = min(32, N - col0);
+               if constexpr (KIND == kTF32) {
+                  float *y = ep.Yf + (size_t)row * N + col0;
+                  float v[32];
+#pragma unroll
+                  for (int j = 0; j < 32; j++) {
+                     float acc = ep.alpha * __uint_as_float(r[j]);
+                     if (j < ncols) {
+                        if (ep.bias_kind == 1) acc += ep.beta * ep.C[col0 + j];
+                        else if (ep.bias_kind == 2) acc += ep.beta * ep.C[(size_t)row * N + col0 + j];
+                     }
+                     v[j] = ep.relu ? relu_ref(acc) : acc;
+                  }
+                  if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+#pragma unroll
+                     for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                  } else {
+#pragma unroll
+                     for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
+                  }
+               } else if constexpr (KIND == kI8) {
+                  uint8_t *y = ep.Yu8 + (size_t)row * N + col0;
+                  uint32_t packed[8];
+#pragma unroll
+                  for (int j = 0; j < 32; j++) {
+                     int q = 0;
+                     if (j < ncols) {
+                        int acc = (int)r[j] + (ep.corr ? ep.corr[col0 + j] : 0);
+                        q = requant_u8(acc, ep.mult[col0 + j], ep.y_zp, ep.relu);
+                     }
+                     if ((j & 3) == 0) packed[j >> 2] = 0;
+                     packed[j >> 2] |= (uint32_t)q << (8 * (j & 3));
+                  }
+                  if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+                     *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                     *reinterpret_cast<uint4 *>(y + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                  } else {
+#pragma unroll
+                     for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
+                  }
+               } else {
+                  uint32_t hb[16], qb[8];
+#pragma unroll
+                  for (int j = 0; j < 32; j++) {
+                     uint16_t h = 0;
+                     uint8_t q = 0;
+                     if (j < ncols) {
+                        float y = __fmul_rn(__uint_as_float(r[j]), ep.scale);
+                        if (ep.bias) y = __fadd_rn(y, ep.bias[col0 + j]);
+                        if (ep.relu) y = relu_ref(y);
+                        h = f32_to_bf16_rne(y);
+                        if (ep.Yq)
+                           q = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(bf16_to_f32(h), ep.q_scale), __NV_SATFINITE, __NV_E4M3);
+                     }
+                     if ((j & 1) == 0) hb[j >> 1] = 0;
+                     hb[j >> 1] |= (uint32_t)h << (16 * (j & 1));
+                     if ((j & 3) == 0) qb[j >> 2] = 0;
+                     qb[j >> 2] |= (uint32_t)q << (8 * (j & 3));
+                  }
+                  if (ep.Ybf16) {
+                     uint16_t *y = ep.Ybf16 + (size_t)row * N + col0;
+                     if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                           reinterpret_cast<uint4 *>(y)[j] = make_uint4(hb[4 * j], hb[4 * j + 1], hb[4 * j + 2], hb[4 * j + 3]);
+                     } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint16_t)(hb[j >> 1] >> (16 * (j & 1)));
+                     }
+                  }
+                  if (ep.Yq) {
+                     uint8_t *y = ep.Yq + (size_t)row * N + col0;
+                     if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+                        *reinterpret_cast<uint4 *>(y) = make_uint4(qb[0], qb[1], qb[2], qb[3]);
+                        *reinterpret_cast<uint4 *>(y + 16) = make_uint4(qb[4], qb[5], qb[6], qb[7]);
+                     } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)(qb[j >> 2] >> (8 * (j & 3)));
+                     }
+                  }
+               }
+            }
+         }
+      }
+   }
+   // A wait only gives up after about a second, long after every copy and MMA this CTA issued has
+   // landed, so nothing is in flight when the TMEM columns are released below.
+   tc_fence_before();
+   __syncthreads();
+   if (warp == 1) {
+      tc_fence_after();
+      tmem_dealloc(tmem_base, TMEM_COLS);
+   }
+}
+
+// ------------------------------------------------------------------------------------------------
+template <int KIND, int BN, int STAGES>
+static int launch_one(cudaStream_t s, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmEpilogue &ep, int M,
+                      int N, int K)
+{
+   using L = GemmSmem<KIND, BN>;
+   constexpr int smem = STAGES * L::kStageBytes + 1024;
+   static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
+   auto kern = umma_gemm_kernel<KIND, BN, STAGES>;
+   static bool configured = false; // per instantiation; attribute is per device but set idempotently below
+   (void)configured;
+   SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+   uint32_t *status = device_status_word();
+   if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
+   dim3 grid(ceil_div(N, BN), ceil_div(M, kBM));
+   kern<<<grid, kGemmThreads, smem, s>>>(tmA, tmB, ep, M, N, K, status);
+   SOFIE_LAUNCH_CHECK("umma_gemm_kernel");
+   set_last_engine(SOFIE_ENGINE_TCGEN05);
+   return SOFIE_CUDA_OK;
+}
+
+template <int KIND>
+static int launch_umma_gemm(cudaStream_t s, const void *A, const void *B, const GemmEpilogue &ep, int M, int N, int K)
+{
+   constexpr int ES = (KIND == kTF32) ? 4 : 1;
+   if (M <= 0 || N <= 0 || K <= 0) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "empty GEMM");
+   if (((size_t)K * ES) % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+      return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "TMA needs 16-byte aligned rows (K*%d %% 16 == 0) and bases", ES);
+   const int BN = N <= 32 ? 32 : (N <= 64 ? 64 : ((KIND == kTF32 || N <= 128) ? 128 : 256));
+   CUtensorMap tmA, tmB;
+   const CUtensorMapDataType dt = (KIND == kTF32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+   uint64_t dimsA[2] = {(uint64_t)K, (uint64_t)M}, dimsB[2] = {(uint64_t)K, (uint64_t)N};
+   uint64_t stride[1] = {(uint64_t)K * ES};
+   uint32_t boxA[2] = {(uint32_t)(kStageK / ES), (uint32_t)kBM}, boxB[2] = {(uint32_t)(kStageK / ES), (uint32_t)BN};
+   int rc = make_tensor_map(&tmA, dt, 2, A, dimsA, stride, boxA, 128);
+   if (rc) return rc;
+   rc = make_tensor_map(&tmB, dt, 2, B, dimsB, stride, boxB, 128);
+   if (rc) return rc;
+   if constexpr (KIND == kTF32) {
+      switch (BN) {
+      case 32: return launch_one<KIND, 32, 4>(s, tmA, tmB, ep, M, N, K);
+      case 64: return launch_one<KIND, 64, 4>(s, tmA, tmB, ep, M, N, K);
+      default: return launch_one<KIND, 128, 3>(s, tmA, tmB, ep, M, N, K);
+      }
+   } else {
+      switch (BN) {
+      case 32: return launch_one<KIND, 32, 6>(s, tmA, tmB, ep, M, N, K);
+      case 64: return launch_one<KIND, 64, 6>(s, tmA, tmB, ep, M, N, K);
+      case 128: return launch_one<KIND, 128, 6>(s, tmA, tmB, ep, M, N, K);
+      default: return launch_one<KIND, 256, 4>(s, tmA, tmB, ep, M, N, K);
+      }
+   }
+}
+
+} // namespace umma
+
+// Entry points used by api.cu. Each returns SOFIE_CUDA_ERR_UNSUPPORTED when the shape does not fit
+// the tensor-core kernel, and the caller then takes the CUDA-core kernel.
+int launch_gemm_f32_umma(cudaStream_t s, const sofie_gemm_f32_desc &d, const float *A, const float *B, const float *C,
+                         float *Y)
+{
+   if (d.transA || !d.transB) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "tensor-core GEMM takes A[M,K] and B[N,K]");
+   umma::GemmEpilogue ep = {};
+   ep.alpha = d.alpha;
+   ep.beta = d.beta;
+   ep.C = C;
+   ep.bias_kind = d.bias_kind;
+   ep.Yf = Y;
+   ep.relu = d.relu;
+   return umma::launch_umma_gemm<umma::kTF32>(s, A, B, ep, d.M, d.N, d.K);
+}
+
+int launch_qgemm_umma(cudaStream_t s, const sofie_qgemm_desc &d, const uint8_t *A, const int8_t *W, const float *mult,
+                      const int32_t *corr, uint8_t *Y)
+{
+   if (!d.w_is_nk) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "tensor-core GEMM takes W as [N,K]");
+   umma::GemmEpilogue ep = {};
+   ep.mult = mult;
+   ep.corr = corr;
+   ep.y_zp = d.y_zp;
+   ep.Yu8 = Y;
+   ep.relu = d.relu;
+   return umma::launch_umma_gemm<umma::kI8>(s, A, W, ep, d.M, d.N, d.K);
+}
+
+int launch_gemm_e4m3_umma(cudaStream_t s, const sofie_fp8_gemm_desc &d, const uint8_t *A, const uint8_t *W,
+                          const float *bias, uint16_t *Ybf16, uint8_t *Yq)
+{
+   umma::GemmEpilogue ep = {};
+   ep.scale = d.a_scale * d.w_scale;
+   ep.q_scale = d.q_scale;
+   ep.bias = bias;
+   ep.Ybf16 = Ybf16;
+   ep.Yq = Yq;
+   ep.relu = d.relu;
+   return umma::launch_umma_gemm<umma::kF8>(s, A, W, ep, d.M, d.N, d.K);
+}
+
+} // namespace sofie
