@@ -150,9 +150,11 @@ int sofie_cuda_conv2d_pack_f32(void *stream, const sofie_conv2d_desc *desc, cons
 /* y = x > 0 ? x : 0 (reference: ROperator_Relu.hxx:54-66). In place allowed. */
 int sofie_cuda_relu_f32(void *stream, const float *X, float *Y, size_t n);
 
-/* MaxPool / AveragePool 2-D (reference: ROperator_Pool.hxx:266-476). `pads` are used exactly as
- * the reference uses the ONNX attribute: rows span [-pads[0], H+pads[1]-kH], columns
- * [-pads[2], W+pads[3]-kW] (ROperator_Pool.hxx:283-289). */
+/* MaxPool / AveragePool 2-D (reference: ROperator_Pool.hxx:266-476). `pads` =
+ * (h_begin, w_begin, h_end, w_end) as in ONNX and in the reference's shape inference
+ * (ROperator_Pool.hxx:172-189). The reference's loop bounds read the vector in another order
+ * (ROperator_Pool.hxx:283-289); both readings agree when the four pads are equal, the only padded
+ * case in which the reference stays inside its output tensor. */
 typedef struct sofie_pool2d_desc {
    int32_t mode;            /* 0 max, 1 average                                            */
    int32_t N, C, H, W;

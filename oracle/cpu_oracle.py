@@ -91,8 +91,8 @@ def relu_f32(X):
 def pool2d_f32(X, mode=0, kernel=(2, 2), stride=(2, 2), pads=(0, 0, 0, 0), count_include_pad=0):
     X = _f(X)
     N, Cc, H, W = X.shape
-    oH = -(-(H + pads[0] + pads[1] - kernel[0] + 1) // stride[0])
-    oW = -(-(W + pads[2] + pads[3] - kernel[1] + 1) // stride[1])
+    oH = -(-(H + pads[0] + pads[2] - kernel[0] + 1) // stride[0])
+    oW = -(-(W + pads[1] + pads[3] - kernel[1] + 1) // stride[1])
     Y = np.empty((N, Cc, oH, oW), np.float32)
     p = (C.c_int * 4)(*pads)
     lib().oracle_pool2d_f32(C.c_int(mode), C.c_size_t(N * Cc), C.c_int(H), C.c_int(W), C.c_int(kernel[0]),

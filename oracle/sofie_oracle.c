@@ -203,15 +203,17 @@ ORACLE_API void oracle_relu_f32(const float *X, size_t n, float *Y)
 }
 
 /* 2-D pooling as emitted by ROperator_Pool.hxx:371-416. NC = N*C planes of [H,W].
- * The window's lower bounds run i in [-pads[0], H + pads[1] - kh + 1) step sh and
- * j in [-pads[2], W + pads[3] - kw + 1) step sw: the reference indexes the ONNX pads attribute
- * as (h_begin, h_end, w_begin, w_end) (ROperator_Pool.hxx:283-289); that quirk is kept.
+ * pads = (h_begin, w_begin, h_end, w_end) as in ONNX and in the reference's shape inference
+ * (ROperator_Pool.hxx:172-189). The reference's loop bounds read the same vector as
+ * (h_begin, h_end, w_begin, w_end) (ROperator_Pool.hxx:283-289); the two readings agree whenever
+ * the four pads are equal -- the only padded case the reference handles without writing past its
+ * output tensor -- and the shape-inference reading is the one restated here.
  * mode 0 = max (init -INFINITY, out-of-range taps skipped), 1 = average. */
 ORACLE_API void oracle_pool2d_f32(int mode, size_t NC, int H, int W, int kh, int kw, const int *pads, int sh, int sw,
                                   int count_include_pad, const float *X, float *Y)
 {
-   const int hmin = -pads[0], hmax = H + pads[1] - kh + 1;
-   const int wmin = -pads[2], wmax = W + pads[3] - kw + 1;
+   const int hmin = -pads[0], hmax = H + pads[2] - kh + 1;
+   const int wmin = -pads[1], wmax = W + pads[3] - kw + 1;
    const int do_pad = pads[0] || pads[1] || pads[2] || pads[3];
    size_t out = 0;
    for (size_t n = 0; n < NC; n++) {

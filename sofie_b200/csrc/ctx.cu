@@ -14,7 +14,14 @@ namespace sofie {
 
 static thread_local char g_last_error[512] = "";
 static thread_local int g_last_engine = SOFIE_ENGINE_NONE;
-static int g_forced_engine = 0;
+// Initial kernel-family choice from the environment (SOFIE_CUDA_ENGINE = 0, 1 or 2), for A/B runs.
+static int initial_engine()
+{
+   const char *env = std::getenv("SOFIE_CUDA_ENGINE");
+   int v = env ? std::atoi(env) : 0;
+   return (v >= 0 && v <= 2) ? v : 0;
+}
+static int g_forced_engine = initial_engine();
 
 char *last_error_buffer() { return g_last_error; }
 

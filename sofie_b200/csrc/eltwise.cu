@@ -61,7 +61,7 @@ __global__ void pool2d_f32_kernel(sofie_pool2d_desc d, int oH, int oW, const flo
          oh = t % oH; t /= oH;
          c = t % d.C; n = t / d.C;
       }
-      const int i0 = -d.pads[0] + oh * d.stride_h, j0 = -d.pads[2] + ow * d.stride_w;
+      const int i0 = -d.pads[0] + oh * d.stride_h, j0 = -d.pads[1] + ow * d.stride_w;
       float value = d.mode == 0 ? -INFINITY : 0.f;
       int nsum = (d.count_include_pad || !do_pad) ? d.kH * d.kW : 0;
       for (int l = i0; l < i0 + d.kH; l++) {
@@ -298,8 +298,8 @@ int sofie_cuda_pool2d_f32(void *stream, const sofie_pool2d_desc *d, const float 
    SOFIE_REQUIRE(d->N >= 0 && d->C > 0 && d->H > 0 && d->W > 0 && d->kH > 0 && d->kW > 0 && d->stride_h > 0 &&
                     d->stride_w > 0,
                  "bad pooling shape");
-   // number of window positions, as the reference's loops count them (ROperator_Pool.hxx:371-373)
-   const int hspan = d->H + d->pads[0] + d->pads[1] - d->kH + 1, wspan = d->W + d->pads[2] + d->pads[3] - d->kW + 1;
+   // number of window positions, as the reference's shape inference counts them (ROperator_Pool.hxx:172-189)
+   const int hspan = d->H + d->pads[0] + d->pads[2] - d->kH + 1, wspan = d->W + d->pads[1] + d->pads[3] - d->kW + 1;
    SOFIE_REQUIRE(hspan > 0 && wspan > 0, "pooling window larger than padded input");
    const int oH = ceil_div(hspan, d->stride_h), oW = ceil_div(wspan, d->stride_w);
    size_t total = (size_t)d->N * d->C * oH * oW;

@@ -92,8 +92,8 @@ def relu_f32(X, out=None):
 def pool2d_f32(X, *, mode=0, kernel=(2, 2), stride=(2, 2), pads=(0, 0, 0, 0), count_include_pad=0,
                layout=LAYOUT_NCHW, shape=None):
     N, Cc, H, W = shape if shape is not None else X.shape
-    oH = -(-(H + pads[0] + pads[1] - kernel[0] + 1) // stride[0])
-    oW = -(-(W + pads[2] + pads[3] - kernel[1] + 1) // stride[1])
+    oH = -(-(H + pads[0] + pads[2] - kernel[0] + 1) // stride[0])
+    oW = -(-(W + pads[1] + pads[3] - kernel[1] + 1) // stride[1])
     yshape = (N, oH, oW, Cc) if layout == LAYOUT_NHWC else (N, Cc, oH, oW)
     Y = torch.empty(yshape, dtype=torch.float32, device=X.device)
     d = capi.Pool2dDesc(mode, N, Cc, H, W, kernel[0], kernel[1], stride[0], stride[1], (capi.i32 * 4)(*pads),

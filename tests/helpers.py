@@ -1,0 +1,142 @@
+"""Shared test helpers: the golden fixtures of the reference, two interchangeable back ends
+(the CPU oracle and the CUDA path through the C ABI) and the error metrics the tests use."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import numpy as np
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def load_fixtures():
+    manifest = json.loads((GOLDEN / "reference_fixtures.json").read_text())
+    arrays = np.load(GOLDEN / "reference_fixtures.npz")
+    return manifest, arrays
+
+
+def rel_err(y, ref):
+    """max_i |y_i - ref_i| / max_i |ref_i|: the error of a tensor relative to the tensor's own scale.
+    This is the metric behind the fp32 tolerance of 1e-5. A per-element ratio is not usable: two
+    correct fp32 evaluations of the same dot product (OpenBLAS's blocked order, a double
+    accumulator) already differ by ~1e-6 absolute, which is 1e-4 of an output that cancels to 0.01."""
+    y = np.asarray(y, np.float64).ravel()
+    ref = np.asarray(ref, np.float64).ravel()
+    assert y.shape == ref.shape, (y.shape, ref.shape)
+    if ref.size == 0:
+        return 0.0
+    return float(np.abs(y - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+class OracleBackend:
+    """numpy in / numpy out through oracle/sofie_oracle.c."""
+
+    def __init__(self):
+        from oracle import cpu_oracle
+        self.o = cpu_oracle
+
+    def gemm(self, A, B, C=None, **kw):
+        return self.o.gemm_f32(A, B, C, **kw)
+
+    def conv(self, X, W, B=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), group=1):
+        return self.o.conv2d_f32(X, W, B, pad=pad, stride=stride, dil=dil, group=group)
+
+    def relu(self, X):
+        return self.o.relu_f32(X)
+
+    def pool(self, X, mode, kernel, stride, pads, count_include_pad=0):
+        return self.o.pool2d_f32(X, mode, kernel, stride, pads, count_include_pad)
+
+    def softmax(self, X, axis):
+        return self.o.softmax_f32(X, axis)
+
+
+class CudaBackend:
+    """numpy in / numpy out through libSOFIE_cuda (C ABI) on cuda:0."""
+
+    def __init__(self, device="cuda:0"):
+        import torch
+        from sofie_b200 import ops
+        self.t, self.ops, self.dev = torch, ops, device
+
+    def _d(self, a):
+        return None if a is None else self.t.from_numpy(np.ascontiguousarray(a)).to(self.dev)
+
+    def gemm(self, A, B, C=None, **kw):
+        return self.ops.gemm_f32(self._d(A), self._d(B), self._d(C), **kw).cpu().numpy()
+
+    def conv(self, X, W, B=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), group=1):
+        return self.ops.conv2d_f32(self._d(X), self._d(W), self._d(B), pad=pad, stride=stride, dil=dil,
+                                   group=group).cpu().numpy()
+
+    def relu(self, X):
+        return self.ops.relu_f32(self._d(X)).cpu().numpy()
+
+    def pool(self, X, mode, kernel, stride, pads, count_include_pad=0):
+        return self.ops.pool2d_f32(self._d(X), mode=mode, kernel=kernel, stride=stride, pads=pads,
+                                   count_include_pad=count_include_pad).cpu().numpy()
+
+    def softmax(self, X, axis):
+        return self.ops.softmax_f32(self._d(X), axis).cpu().numpy()
+
+
+def conv_attrs(attrs, kshape):
+    """ONNX Conv attributes -> (pad_h, pad_w), strides, dilations, group following the reference's
+    rules: no pads attribute means pad 1 (ROperator_Conv.hxx:136-139), SAME_* means k/2 after the
+    averaging of asymmetric pads (ROperator_Conv.hxx:140-158,387-410)."""
+    kh, kw = attrs.get("kernel_shape", kshape)
+    auto = attrs.get("auto_pad", "NOTSET")
+    if auto == "NOTSET":
+        pads = attrs.get("pads", [1, 1, 1, 1])
+    elif auto in ("SAME_UPPER", "SAME_LOWER"):
+        pads = [kh // 2, kw // 2, kh // 2, kw // 2]
+        if kh % 2 == 1:
+            pads[0 if auto == "SAME_UPPER" else 2] += 1
+        if kw % 2 == 1:
+            pads[1 if auto == "SAME_UPPER" else 3] += 1
+    else:
+        pads = [0, 0, 0, 0]
+    pad = ((pads[0] + pads[2]) // 2, (pads[1] + pads[3]) // 2) if (pads[0] != pads[2] or pads[1] != pads[3]) \
+        else (pads[0], pads[1])
+    return pad, tuple(attrs.get("strides", [1, 1])), tuple(attrs.get("dilations", [1, 1])), attrs.get("group", 1)
+
+
+def run_fixture(name, manifest, arrays, backend):
+    """Evaluate one golden fixture's graph with the given back end; returns the flat output."""
+    entry = manifest[name]
+    t = {i: arrays[f"{name}/in/{i}"] for i in entry["inputs"]}
+    for key in arrays.files:
+        if key.startswith(f"{name}/w/"):
+            t[key[len(name) + 3:]] = arrays[key]
+    out = None
+    for n in entry["nodes"]:
+        op, a, ins = n["op"], n["attrs"], n["inputs"]
+        if op == "Gemm":
+            y = backend.gemm(t[ins[0]], t[ins[1]], t[ins[2]] if len(ins) > 2 else None, transA=a.get("transA", 0),
+                             transB=a.get("transB", 0), alpha=a.get("alpha", 1.0), beta=a.get("beta", 1.0))
+        elif op == "Einsum":
+            assert a["equation"] == "ik,kj->ij"
+            y = backend.gemm(t[ins[0]], t[ins[1]], None, beta=0.0)
+        elif op == "Relu":
+            y = backend.relu(t[ins[0]])
+        elif op == "Conv":
+            W = t[ins[1]]
+            pad, stride, dil, group = conv_attrs(a, W.shape[2:])
+            y = backend.conv(t[ins[0]], W, t[ins[2]] if len(ins) > 2 else None, pad=pad, stride=stride, dil=dil, group=group)
+        elif op in ("MaxPool", "AveragePool"):
+            y = backend.pool(t[ins[0]], 0 if op == "MaxPool" else 1, tuple(a["kernel_shape"]),
+                             tuple(a.get("strides", [1, 1])), tuple(a.get("pads", [0, 0, 0, 0])),
+                             a.get("count_include_pad", 0))
+        elif op == "Softmax":
+            y = backend.softmax(t[ins[0]], a.get("axis", -1))
+        else:
+            raise NotImplementedError(op)
+        t[n["outputs"][0]] = y
+        out = y
+    return np.asarray(out).ravel()
+
+
+FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutPadding",
+                 "ConvWithAutopadSameLower", "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "AvgPool",
+                 "Softmax1d", "Softmax2d", "Softmax3d", "Softmax4d", "Einsum_matmul"]

@@ -1,0 +1,67 @@
+"""The C-ABI library loads without a GPU and exports exactly what include/sofie_cuda.h declares."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from sofie_b200 import capi
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "sofie_cuda.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sofie_cuda_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    lib = capi.load()
+    names = declared_symbols()
+    assert len(names) >= 40
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in sofie_cuda.h but not exported by libSOFIE_cuda.so"
+    bound = set(capi.SIGNATURES) | set(capi.STRING_GETTERS)
+    assert bound == set(names), sorted(bound ^ set(names))
+
+
+def test_struct_sizes_match_header():
+    # all descriptor fields are 4 bytes wide, so the size is 4 * number of fields
+    assert C.sizeof(capi.GemmF32Desc) == 9 * 4
+    assert C.sizeof(capi.Conv2dDesc) == 19 * 4
+    assert C.sizeof(capi.Pool2dDesc) == 15 * 4
+    assert C.sizeof(capi.QGemmDesc) == 6 * 4
+    assert C.sizeof(capi.QConv2dDesc) == 18 * 4
+    assert C.sizeof(capi.Fp8GemmDesc) == 7 * 4
+
+
+def test_status_strings_and_argument_errors():
+    lib = capi.load()
+    assert lib.sofie_cuda_strerror(0) == b"success"
+    assert lib.sofie_cuda_strerror(1) == b"invalid argument"
+    assert lib.sofie_cuda_abi_version() == 1
+    # NULL descriptor: rejected before anything touches a device
+    rc = lib.sofie_cuda_gemm_f32(None, None, None, None, None, None)
+    assert rc == capi.ERR_INVALID
+    assert b"NULL" in lib.sofie_cuda_last_error()
+    d = capi.GemmF32Desc(4, 0, 4, 0, 0, 1.0, 1.0, 0, 0)
+    rc = lib.sofie_cuda_gemm_f32(None, C.byref(d), C.c_void_p(16), C.c_void_p(16), None, C.c_void_p(16))
+    assert rc == capi.ERR_INVALID
+    with pytest.raises(capi.SofieCudaError):
+        capi.call("sofie_cuda_set_engine", 7)
+
+
+def test_no_gpu_means_loud_failure_not_cpu_fallback():
+    """Without a device the context cannot be created; nothing computes on the CPU instead."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    lib = capi.load()
+    ctx = C.c_void_p()
+    rc = lib.sofie_cuda_ctx_create(C.byref(ctx), 0, 1 << 20)
+    assert rc != capi.OK and not ctx.value
+    from sofie_b200 import configs, runner
+    m, _ = configs.mlp_f32(batch=4)
+    with pytest.raises(RuntimeError):
+        runner.Session(m)

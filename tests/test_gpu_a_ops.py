@@ -1,0 +1,280 @@
+"""GPU parity of every operator of the dense-contraction path, through the C ABI, against the CPU
+oracle and the reference's golden vectors. The contractions run here on the CUDA-core kernels
+(engine forced); the tcgen05 kernels have their own file.
+Tolerances: fp32 1e-5 (tensor-relative, helpers.rel_err), int8 bit-exact, FP8 2e-2."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import CudaBackend, FIXTURE_CASES, load_fixtures, rel_err, run_fixture
+from oracle import cpu_oracle as o
+from sofie_b200 import capi, ops
+
+pytestmark = pytest.mark.gpu
+FP32_TOL = 1e-5
+
+
+@pytest.fixture(autouse=True)
+def simt_engine(cuda_device):
+    ops.set_engine(capi.ENGINE_SIMT)
+    yield
+    ops.set_engine(0)
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("name", FIXTURE_CASES)
+def test_reference_golden_vectors(name):
+    manifest, arrays = load_fixtures()
+    y = run_fixture(name, manifest, arrays, CudaBackend())
+    exp = arrays[f"{name}/expected"]
+    assert y.shape == exp.shape
+    assert np.abs(y - exp).max() <= 1e-3  # the reference's own tolerance for these vectors
+
+
+@pytest.mark.parametrize("M,N,K,tA,tB,bias", [(1, 1, 1, 0, 0, 0), (37, 29, 53, 0, 0, 1), (64, 128, 64, 0, 1, 1),
+                                              (130, 70, 257, 1, 1, 2), (5, 300, 17, 1, 0, 0), (1024, 10, 128, 0, 1, 1),
+                                              (256, 10, 4096, 0, 1, 1)])
+def test_gemm_f32(M, N, K, tA, tB, bias):
+    rng = np.random.default_rng(M * 7 + N)
+    A = rng.standard_normal((K, M) if tA else (M, K)).astype(np.float32)
+    B = rng.standard_normal((N, K) if tB else (K, N)).astype(np.float32)
+    Cb = None if bias == 0 else rng.standard_normal((N,) if bias == 1 else (M, N)).astype(np.float32)
+    ref = o.gemm_f32(A, B, Cb, transA=tA, transB=tB, alpha=0.75, beta=1.5, relu=True)
+    y = ops.gemm_f32(dev(A), dev(B), None if Cb is None else dev(Cb), transA=tA, transB=tB, alpha=0.75, beta=1.5,
+                     relu=True).cpu().numpy()
+    assert ops.last_engine() == capi.ENGINE_SIMT
+    assert rel_err(y, ref) <= FP32_TOL
+
+
+def test_gemm_empty_batch_and_bad_arguments():
+    B = torch.zeros((4, 8), device="cuda")
+    y = ops.gemm_f32(torch.zeros((0, 8), device="cuda"), B, transB=1)
+    assert y.shape == (0, 4)
+    with pytest.raises(capi.SofieCudaError) as e:
+        d = capi.GemmF32Desc(4, 4, 4, 0, 0, 1.0, 1.0, 1, 0)  # bias_kind set, C NULL
+        capi.call("sofie_cuda_gemm_f32", None, d, B.data_ptr(), B.data_ptr(), None, B.data_ptr())
+    assert e.value.status == capi.ERR_INVALID
+
+
+CONV_CASES = [
+    # N, C, H, W, Cout, k, pad, stride, dil, group
+    (2, 3, 9, 8, 4, (3, 3), (1, 1), (1, 1), (1, 1), 1),
+    (1, 1, 5, 5, 1, (3, 3), (0, 0), (1, 1), (1, 1), 1),
+    (3, 4, 11, 9, 6, (3, 3), (1, 1), (2, 1), (1, 1), 2),
+    (2, 3, 12, 12, 5, (5, 5), (2, 2), (1, 1), (1, 1), 1),
+    (2, 8, 10, 10, 20, (3, 3), (2, 2), (1, 1), (2, 2), 1),
+    (2, 6, 7, 7, 6, (1, 1), (0, 0), (1, 1), (1, 1), 6),
+    (4, 16, 32, 32, 32, (3, 3), (1, 1), (1, 1), (1, 1), 1),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv2d_f32_nchw(case):
+    N, C, H, W, Cout, k, pad, stride, dil, group = case
+    rng = np.random.default_rng(sum(case[:5]))
+    X = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    Wt = rng.standard_normal((Cout, C // group, *k)).astype(np.float32)
+    b = rng.standard_normal(Cout).astype(np.float32)
+    ref = o.conv2d_f32(X, Wt, b, pad=pad, stride=stride, dil=dil, group=group)
+    y = ops.conv2d_f32(dev(X), dev(Wt), dev(b), pad=pad, stride=stride, dil=dil, group=group).cpu().numpy()
+    assert rel_err(y, ref) <= FP32_TOL
+    y2 = ops.conv2d_f32(dev(X), dev(Wt), None, pad=pad, stride=stride, dil=dil, group=group).cpu().numpy()
+    assert rel_err(y2, o.conv2d_f32(X, Wt, None, pad=pad, stride=stride, dil=dil, group=group)) <= FP32_TOL
+
+
+@pytest.mark.parametrize("x_nhwc,y_nhwc,packed,relu,pool", [(0, 1, 0, 1, 0), (1, 1, 1, 1, 2), (1, 0, 1, 0, 2),
+                                                           (0, 0, 0, 1, 2), (1, 1, 0, 0, 0)])
+def test_conv2d_f32_layouts_and_fusion(x_nhwc, y_nhwc, packed, relu, pool):
+    rng = np.random.default_rng(5)
+    N, C, H, W, Cout = 3, 16, 10, 14, 24   # odd pooled extents are covered by H=10 -> 5
+    X = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    Wt = rng.standard_normal((Cout, C, 3, 3)).astype(np.float32)
+    b = rng.standard_normal(Cout).astype(np.float32)
+    ref = o.conv2d_f32(X, Wt, b, pad=(1, 1), relu=bool(relu))
+    if pool:
+        ref = o.pool2d_f32(ref, 0, (2, 2), (2, 2))
+    Xd = dev(X.transpose(0, 2, 3, 1)) if x_nhwc else dev(X)
+    Wd = ops.conv2d_pack_f32(dev(Wt)) if packed else dev(Wt)
+    y = ops.conv2d_f32(Xd, Wd, dev(b), shape=(N, C, H, W), pad=(1, 1), relu=bool(relu), pool=pool, x_layout=x_nhwc,
+                       y_layout=y_nhwc, w_packed=bool(packed), kernel=(3, 3)).cpu().numpy()
+    if y_nhwc:
+        y = y.transpose(0, 3, 1, 2)
+    assert rel_err(y, ref) <= FP32_TOL
+
+
+def test_relu_nan_negzero_and_ragged_sizes():
+    for n in (0, 1, 3, 4, 5, 1023, 4099):
+        x = np.random.default_rng(n).standard_normal(n).astype(np.float32)
+        if n > 3:
+            x[1], x[2], x[3] = np.nan, -0.0, -np.inf
+        y = ops.relu_f32(dev(x)).cpu().numpy() if n else np.zeros(0, np.float32)
+        ref = o.relu_f32(x) if n else y
+        assert np.array_equal(y.view(np.uint32), ref.view(np.uint32))
+    # unaligned pointers take the scalar path
+    x = torch.randn(1001, device="cuda")
+    assert torch.equal(ops.relu_f32(x[1:].contiguous()), torch.clamp_min(x[1:], 0))
+
+
+@pytest.mark.parametrize("mode,k,s,pads,cip", [(0, (2, 2), (2, 2), (0, 0, 0, 0), 0), (0, (3, 2), (1, 1), (0, 0, 0, 0), 0),
+                                               (0, (3, 3), (2, 2), (1, 1, 1, 1), 0), (1, (3, 2), (2, 1), (0, 0, 0, 0), 0),
+                                               (1, (3, 3), (1, 1), (1, 1, 1, 1), 0), (1, (3, 3), (1, 1), (1, 1, 1, 1), 1)])
+def test_pool2d_f32(mode, k, s, pads, cip):
+    rng = np.random.default_rng(3)
+    X = rng.standard_normal((2, 5, 9, 10)).astype(np.float32)
+    ref = o.pool2d_f32(X, mode, k, s, pads, cip)
+    y = ops.pool2d_f32(dev(X), mode=mode, kernel=k, stride=s, pads=pads, count_include_pad=cip).cpu().numpy()
+    assert rel_err(y, ref) <= 1e-6
+    y2 = ops.pool2d_f32(dev(X.transpose(0, 2, 3, 1)), mode=mode, kernel=k, stride=s, pads=pads, count_include_pad=cip,
+                        layout=1, shape=X.shape).cpu().numpy().transpose(0, 3, 1, 2)
+    assert rel_err(y2, ref) <= 1e-6
+
+
+@pytest.mark.parametrize("shape,axis", [((3,), 0), ((1, 3), 1), ((2, 3, 4), 1), ((2, 3, 4, 2), -2), ((64, 10), -1),
+                                        ((5, 1000), 1), ((4, 7, 33), 0)])
+def test_softmax_f32(shape, axis):
+    X = np.random.default_rng(1).standard_normal(shape).astype(np.float32) * 3
+    y = ops.softmax_f32(dev(X), axis).cpu().numpy()
+    assert np.abs(y - o.softmax_f32(X, axis)).max() <= 1e-6
+
+
+def test_layout_round_trips():
+    X = np.random.default_rng(2).standard_normal((3, 5, 7, 9)).astype(np.float32)
+    nhwc = ops.nchw_to_nhwc(dev(X))
+    assert np.array_equal(nhwc.cpu().numpy(), X.transpose(0, 2, 3, 1))
+    assert np.array_equal(ops.nhwc_to_nchw(nhwc).cpu().numpy(), X)
+    U = np.random.default_rng(2).integers(0, 256, (2, 33, 6, 5)).astype(np.uint8)
+    assert np.array_equal(ops.nhwc_to_nchw(ops.nchw_to_nhwc(dev(U))).cpu().numpy(), U)
+    Wm = np.random.default_rng(2).standard_normal((45, 70)).astype(np.float32)
+    assert np.array_equal(ops.transpose2d(dev(Wm)).cpu().numpy(), Wm.T)
+
+
+# ------------------------------------------------------------------------------------ int8
+def test_quantize_dequantize_u8_bit_exact():
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(10007) * 2, np.arange(-300, 300) * 0.01, [1e9, -1e9, 0.01, 0.03, -0.01]]).astype(np.float32)
+    for scale, zp in ((0.02, 128), (8 / 255, 0), (0.5, 255)):
+        q = ops.quantize_u8(dev(x), scale, zp).cpu().numpy()
+        assert np.array_equal(q, o.quantize_u8(x, scale, zp))
+        d = ops.dequantize_u8(dev(q), scale, zp).cpu().numpy()
+        assert np.array_equal(d.view(np.uint32), o.dequantize_u8(q, scale, zp).view(np.uint32))
+
+
+@pytest.mark.parametrize("M,N,K,nk,relu,zp", [(8, 16, 32, 1, 0, 128), (100, 37, 77, 0, 1, 128), (64, 256, 512, 1, 0, 0),
+                                              (33, 1000, 129, 0, 0, 7)])
+def test_qlinear_matmul_bit_exact(M, N, K, nk, relu, zp):
+    rng = np.random.default_rng(N)
+    A = rng.integers(0, 256, (M, K)).astype(np.uint8)
+    W = rng.integers(-127, 128, (N, K) if nk else (K, N)).astype(np.int8)
+    ws = rng.uniform(0.001, 0.01, N).astype(np.float32)
+    y_scale = 0.02 * np.sqrt(K) * 0.3
+    ref = o.qlinear_matmul(A, 0.02, zp, W, ws, y_scale, 128, w_is_nk=bool(nk), relu=bool(relu))
+    mult, corr = ops.qlinear_prepare(W, bool(nk), 0.02, zp, ws, y_scale, None, "cuda")
+    assert np.array_equal(mult.cpu().numpy().view(np.uint32), o.requant_multiplier(0.02, ws, y_scale).view(np.uint32))
+    y = ops.qlinear_matmul(dev(A), dev(W), mult, corr, w_is_nk=bool(nk), y_zp=128, relu=bool(relu)).cpu().numpy()
+    assert np.array_equal(y, ref)
+    assert len(np.unique(ref)) > 20  # the case is not degenerate
+
+
+@pytest.mark.parametrize("x_nhwc,y_nhwc,packed,pool,x_zp", [(0, 0, 0, 0, 0), (0, 1, 0, 2, 0), (1, 1, 1, 2, 0), (1, 0, 1, 0, 3),
+                                                           (0, 0, 0, 2, 128)])
+def test_qlinear_conv2d_bit_exact(x_nhwc, y_nhwc, packed, pool, x_zp):
+    rng = np.random.default_rng(9)
+    N, C, H, W, Cout = 2, 8, 12, 10, 20
+    X = rng.integers(0, 256, (N, C, H, W)).astype(np.uint8)
+    Wt = rng.integers(-127, 128, (Cout, C, 3, 3)).astype(np.int8)
+    ws = rng.uniform(0.001, 0.01, Cout).astype(np.float32)
+    bias = rng.integers(-1000, 1000, Cout).astype(np.int32)
+    ref = o.qlinear_conv2d(X, 0.05, x_zp, Wt, ws, 2.0, 10, bias=bias, pad=(1, 1), relu=True)
+    if pool:
+        ref = o.maxpool2d_u8(ref)
+    mult = dev(o.requant_multiplier(0.05, ws, 2.0))
+    Xd = dev(X.transpose(0, 2, 3, 1)) if x_nhwc else dev(X)
+    Wd = ops.qconv2d_pack_i8(dev(Wt)) if packed else dev(Wt)
+    y = ops.qlinear_conv2d(Xd, Wd, mult, dev(bias), shape=X.shape, pad=(1, 1), x_zp=x_zp, y_zp=10, relu=True, pool=pool,
+                           x_layout=x_nhwc, y_layout=y_nhwc, w_packed=bool(packed), kernel=(3, 3)).cpu().numpy()
+    if y_nhwc:
+        y = y.transpose(0, 3, 1, 2)
+    assert np.array_equal(y, ref)
+    assert len(np.unique(ref)) > 20
+
+
+def test_maxpool2d_u8():
+    X = np.random.default_rng(4).integers(0, 256, (3, 6, 9, 8)).astype(np.uint8)
+    assert np.array_equal(ops.maxpool2d_u8(dev(X)).cpu().numpy(), o.maxpool2d_u8(X))
+    y = ops.maxpool2d_u8(dev(X.transpose(0, 2, 3, 1)), layout=1, shape=X.shape).cpu().numpy().transpose(0, 3, 1, 2)
+    assert np.array_equal(y, o.maxpool2d_u8(X))
+
+
+# ------------------------------------------------------------------------------------ FP8 / bf16
+def test_e4m3_and_bf16_conversions_bit_exact():
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(50000) * 50, rng.standard_normal(5000) * 0.01,
+                        [0, -0.0, 448, 449, 464, 465, 1e6, -1e6, 2 ** -9, 2 ** -10, 1.5 * 2 ** -10, 0.0175]]).astype(np.float32)
+    for scale in (1.0, 0.37):
+        assert np.array_equal(ops.quantize_e4m3(dev(x), scale).cpu().numpy(), o.quantize_e4m3(x, scale))
+    b = ops.cast_f32_bf16(dev(x))
+    assert np.array_equal(b.view(torch.int16).cpu().numpy().view(np.uint16), o.f32_to_bf16_bits(x))
+    assert np.array_equal(ops.cast_bf16_f32(b.view(torch.int16)).cpu().numpy(), o.bf16_bits_to_f32(o.f32_to_bf16_bits(x)))
+    assert np.array_equal(ops.quantize_e4m3(b.view(torch.int16), 0.37).cpu().numpy(),
+                          o.quantize_e4m3(o.bf16_bits_to_f32(o.f32_to_bf16_bits(x)), 0.37))
+    assert float(ops.amax_f32(dev(x)).cpu()) == np.abs(x).max()
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 32, 64), (70, 45, 130), (128, 256, 512)])
+def test_gemm_e4m3(M, N, K):
+    rng = np.random.default_rng(K)
+    X = rng.standard_normal((M, K)).astype(np.float32)
+    Wf = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float32)
+    sa, sw = float(np.abs(X).max() / 448), float(np.abs(Wf).max() / 448)
+    Aq, Wq = o.quantize_e4m3(X, sa), o.quantize_e4m3(Wf, sw)
+    ref = o.bf16_bits_to_f32(o.gemm_e4m3(Aq, sa, Wq, sw, bias, relu=True))
+    Y, Yq = ops.gemm_e4m3(dev(Aq), dev(Wq), dev(bias), a_scale=sa, w_scale=sw, relu=True, q_scale=0.01)
+    y = Y.float().cpu().numpy()
+    assert rel_err(y, ref) <= 2e-2
+    assert rel_err(y, ref) <= 8e-3  # one bf16 ulp: the accumulation itself is fp32
+    # the fused quantised output is exactly the quantisation of the bf16 output
+    assert np.array_equal(Yq.cpu().numpy(), o.quantize_e4m3(y, 0.01))
+
+
+# ------------------------------------------------------------------------------------ context
+def test_context_arena_upload_copy_and_graph():
+    import ctypes as C
+    lib = capi.load()
+    ctx = C.c_void_p()
+    capi.call("sofie_cuda_ctx_create", C.byref(ctx), 0, 1 << 20)
+    try:
+        p = C.c_void_p()
+        capi.call("sofie_cuda_ctx_arena", ctx, 256, 4096, C.byref(p))
+        assert lib.sofie_cuda_ctx_arena(ctx, 100, 16, C.byref(p)) == capi.ERR_INVALID      # misaligned
+        assert lib.sofie_cuda_ctx_arena(ctx, 1 << 20, 256, C.byref(p)) == capi.ERR_NOMEM    # out of range
+        A = np.random.default_rng(0).standard_normal((64, 32)).astype(np.float32)
+        Wm = np.random.default_rng(1).standard_normal((16, 32)).astype(np.float32)
+        dW, dA, dY = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        capi.call("sofie_cuda_ctx_upload", ctx, Wm.ctypes.data_as(C.c_void_p), Wm.nbytes, C.byref(dW))
+        capi.call("sofie_cuda_ctx_arena", ctx, 0, A.nbytes, C.byref(dA))
+        capi.call("sofie_cuda_ctx_arena", ctx, 8192, 64 * 16 * 4, C.byref(dY))
+        stream = C.c_void_p()
+        capi.call("sofie_cuda_ctx_stream", ctx, C.byref(stream))
+        d = capi.GemmF32Desc(64, 16, 32, 0, 1, 1.0, 0.0, 0, 1)
+        capi.call("sofie_cuda_ctx_h2d", ctx, dA, A.ctypes.data_as(C.c_void_p), A.nbytes)
+        # warm-up launch outside capture, then capture and replay
+        capi.call("sofie_cuda_gemm_f32", stream, C.byref(d), dA, dW, None, dY)
+        capi.call("sofie_cuda_ctx_graph_begin", ctx)
+        capi.call("sofie_cuda_gemm_f32", stream, C.byref(d), dA, dW, None, dY)
+        capi.call("sofie_cuda_ctx_graph_end", ctx)
+        ready = C.c_int()
+        capi.call("sofie_cuda_ctx_graph_ready", ctx, C.byref(ready))
+        assert ready.value == 1
+        A2 = (A * 2).astype(np.float32)
+        capi.call("sofie_cuda_ctx_h2d", ctx, dA, A2.ctypes.data_as(C.c_void_p), A2.nbytes)
+        capi.call("sofie_cuda_ctx_graph_launch", ctx)
+        Y = np.empty((64, 16), np.float32)
+        capi.call("sofie_cuda_ctx_d2h", ctx, Y.ctypes.data_as(C.c_void_p), dY, Y.nbytes)
+        assert rel_err(Y, o.gemm_f32(A2, Wm, transB=1, relu=True)) <= FP32_TOL
+        capi.call("sofie_cuda_ctx_check", ctx)
+    finally:
+        capi.call("sofie_cuda_ctx_destroy", ctx)
