@@ -51,11 +51,12 @@ extern "C" {
 int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *d, const float *A, const float *B, const float *C,
                         float *Y)
 {
-   SOFIE_REQUIRE(d && A && B && Y, "NULL argument");
+   SOFIE_REQUIRE(d != nullptr, "NULL descriptor");
    SOFIE_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0, "bad GEMM shape %d x %d x %d", d->M, d->N, d->K);
    SOFIE_REQUIRE(d->bias_kind >= 0 && d->bias_kind <= 2, "bias_kind must be 0, 1 or 2");
    SOFIE_REQUIRE(d->bias_kind == 0 || C != nullptr, "bias_kind set but C is NULL");
-   if (d->M == 0) return SOFIE_CUDA_OK;
+   if (d->M == 0) return SOFIE_CUDA_OK; // an empty batch has no rows to compute (and may have NULL A / Y)
+   SOFIE_REQUIRE(A && B && Y, "NULL tensor");
    cudaStream_t s = as_stream(stream);
    return dispatch([&] { return launch_gemm_f32_umma(s, *d, A, B, C, Y); },
                    [&] { return launch_gemm_f32_simt(s, *d, A, B, C, Y); });
@@ -118,10 +119,11 @@ int sofie_cuda_qlinear_prepare(void *stream, int32_t N, int32_t rows_per_n, cons
 int sofie_cuda_qlinear_matmul(void *stream, const sofie_qgemm_desc *d, const uint8_t *A, const int8_t *W,
                               const float *mult, const int32_t *corr, uint8_t *Y)
 {
-   SOFIE_REQUIRE(d && A && W && mult && Y, "NULL argument");
+   SOFIE_REQUIRE(d != nullptr, "NULL descriptor");
    SOFIE_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0, "bad GEMM shape");
    SOFIE_REQUIRE(d->y_zp >= 0 && d->y_zp <= 255, "y_zp out of range");
    if (d->M == 0) return SOFIE_CUDA_OK;
+   SOFIE_REQUIRE(A && W && mult && Y, "NULL tensor");
    cudaStream_t s = as_stream(stream);
    return dispatch([&] { return launch_qgemm_umma(s, *d, A, W, mult, corr, Y); },
                    [&] { return launch_qgemm_simt(s, *d, A, W, mult, corr, Y); });
@@ -145,10 +147,11 @@ int sofie_cuda_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *d, const u
 int sofie_cuda_gemm_e4m3(void *stream, const sofie_fp8_gemm_desc *d, const uint8_t *A, const uint8_t *W,
                          const float *bias, uint16_t *Ybf16, uint8_t *Yq)
 {
-   SOFIE_REQUIRE(d && A && W && (Ybf16 || Yq), "NULL argument");
+   SOFIE_REQUIRE(d != nullptr, "NULL descriptor");
    SOFIE_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0, "bad GEMM shape");
    SOFIE_REQUIRE(!Yq || d->q_scale > 0.f, "Yq given but q_scale is not positive");
    if (d->M == 0) return SOFIE_CUDA_OK;
+   SOFIE_REQUIRE(A && W && (Ybf16 || Yq), "NULL tensor");
    cudaStream_t s = as_stream(stream);
    return dispatch([&] { return launch_gemm_e4m3_umma(s, *d, A, W, bias, Ybf16, Yq); },
                    [&] { return launch_gemm_e4m3_simt(s, *d, A, W, bias, Ybf16, Yq); });

@@ -93,6 +93,100 @@ struct GemmSmem {
    static constexpr int stages(int budget) { return budget / kStageBytes; }
 };
 
+// Epilogue of 32 consecutive columns of one output row: v[j] is the raw accumulator of column
+// col0 + j (fp32 bits, or int32 for kI8). Vector stores when the row chunk is full and aligned.
+template <int KIND>
+__device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const uint32_t (&r)[32], int row, int col0, int N)
+{
+   const int ncols = min(32, N - col0);
+   if constexpr (KIND == kTF32) {
+      float *y = ep.Yf + (size_t)row * N + col0;
+      float v[32];
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+         float acc = ep.alpha * __uint_as_float(r[j]);
+         if (j < ncols) {
+            if (ep.bias_kind == 1) acc += ep.beta * ep.C[col0 + j];
+            else if (ep.bias_kind == 2) acc += ep.beta * ep.C[(size_t)row * N + col0 + j];
+         }
+         v[j] = ep.relu ? relu_ref(acc) : acc;
+      }
+      if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+#pragma unroll
+         for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+         for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
+      }
+   } else if constexpr (KIND == kI8) {
+      uint8_t *y = ep.Yu8 + (size_t)row * N + col0;
+      uint32_t packed[8];
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+         int q = 0;
+         if (j < ncols) {
+            int acc = (int)r[j] + (ep.corr ? ep.corr[col0 + j] : 0);
+            q = requant_u8(acc, ep.mult[col0 + j], ep.y_zp, ep.relu);
+         }
+         if ((j & 3) == 0) packed[j >> 2] = 0;
+         packed[j >> 2] |= (uint32_t)q << (8 * (j & 3));
+      }
+      if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+         *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+         *reinterpret_cast<uint4 *>(y + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      } else {
+#pragma unroll
+         for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
+      }
+   } else {
+      uint32_t hb[16], qb[8];
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+         uint16_t h = 0;
+         uint8_t q = 0;
+         if (j < ncols) {
+            float y = __fmul_rn(__uint_as_float(r[j]), ep.scale);
+            if (ep.bias) y = __fadd_rn(y, ep.bias[col0 + j]);
+            if (ep.relu) y = relu_ref(y);
+            h = f32_to_bf16_rne(y);
+            if (ep.Yq)
+               q = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(bf16_to_f32(h), ep.q_scale), __NV_SATFINITE, __NV_E4M3);
+         }
+         if ((j & 1) == 0) hb[j >> 1] = 0;
+         hb[j >> 1] |= (uint32_t)h << (16 * (j & 1));
+         if ((j & 3) == 0) qb[j >> 2] = 0;
+         qb[j >> 2] |= (uint32_t)q << (8 * (j & 3));
+      }
+      if (ep.Ybf16) {
+         uint16_t *y = ep.Ybf16 + (size_t)row * N + col0;
+         if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+               reinterpret_cast<uint4 *>(y)[j] = make_uint4(hb[4 * j], hb[4 * j + 1], hb[4 * j + 2], hb[4 * j + 3]);
+         } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint16_t)(hb[j >> 1] >> (16 * (j & 1)));
+         }
+      }
+      if (ep.Yq) {
+         uint8_t *y = ep.Yq + (size_t)row * N + col0;
+         if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+            *reinterpret_cast<uint4 *>(y) = make_uint4(qb[0], qb[1], qb[2], qb[3]);
+            *reinterpret_cast<uint4 *>(y + 16) = make_uint4(qb[4], qb[5], qb[6], qb[7]);
+         } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)(qb[j >> 2] >> (8 * (j & 3)));
+         }
+      }
+   }
+}
+
+// fp32 only: the tensor core adds into its accumulator with truncation, so a long K drifts (about
+// 3e-5 of the result at K = 4096). The fp32 kernel therefore accumulates at most kPromoteKB stages
+// (256 elements of K) in TMEM, then adds that partial sum into fp32 registers with round-to-nearest
+// while the tensor core fills the second TMEM buffer.
+constexpr int kPromoteKB = 8;
+
 template <int KIND, int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmEpilogue ep,
@@ -101,17 +195,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
    using L = GemmSmem<KIND, BN>;
    constexpr int ES = (KIND == kTF32) ? 4 : 1;           // element size in bytes
    constexpr int KE = kStageK / ES;                      // elements of K per stage
-   constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;     // power of two >= 32
+   constexpr int NBUF = (KIND == kTF32) ? 2 : 1;         // TMEM accumulator buffers
+   constexpr uint32_t TMEM_COLS = NBUF * BN < 32 ? 32 : NBUF * BN; // power of two >= 32
    extern __shared__ unsigned char smem_raw[];
    // 1024-byte alignment: the 128B swizzle pattern repeats every 1024 bytes and is address based.
    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-   __shared__ uint64_t full_bar[STAGES], conv_bar[STAGES], empty_bar[STAGES], accum_bar;
+   __shared__ uint64_t full_bar[STAGES], conv_bar[STAGES], empty_bar[STAGES], accum_full[2], accum_empty[2];
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
    const int num_kb = (K * ES + kStageK - 1) / kStageK;
+   const int chunk_kb = (KIND == kTF32) ? kPromoteKB : num_kb; // stages accumulated in TMEM before a drain
+   const int num_chunks = (num_kb + chunk_kb - 1) / chunk_kb;
 
    auto a_hi = [&](int s) { return smem + (size_t)s * L::kStageBytes; };
    auto b_hi = [&](int s) { return smem + (size_t)s * L::kStageBytes + L::kATile; };
@@ -124,7 +221,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
          mbar_init(&conv_bar[s], 128);
          mbar_init(&empty_bar[s], 1);
       }
-      mbar_init(&accum_bar, 1);
+      for (int b = 0; b < 2; b++) {
+         mbar_init(&accum_full[b], 1);
+         mbar_init(&accum_empty[b], 128);
+      }
       abort_flag = 0;
       fence_mbar_init();
       prefetch_tensormap(&tmA);
@@ -155,43 +255,80 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
          constexpr uint32_t idesc = make_idesc<KIND>(kBM, BN);
-         uint32_t accumulate = 0;
          for (int kb = 0; kb < num_kb; kb++) {
             const int s = kb % STAGES;
             const uint32_t ph = (kb / STAGES) & 1;
+            const int chunk = kb / chunk_kb, buf = chunk & (NBUF - 1);
+            const bool chunk_start = (kb % chunk_kb) == 0;
+            if (chunk_start && chunk >= NBUF) {
+               // the buffer is reused: the worker warps must have drained chunk - NBUF from it
+               if (!mbar_wait(&accum_empty[buf], ((chunk / NBUF) - 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x1000 + chunk)) break;
+               tc_fence_after();
+            }
             bool ok = (KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, kb)
                                       : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, kb);
             if (!ok) break;
             tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
             const uint64_t da = make_smem_desc(smem_u32(a_hi(s)), kStageK);
             const uint64_t db = make_smem_desc(smem_u32(b_hi(s)), kStageK);
 #pragma unroll
             for (int k = 0; k < kStageK / kMmaK; k++) {
                // advancing K inside the swizzle row: +32 bytes = +2 in the (>>4) address field
                const uint64_t koff = (uint64_t)(k * (kMmaK >> 4));
+               const uint32_t accumulate = (chunk_start && k == 0) ? 0u : 1u;
                if constexpr (KIND == kTF32) {
                   const uint64_t dal = make_smem_desc(smem_u32(a_lo(s)), kStageK);
                   const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)), kStageK);
-                  tc_mma<KIND>(tmem_base, dal + koff, db + koff, idesc, accumulate);
-                  tc_mma<KIND>(tmem_base, da + koff, dbl + koff, idesc, 1);
-                  tc_mma<KIND>(tmem_base, da + koff, db + koff, idesc, 1);
+                  tc_mma<KIND>(d_tmem, dal + koff, db + koff, idesc, accumulate);
+                  tc_mma<KIND>(d_tmem, da + koff, dbl + koff, idesc, 1);
+                  tc_mma<KIND>(d_tmem, da + koff, db + koff, idesc, 1);
                } else {
-                  tc_mma<KIND>(tmem_base, da + koff, db + koff, idesc, accumulate);
+                  tc_mma<KIND>(d_tmem, da + koff, db + koff, idesc, accumulate);
                }
-               accumulate = 1;
             }
             tc_commit(&empty_bar[s]); // the stage is free once these MMAs have read it
+            if ((kb % chunk_kb) == chunk_kb - 1 || kb == num_kb - 1) tc_commit(&accum_full[buf]);
          }
-         tc_commit(&accum_bar);
       }
    } else {
-      // ---------------- converter (kTF32) then epilogue: warps 2..5 ----------------
+      // ---------------- worker warps 2..5: fp32 split + promotion (kTF32), then the epilogue ----------------
       const int t = threadIdx.x - 64; // 0..127
+      const int lane_base = (warp & 3) * 32;
+      const int row = m0 + lane_base + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
       if constexpr (KIND == kTF32) {
-         for (int kb = 0; kb < num_kb; kb++) {
+         float acc[BN];
+#pragma unroll
+         for (int j = 0; j < BN; j++) acc[j] = 0.f;
+         bool alive = true;
+         // adds the finished TMEM partial sum of chunk `d` into the registers
+         auto drain = [&](int d) {
+            const int buf = d & 1;
+            if (!mbar_wait(&accum_full[buf], (d >> 1) & 1, &abort_flag, status, kStatusWaitAccum, d)) {
+               alive = false;
+               return;
+            }
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+               uint32_t r[32];
+               tmem_ld_32x32(t_row + (uint32_t)(buf * BN + c0), r);
+               tmem_ld_wait();
+#pragma unroll
+               for (int j = 0; j < 32; j++) acc[c0 + j] += __uint_as_float(r[j]);
+            }
+            tc_fence_before();
+            mbar_arrive(&accum_empty[buf]);
+         };
+         int next_drain = 0;
+         for (int kb = 0; kb < num_kb && alive; kb++) {
             const int s = kb % STAGES;
             const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, kb)) break;
+            if (!mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, kb)) {
+               alive = false;
+               break;
+            }
             // The split is elementwise, so the swizzled placement does not matter: the lo tile is
             // written at the same offsets as the hi tile. A and B tiles are contiguous.
             float4 *hi = reinterpret_cast<float4 *>(a_hi(s));
@@ -210,102 +347,31 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             fence_proxy_async(); // make the generic-proxy writes visible to the tensor-core (async) proxy
             mbar_arrive(&conv_bar[s]);
+            // a chunk is drained two stages after its last stage was split, when its MMAs are (almost) done
+            if (next_drain < num_chunks && kb >= (next_drain + 1) * chunk_kb + 1) drain(next_drain++);
          }
-      }
-      // ---- epilogue ----
-      if (mbar_wait(&accum_bar, 0, &abort_flag, status, kStatusWaitAccum, 0)) {
-         tc_fence_after();
-         const int lane_base = (warp & 3) * 32;
-         const int row = m0 + lane_base + lane;
-#pragma unroll 1
-         for (int c0 = 0; c0 < BN; c0 += 32) {
-            if (n0 + c0 >= N) break;
-            uint32_t r[32];
-            tmem_ld_32x32(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
-            tmem_ld_wait();
-            if (row < M) {
-               const int col0 = n0 + c0;
-               const int ncols = min(32, N - col0);
-               if constexpr (KIND == kTF32) {
-                  float *y = ep.Yf + (size_t)row * N + col0;
-                  float v[32];
+         while (alive && next_drain < num_chunks) drain(next_drain++);
+         if (alive && row < M) {
 #pragma unroll
-                  for (int j = 0; j < 32; j++) {
-                     float acc = ep.alpha * __uint_as_float(r[j]);
-                     if (j < ncols) {
-                        if (ep.bias_kind == 1) acc += ep.beta * ep.C[col0 + j];
-                        else if (ep.bias_kind == 2) acc += ep.beta * ep.C[(size_t)row * N + col0 + j];
-                     }
-                     v[j] = ep.relu ? relu_ref(acc) : acc;
-                  }
-                  if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+               if (n0 + c0 < N) {
+                  uint32_t r[32];
 #pragma unroll
-                     for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                  } else {
-#pragma unroll
-                     for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
-                  }
-               } else if constexpr (KIND == kI8) {
-                  uint8_t *y = ep.Yu8 + (size_t)row * N + col0;
-                  uint32_t packed[8];
-#pragma unroll
-                  for (int j = 0; j < 32; j++) {
-                     int q = 0;
-                     if (j < ncols) {
-                        int acc = (int)r[j] + (ep.corr ? ep.corr[col0 + j] : 0);
-                        q = requant_u8(acc, ep.mult[col0 + j], ep.y_zp, ep.relu);
-                     }
-                     if ((j & 3) == 0) packed[j >> 2] = 0;
-                     packed[j >> 2] |= (uint32_t)q << (8 * (j & 3));
-                  }
-                  if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
-                     *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                     *reinterpret_cast<uint4 *>(y + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                  } else {
-#pragma unroll
-                     for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
-                  }
-               } else {
-                  uint32_t hb[16], qb[8];
-#pragma unroll
-                  for (int j = 0; j < 32; j++) {
-                     uint16_t h = 0;
-                     uint8_t q = 0;
-                     if (j < ncols) {
-                        float y = __fmul_rn(__uint_as_float(r[j]), ep.scale);
-                        if (ep.bias) y = __fadd_rn(y, ep.bias[col0 + j]);
-                        if (ep.relu) y = relu_ref(y);
-                        h = f32_to_bf16_rne(y);
-                        if (ep.Yq)
-                           q = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(bf16_to_f32(h), ep.q_scale), __NV_SATFINITE, __NV_E4M3);
-                     }
-                     if ((j & 1) == 0) hb[j >> 1] = 0;
-                     hb[j >> 1] |= (uint32_t)h << (16 * (j & 1));
-                     if ((j & 3) == 0) qb[j >> 2] = 0;
-                     qb[j >> 2] |= (uint32_t)q << (8 * (j & 3));
-                  }
-                  if (ep.Ybf16) {
-                     uint16_t *y = ep.Ybf16 + (size_t)row * N + col0;
-                     if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
-#pragma unroll
-                        for (int j = 0; j < 4; j++)
-                           reinterpret_cast<uint4 *>(y)[j] = make_uint4(hb[4 * j], hb[4 * j + 1], hb[4 * j + 2], hb[4 * j + 3]);
-                     } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint16_t)(hb[j >> 1] >> (16 * (j & 1)));
-                     }
-                  }
-                  if (ep.Yq) {
-                     uint8_t *y = ep.Yq + (size_t)row * N + col0;
-                     if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
-                        *reinterpret_cast<uint4 *>(y) = make_uint4(qb[0], qb[1], qb[2], qb[3]);
-                        *reinterpret_cast<uint4 *>(y + 16) = make_uint4(qb[4], qb[5], qb[6], qb[7]);
-                     } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)(qb[j >> 2] >> (8 * (j & 3)));
-                     }
-                  }
+                  for (int j = 0; j < 32; j++) r[j] = __float_as_uint(acc[c0 + j]);
+                  store_row_chunk<KIND>(ep, r, row, n0 + c0, N);
                }
+            }
+         }
+      } else {
+         if (mbar_wait(&accum_full[0], 0, &abort_flag, status, kStatusWaitAccum, 0)) {
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+               if (n0 + c0 >= N) break;
+               uint32_t r[32];
+               tmem_ld_32x32(t_row + (uint32_t)c0, r);
+               tmem_ld_wait();
+               if (row < M) store_row_chunk<KIND>(ep, r, row, n0 + c0, N);
             }
          }
       }
@@ -315,6 +381,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
    tc_fence_before();
    __syncthreads();
    if (warp == 1) {
+      __syncwarp();
       tc_fence_after();
       tmem_dealloc(tmem_base, TMEM_COLS);
    }

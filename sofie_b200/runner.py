@@ -116,6 +116,29 @@ class Session:
                 raise NotImplementedError(f"operator {op} is outside the dense-contraction path")
         del mw
 
+    def _nhwc_ok(self, name, depth=0):
+        if name == self.model.output_name or depth > 8:
+            return False
+        cons = self._consumers(name)
+        if not cons:
+            return False
+        for L in cons:
+            op = L["op"]
+            if op in ("Conv", "QLinearConv"):
+                if L.get("group", 1) != 1:
+                    return False
+            elif op in ("Relu", "MaxPool"):
+                if not self._nhwc_ok(L["Y"], depth + 1):
+                    return False
+            elif op == "Flatten":
+                nxt = self._consumers(L["Y"])
+                if L["Y"] == self.model.output_name or not nxt or \
+                        any(n["op"] not in ("Gemm", "QLinearMatMul") for n in nxt):
+                    return False
+            else:
+                return False
+        return True
+
     def _flatten_perm(self, src_name, K):
         """Column permutation that maps a weight's K axis from (c,h,w) order to the (h,w,c) order of an
         NHWC activation, or None when the activation is not NHWC / not 4-D."""
@@ -159,8 +182,10 @@ class Session:
         oH, oW = ops.conv_out_hw(H, Wd, kH, kW, (pads[0], pads[1]), strides)
         if pool == 2:
             oH, oW = oH // 2, oW // 2
-        # NHWC output when every consumer is another convolution / pool / flatten->matmul of this runner
-        y_layout = LAYOUT_NHWC if (self.nhwc and group == 1) else LAYOUT_NCHW
+        # NHWC output when the result stays inside the runner: every consumer is a convolution, a
+        # pool, a Relu or a Flatten feeding a matmul (whose weight is permuted instead); model
+        # outputs keep the reference's NCHW order
+        y_layout = LAYOUT_NHWC if (self.nhwc and group == 1 and self._nhwc_ok(out)) else LAYOUT_NCHW
         x_layout = self.layout[x]
         packed = x_layout == LAYOUT_NHWC and group == 1
         self.layout[out], self.shape[out] = y_layout, (N, Cout, oH, oW)

@@ -45,6 +45,8 @@ def test_status_strings_and_argument_errors():
     rc = lib.sofie_cuda_gemm_f32(None, None, None, None, None, None)
     assert rc == capi.ERR_INVALID
     assert b"NULL" in lib.sofie_cuda_last_error()
+    d = capi.GemmF32Desc(0, 4, 4, 0, 0, 1.0, 1.0, 0, 0)   # an empty batch is not an error
+    assert lib.sofie_cuda_gemm_f32(None, C.byref(d), None, None, None, None) == capi.OK
     d = capi.GemmF32Desc(4, 0, 4, 0, 0, 1.0, 1.0, 0, 0)
     rc = lib.sofie_cuda_gemm_f32(None, C.byref(d), C.c_void_p(16), C.c_void_p(16), None, C.c_void_p(16))
     assert rc == capi.ERR_INVALID
