@@ -58,6 +58,9 @@ int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *d, const float 
    if (d->M == 0) return SOFIE_CUDA_OK; // an empty batch has no rows to compute (and may have NULL A / Y)
    SOFIE_REQUIRE(A && B && Y, "NULL tensor");
    cudaStream_t s = as_stream(stream);
+   // few rows, few columns, long K: split K over the grid instead of running on two or three SMs
+   if (forced_engine() != SOFIE_ENGINE_TCGEN05 && splitk_shape_ok(*d) && ceil_div(d->M, 128) < 32)
+      return launch_gemm_f32_splitk_auto(s, *d, A, B, C, Y);
    return dispatch([&] { return launch_gemm_f32_umma(s, *d, A, B, C, Y); },
                    [&] { return launch_gemm_f32_simt(s, *d, A, B, C, Y); });
 }

@@ -1,0 +1,144 @@
+// Skinny fp32 GEMM: few output columns (N <= 16), few rows, long K -- the shape of a classifier head
+// behind a flattened feature map (256 x 10 x 4096). A 128 x N tile machine would run it on two or
+// three SMs; here K is split across the grid instead. Pass 1 writes per-slab partial dot products
+// to a scratch buffer [splits][M][N]; pass 2 adds the slabs in a fixed order (deterministic, no
+// atomics) and applies alpha, bias and Relu.
+#include "contract.cuh"
+
+#include <map>
+#include <mutex>
+
+namespace sofie {
+
+constexpr int kSplitKMaxN = 16;
+constexpr int kSplitKWarps = 8;
+
+// One warp = one output row over one K slab, all N columns. Lanes stride K, so the loads of the A
+// row and of every B row are coalesced 128-byte lines; B is shared by all warps through L1/L2.
+template <bool TB>
+__global__ void __launch_bounds__(kSplitKWarps * 32)
+gemm_f32_splitk_partial_kernel(int M, int N, int K, int slab, const float *__restrict__ A, const float *__restrict__ B,
+                               float *__restrict__ partial)
+{
+   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+   const int m = blockIdx.x * kSplitKWarps + warp;
+   const int s = blockIdx.y;
+   if (m >= M) return;
+   const int k0 = s * slab, k1 = min(K, k0 + slab);
+   float acc[kSplitKMaxN];
+#pragma unroll
+   for (int n = 0; n < kSplitKMaxN; n++) acc[n] = 0.f;
+   const float *a = A + (size_t)m * K;
+   for (int k = k0 + lane; k < k1; k += 32) {
+      const float av = a[k];
+#pragma unroll
+      for (int n = 0; n < kSplitKMaxN; n++)
+         if (n < N) acc[n] = fmaf(av, TB ? B[(size_t)n * K + k] : B[(size_t)k * N + n], acc[n]);
+   }
+#pragma unroll
+   for (int n = 0; n < kSplitKMaxN; n++) {
+      if (n < N) {
+         float v = acc[n];
+         for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+         if (lane == 0) partial[((size_t)s * M + m) * N + n] = v;
+      }
+   }
+}
+
+__global__ void gemm_f32_splitk_reduce_kernel(sofie_gemm_f32_desc d, int splits, const float *__restrict__ partial,
+                                              const float *__restrict__ C, float *__restrict__ Y)
+{
+   const size_t total = (size_t)d.M * d.N;
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+      float sum = 0.f;
+      for (int s = 0; s < splits; s++) sum += partial[(size_t)s * total + i];
+      float y = d.alpha * sum;
+      if (d.bias_kind == 1) y += d.beta * C[i % d.N];
+      else if (d.bias_kind == 2) y += d.beta * C[i];
+      Y[i] = d.relu ? relu_ref(y) : y;
+   }
+}
+
+bool splitk_shape_ok(const sofie_gemm_f32_desc &d)
+{
+   return !d.transA && d.N <= kSplitKMaxN && d.K >= 1024 && (long long)d.M * d.N <= (1 << 16);
+}
+
+int splitk_splits(const sofie_gemm_f32_desc &d, size_t scratch_floats)
+{
+   // enough (row, slab) pairs to fill the GPU about twice, slabs of at least 128 elements of K
+   int splits = (2 * kNumSMs * kSplitKWarps + d.M - 1) / d.M;
+   if (splits > d.K / 128) splits = d.K / 128;
+   if (splits > 64) splits = 64;
+   if (splits < 1) splits = 1;
+   while (splits > 1 && (size_t)splits * d.M * d.N > scratch_floats) splits--;
+   return splits;
+}
+
+// Runs both passes with the given scratch buffer of `scratch_floats` floats (device memory).
+int launch_gemm_f32_splitk(cudaStream_t s, const sofie_gemm_f32_desc &d, const float *A, const float *B, const float *C,
+                           float *Y, float *scratch, size_t scratch_floats)
+{
+   if (!splitk_shape_ok(d)) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "split-K GEMM takes A[M,K], N <= 16, K >= 1024, M*N <= 65536");
+   const int splits = splitk_splits(d, scratch_floats);
+   if ((size_t)splits * d.M * d.N > scratch_floats)
+      return fail(SOFIE_CUDA_ERR_NOMEM, "split-K scratch of %zu floats is too small for M*N = %lld", scratch_floats,
+                  (long long)d.M * d.N);
+   int slab = (d.K + splits - 1) / splits;
+   slab = (slab + 31) & ~31; // whole 128-byte lines per slab
+   const int used = (d.K + slab - 1) / slab;
+   dim3 grid(ceil_div(d.M, kSplitKWarps), used);
+   if (d.transB) gemm_f32_splitk_partial_kernel<true><<<grid, kSplitKWarps * 32, 0, s>>>(d.M, d.N, d.K, slab, A, B, scratch);
+   else gemm_f32_splitk_partial_kernel<false><<<grid, kSplitKWarps * 32, 0, s>>>(d.M, d.N, d.K, slab, A, B, scratch);
+   SOFIE_LAUNCH_CHECK("gemm_f32_splitk_partial_kernel");
+   const int blocks = (int)ceil_div<size_t>((size_t)d.M * d.N, 256);
+   gemm_f32_splitk_reduce_kernel<<<blocks, 256, 0, s>>>(d, used, scratch, C, Y);
+   SOFIE_LAUNCH_CHECK("gemm_f32_splitk_reduce_kernel");
+   set_last_engine(SOFIE_ENGINE_SIMT);
+   return SOFIE_CUDA_OK;
+}
+
+// Library-owned scratch of the regular entry point. A pool of buffers per device is allocated on the
+// first call on that device (which must come before any stream capture); every stream that calls
+// gets its own buffer from the pool, so calls on different streams never share one and no
+// allocation happens once a capture is running.
+constexpr size_t kSplitKScratchFloats = size_t(1) << 19; // 2 MB: 64 slabs x 8192 outputs
+constexpr int kSplitKPoolBuffers = 16;
+
+float *splitk_scratch_for(cudaStream_t s)
+{
+   struct DevicePool {
+      float *base = nullptr;
+      std::map<cudaStream_t, int> slot_of;
+   };
+   static std::mutex mutex;
+   static DevicePool pools[64];
+   int dev = 0;
+   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+   std::lock_guard<std::mutex> lock(mutex);
+   DevicePool &pool = pools[dev];
+   if (!pool.base) {
+      if (cudaMalloc(&pool.base, kSplitKPoolBuffers * kSplitKScratchFloats * sizeof(float)) != cudaSuccess) {
+         cudaGetLastError();
+         pool.base = nullptr;
+         return nullptr;
+      }
+   }
+   auto it = pool.slot_of.find(s);
+   if (it == pool.slot_of.end()) {
+      if ((int)pool.slot_of.size() >= kSplitKPoolBuffers) return nullptr;
+      it = pool.slot_of.emplace(s, (int)pool.slot_of.size()).first;
+   }
+   return pool.base + (size_t)it->second * kSplitKScratchFloats;
+}
+
+int launch_gemm_f32_splitk_auto(cudaStream_t s, const sofie_gemm_f32_desc &d, const float *A, const float *B,
+                                const float *C, float *Y)
+{
+   if (!splitk_shape_ok(d)) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "not a split-K shape");
+   float *scratch = splitk_scratch_for(s);
+   if (!scratch) return fail(SOFIE_CUDA_ERR_NOMEM, "no split-K scratch buffer: allocation failed (first call during a stream capture?) or more than 16 streams in use");
+   return launch_gemm_f32_splitk(s, d, A, B, C, Y, scratch, kSplitKScratchFloats);
+}
+
+} // namespace sofie
