@@ -119,6 +119,32 @@ typedef struct sofie_gemm_f32_desc {
 int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *desc, const float *A, const float *B,
                         const float *C, float *Y);
 
+/*
+ * Allocation-free skinny GEMM (no counterpart in the reference).
+ *
+ * Same arithmetic and descriptor as sofie_cuda_gemm_f32, restricted to the split-K shape class
+ * (A not transposed, N <= 16, K >= 1024) and to M*N <= SOFIE_CUDA_SPLITK_STATIC_MAX_OUTPUTS. It is
+ * meant for callers that must not trigger a device allocation: a serving loop that has handed all
+ * free device memory to its own pool, code that runs while another thread captures a CUDA graph
+ * in global capture mode (where cudaMalloc is an error), or latency-critical callers for whom the
+ * implicit device synchronisation of cudaMalloc / cudaFree is unacceptable. The regular entry point
+ * obtains its per-slab partial sums buffer from the CUDA allocator the first time a stream uses
+ * it; this one keeps that buffer in a fixed 4 MiB array inside the library image (every GPU that
+ * loads libSOFIE_cuda holds those 4 MiB until the process exits) and never calls cudaMalloc,
+ * cudaFree or any allocating routine.
+ *   - The first call on each device looks up the array's address on that device; make that first
+ *     call before starting a stream capture.
+ *   - All calls on a device share the one array. Nothing in it has to start at zero (every partial
+ *     sum is rewritten before it is read), but two calls that overlap on the GPU -- different
+ *     streams, or graphs replayed concurrently -- race on it and corrupt each other's results.
+ *   - Shapes outside the class return SOFIE_CUDA_ERR_UNSUPPORTED; more than
+ *     SOFIE_CUDA_SPLITK_STATIC_MAX_OUTPUTS outputs return SOFIE_CUDA_ERR_INVALID.
+ */
+#define SOFIE_CUDA_SPLITK_STATIC_FLOATS (1u << 20)
+#define SOFIE_CUDA_SPLITK_STATIC_MAX_OUTPUTS 16384
+int sofie_cuda_gemm_f32_splitk_static(void *stream, const sofie_gemm_f32_desc *desc, const float *A, const float *B,
+                                      const float *C, float *Y);
+
 /* out[cols,rows] = in[rows,cols]^T, used once per Session to bring a [K,N] weight to [N,K]. */
 int sofie_cuda_transpose_f32(void *stream, const float *in, float *out, int32_t rows, int32_t cols);
 

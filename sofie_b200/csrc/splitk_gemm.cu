@@ -141,4 +141,59 @@ int launch_gemm_f32_splitk_auto(cudaStream_t s, const sofie_gemm_f32_desc &d, co
    return launch_gemm_f32_splitk(s, d, A, B, C, Y, scratch, kSplitKScratchFloats);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant. Its scratch is this file-scope device array, so no device allocation
+// takes place on any call. In host code the array's name is only a stand-in symbol, not a device
+// address: the address each device uses is looked up once per device with cudaGetSymbolAddress
+// (with that device current) and that pointer is what the kernels receive.
+constexpr size_t kSplitKStaticFloats = SOFIE_CUDA_SPLITK_STATIC_FLOATS;
+static __device__ __align__(256) float g_splitk_static_scratch[kSplitKStaticFloats];
+
+static float *splitk_static_scratch(int *status)
+{
+   static std::mutex mutex;
+   static float *per_device[64] = {nullptr};
+   int dev = 0;
+   cudaError_t err = cudaGetDevice(&dev);
+   if (err != cudaSuccess || dev < 0 || dev >= 64) {
+      *status = fail(SOFIE_CUDA_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(err));
+      return nullptr;
+   }
+   std::lock_guard<std::mutex> lock(mutex);
+   if (!per_device[dev]) {
+      float *p = nullptr;
+      err = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_splitk_static_scratch);
+      if (err != cudaSuccess || !p) {
+         cudaGetLastError();
+         *status = fail(SOFIE_CUDA_ERR_CUDA, "cudaGetSymbolAddress of the static split-K scratch: %s", cudaGetErrorString(err));
+         return nullptr;
+      }
+      per_device[dev] = p;
+   }
+   *status = SOFIE_CUDA_OK;
+   return per_device[dev];
+}
+
 } // namespace sofie
+
+extern "C" int sofie_cuda_gemm_f32_splitk_static(void *stream, const sofie_gemm_f32_desc *d, const float *A, const float *B,
+                                                 const float *C, float *Y)
+{
+   using namespace sofie;
+   SOFIE_REQUIRE(d != nullptr, "NULL descriptor");
+   SOFIE_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0, "bad GEMM shape %d x %d x %d", d->M, d->N, d->K);
+   SOFIE_REQUIRE(d->bias_kind >= 0 && d->bias_kind <= 2, "bias_kind must be 0, 1 or 2");
+   SOFIE_REQUIRE(d->bias_kind == 0 || C != nullptr, "bias_kind set but C is NULL");
+   if (d->M == 0) return SOFIE_CUDA_OK;
+   SOFIE_REQUIRE(A && B && Y, "NULL tensor");
+   if (!splitk_shape_ok(*d))
+      return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "the allocation-free GEMM takes A[M,K] (no transA), N <= 16 and K >= 1024; got %d x %d x %d",
+                  d->M, d->N, d->K);
+   if ((long long)d->M * d->N > SOFIE_CUDA_SPLITK_STATIC_MAX_OUTPUTS)
+      return fail(SOFIE_CUDA_ERR_INVALID, "M*N = %lld outputs exceed the %d the static scratch is sized for",
+                  (long long)d->M * d->N, SOFIE_CUDA_SPLITK_STATIC_MAX_OUTPUTS);
+   int rc = SOFIE_CUDA_OK;
+   float *scratch = splitk_static_scratch(&rc);
+   if (!scratch) return rc;
+   return launch_gemm_f32_splitk(as_stream(stream), *d, A, B, C, Y, scratch, kSplitKStaticFloats);
+}
