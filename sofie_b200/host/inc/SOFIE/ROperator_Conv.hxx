@@ -1,0 +1,203 @@
+// ONNX Conv (2-D), optional fused Relu and MaxPool 2x2.
+//
+// Constructor signatures as in the reference (src/SOFIE_core/inc/SOFIE/ROperator_Conv.hxx:52-92) and
+// the same attribute rules: no `pads` attribute means pad 1 (:136-139), SAME_UPPER / SAME_LOWER give
+// k/2 after the reference's averaging of asymmetric pads (:140-158, :387-410), output extent
+// (in + pads - k_dilated) / stride + 1 (:178-199). The reference emits a weight repack, a per-image
+// UTILITY::Im2col, sgemm_ and saxpy_ (:302-522); this emits ONE call of sofie_cuda_conv2d_f32 and
+// registers no `_f` / `_xcol` scratch tensors. When the model plan fuses a following Relu and
+// MaxPool(2x2, stride 2) the call's descriptor carries them and the output tensor is the pool's.
+// 1-D and 3-D convolutions are outside the CUDA path.
+#ifndef SOFIE_ROPERATOR_CONV
+#define SOFIE_ROPERATOR_CONV
+
+#include <sstream>
+
+#include "SOFIE/Emit.hxx"
+#include "SOFIE/RModel.hxx"
+#include "SOFIE/ROperator.hxx"
+
+namespace SOFIE {
+
+// Attribute resolution shared by Conv and QLinearConv.
+struct ConvAttributes {
+   std::string autopad = "NOTSET";
+   std::vector<size_t> dilations, kernel_shape, pads, strides;
+   size_t group = 1;
+   // resolved values
+   size_t kH = 0, kW = 0, padH = 0, padW = 0, sH = 1, sW = 1, dH = 1, dW = 1;
+
+   void Resolve(const std::vector<size_t> &shapeX, const std::vector<size_t> &shapeW)
+   {
+      if (shapeX.size() != 4 || shapeW.size() != 4)
+         throw std::runtime_error("SOFIE Conv Op: only 2-D convolutions (rank-4 tensors) are generated for the CUDA path");
+      if (group == 0) group = shapeX[1] / shapeW[1];
+      kH = kernel_shape.empty() ? shapeW[2] : kernel_shape[0];
+      kW = kernel_shape.empty() ? shapeW[3] : kernel_shape[1];
+      if (kH != shapeW[2] || kW != shapeW[3]) throw std::runtime_error("SOFIE Conv Op: kernel_shape differs from the weight tensor");
+      dH = dilations.empty() ? 1 : dilations[0];
+      dW = dilations.size() < 2 ? dH : dilations[1];
+      sH = strides.empty() ? 1 : strides[0];
+      sW = strides.size() < 2 ? sH : strides[1];
+      const size_t eH = kH + (dH - 1) * (kH - 1), eW = kW + (dW - 1) * (kW - 1);
+      std::vector<size_t> p;
+      if (autopad == "NOTSET") {
+         p = pads.empty() ? std::vector<size_t>{1, 1, 1, 1} : pads; // the reference's default is 1, not 0
+      } else if (autopad == "SAME_UPPER" || autopad == "SAME_LOWER") {
+         p = {eH / 2, eW / 2, eH / 2, eW / 2};
+         if (eH % 2 == 1) (autopad == "SAME_UPPER") ? p[0]++ : p[2]++;
+         if (eW % 2 == 1) (autopad == "SAME_UPPER") ? p[1]++ : p[3]++;
+      } else if (autopad == "VALID") {
+         p = {0, 0, 0, 0};
+      } else {
+         throw std::runtime_error("SOFIE Conv Op invalid auto_pad " + autopad);
+      }
+      if (p.size() != 4) throw std::runtime_error("SOFIE Conv Op: pads must have 4 values");
+      // asymmetric padding: the reference warns and averages; the same rule keeps results identical
+      padH = (p[0] == p[2]) ? p[0] : (p[0] + p[2]) / 2;
+      padW = (p[1] == p[3]) ? p[1] : (p[1] + p[3]) / 2;
+      pads = p;
+   }
+   std::vector<size_t> OutputShape(const std::vector<size_t> &shapeX, const std::vector<size_t> &shapeW) const
+   {
+      const size_t eH = kH + (dH - 1) * (kH - 1), eW = kW + (dW - 1) * (kW - 1);
+      // the reference sizes the output from the un-averaged pads (ROperator_Conv.hxx:178-189)
+      size_t oH = (shapeX[2] + pads[0] + pads[2] - eH) / sH + 1;
+      size_t oW = (shapeX[3] + pads[1] + pads[3] - eW) / sW + 1;
+      return {shapeX[0], shapeW[0], oH, oW};
+   }
+};
+
+template <typename T>
+class ROperator_Conv final : public ROperator {
+private:
+   ConvAttributes fAttr;
+   std::string fNX, fNW, fNB, fNY;
+   std::string fNWdev;          // weight tensor the emitted call reads (packed or original)
+   std::string fNOut;           // tensor the call writes (the fused pool's output when fused)
+   std::vector<size_t> fShapeX, fShapeW, fShapeB, fShapeY, fShapeOut;
+   bool fFusedRelu = false;
+   int fFusedPool = 0;
+   ELayout fLayoutX = ELayout::NCHW, fLayoutY = ELayout::NCHW;
+   bool fPacked = false;
+
+public:
+   ROperator_Conv() {}
+   ROperator_Conv(std::string autopad, std::vector<size_t> dilations, size_t group, std::vector<size_t> kernelShape,
+                  std::vector<size_t> pads, std::vector<size_t> strides, std::string nameX, std::string nameW,
+                  std::string nameB, std::string nameY)
+      : fNX(UTILITY::Clean_name(nameX)), fNW(UTILITY::Clean_name(nameW)), fNB(UTILITY::Clean_name(nameB)),
+        fNY(UTILITY::Clean_name(nameY))
+   {
+      static_assert(std::is_same_v<T, float>, "SOFIE - Conv is generated for float tensors");
+      fAttr.autopad = autopad;
+      fAttr.dilations = dilations;
+      fAttr.group = group;
+      fAttr.kernel_shape = kernelShape;
+      fAttr.pads = pads;
+      fAttr.strides = strides;
+      fInputTensorNames = {fNX, fNW};
+      if (!fNB.empty()) fInputTensorNames.push_back(fNB);
+      fOutputTensorNames = {fNY};
+      fNOut = fNY;
+   }
+   ROperator_Conv(std::string autopad, std::vector<size_t> dilations, size_t group, std::vector<size_t> kernelShape,
+                  std::vector<size_t> pads, std::vector<size_t> strides, std::string nameX, std::string nameW,
+                  std::string nameY)
+      : ROperator_Conv(autopad, dilations, group, kernelShape, pads, strides, nameX, nameW, "", nameY)
+   {
+   }
+
+   EOpKind Kind() const override { return EOpKind::Conv; }
+   bool AcceptsNHWC(const std::string &input) const override { return input == fNX && fAttr.group == 1; }
+   // fusion interface used by the model plan
+   const std::string &OutputName() const { return fNOut; }
+   void FuseRelu(const std::string &reluOutput)
+   {
+      fFusedRelu = true;
+      fNOut = reluOutput;
+      fOutputTensorNames = {fNOut};
+   }
+   void FusePool2x2(const std::string &poolOutput)
+   {
+      fFusedPool = 2;
+      fNOut = poolOutput;
+      fOutputTensorNames = {fNOut};
+   }
+
+   std::vector<ETensorType> TypeInference(std::vector<ETensorType> input) override { return {input[0]}; }
+   std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override
+   {
+      if (input.size() < 2 || input.size() > 3) throw std::runtime_error("SOFIE Conv Op Shape inference needs 2 or 3 input tensors");
+      fAttr.Resolve(input[0], input[1]);
+      return {fAttr.OutputShape(input[0], input[1])};
+   }
+
+   void Initialize(RModel &model) override
+   {
+      fUseSession = model.UseSession();
+      if (!model.CheckIfTensorAlreadyExist(fNX)) throw std::runtime_error("SOFIE Conv op Input Tensor " + fNX + " is not found in model");
+      if (!model.CheckIfTensorAlreadyExist(fNW)) throw std::runtime_error("SOFIE Conv op Input weight Tensor " + fNW + " is not found in model");
+      if (!model.IsInitializedTensor(fNW)) throw std::runtime_error("SOFIE Conv op: weights must be a constant tensor");
+      fShapeX = model.GetTensorShape(fNX);
+      fShapeW = model.GetTensorShape(fNW);
+      fShapeY = ShapeInference({fShapeX, fShapeW})[0];
+      if (fShapeW[1] * fAttr.group != fShapeX[1]) throw std::runtime_error("SOFIE Conv op: channels of X and W do not match the group count");
+      if (!fNB.empty()) {
+         if (!model.IsInitializedTensor(fNB)) throw std::runtime_error("SOFIE Conv op Input Tensor " + fNB + " is not found in model");
+         fShapeB = model.GetTensorShape(fNB);
+         if (ConvertShapeToLength(fShapeB) != fShapeY[1])
+            throw std::runtime_error("SOFIE Conv op: Bias Tensor has wrong shape: " + ConvertShapeToString(fShapeB));
+      }
+      model.AddIntermediateTensor(fNY, model.GetTensorType(fNX), fShapeY);
+   }
+
+   void PlanDevice(RModel &model) override
+   {
+      fLayoutX = model.GetTensorLayout(model.ResolveAlias(fNX));
+      fShapeOut = model.GetTensorShape(fNOut);
+      fLayoutY = (fAttr.group == 1 && model.CanStayNHWC(fNOut)) ? ELayout::NHWC : ELayout::NCHW;
+      model.SetTensorLayout(fNOut, fLayoutY);
+      // NHWC input: weights packed [Cout][kH][kW][Cin], the operand layout of the tensor-core kernel
+      fPacked = (fLayoutX == ELayout::NHWC && fAttr.group == 1);
+      fNWdev = fNW;
+      if (fPacked) {
+         const float *src = model.GetInitializedTensor(fNW).data<float>();
+         size_t Cout = fShapeW[0], C = fShapeW[1], kH = fShapeW[2], kW = fShapeW[3];
+         std::shared_ptr<void> buf(malloc(Cout * C * kH * kW * sizeof(float)), free);
+         float *dst = static_cast<float *>(buf.get());
+         for (size_t o = 0; o < Cout; o++)
+            for (size_t c = 0; c < C; c++)
+               for (size_t r = 0; r < kH; r++)
+                  for (size_t s = 0; s < kW; s++) dst[((o * kH + r) * kW + s) * C + c] = src[((o * C + c) * kH + r) * kW + s];
+         fNWdev = fNW + "_ohwi";
+         if (!model.IsInitializedTensor(fNWdev)) model.AddInitializedTensor(fNWdev, ETensorType::FLOAT, {Cout, kH, kW, C}, buf);
+      }
+      model.UseOnDevice(fNWdev);
+      if (!fNB.empty()) model.UseOnDevice(fNB);
+   }
+
+   std::string Generate(std::string OpName) override
+   {
+      OpName = "op_" + OpName;
+      if (fShapeX.empty() || fShapeW.empty() || fShapeY.empty())
+         throw std::runtime_error("SOFIE Conv Op called to Generate without being initialized first");
+      std::stringstream out;
+      out << "\n" << SP << "//----  operator Conv " << OpName << (fFusedRelu ? " + Relu" : "") << (fFusedPool ? " + MaxPool2x2" : "")
+          << " -> " << fNOut << " " << ConvertShapeToString(fShapeOut) << (fLayoutY == ELayout::NHWC ? " (NHWC)" : "") << "\n";
+      out << SP << "{\n";
+      out << SP << SP << "const sofie_conv2d_desc d = {" << fShapeX[0] << ", " << fShapeX[1] << ", " << fShapeX[2] << ", "
+          << fShapeX[3] << ", " << fShapeW[0] << ", " << fAttr.kH << ", " << fAttr.kW << ", " << fAttr.padH << ", " << fAttr.padW
+          << ", " << fAttr.sH << ", " << fAttr.sW << ", " << fAttr.dH << ", " << fAttr.dW << ", " << fAttr.group << ", "
+          << (int)fLayoutX << ", " << (int)fLayoutY << ", " << (fPacked ? 1 : 0) << ", " << (fFusedRelu ? 1 : 0) << ", "
+          << fFusedPool << "};\n";
+      out << EMIT::Call(SP + SP, "sofie_cuda_conv2d_f32(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNWdev) + ", " +
+                                    (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB)) + ", " + EMIT::Dev(fNOut) + ")");
+      out << SP << "}\n";
+      return out.str();
+   }
+};
+
+} // namespace SOFIE
+
+#endif

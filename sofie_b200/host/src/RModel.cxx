@@ -1,0 +1,758 @@
+// RModel: tensor registries, device plan and emission of the Session.
+// Public behaviour follows the reference (src/SOFIE_core/src/RModel.cxx); see RModel.hxx for what
+// the emitted Session looks like on the CUDA path.
+#include "SOFIE/RModel.hxx"
+
+#include <algorithm>
+#include <fstream>
+#include <iomanip>
+#include <iostream>
+#include <limits>
+
+#include "SOFIE/Emit.hxx"
+#include "SOFIE/ROperator_Conv.hxx"
+#include "SOFIE/ROperator_Gemm.hxx"
+#include "SOFIE/ROperator_Pool.hxx"
+#include "SOFIE/ROperator_QLinear.hxx"
+#include "SOFIE/ROperator_Relu.hxx"
+#include "SOFIE/ROperator_Reshape.hxx"
+
+namespace SOFIE {
+
+// ---------------------------------------------------------------------------------- registries
+const std::vector<size_t> &RModel::GetTensorShape(std::string name) const
+{
+   auto f = fReadyInputTensorInfos.find(name);
+   if (f != fReadyInputTensorInfos.end()) return f->second.shape;
+   auto f2 = fInitializedTensors.find(name);
+   if (f2 != fInitializedTensors.end()) return f2->second.shape();
+   auto f3 = fIntermediateTensorInfos.find(name);
+   if (f3 != fIntermediateTensorInfos.end()) return f3->second.shape;
+   if (fInputTensorInfos.count(name))
+      throw std::runtime_error("SOFIE tensor [" + name + "] is an input tensor with unspecified dimension parameter");
+   throw std::runtime_error("SOFIE tensor [" + name + "] for which the shape is requested is not found");
+}
+
+std::vector<Dim> RModel::GetDynamicTensorShape(std::string name) const
+{
+   auto f = fInputTensorInfos.find(name);
+   if (f != fInputTensorInfos.end()) return f->second.shape;
+   return ConvertShapeToDim(GetTensorShape(name));
+}
+
+const ETensorType &RModel::GetTensorType(std::string name) const
+{
+   auto f = fReadyInputTensorInfos.find(name);
+   if (f != fReadyInputTensorInfos.end()) return f->second.type;
+   auto f2 = fInitializedTensors.find(name);
+   if (f2 != fInitializedTensors.end()) return f2->second.type();
+   auto f3 = fInputTensorInfos.find(name);
+   if (f3 != fInputTensorInfos.end()) return f3->second.type;
+   auto f4 = fIntermediateTensorInfos.find(name);
+   if (f4 != fIntermediateTensorInfos.end()) return f4->second.type;
+   throw std::runtime_error("SOFIE tensor [" + name + "] for which the type is requested is not found");
+}
+
+bool RModel::CheckIfTensorAlreadyExist(std::string name)
+{
+   return fReadyInputTensorInfos.count(name) || fInitializedTensors.count(name) || fIntermediateTensorInfos.count(name) ||
+          fInputTensorInfos.count(name);
+}
+
+void RModel::AddInputTensorInfo(std::string input_name, ETensorType type, std::vector<Dim> shape)
+{
+   input_name = UTILITY::Clean_name(input_name);
+   if (CheckIfTensorAlreadyExist(input_name))
+      throw std::runtime_error("SOFIE input tensor with name " + input_name + " already exists \n");
+   fInputTensorInfos[input_name] = InputTensorInfo{type, shape};
+}
+
+void RModel::AddInputTensorInfo(std::string input_name, ETensorType type, std::vector<size_t> shape)
+{
+   input_name = UTILITY::Clean_name(input_name);
+   if (CheckIfTensorAlreadyExist(input_name))
+      throw std::runtime_error("SOFIE input tensor with name " + input_name + " already exists \n");
+   fReadyInputTensorInfos[input_name] = TensorInfo{type, shape};
+}
+
+void RModel::AddInputTensorName(std::string name) { fInputTensorNames.emplace_back(UTILITY::Clean_name(name)); }
+
+void RModel::AddOperator(std::unique_ptr<ROperator> op, int order_execution)
+{
+   AddBlasRoutines(op->GetBlasRoutines());
+   for (auto &lib : op->GetStdLibs()) AddNeededStdLib(lib);
+   if (order_execution >= 0 && (size_t)order_execution <= fOperators.size())
+      fOperators.insert(fOperators.begin() + order_execution, std::move(op));
+   else
+      fOperators.push_back(std::move(op));
+}
+
+void RModel::AddInitializedTensor(std::string tensor_name, ETensorType type, std::vector<std::size_t> shape,
+                                  std::shared_ptr<void> data)
+{
+   tensor_name = UTILITY::Clean_name(tensor_name);
+   if (CheckIfTensorAlreadyExist(tensor_name))
+      throw std::runtime_error("SOFIE initialized tensor with name " + tensor_name + " already exists \n");
+   fInitializedTensors[tensor_name] = InitializedTensor{type, shape, data};
+}
+
+void RModel::AddConstantTensor(std::string tensor_name, ETensorType type, std::vector<std::size_t> shape,
+                               std::shared_ptr<void> data)
+{
+   tensor_name = UTILITY::Clean_name(tensor_name);
+   if (CheckIfTensorAlreadyExist(tensor_name))
+      throw std::runtime_error("SOFIE initialized tensor with name " + tensor_name + " already exists \n");
+   fInitializedTensors[tensor_name] = InitializedTensor{type, shape, data, true};
+}
+
+void RModel::SetNotWritableInitializedTensor(const std::string &tensor_name)
+{
+   auto t = fInitializedTensors.find(tensor_name);
+   if (t == fInitializedTensors.end()) throw std::runtime_error("SOFIE initialized tensor " + tensor_name + " not found");
+   t->second.SetNotWritable();
+}
+
+bool RModel::IsInitializedTensor(const std::string &name) const { return fInitializedTensors.count(UTILITY::Clean_name(name)); }
+bool RModel::IsConstantTensor(const std::string &name) const
+{
+   auto it = fInitializedTensors.find(UTILITY::Clean_name(name));
+   return it != fInitializedTensors.end() && it->second.IsConstantTensor();
+}
+bool RModel::IsDimInputTensor(const std::string &name) const { return fInputTensorInfos.count(UTILITY::Clean_name(name)); }
+bool RModel::IsReadyInputTensor(const std::string &name) const { return fReadyInputTensorInfos.count(UTILITY::Clean_name(name)); }
+
+void RModel::AddIntermediateTensor(std::string tensor_name, ETensorType type, std::vector<Dim> dim_shape)
+{
+   auto int_shape = ConvertShapeToInt(dim_shape);
+   if (int_shape.empty() && !dim_shape.empty())
+      throw std::runtime_error("SOFIE intermediate tensor " + tensor_name + " has a parametric shape; shapes are fixed at Generate()");
+   AddIntermediateTensor(tensor_name, type, int_shape);
+}
+
+void RModel::AddIntermediateTensor(std::string tensor_name, ETensorType type, std::vector<std::size_t> shape)
+{
+   tensor_name = UTILITY::Clean_name(tensor_name);
+   if (CheckIfTensorAlreadyExist(tensor_name))
+      throw std::runtime_error("SOFIE intermediate tensor with name " + tensor_name + " already exists \n");
+   fIntermediateTensorInfos[tensor_name] = TensorInfo{type, shape};
+}
+
+void RModel::AddOutputTensorNameList(std::vector<std::string> names)
+{
+   fOutputTensorNames.clear();
+   for (auto &n : names) fOutputTensorNames.emplace_back(UTILITY::Clean_name(n));
+}
+
+void RModel::UpdateOutputTensorList(std::vector<std::string> curr, std::vector<std::string> modify)
+{
+   for (size_t i = 0; i < curr.size(); ++i) {
+      auto it = std::find(fOutputTensorNames.begin(), fOutputTensorNames.end(), UTILITY::Clean_name(curr[i]));
+      if (it != fOutputTensorNames.end()) *it = UTILITY::Clean_name(modify[i]);
+   }
+}
+
+void RModel::UpdateInitializedTensor(std::string tensor_name, ETensorType type, std::vector<std::size_t> shape,
+                                     std::shared_ptr<void> data)
+{
+   tensor_name = UTILITY::Clean_name(tensor_name);
+   if (!fInitializedTensors.count(tensor_name))
+      throw std::runtime_error("SOFIE tensor " + tensor_name + " not found when trying to update it");
+   fInitializedTensors[tensor_name] = InitializedTensor{type, shape, data};
+}
+
+std::shared_ptr<void> RModel::GetInitializedTensorData(std::string tensor_name)
+{
+   auto f = fInitializedTensors.find(tensor_name);
+   if (f == fInitializedTensors.end())
+      throw std::runtime_error("SOFIE tensor " + tensor_name + " not found when trying to get its data");
+   return f->second.sharedptr();
+}
+
+const InitializedTensor &RModel::GetInitializedTensor(const std::string &name) const
+{
+   auto f = fInitializedTensors.find(name);
+   if (f == fInitializedTensors.end()) throw std::runtime_error("SOFIE initialized tensor " + name + " not found");
+   return f->second;
+}
+
+// ---------------------------------------------------------------------------------- device plan helpers
+ELayout RModel::GetTensorLayout(const std::string &name) const
+{
+   auto it = fLayouts.find(name);
+   return it == fLayouts.end() ? ELayout::NCHW : it->second;
+}
+
+std::string RModel::ResolveAlias(std::string name) const
+{
+   for (int depth = 0; depth < 64; depth++) {
+      auto it = fAliases.find(name);
+      if (it == fAliases.end()) return name;
+      name = it->second;
+   }
+   throw std::runtime_error("SOFIE alias chain of tensor " + name + " does not end");
+}
+
+std::vector<ROperator *> RModel::Consumers(const std::string &name) const
+{
+   std::vector<ROperator *> out;
+   for (auto &op : fOperators) {
+      if (op->IsFusedAway()) continue;
+      for (auto &in : op->GetOpInputTensors())
+         if (in == name) {
+            out.push_back(op.get());
+            break;
+         }
+   }
+   return out;
+}
+
+bool RModel::IsModelOutput(const std::string &name) const
+{
+   return std::find(fOutputTensorNames.begin(), fOutputTensorNames.end(), name) != fOutputTensorNames.end();
+}
+
+bool RModel::CanStayNHWC(const std::string &name, int depth) const
+{
+   if (depth > 16 || IsModelOutput(name)) return false;
+   auto shape = GetTensorShape(name);
+   if (shape.size() != 4) return false;
+   auto consumers = Consumers(name);
+   if (consumers.empty()) return false;
+   for (ROperator *op : consumers) {
+      if (!op->AcceptsNHWC(name)) return false;
+      switch (op->Kind()) {
+      case EOpKind::Conv:
+      case EOpKind::QLinearConv: break;
+      case EOpKind::Relu:
+      case EOpKind::Pool:
+         if (!CanStayNHWC(op->GetOpOutputTensors()[0], depth + 1)) return false;
+         break;
+      case EOpKind::Reshape: {
+         // Flatten: every reader of the flattened tensor must be a matmul with a constant weight
+         const std::string &flat = op->GetOpOutputTensors()[0];
+         if (IsModelOutput(flat)) return false;
+         auto readers = Consumers(flat);
+         if (readers.empty()) return false;
+         for (ROperator *r : readers) {
+            if ((r->Kind() != EOpKind::Gemm && r->Kind() != EOpKind::QLinearMatMul) || !r->AcceptsNHWC(flat)) return false;
+            if (r->GetOpInputTensors().size() < 2 || !IsInitializedTensor(r->GetOpInputTensors()[1])) return false;
+         }
+         break;
+      }
+      default: return false;
+      }
+   }
+   return true;
+}
+
+// ---------------------------------------------------------------------------------- Initialize
+void RModel::Initialize(int batchSize, bool verbose)
+{
+   fVerbose = int(verbose);
+   fBatchSize = batchSize;
+   fIntermediateTensorInfos.clear();
+   fLayouts.clear();
+   fAliases.clear();
+   fArenaOffsets.clear();
+   fDeviceWeights.clear();
+   fDeviceBuffers.clear();
+   if (fIsInitialized) throw std::runtime_error("SOFIE: an RModel can be initialized (generated) only once");
+
+   // shapes are fixed at generation time: parametric input dimensions take batchSize when given,
+   // else their default value, else 1 (the reference substitutes batch parameters the same way,
+   // src/SOFIE_core/src/RModel.cxx:399-440, and can leave others dynamic)
+   for (auto &input : fInputTensorInfos) {
+      std::vector<size_t> shape;
+      for (auto &d : input.second.shape) {
+         if (d.isParam) {
+            size_t v = batchSize > 0 ? (size_t)batchSize : (d.dim ? d.dim : 1);
+            fShapeParams[d.param] = std::to_string(v);
+            shape.push_back(v);
+         } else {
+            shape.push_back(d.dim);
+         }
+      }
+      fReadyInputTensorInfos[input.first] = TensorInfo{input.second.type, shape};
+      if (verbose) std::cout << "SOFIE: input " << input.first << " fixed to shape " << ConvertShapeToString(shape) << std::endl;
+   }
+   fInputTensorInfos.clear();
+   if (fInputTensorNames.empty())
+      for (auto &i : fReadyInputTensorInfos) fInputTensorNames.push_back(i.first);
+
+   for (auto &op : fOperators) {
+      if (verbose) std::cout << "Initializing operator " << typeid(*op).name() << std::endl;
+      op->Initialize(*this);
+   }
+   PlanDevice();
+   PlanArena();
+   fIsInitialized = true;
+}
+
+// Step 1-3 of the device plan: fusion, then layouts and weight preparation operator by operator.
+void RModel::PlanDevice()
+{
+   auto single_consumer = [&](const std::string &t) -> ROperator * {
+      if (IsModelOutput(t)) return nullptr;
+      auto c = Consumers(t);
+      return c.size() == 1 ? c[0] : nullptr;
+   };
+   for (auto &opp : fOperators) {
+      ROperator *op = opp.get();
+      if (op->IsFusedAway()) continue;
+      if (op->Kind() == EOpKind::Conv || op->Kind() == EOpKind::QLinearConv) {
+         auto *fconv = dynamic_cast<ROperator_Conv<float> *>(op);
+         auto *qconv = dynamic_cast<ROperator_QLinearConv *>(op);
+         std::string out = fconv ? fconv->OutputName() : qconv->OutputName();
+         if (ROperator *next = single_consumer(out)) {
+            if (auto *relu = dynamic_cast<ROperator_Relu<float> *>(next)) {
+               fconv ? fconv->FuseRelu(relu->OutputName()) : qconv->FuseRelu(relu->OutputName());
+               relu->SetFusedAway();
+               out = relu->OutputName();
+            }
+         }
+         if (ROperator *next = single_consumer(out)) {
+            auto *pool = dynamic_cast<ROperator_Pool<float> *>(next);
+            if (pool && pool->IsMax2x2Stride2()) {
+               fconv ? fconv->FusePool2x2(pool->OutputName()) : qconv->FusePool2x2(pool->OutputName());
+               pool->SetFusedAway();
+            }
+         }
+      } else if (op->Kind() == EOpKind::Gemm) {
+         auto *gemm = dynamic_cast<ROperator_Gemm<float> *>(op);
+         if (ROperator *next = gemm ? single_consumer(gemm->OutputName()) : nullptr)
+            if (auto *relu = dynamic_cast<ROperator_Relu<float> *>(next)) {
+               gemm->SetActivation(EActivationType::RELU);
+               gemm->SetOutputName(relu->OutputName());
+               relu->SetFusedAway();
+            }
+      } else if (op->Kind() == EOpKind::QLinearMatMul) {
+         auto *qmm = dynamic_cast<ROperator_QLinearMatMul *>(op);
+         if (ROperator *next = qmm ? single_consumer(qmm->OutputName()) : nullptr)
+            if (auto *relu = dynamic_cast<ROperator_Relu<float> *>(next)) {
+               qmm->FuseRelu(relu->OutputName());
+               relu->SetFusedAway();
+            }
+      }
+   }
+   for (auto &op : fOperators)
+      if (!op->IsFusedAway()) op->PlanDevice(*this);
+}
+
+// Step 4: liveness-based first-fit placement in one arena (256-byte aligned slices).
+void RModel::PlanArena()
+{
+   struct Slot {
+      std::string name;
+      size_t bytes;
+      int first, last;
+      size_t offset;
+   };
+   const int nOps = (int)fOperators.size();
+   std::vector<Slot> slots;
+   auto bytes_of = [&](const std::string &n) {
+      size_t b = ConvertShapeToLength(GetTensorShape(n)) * GetTypeSize(GetTensorType(n));
+      return (std::max<size_t>(b, 1) + 255) & ~size_t(255);
+   };
+   for (auto &in : fInputTensorNames) slots.push_back({in, bytes_of(in), -1, -1, 0});
+   for (int i = 0; i < nOps; i++) {
+      if (fOperators[i]->IsFusedAway()) continue;
+      for (auto &out : fOperators[i]->GetOpOutputTensors())
+         if (!fAliases.count(out)) slots.push_back({out, bytes_of(out), i, i, 0});
+   }
+   auto slot_of = [&](const std::string &n) -> Slot * {
+      std::string owner = ResolveAlias(n);
+      for (auto &s : slots)
+         if (s.name == owner) return &s;
+      return nullptr;
+   };
+   for (int i = 0; i < nOps; i++) {
+      if (fOperators[i]->IsFusedAway()) continue;
+      for (auto &in : fOperators[i]->GetOpInputTensors())
+         if (Slot *s = slot_of(in)) s->last = std::max(s->last, i);
+   }
+   for (auto &o : fOutputTensorNames) {
+      Slot *s = slot_of(o);
+      if (!s) throw std::runtime_error("SOFIE: output tensor " + o + " is not produced by any operator");
+      s->last = nOps;
+   }
+   fArenaBytes = 0;
+   for (size_t i = 0; i < slots.size(); i++) {
+      // lowest offset that does not overlap an already placed slot alive at the same time
+      size_t off = 0;
+      bool moved = true;
+      while (moved) {
+         moved = false;
+         for (size_t j = 0; j < i; j++) {
+            const Slot &p = slots[j];
+            bool time_overlap = !(p.last < slots[i].first || slots[i].last < p.first);
+            bool space_overlap = off < p.offset + p.bytes && p.offset < off + slots[i].bytes;
+            if (time_overlap && space_overlap) {
+               off = p.offset + p.bytes;
+               moved = true;
+            }
+         }
+      }
+      slots[i].offset = off;
+      fArenaOffsets[slots[i].name] = off;
+      fArenaBytes = std::max(fArenaBytes, off + slots[i].bytes);
+   }
+}
+
+// ---------------------------------------------------------------------------------- Generate
+std::string RModel::GenerateInferSignature(bool isdecl)
+{
+   std::string s;
+   for (auto &name : fInputTensorNames) {
+      if (isdecl) {
+         std::string type = ConvertTypeToString(GetTensorType(name));
+         if (type == "other") throw std::runtime_error("SOFIE: input tensor " + name + " is of a data type which is not yet supported.");
+         s += type + "* ";
+      }
+      s += "tensor_" + name + ",";
+   }
+   if (!fInputTensorNames.empty()) s.pop_back();
+   return s;
+}
+
+void RModel::Generate(std::underlying_type_t<Options> options, int batchSize, long pos, bool verbose)
+{
+   fVerbose = verbose;
+   fBatchSize = batchSize;
+   fReadPos = pos;
+   auto has = [&](Options o) { return (static_cast<std::underlying_type_t<Options>>(o) & options) != 0; };
+   if (has(Options::kNoSession))
+      throw std::runtime_error("SOFIE: kNoSession is not available on the CUDA path: the Session owns the device context");
+   if (has(Options::kRootBinaryWeightFile))
+      throw std::runtime_error("SOFIE: ROOT binary weight files need ROOT I/O, which this build does not have");
+   if (has(Options::kGNN) || has(Options::kGNNComponent))
+      throw std::runtime_error("SOFIE: GNN models are outside the CUDA dense-contraction path");
+   if (has(Options::kNoWeightFile)) {
+      fUseWeightFile = false;
+      fWeightFile = WeightFileType::None;
+   }
+   Initialize(batchSize, verbose);
+   std::string hgname;
+   fGC.clear();
+   GenerateHeaderInfo(hgname);
+   GenerateSessionCode();
+   fGC += ("} //SOFIE_" + fName + "\n");
+   fGC += "\n#endif  // " + hgname + "\n";
+}
+
+static std::string ByteCount(const std::vector<size_t> &shape, ETensorType t)
+{
+   return std::to_string(ConvertShapeToLength(shape) * GetTypeSize(t));
+}
+
+void RModel::GenerateSessionMembers()
+{
+   fGC += "sofie_cuda_ctx * fCtx = nullptr;   // device context: arena, uploaded weights, stream, captured graph\n";
+   fGC += "void * fStream = nullptr;\n";
+   fGC += "bool fGraphReady = false;\n";
+   fGC += "bool fUseGraph = true;\n";
+   fGC += "\n// device pointers: model inputs\n";
+   for (auto &n : fInputTensorNames) fGC += EMIT::CType(GetTensorType(n)) + " * " + EMIT::Dev(n) + " = nullptr;\n";
+   if (!fDeviceWeights.empty()) fGC += "// device pointers: weights uploaded by the constructor\n";
+   for (auto &n : fDeviceWeights) fGC += EMIT::CType(GetTensorType(n)) + " * " + EMIT::Dev(n) + " = nullptr;\n";
+   if (!fDeviceBuffers.empty()) fGC += "// device pointers: tables computed by the constructor\n";
+   for (auto &b : fDeviceBuffers) fGC += EMIT::CType(b.second.type) + " * " + EMIT::Dev(b.first) + " = nullptr;\n";
+   fGC += "// device pointers: intermediate tensors, slices of one arena of " + std::to_string(fArenaBytes) + " bytes\n";
+   for (auto &op : fOperators) {
+      if (op->IsFusedAway()) continue;
+      for (auto &out : op->GetOpOutputTensors()) fGC += EMIT::CType(GetTensorType(out)) + " * " + EMIT::Dev(out) + " = nullptr;\n";
+   }
+}
+
+void RModel::GenerateWeightReader()
+{
+   // same text format as the reference writes and reads (src/SOFIE_core/src/RModel.cxx:970-1018,1121-1158):
+   // "tensor_<name> <length>" followed by the values; integer tensors are written as integers
+   fGC += "   std::ifstream f;\n";
+   fGC += "   f.open(filename);\n";
+   fGC += "   if (!f.is_open()) {\n";
+   fGC += "      throw std::runtime_error(\"sofie failed to open file \" + filename + \" for input weights\");\n";
+   fGC += "   }\n";
+   if (fReadPos > 0) fGC += "   f.seekg(" + std::to_string(fReadPos) + ");\n";
+   fGC += "   std::string tensor_name;\n";
+   fGC += "   size_t length;\n";
+   for (auto &n : fDeviceWeights) {
+      const auto &t = fInitializedTensors.at(n);
+      std::string tname = "tensor_" + n, len = std::to_string(t.length());
+      fGC += "   f >> tensor_name >> length;\n";
+      fGC += "   if (tensor_name != \"" + tname + "\" ) {\n";
+      fGC += "      std::string err_msg = \"SOFIE failed to read the correct tensor name; expected name is " + tname + " , read \" + tensor_name;\n";
+      fGC += "      throw std::runtime_error(err_msg);\n";
+      fGC += "    }\n";
+      fGC += "   if (length != " + len + ") {\n";
+      fGC += "      std::string err_msg = \"SOFIE failed to read the correct tensor size; expected size is " + len + " , read \" + std::to_string(length) ;\n";
+      fGC += "      throw std::runtime_error(err_msg);\n";
+      fGC += "    }\n";
+      if (t.type() == ETensorType::INT8 || t.type() == ETensorType::UINT8)
+         fGC += "   for (size_t i = 0; i < length; ++i) { int v; f >> v; " + EMIT::Host(n) + "[i] = static_cast<" + EMIT::CType(t.type()) + ">(v); }\n";
+      else
+         fGC += "   for (size_t i = 0; i < length; ++i)\n      f >> " + EMIT::Host(n) + "[i];\n";
+      fGC += "   if (f.fail()) {\n";
+      fGC += "      throw std::runtime_error(\"SOFIE failed to read the values for tensor " + tname + "\");\n";
+      fGC += "   }\n";
+   }
+   fGC += "   f.close();\n";
+}
+
+void RModel::GenerateConstructor()
+{
+   if (fUseWeightFile) fGC += "Session(std::string filename =\"" + fName + ".dat\"";
+   else fGC += "Session(std::string = \"\"";
+   for (auto &p : fShapeParams) fGC += ",\n        size_t " + p.first + " = " + p.second;
+   fGC += ") {\n";
+   for (auto &p : fShapeParams)
+      fGC += "   if (" + p.first + " != " + p.second + ") throw std::runtime_error(\"SOFIE: this Session was generated for " + p.first +
+             " = " + p.second + "\");\n";
+   fGC += "   if (const char * g = std::getenv(\"SOFIE_CUDA_GRAPH\")) fUseGraph = (g[0] != '0');\n";
+   fGC += "   Check(sofie_cuda_ctx_create(&fCtx, -1, " + std::to_string(fArenaBytes) + "), \"sofie_cuda_ctx_create\");\n";
+   fGC += "   try {\n";
+   fGC += "   Check(sofie_cuda_ctx_stream(fCtx, &fStream), \"sofie_cuda_ctx_stream\");\n";
+   fGC += "   //--- arena slices of the inputs and intermediate tensors\n";
+   for (auto &slot : fArenaOffsets) {
+      const std::string &n = slot.first;
+      fGC += "   Check(sofie_cuda_ctx_arena(fCtx, " + std::to_string(slot.second) + ", " + ByteCount(GetTensorShape(n), GetTensorType(n)) +
+             ", reinterpret_cast<void**>(&" + EMIT::Dev(n) + ")), \"sofie_cuda_ctx_arena\");\n";
+   }
+   for (auto &a : fAliases)
+      fGC += "   " + EMIT::Dev(a.first) + " = reinterpret_cast<" + EMIT::CType(GetTensorType(a.first)) + "*>(" + EMIT::Dev(ResolveAlias(a.first)) + ");\n";
+   for (auto &b : fDeviceBuffers)
+      fGC += "   Check(sofie_cuda_ctx_alloc(fCtx, " + std::to_string(b.second.length * GetTypeSize(b.second.type)) +
+             ", reinterpret_cast<void**>(&" + EMIT::Dev(b.first) + ")), \"sofie_cuda_ctx_alloc\");\n";
+   fGC += "   //--- weights: host copies live until the end of the constructor\n";
+   for (auto &n : fDeviceWeights) {
+      const auto &t = fInitializedTensors.at(n);
+      std::string ct = EMIT::CType(t.type());
+      if (fUseWeightFile) {
+         fGC += "   std::vector<" + ct + "> " + EMIT::Host(n) + "(" + std::to_string(t.length()) + ");\n";
+      } else {
+         // kNoWeightFile: the values are written into the header
+         std::stringstream vals;
+         vals << std::setprecision(std::numeric_limits<float>::max_digits10);
+         for (size_t i = 0; i < t.length(); i++) {
+            if (i) vals << ", ";
+            if (i % 16 == 15) vals << "\n      ";
+            switch (t.type()) {
+            case ETensorType::FLOAT: {
+               float v = t.data<float>()[i];
+               vals << EMIT::FloatLit(v);
+               break;
+            }
+            case ETensorType::INT8: vals << (int)t.data<int8_t>()[i]; break;
+            case ETensorType::UINT8: vals << (int)t.data<uint8_t>()[i]; break;
+            case ETensorType::INT32: vals << t.data<int32_t>()[i]; break;
+            case ETensorType::INT64: vals << t.data<int64_t>()[i]; break;
+            default: throw std::runtime_error("SOFIE: tensor " + n + " has a type that cannot be written into the header");
+            }
+         }
+         fGC += "   std::vector<" + ct + "> " + EMIT::Host(n) + " = {" + vals.str() + "};\n";
+      }
+   }
+   if (fUseWeightFile && !fDeviceWeights.empty()) {
+      fGC += "\n//--- reading weights from file\n";
+      GenerateWeightReader();
+      fGC += "\n";
+   }
+   for (auto &n : fDeviceWeights) {
+      const auto &t = fInitializedTensors.at(n);
+      fGC += "   Check(sofie_cuda_ctx_upload(fCtx, " + EMIT::Host(n) + ".data(), " + std::to_string(t.length() * GetTypeSize(t.type())) +
+             ", reinterpret_cast<void**>(&" + EMIT::Dev(n) + ")), \"sofie_cuda_ctx_upload\");\n";
+   }
+   for (auto &op : fOperators)
+      if (!op->IsFusedAway()) fGC += op->GenerateInitCode();
+   fGC += "   Check(sofie_cuda_ctx_sync(fCtx), \"sofie_cuda_ctx_sync\");\n";
+   fGC += "   } catch (...) {\n      sofie_cuda_ctx_destroy(fCtx);\n      fCtx = nullptr;\n      throw;\n   }\n";
+   fGC += "}\n\n";
+   fGC += "~Session() { sofie_cuda_ctx_destroy(fCtx); }\n";
+   fGC += "Session(const Session &) = delete;\n";
+   fGC += "Session & operator=(const Session &) = delete;\n\n";
+}
+
+void RModel::GenerateInfer()
+{
+   size_t nOut = fOutputTensorNames.size();
+   if (nOut == 0) throw std::runtime_error("SOFIE: output size=0 are not supported");
+   // the launches of one infer(), in execution order; captured into a CUDA graph on the first call
+   fGC += "// all kernel launches of one inference, on the context stream\n";
+   fGC += "void Launch() {\n";
+   for (size_t i = 0; i < fOperators.size(); i++) {
+      if (fOperators[i]->IsFusedAway()) continue;
+      if (fVerbose) std::cout << "Generating code for operator .... " << i << std::endl;
+      fGC += fOperators[i]->Generate(std::to_string(i));
+   }
+   fGC += "}\n\n";
+
+   ETensorType t0 = GetTensorType(fOutputTensorNames[0]);
+   bool sameTypes = true;
+   for (auto &o : fOutputTensorNames) sameTypes &= GetTensorType(o) == t0;
+   std::string ret;
+   if (nOut == 1) ret = "std::vector<" + ConvertTypeToString(t0) + ">";
+   else if (sameTypes) ret = "std::vector<std::vector<" + ConvertTypeToString(t0) + ">>";
+   else {
+      ret = "std::tuple<";
+      for (size_t i = 0; i < nOut; i++) ret += "std::vector<" + ConvertTypeToString(GetTensorType(fOutputTensorNames[i])) + ">" + (i + 1 < nOut ? "," : "");
+      ret += ">";
+   }
+   fGC += ret + " infer(" + GenerateInferSignature() + "){\n";
+   for (auto &n : fInputTensorNames)
+      fGC += "   Check(sofie_cuda_ctx_h2d(fCtx, " + EMIT::Dev(n) + ", tensor_" + n + ", " + ByteCount(GetTensorShape(n), GetTensorType(n)) +
+             "), \"sofie_cuda_ctx_h2d\");\n";
+   fGC += "   if (fGraphReady) {\n";
+   fGC += "      Check(sofie_cuda_ctx_graph_launch(fCtx), \"sofie_cuda_ctx_graph_launch\");\n";
+   fGC += "   } else {\n";
+   fGC += "      Launch();\n";
+   fGC += "      if (fUseGraph) {\n";
+   fGC += "         Check(sofie_cuda_ctx_graph_begin(fCtx), \"sofie_cuda_ctx_graph_begin\");\n";
+   fGC += "         try { Launch(); } catch (...) { sofie_cuda_ctx_graph_end(fCtx); throw; }\n";
+   fGC += "         Check(sofie_cuda_ctx_graph_end(fCtx), \"sofie_cuda_ctx_graph_end\");\n";
+   fGC += "         fGraphReady = true;\n";
+   fGC += "      }\n";
+   fGC += "   }\n";
+   for (size_t i = 0; i < nOut; i++) {
+      const std::string &o = fOutputTensorNames[i];
+      std::string type = ConvertTypeToString(GetTensorType(o));
+      fGC += "   std::vector<" + type + "> ret_" + std::to_string(i) + "(" + std::to_string(ConvertShapeToLength(GetTensorShape(o))) + ");\n";
+      fGC += "   Check(sofie_cuda_ctx_d2h(fCtx, ret_" + std::to_string(i) + ".data(), " + EMIT::Dev(o) + ", " +
+             ByteCount(GetTensorShape(o), GetTensorType(o)) + "), \"sofie_cuda_ctx_d2h\");\n";
+   }
+   if (nOut == 1) fGC += "   return ret_0;\n";
+   else {
+      fGC += "   return {";
+      for (size_t i = 0; i < nOut; i++) fGC += "ret_" + std::to_string(i) + (i + 1 < nOut ? "," : "");
+      fGC += "};\n";
+   }
+   fGC += "}\n";
+}
+
+void RModel::GenerateSessionCode()
+{
+   fGC += "struct Session {\n";
+   GenerateSessionMembers();
+   fGC += "\n";
+   for (size_t id = 0; id < fOperators.size(); id++)
+      if (!fOperators[id]->IsFusedAway()) fGC += fOperators[id]->GenerateSessionMembersCode(std::to_string(id));
+   for (auto &op : fOperators)
+      if (!op->IsFusedAway()) fGC += op->GenerateDeclCode();
+   fGC += "\n";
+   GenerateConstructor();
+   GenerateInfer();
+   fGC += "};   // end of Session\n";
+}
+
+// ---------------------------------------------------------------------------------- weight file, output
+long RModel::WriteInitializedTensorsToFile(std::string filename)
+{
+   if (fWeightFile != WeightFileType::Text) return -1;
+   if (filename.empty()) filename = fName + ".dat";
+   std::ofstream f(filename, fReadPos > 0 ? std::ios_base::app : std::ios_base::out);
+   if (!f.is_open()) throw std::runtime_error("sofie failed to open file " + filename + " for tensor weight data");
+   // only the tensors the emitted constructor reads, in the order it reads them
+   for (auto &n : fDeviceWeights) {
+      const auto &t = fInitializedTensors.at(n);
+      size_t length = t.length();
+      f << "tensor_" << n << " " << length << "\n";
+      switch (t.type()) {
+      case ETensorType::FLOAT: {
+         const float *data = t.data<float>();
+         for (size_t i = 0; i < length; i++) {
+            // as the reference does: max_digits10 digits, subnormals flushed to zero
+            float v = data[i];
+            if (v != 0.f && std::abs(v) < std::numeric_limits<float>::min()) v = 0.f;
+            f << std::setprecision(std::numeric_limits<float>::max_digits10) << v << (i + 1 < length ? " " : "\n");
+         }
+         break;
+      }
+      case ETensorType::INT8:
+         for (size_t i = 0; i < length; i++) f << (int)t.data<int8_t>()[i] << (i + 1 < length ? " " : "\n");
+         break;
+      case ETensorType::UINT8:
+         for (size_t i = 0; i < length; i++) f << (int)t.data<uint8_t>()[i] << (i + 1 < length ? " " : "\n");
+         break;
+      case ETensorType::INT32:
+         for (size_t i = 0; i < length; i++) f << t.data<int32_t>()[i] << (i + 1 < length ? " " : "\n");
+         break;
+      case ETensorType::INT64:
+         for (size_t i = 0; i < length; i++) f << t.data<int64_t>()[i] << (i + 1 < length ? " " : "\n");
+         break;
+      default: throw std::runtime_error("sofie tensor " + n + " with type " + ConvertTypeToString(t.type()) + " cannot be written to a file");
+      }
+      if (f.fail()) throw std::runtime_error("sofie failed to write tensor data to file for " + n);
+   }
+   long pos = f.tellp();
+   f.close();
+   return pos;
+}
+
+void RModel::OutputGenerated(std::string filename, bool append)
+{
+   RModel_Base::OutputGenerated(filename, append);
+   if (fUseWeightFile) {
+      if (!filename.empty()) {
+         size_t pos = filename.find(".hxx");
+         if (pos != std::string::npos) filename.replace(pos, 4, ".dat");
+         else filename += ".dat";
+      } else {
+         filename = fName + ".dat";
+      }
+      WriteInitializedTensorsToFile(filename);
+   }
+}
+
+void RModel::PrintRequiredInputTensors()
+{
+   std::cout << "Model requires following inputs:\n";
+   for (auto &i : fInputTensorInfos)
+      std::cout << "Parametrised Tensor name: " << i.first << "\ttype: " << ConvertTypeToString(i.second.type)
+                << "\tshape: " << ConvertDynamicShapeToString(i.second.shape) << "\n";
+   for (auto &i : fReadyInputTensorInfos)
+      std::cout << "Fully Specified Tensor name: " << i.first << "\ttype: " << ConvertTypeToString(i.second.type)
+                << "\tshape: " << ConvertShapeToString(i.second.shape) << "\n";
+   std::cout << "\n";
+}
+
+void RModel::PrintInitializedTensors()
+{
+   std::cout << "Model initialized the following tensors:\n";
+   for (auto &it : fInitializedTensors)
+      std::cout << "Tensor name: \"" << it.first << "\"\ttype: " << ConvertTypeToString(it.second.type())
+                << "\tshape: " << ConvertShapeToString(it.second.shape()) << (it.second.IsConstantTensor() ? " (Constant)" : "")
+                << (!it.second.IsWeightTensor() ? " (Not Writable)" : "") << "\n";
+   std::cout << "\n";
+}
+
+void RModel::PrintIntermediateTensors()
+{
+   std::cout << "Model specify the following intermediate tensors:\n";
+   for (auto &it : fIntermediateTensorInfos)
+      std::cout << "Tensor name: \"" << it.first << "\"\ttype: " << ConvertTypeToString(it.second.type)
+                << "\tshape: " << ConvertShapeToString(it.second.shape)
+                << (GetTensorLayout(it.first) == ELayout::NHWC ? " (NHWC on the device)" : "") << "\n";
+   std::cout << "\n";
+}
+
+void RModel::PrintOutputTensors()
+{
+   std::cout << "Model specify the following output tensors:\n";
+   for (auto &it : fOutputTensorNames)
+      std::cout << "Tensor name: \"" << it << "\"\tshape: " << ConvertShapeToString(GetTensorShape(it)) << "\n";
+   std::cout << "\n";
+}
+
+void RModel::HeadInitializedTensors(std::string name, int n_print)
+{
+   auto it = fInitializedTensors.find(name);
+   if (it == fInitializedTensors.end()) {
+      std::cout << "Tensor " << name << " not found in model's initialized tensor list" << std::endl;
+      return;
+   }
+   std::cout << "Tensor name: " << it->first << "\ttype: " << ConvertTypeToString(it->second.type())
+             << "\tshape: " << ConvertShapeToString(it->second.shape()) << "\n";
+   size_t n = std::min<size_t>(it->second.length(), n_print);
+   if (it->second.type() == ETensorType::FLOAT)
+      for (size_t i = 0; i < n; i++) std::cout << it->second.data<float>()[i] << (i + 1 < n ? ", " : "\n");
+}
+
+} // namespace SOFIE

@@ -140,3 +140,27 @@ def run_fixture(name, manifest, arrays, backend):
 FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutPadding",
                  "ConvWithAutopadSameLower", "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "AvgPool",
                  "Softmax1d", "Softmax2d", "Softmax3d", "Softmax4d", "Einsum_matmul"]
+
+
+def fixture_to_onnx(name, manifest, arrays):
+    """Re-serialise one golden fixture (nodes, attributes, weights, input shapes) as ONNX bytes, so the
+    C++ front end can parse the same graphs the reference's tests parse."""
+    from sofie_b200 import onnx_wire as ow
+    entry = manifest[name]
+    nodes = []
+    for n in entry["nodes"]:
+        attrs = []
+        for k, v in n["attrs"].items():
+            if isinstance(v, str):
+                attrs.append(ow.attr_str(k, v))
+            elif isinstance(v, float):
+                attrs.append(ow.attr_float(k, v))
+            elif isinstance(v, int):
+                attrs.append(ow.attr_int(k, v))
+            else:
+                attrs.append(ow.attr_ints(k, v))
+        nodes.append(ow.node(n["op"], n["inputs"], n["outputs"], attrs))
+    inits = [ow.tensor(key[len(name) + 3:], arrays[key]) for key in arrays.files if key.startswith(f"{name}/w/")]
+    inputs = [ow.value_info(i, ow.FLOAT, arrays[f"{name}/in/{i}"].shape) for i in entry["inputs"]]
+    outputs = [ow.value_info(entry["nodes"][-1]["outputs"][0], ow.FLOAT, [])]
+    return ow.model(name, nodes, inputs, outputs, inits)

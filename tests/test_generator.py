@@ -1,0 +1,82 @@
+"""The C++ generator (sofie_b200/host): same user-facing flow as the reference --
+RModelParser_ONNX::Parse -> RModel::Generate -> OutputGenerated -- checked without a GPU: the models
+parse, the emitted header has the reference's Session / infer signatures, calls only libSOFIE_cuda,
+and compiles and links with a plain C++17 compiler."""
+import re
+
+import numpy as np
+import pytest
+
+from helpers import FIXTURE_CASES, fixture_to_onnx, load_fixtures
+from sofie_b200 import configs, generated, onnx_wire
+
+
+def _emit(model, name):
+    return generated.emit(onnx_wire.model_to_onnx(model), name)
+
+
+def test_c2_header_has_reference_signatures_and_fused_plan():
+    m, _ = configs.cnn_f32(batch=8)
+    hxx = _emit(m, "c2_b8")
+    text = hxx.read_text()
+    assert "namespace SOFIE_c2_b8{" in text
+    assert 'Session(std::string filename ="c2_b8.dat")' in text
+    assert "std::vector<float> infer(float* tensor_x){" in text
+    assert '#include "sofie_cuda.h"' in text and "sgemm_" not in text and "Im2col" not in text
+    # Conv+Relu(+MaxPool) collapse into three launches, Flatten is an alias, one Gemm
+    assert text.count("sofie_cuda_conv2d_f32(") == 3 and text.count("sofie_cuda_gemm_f32(") == 1
+    assert "sofie_cuda_relu_f32(" not in text and "sofie_cuda_pool2d_f32(" not in text
+    assert "dev_flat = reinterpret_cast<float*>(dev_p2);" in text
+    # layouts: first conv reads NCHW and writes NHWC; later convs read packed weights
+    descs = re.findall(r"sofie_conv2d_desc d = \{([^}]*)\}", text)
+    fields = [[int(v) for v in d.split(",")] for d in descs]
+    assert [f[14:17] for f in fields] == [[0, 1, 0], [1, 1, 1], [1, 1, 1]]       # x_layout, y_layout, w_packed
+    assert [f[17:19] for f in fields] == [[1, 0], [1, 2], [1, 2]]                # relu, pool
+    dat = hxx.with_suffix(".dat").read_text().split()
+    assert dat[0] == "tensor_cb0" and dat[1] == "16"
+
+
+def test_arena_slices_do_not_overlap_while_alive():
+    m, _ = configs.mlp_f32(batch=64)
+    text = _emit(m, "c1_b64").read_text()
+    slices = {n: (int(o), int(b)) for o, b, n in re.findall(r"sofie_cuda_ctx_arena\(fCtx, (\d+), (\d+), reinterpret_cast<void\*\*>\(&dev_(\w+)\)", text)}
+    assert set(slices) == {"x", "y0", "y1", "y2"}
+    # y0 (read by layer 1) and y1 (written by layer 1) are alive together: disjoint
+    (o0, b0), (o1, b1) = slices["y0"], slices["y1"]
+    assert o0 + b0 <= o1 or o1 + b1 <= o0
+    assert all(o % 256 == 0 for o, _ in slices.values())
+    arena = int(re.search(r"sofie_cuda_ctx_create\(&fCtx, -1, (\d+)\)", text).group(1))
+    assert arena >= max(o + b for o, b in slices.values())
+
+
+@pytest.mark.parametrize("key,kw", [("C1", {}), ("C2", {"batch": 4}), ("C3", {"batch": 32}), ("C5", {"batch": 2})])
+def test_configurations_emit_and_compile(key, kw):
+    m, _ = configs.BUILDERS[key](**kw)
+    name = f"{key.lower()}_gen"
+    hxx = _emit(m, name)
+    so = generated.compile_session(hxx, name)
+    assert so.exists()
+
+
+@pytest.mark.parametrize("name", FIXTURE_CASES)
+def test_reference_fixture_graphs_parse_and_emit(name):
+    manifest, arrays = load_fixtures()
+    hxx = generated.emit(fixture_to_onnx(name, manifest, arrays), name)
+    assert "infer(" in hxx.read_text()
+
+
+def test_unsupported_operator_and_bad_file_raise():
+    with pytest.raises(RuntimeError, match="not yet supported"):
+        generated.emit(onnx_wire.model("g", [onnx_wire.node("LSTM", ["x"], ["y"])], [onnx_wire.value_info("x", 1, [1, 2, 3])],
+                                       [onnx_wire.value_info("y", 1, [])], []), "bad_op")
+    with pytest.raises(RuntimeError):
+        generated.emit(b"\x00\x01garbage", "bad_file")
+
+
+def test_session_without_gpu_throws_the_reference_way():
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    m, _ = configs.mlp_f32(batch=4)
+    with pytest.raises(RuntimeError, match="SOFIE CUDA"):
+        generated.session_from_model(m, "c1_nogpu")

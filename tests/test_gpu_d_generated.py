@@ -1,0 +1,59 @@
+"""The full drop-in path on the GPU: ONNX file -> RModelParser_ONNX::Parse -> RModel::Generate ->
+emitted header compiled with g++ -> Session(file).infer(host pointer) -> host vector, compared with
+the reference's own golden vectors, with the reference's own emitted CPU code and with the oracle."""
+import numpy as np
+import pytest
+
+from helpers import FIXTURE_CASES, GOLDEN, fixture_to_onnx, load_fixtures, rel_err
+from oracle import build_ref, run_model
+from sofie_b200 import configs, generated
+
+pytestmark = pytest.mark.gpu
+REF = np.load(GOLDEN / "ref_outputs.npz")
+
+
+@pytest.mark.parametrize("name", [n for n in FIXTURE_CASES if n != "Einsum_matmul"])
+def test_reference_golden_vectors_through_generated_session(name, cuda_device):
+    manifest, arrays = load_fixtures()
+    hxx = generated.emit(fixture_to_onnx(name, manifest, arrays), name)
+    exp = arrays[f"{name}/expected"]
+    s = generated.GeneratedSession(generated.compile_session(hxx, name), hxx.with_suffix(".dat"), exp.size)
+    x = arrays[f"{name}/in/{manifest[name]['inputs'][0]}"]
+    y = s.infer(x)
+    assert np.abs(y - exp).max() <= 1e-3  # the reference's tolerance for its fixtures
+
+
+@pytest.mark.parametrize("case", ["ref_c1", "ref_c2", "ref_c2_b4", "ref_gemm_nt", "ref_matmul", "ref_conv_grp", "ref_conv5", "ref_softmax"])
+def test_generated_session_matches_reference_emitted_code(case, cuda_device):
+    m, x = build_ref.all_cases()[case]
+    s = generated.session_from_model(m, case + "_cuda")
+    y1 = s.infer(x)
+    y2 = s.infer(x)  # second call replays the captured graph
+    assert np.array_equal(y1, y2)
+    assert rel_err(y1, REF[case]) <= 1e-5
+
+
+def test_generated_int8_sessions_bit_exact(cuda_device):
+    m, x = configs.mlp_i8(batch=512)
+    y = generated.session_from_model(m, "c3_b512").infer(x)
+    assert np.array_equal(y.view(np.uint32), run_model.run(m, x).ravel().view(np.uint32))
+    m, x = configs.cnn_i8(batch=8)
+    y = generated.session_from_model(m, "c5_b8").infer(x)
+    assert np.array_equal(y.view(np.uint32), run_model.run(m, x).ravel().view(np.uint32))
+
+
+def test_missing_and_truncated_weight_file_throw(cuda_device, tmp_path):
+    m, x = configs.mlp_f32(batch=16)
+    s = generated.session_from_model(m, "c1_b16")
+    hxx = next((generated.WORK).glob("c1_b16_*/c1_b16.hxx"))
+    so = hxx.with_suffix(".so")
+    with pytest.raises(RuntimeError, match="failed to open file"):
+        generated.GeneratedSession(so, tmp_path / "nope.dat", 160)
+    text = hxx.with_suffix(".dat").read_text()
+    (tmp_path / "short.dat").write_text(text[: len(text) // 2])
+    with pytest.raises(RuntimeError, match="failed to read"):
+        generated.GeneratedSession(so, tmp_path / "short.dat", 160)
+    (tmp_path / "renamed.dat").write_text(text.replace("tensor_W0_nk_y0", "tensor_other", 1))
+    with pytest.raises(RuntimeError, match="correct tensor name"):
+        generated.GeneratedSession(so, tmp_path / "renamed.dat", 160)
+    assert s.infer(x).shape == (160,)
