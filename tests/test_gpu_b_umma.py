@@ -96,3 +96,48 @@ def test_tensor_core_and_cuda_core_kernels_agree():
     ops.set_engine(capi.ENGINE_SIMT)
     y_cc = ops.gemm_f32(dev(A), dev(B), transB=1).cpu().numpy()
     assert rel_err(y_tc, y_cc) <= 1e-5
+
+
+# ------------------------------------------------------------------------------------ implicit-GEMM convolution
+CONV_TC = [
+    # N, C, H, W, Cout, relu, pool
+    (4, 16, 32, 32, 32, 1, 2), (6, 32, 16, 16, 64, 1, 2), (5, 64, 8, 8, 128, 1, 0), (5, 64, 8, 8, 128, 0, 2),
+    (3, 8, 16, 24, 20, 1, 0), (2, 32, 64, 64, 64, 1, 2), (300, 16, 32, 32, 32, 1, 2), (1, 128, 8, 16, 16, 0, 0),
+]
+
+
+@pytest.mark.parametrize("case", CONV_TC)
+def test_conv3x3_f32_tcgen05(case):
+    N, C, H, W, Cout, relu, pool = case
+    rng = np.random.default_rng(sum(case))
+    X = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    Wt = (rng.standard_normal((Cout, C, 3, 3)) * 0.2).astype(np.float32)
+    b = rng.standard_normal(Cout).astype(np.float32)
+    ref = o.conv2d_f32(X, Wt, b, pad=(1, 1), relu=bool(relu))
+    if pool:
+        ref = o.pool2d_f32(ref, 0, (2, 2), (2, 2))
+    y = ops.conv2d_f32(dev(X.transpose(0, 2, 3, 1)), ops.conv2d_pack_f32(dev(Wt)), dev(b), shape=X.shape, pad=(1, 1),
+                       relu=bool(relu), pool=pool, x_layout=1, y_layout=1, w_packed=True, kernel=(3, 3))
+    assert ops.last_engine() == capi.ENGINE_TCGEN05
+    assert rel_err(y.cpu().numpy().transpose(0, 3, 1, 2), ref) <= 1e-5
+
+
+@pytest.mark.parametrize("case", [(3, 32, 32, 32, 64, 1, 2), (7, 64, 16, 16, 64, 1, 2), (9, 64, 8, 8, 128, 1, 2), (2, 32, 16, 16, 40, 0, 0),
+                                  (130, 32, 32, 32, 64, 1, 2)])
+def test_qlinear_conv3x3_tcgen05_bit_exact(case):
+    N, C, H, W, Cout, relu, pool = case
+    rng = np.random.default_rng(sum(case))
+    X = (rng.integers(0, 256, (N, C, H, W)) * (rng.random((N, C, H, W)) < 0.4)).astype(np.uint8)
+    Wt = rng.integers(-127, 128, (Cout, C, 3, 3)).astype(np.int8)
+    ws = rng.uniform(0.001, 0.01, Cout).astype(np.float32)
+    bias = rng.integers(-1000, 1000, Cout).astype(np.int32)
+    y_scale = 0.05 * 0.005 * 127 * 80 * np.sqrt(C * 9) / 100
+    ref = o.qlinear_conv2d(X, 0.05, 0, Wt, ws, y_scale, 3, bias=bias, pad=(1, 1), relu=bool(relu))
+    if pool:
+        ref = o.maxpool2d_u8(ref)
+    mult = dev(o.requant_multiplier(0.05, ws, y_scale))
+    y = ops.qlinear_conv2d(dev(X.transpose(0, 2, 3, 1)), ops.qconv2d_pack_i8(dev(Wt)), mult, dev(bias), shape=X.shape, pad=(1, 1),
+                           x_zp=0, y_zp=3, relu=bool(relu), pool=pool, x_layout=1, y_layout=1, w_packed=True, kernel=(3, 3))
+    assert ops.last_engine() == capi.ENGINE_TCGEN05
+    assert np.array_equal(y.cpu().numpy().transpose(0, 3, 1, 2), ref)
+    assert len(np.unique(ref)) > 20
