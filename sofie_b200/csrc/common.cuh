@@ -58,10 +58,10 @@ __host__ __device__ constexpr T ceil_div(T a, T b)
 // evaluating nearbyintf((float)acc * mult) under the default rounding mode gets the same bits.
 __device__ __forceinline__ int requant_u8(int acc, float mult, int y_zp, int relu)
 {
-   float r = rintf(__fmul_rn(__int2float_rn(acc), mult));
-   float lo = (float)(0 - y_zp), hi = (float)(255 - y_zp);
-   r = fminf(fmaxf(r, lo), hi);
-   int q = __float2int_rn(r) + y_zp;
+   // round-to-nearest-even conversion that saturates at the int range, then the clamp in integers:
+   // the same value as clamping the rounded float first, in fewer instructions
+   int q = __float2int_rn(__fmul_rn(__int2float_rn(acc), mult));
+   q = min(max(q, 0 - y_zp), 255 - y_zp) + y_zp;
    if (relu && q < y_zp) q = y_zp;
    return q;
 }

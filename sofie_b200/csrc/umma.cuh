@@ -56,7 +56,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
    if (mbar_try_wait(bar, parity)) return true;
    const long long start = clock64();
    while (true) {
-      if (mbar_try_wait(bar, parity)) return true;
+      // poll a few times (each try_wait already suspends the thread for a while) before spending
+      // issue slots on the clock and the abort flag
+#pragma unroll 1
+      for (int spin = 0; spin < 16; spin++)
+         if (mbar_try_wait(bar, parity)) return true;
       if (*abort_flag) return false;
       if (clock64() - start > kWaitLimitCycles) {
          *abort_flag = 1;
@@ -69,6 +73,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
       }
    }
 }
+
+// Optional self-profiling (compile with -DSOFIE_UMMA_PROFILE): every bounded wait adds the cycles it
+// spent to a per-thread counter that the kernels of CTA 0 print per role when they finish.
+#ifdef SOFIE_UMMA_PROFILE
+#define SOFIE_PROF_DECL long long prof_wait = 0; const long long prof_begin = clock64();
+#define SOFIE_PROF_WAIT(call) ([&] { const long long t0__ = clock64(); const bool r__ = (call); prof_wait += clock64() - t0__; return r__; }())
+#define SOFIE_PROF_REPORT(role) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) printf("[umma-prof] %s warp %d: total %lld cycles, waiting %lld\n", role, (int)(threadIdx.x >> 5), clock64() - prof_begin, prof_wait); } while (0)
+#else
+#define SOFIE_PROF_DECL
+#define SOFIE_PROF_WAIT(call) (call)
+#define SOFIE_PROF_REPORT(role) do { } while (0)
+#endif
 
 __device__ __forceinline__ void fence_proxy_async()
 {

@@ -7,7 +7,7 @@
 // is a 2-D box of the packed weights. tcgen05.mma accumulates the 9 x (Cin / chunk) stages of a
 // tile in TMEM; two TMEM buffers let the epilogue of one tile overlap the MMAs of the next
 // (persistent CTAs, one per SM).
-//   kTF32: fp32 in / out, 3xTF32 (hi/lo split of both tiles by 4 converter warps), bias, Relu.
+//   kTF32: fp32 in / out, 3xTF32 (hi/lo split of both tiles by 8 converter warps), bias, Relu.
 //   kI8  : uint8 x int8 -> int32, per-channel requantisation to uint8, Relu = max(q, zp). The input
 //          zero point must be 0 (the zero fill of the halo is then exactly the padding value).
 // Fused MaxPool 2x2: a warp owns 32 consecutive pixels = two (tileW 16) or four (tileW 8) image
@@ -38,9 +38,13 @@ struct ConvTiling {
 };
 
 constexpr int kConvMaxStages = 8;
+constexpr int kConvEpilogueWarps = 8;                          // warps 2..9
+constexpr int kConvConverterWarps = 8;                         // fp32 only: warps 10..17
+constexpr int kConvThreadsI8 = (2 + kConvEpilogueWarps) * 32;
+constexpr int kConvThreadsTF32 = (2 + kConvEpilogueWarps + kConvConverterWarps) * 32;
 
-template <int KIND, int BN, int CB>
-__global__ void __launch_bounds__(KIND == kTF32 ? 320 : 192, 1)
+template <int KIND, int BN, int CB, int TPS>
+__global__ void __launch_bounds__(KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8, 1)
 umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, ConvEpilogue ep,
                     ConvTiling tg, uint32_t *status)
 {
@@ -48,32 +52,48 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
    constexpr int CBE = CB / ES;                         // channels per chunk
    constexpr int A_TILE = 128 * CB, B_TILE = BN * CB;
    constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
-   constexpr int STAGE_BYTES = COPIES * (A_TILE + B_TILE);
-   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+   constexpr int SUB_BYTES = COPIES * (A_TILE + B_TILE); // one (tap, channel chunk): A and B tiles (+ lo copies)
+   // A pipeline stage holds TPS such sub-blocks (TPS = 3: the three taps of one kernel row), so the
+   // fixed cost of a stage hand-over (barrier round trip, commit) is paid once per TPS taps.
+   // Back-to-back MMAs into the same accumulator serialise on the accumulator (about 130 cycles
+   // each, whatever N is), so the MMAs of a tile rotate over NACC accumulators, which the epilogue
+   // adds up. Two such sets of accumulators double-buffer the tiles.
+   constexpr int NACC = 256 / BN > 6 ? 6 : 256 / BN;
+   constexpr uint32_t TMEM_COLS = 512;
+   constexpr int EPI_WARPS = kConvEpilogueWarps;
    extern __shared__ unsigned char smem_raw[];
    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
    __shared__ uint64_t full_bar[kConvMaxStages], conv_bar[kConvMaxStages], empty_bar[kConvMaxStages], tmem_full[2], tmem_empty[2];
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
+   __shared__ float s_bias[128], s_mult[128]; // per output channel, zero / one beyond Cout
+   __shared__ int s_qbias[128];
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+   SOFIE_PROF_DECL
+   for (int c = threadIdx.x; c < 128; c += blockDim.x) {
+      const bool in = c < tg.Cout;
+      s_bias[c] = (KIND == kTF32 && in && ep.bias) ? ep.bias[c] : 0.f;
+      s_mult[c] = (KIND == kI8 && in) ? ep.mult[c] : 0.f;
+      s_qbias[c] = (KIND == kI8 && in && ep.qbias) ? ep.qbias[c] : 0;
+   }
    const int S = tg.stages;
-   const int stages_per_tile = 9 * tg.chunks;
+   const int stages_per_tile = 9 * tg.chunks / TPS; // TPS > 1 only when chunks == 1
 
-   auto a_hi = [&](int s) { return smem + (size_t)s * STAGE_BYTES; };
-   auto b_hi = [&](int s) { return smem + (size_t)s * STAGE_BYTES + A_TILE; };
-   auto a_lo = [&](int s) { return smem + (size_t)s * STAGE_BYTES + A_TILE + B_TILE; };
-   auto b_lo = [&](int s) { return smem + (size_t)s * STAGE_BYTES + 2 * A_TILE + B_TILE; };
+   auto a_hi = [&](int s, int k) { return smem + (size_t)(s * TPS + k) * SUB_BYTES; };
+   auto b_hi = [&](int s, int k) { return smem + (size_t)(s * TPS + k) * SUB_BYTES + A_TILE; };
+   auto a_lo = [&](int s, int k) { return smem + (size_t)(s * TPS + k) * SUB_BYTES + A_TILE + B_TILE; };
+   auto b_lo = [&](int s, int k) { return smem + (size_t)(s * TPS + k) * SUB_BYTES + 2 * A_TILE + B_TILE; };
 
    if (threadIdx.x == 0) {
       for (int s = 0; s < kConvMaxStages; s++) {
          mbar_init(&full_bar[s], 1);
-         mbar_init(&conv_bar[s], 128);
+         mbar_init(&conv_bar[s], kConvConverterWarps * 32);
          mbar_init(&empty_bar[s], 1);
       }
       for (int b = 0; b < 2; b++) {
          mbar_init(&tmem_full[b], 1);
-         mbar_init(&tmem_empty[b], 4);
+         mbar_init(&tmem_empty[b], EPI_WARPS);
       }
       abort_flag = 0;
       fence_mbar_init();
@@ -106,20 +126,22 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
             int n0, h0, w0;
             tile_origin(tile, n0, h0, w0);
             bool ok = true;
-            for (int tap = 0; tap < 9 && ok; tap++) {
-               const int r = tap / 3, sx = tap % 3;
-               for (int ch = 0; ch < tg.chunks; ch++, g++) {
-                  const int s = g % S;
-                  const uint32_t ph = (g / S) & 1;
-                  if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g)) {
-                     ok = false;
-                     break;
-                  }
-                  mbar_expect_tx(&full_bar[s], A_TILE + B_TILE);
+            for (int st = 0; st < stages_per_tile; st++, g++) {
+               const int s = g % S;
+               const uint32_t ph = (g / S) & 1;
+               if (!SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g))) {
+                  ok = false;
+                  break;
+               }
+               mbar_expect_tx(&full_bar[s], TPS * (A_TILE + B_TILE));
+#pragma unroll
+               for (int k = 0; k < TPS; k++) {
+                  const int item = st * TPS + k, tap = item / tg.chunks, ch = item % tg.chunks;
+                  const int r = tap / 3, sx = tap % 3;
                   // x coordinate (channels) is a multiple of CBE, i.e. of 16 bytes; the spatial
                   // coordinates may be -1 or reach H / W: those elements read as zero
-                  tma_load_4d(a_hi(s), &tmX, ch * CBE, w0 + sx - 1, h0 + r - 1, n0, &full_bar[s]);
-                  tma_load_2d(b_hi(s), &tmW, tap * tg.C + ch * CBE, 0, &full_bar[s]);
+                  tma_load_4d(a_hi(s, k), &tmX, ch * CBE, w0 + sx - 1, h0 + r - 1, n0, &full_bar[s]);
+                  tma_load_2d(b_hi(s, k), &tmW, tap * tg.C + ch * CBE, 0, &full_bar[s]);
                }
             }
             if (!ok) break;
@@ -133,30 +155,38 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          bool ok = true;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, lt++) {
             const int buf = lt & 1;
-            if (!mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt)) break;
+            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt))) break;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+            const uint32_t d_base = tmem_base + (uint32_t)(buf * NACC * BN);
+            int mma_idx = 0; // MMAs issued for this tile
             for (int st = 0; st < stages_per_tile; st++, g++) {
                const int s = g % S;
                const uint32_t ph = (g / S) & 1;
-               ok = (KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
-                                    : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g);
+               ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
+                                                    : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
                if (!ok) break;
                tc_fence_after();
-               const uint64_t da = make_smem_desc(smem_u32(a_hi(s)), CB);
-               const uint64_t db = make_smem_desc(smem_u32(b_hi(s)), CB);
 #pragma unroll
-               for (int k = 0; k < CB / 32; k++) {
-                  const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K = 2 units of 16 bytes
-                  const uint32_t accumulate = (st == 0 && k == 0) ? 0u : 1u;
-                  if constexpr (KIND == kTF32) {
-                     const uint64_t dal = make_smem_desc(smem_u32(a_lo(s)), CB);
-                     const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)), CB);
-                     tc_mma<KIND>(d_tmem, dal + koff, db + koff, idesc, accumulate);
-                     tc_mma<KIND>(d_tmem, da + koff, dbl + koff, idesc, 1);
-                     tc_mma<KIND>(d_tmem, da + koff, db + koff, idesc, 1);
-                  } else {
-                     tc_mma<KIND>(d_tmem, da + koff, db + koff, idesc, accumulate);
+               for (int sub = 0; sub < TPS; sub++) {
+                  const uint64_t da = make_smem_desc(smem_u32(a_hi(s, sub)), CB);
+                  const uint64_t db = make_smem_desc(smem_u32(b_hi(s, sub)), CB);
+#pragma unroll
+                  for (int k = 0; k < CB / 32; k++) {
+                     const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K = 2 units of 16 bytes
+                     // the first MMA into each accumulator overwrites it, the later ones add
+                     auto issue = [&](uint64_t adesc, uint64_t bdesc) {
+                        tc_mma<KIND>(d_base + (uint32_t)((mma_idx % NACC) * BN), adesc, bdesc, idesc, mma_idx >= NACC ? 1u : 0u);
+                        mma_idx++;
+                     };
+                     if constexpr (KIND == kTF32) {
+                        const uint64_t dal = make_smem_desc(smem_u32(a_lo(s, sub)), CB);
+                        const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s, sub)), CB);
+                        issue(dal + koff, db + koff);
+                        issue(da + koff, dbl + koff);
+                        issue(da + koff, db + koff);
+                     } else {
+                        issue(da + koff, db + koff);
+                     }
                   }
                }
                tc_commit(&empty_bar[s]);
@@ -164,33 +194,45 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
             if (ok) tc_commit(&tmem_full[buf]);
          }
       }
-   } else if (warp >= 6) {
-      // ---------------- converter warps 6..9 (kTF32): hi/lo split of each stage ----------------
+   } else if (warp >= 2 + EPI_WARPS) {
+      // ---------------- converter warps (kTF32): hi/lo split of each stage ----------------
       if constexpr (KIND == kTF32) {
-         const int t = threadIdx.x - 192; // 0..127
+         constexpr int NT = kConvConverterWarps * 32;
+         const int t = threadIdx.x - (2 + EPI_WARPS) * 32; // 0..NT-1
          int g = 0;
          bool ok = true;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
             for (int st = 0; st < stages_per_tile; st++, g++) {
                const int s = g % S;
                const uint32_t ph = (g / S) & 1;
-               if (!mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g)) {
+               if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) {
                   ok = false;
                   break;
                }
-               float4 *hi = reinterpret_cast<float4 *>(a_hi(s));
-               float4 *lo = reinterpret_cast<float4 *>(a_lo(s));
-               constexpr int n4 = (A_TILE + B_TILE) / 16;
-#pragma unroll 2
-               for (int i = t; i < n4; i += 128) {
-                  float4 v = hi[i], h, l;
-                  uint32_t u;
-                  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.x)); h.x = __uint_as_float(u); l.x = v.x - h.x;
-                  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.y)); h.y = __uint_as_float(u); l.y = v.y - h.y;
-                  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.z)); h.z = __uint_as_float(u); l.z = v.z - h.z;
-                  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.w)); h.w = __uint_as_float(u); l.w = v.w - h.w;
-                  hi[i] = h;
-                  lo[i] = l;
+               // The split is elementwise, so the swizzled placement does not matter. All loads of
+               // a thread are issued before the first conversion so that their latencies overlap.
+               // the TPS sub-blocks of a stage are contiguous: element i of the hi part of sub-block k
+               // sits at k*SUB_BYTES + i*16, its lo twin (A_TILE + B_TILE) bytes further
+               constexpr int sub4 = (A_TILE + B_TILE) / 16, n4 = TPS * sub4;
+               constexpr int PER = (n4 + NT - 1) / NT;
+               float4 v[PER];
+               auto at = [&](int idx) { return reinterpret_cast<float4 *>(a_hi(s, idx / sub4)) + (idx % sub4); };
+#pragma unroll
+               for (int i = 0; i < PER; i++)
+                  if (t + i * NT < n4) v[i] = *at(t + i * NT);
+#pragma unroll
+               for (int i = 0; i < PER; i++) {
+                  if (t + i * NT < n4) {
+                     float4 *p = at(t + i * NT);
+                     float4 h, l;
+                     uint32_t u;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[i].x)); h.x = __uint_as_float(u); l.x = v[i].x - h.x;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[i].y)); h.y = __uint_as_float(u); l.y = v[i].y - h.y;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[i].z)); h.z = __uint_as_float(u); l.z = v[i].z - h.z;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[i].w)); h.w = __uint_as_float(u); l.w = v[i].w - h.w;
+                     p[0] = h;
+                     p[sub4] = l;
+                  }
                }
                fence_proxy_async();
                mbar_arrive(&conv_bar[s]);
@@ -198,8 +240,14 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          }
       }
    } else {
-      // ---------------- epilogue warps 2..5 ----------------
+      // ---------------- epilogue warps 2..9 ----------------
+      // A warp reads the 32 TMEM lanes (pixels) its id modulo 4 selects; the two warps of a lane
+      // quarter split the output channels.
+      const int e = warp - 2;
       const int lane_base = (warp & 3) * 32;
+      constexpr int CW = BN >= 64 ? BN / 2 : BN;            // channels per warp
+      const int c_begin = BN >= 64 ? (e >> 2) * CW : 0;
+      const bool has_columns = BN >= 64 || (e >> 2) == 0;
       const int pix = lane_base + lane; // pixel of the patch = TMEM lane
       const int ww = pix % tg.tileW, hh = (pix / tg.tileW) % tg.tileH, nn = pix / (tg.tileW * tg.tileH);
       const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
@@ -208,7 +256,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          const int buf = lt & 1;
          int n0, h0, w0;
          tile_origin(tile, n0, h0, w0);
-         if (!mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt)) break;
+         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
          tc_fence_after();
          const int n = n0 + nn, h = h0 + hh, w = w0 + ww;
          const bool valid = n < tg.N;
@@ -217,68 +265,75 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          const int oH = ep.pool ? tg.H / 2 : tg.H, oW = ep.pool ? tg.W / 2 : tg.W;
          const int oh = ep.pool ? h / 2 : h, ow = ep.pool ? w / 2 : w;
          const size_t opix = ((size_t)n * oH + oh) * oW + ow;
+         if (has_columns) {
 #pragma unroll 1
-         for (int c0 = 0; c0 < BN; c0 += 32) {
-            if (c0 >= tg.Cout) break;
-            uint32_t r[32];
-            tmem_ld_32x32(t_row + (uint32_t)(buf * BN + c0), r);
-            tmem_ld_wait();
-            const int ncols = min(32, tg.Cout - c0);
-            if constexpr (KIND == kTF32) {
-               float v[32];
+            for (int c0 = c_begin; c0 < c_begin + CW; c0 += 32) {
+               if (c0 >= tg.Cout) break;
+               // sum of the NACC partial accumulators of this tile
+               uint32_t r[32];
+               tmem_ld_32x32(t_row + (uint32_t)(buf * NACC * BN + c0), r);
+               tmem_ld_wait();
 #pragma unroll
-               for (int j = 0; j < 32; j++) {
-                  float acc = __uint_as_float(r[j]);
-                  if (ep.bias && j < ncols) acc += ep.bias[c0 + j];
-                  v[j] = ep.relu ? relu_ref(acc) : acc;
-               }
-               if (ep.pool) {
+               for (int a = 1; a < NACC; a++) {
+                  uint32_t p[32];
+                  tmem_ld_32x32(t_row + (uint32_t)((buf * NACC + a) * BN + c0), p);
+                  tmem_ld_wait();
 #pragma unroll
                   for (int j = 0; j < 32; j++) {
-                     float o = __shfl_xor_sync(0xffffffffu, v[j], 1);
-                     v[j] = o > v[j] ? o : v[j];
-                     o = __shfl_xor_sync(0xffffffffu, v[j], tg.tileW);
-                     v[j] = o > v[j] ? o : v[j];
+                     if constexpr (KIND == kTF32) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(p[j]));
+                     else r[j] = (uint32_t)((int)r[j] + (int)p[j]);
                   }
                }
-               if (store) {
-                  float *y = ep.Yf + opix * tg.Cout + c0;
-                  if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
-#pragma unroll
-                     for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                  } else {
-#pragma unroll
-                     for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
-                  }
-               }
-            } else {
-               int q[32];
-#pragma unroll
-               for (int j = 0; j < 32; j++) {
-                  q[j] = 0;
-                  if (j < ncols) {
-                     int acc = (int)r[j] + (ep.qbias ? ep.qbias[c0 + j] : 0);
-                     q[j] = requant_u8(acc, ep.mult[c0 + j], ep.y_zp, ep.relu);
-                  }
-               }
-               if (ep.pool) {
+               const int ncols = min(32, tg.Cout - c0);
+               if constexpr (KIND == kTF32) {
+                  float v[32];
 #pragma unroll
                   for (int j = 0; j < 32; j++) {
-                     q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], 1));
-                     q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], tg.tileW));
+                     float acc = __uint_as_float(r[j]) + s_bias[c0 + j];
+                     v[j] = ep.relu ? relu_ref(acc) : acc;
                   }
-               }
-               if (store) {
-                  uint8_t *y = ep.Yu8 + opix * tg.Cout + c0;
-                  uint32_t packed[8];
+                  if (ep.pool) {
 #pragma unroll
-                  for (int j = 0; j < 32; j += 4) packed[j >> 2] = (uint32_t)q[j] | ((uint32_t)q[j + 1] << 8) | ((uint32_t)q[j + 2] << 16) | ((uint32_t)q[j + 3] << 24);
-                  if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
-                     *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                     *reinterpret_cast<uint4 *>(y + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                  } else {
+                     for (int j = 0; j < 32; j++) {
+                        float o = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                        v[j] = o > v[j] ? o : v[j];
+                        o = __shfl_xor_sync(0xffffffffu, v[j], tg.tileW);
+                        v[j] = o > v[j] ? o : v[j];
+                     }
+                  }
+                  if (store) {
+                     float *y = ep.Yf + opix * tg.Cout + c0;
+                     if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
 #pragma unroll
-                     for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)q[j];
+                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                     } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
+                     }
+                  }
+               } else {
+                  int q[32];
+#pragma unroll
+                  for (int j = 0; j < 32; j++) q[j] = requant_u8((int)r[j] + s_qbias[c0 + j], s_mult[c0 + j], ep.y_zp, ep.relu);
+                  if (ep.pool) {
+#pragma unroll
+                     for (int j = 0; j < 32; j++) {
+                        q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], 1));
+                        q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], tg.tileW));
+                     }
+                  }
+                  if (store) {
+                     uint8_t *y = ep.Yu8 + opix * tg.Cout + c0;
+                     uint32_t packed[8];
+#pragma unroll
+                     for (int j = 0; j < 32; j += 4) packed[j >> 2] = (uint32_t)q[j] | ((uint32_t)q[j + 1] << 8) | ((uint32_t)q[j + 2] << 16) | ((uint32_t)q[j + 3] << 24);
+                     if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+                        *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        *reinterpret_cast<uint4 *>(y + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                     } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)q[j];
+                     }
                   }
                }
             }
@@ -289,6 +344,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       }
    }
+   SOFIE_PROF_REPORT(warp == 0 ? "producer" : (warp == 1 ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
    // A wait gives up only after about a second, long after every copy and MMA of this CTA landed.
    tc_fence_before();
    __syncthreads();
@@ -300,27 +356,37 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 }
 
 // ------------------------------------------------------------------------------------------------
-template <int KIND, int BN, int CB>
-static int launch_conv_one(cudaStream_t s, const CUtensorMap &tmX, const CUtensorMap &tmW, const ConvEpilogue &ep, ConvTiling tg)
+template <int KIND, int BN, int CB, int TPS>
+static int launch_conv_tps(cudaStream_t s, const CUtensorMap &tmX, const CUtensorMap &tmW, const ConvEpilogue &ep, ConvTiling tg)
 {
-   constexpr int ES = (KIND == kTF32) ? 4 : 1;
    constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
-   constexpr int STAGE_BYTES = COPIES * (128 + BN) * CB;
-   (void)ES;
+   constexpr int STAGE_BYTES = TPS * COPIES * (128 + BN) * CB;
    int stages = (200 * 1024) / STAGE_BYTES;
    if (stages > kConvMaxStages) stages = kConvMaxStages;
    if (stages < 2) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "convolution tile does not fit in shared memory");
    tg.stages = stages;
    const int smem = stages * STAGE_BYTES + 1024;
-   auto kern = umma_conv3x3_kernel<KIND, BN, CB>;
+   auto kern = umma_conv3x3_kernel<KIND, BN, CB, TPS>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
    uint32_t *status = device_status_word();
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int grid = tg.num_tiles < kNumSMs ? tg.num_tiles : kNumSMs;
-   kern<<<grid, KIND == kTF32 ? 320 : 192, smem, s>>>(tmX, tmW, ep, tg, status);
+   kern<<<grid, KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8, smem, s>>>(tmX, tmW, ep, tg, status);
    SOFIE_LAUNCH_CHECK("umma_conv3x3_kernel");
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;
+}
+
+template <int KIND, int BN, int CB>
+static int launch_conv_one(cudaStream_t s, const CUtensorMap &tmX, const CUtensorMap &tmW, const ConvEpilogue &ep, const ConvTiling &tg)
+{
+   // three taps per stage when one tap is a single channel chunk and three such stages still fit
+   constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
+   constexpr bool kFits3 = 3 * 3 * COPIES * (128 + BN) * CB <= 200 * 1024;
+   if constexpr (kFits3) {
+      if (tg.chunks == 1) return launch_conv_tps<KIND, BN, CB, 3>(s, tmX, tmW, ep, tg);
+   }
+   return launch_conv_tps<KIND, BN, CB, 1>(s, tmX, tmW, ep, tg);
 }
 
 template <int KIND, int BN>

@@ -6,9 +6,10 @@
 //   kI8   : uint8 x int8 -> int32, epilogue requantises to uint8.
 //   kF8   : E4M3 x E4M3 -> fp32, epilogue scales, adds bias, Relu, writes bf16 and/or E4M3.
 //
-// CTA = 6 warps: warp 0 issues TMA, warp 1 allocates TMEM and issues MMA, warps 2-5 split the
-// fp32 tiles (kTF32 only) during the main loop and afterwards drain the accumulator (each warp owns
-// the 32 TMEM lanes its warp id modulo 4 selects). One CTA computes one 128 x BN output tile.
+// Persistent CTAs (one per SM). Warp 0 issues TMA, warp 1 allocates TMEM and issues MMA; kI8 / kF8
+// have 16 epilogue warps (warps 2-17: each owns the 32 TMEM lanes its warp id modulo 4 selects and
+// every fourth 32-column chunk); kTF32 has 4 epilogue warps (2-5) and 8 converter warps (6-13) that split
+// every stage into hi / lo. Two TMEM accumulator buffers overlap epilogue and MMAs.
 #include "umma.cuh"
 #include "contract.cuh"
 
@@ -82,7 +83,6 @@ struct GemmEpilogue {
 constexpr int kBM = 128;        // rows of the output tile = TMEM lanes
 constexpr int kStageK = 128;    // bytes of K per pipeline stage = one 128B swizzle row
 constexpr int kMmaK = 32;       // bytes of K per tcgen05.mma
-constexpr int kGemmThreads = 192;
 
 template <int KIND, int BN>
 struct GemmSmem {
@@ -183,32 +183,44 @@ __device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const ui
 
 // fp32 only: the tensor core adds into its accumulator with truncation, so a long K drifts (about
 // 3e-5 of the result at K = 4096). The fp32 kernel therefore accumulates at most kPromoteKB stages
-// (256 elements of K) in TMEM, then adds that partial sum into fp32 registers with round-to-nearest
-// while the tensor core fills the second TMEM buffer.
+// (256 elements of K) in one TMEM buffer, and the epilogue warps add that partial sum into fp32
+// registers with round-to-nearest while the tensor core fills the other TMEM buffer.
 constexpr int kPromoteKB = 8;
+constexpr int kGemmConverterWarps = 8;   // kTF32: warps 6..13 split the stages into hi / lo
+constexpr int kGemmEpilogueWarps8 = 16;  // kI8 / kF8: warps 2..17 drain the accumulator
+constexpr int kGemmMaxStages = 8;
 
-template <int KIND, int BN, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int KIND> constexpr int gemm_threads() { return KIND == kTF32 ? (6 + kGemmConverterWarps) * 32 : (2 + kGemmEpilogueWarps8) * 32; }
+
+// Persistent kernel: each CTA walks output tiles (N fastest, so CTAs running together share A rows
+// and all of B through L2). Work is handed between the roles in "units": one unit = what is
+// accumulated in one TMEM buffer before the epilogue warps drain it -- a whole tile for kI8 / kF8,
+// kPromoteKB stages of a tile for kTF32. Two TMEM buffers: the MMAs of unit u+1 overlap the drain
+// of unit u.
+template <int KIND, int BN>
+__global__ void __launch_bounds__(gemm_threads<KIND>(), 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmEpilogue ep,
-                 int M, int N, int K, uint32_t *status)
+                 int M, int N, int K, int S, uint32_t *status)
 {
    using L = GemmSmem<KIND, BN>;
    constexpr int ES = (KIND == kTF32) ? 4 : 1;           // element size in bytes
    constexpr int KE = kStageK / ES;                      // elements of K per stage
-   constexpr int NBUF = (KIND == kTF32) ? 2 : 1;         // TMEM accumulator buffers
-   constexpr uint32_t TMEM_COLS = NBUF * BN < 32 ? 32 : NBUF * BN; // power of two >= 32
+   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+   constexpr int EPI_WARPS = (KIND == kTF32) ? 4 : kGemmEpilogueWarps8;
    extern __shared__ unsigned char smem_raw[];
    // 1024-byte alignment: the 128B swizzle pattern repeats every 1024 bytes and is address based.
    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-   __shared__ uint64_t full_bar[STAGES], conv_bar[STAGES], empty_bar[STAGES], accum_full[2], accum_empty[2];
+   __shared__ uint64_t full_bar[kGemmMaxStages], conv_bar[kGemmMaxStages], empty_bar[kGemmMaxStages], tmem_full[2], tmem_empty[2];
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-   const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
+   SOFIE_PROF_DECL
+   const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + kBM - 1) / kBM;
+   const int num_tiles = tiles_m * tiles_n;
    const int num_kb = (K * ES + kStageK - 1) / kStageK;
-   const int chunk_kb = (KIND == kTF32) ? kPromoteKB : num_kb; // stages accumulated in TMEM before a drain
-   const int num_chunks = (num_kb + chunk_kb - 1) / chunk_kb;
+   const int chunk_kb = (KIND == kTF32) ? kPromoteKB : num_kb; // stages accumulated in TMEM per unit
+   const int units_per_tile = (num_kb + chunk_kb - 1) / chunk_kb;
 
    auto a_hi = [&](int s) { return smem + (size_t)s * L::kStageBytes; };
    auto b_hi = [&](int s) { return smem + (size_t)s * L::kStageBytes + L::kATile; };
@@ -216,14 +228,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
    auto b_lo = [&](int s) { return smem + (size_t)s * L::kStageBytes + 2 * L::kATile + L::kBTile; };
 
    if (threadIdx.x == 0) {
-      for (int s = 0; s < STAGES; s++) {
+      for (int s = 0; s < kGemmMaxStages; s++) {
          mbar_init(&full_bar[s], 1);
-         mbar_init(&conv_bar[s], 128);
+         mbar_init(&conv_bar[s], kGemmConverterWarps * 32);
          mbar_init(&empty_bar[s], 1);
       }
       for (int b = 0; b < 2; b++) {
-         mbar_init(&accum_full[b], 1);
-         mbar_init(&accum_empty[b], 128);
+         mbar_init(&tmem_full[b], 1);
+         mbar_init(&tmem_empty[b], EPI_WARPS);
       }
       abort_flag = 0;
       fence_mbar_init();
@@ -242,140 +254,181 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
    if (warp == 0) {
       // ---------------- TMA producer ----------------
       if (lane == 0) {
-         for (int kb = 0; kb < num_kb; kb++) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, kb)) break;
-            mbar_expect_tx(&full_bar[s], L::kATile + L::kBTile);
-            tma_load_2d(a_hi(s), &tmA, kb * KE, m0, &full_bar[s]);
-            tma_load_2d(b_hi(s), &tmB, kb * KE, n0, &full_bar[s]);
+         int g = 0;
+         bool ok = true;
+         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+            for (int kb = 0; kb < num_kb; kb++, g++) {
+               const int s = g % S;
+               const uint32_t ph = (g / S) & 1;
+               if (!SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g))) {
+                  ok = false;
+                  break;
+               }
+               mbar_expect_tx(&full_bar[s], L::kATile + L::kBTile);
+               tma_load_2d(a_hi(s), &tmA, kb * KE, m0, &full_bar[s]);
+               tma_load_2d(b_hi(s), &tmB, kb * KE, n0, &full_bar[s]);
+            }
          }
       }
    } else if (warp == 1) {
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
          constexpr uint32_t idesc = make_idesc<KIND>(kBM, BN);
-         for (int kb = 0; kb < num_kb; kb++) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            const int chunk = kb / chunk_kb, buf = chunk & (NBUF - 1);
-            const bool chunk_start = (kb % chunk_kb) == 0;
-            if (chunk_start && chunk >= NBUF) {
-               // the buffer is reused: the worker warps must have drained chunk - NBUF from it
-               if (!mbar_wait(&accum_empty[buf], ((chunk / NBUF) - 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x1000 + chunk)) break;
-               tc_fence_after();
-            }
-            bool ok = (KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, kb)
-                                      : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, kb);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-            const uint64_t da = make_smem_desc(smem_u32(a_hi(s)), kStageK);
-            const uint64_t db = make_smem_desc(smem_u32(b_hi(s)), kStageK);
-#pragma unroll
-            for (int k = 0; k < kStageK / kMmaK; k++) {
-               // advancing K inside the swizzle row: +32 bytes = +2 in the (>>4) address field
-               const uint64_t koff = (uint64_t)(k * (kMmaK >> 4));
-               const uint32_t accumulate = (chunk_start && k == 0) ? 0u : 1u;
-               if constexpr (KIND == kTF32) {
-                  const uint64_t dal = make_smem_desc(smem_u32(a_lo(s)), kStageK);
-                  const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)), kStageK);
-                  tc_mma<KIND>(d_tmem, dal + koff, db + koff, idesc, accumulate);
-                  tc_mma<KIND>(d_tmem, da + koff, dbl + koff, idesc, 1);
-                  tc_mma<KIND>(d_tmem, da + koff, db + koff, idesc, 1);
-               } else {
-                  tc_mma<KIND>(d_tmem, da + koff, db + koff, idesc, accumulate);
+         int g = 0, u = 0;
+         bool ok = true;
+         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int c = 0; c < units_per_tile && ok; c++, u++) {
+               const int buf = u & 1;
+               if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((u >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x1000 + u))) {
+                  ok = false;
+                  break;
                }
+               tc_fence_after();
+               const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+               const int kb_end = min(num_kb, (c + 1) * chunk_kb);
+               for (int kb = c * chunk_kb; kb < kb_end; kb++, g++) {
+                  const int s = g % S;
+                  const uint32_t ph = (g / S) & 1;
+                  ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
+                                                       : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
+                  if (!ok) break;
+                  tc_fence_after();
+                  const uint64_t da = make_smem_desc(smem_u32(a_hi(s)), kStageK);
+                  const uint64_t db = make_smem_desc(smem_u32(b_hi(s)), kStageK);
+#pragma unroll
+                  for (int k = 0; k < kStageK / kMmaK; k++) {
+                     // advancing K inside the swizzle row: +32 bytes = +2 in the (>>4) address field
+                     const uint64_t koff = (uint64_t)(k * (kMmaK >> 4));
+                     const uint32_t accumulate = (kb == c * chunk_kb && k == 0) ? 0u : 1u;
+                     if constexpr (KIND == kTF32) {
+                        const uint64_t dal = make_smem_desc(smem_u32(a_lo(s)), kStageK);
+                        const uint64_t dbl = make_smem_desc(smem_u32(b_lo(s)), kStageK);
+                        tc_mma<KIND>(d_tmem, dal + koff, db + koff, idesc, accumulate);
+                        tc_mma<KIND>(d_tmem, da + koff, dbl + koff, idesc, 1);
+                        tc_mma<KIND>(d_tmem, da + koff, db + koff, idesc, 1);
+                     } else {
+                        tc_mma<KIND>(d_tmem, da + koff, db + koff, idesc, accumulate);
+                     }
+                  }
+                  tc_commit(&empty_bar[s]); // the stage is free once these MMAs have read it
+               }
+               if (ok) tc_commit(&tmem_full[buf]);
             }
-            tc_commit(&empty_bar[s]); // the stage is free once these MMAs have read it
-            if ((kb % chunk_kb) == chunk_kb - 1 || kb == num_kb - 1) tc_commit(&accum_full[buf]);
+         }
+      }
+   } else if (warp >= 2 + EPI_WARPS) {
+      // ---------------- converter warps (kTF32): hi / lo split of every stage ----------------
+      if constexpr (KIND == kTF32) {
+         constexpr int NT = kGemmConverterWarps * 32;
+         const int t = threadIdx.x - (2 + EPI_WARPS) * 32;
+         int g = 0;
+         bool ok = true;
+         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < num_kb; kb++, g++) {
+               const int s = g % S;
+               const uint32_t ph = (g / S) & 1;
+               if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) {
+                  ok = false;
+                  break;
+               }
+               // The split is elementwise, so the swizzled placement does not matter: the lo tile is
+               // written at the same offsets as the hi tile (A and B tiles are contiguous). All loads
+               // of a thread are issued before the first conversion so that their latencies overlap.
+               float4 *hi = reinterpret_cast<float4 *>(a_hi(s));
+               float4 *lo = reinterpret_cast<float4 *>(a_lo(s));
+               constexpr int n4 = (L::kATile + L::kBTile) / 16;
+               constexpr int PER = (n4 + NT - 1) / NT;
+               float4 v[PER];
+#pragma unroll
+               for (int i = 0; i < PER; i++)
+                  if (t + i * NT < n4) v[i] = hi[t + i * NT];
+#pragma unroll
+               for (int i = 0; i < PER; i++) {
+                  if (t + i * NT < n4) {
+                     float4 h, l;
+                     uint32_t w;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w) : "f"(v[i].x)); h.x = __uint_as_float(w); l.x = v[i].x - h.x;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w) : "f"(v[i].y)); h.y = __uint_as_float(w); l.y = v[i].y - h.y;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w) : "f"(v[i].z)); h.z = __uint_as_float(w); l.z = v[i].z - h.z;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w) : "f"(v[i].w)); h.w = __uint_as_float(w); l.w = v[i].w - h.w;
+                     hi[t + i * NT] = h;
+                     lo[t + i * NT] = l;
+                  }
+               }
+               fence_proxy_async(); // make the generic-proxy writes visible to the tensor-core (async) proxy
+               mbar_arrive(&conv_bar[s]);
+            }
          }
       }
    } else {
-      // ---------------- worker warps 2..5: fp32 split + promotion (kTF32), then the epilogue ----------------
-      const int t = threadIdx.x - 64; // 0..127
+      // ---------------- epilogue warps ----------------
+      // TMEM lanes a warp may read are fixed by (warp id mod 4); with 8 epilogue warps two warps
+      // share a lane quarter and split the columns.
       const int lane_base = (warp & 3) * 32;
-      const int row = m0 + lane_base + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
-      if constexpr (KIND == kTF32) {
-         float acc[BN];
+      // the EPI_WARPS / 4 warps of a lane quarter take the 32-column chunks of the tile round-robin
+      constexpr int GROUPS = EPI_WARPS / 4;
+      const int group = (warp - 2) >> 2;
+      int u = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+         const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+         const int row = m0 + lane_base + lane;
+         if constexpr (KIND == kTF32) {
+            float acc[BN];
 #pragma unroll
-         for (int j = 0; j < BN; j++) acc[j] = 0.f;
-         bool alive = true;
-         // adds the finished TMEM partial sum of chunk `d` into the registers
-         auto drain = [&](int d) {
-            const int buf = d & 1;
-            if (!mbar_wait(&accum_full[buf], (d >> 1) & 1, &abort_flag, status, kStatusWaitAccum, d)) {
-               alive = false;
-               return;
+            for (int j = 0; j < BN; j++) acc[j] = 0.f;
+            for (int c = 0; c < units_per_tile; c++, u++) {
+               const int buf = u & 1;
+               if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (u >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + u))) {
+                  ok = false;
+                  break;
+               }
+               tc_fence_after();
+#pragma unroll
+               for (int c0 = 0; c0 < BN; c0 += 32) {
+                  uint32_t r[32];
+                  tmem_ld_32x32(t_row + (uint32_t)(buf * BN + c0), r);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int j = 0; j < 32; j++) acc[c0 + j] += __uint_as_float(r[j]);
+               }
+               tc_fence_before();
+               __syncwarp();
+               if (lane == 0) mbar_arrive(&tmem_empty[buf]);
             }
-            tc_fence_after();
+            if (ok && row < M) {
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+               for (int c0 = 0; c0 < BN; c0 += 32) {
+                  if (n0 + c0 < N) {
+                     uint32_t r[32];
+#pragma unroll
+                     for (int j = 0; j < 32; j++) r[j] = __float_as_uint(acc[c0 + j]);
+                     store_row_chunk<KIND>(ep, r, row, n0 + c0, N);
+                  }
+               }
+            }
+         } else {
+            const int buf = u & 1;
+            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (u >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + u))) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = group * 32; c0 < BN; c0 += GROUPS * 32) {
+               if (n0 + c0 >= N) break;
                uint32_t r[32];
                tmem_ld_32x32(t_row + (uint32_t)(buf * BN + c0), r);
                tmem_ld_wait();
-#pragma unroll
-               for (int j = 0; j < 32; j++) acc[c0 + j] += __uint_as_float(r[j]);
-            }
-            tc_fence_before();
-            mbar_arrive(&accum_empty[buf]);
-         };
-         int next_drain = 0;
-         for (int kb = 0; kb < num_kb && alive; kb++) {
-            const int s = kb % STAGES;
-            const uint32_t ph = (kb / STAGES) & 1;
-            if (!mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, kb)) {
-               alive = false;
-               break;
-            }
-            // The split is elementwise, so the swizzled placement does not matter: the lo tile is
-            // written at the same offsets as the hi tile. A and B tiles are contiguous.
-            float4 *hi = reinterpret_cast<float4 *>(a_hi(s));
-            float4 *lo = reinterpret_cast<float4 *>(a_lo(s));
-            constexpr int n4 = (L::kATile + L::kBTile) / 16;
-#pragma unroll 4
-            for (int i = t; i < n4; i += 128) {
-               float4 v = hi[i], h, l;
-               uint32_t u;
-               asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.x)); h.x = __uint_as_float(u); l.x = v.x - h.x;
-               asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.y)); h.y = __uint_as_float(u); l.y = v.y - h.y;
-               asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.z)); h.z = __uint_as_float(u); l.z = v.z - h.z;
-               asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.w)); h.w = __uint_as_float(u); l.w = v.w - h.w;
-               hi[i] = h;
-               lo[i] = l;
-            }
-            fence_proxy_async(); // make the generic-proxy writes visible to the tensor-core (async) proxy
-            mbar_arrive(&conv_bar[s]);
-            // a chunk is drained two stages after its last stage was split, when its MMAs are (almost) done
-            if (next_drain < num_chunks && kb >= (next_drain + 1) * chunk_kb + 1) drain(next_drain++);
-         }
-         while (alive && next_drain < num_chunks) drain(next_drain++);
-         if (alive && row < M) {
-#pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-               if (n0 + c0 < N) {
-                  uint32_t r[32];
-#pragma unroll
-                  for (int j = 0; j < 32; j++) r[j] = __float_as_uint(acc[c0 + j]);
-                  store_row_chunk<KIND>(ep, r, row, n0 + c0, N);
-               }
-            }
-         }
-      } else {
-         if (mbar_wait(&accum_full[0], 0, &abort_flag, status, kStatusWaitAccum, 0)) {
-            tc_fence_after();
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-               if (n0 + c0 >= N) break;
-               uint32_t r[32];
-               tmem_ld_32x32(t_row + (uint32_t)c0, r);
-               tmem_ld_wait();
                if (row < M) store_row_chunk<KIND>(ep, r, row, n0 + c0, N);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            u++;
          }
       }
    }
+   SOFIE_PROF_REPORT(warp == 0 ? "producer" : (warp == 1 ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
    // A wait only gives up after about a second, long after every copy and MMA this CTA issued has
    // landed, so nothing is in flight when the TMEM columns are released below.
    tc_fence_before();
@@ -388,21 +441,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------
-template <int KIND, int BN, int STAGES>
+template <int KIND, int BN>
 static int launch_one(cudaStream_t s, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmEpilogue &ep, int M,
                       int N, int K)
 {
    using L = GemmSmem<KIND, BN>;
-   constexpr int smem = STAGES * L::kStageBytes + 1024;
-   static_assert(smem <= 227 * 1024, "shared memory budget exceeded");
-   auto kern = umma_gemm_kernel<KIND, BN, STAGES>;
-   static bool configured = false; // per instantiation; attribute is per device but set idempotently below
-   (void)configured;
+   int stages = (200 * 1024) / L::kStageBytes;
+   if (stages > kGemmMaxStages) stages = kGemmMaxStages;
+   const int smem = stages * L::kStageBytes + 1024;
+   auto kern = umma_gemm_kernel<KIND, BN>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
    uint32_t *status = device_status_word();
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
-   dim3 grid(ceil_div(N, BN), ceil_div(M, kBM));
-   kern<<<grid, kGemmThreads, smem, s>>>(tmA, tmB, ep, M, N, K, status);
+   const int tiles = ceil_div(N, BN) * ceil_div(M, kBM);
+   const int grid = tiles < kNumSMs ? tiles : kNumSMs;
+   kern<<<grid, gemm_threads<KIND>(), smem, s>>>(tmA, tmB, ep, M, N, K, stages, status);
    SOFIE_LAUNCH_CHECK("umma_gemm_kernel");
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;
@@ -415,7 +468,8 @@ static int launch_umma_gemm(cudaStream_t s, const void *A, const void *B, const 
    if (M <= 0 || N <= 0 || K <= 0) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "empty GEMM");
    if (((size_t)K * ES) % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
       return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "TMA needs 16-byte aligned rows (K*%d %% 16 == 0) and bases", ES);
-   const int BN = N <= 32 ? 32 : (N <= 64 ? 64 : ((KIND == kTF32 || N <= 128) ? 128 : 256));
+   // fp32 keeps the tile's running sum in registers (promotion), which bounds its width at 64 columns
+   const int BN = N <= 32 ? 32 : ((N <= 64 || KIND == kTF32) ? 64 : (N <= 128 ? 128 : 256));
    CUtensorMap tmA, tmB;
    const CUtensorMapDataType dt = (KIND == kTF32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
    uint64_t dimsA[2] = {(uint64_t)K, (uint64_t)M}, dimsB[2] = {(uint64_t)K, (uint64_t)N};
@@ -426,17 +480,14 @@ static int launch_umma_gemm(cudaStream_t s, const void *A, const void *B, const 
    rc = make_tensor_map(&tmB, dt, 2, B, dimsB, stride, boxB, 128);
    if (rc) return rc;
    if constexpr (KIND == kTF32) {
-      switch (BN) {
-      case 32: return launch_one<KIND, 32, 4>(s, tmA, tmB, ep, M, N, K);
-      case 64: return launch_one<KIND, 64, 4>(s, tmA, tmB, ep, M, N, K);
-      default: return launch_one<KIND, 128, 3>(s, tmA, tmB, ep, M, N, K);
-      }
+      if (BN == 32) return launch_one<KIND, 32>(s, tmA, tmB, ep, M, N, K);
+      return launch_one<KIND, 64>(s, tmA, tmB, ep, M, N, K);
    } else {
       switch (BN) {
-      case 32: return launch_one<KIND, 32, 6>(s, tmA, tmB, ep, M, N, K);
-      case 64: return launch_one<KIND, 64, 6>(s, tmA, tmB, ep, M, N, K);
-      case 128: return launch_one<KIND, 128, 6>(s, tmA, tmB, ep, M, N, K);
-      default: return launch_one<KIND, 256, 4>(s, tmA, tmB, ep, M, N, K);
+      case 32: return launch_one<KIND, 32>(s, tmA, tmB, ep, M, N, K);
+      case 64: return launch_one<KIND, 64>(s, tmA, tmB, ep, M, N, K);
+      case 128: return launch_one<KIND, 128>(s, tmA, tmB, ep, M, N, K);
+      default: return launch_one<KIND, 256>(s, tmA, tmB, ep, M, N, K);
       }
    }
 }
