@@ -55,43 +55,62 @@ def tensor_peak_tflops(workload, pk):
 
 
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi polled every 20 ms for the whole run; stop() keeps the samples that fall inside the
+    timed windows (device-timed steps and end-to-end steps)."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.proc = None
+        self.windows = []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
 
+    def window(self, t0, t1):
+        self.windows.append((t0, t1))
+
     def stop(self):
+        import datetime
         if not self.proc:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, smax, reasons = [], [], set()
+        rows = []
         for line in out.splitlines():
             f = [c.strip() for c in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(f[1]), float(f[2]), f[5:9]))
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+        inside = [r for r in rows if any(t0 - 0.02 <= r[0] <= t1 + 0.02 for t0, t1 in self.windows)]
+        scope = "timed windows"
+        if not inside:  # the timed region was shorter than one sampling period: use the run under load
+            lo = min((t0 for t0, _ in self.windows), default=0) - 1.0
+            inside, scope = [r for r in rows if r[0] >= lo], "whole measurement phase (timed region shorter than one sample)"
+        reasons = set()
+        for r in inside:
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=max(smax) if smax else None,
-                    reasons=sorted(reasons), samples=len(sm))
+        return dict(sm_mhz=float(np.median([r[1] for r in inside])) if inside else None,
+                    sm_max_mhz=max((r[2] for r in inside), default=None), reasons=sorted(reasons), samples=len(inside), scope=scope)
+
+
+# DRAM traffic per launch of the dominant kernels, from ncu captures (profiles/): bytes read + written.
+NCU_TRAFFIC = {}
 
 
 def build_workload(workload, batch_scale=1):
@@ -211,6 +230,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    os.environ["SOFIE_CUDA_DEVICE"] = str(local_rank)  # the emitted Session reads its device from here
+    clocks = ClockSampler(local_rank)
     m, x = build_workload(args.workload)
     scales = None
     if args.workload == "C4":
@@ -226,34 +247,54 @@ def main():
     # ---- device-timed steps, inputs resident in HBM, L2 flushed between steps ----
     for _ in range(args.warmup):
         sess.replay()
-    clocks = ClockSampler(local_rank)
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     barrier()
+    w0 = time.time()
     for i in range(args.steps):
         flush.zero_()
         starts[i].record()
         sess.replay()
         ends[i].record()
     barrier()
+    clocks.window(w0, time.time())
     dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
 
-    # ---- end to end: pinned host input -> device, kernels, device -> host output, every step ----
+    # ---- end to end through the emitted C++ Session (ONNX -> Parse -> Generate -> g++ -> Session::infer):
+    #      pinned host input -> device, captured graph, device -> host output, every step. The FP8
+    #      chain has no ONNX form yet and goes through the Python mirror of the Session instead.
     y_host = torch.empty(tuple(sess.static_out.shape), dtype=sess.static_out.dtype).pin_memory()
+    e2e_path = "emitted C++ Session::infer"
+    gen = None
+    if args.workload != "C4":
+        from sofie_b200 import generated
+        gen = generated.session_from_model(m, f"bench_{args.workload.lower()}_{m.batch()}")
+
+        def e2e_step():
+            gen.infer_ptr(x_pinned.data_ptr(), y_host.data_ptr())
+    else:
+        e2e_path = "Python mirror of the Session (no ONNX form of the FP8 chain)"
+
+        def e2e_step():
+            sess.static_in.copy_(x_pinned, non_blocking=True)
+            sess.replay()
+            y_host.copy_(sess.static_out, non_blocking=True)
+            torch.cuda.synchronize()
     for _ in range(args.warmup):
-        sess.static_in.copy_(x_pinned, non_blocking=True)
-        sess.replay()
-        y_host.copy_(sess.static_out, non_blocking=True)
+        e2e_step()
     barrier()
+    w0 = time.time()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        sess.static_in.copy_(x_pinned, non_blocking=True)
-        sess.replay()
-        y_host.copy_(sess.static_out, non_blocking=True)
-        torch.cuda.synchronize()
+        e2e_step()
     e2e_s = time.perf_counter() - t0
+    clocks.window(w0, time.time())
     barrier()
-    clk = clocks.stop()
+    if gen is not None and args.workload in ("C1", "C2"):
+        # the two paths must agree (same kernels, same weights)
+        ref = sess.static_out.float().cpu().numpy().ravel()
+        got = y_host.float().numpy().ravel()
+        assert np.abs(ref - got).max() <= 1e-5 * max(np.abs(ref).max(), 1e-30), "emitted Session and Python mirror disagree"
 
     # ---- dominant kernel, timed alone with events on the launching stream ----
     dom = max((s for s in sess.steps if s.flops), key=lambda s: s.flops)
@@ -271,6 +312,7 @@ def main():
         b.synchronize()
         k_ms += a.elapsed_time(b)
     k_ms /= reps
+    clk = clocks.stop()
 
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -288,14 +330,14 @@ def main():
         config=dict(workload=f"{args.workload}: {WORKLOAD_DESC[args.workload]}", batch_per_gpu=batch,
                     parallelism=f"batch-sharded x{world}, weights replicated, no collective",
                     l2="flushed between timed steps (256 MiB memset outside the event pairs)",
-                    launch="CUDA graph replay of the infer() kernel sequence"),
+                    launch="CUDA graph replay of the infer() kernel sequence", e2e_path=e2e_path),
         tflops=m.flops_per_sample * batch * world * args.steps / (dev_ms * 1e-3) / 1e12,
         e2e=dict(value=world * batch * args.steps / (e2e_ms * 1e-3), unit="samples/s",
                  h2d_bytes_per_step=int(x_pinned.numel() * x_pinned.element_size()),
                  d2h_bytes_per_step=int(y_host.numel() * y_host.element_size())),
         gpu_launches=sess.kernel_launches() * args.steps,
         roofline=dict(bound="tensor", kernel=dom.name, achieved=achieved, peak=tpeak, unit="TFLOP/s", frac=achieved / tpeak,
-                      traffic=None, kernel_ms=k_ms, flops_per_launch=kflops,
+                      traffic=NCU_TRAFFIC.get((args.workload, dom.name)), kernel_ms=k_ms, flops_per_launch=kflops,
                       peak_basis=f"{pk['source']} bf16 {pk['bf16_tflops']} TFLOP/s scaled to the dtype"),
         clocks=clk,
     )
