@@ -110,14 +110,19 @@ class ClockSampler:
 
 
 # DRAM traffic per launch of the dominant kernels, from ncu captures (profiles/): bytes read + written.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    # profiles/umma_conv3x3_f32_C2.md: conv2 of C2 at the full batch of 256: 16.84 MB read, 0 written
+    # (the pooled output stays in L2)
+    ("C2", "conv:p1"): 16.84e6,
+}
 
 
-def build_workload(workload, batch_scale=1):
+def build_workload(workload, batch=None):
+    """The configuration at its full size, or (profiling aid, --batch) at a reduced batch / row count."""
     from sofie_b200 import configs
     if workload == "C4":
-        return configs.gemm_chain_fp8()
-    return configs.BUILDERS[workload]()
+        return configs.gemm_chain_fp8(rows=batch) if batch else configs.gemm_chain_fp8()
+    return configs.BUILDERS[workload](batch=batch) if batch else configs.BUILDERS[workload]()
 
 
 # ------------------------------------------------------------------------------------ reference arm
@@ -205,6 +210,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOAD_DESC))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=None, help="reduced batch / rows for ncu captures (not a benchmark configuration)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -232,7 +238,7 @@ def main():
 
     os.environ["SOFIE_CUDA_DEVICE"] = str(local_rank)  # the emitted Session reads its device from here
     clocks = ClockSampler(local_rank)
-    m, x = build_workload(args.workload)
+    m, x = build_workload(args.workload, args.batch)
     scales = None
     if args.workload == "C4":
         # static FP8 activation scales from an fp32 run of the chain on a 512-row slice (setup)
@@ -327,7 +333,8 @@ def main():
         metric="samples/s", value=world * batch * args.steps / (dev_ms * 1e-3), unit="samples/s", n_gpus=world,
         steps=args.steps, warmup=args.warmup, ms_per_step=dev_ms / args.steps, higher_is_better=True, scaling="weak",
         vs_baseline=None, dtype=DTYPE[args.workload], data="synthetic",
-        config=dict(workload=f"{args.workload}: {WORKLOAD_DESC[args.workload]}", batch_per_gpu=batch,
+        config=dict(workload=f"{args.workload}: {WORKLOAD_DESC[args.workload]}" + (f" [reduced to batch {args.batch}]" if args.batch else ""),
+                    batch_per_gpu=batch,
                     parallelism=f"batch-sharded x{world}, weights replicated, no collective",
                     l2="flushed between timed steps (256 MiB memset outside the event pairs)",
                     launch="CUDA graph replay of the infer() kernel sequence", e2e_path=e2e_path),

@@ -120,31 +120,34 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 
    if (warp == 0) {
       // ---------------- TMA producer ----------------
-      if (lane == 0) {
-         int g = 0; // stage counter, continuous over the tiles of this CTA
-         for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x) {
-            int n0, h0, w0;
-            tile_origin(tile, n0, h0, w0);
-            bool ok = true;
-            for (int st = 0; st < stages_per_tile; st++, g++) {
-               const int s = g % S;
-               const uint32_t ph = (g / S) & 1;
-               if (!SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g))) {
-                  ok = false;
-                  break;
-               }
-               mbar_expect_tx(&full_bar[s], TPS * (A_TILE + B_TILE));
-#pragma unroll
-               for (int k = 0; k < TPS; k++) {
-                  const int item = st * TPS + k, tap = item / tg.chunks, ch = item % tg.chunks;
-                  const int r = tap / 3, sx = tap % 3;
-                  // x coordinate (channels) is a multiple of CBE, i.e. of 16 bytes; the spatial
-                  // coordinates may be -1 or reach H / W: those elements read as zero
-                  tma_load_4d(a_hi(s, k), &tmX, ch * CBE, w0 + sx - 1, h0 + r - 1, n0, &full_bar[s]);
-                  tma_load_2d(b_hi(s, k), &tmW, tap * tg.C + ch * CBE, 0, &full_bar[s]);
-               }
+      // Issuing a tensor copy costs the issuing thread a few hundred cycles, so the 2 x TPS copies of
+      // a stage are issued by 2 x TPS lanes in parallel; lane 0 waits for the free slot and posts the
+      // expected byte count (the phase cannot complete before that arrive, whatever the order).
+      int g = 0; // stage counter, continuous over the tiles of this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
+         int n0, h0, w0;
+         tile_origin(tile, n0, h0, w0);
+         for (int st = 0; st < stages_per_tile; st++, g++) {
+            const int s = g % S;
+            const uint32_t ph = (g / S) & 1;
+            if (lane == 0) {
+               ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
+               if (ok) mbar_expect_tx(&full_bar[s], TPS * (A_TILE + B_TILE));
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
+            if (lane < 2 * TPS) {
+               const int k = lane >> 1;
+               const int item = st * TPS + k;
+               const int tap = tg.chunks == 1 ? item : item / tg.chunks, ch = tg.chunks == 1 ? 0 : item % tg.chunks;
+               const int r = tap / 3, sx = tap - 3 * r;
+               // x coordinate (channels) is a multiple of CBE, i.e. of 16 bytes; the spatial
+               // coordinates may be -1 or reach H / W: those elements read as zero
+               if (lane & 1) tma_load_2d(b_hi(s, k), &tmW, tap * tg.C + ch * CBE, 0, &full_bar[s]);
+               else tma_load_4d(a_hi(s, k), &tmX, ch * CBE, w0 + sx - 1, h0 + r - 1, n0, &full_bar[s]);
+            }
+            __syncwarp();
          }
       }
    } else if (warp == 1) {

@@ -253,22 +253,24 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
    if (warp == 0) {
       // ---------------- TMA producer ----------------
-      if (lane == 0) {
-         int g = 0;
-         bool ok = true;
-         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
-            for (int kb = 0; kb < num_kb; kb++, g++) {
-               const int s = g % S;
-               const uint32_t ph = (g / S) & 1;
-               if (!SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g))) {
-                  ok = false;
-                  break;
-               }
-               mbar_expect_tx(&full_bar[s], L::kATile + L::kBTile);
-               tma_load_2d(a_hi(s), &tmA, kb * KE, m0, &full_bar[s]);
-               tma_load_2d(b_hi(s), &tmB, kb * KE, n0, &full_bar[s]);
+      // lane 0 waits for the free slot and posts the byte count; lanes 0 and 1 issue the A and the B
+      // copy in parallel (issuing a tensor copy costs the issuing thread a few hundred cycles)
+      int g = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+         const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
+         for (int kb = 0; kb < num_kb; kb++, g++) {
+            const int s = g % S;
+            const uint32_t ph = (g / S) & 1;
+            if (lane == 0) {
+               ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
+               if (ok) mbar_expect_tx(&full_bar[s], L::kATile + L::kBTile);
             }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            if (lane == 0) tma_load_2d(a_hi(s), &tmA, kb * KE, m0, &full_bar[s]);
+            else if (lane == 1) tma_load_2d(b_hi(s), &tmB, kb * KE, n0, &full_bar[s]);
+            __syncwarp();
          }
       }
    } else if (warp == 1) {
