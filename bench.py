@@ -210,6 +210,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOAD_DESC))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer-times", action="store_true", help="also time every step of the plan alone (adds layer_ms to the line)")
     ap.add_argument("--batch", type=int, default=None, help="reduced batch / rows for ncu captures (not a benchmark configuration)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -318,6 +319,21 @@ def main():
         b.synchronize()
         k_ms += a.elapsed_time(b)
     k_ms /= reps
+    layer_ms = None
+    if args.layer_times:
+        # every step of the plan timed alone (cold L2), to see where a step's time goes
+        layer_ms = {}
+        for st in sess.steps:
+            tot = 0.0
+            for _ in range(5):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                st.fn(t)
+                b.record()
+                b.synchronize()
+                tot += a.elapsed_time(b)
+            layer_ms[st.name] = round(tot / 5, 5)
     clk = clocks.stop()
 
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
@@ -348,6 +364,8 @@ def main():
                       peak_basis=f"{pk['source']} bf16 {pk['bf16_tflops']} TFLOP/s scaled to the dtype"),
         clocks=clk,
     )
+    if layer_ms is not None:
+        line["layer_ms"] = layer_ms
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.workload)

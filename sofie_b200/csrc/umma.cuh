@@ -195,6 +195,19 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, int row_b
    return desc;
 }
 
+// K-major operand without swizzle: the tile is made of 8-row x 16-byte core matrices, each 128
+// contiguous bytes (8 rows at a 16-byte pitch). sbo_bytes is the distance between consecutive 8-row
+// groups, lbo_bytes the distance between the two 16-byte K columns one MMA (32 bytes of K) reads.
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+   uint64_t desc = 0;
+   desc |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+   desc |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+   desc |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+   desc |= (uint64_t)1 << 46;
+   return desc;
+}
+
 // Instruction descriptor (dense, K-major A and B, M x N tile):
 //   bits 4-5 accumulator format (1 = f32, 2 = s32)   bits 7-9 A format   bits 10-12 B format
 //   bits 17-22 N >> 3                                 bits 24-28 M >> 4

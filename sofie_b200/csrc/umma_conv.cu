@@ -14,6 +14,8 @@
 // rows of the patch, so every 2x2 window lives in one warp and is reduced with two shuffles.
 #include "umma.cuh"
 #include "contract.cuh"
+#include <cstdlib>
+#include <type_traits>
 
 namespace sofie {
 namespace umma {
@@ -42,6 +44,103 @@ constexpr int kConvEpilogueWarps = 8;                          // warps 2..9
 constexpr int kConvConverterWarps = 8;                         // fp32 only: warps 10..17
 constexpr int kConvThreadsI8 = (2 + kConvEpilogueWarps) * 32;
 constexpr int kConvThreadsTF32 = (2 + kConvEpilogueWarps + kConvConverterWarps) * 32;
+
+// The part of the epilogue one warp does for one finished tile: read its 32 TMEM lanes (pixels) for
+// its share of the output channels, add the NACC partial accumulators, apply bias / Relu or the
+// requantisation, reduce 2x2 windows by shuffles when pooling is fused, and store NHWC.
+// e = index of the epilogue warp (0..7), lane_base = first TMEM lane of its quarter.
+template <int KIND, int BN, int NACC>
+__device__ __forceinline__ void conv_tile_epilogue(const ConvEpilogue &ep, const ConvTiling &tg, const float *s_bias,
+                                                   const float *s_mult, const int *s_qbias, uint32_t tmem_base, int buf, int e,
+                                                   int lane_base, int lane, int n0, int h0, int w0)
+{
+   constexpr int CW = BN >= 64 ? BN / 2 : BN;            // channels per warp
+   const int c_begin = BN >= 64 ? (e >> 2) * CW : 0;
+   const bool has_columns = BN >= 64 || (e >> 2) == 0;
+   const int pix = lane_base + lane; // pixel of the patch = TMEM lane
+   const int ww = pix % tg.tileW, hh = (pix / tg.tileW) % tg.tileH, nn = pix / (tg.tileW * tg.tileH);
+   const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
+   const int n = n0 + nn, h = h0 + hh, w = w0 + ww;
+   const bool valid = n < tg.N;
+   // with pooling only the top-left pixel of each 2x2 window stores
+   const bool store = valid && (!ep.pool || (((hh | ww) & 1) == 0));
+   const int oH = ep.pool ? tg.H / 2 : tg.H, oW = ep.pool ? tg.W / 2 : tg.W;
+   const int oh = ep.pool ? h / 2 : h, ow = ep.pool ? w / 2 : w;
+   const size_t opix = ((size_t)n * oH + oh) * oW + ow;
+   if (has_columns) {
+#pragma unroll 1
+      for (int c0 = c_begin; c0 < c_begin + CW; c0 += 32) {
+         if (c0 >= tg.Cout) break;
+         // sum of the NACC partial accumulators of this tile
+         uint32_t r[32];
+         tmem_ld_32x32(t_row + (uint32_t)(buf * NACC * BN + c0), r);
+         tmem_ld_wait();
+#pragma unroll
+         for (int a = 1; a < NACC; a++) {
+            uint32_t p[32];
+            tmem_ld_32x32(t_row + (uint32_t)((buf * NACC + a) * BN + c0), p);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+               if constexpr (KIND == kTF32) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(p[j]));
+               else r[j] = (uint32_t)((int)r[j] + (int)p[j]);
+            }
+         }
+         const int ncols = min(32, tg.Cout - c0);
+         if constexpr (KIND == kTF32) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+               float acc = __uint_as_float(r[j]) + s_bias[c0 + j];
+               v[j] = ep.relu ? relu_ref(acc) : acc;
+            }
+            if (ep.pool) {
+#pragma unroll
+               for (int j = 0; j < 32; j++) {
+                  float o = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                  v[j] = o > v[j] ? o : v[j];
+                  o = __shfl_xor_sync(0xffffffffu, v[j], tg.tileW);
+                  v[j] = o > v[j] ? o : v[j];
+               }
+            }
+            if (store) {
+               float *y = ep.Yf + opix * tg.Cout + c0;
+               if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+               } else {
+#pragma unroll
+                  for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
+               }
+            }
+         } else {
+            int q[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) q[j] = requant_u8((int)r[j] + s_qbias[c0 + j], s_mult[c0 + j], ep.y_zp, ep.relu);
+            if (ep.pool) {
+#pragma unroll
+               for (int j = 0; j < 32; j++) {
+                  q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], 1));
+                  q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], tg.tileW));
+               }
+            }
+            if (store) {
+               uint8_t *y = ep.Yu8 + opix * tg.Cout + c0;
+               uint32_t packed[8];
+#pragma unroll
+               for (int j = 0; j < 32; j += 4) packed[j >> 2] = (uint32_t)q[j] | ((uint32_t)q[j + 1] << 8) | ((uint32_t)q[j + 2] << 16) | ((uint32_t)q[j + 3] << 24);
+               if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+                  *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                  *reinterpret_cast<uint4 *>(y + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+               } else {
+#pragma unroll
+                  for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)q[j];
+               }
+            }
+         }
+      }
+   }
+}
 
 template <int KIND, int BN, int CB, int TPS>
 __global__ void __launch_bounds__(KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8, 1)
@@ -248,12 +347,6 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       // quarter split the output channels.
       const int e = warp - 2;
       const int lane_base = (warp & 3) * 32;
-      constexpr int CW = BN >= 64 ? BN / 2 : BN;            // channels per warp
-      const int c_begin = BN >= 64 ? (e >> 2) * CW : 0;
-      const bool has_columns = BN >= 64 || (e >> 2) == 0;
-      const int pix = lane_base + lane; // pixel of the patch = TMEM lane
-      const int ww = pix % tg.tileW, hh = (pix / tg.tileW) % tg.tileH, nn = pix / (tg.tileW * tg.tileH);
-      const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
       int lt = 0;
       for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, lt++) {
          const int buf = lt & 1;
@@ -261,86 +354,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          tile_origin(tile, n0, h0, w0);
          if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
          tc_fence_after();
-         const int n = n0 + nn, h = h0 + hh, w = w0 + ww;
-         const bool valid = n < tg.N;
-         // with pooling only the top-left pixel of each 2x2 window stores
-         const bool store = valid && (!ep.pool || (((hh | ww) & 1) == 0));
-         const int oH = ep.pool ? tg.H / 2 : tg.H, oW = ep.pool ? tg.W / 2 : tg.W;
-         const int oh = ep.pool ? h / 2 : h, ow = ep.pool ? w / 2 : w;
-         const size_t opix = ((size_t)n * oH + oh) * oW + ow;
-         if (has_columns) {
-#pragma unroll 1
-            for (int c0 = c_begin; c0 < c_begin + CW; c0 += 32) {
-               if (c0 >= tg.Cout) break;
-               // sum of the NACC partial accumulators of this tile
-               uint32_t r[32];
-               tmem_ld_32x32(t_row + (uint32_t)(buf * NACC * BN + c0), r);
-               tmem_ld_wait();
-#pragma unroll
-               for (int a = 1; a < NACC; a++) {
-                  uint32_t p[32];
-                  tmem_ld_32x32(t_row + (uint32_t)((buf * NACC + a) * BN + c0), p);
-                  tmem_ld_wait();
-#pragma unroll
-                  for (int j = 0; j < 32; j++) {
-                     if constexpr (KIND == kTF32) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(p[j]));
-                     else r[j] = (uint32_t)((int)r[j] + (int)p[j]);
-                  }
-               }
-               const int ncols = min(32, tg.Cout - c0);
-               if constexpr (KIND == kTF32) {
-                  float v[32];
-#pragma unroll
-                  for (int j = 0; j < 32; j++) {
-                     float acc = __uint_as_float(r[j]) + s_bias[c0 + j];
-                     v[j] = ep.relu ? relu_ref(acc) : acc;
-                  }
-                  if (ep.pool) {
-#pragma unroll
-                     for (int j = 0; j < 32; j++) {
-                        float o = __shfl_xor_sync(0xffffffffu, v[j], 1);
-                        v[j] = o > v[j] ? o : v[j];
-                        o = __shfl_xor_sync(0xffffffffu, v[j], tg.tileW);
-                        v[j] = o > v[j] ? o : v[j];
-                     }
-                  }
-                  if (store) {
-                     float *y = ep.Yf + opix * tg.Cout + c0;
-                     if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                     } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
-                     }
-                  }
-               } else {
-                  int q[32];
-#pragma unroll
-                  for (int j = 0; j < 32; j++) q[j] = requant_u8((int)r[j] + s_qbias[c0 + j], s_mult[c0 + j], ep.y_zp, ep.relu);
-                  if (ep.pool) {
-#pragma unroll
-                     for (int j = 0; j < 32; j++) {
-                        q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], 1));
-                        q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], tg.tileW));
-                     }
-                  }
-                  if (store) {
-                     uint8_t *y = ep.Yu8 + opix * tg.Cout + c0;
-                     uint32_t packed[8];
-#pragma unroll
-                     for (int j = 0; j < 32; j += 4) packed[j >> 2] = (uint32_t)q[j] | ((uint32_t)q[j + 1] << 8) | ((uint32_t)q[j + 2] << 16) | ((uint32_t)q[j + 3] << 24);
-                     if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
-                        *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        *reinterpret_cast<uint4 *>(y + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                     } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)q[j];
-                     }
-                  }
-               }
-            }
-         }
+         conv_tile_epilogue<KIND, BN, NACC>(ep, tg, s_bias, s_mult, s_qbias, tmem_base, buf, e, lane_base, lane, n0, h0, w0);
          // this warp is done with the TMEM buffer: the MMA warp may overwrite it
          tc_fence_before();
          __syncwarp();
@@ -355,6 +369,329 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       __syncwarp();
       tc_fence_after();
       tmem_dealloc(tmem_base, TMEM_COLS);
+   }
+}
+
+// ================================================================================================
+// Second kernel for the same convolution: one haloed input patch per tile, resident weights.
+//
+// The kernel above fetches the input tile once per tap (nine overlapping boxes per channel chunk)
+// and the weight tile again for every output tile; the TMA issue cost and, for fp32, the hi/lo split
+// of all those bytes bound it. Here a tile is 16 rows x 8 columns of one image and its input is
+// fetched ONCE, as the 18 x 10 patch including the halo (zero fill outside the image), in a layout
+// that lets every tap address it in place:
+//    patch[plane p][patch row][patch column][16 bytes]     plane = 16 bytes of channels
+// For tap (r,s) the 128 x K operand starts at patch row r, column s: pixel (h, w) of the tile is at
+//    (r + h) * 10 + (s + w)  pixels of 16 bytes,
+// so the 8 pixels of one tile row are 128 contiguous bytes (one core matrix of the no-swizzle
+// K-major layout), consecutive tile rows are 160 bytes apart (the stride between 8-row groups) and
+// consecutive 16-byte K columns are one plane apart (the leading-dimension byte offset). A tap is
+// therefore only a different start address of the same shared-memory bytes.
+// All 9 x C x Cout weights (and their lo parts for fp32) are loaded and split once per CTA and stay
+// in shared memory; the launcher falls back to the kernel above when they do not fit.
+constexpr int kPatchTileH = 16, kPatchTileW = 8;
+constexpr int kPatchH = kPatchTileH + 2, kPatchW = kPatchTileW + 2;
+constexpr int kPlaneBox = kPatchH * kPatchW * 16;                 // bytes one plane copy delivers
+constexpr int kPlaneStride = (kPlaneBox + 127) / 128 * 128;       // TMA destinations are 128-byte aligned
+constexpr int kPatchMaxStages = 4;
+
+struct PatchPlan {
+   int planes;   // 16-byte channel groups per pixel
+   int ksteps;   // MMAs (32 bytes of K) per tap
+   int chunks;   // weight sub-tiles per tap (rows of cb bytes)
+   int cb;       // bytes per weight row chunk: 32, 64 or 128 (selects the swizzle)
+   int stages;   // patches in flight
+   uint32_t patch_bytes, w_bytes;
+};
+
+template <int KIND, int BN, int KSTEPS>
+__global__ void __launch_bounds__(KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8, 1)
+umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, ConvEpilogue ep,
+                          ConvTiling tg, PatchPlan pl, uint32_t *status)
+{
+   constexpr int ES = (KIND == kTF32) ? 4 : 1;
+   constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
+   constexpr uint32_t TMEM_COLS = 2 * BN; // two accumulators of BN columns: 64, 128 or 256
+   constexpr int EPI_WARPS = kConvEpilogueWarps;
+   extern __shared__ unsigned char smem_raw[];
+   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+   __shared__ uint64_t full_bar[kPatchMaxStages], conv_bar[kPatchMaxStages], empty_bar[kPatchMaxStages], tmem_full[2], tmem_empty[2];
+   __shared__ uint64_t w_full, w_conv;
+   __shared__ uint32_t tmem_base_holder;
+   __shared__ volatile uint32_t abort_flag;
+   __shared__ float s_bias[128], s_mult[128];
+   __shared__ int s_qbias[128];
+
+   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+   SOFIE_PROF_DECL
+   for (int c = threadIdx.x; c < 128; c += blockDim.x) {
+      const bool in = c < tg.Cout;
+      s_bias[c] = (KIND == kTF32 && in && ep.bias) ? ep.bias[c] : 0.f;
+      s_mult[c] = (KIND == kI8 && in) ? ep.mult[c] : 0.f;
+      s_qbias[c] = (KIND == kI8 && in && ep.qbias) ? ep.qbias[c] : 0;
+   }
+   const int S = pl.stages;
+   const uint32_t b_tile = (uint32_t)BN * pl.cb;          // one (tap, chunk) weight sub-tile
+   unsigned char *w_hi = smem;
+   unsigned char *w_lo = smem + pl.w_bytes;                // fp32 only
+   unsigned char *patches = smem + (size_t)COPIES * pl.w_bytes;
+   auto patch_hi = [&](int s) { return patches + (size_t)s * COPIES * pl.patch_bytes; };
+
+   if (threadIdx.x == 0) {
+      for (int s = 0; s < kPatchMaxStages; s++) {
+         mbar_init(&full_bar[s], 1);
+         mbar_init(&conv_bar[s], kConvConverterWarps * 32);
+         mbar_init(&empty_bar[s], 1);
+      }
+      for (int b = 0; b < 2; b++) {
+         mbar_init(&tmem_full[b], 1);
+         mbar_init(&tmem_empty[b], EPI_WARPS);
+      }
+      mbar_init(&w_full, 1);
+      mbar_init(&w_conv, kConvConverterWarps * 32);
+      abort_flag = 0;
+      fence_mbar_init();
+      prefetch_tensormap(&tmX);
+      prefetch_tensormap(&tmW);
+   }
+   if (warp == 1) {
+      tmem_alloc(&tmem_base_holder, TMEM_COLS);
+      tmem_relinquish();
+   }
+   tc_fence_before();
+   __syncthreads();
+   tc_fence_after();
+   const uint32_t tmem_base = tmem_base_holder;
+
+   auto tile_origin = [&](int tile, int &n0, int &h0, int &w0) {
+      const int per_image = tg.tilesH * tg.tilesW;
+      const int rem = tile % per_image;
+      n0 = tile / per_image;
+      h0 = (rem / tg.tilesW) * kPatchTileH;
+      w0 = (rem % tg.tilesW) * kPatchTileW;
+   };
+
+   if (warp == 0) {
+      // ---------------- TMA producer ----------------
+      // weights: 9 x chunks boxes of BN rows, all on one barrier
+      const int cbe = pl.cb / ES;
+      if (lane == 0) mbar_expect_tx(&w_full, pl.w_bytes);
+      __syncwarp();
+      for (int item = lane; item < 9 * pl.chunks; item += 32) {
+         const int tap = item / pl.chunks, ch = item - tap * pl.chunks;
+         tma_load_2d(w_hi + (size_t)item * b_tile, &tmW, tap * tg.C + ch * cbe, 0, &w_full);
+      }
+      // patches: one box per plane, issued by as many lanes
+      int g = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, g++) {
+         int n0, h0, w0;
+         tile_origin(tile, n0, h0, w0);
+         const int s = g % S;
+         const uint32_t ph = (g / S) & 1;
+         if (lane == 0) {
+            ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
+            if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)pl.planes * kPlaneBox);
+         }
+         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+         if (!ok) break;
+         // channel coordinate = a multiple of 16 bytes; rows and columns start at -1 (zero fill)
+         if (lane < pl.planes)
+            tma_load_4d(patch_hi(s) + (size_t)lane * kPlaneStride, &tmX, lane * (16 / ES), w0 - 1, h0 - 1, n0, &full_bar[s]);
+         __syncwarp();
+      }
+   } else if (warp == 1) {
+      // ---------------- MMA issuer ----------------
+      if (lane == 0) {
+         constexpr uint32_t idesc = make_idesc<KIND>(128, BN);
+         bool ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&w_conv, 0, &abort_flag, status, kStatusWaitConv, 0x4000)
+                                                   : mbar_wait(&w_full, 0, &abort_flag, status, kStatusWaitFull, 0x4000));
+         tc_fence_after();
+         const uint64_t db0 = make_smem_desc(smem_u32(w_hi), pl.cb);
+         const uint32_t b_hi_word = (uint32_t)(db0 >> 32), b_lo_word = (uint32_t)db0;
+         const uint32_t patch16 = pl.patch_bytes >> 4, wlo16 = pl.w_bytes >> 4; // hi -> lo copy, in 16-byte units
+         int g = 0;
+         for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, g++) {
+            const int buf = g & 1;
+            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((g >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + g))) break;
+            const int s = g % S;
+            const uint32_t ph = (g / S) & 1;
+            ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
+                                                 : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t d = tmem_base + (uint32_t)(buf * BN);
+            // The issuing thread is the pacemaker of the whole CTA, so everything that can be
+            // is folded at compile time: each MMA costs it one 32-bit add per descriptor. The
+            // address field (bits 0..13, in units of 16 bytes) never carries out of its field.
+            const uint64_t da0 = make_smem_desc_noswizzle(smem_u32(patch_hi(s)), kPlaneStride, kPatchW * 16);
+            const uint32_t a_hi_word = (uint32_t)(da0 >> 32), a_lo_word = (uint32_t)da0;
+            auto adesc = [&](uint32_t off16) { return ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + off16); };
+            auto bdesc = [&](uint32_t off16) { return ((uint64_t)b_hi_word << 32) | (uint64_t)(b_lo_word + off16); };
+#pragma unroll
+            for (int tap = 0; tap < 9; tap++) {
+#pragma unroll
+               for (int kk = 0; kk < KSTEPS; kk++) {
+                  constexpr int CBK = KSTEPS * 32 >= 128 ? 128 : KSTEPS * 32; // bytes per weight row chunk
+                  constexpr int CHUNKS = KSTEPS * 32 / CBK;
+                  const uint32_t a16 = (uint32_t)(((tap / 3) * kPatchW + (tap % 3)) * 16 + kk * 2 * kPlaneStride) >> 4;
+                  const uint32_t b16 = (uint32_t)((tap * CHUNKS + (kk * 32) / CBK) * (BN * CBK) + (kk * 32) % CBK) >> 4;
+                  const uint32_t acc = (tap | kk) ? 1u : 0u;
+                  if constexpr (KIND == kTF32) {
+                     tc_mma<KIND>(d, adesc(a16 + patch16), bdesc(b16), idesc, acc);        // lo x hi
+                     tc_mma<KIND>(d, adesc(a16), bdesc(b16 + wlo16), idesc, 1u);           // hi x lo
+                     tc_mma<KIND>(d, adesc(a16), bdesc(b16), idesc, 1u);                   // hi x hi
+                  } else {
+                     tc_mma<KIND>(d, adesc(a16), bdesc(b16), idesc, acc);
+                  }
+               }
+            }
+            tc_commit(&empty_bar[s]);
+            tc_commit(&tmem_full[buf]);
+         }
+      }
+   } else if (warp >= 2 + EPI_WARPS) {
+      // ---------------- converter warps (kTF32): hi/lo split, weights once, then each patch ----------------
+      if constexpr (KIND == kTF32) {
+         constexpr int NT = kConvConverterWarps * 32;
+         const int t = threadIdx.x - (2 + EPI_WARPS) * 32;
+         // Splits n16 16-byte groups at src in place (hi) and writes the lo parts lo_off bytes further.
+         // Four independent loads per thread are issued before the first conversion.
+         auto split = [&](unsigned char *src, uint32_t n16, uint32_t lo_off) {
+            float4 *base = reinterpret_cast<float4 *>(src);
+            const uint32_t lo4 = lo_off / 16;
+            for (uint32_t i0 = t; i0 < n16; i0 += 4 * NT) {
+               float4 v[4];
+#pragma unroll
+               for (int i = 0; i < 4; i++)
+                  if (i0 + i * NT < n16) v[i] = base[i0 + i * NT];
+#pragma unroll
+               for (int i = 0; i < 4; i++) {
+                  if (i0 + i * NT < n16) {
+                     float4 h, l;
+                     uint32_t u;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[i].x)); h.x = __uint_as_float(u); l.x = v[i].x - h.x;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[i].y)); h.y = __uint_as_float(u); l.y = v[i].y - h.y;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[i].z)); h.z = __uint_as_float(u); l.z = v[i].z - h.z;
+                     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[i].w)); h.w = __uint_as_float(u); l.w = v[i].w - h.w;
+                     base[i0 + i * NT] = h;
+                     base[i0 + i * NT + lo4] = l;
+                  }
+               }
+            }
+         };
+         bool ok = SOFIE_PROF_WAIT(mbar_wait(&w_full, 0, &abort_flag, status, kStatusWaitFull, 0x4000));
+         if (ok) {
+            split(w_hi, pl.w_bytes / 16, pl.w_bytes);
+            fence_proxy_async();
+            mbar_arrive(&w_conv);
+         }
+         int g = 0;
+         for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, g++) {
+            const int s = g % S;
+            const uint32_t ph = (g / S) & 1;
+            if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) break;
+            split(patch_hi(s), pl.patch_bytes / 16, pl.patch_bytes);
+            fence_proxy_async();
+            mbar_arrive(&conv_bar[s]);
+         }
+      }
+   } else {
+      // ---------------- epilogue warps 2..9 ----------------
+      const int e = warp - 2;
+      const int lane_base = (warp & 3) * 32;
+      int g = 0;
+      for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, g++) {
+         const int buf = g & 1;
+         int n0, h0, w0;
+         tile_origin(tile, n0, h0, w0);
+         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (g >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + g))) break;
+         tc_fence_after();
+         conv_tile_epilogue<KIND, BN, 1>(ep, tg, s_bias, s_mult, s_qbias, tmem_base, buf, e, lane_base, lane, n0, h0, w0);
+         tc_fence_before();
+         __syncwarp();
+         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      }
+   }
+   SOFIE_PROF_REPORT(warp == 0 ? "producer" : (warp == 1 ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
+   tc_fence_before();
+   __syncthreads();
+   if (warp == 1) {
+      __syncwarp();
+      tc_fence_after();
+      tmem_dealloc(tmem_base, TMEM_COLS);
+   }
+}
+
+// Launches the patch kernel when the shape belongs to it and the weights fit; returns -1 when the
+// caller should use the per-tap kernel instead.
+template <int KIND>
+static int try_launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, const void *Wp, const ConvEpilogue &ep, int BN)
+{
+   constexpr int ES = (KIND == kTF32) ? 4 : 1;
+   constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
+   if (g.H % kPatchTileH != 0 || g.W % kPatchTileW != 0) return -1;
+   const int row_bytes = g.C * ES;
+   if (row_bytes != 32 && row_bytes != 64 && row_bytes != 128 && row_bytes != 256) return -1;
+   PatchPlan pl = {};
+   pl.planes = row_bytes / 16;
+   pl.ksteps = row_bytes / 32;
+   pl.cb = row_bytes >= 128 ? 128 : row_bytes;
+   if (pl.cb != 32 && pl.cb != 64 && pl.cb != 128) return -1;
+   if (row_bytes % pl.cb != 0) return -1;
+   pl.chunks = row_bytes / pl.cb;
+   pl.w_bytes = (uint32_t)(9 * pl.chunks * BN * pl.cb);
+   pl.patch_bytes = (uint32_t)(pl.planes * kPlaneStride);
+   const long budget = 200 * 1024 - (long)COPIES * pl.w_bytes;
+   const long per_stage = (long)COPIES * pl.patch_bytes;
+   if (budget < 2 * per_stage) return -1;
+   pl.stages = (int)(budget / per_stage);
+   if (pl.stages > kPatchMaxStages) pl.stages = kPatchMaxStages;
+   ConvTiling tg = {};
+   tg.N = g.N; tg.H = g.H; tg.W = g.W; tg.C = g.C; tg.Cout = g.Cout;
+   tg.tileW = kPatchTileW; tg.tileH = kPatchTileH; tg.tileN = 1;
+   tg.tilesW = g.W / kPatchTileW;
+   tg.tilesH = g.H / kPatchTileH;
+   tg.num_tiles = g.N * tg.tilesH * tg.tilesW;
+   tg.chunks = pl.chunks;
+   tg.stages = pl.stages;
+   const CUtensorMapDataType dt = (KIND == kTF32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+   CUtensorMap tmX, tmW;
+   uint64_t xdims[4] = {(uint64_t)g.C, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N};
+   uint64_t xstr[3] = {(uint64_t)g.C * ES, (uint64_t)g.W * g.C * ES, (uint64_t)g.H * g.W * g.C * ES};
+   uint32_t xbox[4] = {(uint32_t)(16 / ES), (uint32_t)kPatchW, (uint32_t)kPatchH, 1u};
+   int rc = make_tensor_map(&tmX, dt, 4, X, xdims, xstr, xbox, 0);
+   if (rc) return rc;
+   uint64_t wdims[2] = {(uint64_t)9 * g.C, (uint64_t)g.Cout};
+   uint64_t wstr[1] = {(uint64_t)9 * g.C * ES};
+   uint32_t wbox[2] = {(uint32_t)(pl.cb / ES), (uint32_t)BN};
+   rc = make_tensor_map(&tmW, dt, 2, Wp, wdims, wstr, wbox, pl.cb);
+   if (rc) return rc;
+   const int smem = (int)(COPIES * pl.w_bytes + pl.stages * per_stage) + 1024;
+   uint32_t *status = device_status_word();
+   if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
+   const int grid = tg.num_tiles < kNumSMs ? tg.num_tiles : kNumSMs;
+   const int threads = KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8;
+   auto go = [&](auto kern) -> int {
+      SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, threads, smem, s>>>(tmX, tmW, ep, tg, pl, status);
+      SOFIE_LAUNCH_CHECK("umma_conv3x3_patch_kernel");
+      set_last_engine(SOFIE_ENGINE_TCGEN05);
+      return SOFIE_CUDA_OK;
+   };
+   auto by_ksteps = [&](auto bn) -> int {
+      constexpr int kBN = decltype(bn)::value;
+      switch (pl.ksteps) {
+      case 1: return go(umma_conv3x3_patch_kernel<KIND, kBN, 1>);
+      case 2: return go(umma_conv3x3_patch_kernel<KIND, kBN, 2>);
+      case 4: return go(umma_conv3x3_patch_kernel<KIND, kBN, 4>);
+      default: return go(umma_conv3x3_patch_kernel<KIND, kBN, 8>);
+      }
+   };
+   switch (BN) {
+   case 32: return by_ksteps(std::integral_constant<int, 32>{});
+   case 64: return by_ksteps(std::integral_constant<int, 64>{});
+   default: return by_ksteps(std::integral_constant<int, 128>{});
    }
 }
 
@@ -403,6 +740,13 @@ static int launch_conv_cb(cudaStream_t s, int cb, const CUtensorMap &tmX, const 
    }
 }
 
+// SOFIE_CUDA_CONV_VARIANT=1 keeps every shape on the per-tap kernel (used to compare the two).
+static int conv_variant()
+{
+   static const int v = [] { const char *e = getenv("SOFIE_CUDA_CONV_VARIANT"); return e ? atoi(e) : 0; }();
+   return v;
+}
+
 template <int KIND>
 static int launch_conv(cudaStream_t s, const ConvGeom &g, const void *X, const void *Wp, const ConvEpilogue &ep)
 {
@@ -432,6 +776,10 @@ static int launch_conv(cudaStream_t s, const ConvGeom &g, const void *X, const v
    if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(Wp) & 15))
       return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "TMA needs 16-byte aligned tensors");
    const int BN = g.Cout <= 32 ? 32 : (g.Cout <= 64 ? 64 : 128);
+   if (conv_variant() != 1) {
+      const int prc = try_launch_conv_patch<KIND>(s, g, X, Wp, ep, BN);
+      if (prc >= 0) return prc;
+   }
    // ---- tensor maps ----
    const CUtensorMapDataType dt = (KIND == kTF32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
    CUtensorMap tmX, tmW;
