@@ -304,36 +304,35 @@ def main():
         assert np.abs(ref - got).max() <= 1e-5 * max(np.abs(ref).max(), 1e-30), "emitted Session and Python mirror disagree"
 
     # ---- dominant kernel, timed alone with events on the launching stream ----
+    # The event pair sits INSIDE a captured graph (flush, record, kernel, record), so the interval is
+    # the kernel's time on the device and holds none of the host's launch latency.
     dom = max((s for s in sess.steps if s.flops), key=lambda s: s.flops)
     t = sess._run_steps(x_dev)  # materialise the inputs of every step
-    reps = max(10, min(args.steps, 50))
-    k_ms = 0.0
-    for _ in range(3):
-        dom.fn(t)
-    for _ in range(reps):
-        flush.zero_()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        dom.fn(t)
-        b.record()
-        b.synchronize()
-        k_ms += a.elapsed_time(b)
-    k_ms /= reps
+
+    def device_time_ms(fn, reps):
+        for _ in range(3):
+            fn(t)
+        torch.cuda.synchronize()
+        a = torch.cuda.Event(enable_timing=True, external=True)
+        b = torch.cuda.Event(enable_timing=True, external=True)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            flush.zero_()
+            a.record()
+            fn(t)
+            b.record()
+        tot = 0.0
+        for _ in range(reps):
+            g.replay()
+            torch.cuda.synchronize()
+            tot += a.elapsed_time(b)
+        return tot / reps
+
+    k_ms = device_time_ms(dom.fn, max(10, min(args.steps, 50)))
     layer_ms = None
     if args.layer_times:
         # every step of the plan timed alone (cold L2), to see where a step's time goes
-        layer_ms = {}
-        for st in sess.steps:
-            tot = 0.0
-            for _ in range(5):
-                flush.zero_()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                st.fn(t)
-                b.record()
-                b.synchronize()
-                tot += a.elapsed_time(b)
-            layer_ms[st.name] = round(tot / 5, 5)
+        layer_ms = {st.name: round(device_time_ms(st.fn, 5), 5) for st in sess.steps}
     clk = clocks.stop()
 
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")

@@ -207,6 +207,8 @@ __global__ void quantize_u8_kernel(const float *__restrict__ X, uint8_t *__restr
 {
    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
    size_t n4 = vec ? n / 4 : 0;
+   // several independent 16-byte loads in flight per thread
+#pragma unroll 4
    for (size_t i = tid; i < n4; i += nthreads) {
       float4 v = reinterpret_cast<const float4 *>(X)[i];
       uchar4 q = make_uchar4(quant_u8(v.x, scale, zp), quant_u8(v.y, scale, zp), quant_u8(v.z, scale, zp),
@@ -221,6 +223,7 @@ __global__ void dequantize_u8_kernel(const uint8_t *__restrict__ X, float *__res
 {
    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
    size_t n4 = vec ? n / 4 : 0;
+#pragma unroll 4
    for (size_t i = tid; i < n4; i += nthreads) {
       uchar4 q = reinterpret_cast<const uchar4 *>(X)[i];
       float4 v = make_float4(__fmul_rn((float)((int)q.x - zp), scale), __fmul_rn((float)((int)q.y - zp), scale),

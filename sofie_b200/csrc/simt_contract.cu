@@ -219,11 +219,15 @@ int launch_conv_direct(cudaStream_t s, const ConvGeom &g, const TX *X, const TW 
 int launch_conv2d_f32_simt(cudaStream_t s, const ConvGeom &g, const float *X, const float *W, const float *bias,
                            float *Y)
 {
+   const int rc = launch_conv2d_f32_first(s, g, X, W, bias, Y);
+   if (rc >= 0) return rc;
    return launch_conv_direct<float, float, float, float, EpiF32>(s, g, X, W, EpiF32{bias}, 0, Y);
 }
 int launch_qconv2d_simt(cudaStream_t s, const ConvGeom &g, const uint8_t *X, const int8_t *W, const float *mult,
                         const int32_t *bias, int x_zp, int y_zp, uint8_t *Y)
 {
+   const int rc = launch_qconv2d_first(s, g, X, W, mult, bias, x_zp, y_zp, Y);
+   if (rc >= 0) return rc;
    return launch_conv_direct<uint8_t, int8_t, int, uint8_t, EpiU8>(s, g, X, W, EpiU8{mult, bias, y_zp}, x_zp, Y);
 }
 

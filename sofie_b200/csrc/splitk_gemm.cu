@@ -13,28 +13,63 @@ namespace sofie {
 constexpr int kSplitKMaxN = 16;
 constexpr int kSplitKWarps = 8;
 
-// One warp = one output row over one K slab, all N columns. Lanes stride K, so the loads of the A
-// row and of every B row are coalesced 128-byte lines; B is shared by all warps through L1/L2.
+// A block = 8 output rows (one per warp) over one K slab, all N columns. The slab of B is staged in
+// shared memory once per block, in chunks of kSplitKChunk elements of K, and shared by the 8 rows;
+// a lane reads 16 bytes of its A row and of every staged B row per step, so global loads are whole
+// 512-byte warp requests and several are in flight per lane.
+constexpr int kSplitKChunk = 512; // floats of K per staged chunk: 16 x 512 x 4 B = 32 KB at most
+
 template <bool TB>
 __global__ void __launch_bounds__(kSplitKWarps * 32)
 gemm_f32_splitk_partial_kernel(int M, int N, int K, int slab, const float *__restrict__ A, const float *__restrict__ B,
                                float *__restrict__ partial)
 {
+   __shared__ __align__(16) float bs[kSplitKMaxN * kSplitKChunk];
    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
    const int m = blockIdx.x * kSplitKWarps + warp;
    const int s = blockIdx.y;
-   if (m >= M) return;
    const int k0 = s * slab, k1 = min(K, k0 + slab);
    float acc[kSplitKMaxN];
 #pragma unroll
    for (int n = 0; n < kSplitKMaxN; n++) acc[n] = 0.f;
-   const float *a = A + (size_t)m * K;
-   for (int k = k0 + lane; k < k1; k += 32) {
-      const float av = a[k];
+   const float *a = A + (size_t)(m < M ? m : 0) * K;
+   const bool a_vec = (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+   for (int c0 = k0; c0 < k1; c0 += kSplitKChunk) {
+      const int len = min(kSplitKChunk, k1 - c0);
+      __syncthreads(); // the previous chunk is no longer read
+      for (int i = threadIdx.x; i < N * kSplitKChunk; i += kSplitKWarps * 32) {
+         const int n = TB ? i / kSplitKChunk : i % N, kk = TB ? i % kSplitKChunk : i / N;
+         float v = 0.f;
+         if (kk < len) v = TB ? B[(size_t)n * K + c0 + kk] : B[(size_t)(c0 + kk) * N + n];
+         bs[n * kSplitKChunk + kk] = v;
+      }
+      __syncthreads();
+      if (m < M) {
+#pragma unroll 2
+         for (int kk = lane * 4; kk < len; kk += 128) {
+            float4 av;
+            if (a_vec && kk + 3 < len) {
+               av = *reinterpret_cast<const float4 *>(a + c0 + kk);
+            } else {
+               av.x = a[c0 + kk];
+               av.y = kk + 1 < len ? a[c0 + kk + 1] : 0.f;
+               av.z = kk + 2 < len ? a[c0 + kk + 2] : 0.f;
+               av.w = kk + 3 < len ? a[c0 + kk + 3] : 0.f;
+            }
 #pragma unroll
-      for (int n = 0; n < kSplitKMaxN; n++)
-         if (n < N) acc[n] = fmaf(av, TB ? B[(size_t)n * K + k] : B[(size_t)k * N + n], acc[n]);
+            for (int n = 0; n < kSplitKMaxN; n++) {
+               if (n < N) {
+                  const float4 bv = *reinterpret_cast<const float4 *>(bs + n * kSplitKChunk + kk);
+                  acc[n] = fmaf(av.x, bv.x, acc[n]);
+                  acc[n] = fmaf(av.y, bv.y, acc[n]);
+                  acc[n] = fmaf(av.z, bv.z, acc[n]);
+                  acc[n] = fmaf(av.w, bv.w, acc[n]);
+               }
+            }
+         }
+      }
    }
+   if (m >= M) return;
 #pragma unroll
    for (int n = 0; n < kSplitKMaxN; n++) {
       if (n < N) {
@@ -66,8 +101,9 @@ bool splitk_shape_ok(const sofie_gemm_f32_desc &d)
 
 int splitk_splits(const sofie_gemm_f32_desc &d, size_t scratch_floats)
 {
-   // enough (row, slab) pairs to fill the GPU about twice, slabs of at least 128 elements of K
-   int splits = (2 * kNumSMs * kSplitKWarps + d.M - 1) / d.M;
+   // enough (row group, slab) blocks to fill the GPU about four times, slabs of at least 128 elements of K
+   const int row_groups = ceil_div(d.M, kSplitKWarps);
+   int splits = ceil_div(4 * kNumSMs, row_groups);
    if (splits > d.K / 128) splits = d.K / 128;
    if (splits > 64) splits = 64;
    if (splits < 1) splits = 1;
@@ -85,7 +121,7 @@ int launch_gemm_f32_splitk(cudaStream_t s, const sofie_gemm_f32_desc &d, const f
       return fail(SOFIE_CUDA_ERR_NOMEM, "split-K scratch of %zu floats is too small for M*N = %lld", scratch_floats,
                   (long long)d.M * d.N);
    int slab = (d.K + splits - 1) / splits;
-   slab = (slab + 31) & ~31; // whole 128-byte lines per slab
+   slab = (slab + 127) & ~127; // whole 512-byte warp requests per slab
    const int used = (d.K + slab - 1) / slab;
    dim3 grid(ceil_div(d.M, kSplitKWarps), used);
    if (d.transB) gemm_f32_splitk_partial_kernel<true><<<grid, kSplitKWarps * 32, 0, s>>>(d.M, d.N, d.K, slab, A, B, scratch);

@@ -48,94 +48,167 @@ constexpr int kConvThreadsTF32 = (2 + kConvEpilogueWarps + kConvConverterWarps) 
 // The part of the epilogue one warp does for one finished tile: read its 32 TMEM lanes (pixels) for
 // its share of the output channels, add the NACC partial accumulators, apply bias / Relu or the
 // requantisation, reduce 2x2 windows by shuffles when pooling is fused, and store NHWC.
-// e = index of the epilogue warp (0..7), lane_base = first TMEM lane of its quarter.
-template <int KIND, int BN, int NACC>
+// EPI_WARPS / 4 warps share a lane quarter and split the channels among them in pieces of at least
+// 16; e = index of the epilogue warp, lane_base = first TMEM lane of its quarter.
+template <int KIND, int BN, int NACC, int EPI_WARPS>
 __device__ __forceinline__ void conv_tile_epilogue(const ConvEpilogue &ep, const ConvTiling &tg, const float *s_bias,
-                                                   const float *s_mult, const int *s_qbias, uint32_t tmem_base, int buf, int e,
-                                                   int lane_base, int lane, int n0, int h0, int w0)
+                                                   const float *s_mult, const int *s_qbias, bool pool_first, uint32_t tmem_base,
+                                                   int buf, int e, int lane_base, int lane, int n0, int h0, int w0)
 {
-   constexpr int CW = BN >= 64 ? BN / 2 : BN;            // channels per warp
-   const int c_begin = BN >= 64 ? (e >> 2) * CW : 0;
-   const bool has_columns = BN >= 64 || (e >> 2) == 0;
+   constexpr int WPQ = EPI_WARPS / 4;                       // warps per lane quarter
+   constexpr int CW = BN / WPQ >= 16 ? BN / WPQ : 16;       // channels per warp
+   constexpr int CH = CW >= 32 ? 32 : 16;                   // channels per TMEM read
+   const int c_begin = (e >> 2) * CW;
+   if (c_begin >= BN) return;
    const int pix = lane_base + lane; // pixel of the patch = TMEM lane
    const int ww = pix % tg.tileW, hh = (pix / tg.tileW) % tg.tileH, nn = pix / (tg.tileW * tg.tileH);
    const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
    const int n = n0 + nn, h = h0 + hh, w = w0 + ww;
    const bool valid = n < tg.N;
-   // with pooling only the top-left pixel of each 2x2 window stores
+   // in the pooling path that keeps all columns only the top-left pixel of each 2x2 window stores
    const bool store = valid && (!ep.pool || (((hh | ww) & 1) == 0));
    const int oH = ep.pool ? tg.H / 2 : tg.H, oW = ep.pool ? tg.W / 2 : tg.W;
    const int oh = ep.pool ? h / 2 : h, ow = ep.pool ? w / 2 : w;
    const size_t opix = ((size_t)n * oH + oh) * oW + ow;
-   if (has_columns) {
 #pragma unroll 1
-      for (int c0 = c_begin; c0 < c_begin + CW; c0 += 32) {
-         if (c0 >= tg.Cout) break;
-         // sum of the NACC partial accumulators of this tile
-         uint32_t r[32];
-         tmem_ld_32x32(t_row + (uint32_t)(buf * NACC * BN + c0), r);
+   for (int c0 = c_begin; c0 < c_begin + CW; c0 += CH) {
+      if (c0 >= tg.Cout) break;
+      // sum of the NACC partial accumulators of this tile
+      uint32_t r[CH];
+      tmem_ld_cols<CH>(t_row + (uint32_t)(buf * NACC * BN + c0), r);
+      if constexpr (NACC == 2) {
+         uint32_t p[CH];
+         tmem_ld_cols<CH>(t_row + (uint32_t)((buf * NACC + 1) * BN + c0), p);
+         tmem_ld_wait();
+#pragma unroll
+         for (int j = 0; j < CH; j++) {
+            if constexpr (KIND == kTF32) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(p[j]));
+            else r[j] = (uint32_t)((int)r[j] + (int)p[j]);
+         }
+      } else {
          tmem_ld_wait();
 #pragma unroll
          for (int a = 1; a < NACC; a++) {
-            uint32_t p[32];
-            tmem_ld_32x32(t_row + (uint32_t)((buf * NACC + a) * BN + c0), p);
+            uint32_t p[CH];
+            tmem_ld_cols<CH>(t_row + (uint32_t)((buf * NACC + a) * BN + c0), p);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
+            for (int j = 0; j < CH; j++) {
                if constexpr (KIND == kTF32) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(p[j]));
                else r[j] = (uint32_t)((int)r[j] + (int)p[j]);
             }
          }
-         const int ncols = min(32, tg.Cout - c0);
-         if constexpr (KIND == kTF32) {
-            float v[32];
+      }
+      if (ep.pool == 2 && pool_first) {
+         // Fused 2x2 MaxPool as a reduce-scatter over the four lanes of a window (lane ^ 1 is the
+         // neighbour in the row, lane ^ tileW the one in the next row): each exchange halves the
+         // columns a lane keeps, so a lane ends with CH / 4 channels of its window's maximum and
+         // bias, Relu and requantisation run on a quarter of the values. Taking the maximum of the
+         // raw accumulators first gives the same stored values because every later step is
+         // non-decreasing in the accumulator (pool_first is false when a requantisation
+         // multiplier is negative; the path below then pools the finished values).
+         const bool up1 = lane & 1, up2 = (lane & tg.tileW) != 0;
+         uint32_t m1[CH / 2], m2[CH / 4];
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-               float acc = __uint_as_float(r[j]) + s_bias[c0 + j];
-               v[j] = ep.relu ? relu_ref(acc) : acc;
-            }
-            if (ep.pool) {
+         for (int i = 0; i < CH / 2; i++) {
+            const uint32_t send = up1 ? r[i] : r[CH / 2 + i];
+            const uint32_t mine = up1 ? r[CH / 2 + i] : r[i];
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, send, 1);
+            if constexpr (KIND == kTF32) m1[i] = __uint_as_float(got) > __uint_as_float(mine) ? got : mine;
+            else m1[i] = (uint32_t)max((int)got, (int)mine);
+         }
 #pragma unroll
-               for (int j = 0; j < 32; j++) {
-                  float o = __shfl_xor_sync(0xffffffffu, v[j], 1);
-                  v[j] = o > v[j] ? o : v[j];
-                  o = __shfl_xor_sync(0xffffffffu, v[j], tg.tileW);
-                  v[j] = o > v[j] ? o : v[j];
+         for (int i = 0; i < CH / 4; i++) {
+            const uint32_t send = up2 ? m1[i] : m1[CH / 4 + i];
+            const uint32_t mine = up2 ? m1[CH / 4 + i] : m1[i];
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, send, tg.tileW);
+            if constexpr (KIND == kTF32) m2[i] = __uint_as_float(got) > __uint_as_float(mine) ? got : mine;
+            else m2[i] = (uint32_t)max((int)got, (int)mine);
+         }
+         const int col = c0 + (up1 ? CH / 2 : 0) + (up2 ? CH / 4 : 0); // first of this lane's CH / 4 channels
+         const bool full = col + CH / 4 <= tg.Cout;
+         if (valid) {
+            if constexpr (KIND == kTF32) {
+               float v[CH / 4];
+#pragma unroll
+               for (int i = 0; i < CH / 4; i++) {
+                  const float acc = __uint_as_float(m2[i]) + s_bias[col + i];
+                  v[i] = ep.relu ? relu_ref(acc) : acc;
                }
-            }
-            if (store) {
-               float *y = ep.Yf + opix * tg.Cout + c0;
-               if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+               float *y = ep.Yf + opix * tg.Cout + col;
+               if (full && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
 #pragma unroll
-                  for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                  for (int i = 0; i < CH / 4; i += 4) *reinterpret_cast<float4 *>(y + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                } else {
 #pragma unroll
-                  for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
+                  for (int i = 0; i < CH / 4; i++) if (col + i < tg.Cout) y[i] = v[i];
                }
-            }
-         } else {
-            int q[32];
+            } else {
+               int q[CH / 4];
 #pragma unroll
-            for (int j = 0; j < 32; j++) q[j] = requant_u8((int)r[j] + s_qbias[c0 + j], s_mult[c0 + j], ep.y_zp, ep.relu);
-            if (ep.pool) {
+               for (int i = 0; i < CH / 4; i++) q[i] = requant_u8((int)m2[i] + s_qbias[col + i], s_mult[col + i], ep.y_zp, ep.relu);
+               uint8_t *y = ep.Yu8 + opix * tg.Cout + col;
+               if (full && ((reinterpret_cast<uintptr_t>(y) & 3) == 0)) {
 #pragma unroll
-               for (int j = 0; j < 32; j++) {
-                  q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], 1));
-                  q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], tg.tileW));
-               }
-            }
-            if (store) {
-               uint8_t *y = ep.Yu8 + opix * tg.Cout + c0;
-               uint32_t packed[8];
-#pragma unroll
-               for (int j = 0; j < 32; j += 4) packed[j >> 2] = (uint32_t)q[j] | ((uint32_t)q[j + 1] << 8) | ((uint32_t)q[j + 2] << 16) | ((uint32_t)q[j + 3] << 24);
-               if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
-                  *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                  *reinterpret_cast<uint4 *>(y + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                  for (int i = 0; i < CH / 4; i += 4)
+                     *reinterpret_cast<uint32_t *>(y + i) = (uint32_t)q[i] | ((uint32_t)q[i + 1] << 8) | ((uint32_t)q[i + 2] << 16) | ((uint32_t)q[i + 3] << 24);
                } else {
 #pragma unroll
-                  for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)q[j];
+                  for (int i = 0; i < CH / 4; i++) if (col + i < tg.Cout) y[i] = (uint8_t)q[i];
                }
+            }
+         }
+         continue;
+      }
+      const int ncols = min(CH, tg.Cout - c0);
+      if constexpr (KIND == kTF32) {
+         float v[CH];
+#pragma unroll
+         for (int j = 0; j < CH; j++) {
+            float acc = __uint_as_float(r[j]) + s_bias[c0 + j];
+            v[j] = ep.relu ? relu_ref(acc) : acc;
+         }
+         if (ep.pool) {
+#pragma unroll
+            for (int j = 0; j < CH; j++) {
+               float o = __shfl_xor_sync(0xffffffffu, v[j], 1);
+               v[j] = o > v[j] ? o : v[j];
+               o = __shfl_xor_sync(0xffffffffu, v[j], tg.tileW);
+               v[j] = o > v[j] ? o : v[j];
+            }
+         }
+         if (store) {
+            float *y = ep.Yf + opix * tg.Cout + c0;
+            if (ncols == CH && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+#pragma unroll
+               for (int j = 0; j < CH; j += 4) *reinterpret_cast<float4 *>(y + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+               for (int j = 0; j < CH; j++) if (j < ncols) y[j] = v[j];
+            }
+         }
+      } else {
+         int q[CH];
+#pragma unroll
+         for (int j = 0; j < CH; j++) q[j] = requant_u8((int)r[j] + s_qbias[c0 + j], s_mult[c0 + j], ep.y_zp, ep.relu);
+         if (ep.pool) {
+#pragma unroll
+            for (int j = 0; j < CH; j++) {
+               q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], 1));
+               q[j] = max(q[j], __shfl_xor_sync(0xffffffffu, q[j], tg.tileW));
+            }
+         }
+         if (store) {
+            uint8_t *y = ep.Yu8 + opix * tg.Cout + c0;
+            uint32_t packed[CH / 4];
+#pragma unroll
+            for (int j = 0; j < CH; j += 4) packed[j >> 2] = (uint32_t)q[j] | ((uint32_t)q[j + 1] << 8) | ((uint32_t)q[j + 2] << 16) | ((uint32_t)q[j + 3] << 24);
+            if (ncols == CH && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+#pragma unroll
+               for (int j = 0; j < CH / 4; j += 4) *reinterpret_cast<uint4 *>(y + 4 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+            } else {
+#pragma unroll
+               for (int j = 0; j < CH; j++) if (j < ncols) y[j] = (uint8_t)q[j];
             }
          }
       }
@@ -170,11 +243,13 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    SOFIE_PROF_DECL
+   int negative_mult = 0;
    for (int c = threadIdx.x; c < 128; c += blockDim.x) {
       const bool in = c < tg.Cout;
       s_bias[c] = (KIND == kTF32 && in && ep.bias) ? ep.bias[c] : 0.f;
       s_mult[c] = (KIND == kI8 && in) ? ep.mult[c] : 0.f;
       s_qbias[c] = (KIND == kI8 && in && ep.qbias) ? ep.qbias[c] : 0;
+      if (KIND == kI8 && in && !(ep.mult[c] >= 0.f)) negative_mult = 1;
    }
    const int S = tg.stages;
    const int stages_per_tile = 9 * tg.chunks / TPS; // TPS > 1 only when chunks == 1
@@ -204,7 +279,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       tmem_relinquish();
    }
    tc_fence_before();
-   __syncthreads();
+   const bool pool_first = __syncthreads_or(negative_mult) == 0;
    tc_fence_after();
    const uint32_t tmem_base = tmem_base_holder;
 
@@ -354,7 +429,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          tile_origin(tile, n0, h0, w0);
          if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
          tc_fence_after();
-         conv_tile_epilogue<KIND, BN, NACC>(ep, tg, s_bias, s_mult, s_qbias, tmem_base, buf, e, lane_base, lane, n0, h0, w0);
+         conv_tile_epilogue<KIND, BN, NACC, EPI_WARPS>(ep, tg, s_bias, s_mult, s_qbias, pool_first, tmem_base, buf, e, lane_base, lane, n0, h0, w0);
          // this warp is done with the TMEM buffer: the MMA warp may overwrite it
          tc_fence_before();
          __syncwarp();
@@ -395,24 +470,40 @@ constexpr int kPlaneBox = kPatchH * kPatchW * 16;                 // bytes one p
 constexpr int kPlaneStride = (kPlaneBox + 127) / 128 * 128;       // TMA destinations are 128-byte aligned
 constexpr int kPatchMaxStages = 4;
 
+constexpr int kPatchThreads = 18 * 32; // producer, MMA issuer, 8 epilogue + 8 converter warps (fp32) or 16 epilogue warps (int8)
+
 struct PatchPlan {
-   int planes;   // 16-byte channel groups per pixel
-   int ksteps;   // MMAs (32 bytes of K) per tap
    int chunks;   // weight sub-tiles per tap (rows of cb bytes)
    int cb;       // bytes per weight row chunk: 32, 64 or 128 (selects the swizzle)
-   int stages;   // patches in flight
-   uint32_t patch_bytes, w_bytes;
+   int stages;   // pipeline slots
+   uint32_t stage_bytes; // one copy (hi) of the planes of a stage
+   uint32_t w_bytes;     // one copy (hi) of all weights
 };
 
-template <int KIND, int BN, int KSTEPS>
-__global__ void __launch_bounds__(KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8, 1)
+// KPS = MMAs (32 bytes of K) per tap and stage, G = stages per tile: a stage carries 2 * KPS planes
+// of the patch, so a tile with many channels is streamed in G plane groups and a slot stays small
+// enough for two of them to fit beside the resident weights.
+//
+// fp32 (3xTF32): the weight sub-tile of a (tap, chunk) is stored as [hi rows | lo rows], 2 * BN rows
+// of one operand, so ONE MMA of width 2 * BN multiplies the hi part of the patch with both (the
+// patch, the larger operand, is read once for two of the three products); a second MMA of width BN
+// adds lo(patch) x hi(weights). The two halves of the wide accumulator are added in the epilogue.
+template <int KIND, int BN, int KPS, int G>
+__global__ void __launch_bounds__(kPatchThreads, 1)
 umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, ConvEpilogue ep,
                           ConvTiling tg, PatchPlan pl, uint32_t *status)
 {
    constexpr int ES = (KIND == kTF32) ? 4 : 1;
    constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
-   constexpr uint32_t TMEM_COLS = 2 * BN; // two accumulators of BN columns: 64, 128 or 256
-   constexpr int EPI_WARPS = kConvEpilogueWarps;
+   constexpr int NACC = (KIND == kTF32) ? 2 : 1;
+   constexpr int PGP = 2 * KPS;                              // planes per stage
+   constexpr int KSTEPS = KPS * G;                           // MMAs per tap
+   constexpr int CBK = KSTEPS * 32 >= 128 ? 128 : KSTEPS * 32; // bytes per weight row chunk (== pl.cb)
+   constexpr int CHUNKS = KSTEPS * 32 / CBK;
+   constexpr uint32_t B_TILE = BN * CBK;                     // one copy of a (tap, chunk) weight sub-tile
+   constexpr uint32_t TMEM_COLS = 2 * NACC * BN;             // two buffers: 64 ... 512 columns
+   constexpr int EPI_WARPS = (KIND == kTF32) ? 8 : 16;
+   constexpr int CONV_WARPS = 8;
    extern __shared__ unsigned char smem_raw[];
    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
    __shared__ uint64_t full_bar[kPatchMaxStages], conv_bar[kPatchMaxStages], empty_bar[kPatchMaxStages], tmem_full[2], tmem_empty[2];
@@ -424,23 +515,23 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    SOFIE_PROF_DECL
+   int negative_mult = 0;
    for (int c = threadIdx.x; c < 128; c += blockDim.x) {
       const bool in = c < tg.Cout;
       s_bias[c] = (KIND == kTF32 && in && ep.bias) ? ep.bias[c] : 0.f;
       s_mult[c] = (KIND == kI8 && in) ? ep.mult[c] : 0.f;
       s_qbias[c] = (KIND == kI8 && in && ep.qbias) ? ep.qbias[c] : 0;
+      if (KIND == kI8 && in && !(ep.mult[c] >= 0.f)) negative_mult = 1;
    }
    const int S = pl.stages;
-   const uint32_t b_tile = (uint32_t)BN * pl.cb;          // one (tap, chunk) weight sub-tile
-   unsigned char *w_hi = smem;
-   unsigned char *w_lo = smem + pl.w_bytes;                // fp32 only
-   unsigned char *patches = smem + (size_t)COPIES * pl.w_bytes;
-   auto patch_hi = [&](int s) { return patches + (size_t)s * COPIES * pl.patch_bytes; };
+   unsigned char *w_smem = smem;                                    // 9 * CHUNKS items of COPIES * B_TILE
+   unsigned char *slots = smem + (size_t)COPIES * pl.w_bytes;
+   auto slot_hi = [&](int s) { return slots + (size_t)s * COPIES * pl.stage_bytes; };
 
    if (threadIdx.x == 0) {
       for (int s = 0; s < kPatchMaxStages; s++) {
          mbar_init(&full_bar[s], 1);
-         mbar_init(&conv_bar[s], kConvConverterWarps * 32);
+         mbar_init(&conv_bar[s], CONV_WARPS * 32);
          mbar_init(&empty_bar[s], 1);
       }
       for (int b = 0; b < 2; b++) {
@@ -448,7 +539,7 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          mbar_init(&tmem_empty[b], EPI_WARPS);
       }
       mbar_init(&w_full, 1);
-      mbar_init(&w_conv, kConvConverterWarps * 32);
+      mbar_init(&w_conv, CONV_WARPS * 32);
       abort_flag = 0;
       fence_mbar_init();
       prefetch_tensormap(&tmX);
@@ -459,7 +550,7 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       tmem_relinquish();
    }
    tc_fence_before();
-   __syncthreads();
+   const bool pool_first = __syncthreads_or(negative_mult) == 0;
    tc_fence_after();
    const uint32_t tmem_base = tmem_base_holder;
 
@@ -473,87 +564,90 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 
    if (warp == 0) {
       // ---------------- TMA producer ----------------
-      // weights: 9 x chunks boxes of BN rows, all on one barrier
-      const int cbe = pl.cb / ES;
+      // weights: 9 x CHUNKS boxes of BN rows, all on one barrier
       if (lane == 0) mbar_expect_tx(&w_full, pl.w_bytes);
       __syncwarp();
-      for (int item = lane; item < 9 * pl.chunks; item += 32) {
-         const int tap = item / pl.chunks, ch = item - tap * pl.chunks;
-         tma_load_2d(w_hi + (size_t)item * b_tile, &tmW, tap * tg.C + ch * cbe, 0, &w_full);
+      for (int item = lane; item < 9 * CHUNKS; item += 32) {
+         const int tap = item / CHUNKS, ch = item - tap * CHUNKS;
+         tma_load_2d(w_smem + (size_t)item * COPIES * B_TILE, &tmW, tap * tg.C + ch * (CBK / ES), 0, &w_full);
       }
       // patches: one box per plane, issued by as many lanes
       int g = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, g++) {
+      for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
          int n0, h0, w0;
          tile_origin(tile, n0, h0, w0);
-         const int s = g % S;
-         const uint32_t ph = (g / S) & 1;
-         if (lane == 0) {
-            ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
-            if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)pl.planes * kPlaneBox);
+         for (int grp = 0; grp < G; grp++, g++) {
+            const int s = g % S;
+            const uint32_t ph = (g / S) & 1;
+            if (lane == 0) {
+               ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
+               if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)PGP * kPlaneBox);
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            // channel coordinate = a multiple of 16 bytes; rows and columns start at -1 (zero fill)
+            if (lane < PGP)
+               tma_load_4d(slot_hi(s) + (size_t)lane * kPlaneStride, &tmX, (grp * PGP + lane) * (16 / ES), w0 - 1, h0 - 1, n0, &full_bar[s]);
+            __syncwarp();
          }
-         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-         if (!ok) break;
-         // channel coordinate = a multiple of 16 bytes; rows and columns start at -1 (zero fill)
-         if (lane < pl.planes)
-            tma_load_4d(patch_hi(s) + (size_t)lane * kPlaneStride, &tmX, lane * (16 / ES), w0 - 1, h0 - 1, n0, &full_bar[s]);
-         __syncwarp();
       }
    } else if (warp == 1) {
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
          constexpr uint32_t idesc = make_idesc<KIND>(128, BN);
+         constexpr uint32_t idesc_wide = make_idesc<KIND>(128, NACC * BN);
          bool ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&w_conv, 0, &abort_flag, status, kStatusWaitConv, 0x4000)
                                                    : mbar_wait(&w_full, 0, &abort_flag, status, kStatusWaitFull, 0x4000));
          tc_fence_after();
-         const uint64_t db0 = make_smem_desc(smem_u32(w_hi), pl.cb);
+         // The issuing thread is the pacemaker of the whole CTA, so everything that can be is folded
+         // at compile time: each MMA costs it one 32-bit add per descriptor. The address field (bits
+         // 0..13, in units of 16 bytes) never carries out of its field.
+         const uint64_t db0 = make_smem_desc(smem_u32(w_smem), CBK);
          const uint32_t b_hi_word = (uint32_t)(db0 >> 32), b_lo_word = (uint32_t)db0;
-         const uint32_t patch16 = pl.patch_bytes >> 4, wlo16 = pl.w_bytes >> 4; // hi -> lo copy, in 16-byte units
-         int g = 0;
-         for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, g++) {
-            const int buf = g & 1;
-            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((g >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + g))) break;
-            const int s = g % S;
-            const uint32_t ph = (g / S) & 1;
-            ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
-                                                 : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t d = tmem_base + (uint32_t)(buf * BN);
-            // The issuing thread is the pacemaker of the whole CTA, so everything that can be
-            // is folded at compile time: each MMA costs it one 32-bit add per descriptor. The
-            // address field (bits 0..13, in units of 16 bytes) never carries out of its field.
-            const uint64_t da0 = make_smem_desc_noswizzle(smem_u32(patch_hi(s)), kPlaneStride, kPatchW * 16);
-            const uint32_t a_hi_word = (uint32_t)(da0 >> 32), a_lo_word = (uint32_t)da0;
-            auto adesc = [&](uint32_t off16) { return ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + off16); };
-            auto bdesc = [&](uint32_t off16) { return ((uint64_t)b_hi_word << 32) | (uint64_t)(b_lo_word + off16); };
+         const uint32_t lo16 = pl.stage_bytes >> 4; // hi -> lo copy of a slot, in 16-byte units
+         int g = 0, lt = 0;
+         for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, lt++) {
+            const int buf = lt & 1;
+            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt))) break;
+            const uint32_t d = tmem_base + (uint32_t)(buf * NACC * BN);
 #pragma unroll
-            for (int tap = 0; tap < 9; tap++) {
+            for (int grp = 0; grp < G; grp++, g++) {
+               const int s = g % S;
+               const uint32_t ph = (g / S) & 1;
+               ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
+                                                    : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
+               if (!ok) break;
+               tc_fence_after();
+               const uint64_t da0 = make_smem_desc_noswizzle(smem_u32(slot_hi(s)), kPlaneStride, kPatchW * 16);
+               const uint32_t a_hi_word = (uint32_t)(da0 >> 32), a_lo_word = (uint32_t)da0;
+               auto adesc = [&](uint32_t off16) { return ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + off16); };
+               auto bdesc = [&](uint32_t off16) { return ((uint64_t)b_hi_word << 32) | (uint64_t)(b_lo_word + off16); };
 #pragma unroll
-               for (int kk = 0; kk < KSTEPS; kk++) {
-                  constexpr int CBK = KSTEPS * 32 >= 128 ? 128 : KSTEPS * 32; // bytes per weight row chunk
-                  constexpr int CHUNKS = KSTEPS * 32 / CBK;
-                  const uint32_t a16 = (uint32_t)(((tap / 3) * kPatchW + (tap % 3)) * 16 + kk * 2 * kPlaneStride) >> 4;
-                  const uint32_t b16 = (uint32_t)((tap * CHUNKS + (kk * 32) / CBK) * (BN * CBK) + (kk * 32) % CBK) >> 4;
-                  const uint32_t acc = (tap | kk) ? 1u : 0u;
-                  if constexpr (KIND == kTF32) {
-                     tc_mma<KIND>(d, adesc(a16 + patch16), bdesc(b16), idesc, acc);        // lo x hi
-                     tc_mma<KIND>(d, adesc(a16), bdesc(b16 + wlo16), idesc, 1u);           // hi x lo
-                     tc_mma<KIND>(d, adesc(a16), bdesc(b16), idesc, 1u);                   // hi x hi
-                  } else {
-                     tc_mma<KIND>(d, adesc(a16), bdesc(b16), idesc, acc);
+               for (int tap = 0; tap < 9; tap++) {
+#pragma unroll
+                  for (int kk = 0; kk < KPS; kk++) {
+                     const int kb = (grp * KPS + kk) * 32; // byte offset in the K row of this tap
+                     const uint32_t a16 = (uint32_t)(((tap / 3) * kPatchW + (tap % 3)) * 16 + kk * 2 * kPlaneStride) >> 4;
+                     const uint32_t b16 = (uint32_t)((tap * CHUNKS + kb / CBK) * (COPIES * B_TILE) + kb % CBK) >> 4;
+                     const uint32_t acc = (grp | tap | kk) ? 1u : 0u;
+                     if constexpr (KIND == kTF32) {
+                        tc_mma<KIND>(d, adesc(a16), bdesc(b16), idesc_wide, acc);     // hi x [hi | lo]
+                        tc_mma<KIND>(d, adesc(a16 + lo16), bdesc(b16), idesc, 1u);     // lo x hi
+                     } else {
+                        tc_mma<KIND>(d, adesc(a16), bdesc(b16), idesc, acc);
+                     }
                   }
                }
+               tc_commit(&empty_bar[s]);
             }
-            tc_commit(&empty_bar[s]);
-            tc_commit(&tmem_full[buf]);
+            if (ok) tc_commit(&tmem_full[buf]);
          }
       }
-   } else if (warp >= 2 + EPI_WARPS) {
-      // ---------------- converter warps (kTF32): hi/lo split, weights once, then each patch ----------------
+   } else if (KIND == kTF32 && warp >= 2 + EPI_WARPS) {
+      // ---------------- converter warps (kTF32): hi/lo split, weights once, then each slot ----------------
       if constexpr (KIND == kTF32) {
-         constexpr int NT = kConvConverterWarps * 32;
+         constexpr int NT = CONV_WARPS * 32;
          const int t = threadIdx.x - (2 + EPI_WARPS) * 32;
          // Splits n16 16-byte groups at src in place (hi) and writes the lo parts lo_off bytes further.
          // Four independent loads per thread are issued before the first conversion.
@@ -582,32 +676,37 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          };
          bool ok = SOFIE_PROF_WAIT(mbar_wait(&w_full, 0, &abort_flag, status, kStatusWaitFull, 0x4000));
          if (ok) {
-            split(w_hi, pl.w_bytes / 16, pl.w_bytes);
+            for (int item = 0; item < 9 * CHUNKS; item++) split(w_smem + (size_t)item * COPIES * B_TILE, B_TILE / 16, B_TILE);
             fence_proxy_async();
             mbar_arrive(&w_conv);
          }
          int g = 0;
-         for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, g++) {
-            const int s = g % S;
-            const uint32_t ph = (g / S) & 1;
-            if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) break;
-            split(patch_hi(s), pl.patch_bytes / 16, pl.patch_bytes);
-            fence_proxy_async();
-            mbar_arrive(&conv_bar[s]);
+         for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
+            for (int grp = 0; grp < G; grp++, g++) {
+               const int s = g % S;
+               const uint32_t ph = (g / S) & 1;
+               if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) {
+                  ok = false;
+                  break;
+               }
+               split(slot_hi(s), pl.stage_bytes / 16, pl.stage_bytes);
+               fence_proxy_async();
+               mbar_arrive(&conv_bar[s]);
+            }
          }
       }
    } else {
-      // ---------------- epilogue warps 2..9 ----------------
+      // ---------------- epilogue warps, from warp 2 on ----------------
       const int e = warp - 2;
       const int lane_base = (warp & 3) * 32;
-      int g = 0;
-      for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, g++) {
-         const int buf = g & 1;
+      int lt = 0;
+      for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, lt++) {
+         const int buf = lt & 1;
          int n0, h0, w0;
          tile_origin(tile, n0, h0, w0);
-         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (g >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + g))) break;
+         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
          tc_fence_after();
-         conv_tile_epilogue<KIND, BN, 1>(ep, tg, s_bias, s_mult, s_qbias, tmem_base, buf, e, lane_base, lane, n0, h0, w0);
+         conv_tile_epilogue<KIND, BN, NACC, EPI_WARPS>(ep, tg, s_bias, s_mult, s_qbias, pool_first, tmem_base, buf, e, lane_base, lane, n0, h0, w0);
          tc_fence_before();
          __syncwarp();
          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
@@ -625,28 +724,22 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 
 // Launches the patch kernel when the shape belongs to it and the weights fit; returns -1 when the
 // caller should use the per-tap kernel instead.
-template <int KIND>
-static int try_launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, const void *Wp, const ConvEpilogue &ep, int BN)
+template <int KIND, int BN, int KPS, int G>
+static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, const void *Wp, const ConvEpilogue &ep)
 {
    constexpr int ES = (KIND == kTF32) ? 4 : 1;
    constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
-   if (g.H % kPatchTileH != 0 || g.W % kPatchTileW != 0) return -1;
    const int row_bytes = g.C * ES;
-   if (row_bytes != 32 && row_bytes != 64 && row_bytes != 128 && row_bytes != 256) return -1;
    PatchPlan pl = {};
-   pl.planes = row_bytes / 16;
-   pl.ksteps = row_bytes / 32;
    pl.cb = row_bytes >= 128 ? 128 : row_bytes;
-   if (pl.cb != 32 && pl.cb != 64 && pl.cb != 128) return -1;
-   if (row_bytes % pl.cb != 0) return -1;
    pl.chunks = row_bytes / pl.cb;
    pl.w_bytes = (uint32_t)(9 * pl.chunks * BN * pl.cb);
-   pl.patch_bytes = (uint32_t)(pl.planes * kPlaneStride);
+   pl.stage_bytes = (uint32_t)(2 * KPS * kPlaneStride);
    const long budget = 200 * 1024 - (long)COPIES * pl.w_bytes;
-   const long per_stage = (long)COPIES * pl.patch_bytes;
-   if (budget < 2 * per_stage) return -1;
+   const long per_stage = (long)COPIES * pl.stage_bytes;
    pl.stages = (int)(budget / per_stage);
    if (pl.stages > kPatchMaxStages) pl.stages = kPatchMaxStages;
+   if (pl.stages < 2) return -1;
    ConvTiling tg = {};
    tg.N = g.N; tg.H = g.H; tg.W = g.W; tg.C = g.C; tg.Cout = g.Cout;
    tg.tileW = kPatchTileW; tg.tileH = kPatchTileH; tg.tileN = 1;
@@ -671,27 +764,42 @@ static int try_launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *
    uint32_t *status = device_status_word();
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int grid = tg.num_tiles < kNumSMs ? tg.num_tiles : kNumSMs;
-   const int threads = KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8;
-   auto go = [&](auto kern) -> int {
-      SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-      kern<<<grid, threads, smem, s>>>(tmX, tmW, ep, tg, pl, status);
-      SOFIE_LAUNCH_CHECK("umma_conv3x3_patch_kernel");
-      set_last_engine(SOFIE_ENGINE_TCGEN05);
-      return SOFIE_CUDA_OK;
-   };
-   auto by_ksteps = [&](auto bn) -> int {
-      constexpr int kBN = decltype(bn)::value;
-      switch (pl.ksteps) {
-      case 1: return go(umma_conv3x3_patch_kernel<KIND, kBN, 1>);
-      case 2: return go(umma_conv3x3_patch_kernel<KIND, kBN, 2>);
-      case 4: return go(umma_conv3x3_patch_kernel<KIND, kBN, 4>);
-      default: return go(umma_conv3x3_patch_kernel<KIND, kBN, 8>);
-      }
-   };
+   auto kern = umma_conv3x3_patch_kernel<KIND, BN, KPS, G>;
+   SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+   kern<<<grid, kPatchThreads, smem, s>>>(tmX, tmW, ep, tg, pl, status);
+   SOFIE_LAUNCH_CHECK("umma_conv3x3_patch_kernel");
+   set_last_engine(SOFIE_ENGINE_TCGEN05);
+   return SOFIE_CUDA_OK;
+}
+
+// Plane grouping by channel bytes per pixel: the whole patch in one stage while that leaves room for
+// a deep pipeline, otherwise streamed in groups of 4 planes (2 MMAs per tap and stage).
+template <int KIND, int BN>
+static int try_launch_conv_patch_bn(cudaStream_t s, const ConvGeom &g, const void *X, const void *Wp, const ConvEpilogue &ep)
+{
+   constexpr int ES = (KIND == kTF32) ? 4 : 1;
+   constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
+   const int row_bytes = g.C * ES;
+   const long w_all = (long)COPIES * 9 * row_bytes * BN;
+   // whole patch per stage if at least three such stages fit
+   const bool whole = 200 * 1024 - w_all >= 3L * COPIES * (row_bytes / 16) * kPlaneStride;
+   switch (row_bytes) {
+   case 32: return launch_conv_patch<KIND, BN, 1, 1>(s, g, X, Wp, ep);
+   case 64: return launch_conv_patch<KIND, BN, 2, 1>(s, g, X, Wp, ep);
+   case 128: return whole ? launch_conv_patch<KIND, BN, 4, 1>(s, g, X, Wp, ep) : launch_conv_patch<KIND, BN, 2, 2>(s, g, X, Wp, ep);
+   case 256: return whole ? launch_conv_patch<KIND, BN, 8, 1>(s, g, X, Wp, ep) : launch_conv_patch<KIND, BN, 2, 4>(s, g, X, Wp, ep);
+   default: return -1;
+   }
+}
+
+template <int KIND>
+static int try_launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, const void *Wp, const ConvEpilogue &ep, int BN)
+{
+   if (g.H % kPatchTileH != 0 || g.W % kPatchTileW != 0) return -1;
    switch (BN) {
-   case 32: return by_ksteps(std::integral_constant<int, 32>{});
-   case 64: return by_ksteps(std::integral_constant<int, 64>{});
-   default: return by_ksteps(std::integral_constant<int, 128>{});
+   case 32: return try_launch_conv_patch_bn<KIND, 32>(s, g, X, Wp, ep);
+   case 64: return try_launch_conv_patch_bn<KIND, 64>(s, g, X, Wp, ep);
+   default: return try_launch_conv_patch_bn<KIND, 128>(s, g, X, Wp, ep);
    }
 }
 

@@ -201,6 +201,55 @@ def test_qlinear_conv2d_bit_exact(x_nhwc, y_nhwc, packed, pool, x_zp):
     assert len(np.unique(ref)) > 20
 
 
+FIRST_LAYER = [
+    # N, C, H, W, Cout, x_nhwc, y_nhwc, packed, relu, pool, x_zp
+    (5, 1, 64, 64, 32, 0, 1, 1, 1, 2, 0), (3, 3, 32, 32, 16, 0, 1, 1, 1, 0, 0), (2, 1, 20, 36, 12, 0, 0, 0, 1, 2, 7),
+    (2, 4, 17, 33, 64, 1, 1, 1, 0, 0, 128), (3, 2, 34, 18, 20, 1, 0, 0, 1, 2, 0), (1, 3, 8, 8, 5, 0, 1, 0, 0, 2, 3),
+]
+
+
+@pytest.mark.parametrize("case", FIRST_LAYER)
+def test_first_layer_qconv_bit_exact(case):
+    N, C, H, W, Cout, x_nhwc, y_nhwc, packed, relu, pool, x_zp = case
+    rng = np.random.default_rng(sum(case))
+    X = rng.integers(0, 256, (N, C, H, W)).astype(np.uint8)
+    Wt = rng.integers(-127, 128, (Cout, C, 3, 3)).astype(np.int8)
+    ws = rng.uniform(0.001, 0.01, Cout).astype(np.float32)
+    bias = rng.integers(-1000, 1000, Cout).astype(np.int32)
+    y_scale = 0.05 * 0.005 * 128 * 3 * np.sqrt(C)
+    ref = o.qlinear_conv2d(X, 0.05, x_zp, Wt, ws, y_scale, 10, bias=bias, pad=(1, 1), relu=bool(relu))
+    if pool:
+        ref = o.maxpool2d_u8(ref)
+    mult = dev(o.requant_multiplier(0.05, ws, y_scale))
+    Xd = dev(X.transpose(0, 2, 3, 1)) if x_nhwc else dev(X)
+    Wd = ops.qconv2d_pack_i8(dev(Wt)) if packed else dev(Wt)
+    y = ops.qlinear_conv2d(Xd, Wd, mult, dev(bias), shape=X.shape, pad=(1, 1), x_zp=x_zp, y_zp=10, relu=bool(relu), pool=pool,
+                           x_layout=x_nhwc, y_layout=y_nhwc, w_packed=bool(packed), kernel=(3, 3)).cpu().numpy()
+    if y_nhwc:
+        y = y.transpose(0, 3, 1, 2)
+    assert np.array_equal(y, ref)
+    assert len(np.unique(ref)) > 20
+
+
+@pytest.mark.parametrize("case", FIRST_LAYER)
+def test_first_layer_conv_f32(case):
+    N, C, H, W, Cout, x_nhwc, y_nhwc, packed, relu, pool, _ = case
+    rng = np.random.default_rng(sum(case) + 1)
+    X = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    Wt = rng.standard_normal((Cout, C, 3, 3)).astype(np.float32)
+    b = rng.standard_normal(Cout).astype(np.float32)
+    ref = o.conv2d_f32(X, Wt, b, pad=(1, 1), relu=bool(relu))
+    if pool:
+        ref = o.pool2d_f32(ref, 0, (2, 2), (2, 2))
+    Xd = dev(X.transpose(0, 2, 3, 1)) if x_nhwc else dev(X)
+    Wd = ops.conv2d_pack_f32(dev(Wt)) if packed else dev(Wt)
+    y = ops.conv2d_f32(Xd, Wd, dev(b), shape=(N, C, H, W), pad=(1, 1), relu=bool(relu), pool=pool, x_layout=x_nhwc,
+                       y_layout=y_nhwc, w_packed=bool(packed), kernel=(3, 3)).cpu().numpy()
+    if y_nhwc:
+        y = y.transpose(0, 3, 1, 2)
+    assert rel_err(y, ref) <= FP32_TOL
+
+
 def test_maxpool2d_u8():
     X = np.random.default_rng(4).integers(0, 256, (3, 6, 9, 8)).astype(np.uint8)
     assert np.array_equal(ops.maxpool2d_u8(dev(X)).cpu().numpy(), o.maxpool2d_u8(X))

@@ -103,6 +103,8 @@ CONV_TC = [
     # N, C, H, W, Cout, relu, pool
     (4, 16, 32, 32, 32, 1, 2), (6, 32, 16, 16, 64, 1, 2), (5, 64, 8, 8, 128, 1, 0), (5, 64, 8, 8, 128, 0, 2),
     (3, 8, 16, 24, 20, 1, 0), (2, 32, 64, 64, 64, 1, 2), (300, 16, 32, 32, 32, 1, 2), (1, 128, 8, 16, 16, 0, 0),
+    # haloed-patch kernel: channels streamed in plane groups, partial channel chunks, wide tiles
+    (2, 64, 16, 16, 32, 0, 0), (2, 16, 48, 40, 48, 1, 2), (2, 32, 32, 16, 128, 1, 2), (3, 16, 16, 8, 8, 0, 2),
 ]
 
 
@@ -123,7 +125,8 @@ def test_conv3x3_f32_tcgen05(case):
 
 
 @pytest.mark.parametrize("case", [(3, 32, 32, 32, 64, 1, 2), (7, 64, 16, 16, 64, 1, 2), (9, 64, 8, 8, 128, 1, 2), (2, 32, 16, 16, 40, 0, 0),
-                                  (130, 32, 32, 32, 64, 1, 2)])
+                                  (130, 32, 32, 32, 64, 1, 2), (3, 128, 16, 16, 128, 1, 2), (2, 256, 16, 16, 32, 0, 0),
+                                  (2, 128, 32, 16, 64, 1, 0), (5, 32, 16, 16, 24, 1, 2)])
 def test_qlinear_conv3x3_tcgen05_bit_exact(case):
     N, C, H, W, Cout, relu, pool = case
     rng = np.random.default_rng(sum(case))
