@@ -86,6 +86,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
 #define SOFIE_PROF_REPORT(role) do { } while (0)
 #endif
 
+// Next slot of a ring of S pipeline stages and the parity of its barriers, without a division: the
+// roles that walk the ring do so once per stage, on their critical path.
+__device__ __forceinline__ void ring_next(int &slot, uint32_t &phase, int S)
+{
+   if (++slot == S) {
+      slot = 0;
+      phase ^= 1u;
+   }
+}
+
 __device__ __forceinline__ void fence_proxy_async()
 {
    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -45,6 +45,40 @@ constexpr int kConvConverterWarps = 8;                         // fp32 only: war
 constexpr int kConvThreadsI8 = (2 + kConvEpilogueWarps) * 32;
 constexpr int kConvThreadsTF32 = (2 + kConvEpilogueWarps + kConvConverterWarps) * 32;
 
+// Walks the tiles start, start + step, ... of an (image groups x tile rows x tile columns) grid with
+// adds and compares only: the roles call it once per tile on their critical path.
+struct TileWalker {
+   int n, th, tw;    // current tile: image group, tile row, tile column
+   int dn, dth, dtw; // the stride in the same digits
+   int tilesH, tilesW;
+   __device__ __forceinline__ void init(int start, int step, int tiles_h, int tiles_w)
+   {
+      tilesH = tiles_h;
+      tilesW = tiles_w;
+      const int per_image = tiles_h * tiles_w;
+      n = start / per_image;
+      th = (start % per_image) / tiles_w;
+      tw = start % tiles_w;
+      dn = step / per_image;
+      dth = (step % per_image) / tiles_w;
+      dtw = step % tiles_w;
+   }
+   __device__ __forceinline__ void next()
+   {
+      tw += dtw;
+      if (tw >= tilesW) {
+         tw -= tilesW;
+         th++;
+      }
+      th += dth;
+      if (th >= tilesH) {
+         th -= tilesH;
+         n++;
+      }
+      n += dn;
+   }
+};
+
 // The part of the epilogue one warp does for one finished tile: read its 32 TMEM lanes (pixels) for
 // its share of the output channels, add the NACC partial accumulators, apply bias / Relu or the
 // requantisation, reduce 2x2 windows by shuffles when pooling is fused, and store NHWC.
@@ -53,15 +87,15 @@ constexpr int kConvThreadsTF32 = (2 + kConvEpilogueWarps + kConvConverterWarps) 
 template <int KIND, int BN, int NACC, int EPI_WARPS>
 __device__ __forceinline__ void conv_tile_epilogue(const ConvEpilogue &ep, const ConvTiling &tg, const float *s_bias,
                                                    const float *s_mult, const int *s_qbias, bool pool_first, uint32_t tmem_base,
-                                                   int buf, int e, int lane_base, int lane, int n0, int h0, int w0)
+                                                   int buf, int e, int lane_base, int lane, int nn, int hh, int ww, int n0, int h0,
+                                                   int w0)
 {
    constexpr int WPQ = EPI_WARPS / 4;                       // warps per lane quarter
    constexpr int CW = BN / WPQ >= 16 ? BN / WPQ : 16;       // channels per warp
    constexpr int CH = CW >= 32 ? 32 : 16;                   // channels per TMEM read
    const int c_begin = (e >> 2) * CW;
    if (c_begin >= BN) return;
-   const int pix = lane_base + lane; // pixel of the patch = TMEM lane
-   const int ww = pix % tg.tileW, hh = (pix / tg.tileW) % tg.tileH, nn = pix / (tg.tileW * tg.tileH);
+   // (nn, hh, ww) = image, row and column inside the patch of the pixel in this thread's TMEM lane
    const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
    const int n = n0 + nn, h = h0 + hh, w = w0 + ww;
    const bool valid = n < tg.N;
@@ -283,28 +317,20 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
    tc_fence_after();
    const uint32_t tmem_base = tmem_base_holder;
 
-   // tile -> first image, first row, first column of its patch
-   auto tile_origin = [&](int tile, int &n0, int &h0, int &w0) {
-      const int per_image = tg.tilesH * tg.tilesW;
-      const int nb = tile / per_image, rem = tile % per_image;
-      n0 = nb * tg.tileN;
-      h0 = (rem / tg.tilesW) * tg.tileH;
-      w0 = (rem % tg.tilesW) * tg.tileW;
-   };
 
    if (warp == 0) {
       // ---------------- TMA producer ----------------
       // Issuing a tensor copy costs the issuing thread a few hundred cycles, so the 2 x TPS copies of
       // a stage are issued by 2 x TPS lanes in parallel; lane 0 waits for the free slot and posts the
       // expected byte count (the phase cannot complete before that arrive, whatever the order).
-      int g = 0; // stage counter, continuous over the tiles of this CTA
+      int g = 0, s = 0; // stage counter, continuous over the tiles of this CTA, and its ring slot
+      uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
-         int n0, h0, w0;
-         tile_origin(tile, n0, h0, w0);
-         for (int st = 0; st < stages_per_tile; st++, g++) {
-            const int s = g % S;
-            const uint32_t ph = (g / S) & 1;
+      TileWalker tw;
+      tw.init(blockIdx.x, gridDim.x, tg.tilesH, tg.tilesW);
+      for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, tw.next()) {
+         const int n0 = tw.n * tg.tileN, h0 = tw.th * tg.tileH, w0 = tw.tw * tg.tileW;
+         for (int st = 0; st < stages_per_tile; st++, g++, ring_next(s, ph, S)) {
             if (lane == 0) {
                ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
                if (ok) mbar_expect_tx(&full_bar[s], TPS * (A_TILE + B_TILE));
@@ -328,7 +354,8 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
          constexpr uint32_t idesc = make_idesc<KIND>(128, BN);
-         int g = 0, lt = 0;
+         int g = 0, lt = 0, s = 0;
+         uint32_t ph = 0;
          bool ok = true;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, lt++) {
             const int buf = lt & 1;
@@ -336,9 +363,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
             tc_fence_after();
             const uint32_t d_base = tmem_base + (uint32_t)(buf * NACC * BN);
             int mma_idx = 0; // MMAs issued for this tile
-            for (int st = 0; st < stages_per_tile; st++, g++) {
-               const int s = g % S;
-               const uint32_t ph = (g / S) & 1;
+            for (int st = 0; st < stages_per_tile; st++, g++, ring_next(s, ph, S)) {
                ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
                                                     : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
                if (!ok) break;
@@ -376,12 +401,11 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       if constexpr (KIND == kTF32) {
          constexpr int NT = kConvConverterWarps * 32;
          const int t = threadIdx.x - (2 + EPI_WARPS) * 32; // 0..NT-1
-         int g = 0;
+         int g = 0, s = 0;
+      uint32_t ph = 0;
          bool ok = true;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
-            for (int st = 0; st < stages_per_tile; st++, g++) {
-               const int s = g % S;
-               const uint32_t ph = (g / S) & 1;
+            for (int st = 0; st < stages_per_tile; st++, g++, ring_next(s, ph, S)) {
                if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) {
                   ok = false;
                   break;
@@ -422,14 +446,17 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       // quarter split the output channels.
       const int e = warp - 2;
       const int lane_base = (warp & 3) * 32;
+      const int pix = lane_base + lane; // pixel of the patch = TMEM lane
+      const int ww = pix % tg.tileW, hh = (pix / tg.tileW) % tg.tileH, nn = pix / (tg.tileW * tg.tileH);
+      TileWalker tw;
+      tw.init(blockIdx.x, gridDim.x, tg.tilesH, tg.tilesW);
       int lt = 0;
-      for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, lt++) {
+      for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, lt++, tw.next()) {
          const int buf = lt & 1;
-         int n0, h0, w0;
-         tile_origin(tile, n0, h0, w0);
+         const int n0 = tw.n * tg.tileN, h0 = tw.th * tg.tileH, w0 = tw.tw * tg.tileW;
          if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
          tc_fence_after();
-         conv_tile_epilogue<KIND, BN, NACC, EPI_WARPS>(ep, tg, s_bias, s_mult, s_qbias, pool_first, tmem_base, buf, e, lane_base, lane, n0, h0, w0);
+         conv_tile_epilogue<KIND, BN, NACC, EPI_WARPS>(ep, tg, s_bias, s_mult, s_qbias, pool_first, tmem_base, buf, e, lane_base, lane, nn, hh, ww, n0, h0, w0);
          // this warp is done with the TMEM buffer: the MMA warp may overwrite it
          tc_fence_before();
          __syncwarp();
@@ -554,13 +581,6 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
    tc_fence_after();
    const uint32_t tmem_base = tmem_base_holder;
 
-   auto tile_origin = [&](int tile, int &n0, int &h0, int &w0) {
-      const int per_image = tg.tilesH * tg.tilesW;
-      const int rem = tile % per_image;
-      n0 = tile / per_image;
-      h0 = (rem / tg.tilesW) * kPatchTileH;
-      w0 = (rem % tg.tilesW) * kPatchTileW;
-   };
 
    if (warp == 0) {
       // ---------------- TMA producer ----------------
@@ -572,14 +592,14 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          tma_load_2d(w_smem + (size_t)item * COPIES * B_TILE, &tmW, tap * tg.C + ch * (CBK / ES), 0, &w_full);
       }
       // patches: one box per plane, issued by as many lanes
-      int g = 0;
+      int g = 0, s = 0;
+      uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
-         int n0, h0, w0;
-         tile_origin(tile, n0, h0, w0);
-         for (int grp = 0; grp < G; grp++, g++) {
-            const int s = g % S;
-            const uint32_t ph = (g / S) & 1;
+      TileWalker tw;
+      tw.init(blockIdx.x, gridDim.x, tg.tilesH, tg.tilesW);
+      for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, tw.next()) {
+         const int n0 = tw.n * tg.tileN, h0 = tw.th * tg.tileH, w0 = tw.tw * tg.tileW;
+         for (int grp = 0; grp < G; grp++, g++, ring_next(s, ph, S)) {
             if (lane == 0) {
                ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
                if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)PGP * kPlaneBox);
@@ -606,15 +626,14 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          const uint64_t db0 = make_smem_desc(smem_u32(w_smem), CBK);
          const uint32_t b_hi_word = (uint32_t)(db0 >> 32), b_lo_word = (uint32_t)db0;
          const uint32_t lo16 = pl.stage_bytes >> 4; // hi -> lo copy of a slot, in 16-byte units
-         int g = 0, lt = 0;
+         int g = 0, lt = 0, s = 0;
+         uint32_t ph = 0;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, lt++) {
             const int buf = lt & 1;
             if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt))) break;
             const uint32_t d = tmem_base + (uint32_t)(buf * NACC * BN);
 #pragma unroll
-            for (int grp = 0; grp < G; grp++, g++) {
-               const int s = g % S;
-               const uint32_t ph = (g / S) & 1;
+            for (int grp = 0; grp < G; grp++, g++, ring_next(s, ph, S)) {
                ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
                                                     : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
                if (!ok) break;
@@ -680,11 +699,10 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             fence_proxy_async();
             mbar_arrive(&w_conv);
          }
-         int g = 0;
+         int g = 0, s = 0;
+      uint32_t ph = 0;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
-            for (int grp = 0; grp < G; grp++, g++) {
-               const int s = g % S;
-               const uint32_t ph = (g / S) & 1;
+            for (int grp = 0; grp < G; grp++, g++, ring_next(s, ph, S)) {
                if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) {
                   ok = false;
                   break;
@@ -699,14 +717,17 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       // ---------------- epilogue warps, from warp 2 on ----------------
       const int e = warp - 2;
       const int lane_base = (warp & 3) * 32;
+      const int pix = lane_base + lane; // pixel of the patch = TMEM lane
+      const int ww = pix % tg.tileW, hh = (pix / tg.tileW) % tg.tileH, nn = pix / (tg.tileW * tg.tileH);
+      TileWalker tw;
+      tw.init(blockIdx.x, gridDim.x, tg.tilesH, tg.tilesW);
       int lt = 0;
-      for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, lt++) {
+      for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, lt++, tw.next()) {
          const int buf = lt & 1;
-         int n0, h0, w0;
-         tile_origin(tile, n0, h0, w0);
+         const int n0 = tw.n * tg.tileN, h0 = tw.th * tg.tileH, w0 = tw.tw * tg.tileW;
          if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
          tc_fence_after();
-         conv_tile_epilogue<KIND, BN, NACC, EPI_WARPS>(ep, tg, s_bias, s_mult, s_qbias, pool_first, tmem_base, buf, e, lane_base, lane, n0, h0, w0);
+         conv_tile_epilogue<KIND, BN, NACC, EPI_WARPS>(ep, tg, s_bias, s_mult, s_qbias, pool_first, tmem_base, buf, e, lane_base, lane, nn, hh, ww, n0, h0, w0);
          tc_fence_before();
          __syncwarp();
          if (lane == 0) mbar_arrive(&tmem_empty[buf]);

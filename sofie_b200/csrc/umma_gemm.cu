@@ -255,13 +255,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // ---------------- TMA producer ----------------
       // lane 0 waits for the free slot and posts the byte count; lanes 0 and 1 issue the A and the B
       // copy in parallel (issuing a tensor copy costs the issuing thread a few hundred cycles)
-      int g = 0;
+      int g = 0, s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
          const int m0 = (tile / tiles_n) * kBM, n0 = (tile % tiles_n) * BN;
-         for (int kb = 0; kb < num_kb; kb++, g++) {
-            const int s = g % S;
-            const uint32_t ph = (g / S) & 1;
+         for (int kb = 0; kb < num_kb; kb++, g++, ring_next(s, ph, S)) {
             if (lane == 0) {
                ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
                if (ok) mbar_expect_tx(&full_bar[s], L::kATile + L::kBTile);
@@ -277,7 +276,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // ---------------- MMA issuer ----------------
       if (lane == 0) {
          constexpr uint32_t idesc = make_idesc<KIND>(kBM, BN);
-         int g = 0, u = 0;
+         int g = 0, u = 0, s = 0;
+         uint32_t ph = 0;
          bool ok = true;
          for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (int c = 0; c < units_per_tile && ok; c++, u++) {
@@ -289,9 +289,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                tc_fence_after();
                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
                const int kb_end = min(num_kb, (c + 1) * chunk_kb);
-               for (int kb = c * chunk_kb; kb < kb_end; kb++, g++) {
-                  const int s = g % S;
-                  const uint32_t ph = (g / S) & 1;
+               for (int kb = c * chunk_kb; kb < kb_end; kb++, g++, ring_next(s, ph, S)) {
                   ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
                                                        : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
                   if (!ok) break;
@@ -324,12 +322,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if constexpr (KIND == kTF32) {
          constexpr int NT = kGemmConverterWarps * 32;
          const int t = threadIdx.x - (2 + EPI_WARPS) * 32;
-         int g = 0;
+         int g = 0, s = 0;
+      uint32_t ph = 0;
          bool ok = true;
          for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < num_kb; kb++, g++) {
-               const int s = g % S;
-               const uint32_t ph = (g / S) & 1;
+            for (int kb = 0; kb < num_kb; kb++, g++, ring_next(s, ph, S)) {
                if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) {
                   ok = false;
                   break;
