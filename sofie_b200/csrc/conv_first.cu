@@ -18,6 +18,8 @@ namespace {
 
 constexpr int kFirstThreads = 256;  // 16 x 16 outputs per block
 constexpr int kFirstMaxCout = 64;
+constexpr int kFirstF32Threads = 128; // fp32 kernel: 8 x 16 threads, each a 2 x 2 block of outputs
+constexpr int kFirstF32UnitsY = 8;
 
 __device__ __forceinline__ int dp4a_u8s8_first(unsigned a, int b, int c)
 {
@@ -195,56 +197,63 @@ qconv3x3_first_kernel(ConvGeom g, const uint8_t *__restrict__ X, const int8_t *_
 // fp32: a thread owns a 2 x 2 block of convolution outputs (the pooling window when the pool is
 // fused, four stored pixels otherwise) and 16 output channels at a time. The weights are read from
 // shared memory as 16-byte broadcasts; each one feeds four FMAs per output, 16 in all, which keeps
-// the shared-memory pipe off the critical path. A block covers 32 x 32 convolution outputs.
+// the shared-memory pipe off the critical path. A block of 128 threads covers 16 rows x 32 columns of
+// convolution outputs; blocks are kept that small so that four fit on an SM and the load, compute and
+// store phases of different blocks overlap.
 template <int C, int POOL>
-__global__ void __launch_bounds__(kFirstThreads)
+__global__ void __launch_bounds__(kFirstF32Threads, 4)
 conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *__restrict__ Wt, const float *__restrict__ bias,
                          float *__restrict__ Y, long long num_tiles, int tiles_x, int tiles_y)
 {
    constexpr int K = 9 * C;
-   constexpr int TS = 34;
+   constexpr int TSH = 2 * kFirstF32UnitsY + 2, TS = 34; // haloed input tile: 18 rows x 34 columns
    constexpr int OCC = 8;
-   __shared__ float tile[C][TS][TS + 1];
+   __shared__ float tile[C][TSH][TS + 1];
    __shared__ float4 s_w[K][kFirstMaxCout / 4]; // [tap][channel / 4]
    __shared__ float s_bias[kFirstMaxCout];
 
    const int tid = threadIdx.x;
-   // zero the channels past Cout, then fetch only the K x Cout real weights, a few loads in flight per thread
-   for (int i = tid; i < K * kFirstMaxCout; i += kFirstThreads)
-      if (i % kFirstMaxCout >= g.Cout) reinterpret_cast<float *>(&s_w[0][0])[i] = 0.f;
-   const int real = K * g.Cout;
-#pragma unroll 4
-   for (int i = tid; i < real; i += kFirstThreads) {
-      const int k = i / g.Cout, oc = i - k * g.Cout;
-      reinterpret_cast<float *>(&s_w[k][0])[oc] = __ldg(Wt + weight_index(g, oc, k / 9, (k % 9) / 3, k % 3));
-   }
-   for (int oc = tid; oc < kFirstMaxCout; oc += kFirstThreads) s_bias[oc] = (oc < g.Cout && bias) ? __ldg(bias + oc) : 0.f;
-
    const int ty = tid / 16, tx = tid % 16;
+   bool weights_staged = false;
    for (long long tile_id = blockIdx.x; tile_id < num_tiles; tile_id += gridDim.x) {
       int n, uy0, ux0; // origin in units of 2 x 2 outputs
       first_tile_origin(g, tile_id, tiles_x, tiles_y, n, uy0, ux0);
+      uy0 = uy0 / 16 * kFirstF32UnitsY; // this kernel's tiles are 8 units tall
       const int ih0 = uy0 * 2 - 1, iw0 = ux0 * 2 - 1;
       // all loads of a thread are issued before the first store, so their latencies overlap
-      constexpr int kLoads = (C * TS * TS + kFirstThreads - 1) / kFirstThreads;
+      constexpr int kLoads = (C * TSH * TS + kFirstF32Threads - 1) / kFirstF32Threads;
       float staged[kLoads];
 #pragma unroll
       for (int j = 0; j < kLoads; j++) {
-         const int i = tid + j * kFirstThreads;
-         const int c = i / (TS * TS), rem = i % (TS * TS), r = rem / TS, col = rem % TS;
+         const int i = tid + j * kFirstF32Threads;
+         const int c = i / (TSH * TS), rem = i % (TSH * TS), r = rem / TS, col = rem % TS;
          const int ih = ih0 + r, iw = iw0 + col;
          float v = 0.f;
-         if (i < C * TS * TS && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) {
+         if (i < C * TSH * TS && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) {
             const size_t xi = g.x_nhwc ? (((size_t)n * g.H + ih) * g.W + iw) * C + c : (((size_t)n * C + c) * g.H + ih) * g.W + iw;
             v = __ldg(X + xi);
          }
          staged[j] = v;
       }
+      if (!weights_staged) {
+         // The weights are fetched while the loads of the first tile are still in flight.
+         // zero the channels past Cout, then fetch only the K x Cout real weights, a few loads in flight per thread
+         for (int i = tid; i < K * kFirstMaxCout; i += kFirstF32Threads)
+            if (i % kFirstMaxCout >= g.Cout) reinterpret_cast<float *>(&s_w[0][0])[i] = 0.f;
+         const int real = K * g.Cout;
+#pragma unroll 4
+         for (int i = tid; i < real; i += kFirstF32Threads) {
+            const int k = i / g.Cout, oc = i - k * g.Cout;
+            reinterpret_cast<float *>(&s_w[k][0])[oc] = __ldg(Wt + weight_index(g, oc, k / 9, (k % 9) / 3, k % 3));
+         }
+         for (int oc = tid; oc < kFirstMaxCout; oc += kFirstF32Threads) s_bias[oc] = (oc < g.Cout && bias) ? __ldg(bias + oc) : 0.f;
+         weights_staged = true;
+      }
       __syncthreads(); // weights staged / the previous tile is no longer read
 #pragma unroll
       for (int j = 0; j < kLoads; j++) {
-         const int i = tid + j * kFirstThreads;
-         if (i < C * TS * TS) tile[i / (TS * TS)][(i % (TS * TS)) / TS][i % TS] = staged[j];
+         const int i = tid + j * kFirstF32Threads;
+         if (i < C * TSH * TS) tile[i / (TSH * TS)][(i % (TSH * TS)) / TS][i % TS] = staged[j];
       }
       __syncthreads();
       const int oh0 = (uy0 + ty) * 2, ow0 = (ux0 + tx) * 2; // top-left convolution output of this thread
@@ -342,11 +351,11 @@ struct FirstGrid {
 
 // units_x x units_y = extent in the units a thread owns (stored pixels for the uint8 kernel, 2 x 2
 // blocks of convolution outputs for the fp32 one); a block covers 16 x 16 of them.
-FirstGrid first_grid(const ConvGeom &g, int units_x, int units_y, int blocks_per_sm)
+FirstGrid first_grid(const ConvGeom &g, int units_x, int units_y, int tile_units_y, int blocks_per_sm)
 {
    FirstGrid fg;
    fg.tiles_x = ceil_div(units_x, 16);
-   fg.tiles_y = ceil_div(units_y, 16);
+   fg.tiles_y = ceil_div(units_y, tile_units_y);
    fg.num_tiles = (long long)g.N * fg.tiles_x * fg.tiles_y;
    const long long cap = (long long)kNumSMs * blocks_per_sm;
    fg.blocks = (int)(fg.num_tiles < cap ? fg.num_tiles : cap);
@@ -360,7 +369,7 @@ int launch_qconv2d_first(cudaStream_t s, const ConvGeom &g, const uint8_t *X, co
                          int x_zp, int y_zp, uint8_t *Y)
 {
    if (!first_layer_shape(g)) return -1;
-   const FirstGrid fg = first_grid(g, g.pW, g.pH, 8);
+   const FirstGrid fg = first_grid(g, g.pW, g.pH, 16, 8);
    if (fg.num_tiles == 0) return SOFIE_CUDA_OK;
 #define SOFIE_FIRST_Q(CC, PP)                                                                                                   \
    qconv3x3_first_kernel<CC, PP><<<fg.blocks, kFirstThreads, 0, s>>>(g, X, W, mult, bias, x_zp, y_zp, Y, fg.num_tiles, fg.tiles_x, \
@@ -385,10 +394,10 @@ int launch_qconv2d_first(cudaStream_t s, const ConvGeom &g, const uint8_t *X, co
 int launch_conv2d_f32_first(cudaStream_t s, const ConvGeom &g, const float *X, const float *W, const float *bias, float *Y)
 {
    if (!first_layer_shape(g)) return -1;
-   const FirstGrid fg = first_grid(g, (g.oW + 1) / 2, (g.oH + 1) / 2, 2);
+   const FirstGrid fg = first_grid(g, (g.oW + 1) / 2, (g.oH + 1) / 2, kFirstF32UnitsY, 4);
    if (fg.num_tiles == 0) return SOFIE_CUDA_OK;
 #define SOFIE_FIRST_F(CC, PP) \
-   conv3x3_first_f32_kernel<CC, PP><<<fg.blocks, kFirstThreads, 0, s>>>(g, X, W, bias, Y, fg.num_tiles, fg.tiles_x, fg.tiles_y)
+   conv3x3_first_f32_kernel<CC, PP><<<fg.blocks, kFirstF32Threads, 0, s>>>(g, X, W, bias, Y, fg.num_tiles, fg.tiles_x, fg.tiles_y)
    const int pp = g.pool == 2 ? 2 : 1;
    switch (g.C * 10 + pp) {
    case 11: SOFIE_FIRST_F(1, 1); break;
