@@ -238,10 +238,11 @@ __device__ __forceinline__ uint8_t to_e4m3(float x)
    return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
 }
 
+// Scalar forms: the tail of a tensor and unaligned tensors.
 template <typename In>
-__global__ void quantize_e4m3_kernel(const In *__restrict__ X, uint8_t *__restrict__ Y, size_t n, float scale)
+__global__ void quantize_e4m3_kernel(const In *__restrict__ X, uint8_t *__restrict__ Y, size_t begin, size_t n, float scale)
 {
-   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+   for (size_t i = begin + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
       float x;
       if constexpr (sizeof(In) == 2) x = bf16_to_f32(X[i]);
       else x = X[i];
@@ -249,10 +250,57 @@ __global__ void quantize_e4m3_kernel(const In *__restrict__ X, uint8_t *__restri
    }
 }
 
-__global__ void cast_bf16_f32_kernel(const uint16_t *__restrict__ X, float *__restrict__ Y, size_t n)
+// Eight elements per thread and step: 16- or 32-byte loads, one 8-byte store.
+template <typename In>
+__global__ void quantize_e4m3_vec8_kernel(const In *__restrict__ X, uint8_t *__restrict__ Y, size_t n8, float scale)
 {
-   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+   const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+#pragma unroll 2
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += nthreads) {
+      float v[8];
+      if constexpr (sizeof(In) == 2) {
+         const uint4 p = reinterpret_cast<const uint4 *>(X)[i];
+         const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+         for (int j = 0; j < 4; j++) {
+            v[2 * j] = __uint_as_float(w[j] << 16);
+            v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+         }
+      } else {
+         const float4 a = reinterpret_cast<const float4 *>(X)[2 * i], b = reinterpret_cast<const float4 *>(X)[2 * i + 1];
+         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+         v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      }
+      uint32_t out[2];
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+         uint16_t lo, hi;
+         const float d0 = __fdiv_rn(v[4 * h], scale), d1 = __fdiv_rn(v[4 * h + 1], scale);
+         const float d2 = __fdiv_rn(v[4 * h + 2], scale), d3 = __fdiv_rn(v[4 * h + 3], scale);
+         asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(d1), "f"(d0));
+         asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d3), "f"(d2));
+         out[h] = (uint32_t)lo | ((uint32_t)hi << 16);
+      }
+      reinterpret_cast<uint2 *>(Y)[i] = make_uint2(out[0], out[1]);
+   }
+}
+
+__global__ void cast_bf16_f32_kernel(const uint16_t *__restrict__ X, float *__restrict__ Y, size_t begin, size_t n)
+{
+   for (size_t i = begin + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
       Y[i] = bf16_to_f32(X[i]);
+}
+__global__ void cast_bf16_f32_vec8_kernel(const uint16_t *__restrict__ X, float *__restrict__ Y, size_t n8)
+{
+   const size_t nthreads = (size_t)gridDim.x * blockDim.x;
+#pragma unroll 2
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += nthreads) {
+      const uint4 p = reinterpret_cast<const uint4 *>(X)[i];
+      reinterpret_cast<float4 *>(Y)[2 * i] = make_float4(__uint_as_float(p.x << 16), __uint_as_float(p.x & 0xFFFF0000u),
+                                                         __uint_as_float(p.y << 16), __uint_as_float(p.y & 0xFFFF0000u));
+      reinterpret_cast<float4 *>(Y)[2 * i + 1] = make_float4(__uint_as_float(p.z << 16), __uint_as_float(p.z & 0xFFFF0000u),
+                                                             __uint_as_float(p.w << 16), __uint_as_float(p.w & 0xFFFF0000u));
+   }
 }
 __global__ void cast_f32_bf16_kernel(const float *__restrict__ X, uint16_t *__restrict__ Y, size_t n)
 {
@@ -271,6 +319,23 @@ __global__ void amax_f32_kernel(const float *__restrict__ X, size_t n, unsigned 
    }
    for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
    if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+
+template <typename In>
+static int launch_quantize_e4m3(cudaStream_t s, const In *X, uint8_t *Y, size_t n, float scale)
+{
+   size_t done = 0;
+   if (aligned16(X) && (reinterpret_cast<uintptr_t>(Y) & 7) == 0 && n >= 8) {
+      const size_t n8 = n / 8;
+      quantize_e4m3_vec8_kernel<In><<<grid_for(n8), kThreads, 0, s>>>(X, Y, n8, scale);
+      SOFIE_LAUNCH_CHECK("quantize_e4m3_vec8_kernel");
+      done = n8 * 8;
+   }
+   if (done < n) {
+      quantize_e4m3_kernel<In><<<grid_for(n - done), kThreads, 0, s>>>(X, Y, done, n, scale);
+      SOFIE_LAUNCH_CHECK("quantize_e4m3_kernel");
+   }
+   return SOFIE_CUDA_OK;
 }
 
 } // namespace
@@ -403,24 +468,30 @@ int sofie_cuda_quantize_e4m3_f32(void *stream, const float *X, uint8_t *Y, size_
 {
    SOFIE_REQUIRE(X && Y && scale > 0.f, "bad arguments");
    if (n == 0) return SOFIE_CUDA_OK;
-   quantize_e4m3_kernel<float><<<grid_for(n), kThreads, 0, as_stream(stream)>>>(X, Y, n, scale);
-   SOFIE_LAUNCH_CHECK("quantize_e4m3_kernel");
-   return SOFIE_CUDA_OK;
+   return launch_quantize_e4m3<float>(as_stream(stream), X, Y, n, scale);
 }
 int sofie_cuda_quantize_e4m3_bf16(void *stream, const uint16_t *X, uint8_t *Y, size_t n, float scale)
 {
    SOFIE_REQUIRE(X && Y && scale > 0.f, "bad arguments");
    if (n == 0) return SOFIE_CUDA_OK;
-   quantize_e4m3_kernel<uint16_t><<<grid_for(n), kThreads, 0, as_stream(stream)>>>(X, Y, n, scale);
-   SOFIE_LAUNCH_CHECK("quantize_e4m3_kernel");
-   return SOFIE_CUDA_OK;
+   return launch_quantize_e4m3<uint16_t>(as_stream(stream), X, Y, n, scale);
 }
 int sofie_cuda_cast_bf16_f32(void *stream, const uint16_t *X, float *Y, size_t n)
 {
    SOFIE_REQUIRE(X && Y, "NULL tensor");
    if (n == 0) return SOFIE_CUDA_OK;
-   cast_bf16_f32_kernel<<<grid_for(n), kThreads, 0, as_stream(stream)>>>(X, Y, n);
-   SOFIE_LAUNCH_CHECK("cast_bf16_f32_kernel");
+   cudaStream_t s = as_stream(stream);
+   size_t done = 0;
+   if (aligned16(X) && aligned16(Y) && n >= 8) {
+      const size_t n8 = n / 8;
+      cast_bf16_f32_vec8_kernel<<<grid_for(n8), kThreads, 0, s>>>(X, Y, n8);
+      SOFIE_LAUNCH_CHECK("cast_bf16_f32_vec8_kernel");
+      done = n8 * 8;
+   }
+   if (done < n) {
+      cast_bf16_f32_kernel<<<grid_for(n - done), kThreads, 0, s>>>(X, Y, done, n);
+      SOFIE_LAUNCH_CHECK("cast_bf16_f32_kernel");
+   }
    return SOFIE_CUDA_OK;
 }
 int sofie_cuda_cast_f32_bf16(void *stream, const float *X, uint16_t *Y, size_t n)

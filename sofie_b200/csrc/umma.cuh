@@ -169,6 +169,76 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
    }
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster on one TPC run one MMA of 256 rows ---------
+// The leader (cluster rank 0) issues the MMAs; every CTA keeps its 128 rows of A, its half of the
+// rows of B and its 128 lanes of the accumulator. None of the loads below is a multicast load.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+   uint32_t r;
+   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+   return r;
+}
+// Address, in the cluster's shared window, of the same shared-memory location in CTA `rank`.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t cta_addr, uint32_t rank)
+{
+   uint32_t r;
+   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+   return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tensor copy into this CTA's shared memory whose completion bytes are counted on a barrier that may
+// lie in the peer CTA (cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr)
+{
+   asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+                : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t ncols)
+{
+   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+                : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+{
+   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in every CTA of `cta_mask` once all MMAs issued
+// so far by this thread have completed.
+__device__ __forceinline__ void tc_commit_pair(uint64_t *bar, uint16_t cta_mask)
+{
+   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+                "h"(cta_mask)
+                : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+   static_assert(KIND == kI8 || KIND == kF8, "pair MMAs are built for the 8-bit kinds");
+   if constexpr (KIND == kI8) {
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                   "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                   : "memory");
+   } else {
+      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                   "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                   "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                   : "memory");
+   }
+}
+
 // 32 lanes x 32 columns of 32-bit accumulators: thread t of the warp receives lane (base + t),
 // columns [col, col + 32).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])

@@ -11,6 +11,7 @@
 // every fourth 32-column chunk); kTF32 has 4 epilogue warps (2-5) and 8 converter warps (6-13) that split
 // every stage into hi / lo. Two TMEM accumulator buffers overlap epilogue and MMAs.
 #include "umma.cuh"
+#include <cstdlib>
 #include "contract.cuh"
 
 #include <cuda_fp8.h>
@@ -72,7 +73,7 @@ struct GemmEpilogue {
    int y_zp;
    uint8_t *Yu8;
    // kF8
-   float scale, q_scale;
+   float scale, q_scale, q_inv; // q_inv = 1 / q_scale rounded to fp32
    const float *bias;
    uint16_t *Ybf16;
    uint8_t *Yq;
@@ -93,23 +94,58 @@ struct GemmSmem {
    static constexpr int stages(int budget) { return budget / kStageBytes; }
 };
 
-// Epilogue of 32 consecutive columns of one output row: v[j] is the raw accumulator of column
-// col0 + j (fp32 bits, or int32 for kI8). Vector stores when the row chunk is full and aligned.
+// x / scale for a value that is rounded to E4M3 next. The stored byte must be the one the correctly
+// rounded fp32 quotient gives. x * (1 / scale) is within two units in the last place of that
+// quotient, and the two can only round to different E4M3 values when they lie on different sides of
+// (or on) a rounding boundary of E4M3; every such boundary, in the normal and the subnormal range,
+// is an fp32 number whose low 19 mantissa bits are zero. So the product is used unless its low 19
+// bits are within a few units of zero (about one value in 10^5), where the real division runs.
+__device__ __forceinline__ float div_for_e4m3(float x, float scale, float inv_scale)
+{
+   const float q = __fmul_rn(x, inv_scale);
+   if (((__float_as_uint(q) + 4u) & 0x7FFFFu) < 9u) return __fdiv_rn(x, scale);
+   return q;
+}
+
+// Epilogue of 32 consecutive columns of one output row: r[j] is the raw accumulator of column
+// col0 + j (fp32 bits, or int32 for kI8). The per-column constants (bias, multiplier, correction) are
+// fetched once per chunk, one column per lane, and handed round through `cf`, 64 floats of shared
+// memory private to the calling warp, so the loop reads them as 16-byte broadcasts instead of one
+// global load per output. Vector stores when the row chunk is full and aligned. `row_ok` is false
+// for the rows past M (their lanes still take part in the hand-over).
 template <int KIND>
-__device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const uint32_t (&r)[32], int row, int col0, int N)
+__device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const uint32_t (&r)[32], int row, bool row_ok, int col0, int N,
+                                                float *cf, int lane)
 {
    const int ncols = min(32, N - col0);
+   const bool col_ok = lane < ncols;
+   __syncwarp(); // the previous chunk's constants are no longer read
+   if constexpr (KIND == kTF32) {
+      cf[lane] = (col_ok && ep.bias_kind == 1) ? ep.C[col0 + lane] : 0.f;
+   } else if constexpr (KIND == kI8) {
+      cf[lane] = col_ok ? ep.mult[col0 + lane] : 0.f;
+      cf[32 + lane] = __int_as_float((col_ok && ep.corr) ? ep.corr[col0 + lane] : 0);
+   } else {
+      cf[lane] = (col_ok && ep.bias) ? ep.bias[col0 + lane] : 0.f;
+   }
+   __syncwarp();
+   if (!row_ok) return;
+   const float4 *cf4 = reinterpret_cast<const float4 *>(cf);
    if constexpr (KIND == kTF32) {
       float *y = ep.Yf + (size_t)row * N + col0;
       float v[32];
 #pragma unroll
-      for (int j = 0; j < 32; j++) {
-         float acc = ep.alpha * __uint_as_float(r[j]);
-         if (j < ncols) {
-            if (ep.bias_kind == 1) acc += ep.beta * ep.C[col0 + j];
-            else if (ep.bias_kind == 2) acc += ep.beta * ep.C[(size_t)row * N + col0 + j];
+      for (int j4 = 0; j4 < 8; j4++) {
+         const float4 c = cf4[j4];
+         const float cc[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+         for (int t = 0; t < 4; t++) {
+            const int j = 4 * j4 + t;
+            float acc = ep.alpha * __uint_as_float(r[j]);
+            if (ep.bias_kind == 1) acc += ep.beta * cc[t];
+            else if (ep.bias_kind == 2 && j < ncols) acc += ep.beta * ep.C[(size_t)row * N + col0 + j];
+            v[j] = ep.relu ? relu_ref(acc) : acc;
          }
-         v[j] = ep.relu ? relu_ref(acc) : acc;
       }
       if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
 #pragma unroll
@@ -122,14 +158,13 @@ __device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const ui
       uint8_t *y = ep.Yu8 + (size_t)row * N + col0;
       uint32_t packed[8];
 #pragma unroll
-      for (int j = 0; j < 32; j++) {
-         int q = 0;
-         if (j < ncols) {
-            int acc = (int)r[j] + (ep.corr ? ep.corr[col0 + j] : 0);
-            q = requant_u8(acc, ep.mult[col0 + j], ep.y_zp, ep.relu);
-         }
-         if ((j & 3) == 0) packed[j >> 2] = 0;
-         packed[j >> 2] |= (uint32_t)q << (8 * (j & 3));
+      for (int j4 = 0; j4 < 8; j4++) {
+         const float4 m = cf4[j4], c = cf4[8 + j4];
+         const int q0 = requant_u8((int)r[4 * j4 + 0] + __float_as_int(c.x), m.x, ep.y_zp, ep.relu);
+         const int q1 = requant_u8((int)r[4 * j4 + 1] + __float_as_int(c.y), m.y, ep.y_zp, ep.relu);
+         const int q2 = requant_u8((int)r[4 * j4 + 2] + __float_as_int(c.z), m.z, ep.y_zp, ep.relu);
+         const int q3 = requant_u8((int)r[4 * j4 + 3] + __float_as_int(c.w), m.w, ep.y_zp, ep.relu);
+         packed[j4] = (uint32_t)q0 | ((uint32_t)q1 << 8) | ((uint32_t)q2 << 16) | ((uint32_t)q3 << 24);
       }
       if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
          *reinterpret_cast<uint4 *>(y) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -139,23 +174,33 @@ __device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const ui
          for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
       }
    } else {
+      // y = acc * scale (+ bias) (Relu) -> bf16 (round to nearest even) -> optional E4M3 of bf16(y) / q_scale.
+      // Both conversions use the paired hardware instructions (two values per instruction).
       uint32_t hb[16], qb[8];
 #pragma unroll
-      for (int j = 0; j < 32; j++) {
-         uint16_t h = 0;
-         uint8_t q = 0;
-         if (j < ncols) {
-            float y = __fmul_rn(__uint_as_float(r[j]), ep.scale);
-            if (ep.bias) y = __fadd_rn(y, ep.bias[col0 + j]);
-            if (ep.relu) y = relu_ref(y);
-            h = f32_to_bf16_rne(y);
-            if (ep.Yq)
-               q = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(bf16_to_f32(h), ep.q_scale), __NV_SATFINITE, __NV_E4M3);
+      for (int j4 = 0; j4 < 8; j4++) {
+         const float4 c = cf4[j4];
+         const float cc[4] = {c.x, c.y, c.z, c.w};
+         float yv[4];
+#pragma unroll
+         for (int t = 0; t < 4; t++) {
+            float y = __fmul_rn(__uint_as_float(r[4 * j4 + t]), ep.scale);
+            if (ep.bias) y = __fadd_rn(y, cc[t]);
+            yv[t] = ep.relu ? relu_ref(y) : y;
          }
-         if ((j & 1) == 0) hb[j >> 1] = 0;
-         hb[j >> 1] |= (uint32_t)h << (16 * (j & 1));
-         if ((j & 3) == 0) qb[j >> 2] = 0;
-         qb[j >> 2] |= (uint32_t)q << (8 * (j & 3));
+         // cvt packs {hi, lo}: the first source lands in the upper half
+         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hb[2 * j4]) : "f"(yv[1]), "f"(yv[0]));
+         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hb[2 * j4 + 1]) : "f"(yv[3]), "f"(yv[2]));
+         if (ep.Yq) {
+            const float d0 = div_for_e4m3(__uint_as_float(hb[2 * j4] << 16), ep.q_scale, ep.q_inv);
+            const float d1 = div_for_e4m3(__uint_as_float(hb[2 * j4] & 0xFFFF0000u), ep.q_scale, ep.q_inv);
+            const float d2 = div_for_e4m3(__uint_as_float(hb[2 * j4 + 1] << 16), ep.q_scale, ep.q_inv);
+            const float d3 = div_for_e4m3(__uint_as_float(hb[2 * j4 + 1] & 0xFFFF0000u), ep.q_scale, ep.q_inv);
+            uint16_t lo, hi;
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(d1), "f"(d0));
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d3), "f"(d2));
+            qb[j4] = (uint32_t)lo | ((uint32_t)hi << 16);
+         }
       }
       if (ep.Ybf16) {
          uint16_t *y = ep.Ybf16 + (size_t)row * N + col0;
@@ -213,6 +258,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
    __shared__ uint64_t full_bar[kGemmMaxStages], conv_bar[kGemmMaxStages], empty_bar[kGemmMaxStages], tmem_full[2], tmem_empty[2];
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
+   __shared__ __align__(16) float s_cf[18][64]; // per-warp hand-over of the per-column epilogue constants
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    SOFIE_PROF_DECL
@@ -397,14 +443,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                __syncwarp();
                if (lane == 0) mbar_arrive(&tmem_empty[buf]);
             }
-            if (ok && row < M) {
+            if (ok) {
 #pragma unroll
                for (int c0 = 0; c0 < BN; c0 += 32) {
                   if (n0 + c0 < N) {
                      uint32_t r[32];
 #pragma unroll
                      for (int j = 0; j < 32; j++) r[j] = __float_as_uint(acc[c0 + j]);
-                     store_row_chunk<KIND>(ep, r, row, n0 + c0, N);
+                     store_row_chunk<KIND>(ep, r, row, row < M, n0 + c0, N, s_cf[warp], lane);
                   }
                }
             }
@@ -418,7 +464,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                uint32_t r[32];
                tmem_ld_32x32(t_row + (uint32_t)(buf * BN + c0), r);
                tmem_ld_wait();
-               if (row < M) store_row_chunk<KIND>(ep, r, row, n0 + c0, N);
+               store_row_chunk<KIND>(ep, r, row, row < M, n0 + c0, N, s_cf[warp], lane);
             }
             tc_fence_before();
             __syncwarp();
@@ -437,6 +483,184 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       tmem_dealloc(tmem_base, TMEM_COLS);
    }
+}
+
+// ================================================================================================
+// Pair kernel for the 8-bit kinds: a cluster of two CTAs (one TPC) computes a 256 x 256 output tile
+// with `tcgen05.mma.cta_group::2`. CTA r of the pair keeps rows [128 r, 128 r + 128) of the A tile,
+// rows [128 r, 128 r + 128) of the B tile and the same rows of the accumulator in its own TMEM, so a
+// stage is 32 KB per CTA for 4 MMAs of 128 clocks each: 64 bytes per clock and SM, where the 128 x 256
+// single-CTA tile needs 96 and the copy engine delivers about 48. No load is a multicast load.
+//   Protocol (leader = cluster rank 0; every barrier exists in both CTAs):
+//   full[s]      leader's only: 1 arrival (its producer, with the byte count of BOTH CTAs' copies);
+//                both producers' copies complete on it (the peer's through the cluster address).
+//   empty[s]     each CTA's own: the leader's commit arrives on both (multicast of the commit).
+//   tmem_full[b] each CTA's own: committed on both after the last stage of a tile.
+//   tmem_empty[b] leader's only: 2 x 16 arrivals, one per epilogue warp of either CTA.
+// The CTAs meet at a cluster barrier after initialising their barriers and before releasing TMEM,
+// which every thread reaches (a wait that gives up only leaves its loop).
+constexpr int kPairBN = 256;      // columns of the pair's tile
+constexpr int kPairStages = 6;    // 6 x 32 KB per CTA
+constexpr int kPairStageBytes = 2 * kBM * kStageK;
+
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((2 + kGemmEpilogueWarps8) * 32, 1)
+umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmEpilogue ep,
+                      int M, int N, int K, uint32_t *status)
+{
+   constexpr int S = kPairStages;
+   constexpr uint32_t TMEM_COLS = 2 * kPairBN;
+   constexpr int EPI_WARPS = kGemmEpilogueWarps8;
+   extern __shared__ unsigned char smem_raw[];
+   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+   __shared__ uint64_t full_bar[S], empty_bar[S], tmem_full[2], tmem_empty[2];
+   __shared__ uint32_t tmem_base_holder;
+   __shared__ volatile uint32_t abort_flag;
+   __shared__ __align__(16) float s_cf[18][64]; // per-warp hand-over of the per-column epilogue constants
+
+   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+   SOFIE_PROF_DECL
+   const uint32_t rank = cluster_ctarank();
+   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+   const int tiles_n = (N + kPairBN - 1) / kPairBN, tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
+   const int num_tiles = tiles_m * tiles_n;
+   const int num_kb = (K + kStageK - 1) / kStageK;
+
+   auto a_tile = [&](int s) { return smem + (size_t)s * kPairStageBytes; };
+   auto b_tile = [&](int s) { return smem + (size_t)s * kPairStageBytes + kBM * kStageK; };
+
+   if (threadIdx.x == 0) {
+      for (int s = 0; s < S; s++) {
+         mbar_init(&full_bar[s], 1);
+         mbar_init(&empty_bar[s], 1);
+      }
+      for (int b = 0; b < 2; b++) {
+         mbar_init(&tmem_full[b], 1);
+         mbar_init(&tmem_empty[b], 2 * EPI_WARPS);
+      }
+      abort_flag = 0;
+      fence_mbar_init();
+      prefetch_tensormap(&tmA);
+      prefetch_tensormap(&tmB);
+   }
+   if (warp == 1) {
+      tmem_alloc_pair(&tmem_base_holder, TMEM_COLS);
+      tmem_relinquish_pair();
+   }
+   tc_fence_before();
+   __syncthreads();
+   cluster_sync_all(); // the peer's barriers exist before anything arrives on them
+   tc_fence_after();
+   const uint32_t tmem_base = tmem_base_holder;
+
+   if (warp == 0) {
+      // ---------------- TMA producer (both CTAs) ----------------
+      int g = 0, s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+         const int m0 = (tile / tiles_n) * (2 * kBM) + (int)rank * kBM;
+         const int n0 = (tile % tiles_n) * kPairBN + (int)rank * kBM;
+         for (int kb = 0; kb < num_kb; kb++, g++, ring_next(s, ph, S)) {
+            if (lane == 0) {
+               ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
+               if (ok && rank == 0) mbar_expect_tx(&full_bar[s], 2 * kPairStageBytes);
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) break;
+            const uint32_t full_leader = mapa_shared(smem_u32(&full_bar[s]), 0);
+            if (lane == 0) tma_load_2d_pair(a_tile(s), &tmA, kb * kStageK, m0, full_leader);
+            else if (lane == 1) tma_load_2d_pair(b_tile(s), &tmB, kb * kStageK, n0, full_leader);
+            __syncwarp();
+         }
+      }
+   } else if (warp == 1) {
+      // ---------------- MMA issuer (leader CTA only) ----------------
+      if (lane == 0 && rank == 0) {
+         constexpr uint32_t idesc = make_idesc<KIND>(2 * kBM, kPairBN);
+         int g = 0, u = 0, s = 0;
+         uint32_t ph = 0;
+         bool ok = true;
+         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, u++) {
+            const int buf = u & 1;
+            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((u >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x1000 + u))) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kPairBN);
+            for (int kb = 0; kb < num_kb; kb++, g++, ring_next(s, ph, S)) {
+               ok = SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
+               if (!ok) break;
+               tc_fence_after();
+               const uint64_t da = make_smem_desc(smem_u32(a_tile(s)), kStageK);
+               const uint64_t db = make_smem_desc(smem_u32(b_tile(s)), kStageK);
+#pragma unroll
+               for (int k = 0; k < kStageK / kMmaK; k++) {
+                  const uint64_t koff = (uint64_t)(k * (kMmaK >> 4));
+                  tc_mma_pair<KIND>(d_tmem, da + koff, db + koff, idesc, (kb == 0 && k == 0) ? 0u : 1u);
+               }
+               tc_commit_pair(&empty_bar[s], 3); // both CTAs' slots are free once these MMAs have read them
+            }
+            if (ok) tc_commit_pair(&tmem_full[buf], 3);
+         }
+      }
+   } else {
+      // ---------------- epilogue warps 2..17 (both CTAs) ----------------
+      const int lane_base = (warp & 3) * 32;
+      const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16);
+      constexpr int GROUPS = EPI_WARPS / 4;
+      const int group = (warp - 2) >> 2;
+      int u = 0;
+      for (int tile = pair; tile < num_tiles; tile += num_pairs, u++) {
+         const int m0 = (tile / tiles_n) * (2 * kBM) + (int)rank * kBM, n0 = (tile % tiles_n) * kPairBN;
+         const int row = m0 + lane_base + lane;
+         const int buf = u & 1;
+         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (u >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + u))) break;
+         tc_fence_after();
+#pragma unroll 1
+         for (int c0 = group * 32; c0 < kPairBN; c0 += GROUPS * 32) {
+            if (n0 + c0 >= N) break;
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + (uint32_t)(buf * kPairBN + c0), r);
+            tmem_ld_wait();
+            store_row_chunk<KIND>(ep, r, row, row < M, n0 + c0, N, s_cf[warp], lane);
+         }
+         tc_fence_before();
+         __syncwarp();
+         if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[buf]), 0));
+      }
+   }
+   SOFIE_PROF_REPORT(warp == 0 ? "producer" : (warp == 1 ? "mma" : "epilogue"));
+   // Nothing of this CTA may be released while the peer can still touch it (the leader's MMAs write
+   // the peer's TMEM and its commits arrive on the peer's barriers).
+   tc_fence_before();
+   __syncthreads();
+   cluster_sync_all();
+   if (warp == 1) {
+      tc_fence_after();
+      tmem_dealloc_pair(tmem_base, TMEM_COLS);
+   }
+}
+
+template <int KIND>
+static int launch_pair(cudaStream_t s, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmEpilogue &ep, int M, int N, int K)
+{
+   const int smem = kPairStages * kPairStageBytes + 1024;
+   auto kern = umma_gemm_pair_kernel<KIND>;
+   SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+   uint32_t *status = device_status_word();
+   if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
+   const int tiles = ceil_div(N, kPairBN) * ceil_div(M, 2 * kBM);
+   const int pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
+   kern<<<2 * pairs, (2 + kGemmEpilogueWarps8) * 32, smem, s>>>(tmA, tmB, ep, M, N, K, status);
+   SOFIE_LAUNCH_CHECK("umma_gemm_pair_kernel");
+   set_last_engine(SOFIE_ENGINE_TCGEN05);
+   return SOFIE_CUDA_OK;
+}
+
+// SOFIE_CUDA_GEMM_PAIR=0 keeps every shape on the single-CTA kernel (used to compare the two).
+static bool pair_enabled()
+{
+   static const bool v = [] { const char *e = getenv("SOFIE_CUDA_GEMM_PAIR"); return !e || atoi(e) != 0; }();
+   return v;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -478,6 +702,16 @@ static int launch_umma_gemm(cudaStream_t s, const void *A, const void *B, const 
    if (rc) return rc;
    rc = make_tensor_map(&tmB, dt, 2, B, dimsB, stride, boxB, 128);
    if (rc) return rc;
+   if constexpr (KIND != kTF32) {
+      // wide outputs with enough 256 x 256 tiles for every pair of SMs
+      if (pair_enabled() && N >= 256 && ceil_div(N, kPairBN) * ceil_div(M, 2 * kBM) >= kNumSMs / 2) {
+         CUtensorMap tmBh;
+         uint32_t boxBh[2] = {(uint32_t)kStageK, (uint32_t)kBM};
+         rc = make_tensor_map(&tmBh, dt, 2, B, dimsB, stride, boxBh, 128);
+         if (rc) return rc;
+         return launch_pair<KIND>(s, tmA, tmBh, ep, M, N, K);
+      }
+   }
    if constexpr (KIND == kTF32) {
       if (BN == 32) return launch_one<KIND, 32>(s, tmA, tmB, ep, M, N, K);
       return launch_one<KIND, 64>(s, tmA, tmB, ep, M, N, K);
@@ -528,6 +762,7 @@ int launch_gemm_e4m3_umma(cudaStream_t s, const sofie_fp8_gemm_desc &d, const ui
    umma::GemmEpilogue ep = {};
    ep.scale = d.a_scale * d.w_scale;
    ep.q_scale = d.q_scale;
+   ep.q_inv = d.q_scale != 0.f ? (float)(1.0 / (double)d.q_scale) : 0.f;
    ep.bias = bias;
    ep.Ybf16 = Ybf16;
    ep.Yq = Yq;

@@ -98,6 +98,38 @@ def test_tensor_core_and_cuda_core_kernels_agree():
     assert rel_err(y_tc, y_cc) <= 1e-5
 
 
+# Shapes with at least 74 tiles of 256 x 256 run on CTA pairs (cta_group::2); ragged M and N included.
+@pytest.mark.parametrize("M,N,K,relu,zp", [(4900, 1000, 256, 1, 128), (2048 * 5, 512, 384, 0, 7)])
+def test_qlinear_matmul_pair_kernel_bit_exact(M, N, K, relu, zp):
+    rng = np.random.default_rng(M + N + K)
+    A = rng.integers(0, 256, (M, K)).astype(np.uint8)
+    W = rng.integers(-127, 128, (N, K)).astype(np.int8)
+    ws = rng.uniform(0.001, 0.01, N).astype(np.float32)
+    y_scale = 0.02 * np.sqrt(K) * 0.3
+    ref = o.qlinear_matmul(A, 0.02, zp, W, ws, y_scale, 128, w_is_nk=True, relu=bool(relu))
+    mult, corr = ops.qlinear_prepare(W, True, 0.02, zp, ws, y_scale, None, "cuda")
+    for _ in range(2):  # a second launch reuses the barriers' initial state and TMEM
+        y = ops.qlinear_matmul(dev(A), dev(W), mult, corr, w_is_nk=True, y_zp=128, relu=bool(relu)).cpu().numpy()
+        assert ops.last_engine() == capi.ENGINE_TCGEN05
+        assert np.array_equal(y, ref)
+    assert len(np.unique(ref)) > 20
+
+
+def test_gemm_e4m3_pair_kernel():
+    M, N, K = 4864, 1024, 512
+    rng = np.random.default_rng(3)
+    X = rng.standard_normal((M, K)).astype(np.float32)
+    Wf = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float32)
+    sa, sw = float(np.abs(X).max() / 448), float(np.abs(Wf).max() / 448)
+    Aq, Wq = o.quantize_e4m3(X, sa), o.quantize_e4m3(Wf, sw)
+    ref = o.bf16_bits_to_f32(o.gemm_e4m3(Aq, sa, Wq, sw, bias, relu=True))
+    Y, Yq = ops.gemm_e4m3(dev(Aq), dev(Wq), dev(bias), a_scale=sa, w_scale=sw, relu=True, q_scale=0.01)
+    y = Y.float().cpu().numpy()
+    assert rel_err(y, ref) <= 8e-3
+    assert np.array_equal(Yq.cpu().numpy(), o.quantize_e4m3(y, 0.01))
+
+
 # ------------------------------------------------------------------------------------ implicit-GEMM convolution
 CONV_TC = [
     # N, C, H, W, Cout, relu, pool
