@@ -55,58 +55,74 @@ def tensor_peak_tflops(workload, pk):
 
 
 class ClockSampler:
-    """nvidia-smi polled every 20 ms for the whole run; stop() keeps the samples that fall inside the
-    timed windows (device-timed steps and end-to-end steps)."""
-    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of this rank's GPU, read through NVML every 5 ms by a thread for the
+    whole run (reading only; nothing is set). stop() keeps the samples that fall inside the timed windows
+    (device-timed steps and end-to-end steps). A timed region shorter than a few samples is followed by
+    `load()` -- the same step replayed for a fraction of a second, outside any timing -- so that the
+    clock under this load is still on record."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, gpu_index):
-        self.proc = None
-        self.windows = []
+        import threading
+        self.windows, self.rows, self.err = [], [], None
+        self._stop = threading.Event()
+        self.handle = None
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            pass
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(gpu_index).uuid)
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            self.nv = pynvml
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+        except Exception as e:  # no NVML: the line says so instead of inventing a clock
+            self.err = f"NVML unavailable: {type(e).__name__}"
+
+    def _poll(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                clk = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.rows.append((time.time(), clk, mask))
+            except Exception as e:
+                self.err = f"NVML read failed: {type(e).__name__}"
+                return
+            time.sleep(0.005)
 
     def window(self, t0, t1):
         self.windows.append((t0, t1))
 
-    def stop(self):
-        import datetime
-        if not self.proc:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        time.sleep(0.05)
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        rows = []
-        for line in out.splitlines():
-            f = [c.strip() for c in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
-                rows.append((ts, float(f[1]), float(f[2]), f[5:9]))
-            except ValueError:
-                continue
-        inside = [r for r in rows if any(t0 - 0.02 <= r[0] <= t1 + 0.02 for t0, t1 in self.windows)]
-        scope = "timed windows"
-        if not inside:  # the timed region was shorter than one sampling period: use the run under load
-            lo = min((t0 for t0, _ in self.windows), default=0) - 1.0
-            inside, scope = [r for r in rows if r[0] >= lo], "whole measurement phase (timed region shorter than one sample)"
-        reasons = set()
-        for r in inside:
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return dict(sm_mhz=float(np.median([r[1] for r in inside])) if inside else None,
-                    sm_max_mhz=max((r[2] for r in inside), default=None), reasons=sorted(reasons), samples=len(inside), scope=scope)
+    def samples_in_windows(self):
+        return [r for r in self.rows if any(t0 <= r[0] <= t1 for t0, t1 in self.windows)]
+
+    def load(self, step_fn, seconds=0.4):
+        """Replays the step for `seconds` (untimed) when the timed windows hold fewer than 3 samples."""
+        if self.handle is None or len(self.samples_in_windows()) >= 3:
+            return False
+        import torch
+        t0 = time.time()
+        while time.time() - t0 < seconds:
+            for _ in range(50):
+                step_fn()
+            torch.cuda.synchronize()
+        self.windows = [(t0, time.time())]
+        return True
+
+    def stop(self, scope="timed windows"):
+        if self.handle is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=[self.err or "NVML unavailable"], samples=0, scope=scope)
+        self._stop.set()
+        self.thread.join(timeout=1.0)
+        inside = self.samples_in_windows()
+        reasons = sorted({name for r in inside for name, bit in self.REASONS if r[2] & bit})
+        return dict(sm_mhz=float(np.median([r[1] for r in inside])) if inside else None, sm_max_mhz=self.sm_max,
+                    reasons=reasons, samples=len(inside), scope=scope)
 
 
 # DRAM traffic per launch of the dominant kernels, from ncu captures (profiles/): bytes read + written.
@@ -333,7 +349,9 @@ def main():
     if args.layer_times:
         # every step of the plan timed alone (cold L2), to see where a step's time goes
         layer_ms = {st.name: round(device_time_ms(st.fn, 5), 5) for st in sess.steps}
-    clk = clocks.stop()
+    extended = clocks.load(sess.replay)
+    clk = clocks.stop("timed windows" if not extended else
+                      "0.4 s of replays of the same step right after the timed region (it was shorter than three samples)")
 
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:

@@ -692,7 +692,9 @@ static int launch_umma_gemm(cudaStream_t s, const void *A, const void *B, const 
    if (((size_t)K * ES) % 16 != 0 || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
       return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "TMA needs 16-byte aligned rows (K*%d %% 16 == 0) and bases", ES);
    // fp32 keeps the tile's running sum in registers (promotion), which bounds its width at 64 columns
-   const int BN = N <= 32 ? 32 : ((N <= 64 || KIND == kTF32) ? 64 : (N <= 128 ? 128 : 256));
+   int BN = N <= 32 ? 32 : ((N <= 64 || KIND == kTF32) ? 64 : (N <= 128 ? 128 : 256));
+   // wide tiles are the efficient ones, but not when they leave most SMs without a tile
+   while (BN > 64 && (long long)ceil_div(M, kBM) * ceil_div(N, BN) < (kNumSMs * 4) / 5) BN /= 2;
    CUtensorMap tmA, tmB;
    const CUtensorMapDataType dt = (KIND == kTF32) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
    uint64_t dimsA[2] = {(uint64_t)K, (uint64_t)M}, dimsB[2] = {(uint64_t)K, (uint64_t)N};
