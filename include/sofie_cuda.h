@@ -195,6 +195,48 @@ int sofie_cuda_pool2d_f32(void *stream, const sofie_pool2d_desc *desc, const flo
  * (reference: ROperator_Softmax.hxx:53-184). */
 int sofie_cuda_softmax_f32(void *stream, const float *X, float *Y, size_t outer, size_t axis_len, size_t inner);
 
+/* Unary operators, y[i] = f(x[i]). The formulas are the ones the reference emits
+ * (ROperator_Sigmoid.hxx:59, ROperator_Tanh.hxx:60, ROperator_LeakyRelu.hxx:73, ROperator_Selu.hxx:59,
+ * ROperator_Elu.hxx:71 -- including its `alpha * exp(x) - 1` for x < 0 --, ROperator_BasicUnary.hxx).
+ * alpha is read by LEAKY_RELU and ELU only. */
+enum {
+   SOFIE_UNARY_SIGMOID = 0,
+   SOFIE_UNARY_TANH = 1,
+   SOFIE_UNARY_LEAKY_RELU = 2,
+   SOFIE_UNARY_SELU = 3,
+   SOFIE_UNARY_ELU = 4,
+   SOFIE_UNARY_NEG = 5,
+   SOFIE_UNARY_EXP = 6,
+   SOFIE_UNARY_LOG = 7,
+   SOFIE_UNARY_SQRT = 8,
+   SOFIE_UNARY_RECIPROCAL = 9,
+   SOFIE_UNARY_ABS = 10
+};
+int sofie_cuda_unary_f32(void *stream, int32_t op, float alpha, const float *X, float *Y, size_t n);
+
+/* Binary operators with multidirectional broadcasting (reference: ROperator_BasicBinary.hxx:18-43,
+ * 176-230). The output has `shape` (rank 4, leading 1s for lower ranks); an operand's stride, in
+ * elements, is 0 along a dimension it is broadcast over. */
+enum { SOFIE_BINARY_ADD = 0, SOFIE_BINARY_SUB = 1, SOFIE_BINARY_MUL = 2, SOFIE_BINARY_DIV = 3 };
+typedef struct sofie_binary_desc {
+   int32_t op;
+   int64_t shape[4];
+   int64_t a_stride[4], b_stride[4];
+} sofie_binary_desc;
+int sofie_cuda_binary_f32(void *stream, const sofie_binary_desc *desc, const float *A, const float *B, float *Y);
+
+/* Inference-mode BatchNormalization on [N, C, HW] (NCHW) or [N, HW, C] (NHWC):
+ * y = ((x - mean[c]) * scale[c]) + bias[c], optional Relu; `scale` already holds
+ * gamma / sqrt(var + epsilon), which the reference folds at Initialize time
+ * (ROperator_BatchNormalization.hxx:163-168, 200-226). */
+typedef struct sofie_batchnorm_desc {
+   int32_t N, C, HW;
+   int32_t layout;          /* SOFIE_LAYOUT_* of X and Y */
+   int32_t relu;
+} sofie_batchnorm_desc;
+int sofie_cuda_batchnorm_f32(void *stream, const sofie_batchnorm_desc *desc, const float *X, const float *scale, const float *bias,
+                             const float *mean, float *Y);
+
 /* NCHW <-> NHWC copies for tensors that cross a layout boundary un-fused. */
 int sofie_cuda_nchw_to_nhwc_f32(void *stream, const float *X, float *Y, int32_t N, int32_t C, int32_t H, int32_t W);
 int sofie_cuda_nhwc_to_nchw_f32(void *stream, const float *X, float *Y, int32_t N, int32_t C, int32_t H, int32_t W);

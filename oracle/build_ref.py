@@ -80,6 +80,13 @@ def all_cases():
     m, x = configs.cnn_f32(batch=4)
     m.name = "ref_c2_b4"
     cases["ref_c2_b4"] = (m, x)
+    # residual block with BatchNormalization and the activation family
+    m, x = configs.resblock_f32()
+    m.name = "ref_resblock"
+    cases["ref_resblock"] = (m, x)
+    m, x = configs.mlp_activations_f32()
+    m.name = "ref_mlp_act"
+    cases["ref_mlp_act"] = (m, x)
     return cases
 
 
@@ -108,6 +115,13 @@ def description(m) -> tuple[str, np.ndarray]:
             lines.append(f"flatten {L.get('axis', 1)} {L['X']} {L['Y']}")
         elif op == "Softmax":
             lines.append(f"softmax {L.get('axis', -1)} {L['X']} {L['Y']}")
+        elif op in ("Sigmoid", "Tanh", "LeakyRelu", "Selu", "Elu"):
+            lines.append(f"unary {op} {L.get('alpha', 0.01 if op == 'LeakyRelu' else 1.0)} {L['X']} {L['Y']}")
+        elif op in ("Add", "Sub", "Mul", "Div"):
+            lines.append(f"binary {op} {L['A']} {L['B']} {L['Y']}")
+        elif op == "BatchNormalization":
+            lines.append(f"batchnorm {L.get('epsilon', 1e-5)} {L['X']} {L['scale']} {L['bias']} {L['mean']} {L['var']} {L['Y']} "
+                         f"{int(bool(L.get('relu')))}")
         else:
             raise NotImplementedError(op)
     lines.append(f"output {m.output_name}")

@@ -101,6 +101,62 @@ def pool2d_f32(X, mode=0, kernel=(2, 2), stride=(2, 2), pads=(0, 0, 0, 0), count
     return Y
 
 
+UNARY_OPS = {"Sigmoid": 0, "Tanh": 1, "LeakyRelu": 2, "Selu": 3, "Elu": 4, "Neg": 5, "Exp": 6, "Log": 7, "Sqrt": 8,
+             "Reciprocal": 9, "Abs": 10}
+BINARY_OPS = {"Add": 0, "Sub": 1, "Mul": 2, "Div": 3}
+
+
+def unary_f32(X, op, alpha=0.0):
+    X = _f(X)
+    Y = np.empty_like(X)
+    lib().oracle_unary_f32(C.c_int(UNARY_OPS[op]), C.c_float(alpha), _ptr(X), _ptr(Y), C.c_size_t(X.size))
+    return Y
+
+
+def broadcast_strides(a_shape, b_shape):
+    """(output shape, a strides, b strides) of numpy-style broadcasting, padded to rank 4, in elements."""
+    out = np.broadcast_shapes(tuple(a_shape), tuple(b_shape))
+    if len(out) > 4:
+        raise ValueError("binary operators are built for rank <= 4")
+
+    def strides(shape):
+        shape = (1,) * (len(out) - len(shape)) + tuple(shape)
+        st, dense = [], 1
+        for d in reversed(shape):
+            st.append(0 if d == 1 else dense)
+            dense *= d
+        st = list(reversed(st))
+        return [0] * (4 - len(out)) + [0 if o != d and d == 1 else s for s, d, o in zip(st, shape, out)]
+
+    return out, [1] * (4 - len(out)) + list(out), strides(a_shape), strides(b_shape)
+
+
+def binary_f32(A, B, op):
+    A, B = _f(A), _f(B)
+    out, shape4, sa, sb = broadcast_strides(A.shape, B.shape)
+    Y = np.empty(out, np.float32)
+    i64 = C.c_int64 * 4
+    lib().oracle_binary_f32(C.c_int(BINARY_OPS[op]), i64(*shape4), i64(*sa), i64(*sb), _ptr(A), _ptr(B), _ptr(Y))
+    return Y
+
+
+def batchnorm_f32(X, scale, bias, mean, var, epsilon=1e-5, relu=False):
+    X, scale, bias, mean, var = _f(X), _f(scale), _f(bias), _f(mean), _f(var)
+    N, Cc = X.shape[0], X.shape[1]
+    HW = int(np.prod(X.shape[2:], dtype=np.int64))
+    Y = np.empty_like(X)
+    lib().oracle_batchnorm_f32(C.c_int(N), C.c_int(Cc), C.c_int(HW), C.c_float(epsilon), C.c_int(int(relu)), _ptr(X), _ptr(scale),
+                               _ptr(bias), _ptr(mean), _ptr(var), _ptr(Y))
+    return Y
+
+
+def batchnorm_folded_scale(scale, var, epsilon=1e-5):
+    """scale * (1 / sqrt(var + epsilon)) with the roundings of the reference's Initialize."""
+    v = (_f(var) + np.float32(epsilon)).astype(np.float32)
+    inv = (1.0 / np.sqrt(v.astype(np.float64))).astype(np.float32)
+    return (_f(scale) * inv).astype(np.float32)
+
+
 def softmax_f32(X, axis=-1):
     X = _f(X)
     axis = axis % X.ndim

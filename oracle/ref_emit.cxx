@@ -27,6 +27,13 @@
 #include "SOFIE/ROperator_Pool.hxx"
 #include "SOFIE/ROperator_Reshape.hxx"
 #include "SOFIE/ROperator_Softmax.hxx"
+#include "SOFIE/ROperator_Sigmoid.hxx"
+#include "SOFIE/ROperator_Tanh.hxx"
+#include "SOFIE/ROperator_LeakyRelu.hxx"
+#include "SOFIE/ROperator_Selu.hxx"
+#include "SOFIE/ROperator_Elu.hxx"
+#include "SOFIE/ROperator_BasicBinary.hxx"
+#include "SOFIE/ROperator_BatchNormalization.hxx"
 
 #include <cstdio>
 #include <fstream>
@@ -119,6 +126,32 @@ int main(int argc, char **argv)
             std::string X, Y;
             ss >> axis >> X >> Y;
             model->AddOperator(std::make_unique<ROperator_Softmax<float>>(axis, X, Y), order++);
+         } else if (kw == "unary") {
+            std::string op, X, Y;
+            float alpha;
+            ss >> op >> alpha >> X >> Y;
+            if (op == "Sigmoid") model->AddOperator(std::make_unique<ROperator_Sigmoid<float>>(X, Y), order++);
+            else if (op == "Tanh") model->AddOperator(std::make_unique<ROperator_Tanh<float>>(X, Y), order++);
+            else if (op == "LeakyRelu") model->AddOperator(std::make_unique<ROperator_LeakyRelu<float>>(alpha, X, Y), order++);
+            else if (op == "Selu") model->AddOperator(std::make_unique<ROperator_Selu<float>>(X, Y), order++);
+            else if (op == "Elu") model->AddOperator(std::make_unique<ROperator_Elu<float>>(alpha, X, Y), order++);
+            else throw std::runtime_error("unknown unary operator: " + op);
+         } else if (kw == "binary") {
+            std::string op, A, B, Y;
+            ss >> op >> A >> B >> Y;
+            if (op == "Add") model->AddOperator(std::make_unique<ROperator_BasicBinary<float, Add>>(A, B, Y), order++);
+            else if (op == "Sub") model->AddOperator(std::make_unique<ROperator_BasicBinary<float, Sub>>(A, B, Y), order++);
+            else if (op == "Mul") model->AddOperator(std::make_unique<ROperator_BasicBinary<float, Mul>>(A, B, Y), order++);
+            else if (op == "Div") model->AddOperator(std::make_unique<ROperator_BasicBinary<float, Div>>(A, B, Y), order++);
+            else throw std::runtime_error("unknown binary operator: " + op);
+         } else if (kw == "batchnorm") {
+            float eps;
+            int relu;
+            std::string X, S, B, Mn, V, Y;
+            ss >> eps >> X >> S >> B >> Mn >> V >> Y >> relu;
+            model->AddOperator(std::make_unique<ROperator_BatchNormalization<float>>(
+                                  eps, 0.9f, 0, X, S, B, Mn, V, Y, relu ? EActivationType::RELU : EActivationType::UNDEFINED),
+                               order++);
          } else if (kw == "output") {
             std::string Y;
             ss >> Y;

@@ -40,6 +40,15 @@ def run(model, x, fp8_scales=None, return_all=False):
             t[L["Y"]] = X.reshape(X.shape[0], -1)
         elif op == "Softmax":
             t[L["Y"]] = o.softmax_f32(t[L["X"]], L.get("axis", -1))
+        elif op in o.UNARY_OPS:
+            t[L["Y"]] = o.unary_f32(t[L["X"]], op, L.get("alpha", 0.01 if op == "LeakyRelu" else 1.0))
+        elif op in o.BINARY_OPS:
+            a = w[L["A"]] if L["A"] in w else t[L["A"]]
+            b = w[L["B"]] if L["B"] in w else t[L["B"]]
+            t[L["Y"]] = o.binary_f32(a, b, op)
+        elif op == "BatchNormalization":
+            t[L["Y"]] = o.batchnorm_f32(t[L["X"]], w[L["scale"]], w[L["bias"]], w[L["mean"]], w[L["var"]], L.get("epsilon", 1e-5),
+                                        bool(L.get("relu")))
         elif op == "QuantizeLinear":
             t[L["Y"]] = o.quantize_u8(t[L["X"]], L["scale"], L["zp"])
         elif op == "DequantizeLinear":

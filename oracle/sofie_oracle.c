@@ -263,6 +263,77 @@ ORACLE_API void oracle_softmax_f32(size_t outer, size_t axis_len, size_t inner, 
    }
 }
 
+/* Unary operators with the expressions of the emitted code (ROperator_Sigmoid.hxx:59,
+ * ROperator_Tanh.hxx:60, ROperator_LeakyRelu.hxx:73, ROperator_Selu.hxx:59 -- double constants --,
+ * ROperator_Elu.hxx:71 -- `alpha * exp(x) - 1` as written there --, ROperator_BasicUnary.hxx).
+ * op: 0 Sigmoid, 1 Tanh, 2 LeakyRelu, 3 Selu, 4 Elu, 5 Neg, 6 Exp, 7 Log, 8 Sqrt, 9 Reciprocal, 10 Abs. */
+ORACLE_API void oracle_unary_f32(int op, float alpha, const float *X, float *Y, size_t n)
+{
+   for (size_t i = 0; i < n; i++) {
+      const float x = X[i];
+      float y;
+      switch (op) {
+      case 0: y = 1 / (1 + expf(-x)); break;
+      case 1: y = tanhf(x); break;
+      case 2: y = (x >= 0) ? x : alpha * x; break;
+      case 3: {
+         const double pos = (0.0f > x) ? 0.0f : x;
+         const double t = 1.6732632423543772848170429916717 * (expf(x) - 1);
+         y = (float)(1.0507009873554804934193349852946 * (pos + (0.0 < t ? 0.0 : t)));
+         break;
+      }
+      case 4: y = (x >= 0) ? x : alpha * expf(x) - 1; break;
+      case 5: y = -x; break;
+      case 6: y = expf(x); break;
+      case 7: y = logf(x); break;
+      case 8: y = sqrtf(x); break;
+      case 9: y = 1 / x; break;
+      default: y = fabsf(x); break;
+      }
+      Y[i] = y;
+   }
+}
+
+/* Binary operators with broadcasting (ROperator_BasicBinary.hxx:18-43): the output has `shape`
+ * (rank 4); an operand's element stride is 0 along a broadcast dimension. op: 0 +, 1 -, 2 *, 3 /. */
+ORACLE_API void oracle_binary_f32(int op, const int64_t *shape, const int64_t *a_stride, const int64_t *b_stride, const float *A,
+                                  const float *B, float *Y)
+{
+   size_t i = 0;
+   for (int64_t c0 = 0; c0 < shape[0]; c0++)
+      for (int64_t c1 = 0; c1 < shape[1]; c1++)
+         for (int64_t c2 = 0; c2 < shape[2]; c2++)
+            for (int64_t c3 = 0; c3 < shape[3]; c3++, i++) {
+               const float a = A[c0 * a_stride[0] + c1 * a_stride[1] + c2 * a_stride[2] + c3 * a_stride[3]];
+               const float b = B[c0 * b_stride[0] + c1 * b_stride[1] + c2 * b_stride[2] + c3 * b_stride[3]];
+               Y[i] = op == 0 ? a + b : (op == 1 ? a - b : (op == 2 ? a * b : a / b));
+            }
+}
+
+/* BatchNormalization as emitted (ROperator_BatchNormalization.hxx:163-168, 200-226): at Initialize
+ * the scale becomes scale * (1. / sqrt(var + epsilon)); at run time y = x, y -= mean, y *= scale,
+ * y += bias, optional Relu. X is NCHW viewed as [N, C, HW]. */
+ORACLE_API void oracle_batchnorm_f32(int N, int C_, int HW, float epsilon, int relu, const float *X, const float *scale,
+                                     const float *bias, const float *mean, const float *var, float *Y)
+{
+   for (int c = 0; c < C_; c++) {
+      float v = var[c] + epsilon;
+      float inv = (float)(1. / sqrt(v));
+      float s = scale[c] * inv;
+      for (int n = 0; n < N; n++) {
+         const float *x = X + ((size_t)n * C_ + c) * HW;
+         float *y = Y + ((size_t)n * C_ + c) * HW;
+         for (int i = 0; i < HW; i++) {
+            float t = x[i];
+            t = t + (-1.f) * mean[c];
+            t *= s;
+            t = t + 1.f * bias[c];
+            y[i] = relu ? ((t > 0) ? t : 0) : t;
+         }
+      }
+   }
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* int8 (ONNX operator definitions; parity unpinned by the reference)                          */
 /* ------------------------------------------------------------------------------------------ */

@@ -48,6 +48,14 @@ class QConv2dDesc(C.Structure):
                                    "x_layout", "y_layout", "w_packed", "x_zp", "y_zp", "relu", "pool")]
 
 
+class BinaryDesc(C.Structure):
+    _fields_ = [("op", i32), ("shape", C.c_int64 * 4), ("a_stride", C.c_int64 * 4), ("b_stride", C.c_int64 * 4)]
+
+
+class BatchNormDesc(C.Structure):
+    _fields_ = [(n, i32) for n in ("N", "C", "HW", "layout", "relu")]
+
+
 class Fp8GemmDesc(C.Structure):
     _fields_ = [("M", i32), ("N", i32), ("K", i32), ("a_scale", f32), ("w_scale", f32), ("relu", i32),
                 ("q_scale", f32)]
@@ -83,6 +91,9 @@ SIGNATURES = {
     "sofie_cuda_relu_f32": [vp, vp, vp, sz],
     "sofie_cuda_pool2d_f32": [vp, C.POINTER(Pool2dDesc), vp, vp],
     "sofie_cuda_softmax_f32": [vp, vp, vp, sz, sz, sz],
+    "sofie_cuda_unary_f32": [vp, i32, f32, vp, vp, sz],
+    "sofie_cuda_binary_f32": [vp, C.POINTER(BinaryDesc), vp, vp, vp],
+    "sofie_cuda_batchnorm_f32": [vp, C.POINTER(BatchNormDesc), vp, vp, vp, vp, vp],
     "sofie_cuda_nchw_to_nhwc_f32": [vp, vp, vp, i32, i32, i32, i32],
     "sofie_cuda_nhwc_to_nchw_f32": [vp, vp, vp, i32, i32, i32, i32],
     "sofie_cuda_quantize_u8": [vp, vp, vp, sz, f32, i32],

@@ -150,6 +150,71 @@ def calibrate_fp8_scales(model, x):
     return scales
 
 
+# ------------------------------------------------------------------------------------ elementwise family
+def resblock_f32(batch=8, chans=16, hw=16, key="C2", with_input=True):
+    """Residual block: Conv 8->C + BatchNormalization + Relu; Conv C->C + BatchNormalization; Add(skip); LeakyRelu;
+    MaxPool 2x2; Mul by a per-channel constant; Flatten; Gemm -> 10; Sigmoid. Seeded like C2."""
+    rng = np.random.Generator(np.random.PCG64(SEEDS[key] + 77))
+    m = Model(f"resblock_b{batch}", "x", (batch, 8, hw, hw), [])
+
+    def bn(prefix):
+        m.weights[prefix + "_g"] = rng.uniform(0.5, 1.5, chans).astype(np.float32)
+        m.weights[prefix + "_b"] = rng.uniform(-0.2, 0.2, chans).astype(np.float32)
+        m.weights[prefix + "_m"] = (rng.standard_normal(chans) * 0.1).astype(np.float32)
+        m.weights[prefix + "_v"] = rng.uniform(0.5, 2.0, chans).astype(np.float32)
+        return dict(scale=prefix + "_g", bias=prefix + "_b", mean=prefix + "_m", var=prefix + "_v", epsilon=1e-5)
+
+    for i, cin in enumerate((8, chans)):
+        m.weights[f"w{i}"] = (rng.standard_normal((chans, cin, 3, 3)) * np.sqrt(2.0 / (cin * 9))).astype(np.float32)
+        m.weights[f"b{i}"] = rng.uniform(-0.1, 0.1, chans).astype(np.float32)
+    m.layers.append(dict(op="Conv", X="x", W="w0", B="b0", Y="c0", pads=(1, 1, 1, 1), strides=(1, 1), kernel=(3, 3)))
+    m.layers.append(dict(op="BatchNormalization", X="c0", Y="n0", relu=True, **bn("bn0")))
+    m.layers.append(dict(op="Conv", X="n0", W="w1", B="b1", Y="c1", pads=(1, 1, 1, 1), strides=(1, 1), kernel=(3, 3)))
+    m.layers.append(dict(op="BatchNormalization", X="c1", Y="n1", **bn("bn1")))
+    m.layers.append(dict(op="Add", A="n1", B="n0", Y="s"))
+    m.layers.append(dict(op="LeakyRelu", X="s", Y="a", alpha=0.1))
+    m.layers.append(dict(op="MaxPool", X="a", Y="p", kernel=(2, 2), strides=(2, 2), pads=(0, 0, 0, 0)))
+    m.weights["gain"] = rng.uniform(0.5, 1.5, (chans, 1, 1)).astype(np.float32)
+    m.layers.append(dict(op="Mul", A="p", B="gain", Y="g"))
+    m.layers.append(dict(op="Flatten", X="g", Y="f", axis=1))
+    k = chans * (hw // 2) ** 2
+    m.weights["fw"] = (rng.standard_normal((10, k)) * np.sqrt(1.0 / k)).astype(np.float32)
+    m.weights["fb"] = rng.uniform(-0.1, 0.1, 10).astype(np.float32)
+    m.layers.append(dict(op="Gemm", A="f", B="fw", C="fb", Y="l", transB=1))
+    m.layers.append(dict(op="Sigmoid", X="l", Y="y"))
+    m.output_name = "y"
+    m.flops_per_sample = 2 * hw * hw * chans * 9 * (8 + chans) + 2 * k * 10
+    x = rng.standard_normal((batch, 8, hw, hw)).astype(np.float32) if with_input else None
+    return m, x
+
+
+def mlp_activations_f32(batch=64, key="C1", with_input=True):
+    """Gemm 32->48 + Selu; Gemm 48->48 + Tanh; Sub of a constant row; Gemm 48->24 + Elu; Div by a constant; Sigmoid."""
+    rng = np.random.Generator(np.random.PCG64(SEEDS[key] + 78))
+    m = Model(f"mlp_act_b{batch}", "x", (batch, 32), [])
+    dims = (32, 48, 48, 24)
+    acts = ("Selu", "Tanh", "Elu")
+    prev = "x"
+    for i in range(3):
+        k, n = dims[i], dims[i + 1]
+        m.weights[f"w{i}"] = (rng.standard_normal((n, k)) * np.sqrt(1.0 / k)).astype(np.float32)
+        m.weights[f"b{i}"] = rng.uniform(-0.1, 0.1, n).astype(np.float32)
+        m.layers.append(dict(op="Gemm", A=prev, B=f"w{i}", C=f"b{i}", Y=f"g{i}", transB=1))
+        m.layers.append(dict(op=acts[i], X=f"g{i}", Y=f"a{i}", **({"alpha": 1.0} if acts[i] == "Elu" else {})))
+        prev = f"a{i}"
+        if i == 1:
+            m.weights["shift"] = rng.uniform(-0.5, 0.5, (n,)).astype(np.float32)
+            m.layers.append(dict(op="Sub", A=prev, B="shift", Y="sh"))
+            prev = "sh"
+    m.weights["den"] = rng.uniform(0.5, 2.0, (24,)).astype(np.float32)
+    m.layers.append(dict(op="Div", A=prev, B="den", Y="d"))
+    m.layers.append(dict(op="Sigmoid", X="d", Y="y"))
+    m.output_name = "y"
+    m.flops_per_sample = 2 * sum(dims[i] * dims[i + 1] for i in range(3))
+    x = rng.standard_normal((batch, 32)).astype(np.float32) if with_input else None
+    return m, x
+
+
 # ------------------------------------------------------------------------------------ C5
 # Fixed activation scales of the calorimeter CNN: input energies are clipped at 8 (scale 8/255);
 # the scales after each layer were chosen once so that the seeded activations use the uint8 range.

@@ -32,9 +32,9 @@ static void set_err(char *err, int n, const char *msg) {{ if (err && n > 0) {{ s
 extern "C" void *sofie_session_create(const char *dat, char *err, int errlen) {{
    try {{ return new Session(dat); }} catch (const std::exception &e) {{ set_err(err, errlen, e.what()); return nullptr; }}
 }}
-extern "C" long sofie_session_infer(void *s, {in_type} *x, {out_type} *y, long ny, char *err, int errlen) {{
+extern "C" long sofie_session_infer(void *s, {in_type} **xs, {out_type} *y, long ny, char *err, int errlen) {{
    try {{
-      auto out = static_cast<Session *>(s)->infer(x);
+      auto out = static_cast<Session *>(s)->infer({args});
       if ((long)out.size() > ny) {{ set_err(err, errlen, "output buffer too small"); return -(long)out.size(); }}
       std::memcpy(y, out.data(), out.size() * sizeof({out_type}));
       return (long)out.size();
@@ -66,14 +66,22 @@ def emit(onnx_bytes: bytes, name: str, batch: int | None = None, workdir: Path |
     return hxx
 
 
+def count_inputs(hxx: Path) -> int:
+    """Number of tensors the emitted infer() takes (one pointer argument each)."""
+    import re
+    m = re.search(r"std::vector<float>\s+infer\(([^)]*)\)", hxx.read_text())
+    return max(1, m.group(1).count("tensor_")) if m else 1
+
+
 def compile_session(hxx: Path, name: str, in_type="float", out_type="float") -> Path:
     """Compile the emitted header (plus the trampolines) and link it against libSOFIE_cuda."""
     lib = _build.build()
     so = hxx.with_suffix(".so")
-    if so.exists() and so.stat().st_mtime >= max(hxx.stat().st_mtime, lib.stat().st_mtime):
+    if so.exists() and so.stat().st_mtime >= max(hxx.stat().st_mtime, lib.stat().st_mtime, Path(__file__).stat().st_mtime):
         return so
     src = hxx.with_name(hxx.stem + "_trampoline.cxx")
-    src.write_text(TRAMPOLINE.format(header=hxx.name, name=name, in_type=in_type, out_type=out_type))
+    args = ", ".join(f"xs[{i}]" for i in range(count_inputs(hxx)))
+    src.write_text(TRAMPOLINE.format(header=hxx.name, name=name, in_type=in_type, out_type=out_type, args=args))
     cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I", str(ROOT / "include"), "-I", str(hxx.parent), str(src), "-o", str(so),
            "-L", str(lib.parent), "-lSOFIE_cuda", f"-Wl,-rpath,{lib.parent}"]
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
@@ -98,18 +106,20 @@ class GeneratedSession:
             raise RuntimeError(self.err.value.decode())
         self.out_elems, self.out_dtype = out_elems, out_dtype
 
-    def infer(self, x: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
-        x = np.ascontiguousarray(x)
+    def infer(self, x, out: np.ndarray | None = None) -> np.ndarray:
+        """x: one array, or a list of arrays for a model with several inputs (in the order of infer())."""
+        xs = [np.ascontiguousarray(a) for a in (x if isinstance(x, (list, tuple)) else [x])]
+        ptrs = (C.c_void_p * len(xs))(*[a.ctypes.data_as(C.c_void_p) for a in xs])
         y = out if out is not None else np.empty(self.out_elems, self.out_dtype)
-        n = self.lib.sofie_session_infer(self.handle, x.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), self.out_elems,
-                                         self.err, 1024)
+        n = self.lib.sofie_session_infer(self.handle, ptrs, y.ctypes.data_as(C.c_void_p), self.out_elems, self.err, 1024)
         if n != self.out_elems:
             raise RuntimeError(f"infer failed ({n}): {self.err.value.decode()}")
         return y
 
     def infer_ptr(self, x_ptr: int, y_ptr: int) -> None:
         """infer() on raw host addresses (pinned buffers of the benchmark)."""
-        n = self.lib.sofie_session_infer(self.handle, C.c_void_p(x_ptr), C.c_void_p(y_ptr), self.out_elems, self.err, 1024)
+        ptrs = (C.c_void_p * 1)(C.c_void_p(x_ptr))
+        n = self.lib.sofie_session_infer(self.handle, ptrs, C.c_void_p(y_ptr), self.out_elems, self.err, 1024)
         if n != self.out_elems:
             raise RuntimeError(f"infer failed ({n}): {self.err.value.decode()}")
 

@@ -20,7 +20,7 @@ namespace SOFIE {
 
 class RModel;
 
-enum class EOpKind { Other, Gemm, Conv, Relu, Pool, Reshape, Softmax, Cast, Quantize, Dequantize, QLinearMatMul, QLinearConv, Fp8Gemm };
+enum class EOpKind { Other, Gemm, Conv, Relu, Pool, Reshape, Softmax, Cast, Quantize, Dequantize, QLinearMatMul, QLinearConv, Fp8Gemm, Eltwise };
 
 class ROperator {
 public:

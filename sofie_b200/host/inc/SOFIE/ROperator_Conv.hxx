@@ -11,6 +11,7 @@
 #ifndef SOFIE_ROPERATOR_CONV
 #define SOFIE_ROPERATOR_CONV
 
+#include <cmath>
 #include <sstream>
 
 #include "SOFIE/Emit.hxx"
@@ -116,6 +117,38 @@ public:
    {
       fFusedRelu = true;
       fNOut = reluOutput;
+      fOutputTensorNames = {fNOut};
+   }
+   // Folds an inference BatchNormalization that reads this convolution's output into the weights:
+   // w'[o] = w[o] * s[o], b'[o] = (b[o] - mean[o]) * s[o] + beta[o], s = gamma * float(1. / sqrt(var + eps)).
+   void FoldBatchNorm(RModel &model, const std::string &scale, const std::string &beta, const std::string &mean, const std::string &var,
+                      float epsilon, bool relu, const std::string &bnOutput)
+   {
+      const size_t Cout = fShapeW[0];
+      size_t per = 1;
+      for (size_t i = 1; i < fShapeW.size(); i++) per *= fShapeW[i];
+      const float *w = model.GetInitializedTensor(fNW).template data<float>();
+      const float *b = fNB.empty() ? nullptr : model.GetInitializedTensor(fNB).template data<float>();
+      const float *g = model.GetInitializedTensor(scale).template data<float>();
+      const float *be = model.GetInitializedTensor(beta).template data<float>();
+      const float *mu = model.GetInitializedTensor(mean).template data<float>();
+      const float *va = model.GetInitializedTensor(var).template data<float>();
+      std::shared_ptr<void> wbuf(malloc(Cout * per * sizeof(float)), free), bbuf(malloc(Cout * sizeof(float)), free);
+      float *w2 = static_cast<float *>(wbuf.get()), *b2 = static_cast<float *>(bbuf.get());
+      for (size_t o = 0; o < Cout; o++) {
+         float v = va[o] + epsilon;
+         float inv = 1. / std::sqrt((double)v);
+         float s = g[o] * inv;
+         for (size_t i = 0; i < per; i++) w2[o * per + i] = w[o * per + i] * s;
+         b2[o] = ((b ? b[o] : 0.f) - mu[o]) * s + be[o];
+      }
+      const std::string wname = fNW + "_bn_" + bnOutput, bname = bnOutput + "_bnbias";
+      if (!model.IsInitializedTensor(wname)) model.AddInitializedTensor(wname, ETensorType::FLOAT, fShapeW, wbuf);
+      if (!model.IsInitializedTensor(bname)) model.AddInitializedTensor(bname, ETensorType::FLOAT, {Cout}, bbuf);
+      fNW = wname;
+      fNB = bname;
+      if (relu) fFusedRelu = true;
+      fNOut = bnOutput;
       fOutputTensorNames = {fNOut};
    }
    void FusePool2x2(const std::string &poolOutput)

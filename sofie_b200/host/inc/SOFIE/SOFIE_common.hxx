@@ -124,6 +124,22 @@ private:
 };
 
 namespace UTILITY {
+// Shape of A op B under numpy-style (multidirectional) broadcasting; throws when the shapes do not
+// broadcast (reference: UTILITY::MultidirectionalBroadcastShape, src/SOFIE_core/src/SOFIE_common.cxx).
+inline std::vector<size_t> MultidirectionalBroadcastShape(std::vector<size_t> a, std::vector<size_t> b)
+{
+   if (a.size() < b.size()) a.insert(a.begin(), b.size() - a.size(), 1);
+   if (b.size() < a.size()) b.insert(b.begin(), a.size() - b.size(), 1);
+   std::vector<size_t> out(a.size());
+   for (size_t i = 0; i < a.size(); i++) {
+      if (a[i] != b[i] && a[i] != 1 && b[i] != 1)
+         throw std::runtime_error("SOFIE - Error multidirectional broadcasting shapes " + ConvertShapeToString(a) + " and " +
+                                  ConvertShapeToString(b));
+      out[i] = a[i] == 1 ? b[i] : a[i];
+   }
+   return out;
+}
+
 // Makes a tensor name usable as a C++ identifier (reference: src/SOFIE_core/src/SOFIE_common.cxx:394-400).
 std::string Clean_name(std::string input_tensor_name);
 bool AreSameShape(const std::vector<size_t> &a, const std::vector<size_t> &b);

@@ -10,6 +10,7 @@
 #include <limits>
 
 #include "SOFIE/Emit.hxx"
+#include "SOFIE/ROperator_BatchNormalization.hxx"
 #include "SOFIE/ROperator_Conv.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
 #include "SOFIE/ROperator_Pool.hxx"
@@ -225,6 +226,7 @@ bool RModel::CanStayNHWC(const std::string &name, int depth) const
       case EOpKind::QLinearConv: break;
       case EOpKind::Relu:
       case EOpKind::Pool:
+      case EOpKind::Eltwise:
          if (!CanStayNHWC(op->GetOpOutputTensors()[0], depth + 1)) return false;
          break;
       case EOpKind::Reshape: {
@@ -303,7 +305,18 @@ void RModel::PlanDevice()
          auto *fconv = dynamic_cast<ROperator_Conv<float> *>(op);
          auto *qconv = dynamic_cast<ROperator_QLinearConv *>(op);
          std::string out = fconv ? fconv->OutputName() : qconv->OutputName();
-         if (ROperator *next = single_consumer(out)) {
+         bool relu_done = false;
+         if (fconv)
+            if (ROperator *next = single_consumer(out))
+               if (auto *bn = dynamic_cast<ROperator_BatchNormalization<float> *>(next)) {
+                  // inference BatchNormalization behind a convolution: folded into its weights and bias
+                  fconv->FoldBatchNorm(*this, bn->ScaleName(), bn->BiasName(), bn->MeanName(), bn->VarName(), bn->Epsilon(), bn->HasRelu(),
+                                       bn->OutputName());
+                  bn->SetFusedAway();
+                  out = bn->OutputName();
+                  relu_done = bn->HasRelu();
+               }
+         if (ROperator *next = relu_done ? nullptr : single_consumer(out)) {
             if (auto *relu = dynamic_cast<ROperator_Relu<float> *>(next)) {
                fconv ? fconv->FuseRelu(relu->OutputName()) : qconv->FuseRelu(relu->OutputName());
                relu->SetFusedAway();

@@ -11,6 +11,9 @@
 #include <iostream>
 #include <sstream>
 
+#include "SOFIE/ROperator_BasicBinary.hxx"
+#include "SOFIE/ROperator_BasicUnary.hxx"
+#include "SOFIE/ROperator_BatchNormalization.hxx"
 #include "SOFIE/ROperator_Conv.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
 #include "SOFIE/ROperator_Pool.hxx"
@@ -147,6 +150,66 @@ std::unique_ptr<ROperator> ParseSoftmax(RModelParser_ONNX &p, const onnx::NodePr
    return std::unique_ptr<ROperator>(new ROperator_Softmax<float>(attr_int(n, "axis", -1), n.input(0), n.output(0)));
 }
 
+// Elementwise family (reference: ParseSigmoid.cxx, ParseTanh.cxx, ParseLeakyRelu.cxx, ParseSelu.cxx, ParseElu.cxx,
+// ParseBasicUnary.cxx, ParseBasicBinary.cxx, ParseBatchNormalization.cxx): float only, output type = input type.
+template <typename Make>
+std::unique_ptr<ROperator> ParseUnaryWith(RModelParser_ONNX &p, const onnx::NodeProto &n, Make make)
+{
+   require_type(p, n.input(0), n.op_type());
+   if (p.GetTensorType(n.input(0)) != ETensorType::FLOAT)
+      throw std::runtime_error("SOFIE - Unsupported - Operator " + n.op_type() + " does not yet support this input type");
+   p.RegisterTensorType(n.output(0), ETensorType::FLOAT);
+   return std::unique_ptr<ROperator>(make());
+}
+std::unique_ptr<ROperator> ParseSigmoid(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   return ParseUnaryWith(p, n, [&] { return new ROperator_Sigmoid<float>(n.input(0), n.output(0)); });
+}
+std::unique_ptr<ROperator> ParseTanh(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   return ParseUnaryWith(p, n, [&] { return new ROperator_Tanh<float>(n.input(0), n.output(0)); });
+}
+std::unique_ptr<ROperator> ParseSelu(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   return ParseUnaryWith(p, n, [&] { return new ROperator_Selu<float>(n.input(0), n.output(0)); });
+}
+std::unique_ptr<ROperator> ParseLeakyRelu(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   return ParseUnaryWith(p, n, [&] { return new ROperator_LeakyRelu<float>(attr_float(n, "alpha", 0.01f), n.input(0), n.output(0)); });
+}
+std::unique_ptr<ROperator> ParseElu(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   return ParseUnaryWith(p, n, [&] { return new ROperator_Elu<float>(attr_float(n, "alpha", 1.f), n.input(0), n.output(0)); });
+}
+template <EBasicUnaryOperator Op>
+std::unique_ptr<ROperator> ParseBasicUnary(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   return ParseUnaryWith(p, n, [&] { return new ROperator_BasicUnary<float, Op>(n.input(0), n.output(0)); });
+}
+template <EBasicBinaryOperator Op>
+std::unique_ptr<ROperator> ParseBasicBinary(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   if (n.input_size() != 2) throw std::runtime_error("SOFIE - binary operator " + n.op_type() + " needs two inputs");
+   for (int i = 0; i < 2; i++) {
+      require_type(p, n.input(i), n.op_type());
+      if (p.GetTensorType(n.input(i)) != ETensorType::FLOAT)
+         throw std::runtime_error("SOFIE - Unsupported - Operator " + n.op_type() + " does not yet support this input type");
+   }
+   p.RegisterTensorType(n.output(0), ETensorType::FLOAT);
+   return std::unique_ptr<ROperator>(new ROperator_BasicBinary<float, Op>(n.input(0), n.input(1), n.output(0)));
+}
+std::unique_ptr<ROperator> ParseBatchNormalization(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   require_type(p, n.input(0), "BatchNormalization");
+   if (p.GetTensorType(n.input(0)) != ETensorType::FLOAT)
+      throw std::runtime_error("SOFIE - Unsupported - Operator BatchNormalization does not yet support this input type");
+   if (n.input_size() != 5) throw std::runtime_error("SOFIE - BatchNormalization needs X, scale, B, mean and var");
+   p.RegisterTensorType(n.output(0), ETensorType::FLOAT);
+   return std::unique_ptr<ROperator>(new ROperator_BatchNormalization<float>(attr_float(n, "epsilon", 1e-5f), attr_float(n, "momentum", 0.9f),
+                                                                             (size_t)attr_int(n, "training_mode", 0), n.input(0), n.input(1),
+                                                                             n.input(2), n.input(3), n.input(4), n.output(0)));
+}
+
 std::unique_ptr<ROperator> ParseQuantizeLinear(RModelParser_ONNX &p, const onnx::NodeProto &n)
 {
    require_type(p, n.input(0), "QuantizeLinear");
@@ -221,6 +284,22 @@ RModelParser_ONNX::RModelParser_ONNX() noexcept : fOperatorsMapImpl(std::make_un
    RegisterOperator("Squeeze", ParseReshape);
    RegisterOperator("Unsqueeze", ParseReshape);
    RegisterOperator("Softmax", ParseSoftmax);
+   RegisterOperator("Sigmoid", ParseSigmoid);
+   RegisterOperator("Tanh", ParseTanh);
+   RegisterOperator("Selu", ParseSelu);
+   RegisterOperator("LeakyRelu", ParseLeakyRelu);
+   RegisterOperator("Elu", ParseElu);
+   RegisterOperator("Neg", ParseBasicUnary<EBasicUnaryOperator::kNeg>);
+   RegisterOperator("Exp", ParseBasicUnary<EBasicUnaryOperator::kExp>);
+   RegisterOperator("Log", ParseBasicUnary<EBasicUnaryOperator::kLog>);
+   RegisterOperator("Sqrt", ParseBasicUnary<EBasicUnaryOperator::kSqrt>);
+   RegisterOperator("Reciprocal", ParseBasicUnary<EBasicUnaryOperator::kReciprocal>);
+   RegisterOperator("Abs", ParseBasicUnary<EBasicUnaryOperator::kAbs>);
+   RegisterOperator("Add", ParseBasicBinary<Add>);
+   RegisterOperator("Sub", ParseBasicBinary<Sub>);
+   RegisterOperator("Mul", ParseBasicBinary<Mul>);
+   RegisterOperator("Div", ParseBasicBinary<Div>);
+   RegisterOperator("BatchNormalization", ParseBatchNormalization);
    RegisterOperator("QuantizeLinear", ParseQuantizeLinear);
    RegisterOperator("DequantizeLinear", ParseDequantizeLinear);
    RegisterOperator("QLinearMatMul", ParseQLinearMatMul);
@@ -264,6 +343,18 @@ std::unique_ptr<ROperator> RModelParser_ONNX::ParseOperator(const size_t i, cons
          }
       }
    }
+   // BatchNormalization whose only reader is a Relu: one operator with the activation fused
+   // (reference: ParseFuseBatchnormRelu.cxx, RModelParser_ONNX.cxx:322-330)
+   if (type == "BatchNormalization" && children.size() == 1 && node.input_size() == 5) {
+      const onnx::NodeProto &child = g.node((int)nodes[children[0]]);
+      if (child.op_type() == "Relu" && IsRegisteredTensorType(node.input(0)) && GetTensorType(node.input(0)) == ETensorType::FLOAT) {
+         fFusedOperators[children[0]] = true;
+         RegisterTensorType(child.output(0), ETensorType::FLOAT);
+         return std::unique_ptr<ROperator>(new ROperator_BatchNormalization<float>(
+            attr_float(node, "epsilon", 1e-5f), attr_float(node, "momentum", 0.9f), (size_t)attr_int(node, "training_mode", 0), node.input(0),
+            node.input(1), node.input(2), node.input(3), node.input(4), child.output(0), EActivationType::RELU));
+      }
+   }
    auto it = fOperatorsMapImpl->fOperatorsMap.find(type);
    if (it == fOperatorsMapImpl->fOperatorsMap.end())
       throw std::runtime_error("SOFIE Operator type " + type + " is not yet supported on the CUDA dense-contraction path");
@@ -286,7 +377,7 @@ void RModelParser_ONNX::CheckGraph(const onnx::GraphProto &g, int &level, std::m
    (void)level;
    for (int i = 0; i < g.node_size(); i++) {
       const std::string &t = g.node(i).op_type();
-      if (!IsRegisteredOperator(t) && t != "Add") missingOperators[t]++;
+      if (!IsRegisteredOperator(t)) missingOperators[t]++;
    }
 }
 

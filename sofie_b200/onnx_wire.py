@@ -316,6 +316,19 @@ def model_to_onnx(m) -> bytes:
                                                           attr_ints("strides", L["strides"])]))
             if L.get("relu"):
                 nodes.append(node("Relu", [out], [L["Y"]]))
+        elif op in ("Sigmoid", "Tanh", "Selu", "Neg", "Exp", "Log", "Sqrt", "Reciprocal", "Abs"):
+            nodes.append(node(op, [L["X"]], [L["Y"]]))
+        elif op in ("LeakyRelu", "Elu"):
+            nodes.append(node(op, [L["X"]], [L["Y"]], [attr_float("alpha", L.get("alpha", 0.01 if op == "LeakyRelu" else 1.0))]))
+        elif op in ("Add", "Sub", "Mul", "Div"):
+            nodes.append(node(op, [init(n) if n in w else n for n in (L["A"], L["B"])], [L["Y"]]))
+        elif op == "BatchNormalization":
+            ins = [L["X"], init(L["scale"]), init(L["bias"]), init(L["mean"]), init(L["var"])]
+            out = L["Y"] + "_pre" if L.get("relu") else L["Y"]
+            nodes.append(node(op, ins, [out], [attr_float("epsilon", L.get("epsilon", 1e-5))]))
+            if L.get("relu"):
+                # BatchNormalization + Relu is written as two nodes; the parser fuses them as the reference does
+                nodes.append(node("Relu", [out], [L["Y"]]))
         else:
             raise NotImplementedError(f"no ONNX serialisation for {op}")
     inputs = [value_info(m.input_name, FLOAT, m.input_shape)]

@@ -111,6 +111,51 @@ def softmax_f32(X, axis=-1):
     return Y
 
 
+UNARY_OPS = {"Sigmoid": 0, "Tanh": 1, "LeakyRelu": 2, "Selu": 3, "Elu": 4, "Neg": 5, "Exp": 6, "Log": 7, "Sqrt": 8,
+             "Reciprocal": 9, "Abs": 10}
+BINARY_OPS = {"Add": 0, "Sub": 1, "Mul": 2, "Div": 3}
+
+
+def unary_f32(X, op, alpha=0.0):
+    Y = torch.empty_like(X)
+    capi.call("sofie_cuda_unary_f32", _stream(), UNARY_OPS[op], float(alpha), _p(X), _p(Y), X.numel())
+    return Y
+
+
+def binary_strides(a_shape, b_shape):
+    """Output shape and the rank-4 shape / element strides (0 along broadcast dimensions) of A op B."""
+    out = tuple(torch.broadcast_shapes(tuple(a_shape), tuple(b_shape)))
+    if len(out) > 4:
+        raise ValueError("binary operators are built for rank <= 4")
+
+    def strides(shape):
+        shape = (1,) * (len(out) - len(shape)) + tuple(shape)
+        st, dense = [], 1
+        for d in reversed(shape):
+            st.append(0 if d == 1 else dense)
+            dense *= d
+        return [0] * (4 - len(out)) + list(reversed(st))
+
+    return out, [1] * (4 - len(out)) + list(out), strides(a_shape), strides(b_shape)
+
+
+def binary_f32(A, B, op):
+    out, shape4, sa, sb = binary_strides(A.shape, B.shape)
+    Y = torch.empty(out, dtype=torch.float32, device=A.device)
+    i64 = C.c_int64 * 4
+    d = capi.BinaryDesc(BINARY_OPS[op], i64(*shape4), i64(*sa), i64(*sb))
+    capi.call("sofie_cuda_binary_f32", _stream(), C.byref(d), _p(A), _p(B), _p(Y))
+    return Y
+
+
+def batchnorm_f32(X, scale, bias, mean, N, Cc, HW, layout=LAYOUT_NCHW, relu=False):
+    """scale is the folded gamma / sqrt(var + eps)."""
+    Y = torch.empty_like(X)
+    d = capi.BatchNormDesc(N, Cc, HW, layout, int(relu))
+    capi.call("sofie_cuda_batchnorm_f32", _stream(), C.byref(d), _p(X), _p(scale), _p(bias), _p(mean), _p(Y))
+    return Y
+
+
 def nchw_to_nhwc(X):
     N, Cc, H, W = X.shape
     Y = torch.empty((N, H, W, Cc), dtype=X.dtype, device=X.device)

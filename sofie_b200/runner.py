@@ -51,7 +51,7 @@ class Session:
         return torch.from_numpy(np.ascontiguousarray(arr)).to(self.dev)
 
     def _consumers(self, name):
-        return [L for L in self.model.layers if name in (L.get("X"), L.get("A"))]
+        return [L for L in self.model.layers if name in (L.get("X"), L.get("A"), L.get("B") if L["op"] in ops.BINARY_OPS else None)]
 
     def _plan(self):
         layers = self.model.layers
@@ -67,14 +67,20 @@ class Session:
             elif op in ("Conv", "QLinearConv"):
                 # fuse Conv [+ Relu] [+ MaxPool 2x2 stride 2 no pad] when each intermediate has one consumer
                 j, relu, pool, out = i + 1, bool(L.get("relu", False)), 0, L["Y"]
-                if op == "Conv" and j < len(layers) and layers[j]["op"] == "Relu" and layers[j]["X"] == out and \
+                bn = None
+                if op == "Conv" and j < len(layers) and layers[j]["op"] == "BatchNormalization" and layers[j]["X"] == out and \
+                        len(self._consumers(out)) == 1:
+                    # inference BatchNormalization behind a convolution: folded into its weights and bias
+                    bn, out, j = layers[j], layers[j]["Y"], j + 1
+                    relu = bool(bn.get("relu", False))
+                if op == "Conv" and not relu and j < len(layers) and layers[j]["op"] == "Relu" and layers[j]["X"] == out and \
                         len(self._consumers(out)) == 1:
                     relu, out, j = True, layers[j]["Y"], j + 1
                 if j < len(layers) and layers[j]["op"] == "MaxPool" and layers[j]["X"] == out and \
                         len(self._consumers(out)) == 1 and tuple(layers[j]["kernel"]) == (2, 2) and \
                         tuple(layers[j]["strides"]) == (2, 2) and not any(layers[j]["pads"]):
                     pool, out, j = 2, layers[j]["Y"], j + 1
-                self._plan_conv(L, relu, pool, out, quant=(op == "QLinearConv"))
+                self._plan_conv(L, relu, pool, out, quant=(op == "QLinearConv"), bn=bn)
                 i = j
             elif op == "Relu":
                 x, y = L["X"], L["Y"]
@@ -95,6 +101,18 @@ class Session:
                 x, y, ax = L["X"], L["Y"], L.get("axis", -1)
                 self.layout[y], self.shape[y] = self.layout[x], self.shape[x]
                 self.steps.append(Step(f"softmax:{y}", lambda t, x=x, y=y, ax=ax: t.__setitem__(y, ops.softmax_f32(t[x], ax))))
+                i += 1
+            elif op in ops.UNARY_OPS:
+                x, y = L["X"], L["Y"]
+                alpha = L.get("alpha", {"LeakyRelu": 0.01, "Elu": 1.0}.get(op, 0.0))
+                self.layout[y], self.shape[y] = self.layout[x], self.shape[x]
+                self.steps.append(Step(f"{op.lower()}:{y}", lambda t, x=x, y=y, op=op, alpha=alpha: t.__setitem__(y, ops.unary_f32(t[x], op, alpha))))
+                i += 1
+            elif op in ops.BINARY_OPS:
+                self._plan_binary(L)
+                i += 1
+            elif op == "BatchNormalization":
+                self._plan_batchnorm(L)
                 i += 1
             elif op == "QuantizeLinear":
                 self._plan_quantize(L)
@@ -127,7 +145,7 @@ class Session:
             if op in ("Conv", "QLinearConv"):
                 if L.get("group", 1) != 1:
                     return False
-            elif op in ("Relu", "MaxPool"):
+            elif op in ("Relu", "MaxPool", "BatchNormalization") or op in ops.UNARY_OPS:
                 if not self._nhwc_ok(L["Y"], depth + 1):
                     return False
             elif op == "Flatten":
@@ -170,7 +188,7 @@ class Session:
             t[y] = ops.gemm_f32(A, self.w[b], self.w[c] if c else None, transB=1, alpha=alpha, beta=beta, relu=relu)
         self.steps.append(Step(f"gemm:{y}", run, flops=2 * N * K))
 
-    def _plan_conv(self, L, relu, pool, out, quant):
+    def _plan_conv(self, L, relu, pool, out, quant, bn=None):
         mw = self.model.weights
         x, wname, bname = L["X"], L["W"], L.get("B")
         W = mw[wname]
@@ -203,9 +221,18 @@ class Session:
                                             x_zp=x_zp, y_zp=y_zp, relu=relu, pool=pool, x_layout=x_layout,
                                             y_layout=y_layout, w_packed=packed, kernel=(kH, kW))
         else:
+            Bv = mw[bname] if bname else None
+            if bn is not None:
+                # w' = w * s, b' = (b - mean) * s + beta with s = gamma * float(1 / sqrt(var + eps))
+                v = (mw[bn["var"]].astype(np.float32) + np.float32(bn.get("epsilon", 1e-5))).astype(np.float32)
+                s_ = (mw[bn["scale"]].astype(np.float32) * (1.0 / np.sqrt(v.astype(np.float64))).astype(np.float32)).astype(np.float32)
+                W = (W * s_[:, None, None, None]).astype(np.float32)
+                b0 = Bv.astype(np.float32) if Bv is not None else np.zeros(Cout, np.float32)
+                Bv = ((b0 - mw[bn["mean"]].astype(np.float32)) * s_ + mw[bn["bias"]].astype(np.float32)).astype(np.float32)
+                wname, bname = f"{wname}:bn:{out}", f"{out}:bnbias"
             self.w[wname] = ops.conv2d_pack_f32(self._up(W)) if packed else self._up(W)
             if bname:
-                self.w[bname] = self._up(mw[bname])
+                self.w[bname] = self._up(Bv)
 
             def run(t):
                 t[out] = ops.conv2d_f32(t[x], self.w[wname], self.w[bname] if bname else None,
@@ -213,6 +240,54 @@ class Session:
                                         group=group, relu=relu, pool=pool, x_layout=x_layout, y_layout=y_layout,
                                         w_packed=packed, kernel=(kH, kW))
         self.steps.append(Step(f"conv:{out}", run, flops=flops))
+
+    def _plan_binary(self, L):
+        """Add / Sub / Mul / Div with numpy-style broadcasting; an operand may be a constant of the model."""
+        a, b, y, op = L["A"], L["B"], L["Y"], L["op"]
+        mw = self.model.weights
+
+        def operand(name):
+            if name in mw:
+                self.w[name] = self._up(np.ascontiguousarray(mw[name], np.float32))
+                return tuple(mw[name].shape), True
+            if self.layout.get(name, LAYOUT_NCHW) != LAYOUT_NCHW:
+                raise ValueError(f"{op}: operand {name} must be NCHW")
+            return tuple(self.shape[name]), False
+
+        (sa, ca), (sb, cb) = operand(a), operand(b)
+        out = tuple(np.broadcast_shapes(sa, sb))
+        self.layout[y], self.shape[y] = LAYOUT_NCHW, out
+
+        def run(t):
+            A = self.w[a] if ca else t[a]
+            B = self.w[b] if cb else t[b]
+            # the batch dimension of an activation follows the batch actually given to infer()
+            t[y] = ops.binary_f32(A, B, op)
+        self.steps.append(Step(f"{op.lower()}:{y}", run))
+
+    def _plan_batchnorm(self, L):
+        """Inference BatchNormalization; gamma / sqrt(var + eps) is folded on the host with the roundings
+        of the reference's Initialize (float sum, double reciprocal square root, float product)."""
+        x, y = L["X"], L["Y"]
+        mw = self.model.weights
+        eps = np.float32(L.get("epsilon", 1e-5))
+        v = (mw[L["var"]].astype(np.float32) + eps).astype(np.float32)
+        inv = (1.0 / np.sqrt(v.astype(np.float64))).astype(np.float32)
+        key = f"bn:{y}"
+        self.w[key + ":scale"] = self._up((mw[L["scale"]].astype(np.float32) * inv).astype(np.float32))
+        self.w[key + ":bias"] = self._up(mw[L["bias"]].astype(np.float32))
+        self.w[key + ":mean"] = self._up(mw[L["mean"]].astype(np.float32))
+        shp = self.shape[x]
+        Cc = shp[1]
+        HW = int(np.prod(shp[2:], dtype=np.int64)) if len(shp) > 2 else 1
+        layout = self.layout[x]
+        relu = bool(L.get("relu", False))
+        self.layout[y], self.shape[y] = layout, shp
+
+        def run(t):
+            t[y] = ops.batchnorm_f32(t[x], self.w[key + ":scale"], self.w[key + ":bias"], self.w[key + ":mean"],
+                                     t[x].shape[0], Cc, HW, layout=layout, relu=relu)
+        self.steps.append(Step(f"batchnorm:{y}", run))
 
     def _plan_pool(self, L):
         x, y = L["X"], L["Y"]

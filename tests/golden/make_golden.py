@@ -24,7 +24,10 @@ from sofie_b200 import onnx_wire as ow  # noqa: E402
 
 CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutPadding", "ConvWithAutopadSameLower",
          "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "AvgPool", "Softmax1d", "Softmax2d",
-         "Softmax3d", "Softmax4d", "Einsum_matmul"]
+         "Softmax3d", "Softmax4d", "Einsum_matmul",
+         # elementwise family
+         "LinearWithSelu", "LinearWithSigmoid", "LinearWithLeakyRelu", "Add", "Sub", "Mul", "Div", "Neg", "Exp", "Log", "Elu",
+         "Tanh", "Sqrt", "Reciprocal"]
 TEST_NAME = {"Linear_16": "Linear16", "Linear_32": "Linear32", "Linear_64": "Linear64"}
 FLOAT_RE = re.compile(r"[-+]?(?:\d+\.?\d*|\.\d+)(?:[eE][-+]?\d+)?")
 

@@ -51,6 +51,12 @@ class OracleBackend:
     def softmax(self, X, axis):
         return self.o.softmax_f32(X, axis)
 
+    def unary(self, X, op, alpha):
+        return self.o.unary_f32(X, op, alpha)
+
+    def binary(self, A, B, op):
+        return self.o.binary_f32(A, B, op)
+
 
 class CudaBackend:
     """numpy in / numpy out through libSOFIE_cuda (C ABI) on cuda:0."""
@@ -79,6 +85,12 @@ class CudaBackend:
 
     def softmax(self, X, axis):
         return self.ops.softmax_f32(self._d(X), axis).cpu().numpy()
+
+    def unary(self, X, op, alpha):
+        return self.ops.unary_f32(self._d(X), op, alpha).cpu().numpy()
+
+    def binary(self, A, B, op):
+        return self.ops.binary_f32(self._d(A), self._d(B), op).cpu().numpy()
 
 
 def conv_attrs(attrs, kshape):
@@ -130,6 +142,10 @@ def run_fixture(name, manifest, arrays, backend):
                              a.get("count_include_pad", 0))
         elif op == "Softmax":
             y = backend.softmax(t[ins[0]], a.get("axis", -1))
+        elif op in UNARY_FIXTURE_OPS:
+            y = backend.unary(t[ins[0]], op, a.get("alpha", 0.01 if op == "LeakyRelu" else 1.0))
+        elif op in ("Add", "Sub", "Mul", "Div"):
+            y = backend.binary(t[ins[0]], t[ins[1]], op)
         else:
             raise NotImplementedError(op)
         t[n["outputs"][0]] = y
@@ -137,9 +153,13 @@ def run_fixture(name, manifest, arrays, backend):
     return np.asarray(out).ravel()
 
 
+UNARY_FIXTURE_OPS = ("Sigmoid", "Tanh", "LeakyRelu", "Selu", "Elu", "Neg", "Exp", "Log", "Sqrt", "Reciprocal", "Abs")
+
 FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutPadding",
                  "ConvWithAutopadSameLower", "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "AvgPool",
-                 "Softmax1d", "Softmax2d", "Softmax3d", "Softmax4d", "Einsum_matmul"]
+                 "Softmax1d", "Softmax2d", "Softmax3d", "Softmax4d", "Einsum_matmul",
+                 "LinearWithSelu", "LinearWithSigmoid", "LinearWithLeakyRelu", "Add", "Sub", "Mul", "Div", "Neg", "Exp", "Log",
+                 "Elu", "Tanh", "Sqrt", "Reciprocal"]
 
 
 def fixture_to_onnx(name, manifest, arrays):

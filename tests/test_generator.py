@@ -80,3 +80,22 @@ def test_session_without_gpu_throws_the_reference_way():
     m, _ = configs.mlp_f32(batch=4)
     with pytest.raises(RuntimeError, match="SOFIE CUDA"):
         generated.session_from_model(m, "c1_nogpu")
+
+
+def test_batchnorm_is_folded_into_the_convolution_and_emitted_alone_otherwise():
+    m, _ = configs.resblock_f32(batch=2)
+    text = generated.emit(onnx_wire.model_to_onnx(m), "resblock_fold").read_text()
+    assert text.count("sofie_cuda_conv2d_f32(") == 2
+    assert "sofie_cuda_batchnorm_f32(" not in text          # both normalisations live in the conv weights
+    assert text.count("sofie_cuda_binary_f32(") == 2 and "sofie_cuda_unary_f32(" in text
+    # a normalisation that does not follow a convolution stays an operator of its own
+    m2 = configs.Model("bn_alone", "x", (2, 4, 6, 6), [])
+    rng = np.random.default_rng(1)
+    for k in ("g", "b", "mu", "v"):
+        m2.weights[k] = rng.uniform(0.5, 1.5, 4).astype(np.float32)
+    m2.layers.append(dict(op="MaxPool", X="x", Y="p", kernel=(2, 2), strides=(2, 2), pads=(0, 0, 0, 0)))
+    m2.layers.append(dict(op="BatchNormalization", X="p", Y="y", scale="g", bias="b", mean="mu", var="v", relu=True))
+    m2.output_name = "y"
+    text2 = generated.emit(onnx_wire.model_to_onnx(m2), "bn_alone").read_text()
+    assert "sofie_cuda_batchnorm_f32(" in text2 and "BatchNorm" in text2 and "+ Relu" in text2
+    assert "sofie_cuda_relu_f32(" not in text2               # the Relu behind it is fused as the reference does

@@ -201,6 +201,54 @@ def test_qlinear_conv2d_bit_exact(x_nhwc, y_nhwc, packed, pool, x_zp):
     assert len(np.unique(ref)) > 20
 
 
+# ------------------------------------------------------------------------------------ elementwise family
+@pytest.mark.parametrize("op,alpha", [("Sigmoid", 0), ("Tanh", 0), ("LeakyRelu", 0.1), ("Selu", 0), ("Elu", 1.0), ("Elu", 0.5), ("Neg", 0),
+                                      ("Exp", 0), ("Log", 0), ("Sqrt", 0), ("Reciprocal", 0), ("Abs", 0)])
+def test_unary_f32(op, alpha):
+    rng = np.random.default_rng(len(op))
+    for n in (0, 1, 5, 4099, 1 << 18):
+        x = (rng.standard_normal(n) * 3).astype(np.float32)
+        if op in ("Log", "Sqrt"):
+            x = np.abs(x) + np.float32(1e-3)
+        y = ops.unary_f32(dev(x), op, alpha).cpu().numpy()
+        ref = o.unary_f32(x, op, alpha)
+        assert rel_err(y, ref) <= FP32_TOL
+        # device and libm transcendental functions agree to a few ulp; exp(x) - 1 (Selu, Elu) turns an ulp of
+        # exp(x) near 1 into an absolute error of about 1e-7
+        assert np.allclose(y, ref, rtol=2e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("sa,sb", [((6, 5, 4, 3), (6, 5, 4, 3)), ((6, 5, 4, 3), (3,)), ((6, 5, 4, 3), (5, 1, 1)), ((5, 1, 3), (6, 1, 4, 1)),
+                                   ((1,), (7, 9)), ((1025, 33), (1025, 1)), ((0, 4), (4,))])
+@pytest.mark.parametrize("op", ["Add", "Sub", "Mul", "Div"])
+def test_binary_f32_broadcast(sa, sb, op):
+    rng = np.random.default_rng(len(sa) * 10 + len(sb))
+    a = rng.standard_normal(sa).astype(np.float32)
+    b = (rng.standard_normal(sb) + 3).astype(np.float32)
+    y = ops.binary_f32(dev(a), dev(b), op).cpu().numpy()
+    ref = o.binary_f32(a, b, op)
+    assert y.shape == ref.shape
+    assert np.array_equal(y, ref)  # one IEEE operation per element: bit-exact
+    assert np.array_equal(ref, {"Add": a + b, "Sub": a - b, "Mul": a * b, "Div": a / b}[op])
+
+
+@pytest.mark.parametrize("shape,layout,relu", [((4, 16, 8, 8), 0, 0), ((4, 16, 8, 8), 1, 1), ((3, 5), 0, 1), ((2, 7, 9), 0, 0)])
+def test_batchnorm_f32(shape, layout, relu):
+    rng = np.random.default_rng(sum(shape))
+    Cc = shape[1]
+    x = rng.standard_normal(shape).astype(np.float32)
+    scale, bias, mean = (rng.standard_normal(Cc).astype(np.float32) for _ in range(3))
+    var = rng.uniform(0.5, 2.0, Cc).astype(np.float32)
+    ref = o.batchnorm_f32(x, scale, bias, mean, var, 1e-5, bool(relu))
+    folded = o.batchnorm_folded_scale(scale, var, 1e-5)
+    HW = int(np.prod(shape[2:])) if len(shape) > 2 else 1
+    xd = dev(x.transpose(0, 2, 3, 1)) if layout else dev(x)
+    y = ops.batchnorm_f32(xd, dev(folded), dev(bias), dev(mean), shape[0], Cc, HW, layout=layout, relu=bool(relu)).cpu().numpy()
+    if layout:
+        y = y.transpose(0, 3, 1, 2)
+    assert np.array_equal(y, ref)  # same three roundings per element
+
+
 FIRST_LAYER = [
     # N, C, H, W, Cout, x_nhwc, y_nhwc, packed, relu, pool, x_zp
     (5, 1, 64, 64, 32, 0, 1, 1, 1, 2, 0), (3, 3, 32, 32, 16, 0, 1, 1, 1, 0, 0), (2, 1, 20, 36, 12, 0, 0, 0, 1, 2, 7),
