@@ -52,14 +52,15 @@ def build_generator() -> Path:
     return LIBDIR / "sofie_emit"
 
 
-def emit(onnx_bytes: bytes, name: str, batch: int | None = None, workdir: Path | None = None) -> Path:
-    """Parse -> Generate -> OutputGenerated. Returns the path of <name>.hxx (the .dat lies next to it)."""
+def emit(onnx_bytes: bytes, name: str, batch: int | None = None, workdir: Path | None = None, binary: bool = False) -> Path:
+    """Parse -> Generate -> OutputGenerated. Returns the path of <name>.hxx (the .dat, or with binary=True the
+    .bin, lies next to it)."""
     tool = build_generator()
-    work = Path(workdir) if workdir else WORK / (name + "_" + hashlib.sha1(onnx_bytes).hexdigest()[:10])
+    work = Path(workdir) if workdir else WORK / (name + ("_bin_" if binary else "_") + hashlib.sha1(onnx_bytes).hexdigest()[:10])
     work.mkdir(parents=True, exist_ok=True)
     onnx_path, hxx = work / f"{name}.onnx", work / f"{name}.hxx"
     onnx_path.write_bytes(onnx_bytes)
-    cmd = [str(tool), str(onnx_path), str(hxx)] + ([str(batch)] if batch else [])
+    cmd = [str(tool), str(onnx_path), str(hxx)] + ([str(batch)] if batch else []) + (["--binary"] if binary else [])
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"sofie_emit failed: {r.stdout.strip()}")
@@ -135,11 +136,11 @@ class GeneratedSession:
             pass
 
 
-def session_from_model(model, name: str | None = None, batch: int | None = None) -> GeneratedSession:
+def session_from_model(model, name: str | None = None, batch: int | None = None, binary: bool = False) -> GeneratedSession:
     """configs.Model -> ONNX bytes -> generator -> compiled Session."""
     from . import onnx_wire
     name = name or model.name
-    hxx = emit(onnx_wire.model_to_onnx(model), name, batch)
+    hxx = emit(onnx_wire.model_to_onnx(model), name, batch, binary=binary)
     so = compile_session(hxx, name)
     out_elems = None
     # output size from the emitted header: "std::vector<float> ret_0(N);"
@@ -148,4 +149,4 @@ def session_from_model(model, name: str | None = None, batch: int | None = None)
             out_elems = int(line.split("ret_0(")[1].split(")")[0])
     if out_elems is None:
         raise RuntimeError("cannot find the output size in the emitted header")
-    return GeneratedSession(so, hxx.with_suffix(".dat"), out_elems)
+    return GeneratedSession(so, hxx.with_suffix(".bin" if binary else ".dat"), out_elems)

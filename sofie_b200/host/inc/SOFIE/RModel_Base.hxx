@@ -22,9 +22,10 @@ enum class Options {
    kRootBinaryWeightFile = 0x4, // needs ROOT I/O: not available
    kGNN = 0x8,
    kGNNComponent = 0x10,
+   kBinaryWeightFile = 0x40,    // addition: weights in a raw little-endian side file <name>.bin read with one fread per tensor
 };
 
-enum class WeightFileType { None, RootBinary, Text };
+enum class WeightFileType { None, RootBinary, Text, Binary };
 
 std::underlying_type_t<Options> operator|(Options opA, Options opB);
 std::underlying_type_t<Options> operator|(std::underlying_type_t<Options> opA, Options opB);

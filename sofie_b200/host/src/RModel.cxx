@@ -442,6 +442,8 @@ void RModel::Generate(std::underlying_type_t<Options> options, int batchSize, lo
    if (has(Options::kNoWeightFile)) {
       fUseWeightFile = false;
       fWeightFile = WeightFileType::None;
+   } else if (has(Options::kBinaryWeightFile)) {
+      fWeightFile = WeightFileType::Binary;
    }
    Initialize(batchSize, verbose);
    std::string hgname;
@@ -478,6 +480,38 @@ void RModel::GenerateSessionMembers()
 
 void RModel::GenerateWeightReader()
 {
+   if (fWeightFile == WeightFileType::Binary) {
+      // one fread per tensor straight into the host copy; names, types and sizes are checked
+      fGC += "   std::FILE * f = std::fopen(filename.c_str(), \"rb\");\n";
+      fGC += "   if (!f) {\n";
+      fGC += "      throw std::runtime_error(\"sofie failed to open file \" + filename + \" for input weights\");\n";
+      fGC += "   }\n";
+      fGC += "   struct Closer { std::FILE * f; ~Closer() { std::fclose(f); } } closer{f};\n";
+      if (fReadPos > 0) fGC += "   std::fseek(f, " + std::to_string(fReadPos) + ", SEEK_SET);\n";
+      fGC += "   char magic[8]; uint64_t count = 0;\n";
+      fGC += "   if (std::fread(magic, 1, 8, f) != 8 || std::string(magic, 8) != \"SOFIEBW1\" || std::fread(&count, 8, 1, f) != 1 || count != " +
+             std::to_string(fDeviceWeights.size()) + ") {\n";
+      fGC += "      throw std::runtime_error(\"SOFIE: \" + filename + \" is not the binary weight file of this model\");\n";
+      fGC += "   }\n";
+      fGC += "   auto read_tensor = [&](const char * expected, uint32_t type, uint64_t length, void * dst, size_t bytes) {\n";
+      fGC += "      uint32_t nlen = 0, t = 0; uint64_t len = 0, nbytes = 0; char name[512];\n";
+      fGC += "      if (std::fread(&nlen, 4, 1, f) != 1 || nlen >= sizeof(name) || std::fread(name, 1, nlen, f) != nlen)\n";
+      fGC += "         throw std::runtime_error(std::string(\"SOFIE failed to read the tensor name; expected name is \") + expected);\n";
+      fGC += "      if (std::string(name, nlen) != expected)\n";
+      fGC += "         throw std::runtime_error(std::string(\"SOFIE failed to read the correct tensor name; expected name is \") + expected + \" , read \" + std::string(name, nlen));\n";
+      fGC += "      if (std::fread(&t, 4, 1, f) != 1 || std::fread(&len, 8, 1, f) != 1 || std::fread(&nbytes, 8, 1, f) != 1 || t != type || len != length || nbytes != bytes)\n";
+      fGC += "         throw std::runtime_error(std::string(\"SOFIE failed to read the correct tensor size; expected size is \") + std::to_string(length) + \" for \" + expected);\n";
+      fGC += "      if (std::fread(dst, 1, bytes, f) != bytes)\n";
+      fGC += "         throw std::runtime_error(std::string(\"SOFIE failed to read the values for tensor \") + expected);\n";
+      fGC += "      std::fseek(f, (long)((8 - (nlen + bytes) % 8) % 8), SEEK_CUR);\n";
+      fGC += "   };\n";
+      for (auto &n : fDeviceWeights) {
+         const auto &t = fInitializedTensors.at(n);
+         fGC += "   read_tensor(\"tensor_" + n + "\", " + std::to_string((int)t.type()) + ", " + std::to_string(t.length()) + ", " + EMIT::Host(n) +
+                ".data(), " + std::to_string(t.length() * GetTypeSize(t.type())) + ");\n";
+      }
+      return;
+   }
    // same text format as the reference writes and reads (src/SOFIE_core/src/RModel.cxx:970-1018,1121-1158):
    // "tensor_<name> <length>" followed by the values; integer tensors are written as integers
    fGC += "   std::ifstream f;\n";
@@ -513,7 +547,7 @@ void RModel::GenerateWeightReader()
 
 void RModel::GenerateConstructor()
 {
-   if (fUseWeightFile) fGC += "Session(std::string filename =\"" + fName + ".dat\"";
+   if (fUseWeightFile) fGC += "Session(std::string filename =\"" + fName + (fWeightFile == WeightFileType::Binary ? ".bin" : ".dat") + "\"";
    else fGC += "Session(std::string = \"\"";
    for (auto &p : fShapeParams) fGC += ",\n        size_t " + p.first + " = " + p.second;
    fGC += ") {\n";
@@ -656,8 +690,46 @@ void RModel::GenerateSessionCode()
 }
 
 // ---------------------------------------------------------------------------------- weight file, output
+// Binary side file (Options::kBinaryWeightFile), little-endian:
+//   "SOFIEBW1", uint64 tensor count, then per tensor: uint32 name length, the name ("tensor_<name>"),
+//   uint32 ETensorType, uint64 element count, uint64 byte count, the raw values, zero padding to 8 bytes.
+// A text file of C4's four 4096 x 4096 layers is 800 MB and takes minutes to parse; this form is
+// read at the speed of the file system and stores int8 / FP8 tensors in one byte per value.
+static long WriteBinaryWeights(const std::string &filename, const std::set<std::string> &names,
+                               const std::map<std::string, InitializedTensor> &tensors, long readPos)
+{
+   std::ofstream f(filename, (readPos > 0 ? std::ios_base::app : std::ios_base::out) | std::ios_base::binary);
+   if (!f.is_open()) throw std::runtime_error("sofie failed to open file " + filename + " for tensor weight data");
+   auto put = [&](const void *p, size_t n) { f.write(static_cast<const char *>(p), (std::streamsize)n); };
+   put("SOFIEBW1", 8);
+   uint64_t count = names.size();
+   put(&count, 8);
+   for (auto &n : names) {
+      const auto &t = tensors.at(n);
+      std::string tname = "tensor_" + n;
+      uint32_t nlen = (uint32_t)tname.size(), type = (uint32_t)t.type();
+      uint64_t length = t.length(), bytes = length * GetTypeSize(t.type());
+      put(&nlen, 4);
+      put(tname.data(), nlen);
+      put(&type, 4);
+      put(&length, 8);
+      put(&bytes, 8);
+      put(t.data<char>(), bytes);
+      static const char zeros[8] = {0};
+      put(zeros, (8 - (nlen + bytes) % 8) % 8);
+      if (f.fail()) throw std::runtime_error("sofie failed to write tensor data to file for " + n);
+   }
+   long pos = f.tellp();
+   f.close();
+   return pos;
+}
+
 long RModel::WriteInitializedTensorsToFile(std::string filename)
 {
+   if (fWeightFile == WeightFileType::Binary) {
+      if (filename.empty()) filename = fName + ".bin";
+      return WriteBinaryWeights(filename, fDeviceWeights, fInitializedTensors, fReadPos);
+   }
    if (fWeightFile != WeightFileType::Text) return -1;
    if (filename.empty()) filename = fName + ".dat";
    std::ofstream f(filename, fReadPos > 0 ? std::ios_base::app : std::ios_base::out);
@@ -703,12 +775,13 @@ void RModel::OutputGenerated(std::string filename, bool append)
 {
    RModel_Base::OutputGenerated(filename, append);
    if (fUseWeightFile) {
+      const std::string ext = fWeightFile == WeightFileType::Binary ? ".bin" : ".dat";
       if (!filename.empty()) {
          size_t pos = filename.find(".hxx");
-         if (pos != std::string::npos) filename.replace(pos, 4, ".dat");
-         else filename += ".dat";
+         if (pos != std::string::npos) filename.replace(pos, 4, ext);
+         else filename += ext;
       } else {
-         filename = fName + ".dat";
+         filename = fName + ext;
       }
       WriteInitializedTensorsToFile(filename);
    }

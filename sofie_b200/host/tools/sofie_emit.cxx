@@ -1,21 +1,28 @@
-// sofie_emit <model.onnx> <output.hxx> [batch]
+// sofie_emit <model.onnx> <output.hxx> [batch] [--binary]
 // The reference's usage pattern (src/SOFIE_core/README.md:26-57, test/EmitFromONNX.cxx.in:13-22):
 // Parse -> Generate -> OutputGenerated, which writes the header and, next to it, the weight file.
 #include <cstdlib>
 #include <iostream>
+#include <string>
 
 #include "SOFIE/RModelParser_ONNX.hxx"
 
 int main(int argc, char **argv)
 {
    if (argc < 3) {
-      std::cerr << "usage: " << argv[0] << " <model.onnx> <output.hxx> [batch size for parametric inputs]\n";
+      std::cerr << "usage: " << argv[0] << " <model.onnx> <output.hxx> [batch size for parametric inputs] [--binary]\n";
       return 2;
    }
    try {
       SOFIE::RModelParser_ONNX parser;
       SOFIE::RModel model = parser.Parse(argv[1]);
-      model.Generate(SOFIE::Options::kDefault, argc > 3 ? std::atoi(argv[3]) : -1);
+      bool binary = false;
+      int batch = -1;
+      for (int i = 3; i < argc; i++) {
+         if (std::string(argv[i]) == "--binary") binary = true;
+         else batch = std::atoi(argv[i]);
+      }
+      model.Generate(binary ? SOFIE::Options::kBinaryWeightFile : SOFIE::Options::kDefault, batch);
       model.OutputGenerated(argv[2]);
    } catch (const std::exception &e) {
       std::cerr << "sofie_emit: " << e.what() << "\n";

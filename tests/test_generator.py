@@ -99,3 +99,16 @@ def test_batchnorm_is_folded_into_the_convolution_and_emitted_alone_otherwise():
     text2 = generated.emit(onnx_wire.model_to_onnx(m2), "bn_alone").read_text()
     assert "sofie_cuda_batchnorm_f32(" in text2 and "BatchNorm" in text2 and "+ Relu" in text2
     assert "sofie_cuda_relu_f32(" not in text2               # the Relu behind it is fused as the reference does
+
+
+def test_binary_weight_file_option_emits_and_compiles():
+    m, _ = configs.cnn_f32(batch=2)
+    hxx = generated.emit(onnx_wire.model_to_onnx(m), "c2_binary", binary=True)
+    text = hxx.read_text()
+    assert 'Session(std::string filename ="c2_binary.bin"' in text and "SOFIEBW1" in text and "std::fread" in text
+    blob = hxx.with_suffix(".bin").read_bytes()
+    assert blob[:8] == b"SOFIEBW1" and not hxx.with_suffix(".dat").exists()
+    # every weight is stored once, raw: the file is barely larger than the weights themselves
+    nbytes = sum(v.nbytes for v in m.weights.values())
+    assert nbytes <= len(blob) <= nbytes + 4096
+    generated.compile_session(hxx, "c2_binary")

@@ -6,7 +6,7 @@ import pytest
 
 from helpers import FIXTURE_CASES, GOLDEN, fixture_to_onnx, load_fixtures, rel_err
 from oracle import build_ref, run_model
-from sofie_b200 import configs, generated
+from sofie_b200 import configs, generated, onnx_wire
 
 pytestmark = pytest.mark.gpu
 REF = np.load(GOLDEN / "ref_outputs.npz")
@@ -57,3 +57,21 @@ def test_missing_and_truncated_weight_file_throw(cuda_device, tmp_path):
     with pytest.raises(RuntimeError, match="correct tensor name"):
         generated.GeneratedSession(so, tmp_path / "renamed.dat", 160)
     assert s.infer(x).shape == (160,)
+
+
+def test_binary_weight_file_gives_the_same_session(cuda_device, tmp_path):
+    m, x = configs.cnn_f32(batch=4)
+    y_text = generated.session_from_model(m, "c2_b4_text").infer(x)
+    y_bin = generated.session_from_model(m, "c2_b4_bin", binary=True).infer(x)
+    assert np.array_equal(y_text, y_bin)
+    # a text weight file given to a Session generated for the binary form is refused
+    hxx = generated.emit(onnx_wire.model_to_onnx(m), "c2_b4_bin", binary=True)
+    so = generated.compile_session(hxx, "c2_b4_bin")
+    bad = tmp_path / "bad.bin"
+    bad.write_bytes(b"tensor_x 3\n1 2 3\n")
+    with pytest.raises(RuntimeError, match="not the binary weight file"):
+        generated.GeneratedSession(so, bad, y_bin.size)
+    short = tmp_path / "short.bin"
+    short.write_bytes(hxx.with_suffix(".bin").read_bytes()[:4000])
+    with pytest.raises(RuntimeError, match="SOFIE failed to read"):
+        generated.GeneratedSession(so, short, y_bin.size)
