@@ -77,6 +77,10 @@ int sofie_cuda_ctx_h2d(sofie_cuda_ctx *ctx, void *dst_device, const void *src_ho
  * replaces `return std::vector<float>(tensor_y, tensor_y + n)`,
  * reference: src/SOFIE_core/src/RModel.cxx:717-740). */
 int sofie_cuda_ctx_d2h(sofie_cuda_ctx *ctx, void *dst_host, const void *src_device, size_t bytes);
+/* Copies a device result into a pinned host buffer owned by the context (grown on demand) and
+ * returns its address; valid until the next fetch. The emitted infer() builds the vector it
+ * returns (RModel.cxx:744-801 in the reference) from it in one pass. */
+int sofie_cuda_ctx_fetch(sofie_cuda_ctx *ctx, const void *src_device, size_t bytes, void **host);
 int sofie_cuda_ctx_sync(sofie_cuda_ctx *ctx);
 /* Read and clear the device-side status word that kernels with bounded waits set on give-up. */
 int sofie_cuda_ctx_check(sofie_cuda_ctx *ctx);

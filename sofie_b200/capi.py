@@ -75,6 +75,7 @@ SIGNATURES = {
     "sofie_cuda_ctx_upload": [vp, vp, sz, C.POINTER(vp)],
     "sofie_cuda_ctx_h2d": [vp, vp, vp, sz],
     "sofie_cuda_ctx_d2h": [vp, vp, vp, sz],
+    "sofie_cuda_ctx_fetch": [vp, vp, sz, C.POINTER(vp)],
     "sofie_cuda_ctx_sync": [vp],
     "sofie_cuda_ctx_check": [vp],
     "sofie_cuda_ctx_graph_begin": [vp],

@@ -65,6 +65,8 @@ struct sofie_cuda_ctx {
    std::vector<void *> owned;
    void *staging = nullptr; // pinned
    size_t staging_bytes = 0;
+   void *result = nullptr;  // pinned, grown on demand: where sofie_cuda_ctx_fetch lands device results
+   size_t result_bytes = 0;
    cudaGraph_t graph = nullptr;
    cudaGraphExec_t graph_exec = nullptr;
    bool capturing = false;
@@ -169,6 +171,7 @@ int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx)
    for (void *p : ctx->owned) cudaFree(p);
    if (ctx->arena) cudaFree(ctx->arena);
    if (ctx->staging) cudaFreeHost(ctx->staging);
+   if (ctx->result) cudaFreeHost(ctx->result);
    cudaStreamDestroy(ctx->stream);
    delete ctx;
    return SOFIE_CUDA_OK;
@@ -290,6 +293,27 @@ int sofie_cuda_ctx_d2h(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t b
       std::memcpy(static_cast<char *>(dst) + done, ctx->staging, chunk);
       done += chunk;
    }
+   return SOFIE_CUDA_OK;
+}
+
+// Device -> pinned host buffer owned by the context, at full link speed; the caller builds its
+// result (the vector Session::infer returns) from the returned pointer in one pass, instead of
+// zero-filling a vector first and then staging the copy through it. The pointer stays valid until
+// the next fetch on this context.
+int sofie_cuda_ctx_fetch(sofie_cuda_ctx *ctx, const void *src, size_t bytes, void **host)
+{
+   SOFIE_REQUIRE(ctx && src && host, "NULL argument");
+   DeviceGuard guard(ctx->device);
+   if (bytes > ctx->result_bytes) {
+      if (ctx->result) cudaFreeHost(ctx->result);
+      ctx->result = nullptr;
+      ctx->result_bytes = 0;
+      SOFIE_CUDA_TRY(cudaMallocHost(&ctx->result, bytes));
+      ctx->result_bytes = bytes;
+   }
+   if (bytes) SOFIE_CUDA_TRY(cudaMemcpyAsync(ctx->result, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+   SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+   *host = ctx->result;
    return SOFIE_CUDA_OK;
 }
 

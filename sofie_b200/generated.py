@@ -136,17 +136,19 @@ class GeneratedSession:
             pass
 
 
-def session_from_model(model, name: str | None = None, batch: int | None = None, binary: bool = False) -> GeneratedSession:
+def session_from_model(model, name: str | None = None, batch: int | None = None, binary: bool = False,
+                       fp8_scales=None) -> GeneratedSession:
     """configs.Model -> ONNX bytes -> generator -> compiled Session."""
     from . import onnx_wire
     name = name or model.name
-    hxx = emit(onnx_wire.model_to_onnx(model), name, batch, binary=binary)
+    hxx = emit(onnx_wire.model_to_onnx(model, fp8_scales), name, batch, binary=binary)
     so = compile_session(hxx, name)
     out_elems = None
-    # output size from the emitted header: "std::vector<float> ret_0(N);"
-    for line in hxx.read_text().splitlines():
-        if "ret_0(" in line:
-            out_elems = int(line.split("ret_0(")[1].split(")")[0])
+    # output size from the emitted header: "std::vector<float> ret_0(<pointer>, <pointer> + N);"
+    import re
+    found = re.search(r"ret_0\([^;]*?\+ (\d+)\);", hxx.read_text())
+    if found:
+        out_elems = int(found.group(1))
     if out_elems is None:
         raise RuntimeError("cannot find the output size in the emitted header")
     return GeneratedSession(so, hxx.with_suffix(".bin" if binary else ".dat"), out_elems)

@@ -534,7 +534,7 @@ void RModel::GenerateWeightReader()
       fGC += "      std::string err_msg = \"SOFIE failed to read the correct tensor size; expected size is " + len + " , read \" + std::to_string(length) ;\n";
       fGC += "      throw std::runtime_error(err_msg);\n";
       fGC += "    }\n";
-      if (t.type() == ETensorType::INT8 || t.type() == ETensorType::UINT8)
+      if (t.type() == ETensorType::INT8 || t.type() == ETensorType::UINT8 || t.type() == ETensorType::FLOAT8E4M3FN)
          fGC += "   for (size_t i = 0; i < length; ++i) { int v; f >> v; " + EMIT::Host(n) + "[i] = static_cast<" + EMIT::CType(t.type()) + ">(v); }\n";
       else
          fGC += "   for (size_t i = 0; i < length; ++i)\n      f >> " + EMIT::Host(n) + "[i];\n";
@@ -661,9 +661,13 @@ void RModel::GenerateInfer()
    for (size_t i = 0; i < nOut; i++) {
       const std::string &o = fOutputTensorNames[i];
       std::string type = ConvertTypeToString(GetTensorType(o));
-      fGC += "   std::vector<" + type + "> ret_" + std::to_string(i) + "(" + std::to_string(ConvertShapeToLength(GetTensorShape(o))) + ");\n";
-      fGC += "   Check(sofie_cuda_ctx_d2h(fCtx, ret_" + std::to_string(i) + ".data(), " + EMIT::Dev(o) + ", " +
-             ByteCount(GetTensorShape(o), GetTensorType(o)) + "), \"sofie_cuda_ctx_d2h\");\n";
+      // the result lands in the context's pinned buffer; the returned vector is built from it in one pass
+      const std::string idx = std::to_string(i), len = std::to_string(ConvertShapeToLength(GetTensorShape(o)));
+      fGC += "   void * host_ret_" + idx + " = nullptr;\n";
+      fGC += "   Check(sofie_cuda_ctx_fetch(fCtx, " + EMIT::Dev(o) + ", " + ByteCount(GetTensorShape(o), GetTensorType(o)) + ", &host_ret_" + idx +
+             "), \"sofie_cuda_ctx_fetch\");\n";
+      fGC += "   std::vector<" + type + "> ret_" + idx + "(static_cast<const " + type + " *>(host_ret_" + idx + "), static_cast<const " + type +
+             " *>(host_ret_" + idx + ") + " + len + ");\n";
    }
    if (nOut == 1) fGC += "   return ret_0;\n";
    else {
@@ -754,6 +758,7 @@ long RModel::WriteInitializedTensorsToFile(std::string filename)
          for (size_t i = 0; i < length; i++) f << (int)t.data<int8_t>()[i] << (i + 1 < length ? " " : "\n");
          break;
       case ETensorType::UINT8:
+      case ETensorType::FLOAT8E4M3FN: // bit patterns
          for (size_t i = 0; i < length; i++) f << (int)t.data<uint8_t>()[i] << (i + 1 < length ? " " : "\n");
          break;
       case ETensorType::INT32:

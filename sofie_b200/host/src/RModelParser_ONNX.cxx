@@ -15,6 +15,7 @@
 #include "SOFIE/ROperator_BasicUnary.hxx"
 #include "SOFIE/ROperator_BatchNormalization.hxx"
 #include "SOFIE/ROperator_Conv.hxx"
+#include "SOFIE/ROperator_Fp8.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
 #include "SOFIE/ROperator_Pool.hxx"
 #include "SOFIE/ROperator_QLinear.hxx"
@@ -214,8 +215,34 @@ std::unique_ptr<ROperator> ParseQuantizeLinear(RModelParser_ONNX &p, const onnx:
 {
    require_type(p, n.input(0), "QuantizeLinear");
    if (n.input_size() < 3) throw std::runtime_error("SOFIE - QuantizeLinear needs x, y_scale and y_zero_point (uint8 output)");
+   // the type of the zero point selects the output type (ONNX QuantizeLinear, opset 19)
+   if (p.IsRegisteredTensorType(n.input(2)) && p.GetTensorType(n.input(2)) == ETensorType::FLOAT8E4M3FN) {
+      p.RegisterTensorType(n.output(0), ETensorType::FLOAT8E4M3FN);
+      return std::unique_ptr<ROperator>(new ROperator_QuantizeE4M3(n.input(0), n.input(1), n.output(0)));
+   }
    p.RegisterTensorType(n.output(0), ETensorType::UINT8);
    return std::unique_ptr<ROperator>(new ROperator_QuantizeLinear(n.input(0), n.input(1), n.input(2), n.output(0)));
+}
+
+std::unique_ptr<ROperator> ParseCast(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   require_type(p, n.input(0), "Cast");
+   ETensorType to = static_cast<ETensorType>(attr_int(n, "to", 1));
+   p.RegisterTensorType(n.output(0), to);
+   return std::unique_ptr<ROperator>(new ROperator_Cast(to, n.input(0), n.output(0)));
+}
+
+// Custom operator of the FP8 chain (see ROperator_Fp8.hxx): inputs A (E4M3), W (E4M3 constant [N, K]), optional bias;
+// attributes a_scale, w_scale, out_scale (0: bfloat16 output), relu.
+std::unique_ptr<ROperator> ParseFp8Gemm(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   require_type(p, n.input(0), "Fp8Gemm");
+   if (n.input_size() < 2) throw std::runtime_error("SOFIE - Fp8Gemm needs A and W");
+   float out_scale = attr_float(n, "out_scale", 0.f);
+   p.RegisterTensorType(n.output(0), out_scale > 0.f ? ETensorType::FLOAT8E4M3FN : ETensorType::BFLOAT16);
+   return std::unique_ptr<ROperator>(new ROperator_Fp8Gemm(attr_float(n, "a_scale", 1.f), attr_float(n, "w_scale", 1.f), out_scale,
+                                                           attr_int(n, "relu", 0) != 0, n.input(0), n.input(1),
+                                                           n.input_size() > 2 ? n.input(2) : "", n.output(0)));
 }
 
 std::unique_ptr<ROperator> ParseDequantizeLinear(RModelParser_ONNX &p, const onnx::NodeProto &n)
@@ -300,6 +327,8 @@ RModelParser_ONNX::RModelParser_ONNX() noexcept : fOperatorsMapImpl(std::make_un
    RegisterOperator("Mul", ParseBasicBinary<Mul>);
    RegisterOperator("Div", ParseBasicBinary<Div>);
    RegisterOperator("BatchNormalization", ParseBatchNormalization);
+   RegisterOperator("Cast", ParseCast);
+   RegisterOperator("Fp8Gemm", ParseFp8Gemm);
    RegisterOperator("QuantizeLinear", ParseQuantizeLinear);
    RegisterOperator("DequantizeLinear", ParseDequantizeLinear);
    RegisterOperator("QLinearMatMul", ParseQLinearMatMul);
@@ -463,6 +492,7 @@ void RModelParser_ONNX::ParseONNXGraph(RModel &rmodel, const onnx::GraphProto &g
       case ETensorType::INT64: data = tensor_data<int64_t>(t, length); break;
       case ETensorType::UINT8: data = tensor_data<uint8_t>(t, length); break;
       case ETensorType::INT8: data = tensor_data<int8_t>(t, length); break;
+      case ETensorType::FLOAT8E4M3FN: data = tensor_data<uint8_t>(t, length); break; // raw bit patterns
       default: throw std::runtime_error("SOFIE Data type in weight tensor " + t.name() + " not supported!\n");
       }
       rmodel.AddInitializedTensor(t.name(), type, shape, data);

@@ -251,11 +251,25 @@ def read_model(data: bytes):
 
 
 # ------------------------------------------------------------------------------------ Model -> ONNX
-def model_to_onnx(m) -> bytes:
-    """Serialise a sofie_b200.configs.Model (fp32 and int8 operators) as an ONNX file."""
+def e4m3_bytes(x: np.ndarray, scale: float) -> np.ndarray:
+    """E4M3 bit patterns of x / scale: fp32 division, round to nearest even, saturating at +-448 (the
+    quantisation the library applies on the device)."""
+    import ml_dtypes
+    q = (np.asarray(x, np.float32) / np.float32(scale)).astype(np.float32)
+    return np.clip(q, -448.0, 448.0).astype(ml_dtypes.float8_e4m3fn).view(np.uint8)
+
+
+def model_to_onnx(m, fp8_scales=None) -> bytes:
+    """Serialise a sofie_b200.configs.Model as an ONNX file. The FP8 chain (Fp8Gemm layers) needs its calibrated
+    activation scales: it is written as QuantizeLinear to FLOAT8E4M3FN, one custom Fp8Gemm node per layer with
+    E4M3 weights and static scales as attributes, and a final Cast from bfloat16 to float."""
     nodes, inits = [], []
     w = m.weights
     used = set()
+    fp8_layers = [L for L in m.layers if L["op"] == "Fp8Gemm"]
+    if fp8_layers and (fp8_scales is None or len(fp8_scales) != len(fp8_layers)):
+        raise ValueError("the FP8 chain needs one calibrated activation scale per Fp8Gemm layer")
+    fp8_i = 0
 
     def init(name, arr=None):
         if name not in used:
@@ -316,6 +330,24 @@ def model_to_onnx(m) -> bytes:
                                                           attr_ints("strides", L["strides"])]))
             if L.get("relu"):
                 nodes.append(node("Relu", [out], [L["Y"]]))
+        elif op == "Fp8Gemm":
+            a_scale = float(fp8_scales[fp8_i])
+            last = fp8_i + 1 == len(fp8_layers)
+            out_scale = 0.0 if last else float(fp8_scales[fp8_i + 1])
+            src = L["A"] + "_q"
+            if fp8_i == 0:
+                inits.append(tensor(f"fp8s{i}", np.array(a_scale, np.float32)))
+                inits.append(tensor(f"fp8z{i}", np.zeros((), np.uint8), FLOAT8E4M3FN))
+                nodes.append(node("QuantizeLinear", [L["A"], f"fp8s{i}", f"fp8z{i}"], [src]))
+            wq = L["B"] + "_e4m3"
+            inits.append(tensor(wq, e4m3_bytes(w[L["B"]], L["w_scale"]), FLOAT8E4M3FN))
+            ins = [src, wq] + ([init(L["C"])] if L.get("C") else [])
+            out = L["Y"] + ("_bf16" if last else "_q")
+            nodes.append(node("Fp8Gemm", ins, [out], [attr_float("a_scale", a_scale), attr_float("w_scale", L["w_scale"]),
+                                                    attr_float("out_scale", out_scale), attr_int("relu", int(bool(L.get("relu"))))]))
+            if last:
+                nodes.append(node("Cast", [out], [L["Y"]], [attr_int("to", FLOAT)]))
+            fp8_i += 1
         elif op in ("Sigmoid", "Tanh", "Selu", "Neg", "Exp", "Log", "Sqrt", "Reciprocal", "Abs"):
             nodes.append(node(op, [L["X"]], [L["Y"]]))
         elif op in ("LeakyRelu", "Elu"):

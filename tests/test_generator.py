@@ -112,3 +112,16 @@ def test_binary_weight_file_option_emits_and_compiles():
     nbytes = sum(v.nbytes for v in m.weights.values())
     assert nbytes <= len(blob) <= nbytes + 4096
     generated.compile_session(hxx, "c2_binary")
+
+
+def test_fp8_chain_parses_and_emits_through_the_generator():
+    m, x = configs.gemm_chain_fp8(rows=128, width=256, layers=3)
+    scales = configs.calibrate_fp8_scales(m, x)
+    hxx = generated.emit(onnx_wire.model_to_onnx(m, scales), "c4_tiny", binary=True)
+    text = hxx.read_text()
+    assert text.count("sofie_cuda_gemm_e4m3(") == 3 and text.count("sofie_cuda_quantize_e4m3_f32(") == 1
+    assert text.count("sofie_cuda_cast_bf16_f32(") == 1
+    assert re.search(r"std::vector<float>\s+infer\(float\*\s*tensor_x\)", text)
+    generated.compile_session(hxx, "c4_tiny")
+    with pytest.raises(ValueError):
+        onnx_wire.model_to_onnx(m)  # the chain cannot be written without its calibrated scales

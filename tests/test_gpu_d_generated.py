@@ -75,3 +75,15 @@ def test_binary_weight_file_gives_the_same_session(cuda_device, tmp_path):
     short.write_bytes(hxx.with_suffix(".bin").read_bytes()[:4000])
     with pytest.raises(RuntimeError, match="SOFIE failed to read"):
         generated.GeneratedSession(so, short, y_bin.size)
+
+
+def test_fp8_chain_through_generated_session(cuda_device):
+    from sofie_b200 import runner
+    m, x = configs.gemm_chain_fp8(rows=512, width=512, layers=3)
+    scales = configs.calibrate_fp8_scales(m, x)
+    y = generated.session_from_model(m, "c4_r512", binary=True, fp8_scales=scales).infer(x)
+    # the same launches as the Python mirror of the Session: identical bits
+    y_mirror = runner.Session(m, fp8_scales=scales, use_graph=False).infer(x)
+    assert np.array_equal(y, np.asarray(y_mirror, np.float32).ravel())
+    ref = run_model.run(m, x, fp8_scales=scales)
+    assert rel_err(y, ref) <= 2e-2
