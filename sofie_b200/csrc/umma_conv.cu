@@ -497,7 +497,8 @@ constexpr int kPlaneBox = kPatchH * kPatchW * 16;                 // bytes one p
 constexpr int kPlaneStride = (kPlaneBox + 127) / 128 * 128;       // TMA destinations are 128-byte aligned
 constexpr int kPatchMaxStages = 4;
 
-constexpr int kPatchThreads = 18 * 32; // producer, MMA issuer, 8 epilogue + 8 converter warps (fp32) or 16 epilogue warps (int8)
+constexpr int kPatchThreads = 19 * 32; // producer, MMA issuer, 8 epilogue + 8 converter warps (fp32) or 16 epilogue warps (int8), second MMA issuer
+constexpr int kPatchIssuerB = 18;      // warp of the second issuer
 
 struct PatchPlan {
    int chunks;   // weight sub-tiles per tap (rows of cb bytes)
@@ -505,6 +506,8 @@ struct PatchPlan {
    int stages;   // pipeline slots
    uint32_t stage_bytes; // one copy (hi) of the planes of a stage
    uint32_t w_bytes;     // one copy (hi) of all weights
+   int issuers;          // 1 or 2 threads issuing the MMAs (2: tiles taken alternately)
+   int conv_groups;      // fp32: 1 or 2 groups of converter warps (2: slots taken alternately)
 };
 
 // KPS = MMAs (32 bytes of K) per tap and stage, G = stages per tile: a stage carries 2 * KPS planes
@@ -558,7 +561,7 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
    if (threadIdx.x == 0) {
       for (int s = 0; s < kPatchMaxStages; s++) {
          mbar_init(&full_bar[s], 1);
-         mbar_init(&conv_bar[s], CONV_WARPS * 32);
+         mbar_init(&conv_bar[s], CONV_WARPS * 32 / pl.conv_groups); // the converter threads that split one slot
          mbar_init(&empty_bar[s], 1);
       }
       for (int b = 0; b < 2; b++) {
@@ -612,8 +615,14 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             __syncwarp();
          }
       }
-   } else if (warp == 1) {
-      // ---------------- MMA issuer ----------------
+   } else if (warp == 1 || warp == kPatchIssuerB) {
+      // ---------------- MMA issuers ----------------
+      // Two threads of different warps take the tiles of this CTA alternately (issuer 0 the even
+      // ones into TMEM buffer 0, issuer 1 the odd ones into buffer 1): while one waits for its
+      // barriers and commits, the other keeps the tensor pipe fed, which a single thread cannot --
+      // issuing blocks it whenever the pipe's short queue is full, so its own hand-over work
+      // between two tiles leaves the pipe idle.
+      const int issuer = warp == 1 ? 0 : 1;
       if (lane == 0) {
          constexpr uint32_t idesc = make_idesc<KIND>(128, BN);
          constexpr uint32_t idesc_wide = make_idesc<KIND>(128, NACC * BN);
@@ -630,6 +639,18 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          uint32_t ph = 0;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, lt++) {
             const int buf = lt & 1;
+            if (pl.issuers == 2 ? buf != issuer : issuer != 0) {
+               // The other issuer's tile: step over its stages of the ring, but still see each of them
+               // become ready. A parity wait only tells the last two phases of a barrier apart, so a
+               // thread that skipped a phase of a slot it shares with the other issuer could take an
+               // old completion for the one it waits for.
+               if (pl.issuers == 2) {
+                  for (int grp = 0; grp < G && ok; grp++, g++, ring_next(s, ph, S))
+                     ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
+                                                          : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
+               }
+               continue;
+            }
             if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt))) break;
             const uint32_t d = tmem_base + (uint32_t)(buf * NACC * BN);
 #pragma unroll
@@ -663,14 +684,19 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             if (ok) tc_commit(&tmem_full[buf]);
          }
       }
-   } else if (KIND == kTF32 && warp >= 2 + EPI_WARPS) {
+   } else if (KIND == kTF32 && warp >= 2 + EPI_WARPS && warp < 2 + EPI_WARPS + CONV_WARPS) {
       // ---------------- converter warps (kTF32): hi/lo split, weights once, then each slot ----------------
       if constexpr (KIND == kTF32) {
-         constexpr int NT = CONV_WARPS * 32;
-         const int t = threadIdx.x - (2 + EPI_WARPS) * 32;
-         // Splits n16 16-byte groups at src in place (hi) and writes the lo parts lo_off bytes further.
-         // Four independent loads per thread are issued before the first conversion.
-         auto split = [&](unsigned char *src, uint32_t n16, uint32_t lo_off) {
+         // The eight warps work as two groups of four that take the slots of the ring alternately, so
+         // two slots are being split at any time: one slot's chain of load, convert, store, proxy
+         // fence and arrive is latency, not throughput. The weights are split by all eight together.
+         constexpr int NT_ALL = CONV_WARPS * 32, NT_GROUP = NT_ALL / 2;
+         const int t_all = threadIdx.x - (2 + EPI_WARPS) * 32;
+         const bool two_groups = pl.conv_groups == 2;
+         const int group = two_groups ? t_all / NT_GROUP : 0, t_group = two_groups ? t_all % NT_GROUP : t_all;
+         // Splits n16 16-byte groups at src in place (hi) and writes the lo parts lo_off bytes further,
+         // as thread t of NT. Four independent loads per thread are issued before the first conversion.
+         auto split = [&](unsigned char *src, uint32_t n16, uint32_t lo_off, int t, int NT) {
             float4 *base = reinterpret_cast<float4 *>(src);
             const uint32_t lo4 = lo_off / 16;
             for (uint32_t i0 = t; i0 < n16; i0 += 4 * NT) {
@@ -695,25 +721,28 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          };
          bool ok = SOFIE_PROF_WAIT(mbar_wait(&w_full, 0, &abort_flag, status, kStatusWaitFull, 0x4000));
          if (ok) {
-            for (int item = 0; item < 9 * CHUNKS; item++) split(w_smem + (size_t)item * COPIES * B_TILE, B_TILE / 16, B_TILE);
+            for (int item = 0; item < 9 * CHUNKS; item++) split(w_smem + (size_t)item * COPIES * B_TILE, B_TILE / 16, B_TILE, t_all, NT_ALL);
             fence_proxy_async();
             mbar_arrive(&w_conv);
          }
          int g = 0, s = 0;
-      uint32_t ph = 0;
+         uint32_t ph = 0;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x) {
             for (int grp = 0; grp < G; grp++, g++, ring_next(s, ph, S)) {
+               // every slot's arrival is observed (see the issuers: no phase of a shared barrier is skipped),
+               // the other group's slots are then left to it
                if (!SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g))) {
                   ok = false;
                   break;
                }
-               split(slot_hi(s), pl.stage_bytes / 16, pl.stage_bytes);
+               if (two_groups && (g & 1) != group) continue;
+               split(slot_hi(s), pl.stage_bytes / 16, pl.stage_bytes, t_group, two_groups ? NT_GROUP : NT_ALL);
                fence_proxy_async();
                mbar_arrive(&conv_bar[s]);
             }
          }
       }
-   } else {
+   } else if (warp < 2 + EPI_WARPS) {
       // ---------------- epilogue warps, from warp 2 on ----------------
       const int e = warp - 2;
       const int lane_base = (warp & 3) * 32;
@@ -733,7 +762,7 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       }
    }
-   SOFIE_PROF_REPORT(warp == 0 ? "producer" : (warp == 1 ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
+   SOFIE_PROF_REPORT(warp == 0 ? "producer" : ((warp == 1 || warp == kPatchIssuerB) ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
    tc_fence_before();
    __syncthreads();
    if (warp == 1) {
@@ -756,6 +785,10 @@ static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, c
    pl.chunks = row_bytes / pl.cb;
    pl.w_bytes = (uint32_t)(9 * pl.chunks * BN * pl.cb);
    pl.stage_bytes = (uint32_t)(2 * KPS * kPlaneStride);
+   static const int issuers = [] { const char *e = getenv("SOFIE_CUDA_CONV_ISSUERS"); return e && atoi(e) == 1 ? 1 : 2; }();
+   static const int groups = [] { const char *e = getenv("SOFIE_CUDA_CONV_GROUPS"); return e && atoi(e) == 1 ? 1 : 2; }();
+   pl.issuers = issuers;
+   pl.conv_groups = groups;
    const long budget = 200 * 1024 - (long)COPIES * pl.w_bytes;
    const long per_stage = (long)COPIES * pl.stage_bytes;
    pl.stages = (int)(budget / per_stage);
