@@ -290,12 +290,6 @@ typedef struct sofie_qconv2d_desc {
 } sofie_qconv2d_desc;
 int sofie_cuda_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *desc, const uint8_t *X, const int8_t *W,
                               const float *mult, const int32_t *bias, uint8_t *Y);
-/* QuantizeLinear(x_scale, desc->x_zp) of a float input fused in front of a first-layer QLinearConv
- * (3x3, stride 1, pad 1, at most 4 input and 64 output channels): the quantised input tensor is
- * never materialised. Same result as sofie_cuda_quantize_u8 followed by sofie_cuda_qlinear_conv2d;
- * other shapes return SOFIE_CUDA_ERR_UNSUPPORTED. No counterpart in the reference. */
-int sofie_cuda_quantize_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *desc, float x_scale, const float *X, const int8_t *W,
-                                       const float *mult, const int32_t *bias, uint8_t *Y);
 int sofie_cuda_qconv2d_pack_i8(void *stream, const sofie_qconv2d_desc *desc, const int8_t *W, int8_t *Wpacked);
 /* MaxPool 2-D on uint8 (integer max), no padding. */
 int sofie_cuda_maxpool2d_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W,

@@ -1,7 +1,6 @@
 // extern "C" entry points of the contractions: argument validation, choice between the tcgen05
 // kernels and the CUDA-core kernels, and the host-side preparation of requantisation tables.
 #include "contract.cuh"
-#include <cstdlib>
 
 #include <vector>
 
@@ -60,9 +59,6 @@ int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *d, const float 
    SOFIE_REQUIRE(A && B && Y, "NULL tensor");
    cudaStream_t s = as_stream(stream);
    // few rows, few columns, long K: split K over the grid instead of running on two or three SMs
-   static const bool rowdot = [] { const char *e = getenv("SOFIE_CUDA_ROWDOT"); return !e || atoi(e) != 0; }();
-   if (rowdot && forced_engine() != SOFIE_ENGINE_TCGEN05 && rowdot_shape_ok(*d) && ceil_div(d->M, 128) < 32)
-      return launch_gemm_f32_rowdot(s, *d, A, B, C, Y);
    if (forced_engine() != SOFIE_ENGINE_TCGEN05 && splitk_shape_ok(*d) && ceil_div(d->M, 128) < 32)
       return launch_gemm_f32_splitk_auto(s, *d, A, B, C, Y);
    return dispatch([&] { return launch_gemm_f32_umma(s, *d, A, B, C, Y); },
@@ -149,24 +145,6 @@ int sofie_cuda_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *d, const u
    cudaStream_t s = as_stream(stream);
    return dispatch([&] { return launch_qconv2d_umma(s, g, X, W, mult, bias, d->x_zp, d->y_zp, Y); },
                    [&] { return launch_qconv2d_simt(s, g, X, W, mult, bias, d->x_zp, d->y_zp, Y); });
-}
-
-int sofie_cuda_quantize_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *d, float x_scale, const float *X, const int8_t *W,
-                                       const float *mult, const int32_t *bias, uint8_t *Y)
-{
-   SOFIE_REQUIRE(d && X && W && mult && Y, "NULL argument");
-   SOFIE_REQUIRE(x_scale > 0.f, "the input scale must be positive");
-   SOFIE_REQUIRE(d->x_zp >= 0 && d->x_zp <= 255 && d->y_zp >= 0 && d->y_zp <= 255, "zero point out of range");
-   ConvGeom g;
-   int rc = conv_geometry(g, d->N, d->C, d->H, d->W, d->Cout, d->kH, d->kW, d->pad_h, d->pad_w, d->stride_h, d->stride_w, 1,
-                          1, 1, d->x_layout, d->y_layout, d->w_packed, d->relu, d->pool);
-   if (rc) return rc;
-   if (d->N == 0) return SOFIE_CUDA_OK;
-   rc = launch_quantize_qconv2d_first(as_stream(stream), g, X, x_scale, W, mult, bias, d->x_zp, d->y_zp, Y);
-   if (rc < 0)
-      return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "the fused QuantizeLinear + QLinearConv takes 3x3, stride 1, pad 1 layers with at most 4 input "
-                                              "and 64 output channels; quantise first and call sofie_cuda_qlinear_conv2d otherwise");
-   return rc;
 }
 
 int sofie_cuda_gemm_e4m3(void *stream, const sofie_fp8_gemm_desc *d, const uint8_t *A, const uint8_t *W,

@@ -66,14 +66,6 @@ __device__ __forceinline__ int requant_u8(int acc, float mult, int y_zp, int rel
    return q;
 }
 
-// ONNX QuantizeLinear to uint8: q = saturate(round_half_even(x / scale) + zp), the division in fp32.
-__device__ __forceinline__ uint8_t quant_u8(float x, float scale, int zp)
-{
-   float r = rintf(__fdiv_rn(x, scale));
-   r = fminf(fmaxf(r, (float)(0 - zp)), (float)(255 - zp));
-   return (uint8_t)(__float2int_rn(r) + zp);
-}
-
 __device__ __forceinline__ float relu_ref(float v)
 {
    // The reference's `x > 0 ? x : 0`: NaN and -0 both become +0.

@@ -31,12 +31,8 @@ int launch_qconv2d_umma(cudaStream_t, const ConvGeom &, const uint8_t *, const i
 int launch_conv2d_f32_first(cudaStream_t, const ConvGeom &, const float *, const float *, const float *, float *);
 int launch_qconv2d_first(cudaStream_t, const ConvGeom &, const uint8_t *, const int8_t *, const float *, const int32_t *,
                          int x_zp, int y_zp, uint8_t *);
-int launch_quantize_qconv2d_first(cudaStream_t, const ConvGeom &, const float *, float x_scale, const int8_t *, const float *,
-                                  const int32_t *, int x_zp, int y_zp, uint8_t *);
 // split-K skinny GEMM (splitk_gemm.cu)
 bool splitk_shape_ok(const sofie_gemm_f32_desc &);
-bool rowdot_shape_ok(const sofie_gemm_f32_desc &);
-int launch_gemm_f32_rowdot(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *, float *);
 int launch_gemm_f32_splitk(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *, float *,
                            float *scratch, size_t scratch_floats);
 int launch_gemm_f32_splitk_auto(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *,

@@ -44,12 +44,9 @@ __device__ __forceinline__ void first_tile_origin(const ConvGeom &g, long long t
 }
 
 // ------------------------------------------------------------------------------------------------
-// TX = uint8_t: the input is already quantised. TX = float: the QuantizeLinear in front of the layer is
-// applied while the tile is staged (q = saturate(rne(x / x_scale) + x_zp)), so the quantised input
-// tensor is never written to memory nor read back.
-template <int C, int POOL, typename TX>
+template <int C, int POOL>
 __global__ void __launch_bounds__(kFirstThreads)
-qconv3x3_first_kernel(ConvGeom g, const TX *__restrict__ X, float x_scale, const int8_t *__restrict__ Wt, const float *__restrict__ mult,
+qconv3x3_first_kernel(ConvGeom g, const uint8_t *__restrict__ X, const int8_t *__restrict__ Wt, const float *__restrict__ mult,
                       const int32_t *__restrict__ bias, int x_zp, int y_zp, uint8_t *__restrict__ Y, long long num_tiles,
                       int tiles_x, int tiles_y)
 {
@@ -113,8 +110,7 @@ qconv3x3_first_kernel(ConvGeom g, const TX *__restrict__ X, float x_scale, const
          uint8_t v = (uint8_t)x_zp;
          if (i < C * TS * TS && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W) {
             const size_t xi = g.x_nhwc ? (((size_t)n * g.H + ih) * g.W + iw) * C + c : (((size_t)n * C + c) * g.H + ih) * g.W + iw;
-            if constexpr (sizeof(TX) == 4) v = quant_u8(__ldg(X + xi), x_scale, x_zp);
-            else v = __ldg(X + xi);
+            v = __ldg(X + xi);
          }
          staged[j] = v;
       }
@@ -368,17 +364,16 @@ FirstGrid first_grid(const ConvGeom &g, int units_x, int units_y, int tile_units
 
 } // namespace
 
-// All return -1 when the shape is not a first-layer shape (the caller then takes the general kernel).
-template <typename TX>
-static int launch_qconv_first(cudaStream_t s, const ConvGeom &g, const TX *X, float x_scale, const int8_t *W, const float *mult,
-                              const int32_t *bias, int x_zp, int y_zp, uint8_t *Y)
+// Both return -1 when the shape is not a first-layer shape (the caller then takes the general kernel).
+int launch_qconv2d_first(cudaStream_t s, const ConvGeom &g, const uint8_t *X, const int8_t *W, const float *mult, const int32_t *bias,
+                         int x_zp, int y_zp, uint8_t *Y)
 {
    if (!first_layer_shape(g)) return -1;
    const FirstGrid fg = first_grid(g, g.pW, g.pH, 16, 8);
    if (fg.num_tiles == 0) return SOFIE_CUDA_OK;
-#define SOFIE_FIRST_Q(CC, PP)                                                                                                          \
-   qconv3x3_first_kernel<CC, PP, TX><<<fg.blocks, kFirstThreads, 0, s>>>(g, X, x_scale, W, mult, bias, x_zp, y_zp, Y, fg.num_tiles, \
-                                                                         fg.tiles_x, fg.tiles_y)
+#define SOFIE_FIRST_Q(CC, PP)                                                                                                   \
+   qconv3x3_first_kernel<CC, PP><<<fg.blocks, kFirstThreads, 0, s>>>(g, X, W, mult, bias, x_zp, y_zp, Y, fg.num_tiles, fg.tiles_x, \
+                                                                     fg.tiles_y)
    const int pp = g.pool == 2 ? 2 : 1;
    switch (g.C * 10 + pp) {
    case 11: SOFIE_FIRST_Q(1, 1); break;
@@ -394,19 +389,6 @@ static int launch_qconv_first(cudaStream_t s, const ConvGeom &g, const TX *X, fl
    SOFIE_LAUNCH_CHECK("qconv3x3_first_kernel");
    set_last_engine(SOFIE_ENGINE_SIMT);
    return SOFIE_CUDA_OK;
-}
-
-int launch_qconv2d_first(cudaStream_t s, const ConvGeom &g, const uint8_t *X, const int8_t *W, const float *mult, const int32_t *bias,
-                         int x_zp, int y_zp, uint8_t *Y)
-{
-   return launch_qconv_first<uint8_t>(s, g, X, 1.f, W, mult, bias, x_zp, y_zp, Y);
-}
-
-// QuantizeLinear(x_scale, x_zp) fused in front of the layer: X is the float tensor.
-int launch_quantize_qconv2d_first(cudaStream_t s, const ConvGeom &g, const float *X, float x_scale, const int8_t *W, const float *mult,
-                                  const int32_t *bias, int x_zp, int y_zp, uint8_t *Y)
-{
-   return launch_qconv_first<float>(s, g, X, x_scale, W, mult, bias, x_zp, y_zp, Y);
 }
 
 int launch_conv2d_f32_first(cudaStream_t s, const ConvGeom &g, const float *X, const float *W, const float *bias, float *Y)

@@ -195,6 +195,12 @@ int launch_transpose(cudaStream_t s, const T *in, T *out, int batch, int rows, i
 }
 
 // ---------------------------------------------------------------- (de)quantise, casts ------------
+__device__ __forceinline__ uint8_t quant_u8(float x, float scale, int zp)
+{
+   float r = rintf(__fdiv_rn(x, scale));
+   r = fminf(fmaxf(r, (float)(0 - zp)), (float)(255 - zp));
+   return (uint8_t)(__float2int_rn(r) + zp);
+}
 
 __global__ void quantize_u8_kernel(const float *__restrict__ X, uint8_t *__restrict__ Y, size_t n, float scale, int zp,
                                    bool vec)

@@ -94,82 +94,6 @@ __global__ void gemm_f32_splitk_reduce_kernel(sofie_gemm_f32_desc d, int splits,
    }
 }
 
-// The same shapes with enough rows to fill the GPU on their own (M >= 128): one block per output
-// row, no scratch and no second pass. The 256 threads of a block stride K with 16-byte loads of the
-// A row and of every B row (B comes from L2, it is the same for all blocks); the partial sums are
-// reduced by shuffles and one shared-memory step, in a fixed order.
-template <bool TB>
-__global__ void __launch_bounds__(256)
-gemm_f32_rowdot_kernel(sofie_gemm_f32_desc d, const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ C,
-                       float *__restrict__ Y)
-{
-   __shared__ float s_part[8][kSplitKMaxN];
-   const int m = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-   const int N = d.N, K = d.K;
-   const float *a = A + (size_t)m * K;
-   const bool vec = TB && (K % 4 == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && ((reinterpret_cast<uintptr_t>(B) & 15) == 0);
-   float acc[kSplitKMaxN];
-#pragma unroll
-   for (int n = 0; n < kSplitKMaxN; n++) acc[n] = 0.f;
-   if (vec) {
-#pragma unroll 2
-      for (int k = threadIdx.x * 4; k < K; k += 1024) {
-         const float4 av = *reinterpret_cast<const float4 *>(a + k);
-#pragma unroll
-         for (int n = 0; n < kSplitKMaxN; n++) {
-            if (n < N) {
-               const float4 bv = *reinterpret_cast<const float4 *>(B + (size_t)n * K + k);
-               acc[n] = fmaf(av.x, bv.x, acc[n]);
-               acc[n] = fmaf(av.y, bv.y, acc[n]);
-               acc[n] = fmaf(av.z, bv.z, acc[n]);
-               acc[n] = fmaf(av.w, bv.w, acc[n]);
-            }
-         }
-      }
-   } else {
-      for (int k = threadIdx.x; k < K; k += 256) {
-         const float av = a[k];
-#pragma unroll
-         for (int n = 0; n < kSplitKMaxN; n++)
-            if (n < N) acc[n] = fmaf(av, TB ? B[(size_t)n * K + k] : B[(size_t)k * N + n], acc[n]);
-      }
-   }
-#pragma unroll
-   for (int n = 0; n < kSplitKMaxN; n++) {
-      if (n < N) {
-         float v = acc[n];
-         for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-         if (lane == 0) s_part[warp][n] = v;
-      }
-   }
-   __syncthreads();
-   if (threadIdx.x < N) {
-      const int n = threadIdx.x;
-      float sum = 0.f;
-#pragma unroll
-      for (int w = 0; w < 8; w++) sum += s_part[w][n];
-      float y = d.alpha * sum;
-      if (d.bias_kind == 1) y += d.beta * C[n];
-      else if (d.bias_kind == 2) y += d.beta * C[(size_t)m * N + n];
-      Y[(size_t)m * N + n] = d.relu ? relu_ref(y) : y;
-   }
-}
-
-bool rowdot_shape_ok(const sofie_gemm_f32_desc &d)
-{
-   return !d.transA && d.N <= kSplitKMaxN && d.K >= 1024 && d.M >= 128 && d.M <= 65535;
-}
-
-int launch_gemm_f32_rowdot(cudaStream_t s, const sofie_gemm_f32_desc &d, const float *A, const float *B, const float *C, float *Y)
-{
-   if (!rowdot_shape_ok(d)) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "not a row-per-block GEMM shape");
-   if (d.transB) gemm_f32_rowdot_kernel<true><<<d.M, 256, 0, s>>>(d, A, B, C, Y);
-   else gemm_f32_rowdot_kernel<false><<<d.M, 256, 0, s>>>(d, A, B, C, Y);
-   SOFIE_LAUNCH_CHECK("gemm_f32_rowdot_kernel");
-   set_last_engine(SOFIE_ENGINE_SIMT);
-   return SOFIE_CUDA_OK;
-}
-
 bool splitk_shape_ok(const sofie_gemm_f32_desc &d)
 {
    return !d.transA && d.N <= kSplitKMaxN && d.K >= 1024 && (long long)d.M * d.N <= (1 << 16);

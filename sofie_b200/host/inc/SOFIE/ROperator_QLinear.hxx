@@ -59,11 +59,6 @@ public:
       fOutputTensorNames = {fNY};
    }
    EOpKind Kind() const override { return EOpKind::Quantize; }
-   // read by the model plan when it fuses this operator into the first-layer convolution behind it
-   const std::string &InputName() const { return fNX; }
-   const std::string &OutputName() const { return fNY; }
-   float Scale() const { return fScale; }
-   int ZeroPoint() const { return fZp; }
    std::vector<ETensorType> TypeInference(std::vector<ETensorType>) override { return {ETensorType::UINT8}; }
    std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override { return {input[0]}; }
    void Initialize(RModel &model) override
@@ -261,8 +256,6 @@ class ROperator_QLinearConv final : public ROperator {
    bool fRelu = false, fPacked = false;
    int fPool = 0;
    ELayout fLayoutX = ELayout::NCHW, fLayoutY = ELayout::NCHW;
-   std::string fNXFloat;  // set when the QuantizeLinear in front is applied by the kernel itself
-   float fQuantScale = 0.f;
 
 public:
    ROperator_QLinearConv(std::string autopad, std::vector<size_t> dilations, size_t group, std::vector<size_t> kernelShape,
@@ -298,20 +291,6 @@ public:
       fNOut = o;
       fOutputTensorNames = {fNOut};
    }
-   const std::string &InputName() const { return fNX; }
-   int InputZeroPoint() const { return fXZp; }
-   // the shapes of the first-layer kernel, which can quantise its float input while staging it
-   bool IsFirstLayerShape() const
-   {
-      return fShapeX.size() == 4 && fShapeX[1] <= 4 && fShapeW[0] <= 64 && fAttr.kH == 3 && fAttr.kW == 3 && fAttr.padH == 1 &&
-             fAttr.padW == 1 && fAttr.sH == 1 && fAttr.sW == 1 && fAttr.group == 1;
-   }
-   void FuseQuantize(const std::string &floatInput, float scale)
-   {
-      fNXFloat = floatInput;
-      fQuantScale = scale;
-      fInputTensorNames = {fNXFloat, fNW};
-   }
    std::vector<ETensorType> TypeInference(std::vector<ETensorType>) override { return {ETensorType::UINT8}; }
    std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override
    {
@@ -343,7 +322,7 @@ public:
    }
    void PlanDevice(RModel &model) override
    {
-      fLayoutX = model.GetTensorLayout(model.ResolveAlias(fNXFloat.empty() ? fNX : fNXFloat));
+      fLayoutX = model.GetTensorLayout(model.ResolveAlias(fNX));
       fShapeOut = model.GetTensorShape(fNOut);
       fLayoutY = model.CanStayNHWC(fNOut) ? ELayout::NHWC : ELayout::NCHW;
       model.SetTensorLayout(fNOut, fLayoutY);
@@ -390,21 +369,16 @@ public:
    std::string Generate(std::string OpName) override
    {
       std::stringstream out;
-      out << "\n" << SP << "//----  operator " << (fNXFloat.empty() ? "" : "QuantizeLinear + ") << "QLinearConv op_" << OpName << (fRelu ? " + Relu" : "") << (fPool ? " + MaxPool2x2" : "") << " -> "
+      out << "\n" << SP << "//----  operator QLinearConv op_" << OpName << (fRelu ? " + Relu" : "") << (fPool ? " + MaxPool2x2" : "") << " -> "
           << fNOut << " " << ConvertShapeToString(fShapeOut) << (fLayoutY == ELayout::NHWC ? " (NHWC)" : "") << "\n";
       out << SP << "{\n";
       out << SP << SP << "const sofie_qconv2d_desc d = {" << fShapeX[0] << ", " << fShapeX[1] << ", " << fShapeX[2] << ", " << fShapeX[3]
           << ", " << fShapeW[0] << ", " << fAttr.kH << ", " << fAttr.kW << ", " << fAttr.padH << ", " << fAttr.padW << ", " << fAttr.sH
           << ", " << fAttr.sW << ", " << (int)fLayoutX << ", " << (int)fLayoutY << ", " << (fPacked ? 1 : 0) << ", " << fXZp << ", "
           << fYZp << ", " << (fRelu ? 1 : 0) << ", " << fPool << "};\n";
-      if (!fNXFloat.empty())
-         out << EMIT::Call(SP + SP, "sofie_cuda_quantize_qlinear_conv2d(fStream, &d, " + EMIT::FloatLit(fQuantScale) + ", " + EMIT::Dev(fNXFloat) +
-                                       ", " + EMIT::Dev(fNWdev) + ", " + EMIT::Dev(fNMult) + ", " +
-                                       (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNCorr)) + ", " + EMIT::Dev(fNOut) + ")");
-      else
-         out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_conv2d(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNWdev) + ", " +
-                                       EMIT::Dev(fNMult) + ", " + (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNCorr)) + ", " +
-                                       EMIT::Dev(fNOut) + ")");
+      out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_conv2d(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNWdev) + ", " +
+                                    EMIT::Dev(fNMult) + ", " + (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNCorr)) + ", " +
+                                    EMIT::Dev(fNOut) + ")");
       out << SP << "}\n";
       return out.str();
    }

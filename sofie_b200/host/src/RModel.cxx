@@ -301,18 +301,6 @@ void RModel::PlanDevice()
    for (auto &opp : fOperators) {
       ROperator *op = opp.get();
       if (op->IsFusedAway()) continue;
-      if (op->Kind() == EOpKind::Quantize) {
-         // QuantizeLinear whose only reader is a first-layer QLinearConv with the same zero point: the
-         // convolution kernel quantises its float input itself, the uint8 tensor is never written
-         if (auto *q = dynamic_cast<ROperator_QuantizeLinear *>(op))
-            if (ROperator *next = single_consumer(q->OutputName()))
-               if (auto *qconv = dynamic_cast<ROperator_QLinearConv *>(next))
-                  if (qconv->InputName() == q->OutputName() && qconv->IsFirstLayerShape() && qconv->InputZeroPoint() == q->ZeroPoint()) {
-                     qconv->FuseQuantize(q->InputName(), q->Scale());
-                     q->SetFusedAway();
-                  }
-         continue;
-      }
       if (op->Kind() == EOpKind::Conv || op->Kind() == EOpKind::QLinearConv) {
          auto *fconv = dynamic_cast<ROperator_Conv<float> *>(op);
          auto *qconv = dynamic_cast<ROperator_QLinearConv *>(op);

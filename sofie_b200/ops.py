@@ -224,8 +224,7 @@ def qlinear_matmul(A, W, mult, corr, *, w_is_nk=True, y_zp=0, relu=False):
 
 
 def qlinear_conv2d(X, W, mult, bias=None, *, shape=None, pad=(0, 0), stride=(1, 1), x_zp=0, y_zp=0, relu=False,
-                   pool=0, x_layout=LAYOUT_NCHW, y_layout=LAYOUT_NCHW, w_packed=False, kernel=None, x_scale=None):
-    """x_scale given: X is the float tensor and QuantizeLinear(x_scale, x_zp) is fused in front of the layer."""
+                   pool=0, x_layout=LAYOUT_NCHW, y_layout=LAYOUT_NCHW, w_packed=False, kernel=None):
     N, Cin, H, Wd = shape if shape is not None else X.shape
     if w_packed:
         Cout, kH, kW = W.shape[0], kernel[0], kernel[1]
@@ -238,10 +237,7 @@ def qlinear_conv2d(X, W, mult, bias=None, *, shape=None, pad=(0, 0), stride=(1, 
     Y = torch.empty(yshape, dtype=torch.uint8, device=X.device)
     d = capi.QConv2dDesc(N, Cin, H, Wd, Cout, kH, kW, pad[0], pad[1], stride[0], stride[1], x_layout, y_layout,
                          int(w_packed), int(x_zp), int(y_zp), int(relu), pool)
-    if x_scale is not None:
-        capi.call("sofie_cuda_quantize_qlinear_conv2d", _stream(), C.byref(d), float(x_scale), _p(X), _p(W), _p(mult), _p(bias), _p(Y))
-    else:
-        capi.call("sofie_cuda_qlinear_conv2d", _stream(), C.byref(d), _p(X), _p(W), _p(mult), _p(bias), _p(Y))
+    capi.call("sofie_cuda_qlinear_conv2d", _stream(), C.byref(d), _p(X), _p(W), _p(mult), _p(bias), _p(Y))
     return Y
 
 

@@ -35,7 +35,6 @@ class Session:
         self.nhwc = nhwc
         self.fp8_scales = fp8_scales
         self.w = {}
-        self.fused_quant = {}  # quantised tensor that is never materialised -> (float source, scale)
         self.steps: list[Step] = []
         self.layout = {model.input_name: LAYOUT_NCHW}
         self.shape = {model.input_name: tuple(model.input_shape)}  # logical (NCHW / row-major) shapes
@@ -116,14 +115,7 @@ class Session:
                 self._plan_batchnorm(L)
                 i += 1
             elif op == "QuantizeLinear":
-                nxt = self._consumers(L["Y"])
-                if len(nxt) == 1 and nxt[0]["op"] == "QLinearConv" and L["Y"] != self.model.output_name and \
-                        self._first_layer_shape(nxt[0], self.shape[L["X"]]) and nxt[0]["x_zp"] == L["zp"]:
-                    # the quantisation is applied by the first-layer kernel while it stages its input tile
-                    self.fused_quant[L["Y"]] = (L["X"], L["scale"])
-                    self.layout[L["Y"]], self.shape[L["Y"]] = self.layout[L["X"]], self.shape[L["X"]]
-                else:
-                    self._plan_quantize(L)
+                self._plan_quantize(L)
                 i += 1
             elif op == "DequantizeLinear":
                 x, y, s, zp = L["X"], L["Y"], L["scale"], L["zp"]
@@ -141,12 +133,6 @@ class Session:
             else:
                 raise NotImplementedError(f"operator {op} is outside the dense-contraction path")
         del mw
-
-    def _first_layer_shape(self, L, xshape):
-        """Shapes of the first-layer kernels: 3x3, stride 1, pad 1, group 1, at most 4 input and 64 output channels."""
-        W = self.model.weights[L["W"]]
-        return len(xshape) == 4 and xshape[1] <= 4 and W.shape[0] <= 64 and tuple(W.shape[2:]) == (3, 3) and \
-            tuple(L["pads"]) == (1, 1, 1, 1) and tuple(L["strides"]) == (1, 1) and L.get("group", 1) == 1
 
     def _nhwc_ok(self, name, depth=0):
         if name == self.model.output_name or depth > 8:
@@ -228,13 +214,12 @@ class Session:
                                              mw.get(bname) if bname else None, self.dev)
             self.w[wname + ":mult"], self.w[wname + ":bias"] = mult, (corr if bname else None)
             x_zp, y_zp = L["x_zp"], L["y_zp"]
-            src, x_scale = self.fused_quant.get(x, (x, None))
 
             def run(t):
-                t[out] = ops.qlinear_conv2d(t[src], self.w[wname], self.w[wname + ":mult"], self.w[wname + ":bias"],
-                                            shape=(t[src].shape[0], C, H, Wd), pad=(pads[0], pads[1]), stride=strides,
+                t[out] = ops.qlinear_conv2d(t[x], self.w[wname], self.w[wname + ":mult"], self.w[wname + ":bias"],
+                                            shape=(t[x].shape[0], C, H, Wd), pad=(pads[0], pads[1]), stride=strides,
                                             x_zp=x_zp, y_zp=y_zp, relu=relu, pool=pool, x_layout=x_layout,
-                                            y_layout=y_layout, w_packed=packed, kernel=(kH, kW), x_scale=x_scale)
+                                            y_layout=y_layout, w_packed=packed, kernel=(kH, kW))
         else:
             Bv = mw[bname] if bname else None
             if bn is not None:

@@ -125,11 +125,3 @@ def test_fp8_chain_parses_and_emits_through_the_generator():
     generated.compile_session(hxx, "c4_tiny")
     with pytest.raises(ValueError):
         onnx_wire.model_to_onnx(m)  # the chain cannot be written without its calibrated scales
-
-
-def test_quantize_is_fused_into_the_first_layer_convolution():
-    m, _ = configs.cnn_i8(batch=4)
-    text = generated.emit(onnx_wire.model_to_onnx(m), "c5_fusedq").read_text()
-    assert text.count("sofie_cuda_quantize_qlinear_conv2d(") == 1   # QuantizeLinear + conv0 in one launch
-    assert "sofie_cuda_quantize_u8(" not in text
-    assert text.count("sofie_cuda_qlinear_conv2d(") == 3

@@ -36,10 +36,7 @@ def test_reference_golden_vectors(name):
 
 @pytest.mark.parametrize("M,N,K,tA,tB,bias", [(1, 1, 1, 0, 0, 0), (37, 29, 53, 0, 0, 1), (64, 128, 64, 0, 1, 1),
                                               (130, 70, 257, 1, 1, 2), (5, 300, 17, 1, 0, 0), (1024, 10, 128, 0, 1, 1),
-                                              (256, 10, 4096, 0, 1, 1),
-                                              # skinny shapes: split-K below 128 rows, one block per row from there on
-                                              (24, 10, 4096, 0, 1, 1), (100, 16, 1500, 0, 0, 2), (300, 7, 2050, 0, 1, 2),
-                                              (129, 16, 1025, 0, 0, 1), (640, 1, 8192, 0, 1, 0)])
+                                              (256, 10, 4096, 0, 1, 1)])
 def test_gemm_f32(M, N, K, tA, tB, bias):
     rng = np.random.default_rng(M * 7 + N)
     A = rng.standard_normal((K, M) if tA else (M, K)).astype(np.float32)
@@ -280,39 +277,6 @@ def test_first_layer_qconv_bit_exact(case):
         y = y.transpose(0, 3, 1, 2)
     assert np.array_equal(y, ref)
     assert len(np.unique(ref)) > 20
-
-
-@pytest.mark.parametrize("case", FIRST_LAYER)
-def test_first_layer_qconv_with_fused_quantize(case):
-    N, C, H, W, Cout, x_nhwc, y_nhwc, packed, relu, pool, x_zp = case
-    rng = np.random.default_rng(sum(case) + 5)
-    Xf = (rng.standard_normal((N, C, H, W)) * 3).astype(np.float32)
-    Xf[0, 0, 0, :4] = [1e9, -1e9, 0.025, 0.075]  # saturation and ties of the rounding
-    x_scale = 0.05
-    Wt = rng.integers(-127, 128, (Cout, C, 3, 3)).astype(np.int8)
-    ws = rng.uniform(0.001, 0.01, Cout).astype(np.float32)
-    bias = rng.integers(-1000, 1000, Cout).astype(np.int32)
-    y_scale = x_scale * 0.005 * 128 * 3 * np.sqrt(C)
-    Xq = o.quantize_u8(Xf, x_scale, x_zp)
-    ref = o.qlinear_conv2d(Xq, x_scale, x_zp, Wt, ws, y_scale, 10, bias=bias, pad=(1, 1), relu=bool(relu))
-    if pool:
-        ref = o.maxpool2d_u8(ref)
-    mult = dev(o.requant_multiplier(x_scale, ws, y_scale))
-    Xd = dev(Xf.transpose(0, 2, 3, 1)) if x_nhwc else dev(Xf)
-    Wd = ops.qconv2d_pack_i8(dev(Wt)) if packed else dev(Wt)
-    y = ops.qlinear_conv2d(Xd, Wd, mult, dev(bias), shape=Xf.shape, pad=(1, 1), x_zp=x_zp, y_zp=10, relu=bool(relu), pool=pool,
-                           x_layout=x_nhwc, y_layout=y_nhwc, w_packed=bool(packed), kernel=(3, 3), x_scale=x_scale).cpu().numpy()
-    if y_nhwc:
-        y = y.transpose(0, 3, 1, 2)
-    assert np.array_equal(y, ref)
-
-
-def test_fused_quantize_refuses_other_shapes():
-    X = torch.zeros((1, 8, 8, 8), device="cuda")
-    W = torch.zeros((4, 8, 3, 3), dtype=torch.int8, device="cuda")
-    with pytest.raises(capi.SofieCudaError) as e:
-        ops.qlinear_conv2d(X, W, torch.ones(4, device="cuda"), None, pad=(1, 1), x_scale=0.1)
-    assert e.value.status == capi.ERR_UNSUPPORTED
 
 
 @pytest.mark.parametrize("case", FIRST_LAYER)
