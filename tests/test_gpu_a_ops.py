@@ -36,7 +36,10 @@ def test_reference_golden_vectors(name):
 
 @pytest.mark.parametrize("M,N,K,tA,tB,bias", [(1, 1, 1, 0, 0, 0), (37, 29, 53, 0, 0, 1), (64, 128, 64, 0, 1, 1),
                                               (130, 70, 257, 1, 1, 2), (5, 300, 17, 1, 0, 0), (1024, 10, 128, 0, 1, 1),
-                                              (256, 10, 4096, 0, 1, 1)])
+                                              (256, 10, 4096, 0, 1, 1),
+                                              # skinny shapes of the split-K kernel: ragged K, both B layouts, full bias
+                                              (24, 10, 4096, 0, 1, 1), (100, 16, 1500, 0, 0, 2), (300, 7, 2050, 0, 1, 2),
+                                              (129, 16, 1025, 0, 0, 1), (640, 1, 8192, 0, 1, 0)])
 def test_gemm_f32(M, N, K, tA, tB, bias):
     rng = np.random.default_rng(M * 7 + N)
     A = rng.standard_normal((K, M) if tA else (M, K)).astype(np.float32)

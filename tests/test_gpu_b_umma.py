@@ -176,3 +176,24 @@ def test_qlinear_conv3x3_tcgen05_bit_exact(case):
     assert ops.last_engine() == capi.ENGINE_TCGEN05
     assert np.array_equal(y.cpu().numpy().transpose(0, 3, 1, 2), ref)
     assert len(np.unique(ref)) > 20
+
+
+@pytest.mark.parametrize("case", [(3, 32, 32, 32, 64), (2, 64, 16, 16, 64), (4, 1, 32, 32, 16), (2, 64, 8, 8, 128)])
+def test_qconv_pool_with_negative_multipliers(case):
+    """A negative requantisation multiplier makes the requantisation decreasing in the accumulator, so the
+    kernels must not pool the raw accumulators first; they detect it and pool the finished values."""
+    N, C, H, W, Cout = case
+    if C <= 4:
+        ops.set_engine(0)  # the first-layer kernel is a CUDA-core kernel; this file forces tcgen05 otherwise
+    rng = np.random.default_rng(sum(case))
+    X = rng.integers(0, 256, (N, C, H, W)).astype(np.uint8)
+    Wt = rng.integers(-127, 128, (Cout, C, 3, 3)).astype(np.int8)
+    ws = (rng.uniform(0.001, 0.01, Cout) * rng.choice([-1.0, 1.0], Cout)).astype(np.float32)
+    assert (ws < 0).any() and (ws > 0).any()
+    y_scale = 0.02 * 0.005 * 128 * 3 * np.sqrt(C)
+    ref = o.maxpool2d_u8(o.qlinear_conv2d(X, 0.02, 0, Wt, ws, y_scale, 100, pad=(1, 1), relu=False))
+    mult = dev(o.requant_multiplier(0.02, ws, y_scale))
+    y = ops.qlinear_conv2d(dev(X.transpose(0, 2, 3, 1)), ops.qconv2d_pack_i8(dev(Wt)), mult, None, shape=X.shape, pad=(1, 1),
+                           x_zp=0, y_zp=100, relu=False, pool=2, x_layout=1, y_layout=1, w_packed=True, kernel=(3, 3)).cpu().numpy()
+    assert np.array_equal(y.transpose(0, 3, 1, 2), ref)
+    assert len(np.unique(ref)) > 20
