@@ -6,7 +6,7 @@ with a tiny extern "C" wrapper each and linked against the multithreaded OpenBLA
 the scipy wheel. Everything lands in oracle/_ref/ (git-ignored; it travels to the GPU box as
 built files). Needs the reference checkout; on a machine without it the prebuilt files are used.
 
-usage: python oracle/build_ref.py [/root/reference]
+usage: python oracle/build_ref.py [path of the reference checkout]
 """
 from __future__ import annotations
 

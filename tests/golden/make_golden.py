@@ -6,7 +6,7 @@ Sources (read as data, in the container that has the reference checkout):
   <ref>/src/SOFIE_core/test/input_models/references/<Name>.ref.hxx   expected outputs
   <ref>/src/SOFIE_core/test/TestCustomModelsFromONNX.cxx             the inputs (all-ones / iota / literals)
 
-Run:  python tests/golden/make_golden.py [/root/reference]
+Run:  python tests/golden/make_golden.py [path of the reference checkout]
 The tests only read the two generated files; they never touch the reference checkout.
 """
 from __future__ import annotations
