@@ -199,6 +199,45 @@ int sofie_cuda_pool2d_f32(void *stream, const sofie_pool2d_desc *desc, const flo
  * (reference: ROperator_Softmax.hxx:53-184). */
 int sofie_cuda_softmax_f32(void *stream, const float *X, float *Y, size_t outer, size_t axis_len, size_t inner);
 
+/* Fused multi-layer perceptron: Y = L_{n-1}(... L_0(X)) with L_l(x) = act(x W_l^T + b_l), one launch
+ * for the whole chain of Gemm (+ Relu) operators (reference: one ROperator_Gemm::Generate,
+ * ROperator_Gemm.hxx:292-390, per layer). For small layers only: every width <= SOFIE_MLP_MAX_WIDTH
+ * and sofie_mlp_smem_bytes(desc) <= SOFIE_MLP_MAX_SMEM (all weights, padded, plus three activation
+ * tiles in shared memory); otherwise SOFIE_CUDA_ERR_UNSUPPORTED and the caller issues one
+ * sofie_cuda_gemm_f32 per layer. W and B are HOST arrays of `layers` device pointers (B or B[l] may
+ * be NULL); w_is_nk[l] = 1 when W_l is stored [dims[l+1]][dims[l]] (ONNX Gemm with transB = 1), 0 for
+ * [dims[l]][dims[l+1]]. X is [M, dims[0]], Y is [M, dims[layers]]. 16-byte aligned pointers, [N][K]
+ * weights and widths that are multiples of 4 take the fast staging path; everything else is
+ * correct but staged element by element. */
+#define SOFIE_MLP_MAX_LAYERS 8
+#define SOFIE_MLP_MAX_WIDTH 256
+#define SOFIE_MLP_MAX_SMEM (200 * 1024)
+typedef struct sofie_mlp_desc {
+   int32_t M;
+   int32_t layers;
+   int32_t dims[SOFIE_MLP_MAX_LAYERS + 1];
+   int32_t relu[SOFIE_MLP_MAX_LAYERS];
+   int32_t w_is_nk[SOFIE_MLP_MAX_LAYERS];
+} sofie_mlp_desc;
+int sofie_cuda_mlp_f32(void *stream, const sofie_mlp_desc *desc, const float *X, const float *const *W, const float *const *B, float *Y);
+/* Shared memory the fused kernel needs for a chain (independent of M): host arithmetic only, so that a
+ * code generator can decide between the fused call and one GEMM per layer without a GPU.
+ * Rows are padded to a multiple of 4 floats whose quarter is odd (bank spreading). */
+static inline int32_t sofie_mlp_padded_ld(int32_t k) { return 4 * ((((k + 3) >> 2) + 1) | 1); }
+static inline size_t sofie_mlp_smem_bytes(const sofie_mlp_desc *d)
+{
+   size_t floats = 0;
+   int32_t maxact = 0, l;
+   for (l = 0; l < d->layers; l++) {
+      const int32_t np = (d->dims[l + 1] + 31) & ~31;
+      floats += (size_t)np * sofie_mlp_padded_ld(d->dims[l]) + np;
+      if (d->dims[l + 1] > maxact) maxact = d->dims[l + 1];
+   }
+   floats += 32 * (size_t)sofie_mlp_padded_ld(d->dims[0]) + 2 * 32 * (size_t)sofie_mlp_padded_ld(maxact);
+   return floats * sizeof(float);
+}
+size_t sofie_cuda_mlp_f32_smem(const sofie_mlp_desc *desc); /* the same value, as an exported symbol */
+
 /* Unary operators, y[i] = f(x[i]). The formulas are the ones the reference emits
  * (ROperator_Sigmoid.hxx:59, ROperator_Tanh.hxx:60, ROperator_LeakyRelu.hxx:73, ROperator_Selu.hxx:59,
  * ROperator_Elu.hxx:71 -- including its `alpha * exp(x) - 1` for x < 0 --, ROperator_BasicUnary.hxx).

@@ -165,8 +165,9 @@ def main():
         text, blob = description(m)
         (REF_OUT / f"{name}.txt").write_text(text)
         blob.tofile(REF_OUT / f"{name}.f32")
+        # the reference's generator prints the tensors it broadcasts: kept out of the build log
         subprocess.run([str(REF_OUT / "ref_emit"), str(REF_OUT / f"{name}.txt"), str(REF_OUT / f"{name}.f32"), str(REF_OUT)],
-                       check=True)
+                       check=True, stdout=subprocess.DEVNULL)
         os.remove(REF_OUT / f"{name}.f32")
         (REF_OUT / f"{name}_wrap.cxx").write_text(WRAPPER.format(name=name))
         obj = REF_OUT / f"{name}_wrap.o"

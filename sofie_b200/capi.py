@@ -48,6 +48,10 @@ class QConv2dDesc(C.Structure):
                                    "x_layout", "y_layout", "w_packed", "x_zp", "y_zp", "relu", "pool")]
 
 
+class MlpDesc(C.Structure):
+    _fields_ = [("M", i32), ("layers", i32), ("dims", i32 * 9), ("relu", i32 * 8), ("w_is_nk", i32 * 8)]
+
+
 class BinaryDesc(C.Structure):
     _fields_ = [("op", i32), ("shape", C.c_int64 * 4), ("a_stride", C.c_int64 * 4), ("b_stride", C.c_int64 * 4)]
 
@@ -92,6 +96,7 @@ SIGNATURES = {
     "sofie_cuda_relu_f32": [vp, vp, vp, sz],
     "sofie_cuda_pool2d_f32": [vp, C.POINTER(Pool2dDesc), vp, vp],
     "sofie_cuda_softmax_f32": [vp, vp, vp, sz, sz, sz],
+    "sofie_cuda_mlp_f32": [vp, C.POINTER(MlpDesc), vp, C.POINTER(vp), C.POINTER(vp), vp],
     "sofie_cuda_unary_f32": [vp, i32, f32, vp, vp, sz],
     "sofie_cuda_binary_f32": [vp, C.POINTER(BinaryDesc), vp, vp, vp],
     "sofie_cuda_batchnorm_f32": [vp, C.POINTER(BatchNormDesc), vp, vp, vp, vp, vp],
@@ -115,6 +120,8 @@ SIGNATURES = {
     "sofie_cuda_gemm_e4m3": [vp, C.POINTER(Fp8GemmDesc), vp, vp, vp, vp, vp],
 }
 STRING_GETTERS = {"sofie_cuda_strerror": [C.c_int], "sofie_cuda_last_error": []}
+SIZE_GETTERS = {"sofie_cuda_mlp_f32_smem": [C.POINTER(MlpDesc)]}
+MLP_MAX_LAYERS, MLP_MAX_WIDTH, MLP_MAX_SMEM = 8, 256, 200 * 1024
 
 _lib = None
 
@@ -140,6 +147,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = C.c_char_p
+    for name, args in SIZE_GETTERS.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = C.c_size_t
     if lib.sofie_cuda_abi_version() != 1:
         raise RuntimeError("libSOFIE_cuda ABI version mismatch")
     _lib = lib

@@ -705,8 +705,9 @@ static int launch_umma_gemm(cudaStream_t s, const void *A, const void *B, const 
    rc = make_tensor_map(&tmB, dt, 2, B, dimsB, stride, boxB, 128);
    if (rc) return rc;
    if constexpr (KIND != kTF32) {
-      // wide outputs with enough 256 x 256 tiles for every pair of SMs
-      if (pair_enabled() && N >= 256 && ceil_div(N, kPairBN) * ceil_div(M, 2 * kBM) >= kNumSMs / 2) {
+      // wide outputs with enough 256 x 256 tiles to keep every pair of SMs busy for several rounds: with one or two
+      // tiles per pair the fill of the deeper pipeline and the uneven last round cost more than the pair saves
+      if (pair_enabled() && N >= 256 && ceil_div(N, kPairBN) * ceil_div(M, 2 * kBM) >= 4 * (kNumSMs / 2)) {
          CUtensorMap tmBh;
          uint32_t boxBh[2] = {(uint32_t)kStageK, (uint32_t)kBM};
          rc = make_tensor_map(&tmBh, dt, 2, B, dimsB, stride, boxBh, 128);

@@ -26,6 +26,9 @@ private:
    int_t fAttrTransB = 0;
    std::string fNA, fNB, fNC, fNY;
    std::string fNBdev, fNCdev; // prepared copies used by the emitted call
+   bool fPlainInput = true;     // false when A is the flattening of an NHWC activation (K axis permuted)
+   std::vector<ROperator_Gemm<T> *> fChain; // the layers behind this one that its fused call covers
+   std::string fNYChain;
    EActivationType fActivation = EActivationType::UNDEFINED;
    std::vector<size_t> fShapeA, fShapeB, fShapeC, fShapeY;
    size_t fM = 0, fN = 0, fK = 0;
@@ -56,6 +59,26 @@ public:
 
    EOpKind Kind() const override { return EOpKind::Gemm; }
    bool AcceptsNHWC(const std::string &input) const override { return input == fNA && !fAttrTransA; }
+   // ---- fused chain of small layers (sofie_cuda_mlp_f32): the head of a chain emits one call for all its layers ----
+   const std::string &InputName() const { return fNA; }
+   size_t WidthIn() const { return fK; }
+   size_t WidthOut() const { return fN; }
+   size_t Rows() const { return fM; }
+   // Largest batch for the fused kernel: fp32 FMA out of shared memory beats one tensor-core GEMM launch per
+   // layer only while those launches are latency bound (measured cross-over between 2048 and 4096 rows).
+   static constexpr size_t kMlpFusedMaxRows = 2048;
+   // valid after PlanDevice: a plain x W^T (+ b) (+ Relu) with constant weights on a row-major input
+   bool MlpFusable() const
+   {
+      return fPlainInput && fNBdev != fNB && fAttrAlpha == 1.f && !fAttrTransA && (fBiasKind == 0 || (fBiasKind == 1 && fAttrBeta == 1.f)) &&
+             fK <= 256 && fN <= 256 && fM <= kMlpFusedMaxRows && fShapeA.size() == 2;
+   }
+   void AbsorbChain(const std::vector<ROperator_Gemm<T> *> &tail)
+   {
+      fChain = tail;
+      fNYChain = tail.back()->fNY;
+      fOutputTensorNames = {fNYChain};
+   }
    void SetActivation(EActivationType a) { fActivation = a; }
    void SetOutputName(const std::string &y) { fNY = y; fOutputTensorNames = {fNY}; }
    const std::string &OutputName() const { return fNY; }
@@ -123,6 +146,7 @@ public:
          for (size_t k = 0; k < fK; k++) kperm[k] = k;
          std::string owner = model.ResolveAlias(fNA);
          if (model.GetTensorLayout(owner) == ELayout::NHWC) {
+            fPlainInput = false;
             auto s4 = model.GetTensorShape(owner); // logical N,C,H,W
             if (s4.size() != 4 || s4[1] * s4[2] * s4[3] != fK)
                throw std::runtime_error("SOFIE Gemm Op: NHWC input " + fNA + " does not flatten to K");
@@ -181,6 +205,28 @@ public:
       if (fShapeA.empty() || fShapeB.empty() || fShapeY.empty())
          throw std::runtime_error("SOFIE Gemm Op called to Generate without being initialized first");
       std::stringstream out;
+      if (!fChain.empty()) {
+         // one launch for the whole chain: widths, Relu flags and the device pointers of every layer
+         std::vector<const ROperator_Gemm<T> *> layers{this};
+         layers.insert(layers.end(), fChain.begin(), fChain.end());
+         out << "\n" << SP << "//--------- fused MLP " << opName << ": " << layers.size() << " Gemm layers, [" << fM << "," << fK << "] -> ["
+             << fM << "," << layers.back()->fN << "]\n";
+         out << SP << "{\n";
+         std::string dims = std::to_string(fK), relu, nk, w, b;
+         for (size_t l = 0; l < layers.size(); l++) {
+            dims += ", " + std::to_string(layers[l]->fN);
+            relu += (l ? ", " : "") + std::string(layers[l]->fActivation == EActivationType::RELU ? "1" : "0");
+            nk += (l ? ", " : "") + std::string("1");
+            w += (l ? ", " : "") + EMIT::Dev(layers[l]->fNBdev);
+            b += (l ? ", " : "") + (layers[l]->fBiasKind ? EMIT::Dev(layers[l]->fNCdev) : std::string("nullptr"));
+         }
+         out << SP << SP << "const sofie_mlp_desc d = {" << fM << ", " << layers.size() << ", {" << dims << "}, {" << relu << "}, {" << nk << "}};\n";
+         out << SP << SP << "const float * const w[] = {" << w << "};\n";
+         out << SP << SP << "const float * const b[] = {" << b << "};\n";
+         out << EMIT::Call(SP + SP, "sofie_cuda_mlp_f32(fStream, &d, " + EMIT::Dev(fNA) + ", w, b, " + EMIT::Dev(fNYChain) + ")");
+         out << SP << "}\n";
+         return out.str();
+      }
       out << "\n" << SP << "//--------- Gemm " << opName << ": [" << fM << "," << fK << "] x [" << fK << "," << fN << "]\n";
       out << SP << "{\n";
       out << SP << SP << "const sofie_gemm_f32_desc d = {" << fM << ", " << fN << ", " << fK << ", " << fAttrTransA << ", "

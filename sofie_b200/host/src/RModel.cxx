@@ -10,6 +10,7 @@
 #include <limits>
 
 #include "SOFIE/Emit.hxx"
+#include "sofie_cuda.h" // sofie_mlp_smem_bytes: host arithmetic only, nothing of the library is linked
 #include "SOFIE/ROperator_BatchNormalization.hxx"
 #include "SOFIE/ROperator_Conv.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
@@ -349,6 +350,32 @@ void RModel::PlanDevice()
    }
    for (auto &op : fOperators)
       if (!op->IsFusedAway()) op->PlanDevice(*this);
+   // Chains of small Gemm layers, each read only by the next: one fused launch (the layers keep their weights
+   // in shared memory and the activations never leave the SM). Needs what PlanDevice prepared.
+   for (auto &opp : fOperators) {
+      auto *head = dynamic_cast<ROperator_Gemm<float> *>(opp.get());
+      if (!head || head->IsFusedAway() || !head->MlpFusable()) continue;
+      std::vector<ROperator_Gemm<float> *> tail;
+      // the library's own arithmetic decides whether the layers' weights fit in shared memory
+      sofie_mlp_desc d = {};
+      d.layers = 1;
+      d.dims[0] = static_cast<int32_t>(head->WidthIn());
+      d.dims[1] = static_cast<int32_t>(head->WidthOut());
+      ROperator_Gemm<float> *last = head;
+      while (d.layers < SOFIE_MLP_MAX_LAYERS) {
+         ROperator *next = single_consumer(last->OutputName());
+         auto *g = dynamic_cast<ROperator_Gemm<float> *>(next);
+         if (!g || g->IsFusedAway() || g->InputName() != last->OutputName() || !g->MlpFusable() || g->Rows() != head->Rows()) break;
+         d.dims[d.layers + 1] = static_cast<int32_t>(g->WidthOut());
+         d.layers++;
+         if (sofie_mlp_smem_bytes(&d) > SOFIE_MLP_MAX_SMEM) break;
+         tail.push_back(g);
+         last = g;
+      }
+      if (tail.empty()) continue;
+      head->AbsorbChain(tail);
+      for (auto *g : tail) g->SetFusedAway();
+   }
 }
 
 // Step 4: liveness-based first-fit placement in one arena (256-byte aligned slices).

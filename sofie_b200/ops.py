@@ -111,6 +111,32 @@ def softmax_f32(X, axis=-1):
     return Y
 
 
+def mlp_desc(M, dims, relu, w_is_nk):
+    L = len(dims) - 1
+    return capi.MlpDesc(M, L, (capi.i32 * 9)(*(list(dims) + [0] * (8 - L))), (capi.i32 * 8)(*([int(r) for r in relu] + [0] * (8 - L))),
+                        (capi.i32 * 8)(*([int(n) for n in w_is_nk] + [0] * (8 - L))))
+
+
+def mlp_fits(dims):
+    """Whether a chain of layers with these widths is within what the fused MLP kernel takes (host arithmetic)."""
+    if not 2 <= len(dims) <= capi.MLP_MAX_LAYERS + 1 or max(dims) > capi.MLP_MAX_WIDTH or min(dims) < 1:
+        return False
+    d = mlp_desc(0, dims, [0] * (len(dims) - 1), [0] * (len(dims) - 1))
+    return capi.load().sofie_cuda_mlp_f32_smem(C.byref(d)) <= capi.MLP_MAX_SMEM
+
+
+def mlp_f32(X, weights, biases, relu, w_is_nk):
+    """Fused chain of Gemm (+ Relu) layers; weights[l] is [N, K] when w_is_nk[l] else [K, N]."""
+    L = len(weights)
+    dims = [X.shape[1]] + [(W.shape[0] if nk else W.shape[1]) for W, nk in zip(weights, w_is_nk)]
+    Y = torch.empty((X.shape[0], dims[-1]), dtype=torch.float32, device=X.device)
+    d = mlp_desc(X.shape[0], dims, relu, w_is_nk)
+    Wp = (C.c_void_p * L)(*[_p(W) for W in weights])
+    Bp = (C.c_void_p * L)(*[(_p(b) if b is not None else None) for b in biases])
+    capi.call("sofie_cuda_mlp_f32", _stream(), C.byref(d), _p(X), Wp, Bp, _p(Y))
+    return Y
+
+
 UNARY_OPS = {"Sigmoid": 0, "Tanh": 1, "LeakyRelu": 2, "Selu": 3, "Elu": 4, "Neg": 5, "Exp": 6, "Log": 7, "Sqrt": 8,
              "Reciprocal": 9, "Abs": 10}
 BINARY_OPS = {"Add": 0, "Sub": 1, "Mul": 2, "Div": 3}

@@ -15,7 +15,13 @@ import numpy as np
 import torch
 
 from . import ops
+from . import capi
 from .capi import LAYOUT_NCHW, LAYOUT_NHWC
+
+# Largest batch that goes to the fused MLP kernel: it computes with fp32 FMA out of shared memory, which beats one
+# tensor-core GEMM launch per layer only while those launches are latency bound (measured cross-over between 2048
+# and 4096 rows for 64-128-128-10).
+MLP_FUSED_MAX_ROWS = 2048
 
 
 class Step:
@@ -62,8 +68,13 @@ class Session:
             L = layers[i]
             op = L["op"]
             if op == "Gemm":
-                self._plan_gemm(L)
-                i += 1
+                chain = self._mlp_chain(i)
+                if len(chain) >= 2:
+                    self._plan_mlp(chain)
+                    i += len(chain)
+                else:
+                    self._plan_gemm(L)
+                    i += 1
             elif op in ("Conv", "QLinearConv"):
                 # fuse Conv [+ Relu] [+ MaxPool 2x2 stride 2 no pad] when each intermediate has one consumer
                 j, relu, pool, out = i + 1, bool(L.get("relu", False)), 0, L["Y"]
@@ -166,6 +177,54 @@ class Session:
         _, c, h, w = shp
         assert c * h * w == K
         return np.arange(K).reshape(c, h, w).transpose(1, 2, 0).reshape(-1)
+
+    def _mlp_chain(self, i):
+        """Consecutive Gemm layers starting at layer i that the fused MLP kernel takes in one launch: each feeds only
+        the next, plain x W^T + b (alpha = beta = 1 or no bias), widths <= 256, weights within shared memory, and a
+        batch of at most MLP_FUSED_MAX_ROWS rows."""
+        layers, mw = self.model.layers, self.model.weights
+        chain, dims = [], []
+        j = i
+        while j < len(layers) and len(chain) < capi.MLP_MAX_LAYERS:
+            L = layers[j]
+            if L["op"] != "Gemm" or L.get("alpha", 1.0) != 1.0 or (L.get("C") and L.get("beta", 1.0) != 1.0):
+                break
+            if chain and L["A"] != chain[-1]["Y"]:
+                break
+            W = mw[L["B"]]
+            N, K = (W.shape if L.get("transB", 0) else W.shape[::-1])
+            if not chain:
+                shp = self.shape.get(L["A"])
+                if shp is None or len(shp) != 2 or shp[0] > MLP_FUSED_MAX_ROWS or self._flatten_perm(L["A"], K) is not None:
+                    break
+                dims = [K]
+            if (L.get("C") and mw[L["C"]].shape != (N,)) or not ops.mlp_fits(dims + [N]):
+                break
+            dims.append(N)
+            chain.append(L)
+            if L["Y"] == self.model.output_name or len(self._consumers(L["Y"])) != 1:
+                break
+            j += 1
+        return chain
+
+    def _plan_mlp(self, chain):
+        mw = self.model.weights
+        names = []
+        for L in chain:
+            self.w[L["B"]] = self._up(mw[L["B"]])  # kept in the model's own layout; the kernel transposes while staging
+            if L.get("C"):
+                self.w[L["C"]] = self._up(mw[L["C"]])
+            names.append((L["B"], L.get("C")))
+        relu = [bool(L.get("relu", False)) for L in chain]
+        nk = [bool(L.get("transB", 0)) for L in chain]
+        a, y = chain[0]["A"], chain[-1]["Y"]
+        N_out = mw[chain[-1]["B"]].shape[0 if nk[-1] else 1]
+        self.layout[y], self.shape[y] = LAYOUT_NCHW, (self.shape[a][0], N_out)
+        flops = sum(2 * int(np.prod(mw[L["B"]].shape)) for L in chain)
+
+        def run(t):
+            t[y] = ops.mlp_f32(t[a], [self.w[b] for b, _ in names], [self.w[c] if c else None for _, c in names], relu, nk)
+        self.steps.append(Step(f"mlp:{y}", run, flops=flops))
 
     def _plan_gemm(self, L):
         mw = self.model.weights

@@ -22,7 +22,7 @@ def test_every_declared_symbol_is_exported_and_bound():
     assert len(names) >= 40
     for n in names:
         assert hasattr(lib, n), f"{n} declared in sofie_cuda.h but not exported by libSOFIE_cuda.so"
-    bound = set(capi.SIGNATURES) | set(capi.STRING_GETTERS)
+    bound = set(capi.SIGNATURES) | set(capi.STRING_GETTERS) | set(capi.SIZE_GETTERS)
     assert bound == set(names), sorted(bound ^ set(names))
 
 
@@ -34,6 +34,17 @@ def test_struct_sizes_match_header():
     assert C.sizeof(capi.QGemmDesc) == 6 * 4
     assert C.sizeof(capi.QConv2dDesc) == 18 * 4
     assert C.sizeof(capi.Fp8GemmDesc) == 7 * 4
+    assert C.sizeof(capi.MlpDesc) == (2 + 9 + 8 + 8) * 4
+
+
+def test_fused_mlp_shared_memory_arithmetic():
+    from sofie_b200 import ops
+    # 64 -> 128 -> 128 -> 10: padded weight rows (68, 132, 132 floats), biases, one input tile and two activation tiles of 32 rows
+    d = ops.mlp_desc(0, [64, 128, 128, 10], [1, 1, 0], [1, 1, 1])
+    want = 4 * (128 * 68 + 128 + 128 * 132 + 128 + 32 * 132 + 32 + 32 * 68 + 2 * 32 * 132)
+    assert capi.load().sofie_cuda_mlp_f32_smem(C.byref(d)) == want
+    assert ops.mlp_fits([64, 128, 128, 10]) and ops.mlp_fits([256, 96, 1])
+    assert not ops.mlp_fits([256, 256, 8]) and not ops.mlp_fits([300, 8]) and not ops.mlp_fits([8] * 10)
 
 
 def test_status_strings_and_argument_errors():

@@ -37,16 +37,38 @@ def test_c2_header_has_reference_signatures_and_fused_plan():
 
 
 def test_arena_slices_do_not_overlap_while_alive():
-    m, _ = configs.mlp_f32(batch=64)
-    text = _emit(m, "c1_b64").read_text()
+    m, _ = configs.mlp_activations_f32(batch=64)   # Gemm / activation / binary operators alternate: nothing fuses away
+    text = _emit(m, "mlp_act_b64").read_text()
     slices = {n: (int(o), int(b)) for o, b, n in re.findall(r"sofie_cuda_ctx_arena\(fCtx, (\d+), (\d+), reinterpret_cast<void\*\*>\(&dev_(\w+)\)", text)}
-    assert set(slices) == {"x", "y0", "y1", "y2"}
-    # y0 (read by layer 1) and y1 (written by layer 1) are alive together: disjoint
-    (o0, b0), (o1, b1) = slices["y0"], slices["y1"]
-    assert o0 + b0 <= o1 or o1 + b1 <= o0
+    assert {"x", "g0", "a0", "g1", "a1", "sh", "g2", "a2", "d", "y"} <= set(slices)
+    # an operator's input and output are alive together: their slices are disjoint
+    for a, b in [("x", "g0"), ("g0", "a0"), ("a0", "g1"), ("g1", "a1"), ("a1", "sh"), ("sh", "g2"), ("g2", "a2"), ("a2", "d"), ("d", "y")]:
+        (o0, b0), (o1, b1) = slices[a], slices[b]
+        assert o0 + b0 <= o1 or o1 + b1 <= o0, (a, b)
     assert all(o % 256 == 0 for o, _ in slices.values())
     arena = int(re.search(r"sofie_cuda_ctx_create\(&fCtx, -1, (\d+)\)", text).group(1))
     assert arena >= max(o + b for o, b in slices.values())
+    # slices are reused once their tensor is dead: the arena is smaller than the sum of all slices
+    assert arena < sum(b for _, b in slices.values())
+
+
+def test_small_gemm_chain_is_one_fused_launch():
+    m, _ = configs.mlp_f32(batch=64)
+    text = _emit(m, "c1_b64").read_text()
+    assert text.count("sofie_cuda_mlp_f32(") == 1 and "sofie_cuda_gemm_f32(" not in text
+    assert "{64, 3, {64, 128, 128, 10}, {1, 1, 0}, {1, 1, 1}}" in text
+    # the intermediate activations of the chain have no arena slice any more
+    assert "dev_y0" not in text and "dev_y1" not in text
+    # a wide layer is outside the fused kernel: one GEMM per layer again
+    m2 = configs.Model("wide", "x", (16, 300), [])
+    rng = np.random.default_rng(0)
+    m2.weights["w0"] = rng.standard_normal((64, 300)).astype(np.float32)
+    m2.weights["w1"] = rng.standard_normal((8, 64)).astype(np.float32)
+    m2.layers.append(dict(op="Gemm", A="x", B="w0", Y="h", transB=1, relu=True))
+    m2.layers.append(dict(op="Gemm", A="h", B="w1", Y="y", transB=1))
+    m2.output_name = "y"
+    text2 = _emit(m2, "wide").read_text()
+    assert text2.count("sofie_cuda_gemm_f32(") == 2 and "sofie_cuda_mlp_f32(" not in text2
 
 
 @pytest.mark.parametrize("key,kw", [("C1", {}), ("C2", {"batch": 4}), ("C3", {"batch": 32}), ("C5", {"batch": 2})])

@@ -52,6 +52,48 @@ def test_gemm_f32(M, N, K, tA, tB, bias):
     assert rel_err(y, ref) <= FP32_TOL
 
 
+def _mlp_reference(x, Ws, Bs, relu, nk):
+    for W, b, r, t in zip(Ws, Bs, relu, nk):
+        x = o.gemm_f32(x, W, b, transB=int(t), relu=bool(r))
+    return x
+
+
+@pytest.mark.parametrize("M,dims,relu,nk,bias", [
+    (1024, (64, 128, 128, 10), (1, 1, 0), (1, 1, 1), (1, 1, 1)),      # the three-layer perceptron configuration
+    (1, (7, 5), (0,), (1,), (0,)),                                    # one row, one layer, no bias
+    (33, (19, 45, 3), (1, 1), (0, 1), (1, 0)),                        # ragged rows and widths, both weight layouts
+    (257, (256, 96, 1), (0, 1), (1, 0), (1, 1)),                      # the widest layer the kernel takes
+    (300, (150, 100, 7), (1, 0), (1, 1), (1, 1)),                     # widths that are not multiples of 4: element-wise staging
+    (20000, (64, 128, 128, 10), (1, 1, 0), (1, 1, 1), (1, 1, 1)),     # several tiles per block: the input prefetch
+    (5000, (32, 64, 32, 64, 32, 64, 32, 64, 8), (1, 0, 1, 0, 1, 0, 1, 1), (1, 0, 1, 0, 1, 0, 1, 0), (1,) * 8),  # eight layers, more tiles than SMs
+    (96, (100, 33, 200), (1, 0), (0, 0), (0, 1)),
+])
+def test_mlp_f32_fused_chain(M, dims, relu, nk, bias):
+    rng = np.random.default_rng(M + len(dims))
+    x = rng.standard_normal((M, dims[0])).astype(np.float32)
+    Ws, Bs = [], []
+    for l in range(len(dims) - 1):
+        K, N = dims[l], dims[l + 1]
+        Ws.append((rng.standard_normal((N, K) if nk[l] else (K, N)) / np.sqrt(K)).astype(np.float32))
+        Bs.append(rng.standard_normal(N).astype(np.float32) if bias[l] else None)
+    ref = _mlp_reference(x, Ws, Bs, relu, nk)
+    y = ops.mlp_f32(dev(x), [dev(W) for W in Ws], [None if b is None else dev(b) for b in Bs], relu, nk).cpu().numpy()
+    assert y.shape == ref.shape and rel_err(y, ref) <= FP32_TOL
+
+
+def test_mlp_f32_limits_and_empty_batch():
+    W = torch.zeros((8, 300), device="cuda")
+    with pytest.raises(capi.SofieCudaError) as e:
+        ops.mlp_f32(torch.zeros((4, 300), device="cuda"), [W], [None], [0], [1])       # wider than the kernel takes
+    assert e.value.status == capi.ERR_UNSUPPORTED
+    Ws = [torch.zeros((256, 256), device="cuda") for _ in range(4)]
+    with pytest.raises(capi.SofieCudaError) as e:
+        ops.mlp_f32(torch.zeros((4, 256), device="cuda"), Ws, [None] * 4, [0] * 4, [1] * 4)  # weights beyond shared memory
+    assert e.value.status == capi.ERR_UNSUPPORTED
+    y = ops.mlp_f32(torch.zeros((0, 300 - 44), device="cuda"), [torch.zeros((8, 256), device="cuda")], [None], [0], [1])
+    assert y.shape == (0, 8)
+
+
 def test_gemm_empty_batch_and_bad_arguments():
     B = torch.zeros((4, 8), device="cuda")
     y = ops.gemm_f32(torch.zeros((0, 8), device="cuda"), B, transB=1)

@@ -98,8 +98,8 @@ def test_tensor_core_and_cuda_core_kernels_agree():
     assert rel_err(y_tc, y_cc) <= 1e-5
 
 
-# Shapes with at least 74 tiles of 256 x 256 run on CTA pairs (cta_group::2); ragged M and N included.
-@pytest.mark.parametrize("M,N,K,relu,zp", [(4900, 1000, 256, 1, 128), (2048 * 5, 512, 384, 0, 7)])
+# Shapes with at least 296 tiles of 256 x 256 run on CTA pairs (cta_group::2); ragged M and N included.
+@pytest.mark.parametrize("M,N,K,relu,zp", [(19000, 1000, 256, 1, 128), (2048 * 19, 512, 128, 0, 7)])
 def test_qlinear_matmul_pair_kernel_bit_exact(M, N, K, relu, zp):
     rng = np.random.default_rng(M + N + K)
     A = rng.integers(0, 256, (M, K)).astype(np.uint8)
@@ -116,7 +116,7 @@ def test_qlinear_matmul_pair_kernel_bit_exact(M, N, K, relu, zp):
 
 
 def test_gemm_e4m3_pair_kernel():
-    M, N, K = 4864, 1024, 512
+    M, N, K = 19200, 1024, 256
     rng = np.random.default_rng(3)
     X = rng.standard_normal((M, K)).astype(np.float32)
     Wf = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
