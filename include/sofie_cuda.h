@@ -176,6 +176,21 @@ int sofie_cuda_conv2d_f32(void *stream, const sofie_conv2d_desc *desc, const flo
 /* Repack ONNX weights [Cout,C,kH,kW] to the tensor-core layout [Cout][kH][kW][C] (group 1). */
 int sofie_cuda_conv2d_pack_f32(void *stream, const sofie_conv2d_desc *desc, const float *W, float *Wpacked);
 
+/* ConvTranspose 2-D, group 1 (reference: ROperator_ConvTranspose.icc:364-474 with UTILITY::col2im,
+ * SOFIE_common.hxx:576-620: per-image filter GEMM, scatter-add, broadcast bias added at the end).
+ * X [N,C,H,W], W [C,Cout,kH,kW] (the ONNX layout), bias [Cout] or NULL, Y [N,Cout,oH,oW] with
+ * o = stride*(i-1) + dil*(k-1)+1 + out_pad - 2*pad (ShapeInference :83-90), all NCHW.
+ * A 1-D ConvTranspose is the same call with H = kH = 1. */
+typedef struct sofie_conv_transpose2d_desc {
+   int32_t N, C, H, W;
+   int32_t Cout;
+   int32_t kH, kW, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w;
+   int32_t out_pad_h, out_pad_w;
+   int32_t relu;            /* fused y = max(y, 0)                                          */
+} sofie_conv_transpose2d_desc;
+int sofie_cuda_conv_transpose2d_f32(void *stream, const sofie_conv_transpose2d_desc *desc, const float *X, const float *W,
+                                    const float *bias, float *Y);
+
 /* ------------------------------------------------------------------ fp32 memory-bound ops --- */
 /* y = x > 0 ? x : 0 (reference: ROperator_Relu.hxx:54-66). In place allowed. */
 int sofie_cuda_relu_f32(void *stream, const float *X, float *Y, size_t n);

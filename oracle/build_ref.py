@@ -87,6 +87,10 @@ def all_cases():
     m, x = configs.mlp_activations_f32()
     m.name = "ref_mlp_act"
     cases["ref_mlp_act"] = (m, x)
+    # transposed convolutions (strided, padded, output_padding, with and without bias)
+    m, x = configs.upsample_f32()
+    m.name = "ref_upsample"
+    cases["ref_upsample"] = (m, x)
     return cases
 
 
@@ -105,6 +109,10 @@ def description(m) -> tuple[str, np.ndarray]:
         elif op == "Conv":
             p, s, k = L["pads"], L["strides"], L["kernel"]
             lines.append(f"conv {L.get('group', 1)} {k[0]} {k[1]} {p[0]} {p[1]} {p[2]} {p[3]} {s[0]} {s[1]} 1 1 "
+                         f"{L['X']} {L['W']} {L.get('B') or '-'} {L['Y']}")
+        elif op == "ConvTranspose":
+            p, s, k, q = L["pads"], L["strides"], L["kernel"], L.get("output_padding", (0, 0))
+            lines.append(f"convtr {k[0]} {k[1]} {p[0]} {p[1]} {p[2]} {p[3]} {s[0]} {s[1]} {q[0]} {q[1]} "
                          f"{L['X']} {L['W']} {L.get('B') or '-'} {L['Y']}")
         elif op == "Relu":
             lines.append(f"relu {L['X']} {L['Y']}")

@@ -81,6 +81,21 @@ def conv2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), group=1, 
     return Y
 
 
+def conv_transpose2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0)):
+    """X [N, C, H, W], W [C, Cout, kh, kw] (ONNX ConvTranspose, group 1) -> [N, Cout, oH, oW]."""
+    X, W = _f(X), _f(W)
+    N, Cin, H, Wd = X.shape
+    _, Cout, kh, kw = W.shape
+    oH = stride[0] * (H - 1) + dil[0] * (kh - 1) + 1 + out_pad[0] - 2 * pad[0]
+    oW = stride[1] * (Wd - 1) + dil[1] * (kw - 1) + 1 + out_pad[1] - 2 * pad[1]
+    if bias is not None:
+        bias = _f(bias)
+    Y = np.empty((N, Cout, oH, oW), np.float32)
+    ints = [N, Cin, H, Wd, Cout, kh, kw, pad[0], pad[1], stride[0], stride[1], dil[0], dil[1], out_pad[0], out_pad[1]]
+    lib().oracle_conv_transpose2d_f32(*[C.c_int(v) for v in ints], _ptr(X), _ptr(W), _ptr(bias), _ptr(Y))
+    return Y
+
+
 def relu_f32(X):
     X = _f(X)
     Y = np.empty_like(X)

@@ -12,6 +12,7 @@
 //   weight  <tensor> <d0> <d1> ...           (float32 values taken, in order, from the blob file)
 //   gemm    <alpha> <beta> <transA> <transB> <A> <B> <C|-> <Y> <relu 0|1>
 //   conv    <group> <kh> <kw> <pad_t> <pad_l> <pad_b> <pad_r> <sh> <sw> <dh> <dw> <X> <W> <B|-> <Y>
+//   convtr  <kh> <kw> <pad_t> <pad_l> <pad_b> <pad_r> <sh> <sw> <oph> <opw> <X> <W> <B|-> <Y>
 //   relu    <X> <Y>
 //   maxpool <kh> <kw> <p0> <p1> <p2> <p3> <sh> <sw> <X> <Y>      (pads exactly as the ONNX attribute)
 //   avgpool <kh> <kw> <p0> <p1> <p2> <p3> <sh> <sw> <X> <Y>
@@ -23,6 +24,7 @@
 #include "SOFIE/RModel.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
 #include "SOFIE/ROperator_Conv.hxx"
+#include "SOFIE/ROperator_ConvTranspose.hxx"
 #include "SOFIE/ROperator_Relu.hxx"
 #include "SOFIE/ROperator_Pool.hxx"
 #include "SOFIE/ROperator_Reshape.hxx"
@@ -103,6 +105,14 @@ int main(int argc, char **argv)
                model->AddOperator(std::make_unique<ROperator_Conv<float>>("NOTSET", dil, g, ks, pads, str, X, W, Y), order++);
             else
                model->AddOperator(std::make_unique<ROperator_Conv<float>>("NOTSET", dil, g, ks, pads, str, X, W, B, Y), order++);
+         } else if (kw == "convtr") {
+            size_t kh, kw_, pt, pl, pb, pr, sh, sw, oph, opw;
+            std::string X, W, B, Y;
+            ss >> kh >> kw_ >> pt >> pl >> pb >> pr >> sh >> sw >> oph >> opw >> X >> W >> B >> Y;
+            std::vector<size_t> dil{1, 1}, ks{kh, kw_}, pads{pt, pl, pb, pr}, str{sh, sw}, opad{oph, opw};
+            model->AddOperator(std::make_unique<ROperator_ConvTranspose<float>>("NOTSET", dil, 1, ks, opad, std::vector<size_t>{}, pads,
+                                                                                 str, X, W, B == "-" ? std::string() : B, Y),
+                               order++);
          } else if (kw == "relu") {
             std::string X, Y;
             ss >> X >> Y;

@@ -27,6 +27,10 @@ def run(model, x, fp8_scales=None, return_all=False):
             p, s = L["pads"], L["strides"]
             t[L["Y"]] = o.conv2d_f32(t[L["X"]], w[L["W"]], w.get(L.get("B")), pad=(p[0], p[1]), stride=s,
                                      group=L.get("group", 1))
+        elif op == "ConvTranspose":
+            p, s = L["pads"], L["strides"]
+            t[L["Y"]] = o.conv_transpose2d_f32(t[L["X"]], w[L["W"]], w.get(L.get("B")), pad=(p[0], p[1]), stride=s,
+                                               out_pad=L.get("output_padding", (0, 0)))
         elif op == "Relu":
             t[L["Y"]] = o.relu_f32(t[L["X"]])
         elif op == "MaxPool":

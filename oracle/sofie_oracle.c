@@ -196,6 +196,68 @@ ORACLE_API void oracle_conv2d_f32(int N, int C, int H, int W, int Cout, int kh, 
    oracle_parallel_for(N, conv2d_f32_images, &a);
 }
 
+/* ConvTranspose, 2-D, group 1, as emitted by ROperator_ConvTranspose.icc:364-474:
+ *   per image   xcol[(oc,r,s)][ih*W+iw] = sum_ic X[ic][ih][iw] * Wt[ic][oc][r][s]      (the sgemm_ at :370-375)
+ *               Y_n = col2im(xcol)      scatter-add into the zeroed image, UTILITY::col2im (SOFIE_common.hxx:576-620)
+ *   at the end  Y += bias broadcast per output channel                                 (the saxpy_ at :462-471)
+ * Output size (ShapeInference :83-90): o = stride*(i-1) + dil*(k-1)+1 + output_padding - 2*pad.
+ * The reference's own tests pin dilation 1 only (its emission dilates the filter matrix AND passes the
+ * dilation to col2im, :233-262,:380-391); this restates the ONNX definition, which is the same thing at dilation 1. */
+typedef struct {
+   int N, C, H, W, Cout, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w, oH, oW;
+   const float *X, *Wt, *bias;
+   float *Y;
+} convtr_args;
+static void conv_transpose2d_images(long n0, long n1, void *ctx)
+{
+   const convtr_args *a = (const convtr_args *)ctx;
+   const size_t in_hw = (size_t)a->H * a->W, out_hw = (size_t)a->oH * a->oW, taps = (size_t)a->kh * a->kw;
+   float *col = (float *)malloc(sizeof(float) * a->Cout * taps * in_hw);
+   for (long n = n0; n < n1; n++) {
+      const float *x = a->X + (size_t)n * a->C * in_hw;
+      float *y = a->Y + (size_t)n * a->Cout * out_hw;
+      for (size_t j = 0; j < (size_t)a->Cout * taps; j++) { /* j = (oc, r, s) */
+         const size_t oc = j / taps, t = j % taps;
+         for (size_t p = 0; p < in_hw; p++) {
+            float acc = 0.f;
+            for (int ic = 0; ic < a->C; ic++) acc += x[(size_t)ic * in_hw + p] * a->Wt[((size_t)ic * a->Cout + oc) * taps + t];
+            col[j * in_hw + p] = acc;
+         }
+      }
+      for (size_t i = 0; i < (size_t)a->Cout * out_hw; i++) y[i] = 0.f;
+      const float *c = col;
+      for (int oc = 0; oc < a->Cout; oc++) {
+         float *im = y + (size_t)oc * out_hw;
+         for (int r = 0; r < a->kh; r++)
+            for (int s = 0; s < a->kw; s++) {
+               int row = -a->pad_h + r * a->dil_h;
+               for (int ih = 0; ih < a->H; ih++, row += a->stride_h) {
+                  if (row < 0 || row >= a->oH) {
+                     c += a->W;
+                     continue;
+                  }
+                  int colx = -a->pad_w + s * a->dil_w;
+                  for (int iw = 0; iw < a->W; iw++, colx += a->stride_w, c++)
+                     if (colx >= 0 && colx < a->oW) im[(size_t)row * a->oW + colx] += *c;
+               }
+            }
+      }
+      if (a->bias)
+         for (int oc = 0; oc < a->Cout; oc++)
+            for (size_t i = 0; i < out_hw; i++) y[(size_t)oc * out_hw + i] += a->bias[oc];
+   }
+   free(col);
+}
+ORACLE_API void oracle_conv_transpose2d_f32(int N, int C, int H, int W, int Cout, int kh, int kw, int pad_h, int pad_w,
+                                            int stride_h, int stride_w, int dil_h, int dil_w, int outpad_h, int outpad_w,
+                                            const float *X, const float *Wt, const float *bias, float *Y)
+{
+   convtr_args a = {N, C, H, W, Cout, kh, kw, pad_h, pad_w, stride_h, stride_w, dil_h, dil_w,
+                    stride_h * (H - 1) + dil_h * (kh - 1) + 1 + outpad_h - 2 * pad_h,
+                    stride_w * (W - 1) + dil_w * (kw - 1) + 1 + outpad_w - 2 * pad_w, X, Wt, bias, Y};
+   oracle_parallel_for(N, conv_transpose2d_images, &a);
+}
+
 /* ROperator_Relu.hxx:54-66 */
 ORACLE_API void oracle_relu_f32(const float *X, size_t n, float *Y)
 {

@@ -48,6 +48,11 @@ class QConv2dDesc(C.Structure):
                                    "x_layout", "y_layout", "w_packed", "x_zp", "y_zp", "relu", "pool")]
 
 
+class ConvTranspose2dDesc(C.Structure):
+    _fields_ = [(n, i32) for n in ("N", "C", "H", "W", "Cout", "kH", "kW", "pad_h", "pad_w", "stride_h", "stride_w", "dil_h", "dil_w",
+                                   "out_pad_h", "out_pad_w", "relu")]
+
+
 class MlpDesc(C.Structure):
     _fields_ = [("M", i32), ("layers", i32), ("dims", i32 * 9), ("relu", i32 * 8), ("w_is_nk", i32 * 8)]
 
@@ -93,6 +98,7 @@ SIGNATURES = {
     "sofie_cuda_transpose_f32": [vp, vp, vp, i32, i32],
     "sofie_cuda_conv2d_f32": [vp, C.POINTER(Conv2dDesc), vp, vp, vp, vp],
     "sofie_cuda_conv2d_pack_f32": [vp, C.POINTER(Conv2dDesc), vp, vp],
+    "sofie_cuda_conv_transpose2d_f32": [vp, C.POINTER(ConvTranspose2dDesc), vp, vp, vp, vp],
     "sofie_cuda_relu_f32": [vp, vp, vp, sz],
     "sofie_cuda_pool2d_f32": [vp, C.POINTER(Pool2dDesc), vp, vp],
     "sofie_cuda_softmax_f32": [vp, vp, vp, sz, sz, sz],

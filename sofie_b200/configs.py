@@ -188,6 +188,30 @@ def resblock_f32(batch=8, chans=16, hw=16, key="C2", with_input=True):
     return m, x
 
 
+def upsample_f32(batch=4, hw=12, key="C2", with_input=True):
+    """Decoder-style stack: Conv 3->8 + Relu; ConvTranspose 8->6, 2x2 stride 2; Relu; ConvTranspose 6->3, 3x3 stride 2 pad 1
+    output_padding 1, with bias; Tanh. Seeded like C2."""
+    rng = np.random.Generator(np.random.PCG64(SEEDS[key] + 79))
+    m = Model(f"upsample_b{batch}", "x", (batch, 3, hw, hw), [])
+    m.weights["w0"] = (rng.standard_normal((8, 3, 3, 3)) * np.sqrt(2.0 / 27)).astype(np.float32)
+    m.weights["b0"] = rng.uniform(-0.1, 0.1, 8).astype(np.float32)
+    m.weights["t1"] = (rng.standard_normal((8, 6, 2, 2)) * np.sqrt(2.0 / 8)).astype(np.float32)
+    m.weights["t2"] = (rng.standard_normal((6, 3, 3, 3)) * np.sqrt(2.0 / 14)).astype(np.float32)
+    m.weights["tb2"] = rng.uniform(-0.1, 0.1, 3).astype(np.float32)
+    m.layers.append(dict(op="Conv", X="x", W="w0", B="b0", Y="c0", pads=(1, 1, 1, 1), strides=(1, 1), kernel=(3, 3)))
+    m.layers.append(dict(op="Relu", X="c0", Y="r0"))
+    m.layers.append(dict(op="ConvTranspose", X="r0", W="t1", Y="u1", pads=(0, 0, 0, 0), strides=(2, 2), kernel=(2, 2),
+                         output_padding=(0, 0)))
+    m.layers.append(dict(op="Relu", X="u1", Y="r1"))
+    m.layers.append(dict(op="ConvTranspose", X="r1", W="t2", B="tb2", Y="u2", pads=(1, 1, 1, 1), strides=(2, 2), kernel=(3, 3),
+                         output_padding=(1, 1)))
+    m.layers.append(dict(op="Tanh", X="u2", Y="y"))
+    m.output_name = "y"
+    m.flops_per_sample = 2 * hw * hw * (8 * 27 + 8 * 6 * 4 + 4 * 6 * 3 * 9)
+    x = rng.standard_normal((batch, 3, hw, hw)).astype(np.float32) if with_input else None
+    return m, x
+
+
 def mlp_activations_f32(batch=64, key="C1", with_input=True):
     """Gemm 32->48 + Selu; Gemm 48->48 + Tanh; Sub of a constant row; Gemm 48->24 + Elu; Div by a constant; Sigmoid."""
     rng = np.random.Generator(np.random.PCG64(SEEDS[key] + 78))

@@ -17,6 +17,7 @@
 #include "SOFIE/ROperator_Conv.hxx"
 #include "SOFIE/ROperator_Fp8.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
+#include "SOFIE/ROperator_ConvTranspose.hxx"
 #include "SOFIE/ROperator_Pool.hxx"
 #include "SOFIE/ROperator_QLinear.hxx"
 #include "SOFIE/ROperator_Relu.hxx"
@@ -101,6 +102,20 @@ std::unique_ptr<ROperator> ParseConv(RModelParser_ONNX &p, const onnx::NodeProto
                                                                (size_t)attr_int(n, "group", 1), attr_ints(n, "kernel_shape"),
                                                                attr_ints(n, "pads"), attr_ints(n, "strides"), n.input(0), n.input(1),
                                                                bias, n.output(0)));
+}
+
+std::unique_ptr<ROperator> ParseConvTranspose(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   require_type(p, n.input(0), "ConvTranspose");
+   ETensorType type = p.GetTensorType(n.input(0));
+   if (type != ETensorType::FLOAT)
+      throw std::runtime_error("SOFIE - Unsupported - Operator ConvTranspose does not yet support this input type");
+   std::string bias = n.input_size() > 2 ? n.input(2) : "";
+   p.RegisterTensorType(n.output(0), type);
+   return std::unique_ptr<ROperator>(new ROperator_ConvTranspose<float>(
+      attr_string(n, "auto_pad", "NOTSET"), attr_ints(n, "dilations"), (size_t)attr_int(n, "group", 1), attr_ints(n, "kernel_shape"),
+      attr_ints(n, "output_padding"), attr_ints(n, "output_shape"), attr_ints(n, "pads"), attr_ints(n, "strides"), n.input(0), n.input(1),
+      bias, n.output(0)));
 }
 
 std::unique_ptr<ROperator> ParseRelu(RModelParser_ONNX &p, const onnx::NodeProto &n)
@@ -302,6 +317,7 @@ RModelParser_ONNX::RModelParser_ONNX() noexcept : fOperatorsMapImpl(std::make_un
    RegisterOperator("MatMul", ParseMatMul);
    RegisterOperator("Einsum", ParseEinsum);
    RegisterOperator("Conv", ParseConv);
+   RegisterOperator("ConvTranspose", ParseConvTranspose);
    RegisterOperator("Relu", ParseRelu);
    RegisterOperator("MaxPool", ParsePool);
    RegisterOperator("AveragePool", ParsePool);

@@ -298,6 +298,12 @@ def model_to_onnx(m, fp8_scales=None) -> bytes:
             nodes.append(node("Conv", ins, [L["Y"]], [attr_ints("kernel_shape", L["kernel"]), attr_ints("pads", L["pads"]),
                                                       attr_ints("strides", L["strides"]), attr_int("group", L.get("group", 1)),
                                                       attr_ints("dilations", (1, 1))]))
+        elif op == "ConvTranspose":
+            ins = [L["X"], init(L["W"])] + ([init(L["B"])] if L.get("B") else [])
+            nodes.append(node("ConvTranspose", ins, [L["Y"]],
+                              [attr_ints("kernel_shape", L["kernel"]), attr_ints("pads", L["pads"]), attr_ints("strides", L["strides"]),
+                               attr_ints("output_padding", L.get("output_padding", (0, 0))), attr_int("group", 1),
+                               attr_ints("dilations", (1, 1))]))
         elif op == "Relu":
             nodes.append(node("Relu", [L["X"]], [L["Y"]]))
         elif op == "MaxPool":

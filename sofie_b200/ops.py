@@ -111,6 +111,19 @@ def softmax_f32(X, axis=-1):
     return Y
 
 
+def conv_transpose2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0), relu=False):
+    """ONNX ConvTranspose, group 1: X [N, C, H, W], W [C, Cout, kH, kW] -> [N, Cout, oH, oW]."""
+    N, Cin, H, Wd = X.shape
+    _, Cout, kH, kW = W.shape
+    oH = stride[0] * (H - 1) + dil[0] * (kH - 1) + 1 + out_pad[0] - 2 * pad[0]
+    oW = stride[1] * (Wd - 1) + dil[1] * (kW - 1) + 1 + out_pad[1] - 2 * pad[1]
+    Y = torch.empty((N, Cout, max(oH, 0), max(oW, 0)), dtype=torch.float32, device=X.device)
+    d = capi.ConvTranspose2dDesc(N, Cin, H, Wd, Cout, kH, kW, pad[0], pad[1], stride[0], stride[1], dil[0], dil[1], out_pad[0],
+                                 out_pad[1], int(relu))
+    capi.call("sofie_cuda_conv_transpose2d_f32", _stream(), C.byref(d), _p(X), _p(W), _p(bias) if bias is not None else None, _p(Y))
+    return Y
+
+
 def mlp_desc(M, dims, relu, w_is_nk):
     L = len(dims) - 1
     return capi.MlpDesc(M, L, (capi.i32 * 9)(*(list(dims) + [0] * (8 - L))), (capi.i32 * 8)(*([int(r) for r in relu] + [0] * (8 - L))),

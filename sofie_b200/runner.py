@@ -101,6 +101,9 @@ class Session:
             elif op == "MaxPool":
                 self._plan_pool(L)
                 i += 1
+            elif op == "ConvTranspose":
+                self._plan_conv_transpose(L)
+                i += 1
             elif op == "Flatten":
                 x, y = L["X"], L["Y"]
                 # a flattened NHWC tensor keeps its memory; consumers permute their weights instead
@@ -365,6 +368,26 @@ class Session:
             else:
                 t[y] = ops.pool2d_f32(X, mode=0, kernel=k, stride=s, pads=p, layout=lay, shape=shp)
         self.steps.append(Step(f"maxpool:{y}", run))
+
+    def _plan_conv_transpose(self, L):
+        mw = self.model.weights
+        x, y, wn, bn = L["X"], L["Y"], L["W"], L.get("B")
+        N, C, H, Wd = self.shape[x]
+        W = mw[wn]
+        p, s, op_ = L["pads"], L["strides"], L.get("output_padding", (0, 0))
+        if L.get("group", 1) != 1 or p[0] != p[2] or p[1] != p[3]:
+            raise NotImplementedError("ConvTranspose: group 1 and symmetric pads only")
+        self.w[wn] = self._up(W)
+        if bn:
+            self.w[bn] = self._up(mw[bn])
+        oH = s[0] * (H - 1) + W.shape[2] + op_[0] - 2 * p[0]
+        oW = s[1] * (Wd - 1) + W.shape[3] + op_[1] - 2 * p[1]
+        self.layout[y], self.shape[y] = LAYOUT_NCHW, (N, W.shape[1], oH, oW)
+
+        def run(t):
+            t[y] = ops.conv_transpose2d_f32(t[x], self.w[wn], self.w[bn] if bn else None, pad=(p[0], p[1]), stride=tuple(s),
+                                            out_pad=tuple(op_))
+        self.steps.append(Step(f"convtr:{y}", run, flops=2 * H * Wd * C * int(np.prod(W.shape[1:]))))
 
     def _plan_quantize(self, L):
         x, y, s, zp = L["X"], L["Y"], L["scale"], L["zp"]

@@ -27,7 +27,10 @@ CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutP
          "Softmax3d", "Softmax4d", "Einsum_matmul",
          # elementwise family
          "LinearWithSelu", "LinearWithSigmoid", "LinearWithLeakyRelu", "Add", "Sub", "Mul", "Div", "Neg", "Exp", "Log", "Elu",
-         "Tanh", "Sqrt", "Reciprocal"]
+         "Tanh", "Sqrt", "Reciprocal",
+         # broadcasting Add (rank <= 4) and transposed convolutions
+         "AddBroadcast1", "AddBroadcast2", "AddBroadcast3", "AddBroadcast4", "AddBroadcast5", "AddBroadcast7",
+         "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched"]
 TEST_NAME = {"Linear_16": "Linear16", "Linear_32": "Linear32", "Linear_64": "Linear64"}
 FLOAT_RE = re.compile(r"[-+]?(?:\d+\.?\d*|\.\d+)(?:[eE][-+]?\d+)?")
 
@@ -54,7 +57,7 @@ def test_block(src: str, test: str) -> str:
 
 def test_inputs(block: str, n_elems: list[int]) -> list[np.ndarray]:
     """Inputs as the reference test builds them: fill_n(1.0f), iota from 0, or literal vectors."""
-    lits = re.findall(r"std::vector<float>\s+input\w*\s*(?:\(\s*\{|\{)([^}]*)\}", block, re.S)
+    lits = re.findall(r"std::vector<float>\s+(?:input\w*|[ABC])\s*(?:\(\s*\{|\{)([^}]*)\}", block, re.S)
     if lits:
         return [np.array([float(v) for v in FLOAT_RE.findall(b)], np.float32) for b in lits]
     if "std::iota" in block:

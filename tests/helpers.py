@@ -42,6 +42,9 @@ class OracleBackend:
     def conv(self, X, W, B=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), group=1):
         return self.o.conv2d_f32(X, W, B, pad=pad, stride=stride, dil=dil, group=group)
 
+    def conv_transpose(self, X, W, B=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0)):
+        return self.o.conv_transpose2d_f32(X, W, B, pad=pad, stride=stride, dil=dil, out_pad=out_pad)
+
     def relu(self, X):
         return self.o.relu_f32(X)
 
@@ -75,6 +78,10 @@ class CudaBackend:
     def conv(self, X, W, B=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), group=1):
         return self.ops.conv2d_f32(self._d(X), self._d(W), self._d(B), pad=pad, stride=stride, dil=dil,
                                    group=group).cpu().numpy()
+
+    def conv_transpose(self, X, W, B=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0)):
+        return self.ops.conv_transpose2d_f32(self._d(X), self._d(W), self._d(B), pad=pad, stride=stride, dil=dil,
+                                             out_pad=out_pad).cpu().numpy()
 
     def relu(self, X):
         return self.ops.relu_f32(self._d(X)).cpu().numpy()
@@ -136,6 +143,21 @@ def run_fixture(name, manifest, arrays, backend):
             W = t[ins[1]]
             pad, stride, dil, group = conv_attrs(a, W.shape[2:])
             y = backend.conv(t[ins[0]], W, t[ins[2]] if len(ins) > 2 else None, pad=pad, stride=stride, dil=dil, group=group)
+        elif op == "ConvTranspose":
+            X, W = t[ins[0]], t[ins[1]]
+            one_d = X.ndim == 3  # a 1-D transposed convolution is the 2-D one with a height of 1
+            if one_d:
+                X, W = X[:, :, None, :], W[:, :, None, :]
+            nd = 1 if one_d else 2
+            lift = (lambda v, fill: (fill, v[0]) if one_d else tuple(v))
+            pads = a.get("pads", [0] * (2 * nd))
+            # asymmetric pads are averaged, as the reference does (ROperator_ConvTranspose.icc:332-346)
+            pad = lift([(pads[i] + pads[i + nd]) // 2 if pads[i] != pads[i + nd] else pads[i] for i in range(nd)], 0)
+            y = backend.conv_transpose(X, W, t[ins[2]] if len(ins) > 2 else None, pad=pad,
+                                       stride=lift(a.get("strides", [1] * nd), 1), dil=lift(a.get("dilations", [1] * nd), 1),
+                                       out_pad=lift(a.get("output_padding", [0] * nd), 0))
+            if one_d:
+                y = y[:, :, 0, :]
         elif op in ("MaxPool", "AveragePool"):
             y = backend.pool(t[ins[0]], 0 if op == "MaxPool" else 1, tuple(a["kernel_shape"]),
                              tuple(a.get("strides", [1, 1])), tuple(a.get("pads", [0, 0, 0, 0])),
@@ -159,7 +181,9 @@ FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "Conv
                  "ConvWithAutopadSameLower", "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "AvgPool",
                  "Softmax1d", "Softmax2d", "Softmax3d", "Softmax4d", "Einsum_matmul",
                  "LinearWithSelu", "LinearWithSigmoid", "LinearWithLeakyRelu", "Add", "Sub", "Mul", "Div", "Neg", "Exp", "Log",
-                 "Elu", "Tanh", "Sqrt", "Reciprocal"]
+                 "Elu", "Tanh", "Sqrt", "Reciprocal",
+                 "AddBroadcast1", "AddBroadcast2", "AddBroadcast3", "AddBroadcast4", "AddBroadcast5", "AddBroadcast7",
+                 "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched"]
 
 
 def fixture_to_onnx(name, manifest, arrays):

@@ -147,3 +147,22 @@ def test_fp8_chain_parses_and_emits_through_the_generator():
     generated.compile_session(hxx, "c4_tiny")
     with pytest.raises(ValueError):
         onnx_wire.model_to_onnx(m)  # the chain cannot be written without its calibrated scales
+
+
+def test_conv_transpose_emits_one_call_and_refuses_what_the_reference_refuses():
+    m, _ = configs.upsample_f32(batch=2)
+    text = _emit(m, "upsample_b2").read_text()
+    assert text.count("sofie_cuda_conv_transpose2d_f32(") == 2 and "_xcol" not in text and "col2im" not in text
+    descs = re.findall(r"sofie_conv_transpose2d_desc d = \{([^}]*)\}", text)
+    assert [int(v) for v in descs[0].split(",")] == [2, 8, 12, 12, 6, 2, 2, 0, 0, 2, 2, 1, 1, 0, 0, 0]
+    assert [int(v) for v in descs[1].split(",")] == [2, 6, 24, 24, 3, 3, 3, 1, 1, 2, 2, 1, 1, 1, 1, 0]
+    generated.compile_session(_emit(m, "upsample_b2"), "upsample_b2")
+
+    def graph(attrs):
+        w = np.zeros((3, 2, 3, 3), np.float32)
+        return onnx_wire.model("g", [onnx_wire.node("ConvTranspose", ["x", "w"], ["y"], attrs)], [onnx_wire.value_info("x", 1, [1, 3, 4, 4])],
+                               [onnx_wire.value_info("y", 1, [])], [onnx_wire.tensor("w", w)])
+    with pytest.raises(RuntimeError, match="output_shape explicitly set"):
+        generated.emit(graph([onnx_wire.attr_ints("output_shape", [8, 8])]), "convtr_oshape")
+    with pytest.raises(RuntimeError, match="group"):
+        generated.emit(graph([onnx_wire.attr_int("group", 3)]), "convtr_group")

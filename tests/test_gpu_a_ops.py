@@ -150,6 +150,41 @@ def test_conv2d_f32_layouts_and_fusion(x_nhwc, y_nhwc, packed, relu, pool):
     assert rel_err(y, ref) <= FP32_TOL
 
 
+@pytest.mark.parametrize("case", [
+    # N, C, H, W, Cout, k, pad, stride, dil, out_pad, bias, relu
+    (2, 3, 5, 6, 4, (3, 3), (0, 0), (1, 1), (1, 1), (0, 0), True, False),
+    (1, 1, 3, 3, 2, (3, 3), (0, 0), (1, 1), (1, 1), (0, 0), False, False),
+    (3, 8, 7, 5, 6, (2, 2), (0, 0), (2, 2), (1, 1), (0, 0), True, True),
+    (2, 6, 9, 9, 3, (3, 3), (1, 1), (2, 2), (1, 1), (1, 1), True, False),      # the usual 2x upsampling layer
+    (2, 5, 6, 4, 7, (3, 2), (1, 0), (3, 2), (2, 1), (2, 1), False, False),     # dilation, output_padding, Cout not a multiple of 4
+    (1, 4, 1, 17, 5, (1, 5), (0, 2), (1, 3), (1, 1), (0, 0), True, False),     # a 1-D transposed convolution
+    (4, 32, 16, 16, 16, (4, 4), (1, 1), (2, 2), (1, 1), (0, 0), True, True),
+])
+def test_conv_transpose2d_f32(case):
+    N, Cin, H, W, Cout, k, pad, stride, dil, out_pad, bias, relu = case
+    rng = np.random.default_rng(N * 100 + Cin)
+    X = rng.standard_normal((N, Cin, H, W)).astype(np.float32)
+    Wt = (rng.standard_normal((Cin, Cout) + k) / np.sqrt(Cin * k[0] * k[1])).astype(np.float32)
+    b = rng.standard_normal(Cout).astype(np.float32) if bias else None
+    ref = o.conv_transpose2d_f32(X, Wt, b, pad=pad, stride=stride, dil=dil, out_pad=out_pad)
+    if relu:
+        ref = o.relu_f32(ref)
+    y = ops.conv_transpose2d_f32(dev(X), dev(Wt), None if b is None else dev(b), pad=pad, stride=stride, dil=dil, out_pad=out_pad,
+                                 relu=relu).cpu().numpy()
+    assert y.shape == ref.shape and rel_err(y, ref) <= FP32_TOL
+
+
+def test_conv_transpose2d_empty_batch_and_bad_arguments():
+    Wt = torch.zeros((3, 2, 3, 3), device="cuda")
+    assert ops.conv_transpose2d_f32(torch.zeros((0, 3, 4, 4), device="cuda"), Wt).shape == (0, 2, 6, 6)
+    with pytest.raises(capi.SofieCudaError) as e:   # the pads eat the whole output
+        ops.conv_transpose2d_f32(torch.zeros((1, 3, 1, 1), device="cuda"), Wt, pad=(2, 2))
+    assert e.value.status == capi.ERR_INVALID
+    with pytest.raises(capi.SofieCudaError) as e:   # output_padding not below the stride
+        ops.conv_transpose2d_f32(torch.zeros((1, 3, 4, 4), device="cuda"), Wt, stride=(2, 2), out_pad=(2, 0))
+    assert e.value.status == capi.ERR_INVALID
+
+
 def test_relu_nan_negzero_and_ragged_sizes():
     for n in (0, 1, 3, 4, 5, 1023, 4099):
         x = np.random.default_rng(n).standard_normal(n).astype(np.float32)

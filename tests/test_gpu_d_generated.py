@@ -23,7 +23,7 @@ def test_reference_golden_vectors_through_generated_session(name, cuda_device):
     assert np.abs(y - exp).max() <= 1e-3  # the reference's tolerance for its fixtures
 
 
-@pytest.mark.parametrize("case", ["ref_c1", "ref_c2", "ref_c2_b4", "ref_gemm_nt", "ref_matmul", "ref_conv_grp", "ref_conv5", "ref_softmax", "ref_resblock", "ref_mlp_act"])
+@pytest.mark.parametrize("case", ["ref_c1", "ref_c2", "ref_c2_b4", "ref_gemm_nt", "ref_matmul", "ref_conv_grp", "ref_conv5", "ref_softmax", "ref_resblock", "ref_mlp_act", "ref_upsample"])
 def test_generated_session_matches_reference_emitted_code(case, cuda_device):
     m, x = build_ref.all_cases()[case]
     s = generated.session_from_model(m, case + "_cuda")

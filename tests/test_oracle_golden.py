@@ -14,3 +14,20 @@ def test_oracle_reproduces_reference_golden(name):
     exp = arrays[f"{name}/expected"]
     assert y.shape == exp.shape
     assert np.abs(y - exp).max() <= manifest[name]["tolerance"]
+
+
+@pytest.mark.parametrize("stride,pad,dil,out_pad", [((1, 1), (0, 0), (1, 1), (0, 0)), ((2, 2), (1, 1), (1, 1), (1, 1)),
+                                                    ((3, 2), (1, 0), (2, 1), (2, 1)), ((2, 1), (0, 2), (1, 2), (0, 0))])
+def test_conv_transpose_oracle_against_an_independent_implementation(stride, pad, dil, out_pad):
+    """The restated ConvTranspose (reference: filter GEMM + col2im) against torch's CPU operator, beyond the
+    un-strided, un-padded shapes the reference's own fixtures cover."""
+    import torch
+    from oracle import cpu_oracle as o
+    rng = np.random.default_rng(7)
+    X = rng.standard_normal((2, 5, 6, 7)).astype(np.float32)
+    W = rng.standard_normal((5, 4, 3, 3)).astype(np.float32)
+    b = rng.standard_normal(4).astype(np.float32)
+    y = o.conv_transpose2d_f32(X, W, b, pad=pad, stride=stride, dil=dil, out_pad=out_pad)
+    ref = torch.nn.functional.conv_transpose2d(torch.from_numpy(X), torch.from_numpy(W), torch.from_numpy(b), stride=stride,
+                                               padding=pad, output_padding=out_pad, dilation=dil).numpy()
+    assert y.shape == ref.shape and np.abs(y - ref).max() <= 1e-5 * np.abs(ref).max()
