@@ -37,6 +37,8 @@ int launch_gemm_f32_splitk(cudaStream_t, const sofie_gemm_f32_desc &, const floa
                            float *scratch, size_t scratch_floats);
 int launch_gemm_f32_splitk_auto(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *,
                                 float *);
+// gives the split-K scratch buffer of a stream back to the per-device pool (context teardown)
+void splitk_scratch_release(int device, cudaStream_t stream);
 template <typename T>
 int launch_pack_ohwi(cudaStream_t, const T *, T *, int Cout, int C, int kH, int kW);
 

@@ -5,6 +5,7 @@
 // (reference: src/SOFIE_core/src/RModel.cxx:574-595) and the `new char[]` intermediate pool
 // (reference: src/SOFIE_core/src/RModel.cxx:597-604).
 #include "common.cuh"
+#include "contract.cuh"
 
 #include <cstdlib>
 #include <mutex>
@@ -172,6 +173,7 @@ int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx)
    if (ctx->arena) cudaFree(ctx->arena);
    if (ctx->staging) cudaFreeHost(ctx->staging);
    if (ctx->result) cudaFreeHost(ctx->result);
+   splitk_scratch_release(ctx->device, ctx->stream);
    cudaStreamDestroy(ctx->stream);
    delete ctx;
    return SOFIE_CUDA_OK;

@@ -7,6 +7,7 @@
 
 #include <map>
 #include <mutex>
+#include <vector>
 
 namespace sofie {
 
@@ -141,18 +142,21 @@ int launch_gemm_f32_splitk(cudaStream_t s, const sofie_gemm_f32_desc &d, const f
 constexpr size_t kSplitKScratchFloats = size_t(1) << 19; // 2 MB: 64 slabs x 8192 outputs
 constexpr int kSplitKPoolBuffers = 16;
 
+struct SplitKDevicePool {
+   float *base = nullptr;
+   std::map<cudaStream_t, int> slot_of;
+   std::vector<int> free_slots;
+   int next_slot = 0;
+};
+std::mutex g_splitk_pool_mutex;
+SplitKDevicePool g_splitk_pools[64];
+
 float *splitk_scratch_for(cudaStream_t s)
 {
-   struct DevicePool {
-      float *base = nullptr;
-      std::map<cudaStream_t, int> slot_of;
-   };
-   static std::mutex mutex;
-   static DevicePool pools[64];
    int dev = 0;
    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-   std::lock_guard<std::mutex> lock(mutex);
-   DevicePool &pool = pools[dev];
+   std::lock_guard<std::mutex> lock(g_splitk_pool_mutex);
+   SplitKDevicePool &pool = g_splitk_pools[dev];
    if (!pool.base) {
       if (cudaMalloc(&pool.base, kSplitKPoolBuffers * kSplitKScratchFloats * sizeof(float)) != cudaSuccess) {
          cudaGetLastError();
@@ -162,10 +166,31 @@ float *splitk_scratch_for(cudaStream_t s)
    }
    auto it = pool.slot_of.find(s);
    if (it == pool.slot_of.end()) {
-      if ((int)pool.slot_of.size() >= kSplitKPoolBuffers) return nullptr;
-      it = pool.slot_of.emplace(s, (int)pool.slot_of.size()).first;
+      int slot;
+      if (!pool.free_slots.empty()) {
+         slot = pool.free_slots.back();
+         pool.free_slots.pop_back();
+      } else if (pool.next_slot < kSplitKPoolBuffers) {
+         slot = pool.next_slot++;
+      } else {
+         return nullptr;
+      }
+      it = pool.slot_of.emplace(s, slot).first;
    }
    return pool.base + (size_t)it->second * kSplitKScratchFloats;
+}
+
+// A stream that is about to be destroyed gives its buffer back (called by the context's destructor after
+// the stream has drained), so that the pool bounds the streams alive at one time, not the streams ever made.
+void splitk_scratch_release(int device, cudaStream_t s)
+{
+   if (device < 0 || device >= 64) return;
+   std::lock_guard<std::mutex> lock(g_splitk_pool_mutex);
+   SplitKDevicePool &pool = g_splitk_pools[device];
+   auto it = pool.slot_of.find(s);
+   if (it == pool.slot_of.end()) return;
+   pool.free_slots.push_back(it->second);
+   pool.slot_of.erase(it);
 }
 
 int launch_gemm_f32_splitk_auto(cudaStream_t s, const sofie_gemm_f32_desc &d, const float *A, const float *B,
@@ -173,7 +198,7 @@ int launch_gemm_f32_splitk_auto(cudaStream_t s, const sofie_gemm_f32_desc &d, co
 {
    if (!splitk_shape_ok(d)) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "not a split-K shape");
    float *scratch = splitk_scratch_for(s);
-   if (!scratch) return fail(SOFIE_CUDA_ERR_NOMEM, "no split-K scratch buffer: allocation failed (first call during a stream capture?) or more than 16 streams in use");
+   if (!scratch) return fail(SOFIE_CUDA_ERR_NOMEM, "no split-K scratch buffer: allocation failed (first call during a stream capture?) or more than 16 streams in use at one time");
    return launch_gemm_f32_splitk(s, d, A, B, C, Y, scratch, kSplitKScratchFloats);
 }
 

@@ -488,20 +488,25 @@ static std::string ByteCount(const std::vector<size_t> &shape, ETensorType t)
 
 void RModel::GenerateSessionMembers()
 {
+   fSessionMembers = {"fCtx", "fStream", "fGraphReady", "fUseGraph"};
    fGC += "sofie_cuda_ctx * fCtx = nullptr;   // device context: arena, uploaded weights, stream, captured graph\n";
    fGC += "void * fStream = nullptr;\n";
    fGC += "bool fGraphReady = false;\n";
    fGC += "bool fUseGraph = true;\n";
+   auto pointer = [this](ETensorType type, const std::string &name) {
+      fGC += EMIT::CType(type) + " * " + EMIT::Dev(name) + " = nullptr;\n";
+      fSessionMembers.push_back(EMIT::Dev(name));
+   };
    fGC += "\n// device pointers: model inputs\n";
-   for (auto &n : fInputTensorNames) fGC += EMIT::CType(GetTensorType(n)) + " * " + EMIT::Dev(n) + " = nullptr;\n";
+   for (auto &n : fInputTensorNames) pointer(GetTensorType(n), n);
    if (!fDeviceWeights.empty()) fGC += "// device pointers: weights uploaded by the constructor\n";
-   for (auto &n : fDeviceWeights) fGC += EMIT::CType(GetTensorType(n)) + " * " + EMIT::Dev(n) + " = nullptr;\n";
+   for (auto &n : fDeviceWeights) pointer(GetTensorType(n), n);
    if (!fDeviceBuffers.empty()) fGC += "// device pointers: tables computed by the constructor\n";
-   for (auto &b : fDeviceBuffers) fGC += EMIT::CType(b.second.type) + " * " + EMIT::Dev(b.first) + " = nullptr;\n";
+   for (auto &b : fDeviceBuffers) pointer(b.second.type, b.first);
    fGC += "// device pointers: intermediate tensors, slices of one arena of " + std::to_string(fArenaBytes) + " bytes\n";
    for (auto &op : fOperators) {
       if (op->IsFusedAway()) continue;
-      for (auto &out : op->GetOpOutputTensors()) fGC += EMIT::CType(GetTensorType(out)) + " * " + EMIT::Dev(out) + " = nullptr;\n";
+      for (auto &out : op->GetOpOutputTensors()) pointer(GetTensorType(out), out);
    }
 }
 
@@ -642,7 +647,13 @@ void RModel::GenerateConstructor()
    fGC += "}\n\n";
    fGC += "~Session() { sofie_cuda_ctx_destroy(fCtx); }\n";
    fGC += "Session(const Session &) = delete;\n";
-   fGC += "Session & operator=(const Session &) = delete;\n\n";
+   fGC += "Session & operator=(const Session &) = delete;\n";
+   // movable, so that Sessions can live in a std::vector (one per slot, as SofieFunctor keeps them): the device
+   // context and every pointer into it change hands, the source is left without a context
+   fGC += "Session(Session && other) noexcept\n   : ";
+   for (size_t i = 0; i < fSessionMembers.size(); i++)
+      fGC += (i ? ", " : "") + fSessionMembers[i] + "(other." + fSessionMembers[i] + ")";
+   fGC += "\n{\n   other.fCtx = nullptr;\n}\n\n";
 }
 
 void RModel::GenerateInfer()

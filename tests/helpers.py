@@ -208,3 +208,80 @@ def fixture_to_onnx(name, manifest, arrays):
     inputs = [ow.value_info(i, ow.FLOAT, arrays[f"{name}/in/{i}"].shape) for i in entry["inputs"]]
     outputs = [ow.value_info(entry["nodes"][-1]["outputs"][0], ow.FLOAT, [])]
     return ow.model(name, nodes, inputs, outputs, inits)
+
+
+FUNCTOR_MAIN = r"""
+#include "{header}"
+#include "SOFIE/SOFIEHelpers.hxx"
+#include <cstdio>
+#include <thread>
+#include <vector>
+int main(int argc, char **argv)
+{{
+   if (argc != 4) return 2;
+   const unsigned nslots = 3;
+   try {{
+      auto f = SofieFunctor<{nfeat}, SOFIE_{name}::Session>(nslots, argv[1]);
+      // Sessions are movable: they can be kept in a std::vector, as the reference's functor keeps them
+      std::vector<SOFIE_{name}::Session> sessions;
+      sessions.emplace_back(argv[1]);
+      sessions.emplace_back(argv[1]);
+      const long rows = std::atol(argv[3]);
+      std::vector<float> x(rows * {nfeat});
+      std::FILE *fp = std::fopen(argv[2], "rb");
+      if (!fp || std::fread(x.data(), sizeof(float), x.size(), fp) != x.size()) return 3;
+      std::fclose(fp);
+      std::vector<double> y(rows);
+      std::vector<std::thread> pool;
+      for (unsigned s = 0; s < nslots; s++)
+         pool.emplace_back([&, s] {{
+            for (long i = s; i < rows; i += nslots) {{
+               const float *r = x.data() + i * {nfeat};
+               y[i] = f(s, {args});
+            }}
+         }});
+      for (auto &t : pool) t.join();
+      for (long i = 0; i < rows; i++) std::printf("%.9g\n", y[i]);
+      float first[{nfeat}];
+      for (int k = 0; k < {nfeat}; k++) first[k] = x[k];
+      std::printf("%.9g\n", (double)sessions[1].infer(first)[0]);
+   }} catch (const std::exception &e) {{
+      std::fprintf(stderr, "%s\n", e.what());
+      return 1;
+   }}
+   return 0;
+}}
+"""
+
+
+def build_functor_program(model, name, nfeat):
+    """Emits `model` (batch 1, nfeat input features) and builds a small program that evaluates it through
+    SofieFunctor from three threads. Returns (program, weight file)."""
+    import subprocess
+    from sofie_b200 import _build, generated, onnx_wire
+    hxx = generated.emit(onnx_wire.model_to_onnx(model), name)
+    lib = _build.build()
+    src = hxx.with_name(name + "_functor.cxx")
+    src.write_text(FUNCTOR_MAIN.format(header=hxx.name, name=name, nfeat=nfeat, args=", ".join(f"r[{i}]" for i in range(nfeat))))
+    exe = hxx.with_name(name + "_functor")
+    cmd = ["g++", "-std=c++17", "-O2", "-pthread", "-I", str(generated.ROOT / "include"), "-I", str(generated.HOST / "inc"),
+           "-I", str(hxx.parent), str(src), "-o", str(exe), "-L", str(lib.parent), "-lSOFIE_cuda", f"-Wl,-rpath,{lib.parent}"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compiling the functor program failed:\n{r.stdout}")
+    return exe, hxx.with_suffix(".dat")
+
+
+def tiny_regressor(nfeat=4):
+    """Gemm nfeat -> 8 + Relu, Gemm 8 -> 1 on a single row: the shape of model SofieFunctor is used with."""
+    from sofie_b200 import configs
+    rng = np.random.default_rng(11)
+    m = configs.Model("regressor", "x", (1, nfeat), [])
+    m.weights["w0"] = rng.standard_normal((8, nfeat)).astype(np.float32)
+    m.weights["b0"] = rng.standard_normal(8).astype(np.float32)
+    m.weights["w1"] = rng.standard_normal((1, 8)).astype(np.float32)
+    m.weights["b1"] = rng.standard_normal(1).astype(np.float32)
+    m.layers.append(dict(op="Gemm", A="x", B="w0", C="b0", Y="h", transB=1, relu=True))
+    m.layers.append(dict(op="Gemm", A="h", B="w1", C="b1", Y="y", transB=1))
+    m.output_name = "y"
+    return m

@@ -7,7 +7,7 @@ import re
 import numpy as np
 import pytest
 
-from helpers import FIXTURE_CASES, fixture_to_onnx, load_fixtures
+from helpers import FIXTURE_CASES, build_functor_program, fixture_to_onnx, load_fixtures, tiny_regressor
 from sofie_b200 import configs, generated, onnx_wire
 
 
@@ -166,3 +166,10 @@ def test_conv_transpose_emits_one_call_and_refuses_what_the_reference_refuses():
         generated.emit(graph([onnx_wire.attr_ints("output_shape", [8, 8])]), "convtr_oshape")
     with pytest.raises(RuntimeError, match="group"):
         generated.emit(graph([onnx_wire.attr_int("group", 3)]), "convtr_group")
+
+
+def test_sessions_are_movable_and_the_functor_helper_compiles():
+    exe, dat = build_functor_program(tiny_regressor(), "regressor", 4)
+    assert exe.exists() and dat.exists()
+    text = exe.with_name("regressor.hxx").read_text()
+    assert "Session(Session && other) noexcept" in text and "other.fCtx = nullptr;" in text

@@ -455,3 +455,43 @@ def test_context_arena_upload_copy_and_graph():
         capi.call("sofie_cuda_ctx_check", ctx)
     finally:
         capi.call("sofie_cuda_ctx_destroy", ctx)
+
+
+def test_many_contexts_one_after_another_share_the_splitk_scratch_pool():
+    """Each context's stream borrows a split-K scratch buffer from a pool of 16 and gives it back when the
+    context is destroyed: far more than 16 contexts can come and go, and 16 can be alive at once."""
+    import ctypes as C
+    A = np.random.default_rng(3).standard_normal((24, 2048)).astype(np.float32)
+    Wm = np.random.default_rng(4).standard_normal((10, 2048)).astype(np.float32)
+    ref = o.gemm_f32(A, Wm, transB=1)
+    d = capi.GemmF32Desc(24, 10, 2048, 0, 1, 1.0, 0.0, 0, 0)
+
+    def run(ctx):
+        dW, dA, dY, stream = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+        capi.call("sofie_cuda_ctx_upload", ctx, Wm.ctypes.data_as(C.c_void_p), Wm.nbytes, C.byref(dW))
+        capi.call("sofie_cuda_ctx_arena", ctx, 0, A.nbytes, C.byref(dA))
+        capi.call("sofie_cuda_ctx_arena", ctx, 1 << 18, 24 * 10 * 4, C.byref(dY))
+        capi.call("sofie_cuda_ctx_stream", ctx, C.byref(stream))
+        capi.call("sofie_cuda_ctx_h2d", ctx, dA, A.ctypes.data_as(C.c_void_p), A.nbytes)
+        capi.call("sofie_cuda_gemm_f32", stream, C.byref(d), dA, dW, None, dY)
+        Y = np.empty((24, 10), np.float32)
+        capi.call("sofie_cuda_ctx_d2h", ctx, Y.ctypes.data_as(C.c_void_p), dY, Y.nbytes)
+        assert rel_err(Y, ref) <= FP32_TOL
+
+    for _ in range(40):
+        ctx = C.c_void_p()
+        capi.call("sofie_cuda_ctx_create", C.byref(ctx), 0, 1 << 19)
+        try:
+            run(ctx)
+        finally:
+            capi.call("sofie_cuda_ctx_destroy", ctx)
+    alive = []
+    try:
+        for _ in range(15):   # the test session's own stream may hold one buffer of the pool
+            ctx = C.c_void_p()
+            capi.call("sofie_cuda_ctx_create", C.byref(ctx), 0, 1 << 19)
+            alive.append(ctx)
+            run(ctx)
+    finally:
+        for ctx in alive:
+            capi.call("sofie_cuda_ctx_destroy", ctx)

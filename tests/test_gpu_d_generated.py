@@ -87,3 +87,21 @@ def test_fp8_chain_through_generated_session(cuda_device):
     assert np.array_equal(y, np.asarray(y_mirror, np.float32).ravel())
     ref = run_model.run(m, x, fp8_scales=scales)
     assert rel_err(y, ref) <= 2e-2
+
+
+def test_functor_with_one_session_per_slot_on_three_threads(cuda_device, tmp_path):
+    import subprocess
+    from helpers import build_functor_program, tiny_regressor
+    m = tiny_regressor()
+    exe, dat = build_functor_program(m, "regressor", 4)
+    rows = 60
+    x = np.random.default_rng(5).standard_normal((rows, 4)).astype(np.float32)
+    (tmp_path / "x.f32").write_bytes(x.tobytes())
+    r = subprocess.run([str(exe), str(dat), str(tmp_path / "x.f32"), str(rows)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    y = np.array([float(v) for v in r.stdout.split()])
+    m.input_shape = (rows, 4)
+    ref = run_model.run(m, x).ravel()
+    assert y.size == rows + 1
+    assert rel_err(y[:rows].astype(np.float32), ref) <= 1e-5
+    assert abs(y[rows] - ref[0]) <= 1e-5 * np.abs(ref).max()
