@@ -47,6 +47,36 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 
 constexpr int kNumSMs = 148; // B200
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched with launch_dependent() may start while the kernel before it on the stream is
+// still running: its blocks become resident as soon as every block of the predecessor has executed
+// griddep_launch_dependents() (or exited) and resources are free, run their prologue (barrier setup,
+// TMEM allocation, constant weights into shared memory) and then block in griddep_wait() until the
+// predecessor has completed and its writes are visible. Rules kept by every kernel launched this way:
+// every block executes griddep_wait() before it reads or writes anything another kernel touches and
+// before it exits (so that completion of this grid implies completion of all earlier ones); only
+// constant data (weights, biases, descriptors) is touched before it. Both instructions are no-ops in
+// a kernel that was launched the ordinary way. SOFIE_CUDA_PDL=0 turns the attribute off.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args)
+{
+   cudaLaunchConfig_t cfg = {};
+   cfg.gridDim = grid;
+   cfg.blockDim = block;
+   cfg.dynamicSmemBytes = smem;
+   cfg.stream = stream;
+   cudaLaunchAttribute attr[1];
+   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+   attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+   cfg.attrs = attr;
+   cfg.numAttrs = 1;
+   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename T>
 __host__ __device__ constexpr T ceil_div(T a, T b)
 {

@@ -50,6 +50,7 @@ qconv3x3_first_kernel(ConvGeom g, const uint8_t *__restrict__ X, const int8_t *_
                       const int32_t *__restrict__ bias, int x_zp, int y_zp, uint8_t *__restrict__ Y, long long num_tiles,
                       int tiles_x, int tiles_y)
 {
+   griddep_launch_dependents(); // the next kernel may set itself up (weights into shared memory) while this one runs
    constexpr int K = 9 * C, KW = (K + 3) / 4;
    constexpr int TS = 16 * POOL + 2;  // side of the haloed input tile
    constexpr int TP = (TS + 3) / 4 * 4;
@@ -205,6 +206,7 @@ __global__ void __launch_bounds__(kFirstF32Threads, 4)
 conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *__restrict__ Wt, const float *__restrict__ bias,
                          float *__restrict__ Y, long long num_tiles, int tiles_x, int tiles_y)
 {
+   griddep_launch_dependents(); // the next kernel may set itself up (weights into shared memory) while this one runs
    constexpr int K = 9 * C;
    constexpr int TSH = 2 * kFirstF32UnitsY + 2, TS = 34; // haloed input tile: 18 rows x 34 columns
    constexpr int OCC = 8;

@@ -36,6 +36,11 @@ int fail(int status, const char *fmt, ...)
 }
 
 void set_last_engine(int engine) { g_last_engine = engine; }
+bool pdl_enabled()
+{
+   static const bool v = [] { const char *e = getenv("SOFIE_CUDA_PDL"); return !e || atoi(e) != 0; }();
+   return v;
+}
 int forced_engine() { return g_forced_engine; }
 
 // One status word per device, allocated on first use with that device current.

@@ -205,6 +205,8 @@ __device__ __forceinline__ uint8_t quant_u8(float x, float scale, int zp)
 __global__ void quantize_u8_kernel(const float *__restrict__ X, uint8_t *__restrict__ Y, size_t n, float scale, int zp,
                                    bool vec)
 {
+   griddep_launch_dependents();
+   griddep_wait(); // X is the previous kernel's output
    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
    size_t n4 = vec ? n / 4 : 0;
    // several independent 16-byte loads in flight per thread
@@ -221,6 +223,8 @@ __global__ void quantize_u8_kernel(const float *__restrict__ X, uint8_t *__restr
 __global__ void dequantize_u8_kernel(const uint8_t *__restrict__ X, float *__restrict__ Y, size_t n, float scale,
                                      int zp, bool vec)
 {
+   griddep_launch_dependents();
+   griddep_wait(); // X is the previous kernel's output
    const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
    size_t n4 = vec ? n / 4 : 0;
 #pragma unroll 4
@@ -449,8 +453,8 @@ int sofie_cuda_quantize_u8(void *stream, const float *X, uint8_t *Y, size_t n, f
    SOFIE_REQUIRE(scale > 0.f && zp >= 0 && zp <= 255, "bad quantisation parameters");
    if (n == 0) return SOFIE_CUDA_OK;
    bool vec = aligned16(X) && (reinterpret_cast<uintptr_t>(Y) & 3) == 0;
-   quantize_u8_kernel<<<grid_for(vec ? n / 4 + 1 : n), kThreads, 0, as_stream(stream)>>>(X, Y, n, scale, zp, vec);
-   SOFIE_LAUNCH_CHECK("quantize_u8_kernel");
+   SOFIE_CUDA_TRY(launch_dependent(quantize_u8_kernel, dim3(grid_for(vec ? n / 4 + 1 : n)), dim3(kThreads), 0, as_stream(stream), X, Y, n, scale,
+                                   (int)zp, vec));
    return SOFIE_CUDA_OK;
 }
 
@@ -459,8 +463,8 @@ int sofie_cuda_dequantize_u8(void *stream, const uint8_t *X, float *Y, size_t n,
    SOFIE_REQUIRE(X && Y, "NULL tensor");
    if (n == 0) return SOFIE_CUDA_OK;
    bool vec = aligned16(Y) && (reinterpret_cast<uintptr_t>(X) & 3) == 0;
-   dequantize_u8_kernel<<<grid_for(vec ? n / 4 + 1 : n), kThreads, 0, as_stream(stream)>>>(X, Y, n, scale, zp, vec);
-   SOFIE_LAUNCH_CHECK("dequantize_u8_kernel");
+   SOFIE_CUDA_TRY(launch_dependent(dequantize_u8_kernel, dim3(grid_for(vec ? n / 4 + 1 : n)), dim3(kThreads), 0, as_stream(stream), X, Y, n, scale,
+                                   (int)zp, vec));
    return SOFIE_CUDA_OK;
 }
 

@@ -27,6 +27,8 @@ gemm_f32_splitk_partial_kernel(int M, int N, int K, int slab, const float *__res
 {
    __shared__ __align__(16) float bs[kSplitKMaxN * kSplitKChunk];
    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+   griddep_launch_dependents();
+   griddep_wait(); // A (and possibly B) are the previous kernel's output; nothing worth doing before it
    const int m = blockIdx.x * kSplitKWarps + warp;
    const int s = blockIdx.y;
    const int k0 = s * slab, k1 = min(K, k0 + slab);
@@ -85,6 +87,8 @@ __global__ void gemm_f32_splitk_reduce_kernel(sofie_gemm_f32_desc d, int splits,
                                               const float *__restrict__ C, float *__restrict__ Y)
 {
    const size_t total = (size_t)d.M * d.N;
+   griddep_launch_dependents();
+   griddep_wait(); // the partial sums of the kernel before
    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
       float sum = 0.f;
       for (int s = 0; s < splits; s++) sum += partial[(size_t)s * total + i];
@@ -125,12 +129,12 @@ int launch_gemm_f32_splitk(cudaStream_t s, const sofie_gemm_f32_desc &d, const f
    slab = (slab + 127) & ~127; // whole 512-byte warp requests per slab
    const int used = (d.K + slab - 1) / slab;
    dim3 grid(ceil_div(d.M, kSplitKWarps), used);
-   if (d.transB) gemm_f32_splitk_partial_kernel<true><<<grid, kSplitKWarps * 32, 0, s>>>(d.M, d.N, d.K, slab, A, B, scratch);
-   else gemm_f32_splitk_partial_kernel<false><<<grid, kSplitKWarps * 32, 0, s>>>(d.M, d.N, d.K, slab, A, B, scratch);
-   SOFIE_LAUNCH_CHECK("gemm_f32_splitk_partial_kernel");
+   if (d.transB)
+      SOFIE_CUDA_TRY(launch_dependent(gemm_f32_splitk_partial_kernel<true>, grid, dim3(kSplitKWarps * 32), 0, s, d.M, d.N, d.K, slab, A, B, scratch));
+   else
+      SOFIE_CUDA_TRY(launch_dependent(gemm_f32_splitk_partial_kernel<false>, grid, dim3(kSplitKWarps * 32), 0, s, d.M, d.N, d.K, slab, A, B, scratch));
    const int blocks = (int)ceil_div<size_t>((size_t)d.M * d.N, 256);
-   gemm_f32_splitk_reduce_kernel<<<blocks, 256, 0, s>>>(d, used, scratch, C, Y);
-   SOFIE_LAUNCH_CHECK("gemm_f32_splitk_reduce_kernel");
+   SOFIE_CUDA_TRY(launch_dependent(gemm_f32_splitk_reduce_kernel, dim3(blocks), dim3(256), 0, s, d, used, (const float *)scratch, C, Y));
    set_last_engine(SOFIE_ENGINE_SIMT);
    return SOFIE_CUDA_OK;
 }

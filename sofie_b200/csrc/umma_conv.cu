@@ -277,6 +277,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    SOFIE_PROF_DECL
+   griddep_launch_dependents(); // the next kernel may set itself up while this one runs
    int negative_mult = 0;
    for (int c = threadIdx.x; c < 128; c += blockDim.x) {
       const bool in = c < tg.Cout;
@@ -323,6 +324,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       // Issuing a tensor copy costs the issuing thread a few hundred cycles, so the 2 x TPS copies of
       // a stage are issued by 2 x TPS lanes in parallel; lane 0 waits for the free slot and posts the
       // expected byte count (the phase cannot complete before that arrive, whatever the order).
+      griddep_wait(); // the activations (and, in this variant, every stage) come after the previous kernel
       int g = 0, s = 0; // stage counter, continuous over the tiles of this CTA, and its ring slot
       uint32_t ph = 0;
       bool ok = true;
@@ -545,6 +547,7 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    SOFIE_PROF_DECL
+   griddep_launch_dependents(); // the next kernel may set itself up while this one runs
    int negative_mult = 0;
    for (int c = threadIdx.x; c < 128; c += blockDim.x) {
       const bool in = c < tg.Cout;
@@ -594,6 +597,8 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          const int tap = item / CHUNKS, ch = item - tap * CHUNKS;
          tma_load_2d(w_smem + (size_t)item * COPIES * B_TILE, &tmW, tap * tg.C + ch * (CBK / ES), 0, &w_full);
       }
+      // everything above touched constants only; the activations are the previous kernel's output
+      griddep_wait();
       // patches: one box per plane, issued by as many lanes
       int g = 0, s = 0;
       uint32_t ph = 0;
@@ -820,7 +825,7 @@ static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, c
    const int grid = tg.num_tiles < kNumSMs ? tg.num_tiles : kNumSMs;
    auto kern = umma_conv3x3_patch_kernel<KIND, BN, KPS, G>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-   kern<<<grid, kPatchThreads, smem, s>>>(tmX, tmW, ep, tg, pl, status);
+   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kPatchThreads), smem, s, tmX, tmW, ep, tg, pl, status));
    SOFIE_LAUNCH_CHECK("umma_conv3x3_patch_kernel");
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;
@@ -873,7 +878,7 @@ static int launch_conv_tps(cudaStream_t s, const CUtensorMap &tmX, const CUtenso
    uint32_t *status = device_status_word();
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int grid = tg.num_tiles < kNumSMs ? tg.num_tiles : kNumSMs;
-   kern<<<grid, KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8, smem, s>>>(tmX, tmW, ep, tg, status);
+   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8), smem, s, tmX, tmW, ep, tg, status));
    SOFIE_LAUNCH_CHECK("umma_conv3x3_kernel");
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;

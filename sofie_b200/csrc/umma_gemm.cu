@@ -262,6 +262,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    SOFIE_PROF_DECL
+   griddep_launch_dependents(); // the next kernel may set itself up while this one runs
    const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + kBM - 1) / kBM;
    const int num_tiles = tiles_m * tiles_n;
    const int num_kb = (K * ES + kStageK - 1) / kStageK;
@@ -301,6 +302,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // ---------------- TMA producer ----------------
       // lane 0 waits for the free slot and posts the byte count; lanes 0 and 1 issue the A and the B
       // copy in parallel (issuing a tensor copy costs the issuing thread a few hundred cycles)
+      griddep_wait(); // A is the previous kernel's output
       int g = 0, s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -520,6 +522,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    SOFIE_PROF_DECL
+   griddep_launch_dependents(); // the next kernel may set itself up while this one runs
    const uint32_t rank = cluster_ctarank();
    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
    const int tiles_n = (N + kPairBN - 1) / kPairBN, tiles_m = (M + 2 * kBM - 1) / (2 * kBM);
@@ -555,6 +558,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
    if (warp == 0) {
       // ---------------- TMA producer (both CTAs) ----------------
+      griddep_wait(); // A is the previous kernel's output
       int g = 0, s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -650,8 +654,7 @@ static int launch_pair(cudaStream_t s, const CUtensorMap &tmA, const CUtensorMap
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int tiles = ceil_div(N, kPairBN) * ceil_div(M, 2 * kBM);
    const int pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
-   kern<<<2 * pairs, (2 + kGemmEpilogueWarps8) * 32, smem, s>>>(tmA, tmB, ep, M, N, K, status);
-   SOFIE_LAUNCH_CHECK("umma_gemm_pair_kernel");
+   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(2 * pairs), dim3((2 + kGemmEpilogueWarps8) * 32), smem, s, tmA, tmB, ep, M, N, K, status));
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;
 }
@@ -678,8 +681,7 @@ static int launch_one(cudaStream_t s, const CUtensorMap &tmA, const CUtensorMap 
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int tiles = ceil_div(N, BN) * ceil_div(M, kBM);
    const int grid = tiles < kNumSMs ? tiles : kNumSMs;
-   kern<<<grid, gemm_threads<KIND>(), smem, s>>>(tmA, tmB, ep, M, N, K, stages, status);
-   SOFIE_LAUNCH_CHECK("umma_gemm_kernel");
+   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(gemm_threads<KIND>()), smem, s, tmA, tmB, ep, M, N, K, stages, status));
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;
 }
