@@ -76,6 +76,9 @@ struct sofie_cuda_ctx {
    cudaGraph_t graph = nullptr;
    cudaGraphExec_t graph_exec = nullptr;
    bool capturing = false;
+   // pipelined input upload: parts of the input are copied on a stream of their own, one event per part
+   cudaStream_t copy_stream = nullptr;
+   cudaEvent_t part_event[SOFIE_CUDA_MAX_PARTS] = {};
 };
 
 using namespace sofie;
@@ -179,6 +182,12 @@ int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx)
    if (ctx->staging) cudaFreeHost(ctx->staging);
    if (ctx->result) cudaFreeHost(ctx->result);
    splitk_scratch_release(ctx->device, ctx->stream);
+   if (ctx->copy_stream) {
+      cudaStreamSynchronize(ctx->copy_stream);
+      cudaStreamDestroy(ctx->copy_stream);
+   }
+   for (cudaEvent_t e : ctx->part_event)
+      if (e) cudaEventDestroy(e);
    cudaStreamDestroy(ctx->stream);
    delete ctx;
    return SOFIE_CUDA_OK;
@@ -277,6 +286,37 @@ int sofie_cuda_ctx_h2d(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t b
                                      ctx->stream));
       done += chunk;
    }
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_h2d_part(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t bytes, int part)
+{
+   SOFIE_REQUIRE(ctx && dst && src, "NULL argument");
+   SOFIE_REQUIRE(part >= 0 && part < SOFIE_CUDA_MAX_PARTS, "part index out of range");
+   SOFIE_REQUIRE(!ctx->capturing, "input copies are not part of the captured graph");
+   DeviceGuard guard(ctx->device);
+   if (!ctx->part_event[part]) SOFIE_CUDA_TRY(cudaEventCreateWithFlags(&ctx->part_event[part], cudaEventDisableTiming));
+   if (!is_pinned(src)) {
+      // pageable memory goes through the staging buffer on the compute stream: nothing to overlap, the event
+      // only keeps sofie_cuda_ctx_wait_part valid
+      int rc = sofie_cuda_ctx_h2d(ctx, dst, src, bytes);
+      if (rc) return rc;
+      SOFIE_CUDA_TRY(cudaEventRecord(ctx->part_event[part], ctx->stream));
+      return SOFIE_CUDA_OK;
+   }
+   if (!ctx->copy_stream) SOFIE_CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+   SOFIE_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+   SOFIE_CUDA_TRY(cudaEventRecord(ctx->part_event[part], ctx->copy_stream));
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_wait_part(sofie_cuda_ctx *ctx, int part)
+{
+   SOFIE_REQUIRE(ctx != nullptr, "NULL context");
+   SOFIE_REQUIRE(part >= 0 && part < SOFIE_CUDA_MAX_PARTS && ctx->part_event[part], "no copy was issued for this part");
+   SOFIE_REQUIRE(!ctx->capturing, "input copies are not part of the captured graph");
+   DeviceGuard guard(ctx->device);
+   SOFIE_CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->part_event[part], 0));
    return SOFIE_CUDA_OK;
 }
 

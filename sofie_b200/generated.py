@@ -52,15 +52,17 @@ def build_generator() -> Path:
     return LIBDIR / "sofie_emit"
 
 
-def emit(onnx_bytes: bytes, name: str, batch: int | None = None, workdir: Path | None = None, binary: bool = False) -> Path:
+def emit(onnx_bytes: bytes, name: str, batch: int | None = None, workdir: Path | None = None, binary: bool = False,
+         pipelined: bool = False) -> Path:
     """Parse -> Generate -> OutputGenerated. Returns the path of <name>.hxx (the .dat, or with binary=True the
     .bin, lies next to it)."""
     tool = build_generator()
-    work = Path(workdir) if workdir else WORK / (name + ("_bin_" if binary else "_") + hashlib.sha1(onnx_bytes).hexdigest()[:10])
+    work = Path(workdir) if workdir else WORK / (name + ("_bin_" if binary else "_") + ("pipe_" if pipelined else "") +
+                                                 hashlib.sha1(onnx_bytes).hexdigest()[:10])
     work.mkdir(parents=True, exist_ok=True)
     onnx_path, hxx = work / f"{name}.onnx", work / f"{name}.hxx"
     onnx_path.write_bytes(onnx_bytes)
-    cmd = [str(tool), str(onnx_path), str(hxx)] + ([str(batch)] if batch else []) + (["--binary"] if binary else [])
+    cmd = [str(tool), str(onnx_path), str(hxx)] + ([str(batch)] if batch else []) + (["--binary"] if binary else []) + (["--pipelined-upload"] if pipelined else [])
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"sofie_emit failed: {r.stdout.strip()}")
@@ -137,11 +139,11 @@ class GeneratedSession:
 
 
 def session_from_model(model, name: str | None = None, batch: int | None = None, binary: bool = False,
-                       fp8_scales=None) -> GeneratedSession:
+                       fp8_scales=None, pipelined: bool = False) -> GeneratedSession:
     """configs.Model -> ONNX bytes -> generator -> compiled Session."""
     from . import onnx_wire
     name = name or model.name
-    hxx = emit(onnx_wire.model_to_onnx(model, fp8_scales), name, batch, binary=binary)
+    hxx = emit(onnx_wire.model_to_onnx(model, fp8_scales), name, batch, binary=binary, pipelined=pipelined)
     so = compile_session(hxx, name)
     out_elems = None
     # output size from the emitted header: "std::vector<float> ret_0(<pointer>, <pointer> + N);"

@@ -23,6 +23,7 @@ enum class Options {
    kGNN = 0x8,
    kGNNComponent = 0x10,
    kBinaryWeightFile = 0x40,    // addition: weights in a raw little-endian side file <name>.bin read with one fread per tensor
+   kPipelinedUpload = 0x80,     // addition: upload the input in parts under the first convolution whatever its size (default: from 32 MB)
 };
 
 enum class WeightFileType { None, RootBinary, Text, Binary };

@@ -44,6 +44,12 @@ public:
    // true when the operator can read a rank-4 input stored NHWC on the device
    virtual bool AcceptsNHWC(const std::string & /*input*/) const { return false; }
 
+   // Pipelined input upload: an operator that reads the model input and treats the samples of a batch
+   // independently can be launched on slice `part` of `parts` equal slices of the batch (`part` is a
+   // variable of the emitted code), so that it works on one slice while the next is still being copied.
+   virtual bool CanSliceBatch(size_t /*parts*/) const { return false; }
+   virtual std::string GenerateBatchSlice(std::string /*OpName*/, size_t /*parts*/) { return ""; }
+
    const std::vector<std::string> &GetOpInputTensors() const { return fInputTensorNames; }
    const std::vector<std::string> &GetOpOutputTensors() const { return fOutputTensorNames; }
 

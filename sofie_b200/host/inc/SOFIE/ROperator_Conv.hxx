@@ -210,22 +210,37 @@ public:
       if (!fNB.empty()) model.UseOnDevice(fNB);
    }
 
-   std::string Generate(std::string OpName) override
+   // the samples of a batch are independent: any equal split of the batch axis is a valid launch
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && !fShapeX.empty() && fShapeX[0] % parts == 0 && fShapeX[0] >= parts; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   // parts == 1: the whole batch; otherwise the launch for slice `part` (a variable of the emitted code)
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       OpName = "op_" + OpName;
       if (fShapeX.empty() || fShapeW.empty() || fShapeY.empty())
          throw std::runtime_error("SOFIE Conv Op called to Generate without being initialized first");
       std::stringstream out;
       out << "\n" << SP << "//----  operator Conv " << OpName << (fFusedRelu ? " + Relu" : "") << (fFusedPool ? " + MaxPool2x2" : "")
-          << " -> " << fNOut << " " << ConvertShapeToString(fShapeOut) << (fLayoutY == ELayout::NHWC ? " (NHWC)" : "") << "\n";
+          << " -> " << fNOut << " " << ConvertShapeToString(fShapeOut) << (fLayoutY == ELayout::NHWC ? " (NHWC)" : "");
+      if (parts > 1) out << ", one of " << parts << " slices of the batch";
+      out << "\n";
       out << SP << "{\n";
-      out << SP << SP << "const sofie_conv2d_desc d = {" << fShapeX[0] << ", " << fShapeX[1] << ", " << fShapeX[2] << ", "
+      std::string x = EMIT::Dev(fNX), y = EMIT::Dev(fNOut);
+      if (parts > 1) {
+         // the batch axis is outermost in NCHW and in NHWC: a slice is a contiguous range of both tensors
+         x += " + (size_t)part * " + std::to_string(ConvertShapeToLength(fShapeX) / parts);
+         y += " + (size_t)part * " + std::to_string(ConvertShapeToLength(fShapeOut) / parts);
+      }
+      out << SP << SP << "const sofie_conv2d_desc d = {" << fShapeX[0] / parts << ", " << fShapeX[1] << ", " << fShapeX[2] << ", "
           << fShapeX[3] << ", " << fShapeW[0] << ", " << fAttr.kH << ", " << fAttr.kW << ", " << fAttr.padH << ", " << fAttr.padW
           << ", " << fAttr.sH << ", " << fAttr.sW << ", " << fAttr.dH << ", " << fAttr.dW << ", " << fAttr.group << ", "
           << (int)fLayoutX << ", " << (int)fLayoutY << ", " << (fPacked ? 1 : 0) << ", " << (fFusedRelu ? 1 : 0) << ", "
           << fFusedPool << "};\n";
-      out << EMIT::Call(SP + SP, "sofie_cuda_conv2d_f32(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNWdev) + ", " +
-                                    (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB)) + ", " + EMIT::Dev(fNOut) + ")");
+      out << EMIT::Call(SP + SP, "sofie_cuda_conv2d_f32(fStream, &d, " + x + ", " + EMIT::Dev(fNWdev) + ", " +
+                                    (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB)) + ", " + y + ")");
       out << SP << "}\n";
       return out.str();
    }

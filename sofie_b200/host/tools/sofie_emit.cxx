@@ -1,4 +1,4 @@
-// sofie_emit <model.onnx> <output.hxx> [batch] [--binary]
+// sofie_emit <model.onnx> <output.hxx> [batch] [--binary] [--pipelined-upload]
 // The reference's usage pattern (src/SOFIE_core/README.md:26-57, test/EmitFromONNX.cxx.in:13-22):
 // Parse -> Generate -> OutputGenerated, which writes the header and, next to it, the weight file.
 #include <cstdlib>
@@ -10,19 +10,20 @@
 int main(int argc, char **argv)
 {
    if (argc < 3) {
-      std::cerr << "usage: " << argv[0] << " <model.onnx> <output.hxx> [batch size for parametric inputs] [--binary]\n";
+      std::cerr << "usage: " << argv[0] << " <model.onnx> <output.hxx> [batch size for parametric inputs] [--binary] [--pipelined-upload]\n";
       return 2;
    }
    try {
       SOFIE::RModelParser_ONNX parser;
       SOFIE::RModel model = parser.Parse(argv[1]);
-      bool binary = false;
+      auto options = static_cast<std::underlying_type_t<SOFIE::Options>>(SOFIE::Options::kDefault);
       int batch = -1;
       for (int i = 3; i < argc; i++) {
-         if (std::string(argv[i]) == "--binary") binary = true;
+         if (std::string(argv[i]) == "--binary") options = options | SOFIE::Options::kBinaryWeightFile;
+         else if (std::string(argv[i]) == "--pipelined-upload") options = options | SOFIE::Options::kPipelinedUpload;
          else batch = std::atoi(argv[i]);
       }
-      model.Generate(binary ? SOFIE::Options::kBinaryWeightFile : SOFIE::Options::kDefault, batch);
+      model.Generate(options, batch);
       model.OutputGenerated(argv[2]);
    } catch (const std::exception &e) {
       std::cerr << "sofie_emit: " << e.what() << "\n";

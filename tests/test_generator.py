@@ -173,3 +173,19 @@ def test_sessions_are_movable_and_the_functor_helper_compiles():
     assert exe.exists() and dat.exists()
     text = exe.with_name("regressor.hxx").read_text()
     assert "Session(Session && other) noexcept" in text and "other.fCtx = nullptr;" in text
+
+
+def test_large_input_is_uploaded_in_parts_under_the_first_convolution():
+    m, _ = configs.cnn_f32(batch=256)
+    text = generated.emit(onnx_wire.model_to_onnx(m), "c2_b256", pipelined=True).read_text()
+    # four copies on the copy stream, the first convolution once per part, the rest of the model as the captured graph
+    assert "void LaunchHead(int part)" in text and text.count("sofie_cuda_ctx_h2d_part(") == 1 and "sofie_cuda_ctx_wait_part(fCtx, part)" in text
+    assert "const sofie_conv2d_desc d = {64, 3, 32, 32, 16," in text       # a quarter of the batch per launch
+    assert "dev_x + (size_t)part * 196608" in text and "dev_r0 + (size_t)part * 1048576" in text
+    assert text.count("sofie_cuda_conv2d_f32(") == 3 and "sofie_cuda_ctx_h2d(fCtx" not in text
+    # without the option an input of a few megabytes is copied in one piece (a copy's fixed cost outweighs the overlap) ...
+    plain = _emit(m, "c2_b256").read_text()
+    assert "LaunchHead" not in plain and "sofie_cuda_ctx_h2d(fCtx, dev_x" in plain
+    # ... and from 32 MB on the parts come by themselves
+    big = _emit(configs.cnn_f32(batch=4096, with_input=False)[0], "c2_b4096").read_text()
+    assert "void LaunchHead(int part)" in big and "const sofie_conv2d_desc d = {1024, 3, 32, 32, 16," in big

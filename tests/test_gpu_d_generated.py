@@ -105,3 +105,23 @@ def test_functor_with_one_session_per_slot_on_three_threads(cuda_device, tmp_pat
     assert y.size == rows + 1
     assert rel_err(y[:rows].astype(np.float32), ref) <= 1e-5
     assert abs(y[rows] - ref[0]) <= 1e-5 * np.abs(ref).max()
+
+
+def test_pipelined_upload_from_pinned_and_pageable_memory(cuda_device):
+    """C2 at batch 256 with the pipelined upload forced: the emitted infer() copies the input in four parts and launches the first convolution per part.
+    Pinned host memory takes the copy stream, pageable memory the staging path; both give the reference's numbers."""
+    import torch
+    m, x = configs.cnn_f32()
+    s = generated.session_from_model(m, "c2_b256_pipe", pipelined=True)
+    y_pageable = s.infer(x)
+    xp = torch.from_numpy(x).pin_memory()
+    yp = torch.empty(s.out_elems, dtype=torch.float32).pin_memory()
+    for _ in range(3):      # eager first call, then graph replays
+        s.infer_ptr(xp.data_ptr(), yp.data_ptr())
+    assert np.array_equal(yp.numpy(), y_pageable)
+    assert rel_err(y_pageable, REF["ref_c2"]) <= 1e-5
+    # another batch through the same Session: no stale slice survives
+    x2 = np.ascontiguousarray(x[::-1])
+    xp.copy_(torch.from_numpy(x2))
+    s.infer_ptr(xp.data_ptr(), yp.data_ptr())
+    assert rel_err(yp.numpy().reshape(256, -1)[::-1], REF["ref_c2"].reshape(256, -1)) <= 1e-5
