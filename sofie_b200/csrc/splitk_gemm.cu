@@ -40,22 +40,11 @@ gemm_f32_splitk_partial_kernel(int M, int N, int K, int slab, const float *__res
    for (int c0 = k0; c0 < k1; c0 += kSplitKChunk) {
       const int len = min(kSplitKChunk, k1 - c0);
       __syncthreads(); // the previous chunk is no longer read
-      // Only the `len` columns that are read below are staged (rounded up to the 4 a lane reads at once, the
-      // rest of a quad zero). Several loads are in flight per thread: staged one at a time, the 10 to 20 loads
-      // of a thread cost one L2 round trip each, which was half of this kernel's time.
-      const int len4 = (len + 3) & ~3;
-      if (TB) {
-#pragma unroll 8
-         for (int i = threadIdx.x; i < N * len4; i += kSplitKWarps * 32) {
-            const int n = i / len4, kk = i - n * len4;
-            bs[n * kSplitKChunk + kk] = kk < len ? __ldg(B + (size_t)n * K + c0 + kk) : 0.f;
-         }
-      } else {
-#pragma unroll 8
-         for (int i = threadIdx.x; i < N * len4; i += kSplitKWarps * 32) {
-            const int kk = i / N, n = i - kk * N;
-            bs[n * kSplitKChunk + kk] = kk < len ? __ldg(B + (size_t)(c0 + kk) * N + n) : 0.f;
-         }
+      for (int i = threadIdx.x; i < N * kSplitKChunk; i += kSplitKWarps * 32) {
+         const int n = TB ? i / kSplitKChunk : i % N, kk = TB ? i % kSplitKChunk : i / N;
+         float v = 0.f;
+         if (kk < len) v = TB ? B[(size_t)n * K + c0 + kk] : B[(size_t)(c0 + kk) * N + n];
+         bs[n * kSplitKChunk + kk] = v;
       }
       __syncthreads();
       if (m < M) {
@@ -101,17 +90,8 @@ __global__ void gemm_f32_splitk_reduce_kernel(sofie_gemm_f32_desc d, int splits,
    griddep_launch_dependents();
    griddep_wait(); // the partial sums of the kernel before
    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-      // the partial sums are added in slab order, eight loads in flight at a time
       float sum = 0.f;
-      int s = 0;
-      for (; s + 8 <= splits; s += 8) {
-         float v[8];
-#pragma unroll
-         for (int j = 0; j < 8; j++) v[j] = partial[(size_t)(s + j) * total + i];
-#pragma unroll
-         for (int j = 0; j < 8; j++) sum += v[j];
-      }
-      for (; s < splits; s++) sum += partial[(size_t)s * total + i];
+      for (int s = 0; s < splits; s++) sum += partial[(size_t)s * total + i];
       float y = d.alpha * sum;
       if (d.bias_kind == 1) y += d.beta * C[i % d.N];
       else if (d.bias_kind == 2) y += d.beta * C[i];
