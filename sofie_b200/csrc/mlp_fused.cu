@@ -107,13 +107,44 @@ __device__ __forceinline__ void load_x_tile(const MlpParams &p, const float *__r
    }
 }
 
+// One layer for one thread: batch row `arow`, columns q + CSTEP j for j < J, J = NB * 32 / CSTEP known at compile time
+// (NB = the layer's width in units of 32 columns).
+template <int ROWS, int NB>
+__device__ __forceinline__ void mlp_layer(const float *__restrict__ arow, const float *__restrict__ wrow, const float *__restrict__ bs,
+                                          float *__restrict__ nxt, int Kp, int ldw, int N4, int q, bool relu)
+{
+   constexpr int CSTEP = 8 * (32 / ROWS);
+   constexpr int J = NB * 32 / CSTEP;
+   float acc[J];
+#pragma unroll
+   for (int j = 0; j < J; j++) acc[j] = 0.f;
+#pragma unroll 2
+   for (int k = 0; k < Kp; k += 4) {
+      const float4 a = *reinterpret_cast<const float4 *>(arow + k);
+#pragma unroll
+      for (int j = 0; j < J; j++) {
+         const float4 wv = *reinterpret_cast<const float4 *>(wrow + j * CSTEP * ldw + k);
+         acc[j] = fmaf(a.x, wv.x, acc[j]);
+         acc[j] = fmaf(a.y, wv.y, acc[j]);
+         acc[j] = fmaf(a.z, wv.z, acc[j]);
+         acc[j] = fmaf(a.w, wv.w, acc[j]);
+      }
+   }
+#pragma unroll
+   for (int j = 0; j < J; j++) {
+      const int n = q + CSTEP * j;
+      if (n < N4) {
+         const float v = acc[j] + bs[n];
+         nxt[n] = relu ? relu_ref(v) : v;
+      }
+   }
+}
+
 template <int ROWS>
 __global__ void __launch_bounds__(kMlpThreads, 1)
 mlp_fused_f32_kernel(MlpParams p, const float *__restrict__ X, float *__restrict__ Y)
 {
-   constexpr int SUB = 32 / ROWS;  // column subgroups of a warp
-   constexpr int CSTEP = 8 * SUB;  // distance between two columns of one thread
-   constexpr int NCOL = 256 / CSTEP; // most columns a thread can own
+   constexpr int SUB = 32 / ROWS;  // column subgroups of a warp; two columns of one thread are 8 * SUB apart
    extern __shared__ __align__(16) float sm[];
    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
    const int r = lane % ROWS, q = w * SUB + lane / ROWS;
@@ -166,40 +197,23 @@ mlp_fused_f32_kernel(MlpParams p, const float *__restrict__ X, float *__restrict
             cp_async_wait_pending(L - 1 - l + (l > 0 ? 1 : 0));
             __syncthreads();
          }
-         const int K = p.d.dims[l], N = p.d.dims[l + 1], Kp = (K + 3) & ~3, J = ((N + 31) & ~31) / CSTEP;
+         const int K = p.d.dims[l], N = p.d.dims[l + 1], Kp = (K + 3) & ~3;
          const int ldw = p.w_ld[l], lda = l == 0 ? p.x_ld : p.act_ld;
          const float *arow = sm + (l == 0 ? p.x_off : p.act_off[(l - 1) & 1]) + r * lda;
          const float *wrow = sm + p.w_off[l] + q * ldw;
          const float *bs = sm + p.b_off[l];
-         float acc[NCOL];
-#pragma unroll
-         for (int j = 0; j < NCOL; j++) acc[j] = 0.f;
-#pragma unroll 2
-         for (int k = 0; k < Kp; k += 4) {
-            const float4 a = *reinterpret_cast<const float4 *>(arow + k);
-#pragma unroll
-            for (int j = 0; j < NCOL; j++) {
-               if (j < J) {
-                  const float4 wv = *reinterpret_cast<const float4 *>(wrow + j * CSTEP * ldw + k);
-                  acc[j] = fmaf(a.x, wv.x, acc[j]);
-                  acc[j] = fmaf(a.y, wv.y, acc[j]);
-                  acc[j] = fmaf(a.z, wv.z, acc[j]);
-                  acc[j] = fmaf(a.w, wv.w, acc[j]);
-               }
-            }
-         }
          const bool relu = p.d.relu[l] != 0;
          const int N4 = (N + 3) & ~3; // the next layer reads k up to its K rounded to 4: columns N .. N4 are written as zeros
          float *nxt = sm + p.act_off[l & 1] + r * p.act_ld;
-#pragma unroll
-         for (int j = 0; j < NCOL; j++) {
-            if (j < J) {
-               const int n = q + CSTEP * j;
-               if (n < N4) {
-                  const float v = acc[j] + bs[n];
-                  nxt[n] = relu ? relu_ref(v) : v;
-               }
-            }
+         switch (((N + 31) & ~31) >> 5) { // the column count is a compile-time constant inside: no predicated-off work
+         case 1: mlp_layer<ROWS, 1>(arow, wrow, bs, nxt, Kp, ldw, N4, q, relu); break;
+         case 2: mlp_layer<ROWS, 2>(arow, wrow, bs, nxt, Kp, ldw, N4, q, relu); break;
+         case 3: mlp_layer<ROWS, 3>(arow, wrow, bs, nxt, Kp, ldw, N4, q, relu); break;
+         case 4: mlp_layer<ROWS, 4>(arow, wrow, bs, nxt, Kp, ldw, N4, q, relu); break;
+         case 5: mlp_layer<ROWS, 5>(arow, wrow, bs, nxt, Kp, ldw, N4, q, relu); break;
+         case 6: mlp_layer<ROWS, 6>(arow, wrow, bs, nxt, Kp, ldw, N4, q, relu); break;
+         case 7: mlp_layer<ROWS, 7>(arow, wrow, bs, nxt, Kp, ldw, N4, q, relu); break;
+         default: mlp_layer<ROWS, 8>(arow, wrow, bs, nxt, Kp, ldw, N4, q, relu); break;
          }
          __syncthreads(); // the next layer (or the copy-out) reads what every warp wrote
          if (l == 0) {
