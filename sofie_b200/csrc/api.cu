@@ -59,8 +59,10 @@ int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *d, const float 
    SOFIE_REQUIRE(A && B && Y, "NULL tensor");
    cudaStream_t s = as_stream(stream);
    // few rows, few columns, long K: split K over the grid instead of running on two or three SMs
-   if (forced_engine() != SOFIE_ENGINE_TCGEN05 && splitk_shape_ok(*d) && ceil_div(d->M, 128) < 32)
+   if (forced_engine() != SOFIE_ENGINE_TCGEN05 && splitk_shape_ok(*d) && ceil_div(d->M, 128) < 32) {
+      if (rowblock_shape_ok(*d, A, B)) return launch_gemm_f32_rowblock(s, *d, A, B, C, Y); // small batch: one launch, no scratch
       return launch_gemm_f32_splitk_auto(s, *d, A, B, C, Y);
+   }
    return dispatch([&] { return launch_gemm_f32_umma(s, *d, A, B, C, Y); },
                    [&] { return launch_gemm_f32_simt(s, *d, A, B, C, Y); });
 }

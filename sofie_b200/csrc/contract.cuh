@@ -33,6 +33,8 @@ int launch_qconv2d_first(cudaStream_t, const ConvGeom &, const uint8_t *, const 
                          int x_zp, int y_zp, uint8_t *);
 // split-K skinny GEMM (splitk_gemm.cu)
 bool splitk_shape_ok(const sofie_gemm_f32_desc &);
+bool rowblock_shape_ok(const sofie_gemm_f32_desc &, const float *A, const float *B);
+int launch_gemm_f32_rowblock(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *, float *);
 int launch_gemm_f32_splitk(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *, float *,
                            float *scratch, size_t scratch_floats);
 int launch_gemm_f32_splitk_auto(cudaStream_t, const sofie_gemm_f32_desc &, const float *, const float *, const float *,

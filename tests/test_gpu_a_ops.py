@@ -39,7 +39,9 @@ def test_reference_golden_vectors(name):
                                               (256, 10, 4096, 0, 1, 1),
                                               # skinny shapes of the split-K kernel: ragged K, both B layouts, full bias
                                               (24, 10, 4096, 0, 1, 1), (100, 16, 1500, 0, 0, 2), (300, 7, 2050, 0, 1, 2),
-                                              (129, 16, 1025, 0, 0, 1), (640, 1, 8192, 0, 1, 0)])
+                                              (129, 16, 1025, 0, 0, 1), (640, 1, 8192, 0, 1, 0),
+                                              # one-launch row-block kernel: rows not a multiple of 4, every bias kind, widest N
+                                              (2, 10, 1024, 0, 1, 2), (1027, 16, 4096, 0, 1, 1), (2048, 3, 1028, 0, 1, 0)])
 def test_gemm_f32(M, N, K, tA, tB, bias):
     rng = np.random.default_rng(M * 7 + N)
     A = rng.standard_normal((K, M) if tA else (M, K)).astype(np.float32)
@@ -461,10 +463,10 @@ def test_many_contexts_one_after_another_share_the_splitk_scratch_pool():
     """Each context's stream borrows a split-K scratch buffer from a pool of 16 and gives it back when the
     context is destroyed: far more than 16 contexts can come and go, and 16 can be alive at once."""
     import ctypes as C
-    A = np.random.default_rng(3).standard_normal((24, 2048)).astype(np.float32)
-    Wm = np.random.default_rng(4).standard_normal((10, 2048)).astype(np.float32)
+    A = np.random.default_rng(3).standard_normal((24, 2050)).astype(np.float32)
+    Wm = np.random.default_rng(4).standard_normal((10, 2050)).astype(np.float32)
     ref = o.gemm_f32(A, Wm, transB=1)
-    d = capi.GemmF32Desc(24, 10, 2048, 0, 1, 1.0, 0.0, 0, 0)
+    d = capi.GemmF32Desc(24, 10, 2050, 0, 1, 1.0, 0.0, 0, 0)  # K not a multiple of 4: the split-K pair, not the one-launch kernel
 
     def run(ctx):
         dW, dA, dY, stream = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
