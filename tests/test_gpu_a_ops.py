@@ -242,6 +242,24 @@ def test_quantize_dequantize_u8_bit_exact():
         assert np.array_equal(q, o.quantize_u8(x, scale, zp))
         d = ops.dequantize_u8(dev(q), scale, zp).cpu().numpy()
         assert np.array_equal(d.view(np.uint32), o.dequantize_u8(q, scale, zp).view(np.uint32))
+        # a view that starts 4 bytes into the buffer: not 16-byte aligned, the element-wise kernel takes it
+        q1 = ops.quantize_u8(dev(x)[1:], scale, zp).cpu().numpy()
+        assert np.array_equal(q1, o.quantize_u8(x[1:], scale, zp))
+
+
+def test_quantize_u8_rounding_boundaries_bit_exact():
+    """The kernel multiplies by 1 / scale and falls back to the exact division near a half-integer quotient: inputs on and
+    one ulp either side of every tie, across scales whose reciprocal is not exact, must still match the divided value."""
+    rng = np.random.default_rng(1)
+    for scale in (0.02, 8 / 255, 0.5, 0.0173, 1e-3, 3.7, 1e-38):
+        s32 = np.float32(scale)
+        ties = ((np.arange(-300, 300) + 0.5) * np.float64(s32)).astype(np.float32)
+        x = np.concatenate([ties, np.nextafter(ties, np.float32(np.inf)), np.nextafter(ties, np.float32(-np.inf)),
+                            (rng.standard_normal(50000) * 100 * scale).astype(np.float32),
+                            np.array([0.0, -0.0, np.inf, -np.inf, 3e38, -3e38, 1e-45, 1e-39], np.float32)])
+        for zp in (0, 128, 255):
+            q = ops.quantize_u8(dev(x), float(s32), zp).cpu().numpy()
+            assert np.array_equal(q, o.quantize_u8(x, float(s32), zp)), (scale, zp)
 
 
 @pytest.mark.parametrize("M,N,K,nk,relu,zp", [(8, 16, 32, 1, 0, 128), (100, 37, 77, 0, 1, 128), (64, 256, 512, 1, 0, 0),
