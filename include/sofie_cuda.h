@@ -338,6 +338,11 @@ typedef struct sofie_qgemm_desc {
 } sofie_qgemm_desc;
 int sofie_cuda_qlinear_matmul(void *stream, const sofie_qgemm_desc *desc, const uint8_t *A, const int8_t *W,
                               const float *mult, const int32_t *corr, uint8_t *Y);
+/* QLinearMatMul followed by DequantizeLinear (same scale and zero point as the product's output) in one
+ * pass: Y = (q - y_zp) * y_scale with q the uint8 value sofie_cuda_qlinear_matmul writes, bit for bit what
+ * sofie_cuda_dequantize_u8 computes from it, without the uint8 tensor's trip through memory. */
+int sofie_cuda_qlinear_matmul_f32(void *stream, const sofie_qgemm_desc *desc, const uint8_t *A, const int8_t *W, const float *mult,
+                                  const int32_t *corr, float y_scale, float *Yf32);
 /* out[N,K] = in[K,N]^T for int8 weights. */
 int sofie_cuda_transpose_i8(void *stream, const int8_t *in, int8_t *out, int32_t rows, int32_t cols);
 
@@ -384,6 +389,11 @@ typedef struct sofie_fp8_gemm_desc {
 } sofie_fp8_gemm_desc;
 int sofie_cuda_gemm_e4m3(void *stream, const sofie_fp8_gemm_desc *desc, const uint8_t *A, const uint8_t *W,
                          const float *bias, uint16_t *Ybf16, uint8_t *Yq);
+/* The same product with the result written as float: Y = float( bf16( relu(...) ) ), bit for bit what
+ * sofie_cuda_gemm_e4m3 followed by sofie_cuda_cast_bf16_f32 writes, without the bf16 tensor's trip through
+ * memory (the last layer of a chain whose result goes back to the host as float). q_scale is ignored. */
+int sofie_cuda_gemm_e4m3_f32(void *stream, const sofie_fp8_gemm_desc *desc, const uint8_t *A, const uint8_t *W,
+                             const float *bias, float *Yf32);
 
 #ifdef __cplusplus
 }

@@ -114,6 +114,7 @@ SIGNATURES = {
     "sofie_cuda_dequantize_u8": [vp, vp, vp, sz, f32, i32],
     "sofie_cuda_qlinear_prepare": [vp, i32, i32, vp, i32, f32, i32, vp, f32, vp, vp, vp],
     "sofie_cuda_qlinear_matmul": [vp, C.POINTER(QGemmDesc), vp, vp, vp, vp, vp],
+    "sofie_cuda_qlinear_matmul_f32": [vp, C.POINTER(QGemmDesc), vp, vp, vp, vp, f32, vp],
     "sofie_cuda_transpose_i8": [vp, vp, vp, i32, i32],
     "sofie_cuda_qlinear_conv2d": [vp, C.POINTER(QConv2dDesc), vp, vp, vp, vp, vp],
     "sofie_cuda_qconv2d_pack_i8": [vp, C.POINTER(QConv2dDesc), vp, vp],
@@ -126,6 +127,7 @@ SIGNATURES = {
     "sofie_cuda_cast_f32_bf16": [vp, vp, vp, sz],
     "sofie_cuda_amax_f32": [vp, vp, sz, vp],
     "sofie_cuda_gemm_e4m3": [vp, C.POINTER(Fp8GemmDesc), vp, vp, vp, vp, vp],
+    "sofie_cuda_gemm_e4m3_f32": [vp, C.POINTER(Fp8GemmDesc), vp, vp, vp, vp],
 }
 STRING_GETTERS = {"sofie_cuda_strerror": [C.c_int], "sofie_cuda_last_error": []}
 SIZE_GETTERS = {"sofie_cuda_mlp_f32_smem": [C.POINTER(MlpDesc)]}

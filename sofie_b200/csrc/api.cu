@@ -130,8 +130,21 @@ int sofie_cuda_qlinear_matmul(void *stream, const sofie_qgemm_desc *d, const uin
    if (d->M == 0) return SOFIE_CUDA_OK;
    SOFIE_REQUIRE(A && W && mult && Y, "NULL tensor");
    cudaStream_t s = as_stream(stream);
-   return dispatch([&] { return launch_qgemm_umma(s, *d, A, W, mult, corr, Y); },
-                   [&] { return launch_qgemm_simt(s, *d, A, W, mult, corr, Y); });
+   return dispatch([&] { return launch_qgemm_umma(s, *d, A, W, mult, corr, Y, nullptr, 0.f); },
+                   [&] { return launch_qgemm_simt(s, *d, A, W, mult, corr, Y, nullptr, 0.f); });
+}
+
+int sofie_cuda_qlinear_matmul_f32(void *stream, const sofie_qgemm_desc *d, const uint8_t *A, const int8_t *W, const float *mult,
+                                  const int32_t *corr, float y_scale, float *Yf32)
+{
+   SOFIE_REQUIRE(d != nullptr, "NULL descriptor");
+   SOFIE_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0, "bad GEMM shape");
+   SOFIE_REQUIRE(d->y_zp >= 0 && d->y_zp <= 255, "y_zp out of range");
+   if (d->M == 0) return SOFIE_CUDA_OK;
+   SOFIE_REQUIRE(A && W && mult && Yf32, "NULL tensor");
+   cudaStream_t s = as_stream(stream);
+   return dispatch([&] { return launch_qgemm_umma(s, *d, A, W, mult, corr, nullptr, Yf32, y_scale); },
+                   [&] { return launch_qgemm_simt(s, *d, A, W, mult, corr, nullptr, Yf32, y_scale); });
 }
 
 int sofie_cuda_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *d, const uint8_t *X, const int8_t *W,
@@ -158,8 +171,20 @@ int sofie_cuda_gemm_e4m3(void *stream, const sofie_fp8_gemm_desc *d, const uint8
    if (d->M == 0) return SOFIE_CUDA_OK;
    SOFIE_REQUIRE(A && W && (Ybf16 || Yq), "NULL tensor");
    cudaStream_t s = as_stream(stream);
-   return dispatch([&] { return launch_gemm_e4m3_umma(s, *d, A, W, bias, Ybf16, Yq); },
-                   [&] { return launch_gemm_e4m3_simt(s, *d, A, W, bias, Ybf16, Yq); });
+   return dispatch([&] { return launch_gemm_e4m3_umma(s, *d, A, W, bias, Ybf16, Yq, nullptr); },
+                   [&] { return launch_gemm_e4m3_simt(s, *d, A, W, bias, Ybf16, Yq, nullptr); });
+}
+
+int sofie_cuda_gemm_e4m3_f32(void *stream, const sofie_fp8_gemm_desc *d, const uint8_t *A, const uint8_t *W, const float *bias,
+                             float *Yf32)
+{
+   SOFIE_REQUIRE(d != nullptr, "NULL descriptor");
+   SOFIE_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0, "bad GEMM shape");
+   if (d->M == 0) return SOFIE_CUDA_OK;
+   SOFIE_REQUIRE(A && W && Yf32, "NULL tensor");
+   cudaStream_t s = as_stream(stream);
+   return dispatch([&] { return launch_gemm_e4m3_umma(s, *d, A, W, bias, nullptr, nullptr, Yf32); },
+                   [&] { return launch_gemm_e4m3_simt(s, *d, A, W, bias, nullptr, nullptr, Yf32); });
 }
 
 } // extern "C"

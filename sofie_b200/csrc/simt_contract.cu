@@ -245,7 +245,8 @@ __device__ __forceinline__ int dp4a_u8s8(unsigned a, int b, int c)
 template <bool WNK>
 __global__ void __launch_bounds__(256)
 qgemm_simt_kernel(sofie_qgemm_desc d, const uint8_t *__restrict__ A, const int8_t *__restrict__ W,
-                  const float *__restrict__ mult, const int32_t *__restrict__ corr, uint8_t *__restrict__ Y)
+                  const float *__restrict__ mult, const int32_t *__restrict__ corr, uint8_t *__restrict__ Y, float *__restrict__ Yf32,
+                  float dq_scale)
 {
    constexpr int BM = 64, BN = 64, BK = 64;
    __shared__ unsigned As[BM][BK / 4 + 1];
@@ -293,17 +294,19 @@ qgemm_simt_kernel(sofie_qgemm_desc d, const uint8_t *__restrict__ A, const int8_
          int gn = n0 + tx * 4 + j;
          if (gn >= d.N) continue;
          int a = acc[i][j] + (corr ? corr[gn] : 0);
-         Y[(size_t)gm * d.N + gn] = (uint8_t)requant_u8(a, mult[gn], d.y_zp, d.relu);
+         const int q = requant_u8(a, mult[gn], d.y_zp, d.relu);
+         if (Yf32) Yf32[(size_t)gm * d.N + gn] = __fmul_rn((float)(q - d.y_zp), dq_scale);
+         else Y[(size_t)gm * d.N + gn] = (uint8_t)q;
       }
    }
 }
 
 int launch_qgemm_simt(cudaStream_t s, const sofie_qgemm_desc &d, const uint8_t *A, const int8_t *W, const float *mult,
-                      const int32_t *corr, uint8_t *Y)
+                      const int32_t *corr, uint8_t *Y, float *Yf32, float dq_scale)
 {
    dim3 grid(ceil_div(d.N, 64), ceil_div(d.M, 64));
-   if (d.w_is_nk) qgemm_simt_kernel<true><<<grid, 256, 0, s>>>(d, A, W, mult, corr, Y);
-   else qgemm_simt_kernel<false><<<grid, 256, 0, s>>>(d, A, W, mult, corr, Y);
+   if (d.w_is_nk) qgemm_simt_kernel<true><<<grid, 256, 0, s>>>(d, A, W, mult, corr, Y, Yf32, dq_scale);
+   else qgemm_simt_kernel<false><<<grid, 256, 0, s>>>(d, A, W, mult, corr, Y, Yf32, dq_scale);
    SOFIE_LAUNCH_CHECK("qgemm_simt_kernel");
    set_last_engine(SOFIE_ENGINE_SIMT);
    return SOFIE_CUDA_OK;
@@ -324,7 +327,7 @@ __device__ __forceinline__ float e4m3_decode(unsigned v)
 
 __global__ void __launch_bounds__(256)
 gemm_e4m3_simt_kernel(sofie_fp8_gemm_desc d, const uint8_t *__restrict__ A, const uint8_t *__restrict__ W,
-                      const float *__restrict__ bias, uint16_t *__restrict__ Ybf16, uint8_t *__restrict__ Yq)
+                      const float *__restrict__ bias, uint16_t *__restrict__ Ybf16, uint8_t *__restrict__ Yq, float *__restrict__ Yf32)
 {
    constexpr int BM = 64, BN = 64, BK = 16;
    __shared__ float lut[256];
@@ -373,6 +376,7 @@ gemm_e4m3_simt_kernel(sofie_fp8_gemm_desc d, const uint8_t *__restrict__ A, cons
          if (d.relu) y = relu_ref(y);
          uint16_t h = f32_to_bf16_rne(y);
          if (Ybf16) Ybf16[(size_t)gm * d.N + gn] = h;
+         if (Yf32) Yf32[(size_t)gm * d.N + gn] = bf16_to_f32(h);
          if (Yq) Yq[(size_t)gm * d.N + gn] =
             (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(bf16_to_f32(h), d.q_scale), __NV_SATFINITE, __NV_E4M3);
       }
@@ -380,10 +384,10 @@ gemm_e4m3_simt_kernel(sofie_fp8_gemm_desc d, const uint8_t *__restrict__ A, cons
 }
 
 int launch_gemm_e4m3_simt(cudaStream_t s, const sofie_fp8_gemm_desc &d, const uint8_t *A, const uint8_t *W,
-                          const float *bias, uint16_t *Ybf16, uint8_t *Yq)
+                          const float *bias, uint16_t *Ybf16, uint8_t *Yq, float *Yf32)
 {
    dim3 grid(ceil_div(d.N, 64), ceil_div(d.M, 64));
-   gemm_e4m3_simt_kernel<<<grid, 256, 0, s>>>(d, A, W, bias, Ybf16, Yq);
+   gemm_e4m3_simt_kernel<<<grid, 256, 0, s>>>(d, A, W, bias, Ybf16, Yq, Yf32);
    SOFIE_LAUNCH_CHECK("gemm_e4m3_simt_kernel");
    set_last_engine(SOFIE_ENGINE_SIMT);
    return SOFIE_CUDA_OK;

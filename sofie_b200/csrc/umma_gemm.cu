@@ -155,6 +155,30 @@ __device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const ui
          for (int j = 0; j < 32; j++) if (j < ncols) y[j] = v[j];
       }
    } else if constexpr (KIND == kI8) {
+      if (ep.Yf) {
+         // DequantizeLinear of the requantised value in the same pass: y = (q - y_zp) * scale, the float a separate
+         // dequantise kernel would compute from the uint8 tensor
+         float *yf = ep.Yf + (size_t)row * N + col0;
+         const bool vec = ncols == 32 && ((reinterpret_cast<uintptr_t>(yf) & 15) == 0);
+#pragma unroll
+         for (int j4 = 0; j4 < 8; j4++) {
+            const float4 m = cf4[j4], c = cf4[8 + j4];
+            float4 o;
+            o.x = __fmul_rn((float)(requant_u8((int)r[4 * j4 + 0] + __float_as_int(c.x), m.x, ep.y_zp, ep.relu) - ep.y_zp), ep.scale);
+            o.y = __fmul_rn((float)(requant_u8((int)r[4 * j4 + 1] + __float_as_int(c.y), m.y, ep.y_zp, ep.relu) - ep.y_zp), ep.scale);
+            o.z = __fmul_rn((float)(requant_u8((int)r[4 * j4 + 2] + __float_as_int(c.z), m.z, ep.y_zp, ep.relu) - ep.y_zp), ep.scale);
+            o.w = __fmul_rn((float)(requant_u8((int)r[4 * j4 + 3] + __float_as_int(c.w), m.w, ep.y_zp, ep.relu) - ep.y_zp), ep.scale);
+            if (vec) {
+               *reinterpret_cast<float4 *>(yf + 4 * j4) = o;
+            } else {
+               const float ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+               for (int t = 0; t < 4; t++)
+                  if (4 * j4 + t < ncols) yf[4 * j4 + t] = ov[t];
+            }
+         }
+         return;
+      }
       uint8_t *y = ep.Yu8 + (size_t)row * N + col0;
       uint32_t packed[8];
 #pragma unroll
@@ -211,6 +235,20 @@ __device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const ui
          } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) if (j < ncols) y[j] = (uint16_t)(hb[j >> 1] >> (16 * (j & 1)));
+         }
+      }
+      if (ep.Yf) {
+         // the bf16 result widened to fp32 in the same pass (a Cast behind the last layer of a chain): the low
+         // 16 bits of every float are zero, the value is exactly what a separate bf16 -> float kernel would write
+         float *y = ep.Yf + (size_t)row * N + col0;
+         if (ncols == 32 && ((reinterpret_cast<uintptr_t>(y) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+               reinterpret_cast<uint4 *>(y)[j] = make_uint4(hb[2 * j] << 16, hb[2 * j] & 0xFFFF0000u, hb[2 * j + 1] << 16, hb[2 * j + 1] & 0xFFFF0000u);
+         } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++)
+               if (j < ncols) y[j] = __uint_as_float((j & 1) ? (hb[j >> 1] & 0xFFFF0000u) : (hb[j >> 1] << 16));
          }
       }
       if (ep.Yq) {
@@ -749,7 +787,7 @@ int launch_gemm_f32_umma(cudaStream_t s, const sofie_gemm_f32_desc &d, const flo
 }
 
 int launch_qgemm_umma(cudaStream_t s, const sofie_qgemm_desc &d, const uint8_t *A, const int8_t *W, const float *mult,
-                      const int32_t *corr, uint8_t *Y)
+                      const int32_t *corr, uint8_t *Y, float *Yf32, float dq_scale)
 {
    if (!d.w_is_nk) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "tensor-core GEMM takes W as [N,K]");
    umma::GemmEpilogue ep = {};
@@ -757,12 +795,14 @@ int launch_qgemm_umma(cudaStream_t s, const sofie_qgemm_desc &d, const uint8_t *
    ep.corr = corr;
    ep.y_zp = d.y_zp;
    ep.Yu8 = Y;
+   ep.Yf = Yf32;
+   ep.scale = dq_scale;
    ep.relu = d.relu;
    return umma::launch_umma_gemm<umma::kI8>(s, A, W, ep, d.M, d.N, d.K);
 }
 
 int launch_gemm_e4m3_umma(cudaStream_t s, const sofie_fp8_gemm_desc &d, const uint8_t *A, const uint8_t *W,
-                          const float *bias, uint16_t *Ybf16, uint8_t *Yq)
+                          const float *bias, uint16_t *Ybf16, uint8_t *Yq, float *Yf32)
 {
    umma::GemmEpilogue ep = {};
    ep.scale = d.a_scale * d.w_scale;
@@ -771,6 +811,7 @@ int launch_gemm_e4m3_umma(cudaStream_t s, const sofie_fp8_gemm_desc &d, const ui
    ep.bias = bias;
    ep.Ybf16 = Ybf16;
    ep.Yq = Yq;
+   ep.Yf = Yf32;
    ep.relu = d.relu;
    return umma::launch_umma_gemm<umma::kF8>(s, A, W, ep, d.M, d.N, d.K);
 }

@@ -72,6 +72,9 @@ public:
       fOutputTensorNames = {fNY};
    }
    EOpKind Kind() const override { return EOpKind::Cast; }
+   const std::string &InputName() const { return fNX; }
+   const std::string &OutputName() const { return fNY; }
+   bool IsBf16ToFloat() const { return fFrom == ETensorType::BFLOAT16 && fTo == ETensorType::FLOAT; }
    std::vector<ETensorType> TypeInference(std::vector<ETensorType>) override { return {fTo}; }
    std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override { return {input[0]}; }
    void Initialize(RModel &model) override
@@ -99,6 +102,7 @@ class ROperator_Fp8Gemm final : public ROperator {
    float fAScale, fWScale, fOutScale;
    bool fRelu;
    std::vector<size_t> fShapeA, fShapeW;
+   std::string fNYFloat; // set when a Cast to float behind this layer is written by the same launch
 
 public:
    ROperator_Fp8Gemm(float aScale, float wScale, float outScale, bool relu, std::string nameA, std::string nameW, std::string nameB,
@@ -110,6 +114,14 @@ public:
       fOutputTensorNames = {fNY};
    }
    EOpKind Kind() const override { return EOpKind::Fp8Gemm; }
+   const std::string &OutputName() const { return fNY; }
+   bool WritesBf16() const { return !(fOutScale > 0.f); }
+   // a bfloat16 -> float Cast that is the only reader of this layer's output: the epilogue writes the float tensor
+   void FuseCastToFloat(const std::string &castOutput)
+   {
+      fNYFloat = castOutput;
+      fOutputTensorNames = {castOutput};
+   }
    std::vector<ETensorType> TypeInference(std::vector<ETensorType>) override
    {
       return {fOutScale > 0.f ? ETensorType::FLOAT8E4M3FN : ETensorType::BFLOAT16};
@@ -141,14 +153,20 @@ public:
    std::string Generate(std::string OpName) override
    {
       std::stringstream out;
-      out << "\n" << SP << "//------ Fp8Gemm op_" << OpName << (fRelu ? " + Relu" : "") << (fOutScale > 0.f ? " -> E4M3" : " -> bfloat16") << "\n";
+      out << "\n" << SP << "//------ Fp8Gemm op_" << OpName << (fRelu ? " + Relu" : "")
+          << (fOutScale > 0.f ? " -> E4M3" : (fNYFloat.empty() ? " -> bfloat16" : " -> bfloat16 -> float (Cast fused)")) << "\n";
       out << SP << "{\n";
       out << SP << SP << "const sofie_fp8_gemm_desc d = {" << fShapeA[0] << ", " << fShapeW[0] << ", " << fShapeA[1] << ", "
           << EMIT::FloatLit(fAScale) << ", " << EMIT::FloatLit(fWScale) << ", " << (fRelu ? 1 : 0) << ", " << EMIT::FloatLit(fOutScale) << "};\n";
       const std::string bias = fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB);
-      const std::string ybf = fOutScale > 0.f ? std::string("nullptr") : EMIT::Dev(fNY);
-      const std::string yq = fOutScale > 0.f ? EMIT::Dev(fNY) : std::string("nullptr");
-      out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNW) + ", " + bias + ", " + ybf + ", " + yq + ")");
+      if (!fNYFloat.empty()) {
+         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3_f32(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNW) + ", " + bias + ", " +
+                                       EMIT::Dev(fNYFloat) + ")");
+      } else {
+         const std::string ybf = fOutScale > 0.f ? std::string("nullptr") : EMIT::Dev(fNY);
+         const std::string yq = fOutScale > 0.f ? EMIT::Dev(fNY) : std::string("nullptr");
+         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNW) + ", " + bias + ", " + ybf + ", " + yq + ")");
+      }
       out << SP << "}\n";
       return out.str();
    }

@@ -97,6 +97,9 @@ public:
       fOutputTensorNames = {fNY};
    }
    EOpKind Kind() const override { return EOpKind::Dequantize; }
+   const std::string &OutputName() const { return fNY; }
+   float Scale() const { return fScale; }
+   int ZeroPoint() const { return fZp; }
    std::vector<ETensorType> TypeInference(std::vector<ETensorType>) override { return {ETensorType::FLOAT}; }
    std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override { return {input[0]}; }
    void Initialize(RModel &model) override
@@ -127,6 +130,8 @@ public:
 class ROperator_QLinearMatMul final : public ROperator {
    std::string fNA, fNAScale, fNAZp, fNB, fNBScale, fNBZp, fNYScale, fNYZp, fNY;
    std::string fNBdev, fNMult, fNCorr;
+   std::string fNYFloat;       // output of a fused DequantizeLinear
+   float fDequantScale = 0.f;
    std::vector<size_t> fShapeA, fShapeB, fShapeY;
    size_t fM = 0, fN = 0, fK = 0;
    float fAScale = 1.f, fYScale = 1.f;
@@ -152,6 +157,15 @@ public:
       fOutputTensorNames = {fNY};
    }
    const std::string &OutputName() const { return fNY; }
+   int OutputZeroPoint() const { return fYZp; }
+   // A DequantizeLinear with this product's zero point that is the only reader of its output: the product's own
+   // launch writes the float tensor (the scale is the DequantizeLinear's, whatever the product's y_scale)
+   void FuseDequantize(const std::string &floatOutput, float scale)
+   {
+      fNYFloat = floatOutput;
+      fDequantScale = scale;
+      fOutputTensorNames = {floatOutput};
+   }
    std::vector<ETensorType> TypeInference(std::vector<ETensorType>) override { return {ETensorType::UINT8}; }
    std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override
    {
@@ -238,8 +252,13 @@ public:
           << "," << fN << "]\n";
       out << SP << "{\n";
       out << SP << SP << "const sofie_qgemm_desc d = {" << fM << ", " << fN << ", " << fK << ", 1, " << fYZp << ", " << (fRelu ? 1 : 0) << "};\n";
-      out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_matmul(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNBdev) + ", " +
-                                    EMIT::Dev(fNMult) + ", " + EMIT::Dev(fNCorr) + ", " + EMIT::Dev(fNY) + ")");
+      if (!fNYFloat.empty())
+         out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_matmul_f32(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNBdev) + ", " +
+                                       EMIT::Dev(fNMult) + ", " + EMIT::Dev(fNCorr) + ", " + EMIT::FloatLit(fDequantScale) + ", " +
+                                       EMIT::Dev(fNYFloat) + ")  /* + DequantizeLinear */");
+      else
+         out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_matmul(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNBdev) + ", " +
+                                       EMIT::Dev(fNMult) + ", " + EMIT::Dev(fNCorr) + ", " + EMIT::Dev(fNY) + ")");
       out << SP << "}\n";
       return out.str();
    }

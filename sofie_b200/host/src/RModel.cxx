@@ -13,6 +13,7 @@
 #include "sofie_cuda.h" // sofie_mlp_smem_bytes: host arithmetic only, nothing of the library is linked
 #include "SOFIE/ROperator_BatchNormalization.hxx"
 #include "SOFIE/ROperator_Conv.hxx"
+#include "SOFIE/ROperator_Fp8.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
 #include "SOFIE/ROperator_Pool.hxx"
 #include "SOFIE/ROperator_QLinear.hxx"
@@ -339,6 +340,15 @@ void RModel::PlanDevice()
                gemm->SetOutputName(relu->OutputName());
                relu->SetFusedAway();
             }
+      } else if (op->Kind() == EOpKind::Fp8Gemm) {
+         // the bfloat16 result of the last FP8 layer, read only by a Cast to float: one launch writes the float tensor
+         auto *g = dynamic_cast<ROperator_Fp8Gemm *>(op);
+         if (ROperator *next = (g && g->WritesBf16()) ? single_consumer(g->OutputName()) : nullptr)
+            if (auto *cast = dynamic_cast<ROperator_Cast *>(next))
+               if (cast->IsBf16ToFloat()) {
+                  g->FuseCastToFloat(cast->OutputName());
+                  cast->SetFusedAway();
+               }
       } else if (op->Kind() == EOpKind::QLinearMatMul) {
          auto *qmm = dynamic_cast<ROperator_QLinearMatMul *>(op);
          if (ROperator *next = qmm ? single_consumer(qmm->OutputName()) : nullptr)
@@ -346,6 +356,13 @@ void RModel::PlanDevice()
                qmm->FuseRelu(relu->OutputName());
                relu->SetFusedAway();
             }
+         // the uint8 product read only by a DequantizeLinear with the same zero point: one launch writes the floats
+         if (ROperator *next = qmm ? single_consumer(qmm->OutputName()) : nullptr)
+            if (auto *dq = dynamic_cast<ROperator_DequantizeLinear *>(next))
+               if (dq->ZeroPoint() == qmm->OutputZeroPoint()) {
+                  qmm->FuseDequantize(dq->OutputName(), dq->Scale());
+                  dq->SetFusedAway();
+               }
       }
    }
    for (auto &op : fOperators)

@@ -262,6 +262,16 @@ def qlinear_matmul(A, W, mult, corr, *, w_is_nk=True, y_zp=0, relu=False):
     return Y
 
 
+def qlinear_matmul_f32(A, W, mult, corr, y_scale, *, w_is_nk=True, y_zp=0, relu=False):
+    """QLinearMatMul + DequantizeLinear (same zero point) in one pass: float32 (q - y_zp) * y_scale."""
+    M, K = A.shape
+    N = W.shape[0] if w_is_nk else W.shape[1]
+    Y = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    d = capi.QGemmDesc(M, N, K, int(w_is_nk), int(y_zp), int(relu))
+    capi.call("sofie_cuda_qlinear_matmul_f32", _stream(), C.byref(d), _p(A), _p(W), _p(mult), _p(corr), float(y_scale), _p(Y))
+    return Y
+
+
 def qlinear_conv2d(X, W, mult, bias=None, *, shape=None, pad=(0, 0), stride=(1, 1), x_zp=0, y_zp=0, relu=False,
                    pool=0, x_layout=LAYOUT_NCHW, y_layout=LAYOUT_NCHW, w_packed=False, kernel=None):
     N, Cin, H, Wd = shape if shape is not None else X.shape
@@ -336,3 +346,13 @@ def gemm_e4m3(A, W, bias=None, *, a_scale=1.0, w_scale=1.0, relu=False, q_scale=
     d = capi.Fp8GemmDesc(M, N, K, float(a_scale), float(w_scale), int(relu), float(q_scale))
     capi.call("sofie_cuda_gemm_e4m3", _stream(), C.byref(d), _p(A), _p(W), _p(bias), _p(Y), _p(Yq))
     return Y, Yq
+
+
+def gemm_e4m3_f32(A, W, bias=None, *, a_scale=1.0, w_scale=1.0, relu=False):
+    """The FP8 product with the bf16-rounded result written as float32 (Fp8Gemm + Cast in one pass)."""
+    M, K = A.shape
+    N = W.shape[0]
+    Y = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    d = capi.Fp8GemmDesc(M, N, K, float(a_scale), float(w_scale), int(relu), 0.0)
+    capi.call("sofie_cuda_gemm_e4m3_f32", _stream(), C.byref(d), _p(A), _p(W), _p(bias), _p(Y))
+    return Y

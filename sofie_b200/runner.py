@@ -137,8 +137,15 @@ class Session:
                 self.steps.append(Step(f"dequant:{y}", lambda t, x=x, y=y, s=s, zp=zp: t.__setitem__(y, ops.dequantize_u8(t[x], s, zp))))
                 i += 1
             elif op == "QLinearMatMul":
-                self._plan_qmatmul(L)
-                i += 1
+                # a DequantizeLinear with the product's zero point as the only reader: the product writes the floats
+                dq = layers[i + 1] if i + 1 < len(layers) else None
+                if dq is not None and dq["op"] == "DequantizeLinear" and dq["X"] == L["Y"] and dq["zp"] == L["y_zp"] and \
+                        L["Y"] != self.model.output_name and len(self._consumers(L["Y"])) == 1:
+                    self._plan_qmatmul(L, dequant=dq)
+                    i += 2
+                else:
+                    self._plan_qmatmul(L)
+                    i += 1
             elif op == "Fp8Gemm":
                 nxt = layers[i + 1] if i + 1 < len(layers) and layers[i + 1]["op"] == "Fp8Gemm" else None
                 self._plan_fp8(L, fp8_i, first=(fp8_i == 0), nxt=nxt)
@@ -394,7 +401,7 @@ class Session:
         self.layout[y], self.shape[y] = self.layout[x], self.shape[x]
         self.steps.append(Step(f"quant:{y}", lambda t: t.__setitem__(y, ops.quantize_u8(t[x], s, zp))))
 
-    def _plan_qmatmul(self, L):
+    def _plan_qmatmul(self, L, dequant=None):
         mw = self.model.weights
         a, b, y = L["A"], L["B"], L["Y"]
         Wkn = mw[b]  # ONNX order [K,N]
@@ -408,6 +415,17 @@ class Session:
         self.w[b + ":mult"], self.w[b + ":corr"] = mult, corr
         y_zp, relu = L["y_zp"], L.get("relu", False)
         self.layout[y], self.shape[y] = LAYOUT_NCHW, (self.shape[a][0], N)
+
+        if dequant is not None:
+            yf, dq_scale = dequant["Y"], dequant["scale"]
+            self.layout[yf], self.shape[yf] = LAYOUT_NCHW, (self.shape[a][0], N)
+
+            def run_f32(t):
+                A = t[a].reshape(t[a].shape[0], -1)
+                t[yf] = ops.qlinear_matmul_f32(A, self.w[b], self.w[b + ":mult"], self.w[b + ":corr"], dq_scale, w_is_nk=True,
+                                               y_zp=y_zp, relu=relu)
+            self.steps.append(Step(f"qmatmul:{yf}", run_f32, flops=2 * N * K))
+            return
 
         def run(t):
             A = t[a].reshape(t[a].shape[0], -1)
@@ -431,16 +449,18 @@ class Session:
         if first:
             self.steps.append(Step(f"quant_e4m3:{a}", lambda t: t.__setitem__(a + ":q", ops.quantize_e4m3(t[a], a_scale))))
 
-        def run(t):
-            Y, Yq = ops.gemm_e4m3(t[a + ":q"], self.w[b], self.w[c] if c else None, a_scale=a_scale, w_scale=w_scale,
-                                  relu=relu, q_scale=q_scale, want_bf16=(nxt is None))
-            if Yq is not None:
-                t[y + ":q"] = Yq
-            if Y is not None:
-                t[y] = Y
-        self.steps.append(Step(f"fp8gemm:{y}", run, flops=2 * N * K))
         if nxt is None:
-            self.steps.append(Step(f"cast:{y}", lambda t: t.__setitem__(y, ops.cast_bf16_f32(t[y].view(torch.int16)))))
+            # last layer of the chain: bf16 result widened to float in the GEMM's own epilogue (Fp8Gemm + Cast)
+            def run_last(t):
+                t[y] = ops.gemm_e4m3_f32(t[a + ":q"], self.w[b], self.w[c] if c else None, a_scale=a_scale, w_scale=w_scale, relu=relu)
+            self.steps.append(Step(f"fp8gemm:{y}", run_last, flops=2 * N * K))
+            return
+
+        def run(t):
+            _, Yq = ops.gemm_e4m3(t[a + ":q"], self.w[b], self.w[c] if c else None, a_scale=a_scale, w_scale=w_scale,
+                                  relu=relu, q_scale=q_scale, want_bf16=False)
+            t[y + ":q"] = Yq
+        self.steps.append(Step(f"fp8gemm:{y}", run, flops=2 * N * K))
 
     # ------------------------------------------------------------------ execution
     def _run_steps(self, x_dev):

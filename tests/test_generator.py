@@ -141,8 +141,9 @@ def test_fp8_chain_parses_and_emits_through_the_generator():
     scales = configs.calibrate_fp8_scales(m, x)
     hxx = generated.emit(onnx_wire.model_to_onnx(m, scales), "c4_tiny", binary=True)
     text = hxx.read_text()
-    assert text.count("sofie_cuda_gemm_e4m3(") == 3 and text.count("sofie_cuda_quantize_e4m3_f32(") == 1
-    assert text.count("sofie_cuda_cast_bf16_f32(") == 1
+    assert text.count("sofie_cuda_gemm_e4m3(") == 2 and text.count("sofie_cuda_quantize_e4m3_f32(") == 1
+    # the Cast to float behind the last layer is written by that layer's own launch
+    assert text.count("sofie_cuda_gemm_e4m3_f32(") == 1 and "sofie_cuda_cast_bf16_f32(" not in text
     assert re.search(r"std::vector<float>\s+infer\(float\*\s*tensor_x\)", text)
     generated.compile_session(hxx, "c4_tiny")
     with pytest.raises(ValueError):
@@ -189,3 +190,10 @@ def test_large_input_is_uploaded_in_parts_under_the_first_convolution():
     # ... and from 32 MB on the parts come by themselves
     big = _emit(configs.cnn_f32(batch=4096, with_input=False)[0], "c2_b4096").read_text()
     assert "void LaunchHead(int part)" in big and "const sofie_conv2d_desc d = {1024, 3, 32, 32, 16," in big
+
+
+def test_trailing_dequantize_is_written_by_the_last_quantised_product():
+    m, _ = configs.mlp_i8(batch=64)
+    text = _emit(m, "c3_b64").read_text()
+    assert text.count("sofie_cuda_qlinear_matmul(") == 2 and text.count("sofie_cuda_qlinear_matmul_f32(") == 1
+    assert "sofie_cuda_dequantize_u8(" not in text and not re.search(r"\bdev_q3\b", text)   # the uint8 tensor has no slice

@@ -247,6 +247,27 @@ def test_quantize_dequantize_u8_bit_exact():
         assert np.array_equal(q1, o.quantize_u8(x[1:], scale, zp))
 
 
+@pytest.mark.parametrize("M,N,K,relu,zp", [(64, 256, 512, 0, 128), (100, 40, 64, 1, 7), (8192, 256, 1024, 0, 128)])
+def test_qlinear_matmul_float_output_equals_matmul_then_dequantize(M, N, K, relu, zp):
+    rng = np.random.default_rng(N)
+    A = dev(rng.integers(0, 256, (M, K), dtype=np.uint8))
+    Wnk = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    w_scale = rng.uniform(0.001, 0.01, N).astype(np.float32)
+    mult, corr = ops.qlinear_prepare(Wnk, True, 0.02, 128, w_scale, 0.05, None, "cuda")
+    W = dev(Wnk)
+    for engine in (1, 2):
+        ops.set_engine(engine)
+        try:
+            q = ops.qlinear_matmul(A, W, mult, corr, w_is_nk=True, y_zp=zp, relu=bool(relu))
+            yf = ops.qlinear_matmul_f32(A, W, mult, corr, 0.037, w_is_nk=True, y_zp=zp, relu=bool(relu))
+        except capi.SofieCudaError as e:
+            assert engine == 2 and e.status == capi.ERR_UNSUPPORTED
+            continue
+        finally:
+            ops.set_engine(0)
+        assert torch.equal(yf.view(torch.int32), ops.dequantize_u8(q, 0.037, zp).view(torch.int32))
+
+
 def test_quantize_u8_rounding_boundaries_bit_exact():
     """The kernel multiplies by 1 / scale and falls back to the exact division near a half-integer quotient: inputs on and
     one ulp either side of every tie, across scales whose reciprocal is not exact, must still match the divided value."""
@@ -438,6 +459,28 @@ def test_gemm_e4m3(M, N, K):
 
 
 # ------------------------------------------------------------------------------------ context
+@pytest.mark.parametrize("M,N,K,bias,relu", [(64, 96, 128, True, True), (130, 70, 48, False, False), (256, 512, 1024, True, False)])
+def test_gemm_e4m3_float_output_equals_gemm_then_cast(M, N, K, bias, relu):
+    rng = np.random.default_rng(M + N)
+    A = torch.from_numpy(rng.integers(0, 256, (M, K), dtype=np.uint8)).cuda()
+    W = torch.from_numpy(rng.integers(0, 256, (N, K), dtype=np.uint8)).cuda()
+    # keep NaN codes (0x7F / 0xFF) out of the operands
+    A[(A & 0x7F) == 0x7F] = 0
+    W[(W & 0x7F) == 0x7F] = 0
+    b = dev(rng.standard_normal(N).astype(np.float32)) if bias else None
+    for engine in (0, 1, 2):     # automatic, CUDA cores, tensor cores (shapes the tensor-core kernel refuses fall through)
+        ops.set_engine(engine)
+        try:
+            y16, _ = ops.gemm_e4m3(A, W, b, a_scale=0.01, w_scale=0.02, relu=relu)
+            y32 = ops.gemm_e4m3_f32(A, W, b, a_scale=0.01, w_scale=0.02, relu=relu)
+        except capi.SofieCudaError as e:
+            assert engine == 2 and e.status == capi.ERR_UNSUPPORTED
+            continue
+        finally:
+            ops.set_engine(0)
+        assert torch.equal(y32.view(torch.int32), ops.cast_bf16_f32(y16.view(torch.int16)).view(torch.int32))
+
+
 def test_context_arena_upload_copy_and_graph():
     import ctypes as C
     lib = capi.load()
