@@ -13,6 +13,8 @@
 // zero point enters through the padding value and a per-channel correction -zp * sum(w).
 #include "contract.cuh"
 
+#include <cstdlib>
+
 namespace sofie {
 namespace {
 
@@ -195,6 +197,138 @@ qconv3x3_first_kernel(ConvGeom g, const uint8_t *__restrict__ X, const int8_t *_
 }
 
 // ------------------------------------------------------------------------------------------------
+// One input channel with the 2 x 2 pool fused (grey-scale / calorimeter images): the kernel is instruction
+// bound, so everything around the 12 dp4a of a pooled output is cut down.
+//   * a dp4a takes one ROW of the 4 x 4 input patch under a pooling window as it lies in the image (four
+//     consecutive pixels, no repacking of taps); the filter row is stored twice, as (w0,w1,w2,0) for the
+//     left output of the window and as (0,w0,w1,w2) for the right one;
+//   * the six filter words of a channel, its bias and its multiplier are two 16-byte shared-memory loads;
+//   * the input tile is staged with 32-bit loads (the image width is a multiple of 4 and a tile starts on
+//     a multiple of 32 columns, so a word is either inside the image or entirely padding) and a thread
+//     builds each of its four patch rows from two shared words and one funnel shift.
+// Same arithmetic as the general kernel: padding holds the input zero point, bias' = bias - x_zp * sum(w),
+// pooling over the raw sums before requantisation when every multiplier is non-negative.
+__global__ void __launch_bounds__(kFirstThreads)
+qconv3x3_first_c1_pool_kernel(ConvGeom g, const uint8_t *__restrict__ X, const int8_t *__restrict__ Wt, const float *__restrict__ mult,
+                              const int32_t *__restrict__ bias, int x_zp, int y_zp, uint8_t *__restrict__ Y, long long num_tiles,
+                              int tiles_x, int tiles_y)
+{
+   griddep_launch_dependents();
+   constexpr int TS = 34;     // rows of the haloed tile
+   constexpr int TW = 10;     // words per row: image columns px0*2 - 4 .. px0*2 + 35
+   constexpr int OCC = 8;
+   __shared__ unsigned tile[TS][TW + 1];
+   __shared__ uint4 s_wa[kFirstMaxCout]; // filter rows for the left output (w0,w1,w2,0) x 3, bias'
+   __shared__ uint4 s_wb[kFirstMaxCout]; // filter rows for the right output (0,w0,w1,w2) x 3, multiplier bits
+   __shared__ int s_negative;
+
+   const int tid = threadIdx.x;
+   if (tid == 0) s_negative = 0;
+   __syncthreads();
+   for (int oc = tid; oc < kFirstMaxCout; oc += kFirstThreads) {
+      unsigned a[3] = {0, 0, 0}, b[3] = {0, 0, 0};
+      float m = 0.f;
+      int bb = 0;
+      if (oc < g.Cout) {
+         int wsum = 0;
+         for (int r = 0; r < 3; r++) {
+            unsigned w = 0;
+            for (int t = 0; t < 3; t++) {
+               const int v = (int)Wt[weight_index(g, oc, 0, r, t)];
+               wsum += v;
+               w |= (unsigned)(uint8_t)v << (8 * t);
+            }
+            a[r] = w;
+            b[r] = w << 8;
+         }
+         m = mult[oc];
+         bb = (bias ? bias[oc] : 0) - x_zp * wsum;
+         if (!(m >= 0.f)) s_negative = 1;
+      }
+      s_wa[oc] = make_uint4(a[0], a[1], a[2], (unsigned)bb);
+      s_wb[oc] = make_uint4(b[0], b[1], b[2], __float_as_uint(m));
+   }
+   __syncthreads();
+   const bool pool_first = !s_negative;
+   const unsigned pad_word = (unsigned)x_zp * 0x01010101u;
+   const int ty = tid / 16, tx = tid % 16;
+   const int wcols = g.W >> 2; // words per image row
+   for (long long tile_id = blockIdx.x; tile_id < num_tiles; tile_id += gridDim.x) {
+      int n, py0, px0;
+      first_tile_origin(g, tile_id, tiles_x, tiles_y, n, py0, px0);
+      const int ih0 = py0 * 2 - 1, wc0 = (px0 * 2 - 4) >> 2; // first row and first word column of the tile (may be -1)
+      const unsigned *img = reinterpret_cast<const unsigned *>(X + (size_t)n * g.H * g.W);
+      unsigned staged[2];
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+         const int i = tid + j * kFirstThreads;
+         const int r = i / TW, c = i - r * TW;
+         const int ih = ih0 + r, wc = wc0 + c;
+         unsigned v = pad_word;
+         if (i < TS * TW && ih >= 0 && ih < g.H && wc >= 0 && wc < wcols) v = __ldg(img + (size_t)ih * wcols + wc);
+         staged[j] = v;
+      }
+      __syncthreads(); // the previous tile is no longer read
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+         const int i = tid + j * kFirstThreads;
+         if (i < TS * TW) tile[i / TW][i % TW] = staged[j];
+      }
+      __syncthreads();
+      const int ph = py0 + ty, pw = px0 + tx;
+      if (ph >= g.pH || pw >= g.pW) continue;
+      // the four rows of the 4 x 4 patch: image columns 2 pw - 1 .. 2 pw + 2 = tile bytes 3 + 2 tx .. 6 + 2 tx
+      unsigned row[4];
+      {
+         const int byte0 = 3 + 2 * tx, w0 = byte0 >> 2, sh = 8 * (byte0 & 3);
+#pragma unroll
+         for (int r = 0; r < 4; r++) row[r] = __funnelshift_r(tile[2 * ty + r][w0], tile[2 * ty + r][w0 + 1], sh);
+      }
+      const size_t opix = ((size_t)n * g.pH + ph) * g.pW + pw;
+      for (int oc0 = 0; oc0 < g.Cout; oc0 += OCC) {
+         int out[OCC];
+#pragma unroll
+         for (int o = 0; o < OCC; o++) {
+            const uint4 wa = s_wa[oc0 + o], wb = s_wb[oc0 + o]; // channels past Cout hold zeros
+            int a00 = dp4a_u8s8_first(row[0], (int)wa.x, 0), a01 = dp4a_u8s8_first(row[0], (int)wb.x, 0);
+            int a10 = dp4a_u8s8_first(row[1], (int)wa.x, 0), a11 = dp4a_u8s8_first(row[1], (int)wb.x, 0);
+            a00 = dp4a_u8s8_first(row[1], (int)wa.y, a00), a01 = dp4a_u8s8_first(row[1], (int)wb.y, a01);
+            a10 = dp4a_u8s8_first(row[2], (int)wa.y, a10), a11 = dp4a_u8s8_first(row[2], (int)wb.y, a11);
+            a00 = dp4a_u8s8_first(row[2], (int)wa.z, a00), a01 = dp4a_u8s8_first(row[2], (int)wb.z, a01);
+            a10 = dp4a_u8s8_first(row[3], (int)wa.z, a10), a11 = dp4a_u8s8_first(row[3], (int)wb.z, a11);
+            const int b = (int)wa.w;
+            const float m = __uint_as_float(wb.w);
+            int v;
+            if (pool_first) {
+               v = requant_u8(max(max(a00, a01), max(a10, a11)) + b, m, y_zp, g.relu);
+            } else {
+               v = max(max(requant_u8(a00 + b, m, y_zp, g.relu), requant_u8(a01 + b, m, y_zp, g.relu)),
+                       max(requant_u8(a10 + b, m, y_zp, g.relu), requant_u8(a11 + b, m, y_zp, g.relu)));
+            }
+            out[o] = v;
+         }
+         if (g.y_nhwc) {
+            uint8_t *y = Y + opix * g.Cout + oc0;
+            if (oc0 + OCC <= g.Cout && ((reinterpret_cast<uintptr_t>(y) & 7) == 0)) {
+               uint2 pk;
+               pk.x = (unsigned)out[0] | ((unsigned)out[1] << 8) | ((unsigned)out[2] << 16) | ((unsigned)out[3] << 24);
+               pk.y = (unsigned)out[4] | ((unsigned)out[5] << 8) | ((unsigned)out[6] << 16) | ((unsigned)out[7] << 24);
+               *reinterpret_cast<uint2 *>(y) = pk;
+            } else {
+#pragma unroll
+               for (int o = 0; o < OCC; o++)
+                  if (oc0 + o < g.Cout) y[o] = (uint8_t)out[o];
+            }
+         } else {
+#pragma unroll
+            for (int o = 0; o < OCC; o++)
+               if (oc0 + o < g.Cout) Y[(((size_t)n * g.Cout + oc0 + o) * g.pH + ph) * g.pW + pw] = (uint8_t)out[o];
+         }
+      }
+   }
+}
+
+// ------------------------------------------------------------------------------------------------
 // fp32: a thread owns a 2 x 2 block of convolution outputs (the pooling window when the pool is
 // fused, four stored pixels otherwise) and 16 output channels at a time. The weights are read from
 // shared memory as 16-byte broadcasts; each one feeds four FMAs per output, 16 in all, which keeps
@@ -340,6 +474,13 @@ conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *_
    }
 }
 
+// SOFIE_CUDA_FIRST_C1=0 keeps single-channel first layers on the general kernel (used to compare the two)
+bool first_c1_enabled()
+{
+   static const bool v = [] { const char *e = getenv("SOFIE_CUDA_FIRST_C1"); return !e || atoi(e) != 0; }();
+   return v;
+}
+
 bool first_layer_shape(const ConvGeom &g)
 {
    return g.kH == 3 && g.kW == 3 && g.pad_h == 1 && g.pad_w == 1 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 && g.group == 1 &&
@@ -377,6 +518,12 @@ int launch_qconv2d_first(cudaStream_t s, const ConvGeom &g, const uint8_t *X, co
    qconv3x3_first_kernel<CC, PP><<<fg.blocks, kFirstThreads, 0, s>>>(g, X, W, mult, bias, x_zp, y_zp, Y, fg.num_tiles, fg.tiles_x, \
                                                                      fg.tiles_y)
    const int pp = g.pool == 2 ? 2 : 1;
+   if (g.C == 1 && pp == 2 && g.W % 4 == 0 && (reinterpret_cast<uintptr_t>(X) & 3) == 0 && first_c1_enabled()) {
+      qconv3x3_first_c1_pool_kernel<<<fg.blocks, kFirstThreads, 0, s>>>(g, X, W, mult, bias, x_zp, y_zp, Y, fg.num_tiles, fg.tiles_x, fg.tiles_y);
+      SOFIE_LAUNCH_CHECK("qconv3x3_first_c1_pool_kernel");
+      set_last_engine(SOFIE_ENGINE_SIMT);
+      return SOFIE_CUDA_OK;
+   }
    switch (g.C * 10 + pp) {
    case 11: SOFIE_FIRST_Q(1, 1); break;
    case 12: SOFIE_FIRST_Q(1, 2); break;

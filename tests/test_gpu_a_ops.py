@@ -374,6 +374,10 @@ FIRST_LAYER = [
     # N, C, H, W, Cout, x_nhwc, y_nhwc, packed, relu, pool, x_zp
     (5, 1, 64, 64, 32, 0, 1, 1, 1, 2, 0), (3, 3, 32, 32, 16, 0, 1, 1, 1, 0, 0), (2, 1, 20, 36, 12, 0, 0, 0, 1, 2, 7),
     (2, 4, 17, 33, 64, 1, 1, 1, 0, 0, 128), (3, 2, 34, 18, 20, 1, 0, 0, 1, 2, 0), (1, 3, 8, 8, 5, 0, 1, 0, 0, 2, 3),
+    # one channel with the pool fused and a width that is a multiple of 4: the specialised row-word kernel
+    (3, 1, 30, 68, 24, 1, 1, 1, 0, 2, 128), (2, 1, 66, 100, 9, 0, 1, 0, 1, 2, 200), (1, 1, 4, 4, 8, 0, 0, 1, 1, 2, 1),
+    # ... and a width that is not: the general kernel
+    (2, 1, 22, 34, 16, 0, 1, 1, 1, 2, 5),
 ]
 
 
