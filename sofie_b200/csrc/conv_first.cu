@@ -335,7 +335,10 @@ qconv3x3_first_c1_pool_kernel(ConvGeom g, const uint8_t *__restrict__ X, const i
 // the shared-memory pipe off the critical path. A block of 128 threads covers 16 rows x 32 columns of
 // convolution outputs; blocks are kept that small so that four fit on an SM and the load, compute and
 // store phases of different blocks overlap.
-template <int C, int POOL>
+// VEC: NCHW input whose width is a multiple of 4 (and a 16-byte aligned base): the tile is staged with 16-byte
+// asynchronous copies of whole words of the image rows (a tile starts on a multiple of 32 columns, so a word is
+// either inside the image or entirely padding, which the copy zero-fills); the patch then starts at column 3.
+template <int C, int POOL, bool VEC>
 __global__ void __launch_bounds__(kFirstF32Threads, 4)
 conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *__restrict__ Wt, const float *__restrict__ bias,
                          float *__restrict__ Y, long long num_tiles, int tiles_x, int tiles_y)
@@ -344,7 +347,10 @@ conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *_
    constexpr int K = 9 * C;
    constexpr int TSH = 2 * kFirstF32UnitsY + 2, TS = 34; // haloed input tile: 18 rows x 34 columns
    constexpr int OCC = 8;
-   __shared__ float tile[C][TSH][TS + 1];
+   constexpr int TW4 = 10;                       // VEC: 16-byte words per tile row, image columns ux0*2 - 4 .. ux0*2 + 35
+   constexpr int TSW = VEC ? 4 * TW4 : TS + 1;   // row stride of the tile in floats
+   constexpr int COL0 = VEC ? 3 : 0;             // tile column of the patch's first input column
+   __shared__ __align__(16) float tile[C][TSH][TSW];
    __shared__ float4 s_w[K][kFirstMaxCout / 4]; // [tap][channel / 4]
    __shared__ float s_bias[kFirstMaxCout];
 
@@ -357,8 +363,27 @@ conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *_
       uy0 = uy0 / 16 * kFirstF32UnitsY; // this kernel's tiles are 8 units tall
       const int ih0 = uy0 * 2 - 1, iw0 = ux0 * 2 - 1;
       // all loads of a thread are issued before the first store, so their latencies overlap
-      constexpr int kLoads = (C * TSH * TS + kFirstF32Threads - 1) / kFirstF32Threads;
+      constexpr int kLoads = VEC ? 1 : (C * TSH * TS + kFirstF32Threads - 1) / kFirstF32Threads;
       float staged[kLoads];
+      if constexpr (VEC) {
+         __syncthreads(); // the previous tile is no longer read: the copies below write the tile directly
+         constexpr int kPieces = C * TSH * TW4;
+         const int wc0 = (ux0 * 2 - 4) >> 2, wcols = g.W >> 2;
+#pragma unroll
+         for (int j = 0; j < (kPieces + kFirstF32Threads - 1) / kFirstF32Threads; j++) {
+            const int i = tid + j * kFirstF32Threads;
+            if (i < kPieces) {
+               const int c = i / (TSH * TW4), rem = i % (TSH * TW4), r = rem / TW4, w = rem % TW4;
+               const int ih = ih0 + r, wc = wc0 + w;
+               const bool ok = ih >= 0 && ih < g.H && wc >= 0 && wc < wcols;
+               const float *src = X + (((size_t)n * C + c) * g.H + (ok ? ih : 0)) * g.W + 4 * (ok ? wc : 0);
+               const unsigned dst = (unsigned)__cvta_generic_to_shared(&tile[c][r][4 * w]);
+               const int bytes = ok ? 16 : 0; // zero-filled when the word lies outside the image
+               asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+            }
+         }
+         staged[0] = 0.f;
+      } else {
 #pragma unroll
       for (int j = 0; j < kLoads; j++) {
          const int i = tid + j * kFirstF32Threads;
@@ -370,6 +395,7 @@ conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *_
             v = __ldg(X + xi);
          }
          staged[j] = v;
+      }
       }
       if (!weights_staged) {
          // The weights are fetched while the loads of the first tile are still in flight.
@@ -385,13 +411,17 @@ conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *_
          for (int oc = tid; oc < kFirstMaxCout; oc += kFirstF32Threads) s_bias[oc] = (oc < g.Cout && bias) ? __ldg(bias + oc) : 0.f;
          weights_staged = true;
       }
-      __syncthreads(); // weights staged / the previous tile is no longer read
+      if constexpr (VEC) {
+         asm volatile("cp.async.wait_all;\n" ::: "memory");
+      } else {
+         __syncthreads(); // weights staged / the previous tile is no longer read
 #pragma unroll
-      for (int j = 0; j < kLoads; j++) {
-         const int i = tid + j * kFirstF32Threads;
-         if (i < C * TSH * TS) tile[i / (TSH * TS)][(i % (TSH * TS)) / TS][i % TS] = staged[j];
+         for (int j = 0; j < kLoads; j++) {
+            const int i = tid + j * kFirstF32Threads;
+            if (i < C * TSH * TS) tile[i / (TSH * TS)][(i % (TSH * TS)) / TS][i % TS] = staged[j];
+         }
       }
-      __syncthreads();
+      __syncthreads(); // tile and weights are in shared memory
       const int oh0 = (uy0 + ty) * 2, ow0 = (ux0 + tx) * 2; // top-left convolution output of this thread
       if (oh0 >= g.oH || ow0 >= g.oW) continue;
       for (int oc0 = 0; oc0 < g.Cout; oc0 += OCC) {
@@ -406,7 +436,7 @@ conv3x3_first_f32_kernel(ConvGeom g, const float *__restrict__ X, const float *_
 #pragma unroll
             for (int r = 0; r < 4; r++)
 #pragma unroll
-               for (int t = 0; t < 4; t++) win[r][t] = tile[c][ty * 2 + r][tx * 2 + t];
+               for (int t = 0; t < 4; t++) win[r][t] = tile[c][ty * 2 + r][COL0 + tx * 2 + t];
 #pragma unroll
             for (int rt = 0; rt < 9; rt++) {
                const int r = rt / 3, t = rt % 3;
@@ -545,8 +575,11 @@ int launch_conv2d_f32_first(cudaStream_t s, const ConvGeom &g, const float *X, c
    if (!first_layer_shape(g)) return -1;
    const FirstGrid fg = first_grid(g, (g.oW + 1) / 2, (g.oH + 1) / 2, kFirstF32UnitsY, 4);
    if (fg.num_tiles == 0) return SOFIE_CUDA_OK;
-#define SOFIE_FIRST_F(CC, PP) \
-   conv3x3_first_f32_kernel<CC, PP><<<fg.blocks, kFirstF32Threads, 0, s>>>(g, X, W, bias, Y, fg.num_tiles, fg.tiles_x, fg.tiles_y)
+   static const bool vec_enabled = [] { const char *e = getenv("SOFIE_CUDA_FIRST_VEC"); return !e || atoi(e) != 0; }();
+   const bool vec = vec_enabled && !g.x_nhwc && g.W % 4 == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0;
+#define SOFIE_FIRST_F(CC, PP)                                                                                                      \
+   if (vec) conv3x3_first_f32_kernel<CC, PP, true><<<fg.blocks, kFirstF32Threads, 0, s>>>(g, X, W, bias, Y, fg.num_tiles, fg.tiles_x, fg.tiles_y); \
+   else conv3x3_first_f32_kernel<CC, PP, false><<<fg.blocks, kFirstF32Threads, 0, s>>>(g, X, W, bias, Y, fg.num_tiles, fg.tiles_x, fg.tiles_y)
    const int pp = g.pool == 2 ? 2 : 1;
    switch (g.C * 10 + pp) {
    case 11: SOFIE_FIRST_F(1, 1); break;
