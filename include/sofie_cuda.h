@@ -90,6 +90,11 @@ int sofie_cuda_ctx_d2h(sofie_cuda_ctx *ctx, void *dst_host, const void *src_devi
  * returns its address; valid until the next fetch. The emitted infer() builds the vector it
  * returns (RModel.cxx:744-801 in the reference) from it in one pass. */
 int sofie_cuda_ctx_fetch(sofie_cuda_ctx *ctx, const void *src_device, size_t bytes, void **host);
+/* A small result tensor placed in mapped pinned host memory: the kernel that computes it writes across PCIe
+ * itself and sofie_cuda_ctx_fetch of that pointer only waits for the stream (no device-to-host copy, which
+ * costs more than the few kilobytes of a classifier's output are worth). Meant for tensors that no kernel
+ * reads; the memory is zero-initialised and owned by the context. */
+int sofie_cuda_ctx_host_output(sofie_cuda_ctx *ctx, size_t bytes, void **dptr);
 int sofie_cuda_ctx_sync(sofie_cuda_ctx *ctx);
 /* Read and clear the device-side status word that kernels with bounded waits set on give-up. */
 int sofie_cuda_ctx_check(sofie_cuda_ctx *ctx);

@@ -87,6 +87,7 @@ SIGNATURES = {
     "sofie_cuda_ctx_fetch": [vp, vp, sz, C.POINTER(vp)],
     "sofie_cuda_ctx_sync": [vp],
     "sofie_cuda_ctx_check": [vp],
+    "sofie_cuda_ctx_host_output": [vp, sz, C.POINTER(vp)],
     "sofie_cuda_ctx_h2d_part": [vp, vp, vp, sz, C.c_int],
     "sofie_cuda_ctx_wait_part": [vp, C.c_int],
     "sofie_cuda_ctx_graph_begin": [vp],

@@ -8,6 +8,7 @@
 #include "contract.cuh"
 
 #include <cstdlib>
+#include <utility>
 #include <mutex>
 #include <vector>
 
@@ -76,6 +77,8 @@ struct sofie_cuda_ctx {
    cudaGraph_t graph = nullptr;
    cudaGraphExec_t graph_exec = nullptr;
    bool capturing = false;
+   // small results written by the last kernel straight into mapped pinned host memory (no device-to-host copy)
+   std::vector<std::pair<char *, size_t>> host_outputs;
    // pipelined input upload: parts of the input are copied on a stream of their own, one event per part
    cudaStream_t copy_stream = nullptr;
    cudaEvent_t part_event[SOFIE_CUDA_MAX_PARTS] = {};
@@ -179,6 +182,7 @@ int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx)
    if (ctx->graph) cudaGraphDestroy(ctx->graph);
    for (void *p : ctx->owned) cudaFree(p);
    if (ctx->arena) cudaFree(ctx->arena);
+   for (auto &h : ctx->host_outputs) cudaFreeHost(h.first);
    if (ctx->staging) cudaFreeHost(ctx->staging);
    if (ctx->result) cudaFreeHost(ctx->result);
    splitk_scratch_release(ctx->device, ctx->stream);
@@ -347,10 +351,38 @@ int sofie_cuda_ctx_d2h(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t b
 // result (the vector Session::infer returns) from the returned pointer in one pass, instead of
 // zero-filling a vector first and then staging the copy through it. The pointer stays valid until
 // the next fetch on this context.
+int sofie_cuda_ctx_host_output(sofie_cuda_ctx *ctx, size_t bytes, void **dptr)
+{
+   SOFIE_REQUIRE(ctx && dptr, "NULL argument");
+   SOFIE_REQUIRE(bytes > 0, "empty output");
+   DeviceGuard guard(ctx->device);
+   void *p = nullptr, *d = nullptr;
+   SOFIE_CUDA_TRY(cudaHostAlloc(&p, bytes, cudaHostAllocMapped));
+   cudaError_t err = cudaHostGetDevicePointer(&d, p, 0);
+   if (err != cudaSuccess || d != p) { // without unified addressing the two views differ: not supported here
+      cudaFreeHost(p);
+      cudaGetLastError();
+      return fail(SOFIE_CUDA_ERR_CUDA, "mapped host memory is not addressable by the device at its host address");
+   }
+   std::memset(p, 0, bytes);
+   ctx->host_outputs.emplace_back(static_cast<char *>(p), bytes);
+   *dptr = d;
+   return SOFIE_CUDA_OK;
+}
+
 int sofie_cuda_ctx_fetch(sofie_cuda_ctx *ctx, const void *src, size_t bytes, void **host)
 {
    SOFIE_REQUIRE(ctx && src && host, "NULL argument");
    DeviceGuard guard(ctx->device);
+   for (auto &h : ctx->host_outputs) {
+      const char *s8 = static_cast<const char *>(src);
+      if (s8 >= h.first && s8 + bytes <= h.first + h.second) {
+         // the kernels wrote the result into host memory themselves: wait for them, nothing to copy
+         SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+         *host = const_cast<char *>(s8);
+         return SOFIE_CUDA_OK;
+      }
+   }
    if (bytes > ctx->result_bytes) {
       if (ctx->result) cudaFreeHost(ctx->result);
       ctx->result = nullptr;

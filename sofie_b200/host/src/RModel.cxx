@@ -504,6 +504,9 @@ static std::string ByteCount(const std::vector<size_t> &shape, ETensorType t)
    return std::to_string(ConvertShapeToLength(shape) * GetTypeSize(t));
 }
 
+// results up to this size are written by the kernels straight into mapped host memory
+static constexpr size_t kHostOutputMaxBytes = 64 * 1024;
+
 void RModel::GenerateSessionMembers()
 {
    fSessionMembers = {"fCtx", "fStream", "fGraphReady", "fUseGraph"};
@@ -611,6 +614,16 @@ void RModel::GenerateConstructor()
    fGC += "   //--- arena slices of the inputs and intermediate tensors\n";
    for (auto &slot : fArenaOffsets) {
       const std::string &n = slot.first;
+      // A small model output that no operator reads lives in mapped host memory: the last kernel writes it across
+      // PCIe and infer() only waits for the stream instead of issuing a device-to-host copy.
+      const size_t nbytes = ConvertShapeToLength(GetTensorShape(n)) * GetTypeSize(GetTensorType(n));
+      bool aliased = false;
+      for (auto &a : fAliases) aliased = aliased || a.first == n || ResolveAlias(a.first) == n;
+      if (IsModelOutput(n) && Consumers(n).empty() && !aliased && nbytes > 0 && nbytes <= kHostOutputMaxBytes) {
+         fGC += "   Check(sofie_cuda_ctx_host_output(fCtx, " + std::to_string(nbytes) + ", reinterpret_cast<void**>(&" + EMIT::Dev(n) +
+                ")), \"sofie_cuda_ctx_host_output\");\n";
+         continue;
+      }
       fGC += "   Check(sofie_cuda_ctx_arena(fCtx, " + std::to_string(slot.second) + ", " + ByteCount(GetTensorShape(n), GetTensorType(n)) +
              ", reinterpret_cast<void**>(&" + EMIT::Dev(n) + ")), \"sofie_cuda_ctx_arena\");\n";
    }
