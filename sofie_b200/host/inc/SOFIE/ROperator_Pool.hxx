@@ -35,6 +35,7 @@ private:
    RAttributes_Pool fAttr;
    std::string fNX, fNY;
    std::vector<size_t> fShapeX, fShapeY;
+   std::vector<size_t> fShape4; // the input viewed as [N, C, H, W] (H = 1 for a 1-D pooling)
    size_t fKH = 0, fKW = 0, fSH = 1, fSW = 1;
    std::vector<size_t> fPads;
    ELayout fLayout = ELayout::NCHW;
@@ -67,15 +68,24 @@ public:
    std::vector<ETensorType> TypeInference(std::vector<ETensorType> input) override { return input; }
    std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override
    {
-      if (input.size() != 1 || input[0].size() != 4)
-         throw std::runtime_error("SOFIE " + Name() + " Op: only 2-D pooling of a rank-4 tensor is generated for the CUDA path");
-      const auto &x = input[0];
-      fKH = fAttr.kernel_shape.empty() ? x[2] : fAttr.kernel_shape[0];
-      fKW = fAttr.kernel_shape.size() < 2 ? (fAttr.kernel_shape.empty() ? x[3] : fKH) : fAttr.kernel_shape[1];
-      fSH = fAttr.strides.empty() ? 1 : fAttr.strides[0];
-      fSW = fAttr.strides.size() < 2 ? fSH : fAttr.strides[1];
+      if (input.size() != 1 || (input[0].size() != 4 && input[0].size() != 3))
+         throw std::runtime_error("SOFIE " + Name() + " Op: only 1-D and 2-D pooling (rank-3 and rank-4 tensors) is generated for the CUDA path");
+      // a 1-D pooling of [N, C, W] is the 2-D one of [N, C, 1, W] with a window of height 1
+      const bool oneD = input[0].size() == 3;
+      std::vector<size_t> x = input[0];
+      if (oneD) x.insert(x.begin() + 2, 1);
+      auto lift = [&](std::vector<size_t> v, size_t fill) {
+         if (oneD && v.size() == 1) v.insert(v.begin(), fill);
+         return v;
+      };
+      std::vector<size_t> kernel = lift(fAttr.kernel_shape, 1), strides = lift(fAttr.strides, 1), pads = fAttr.pads;
+      if (oneD && pads.size() == 2) pads = {0, pads[0], 0, pads[1]};
+      fKH = kernel.empty() ? x[2] : kernel[0];
+      fKW = kernel.size() < 2 ? (kernel.empty() ? x[3] : fKH) : kernel[1];
+      fSH = strides.empty() ? 1 : strides[0];
+      fSW = strides.size() < 2 ? fSH : strides[1];
       if (fAttr.auto_pad == "NOTSET") {
-         fPads = fAttr.pads.empty() ? std::vector<size_t>{0, 0, 0, 0} : fAttr.pads;
+         fPads = pads.empty() ? std::vector<size_t>{0, 0, 0, 0} : pads;
       } else if (fAttr.auto_pad == "SAME_UPPER" || fAttr.auto_pad == "SAME_LOWER") {
          fPads = {fKH / 2, fKW / 2, fKH / 2, fKW / 2};
          if (fKH % 2 == 1) (fAttr.auto_pad == "SAME_UPPER") ? fPads[0]++ : fPads[2]++;
@@ -86,8 +96,10 @@ public:
          throw std::runtime_error("SOFIE " + Name() + " Op invalid auto_pad value : " + fAttr.auto_pad);
       }
       if (fPads.size() != 4) throw std::runtime_error("SOFIE " + Name() + " Op: pads must have 4 values");
+      fShape4 = x;
       size_t oH = (x[2] + fPads[0] + fPads[2] - fKH) / fSH + 1;
       size_t oW = (x[3] + fPads[1] + fPads[3] - fKW) / fSW + 1;
+      if (oneD) return {{x[0], x[1], oW}};
       return {{x[0], x[1], oH, oW}};
    }
 
@@ -124,14 +136,14 @@ public:
       out << "\n" << SP << "//----  operator " << Name() << "  " << OpName << "\n";
       if (fType == ETensorType::UINT8) {
          out << EMIT::Call(SP, "sofie_cuda_maxpool2d_u8(fStream, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ", " +
-                                  std::to_string(fShapeX[0]) + ", " + std::to_string(fShapeX[1]) + ", " + std::to_string(fShapeX[2]) +
-                                  ", " + std::to_string(fShapeX[3]) + ", " + std::to_string(fKH) + ", " + std::to_string(fKW) + ", " +
+                                  std::to_string(fShape4[0]) + ", " + std::to_string(fShape4[1]) + ", " + std::to_string(fShape4[2]) +
+                                  ", " + std::to_string(fShape4[3]) + ", " + std::to_string(fKH) + ", " + std::to_string(fKW) + ", " +
                                   std::to_string(fSH) + ", " + std::to_string(fSW) + ", " + std::to_string((int)fLayout) + ")");
          return out.str();
       }
       out << SP << "{\n";
-      out << SP << SP << "const sofie_pool2d_desc d = {" << (fPoolMode == MaxPool ? 0 : 1) << ", " << fShapeX[0] << ", " << fShapeX[1]
-          << ", " << fShapeX[2] << ", " << fShapeX[3] << ", " << fKH << ", " << fKW << ", " << fSH << ", " << fSW << ", {" << fPads[0]
+      out << SP << SP << "const sofie_pool2d_desc d = {" << (fPoolMode == MaxPool ? 0 : 1) << ", " << fShape4[0] << ", " << fShape4[1]
+          << ", " << fShape4[2] << ", " << fShape4[3] << ", " << fKH << ", " << fKW << ", " << fSH << ", " << fSW << ", {" << fPads[0]
           << ", " << fPads[1] << ", " << fPads[2] << ", " << fPads[3] << "}, " << fAttr.count_include_pad << ", " << (int)fLayout << "};\n";
       out << EMIT::Call(SP + SP, "sofie_cuda_pool2d_f32(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ")");
       out << SP << "}\n";

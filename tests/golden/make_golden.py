@@ -30,7 +30,7 @@ CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutP
          "Tanh", "Sqrt", "Reciprocal",
          # broadcasting Add (rank <= 4) and transposed convolutions
          "AddBroadcast1", "AddBroadcast2", "AddBroadcast3", "AddBroadcast4", "AddBroadcast5", "AddBroadcast7",
-         "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched"]
+         "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched", "MaxPool1d"]
 TEST_NAME = {"Linear_16": "Linear16", "Linear_32": "Linear32", "Linear_64": "Linear64"}
 FLOAT_RE = re.compile(r"[-+]?(?:\d+\.?\d*|\.\d+)(?:[eE][-+]?\d+)?")
 

@@ -159,9 +159,15 @@ def run_fixture(name, manifest, arrays, backend):
             if one_d:
                 y = y[:, :, 0, :]
         elif op in ("MaxPool", "AveragePool"):
-            y = backend.pool(t[ins[0]], 0 if op == "MaxPool" else 1, tuple(a["kernel_shape"]),
-                             tuple(a.get("strides", [1, 1])), tuple(a.get("pads", [0, 0, 0, 0])),
-                             a.get("count_include_pad", 0))
+            X = t[ins[0]]
+            if X.ndim == 3:   # a 1-D pooling is the 2-D one with a height of 1
+                p1 = a.get("pads", [0, 0])
+                y = backend.pool(X[:, :, None, :], 0 if op == "MaxPool" else 1, (1, a["kernel_shape"][0]), (1, a.get("strides", [1])[0]),
+                                 (0, p1[0], 0, p1[1]), a.get("count_include_pad", 0))[:, :, 0, :]
+            else:
+                y = backend.pool(X, 0 if op == "MaxPool" else 1, tuple(a["kernel_shape"]),
+                                 tuple(a.get("strides", [1, 1])), tuple(a.get("pads", [0, 0, 0, 0])),
+                                 a.get("count_include_pad", 0))
         elif op == "Softmax":
             y = backend.softmax(t[ins[0]], a.get("axis", -1))
         elif op in UNARY_FIXTURE_OPS:
@@ -183,7 +189,7 @@ FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "Conv
                  "LinearWithSelu", "LinearWithSigmoid", "LinearWithLeakyRelu", "Add", "Sub", "Mul", "Div", "Neg", "Exp", "Log",
                  "Elu", "Tanh", "Sqrt", "Reciprocal",
                  "AddBroadcast1", "AddBroadcast2", "AddBroadcast3", "AddBroadcast4", "AddBroadcast5", "AddBroadcast7",
-                 "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched"]
+                 "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched", "MaxPool1d"]
 
 
 def fixture_to_onnx(name, manifest, arrays):
