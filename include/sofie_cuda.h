@@ -205,6 +205,19 @@ typedef struct sofie_conv_transpose2d_desc {
 int sofie_cuda_conv_transpose2d_f32(void *stream, const sofie_conv_transpose2d_desc *desc, const float *X, const float *W,
                                     const float *bias, float *Y);
 
+/* Einsum of two operands, general form (reference: ROperator_Einsum.hxx:200-332, nested loops or one sgemm_ per
+ * stack index): Y[out labels] = sum over all other labels of A[...] * B[...]. The labels are listed by extent, first
+ * the n_out output labels in output order, then the n_sum summed ones; a_stride / b_stride give the element stride
+ * of each label in A and B (0 when the operand does not carry it). Y is dense row-major over the output labels. */
+#define SOFIE_EINSUM_MAX_LABELS 8
+typedef struct sofie_einsum_desc {
+   int32_t n_out, n_sum;
+   int64_t extent[SOFIE_EINSUM_MAX_LABELS];
+   int64_t a_stride[SOFIE_EINSUM_MAX_LABELS];
+   int64_t b_stride[SOFIE_EINSUM_MAX_LABELS];
+} sofie_einsum_desc;
+int sofie_cuda_einsum_f32(void *stream, const sofie_einsum_desc *desc, const float *A, const float *B, float *Y);
+
 /* ------------------------------------------------------------------ fp32 memory-bound ops --- */
 /* y = x > 0 ? x : 0 (reference: ROperator_Relu.hxx:54-66). In place allowed. */
 int sofie_cuda_relu_f32(void *stream, const float *X, float *Y, size_t n);

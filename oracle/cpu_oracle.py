@@ -96,6 +96,17 @@ def conv_transpose2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1),
     return Y
 
 
+def einsum_f32(equation, A, B):
+    """Two-operand Einsum without ellipsis, e.g. "abc,abd->ad"."""
+    from sofie_b200.ops import einsum_plan
+    A, B = _f(A), _f(B)
+    out_shape, n_out, n_sum, extent, sa, sb = einsum_plan(equation, A.shape, B.shape)
+    Y = np.empty(out_shape, np.float32)
+    arr = lambda v: (C.c_longlong * 8)(*(list(v) + [0] * (8 - len(v))))
+    lib().oracle_einsum_f32(C.c_int(n_out), C.c_int(n_sum), arr(extent), arr(sa), arr(sb), _ptr(A), _ptr(B), _ptr(Y))
+    return Y
+
+
 def relu_f32(X):
     X = _f(X)
     Y = np.empty_like(X)

@@ -258,6 +258,40 @@ ORACLE_API void oracle_conv_transpose2d_f32(int N, int C, int H, int W, int Cout
    oracle_parallel_for(N, conv_transpose2d_images, &a);
 }
 
+/* Einsum of two operands, the general form the reference emits as nested loops over the output labels and then the
+ * summation labels (ROperator_Einsum.hxx:200-274; the matrix-product shapes it hands to sgemm_, :275-332, are the same
+ * sum): Y[out] = sum over the non-output labels of A[...] * B[...]. Labels are given by their extents (first the n_out
+ * output labels in output order, then the n_sum summed ones) and by the element stride each has in A and in B (0 when the
+ * operand does not carry the label). Double accumulator, rounded once. */
+ORACLE_API void oracle_einsum_f32(int n_out, int n_sum, const long long *extent, const long long *a_stride, const long long *b_stride,
+                                  const float *A, const float *B, float *Y)
+{
+   long long out_total = 1, sum_total = 1;
+   for (int i = 0; i < n_out; i++) out_total *= extent[i];
+   for (int i = 0; i < n_sum; i++) sum_total *= extent[n_out + i];
+   for (long long o = 0; o < out_total; o++) {
+      long long rem = o, a0 = 0, b0 = 0;
+      for (int i = n_out - 1; i >= 0; i--) {
+         const long long idx = rem % extent[i];
+         rem /= extent[i];
+         a0 += idx * a_stride[i];
+         b0 += idx * b_stride[i];
+      }
+      double acc = 0.0;
+      for (long long q = 0; q < sum_total; q++) {
+         long long r2 = q, a = a0, b = b0;
+         for (int i = n_sum - 1; i >= 0; i--) {
+            const long long idx = r2 % extent[n_out + i];
+            r2 /= extent[n_out + i];
+            a += idx * a_stride[n_out + i];
+            b += idx * b_stride[n_out + i];
+         }
+         acc += (double)A[a] * (double)B[b];
+      }
+      Y[o] = (float)acc;
+   }
+}
+
 /* ROperator_Relu.hxx:54-66 */
 ORACLE_API void oracle_relu_f32(const float *X, size_t n, float *Y)
 {

@@ -53,6 +53,10 @@ class ConvTranspose2dDesc(C.Structure):
                                    "out_pad_h", "out_pad_w", "relu")]
 
 
+class EinsumDesc(C.Structure):
+    _fields_ = [("n_out", i32), ("n_sum", i32), ("extent", C.c_int64 * 8), ("a_stride", C.c_int64 * 8), ("b_stride", C.c_int64 * 8)]
+
+
 class MlpDesc(C.Structure):
     _fields_ = [("M", i32), ("layers", i32), ("dims", i32 * 9), ("relu", i32 * 8), ("w_is_nk", i32 * 8)]
 
@@ -102,6 +106,7 @@ SIGNATURES = {
     "sofie_cuda_conv2d_f32": [vp, C.POINTER(Conv2dDesc), vp, vp, vp, vp],
     "sofie_cuda_conv2d_pack_f32": [vp, C.POINTER(Conv2dDesc), vp, vp],
     "sofie_cuda_conv_transpose2d_f32": [vp, C.POINTER(ConvTranspose2dDesc), vp, vp, vp, vp],
+    "sofie_cuda_einsum_f32": [vp, C.POINTER(EinsumDesc), vp, vp, vp],
     "sofie_cuda_relu_f32": [vp, vp, vp, sz],
     "sofie_cuda_pool2d_f32": [vp, C.POINTER(Pool2dDesc), vp, vp],
     "sofie_cuda_softmax_f32": [vp, vp, vp, sz, sz, sz],

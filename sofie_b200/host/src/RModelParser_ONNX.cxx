@@ -18,6 +18,7 @@
 #include "SOFIE/ROperator_Fp8.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
 #include "SOFIE/ROperator_ConvTranspose.hxx"
+#include "SOFIE/ROperator_Einsum.hxx"
 #include "SOFIE/ROperator_Pool.hxx"
 #include "SOFIE/ROperator_QLinear.hxx"
 #include "SOFIE/ROperator_Relu.hxx"
@@ -86,9 +87,12 @@ std::unique_ptr<ROperator> ParseEinsum(RModelParser_ONNX &p, const onnx::NodePro
 {
    std::string eq = attr_string(n, "equation", "");
    eq.erase(std::remove(eq.begin(), eq.end(), ' '), eq.end());
-   if (eq != "ik,kj->ij" || n.input_size() != 2)
-      throw std::runtime_error("SOFIE - Einsum " + eq + " is outside the dense-contraction path (only ik,kj->ij is generated)");
-   return ParseMatMul(p, n);
+   if (eq == "ik,kj->ij" && n.input_size() == 2) return ParseMatMul(p, n); // a plain matrix product: the GEMM kernels
+   if (n.input_size() != 2) throw std::runtime_error("SOFIE - Einsum with " + std::to_string(n.input_size()) + " operands is not generated for the CUDA path");
+   require_type(p, n.input(0), "Einsum");
+   if (p.GetTensorType(n.input(0)) != ETensorType::FLOAT) throw std::runtime_error("SOFIE - Unsupported - Operator Einsum does not yet support this input type");
+   p.RegisterTensorType(n.output(0), ETensorType::FLOAT);
+   return std::unique_ptr<ROperator>(new ROperator_Einsum<float>(eq, {n.input(0), n.input(1)}, n.output(0)));
 }
 
 std::unique_ptr<ROperator> ParseConv(RModelParser_ONNX &p, const onnx::NodeProto &n)

@@ -124,6 +124,46 @@ def conv_transpose2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1),
     return Y
 
 
+def einsum_plan(equation, shape_a, shape_b):
+    """Two-operand Einsum without ellipsis -> (output shape, n_out, n_sum, extents, strides in A, strides in B):
+    the output labels first, in output order, then every other label in order of first appearance."""
+    eq = equation.replace(" ", "")
+    lhs, out = eq.split("->") if "->" in eq else (eq, None)
+    la, lb = lhs.split(",")
+    if "." in eq or len(la) != len(shape_a) or len(lb) != len(shape_b):
+        raise ValueError(f"Einsum {equation}: two operands, one label per axis, no ellipsis")
+    if out is None:   # implicit form: the labels that appear once, sorted
+        out = "".join(sorted(c for c in set(la + lb) if (la + lb).count(c) == 1))
+    size = {}
+    for labels, shape in ((la, shape_a), (lb, shape_b)):
+        for c, n in zip(labels, shape):
+            if size.setdefault(c, int(n)) != int(n):
+                raise ValueError(f"Einsum {equation}: label {c} has two extents")
+    if len(set(la)) != len(la) or len(set(lb)) != len(lb) or len(set(out)) != len(out) or any(c not in size for c in out):
+        raise ValueError(f"Einsum {equation}: repeated labels within one operand are not supported")
+    summed = [c for c in dict.fromkeys(la + lb) if c not in out]
+    labels = list(out) + summed
+    if len(labels) > 8:
+        raise ValueError("Einsum: at most 8 labels")
+
+    def strides(lab, shape):
+        st, dense = {}, 1
+        for c, n in zip(reversed(lab), reversed(shape)):
+            st[c] = dense
+            dense *= int(n)
+        return [st.get(c, 0) for c in labels]
+    return tuple(size[c] for c in out), len(out), len(summed), [size[c] for c in labels], strides(la, shape_a), strides(lb, shape_b)
+
+
+def einsum_f32(equation, A, B):
+    out_shape, n_out, n_sum, extent, sa, sb = einsum_plan(equation, tuple(A.shape), tuple(B.shape))
+    Y = torch.empty(out_shape, dtype=torch.float32, device=A.device)
+    pad = lambda v: (C.c_int64 * 8)(*(list(v) + [0] * (8 - len(v))))
+    d = capi.EinsumDesc(n_out, n_sum, pad(extent), pad(sa), pad(sb))
+    capi.call("sofie_cuda_einsum_f32", _stream(), C.byref(d), _p(A), _p(B), _p(Y))
+    return Y
+
+
 def mlp_desc(M, dims, relu, w_is_nk):
     L = len(dims) - 1
     return capi.MlpDesc(M, L, (capi.i32 * 9)(*(list(dims) + [0] * (8 - L))), (capi.i32 * 8)(*([int(r) for r in relu] + [0] * (8 - L))),

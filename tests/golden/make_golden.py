@@ -30,7 +30,9 @@ CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutP
          "Tanh", "Sqrt", "Reciprocal",
          # broadcasting Add (rank <= 4) and transposed convolutions
          "AddBroadcast1", "AddBroadcast2", "AddBroadcast3", "AddBroadcast4", "AddBroadcast5", "AddBroadcast7",
-         "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched", "MaxPool1d"]
+         "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched", "MaxPool1d",
+         # general two-operand Einsum (expectations in the test bodies)
+         "Einsum_3", "Einsum_4", "Einsum_dotprod"]
 TEST_NAME = {"Linear_16": "Linear16", "Linear_32": "Linear32", "Linear_64": "Linear64"}
 FLOAT_RE = re.compile(r"[-+]?(?:\d+\.?\d*|\.\d+)(?:[eE][-+]?\d+)?")
 
@@ -79,8 +81,10 @@ def main():
         ins = test_inputs(block, [int(np.prod(s)) for _, s in graph_inputs])
         exp = expected_output(tdir / "input_models/references", name)
         if exp is None:  # Einsum_matmul keeps its expectation in the test body
-            exp = np.array([float(v) for v in FLOAT_RE.findall(re.search(r"correct_output\s*=\s*\{([^}]*)\}", block).group(1))],
-                           np.float32)
+            body = re.search(r"correct_output\s*=?\s*\{([^}]*)\}", block).group(1)
+            # items are literals or sums of literals ("5 + 12 + 21")
+            exp = np.array([sum(float(v) for v in FLOAT_RE.findall(item.replace(" ", "").replace("+", " "))) for item in body.split(",")
+                            if item.strip()], np.float32)
         entry = dict(inputs=[], nodes=[], tolerance=1e-3)
         for (iname, shape), arr in zip(graph_inputs, ins):
             arrays[f"{name}/in/{iname}"] = arr.reshape(shape)

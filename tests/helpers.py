@@ -45,6 +45,9 @@ class OracleBackend:
     def conv_transpose(self, X, W, B=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0)):
         return self.o.conv_transpose2d_f32(X, W, B, pad=pad, stride=stride, dil=dil, out_pad=out_pad)
 
+    def einsum(self, equation, A, B):
+        return self.o.einsum_f32(equation, A, B)
+
     def relu(self, X):
         return self.o.relu_f32(X)
 
@@ -82,6 +85,9 @@ class CudaBackend:
     def conv_transpose(self, X, W, B=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0)):
         return self.ops.conv_transpose2d_f32(self._d(X), self._d(W), self._d(B), pad=pad, stride=stride, dil=dil,
                                              out_pad=out_pad).cpu().numpy()
+
+    def einsum(self, equation, A, B):
+        return self.ops.einsum_f32(equation, self._d(A), self._d(B)).cpu().numpy()
 
     def relu(self, X):
         return self.ops.relu_f32(self._d(X)).cpu().numpy()
@@ -135,8 +141,10 @@ def run_fixture(name, manifest, arrays, backend):
             y = backend.gemm(t[ins[0]], t[ins[1]], t[ins[2]] if len(ins) > 2 else None, transA=a.get("transA", 0),
                              transB=a.get("transB", 0), alpha=a.get("alpha", 1.0), beta=a.get("beta", 1.0))
         elif op == "Einsum":
-            assert a["equation"] == "ik,kj->ij"
-            y = backend.gemm(t[ins[0]], t[ins[1]], None, beta=0.0)
+            if a["equation"].replace(" ", "") == "ik,kj->ij":
+                y = backend.gemm(t[ins[0]], t[ins[1]], None, beta=0.0)
+            else:
+                y = backend.einsum(a["equation"], t[ins[0]], t[ins[1]])
         elif op == "Relu":
             y = backend.relu(t[ins[0]])
         elif op == "Conv":
@@ -189,7 +197,8 @@ FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "Conv
                  "LinearWithSelu", "LinearWithSigmoid", "LinearWithLeakyRelu", "Add", "Sub", "Mul", "Div", "Neg", "Exp", "Log",
                  "Elu", "Tanh", "Sqrt", "Reciprocal",
                  "AddBroadcast1", "AddBroadcast2", "AddBroadcast3", "AddBroadcast4", "AddBroadcast5", "AddBroadcast7",
-                 "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched", "MaxPool1d"]
+                 "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched", "MaxPool1d",
+                 "Einsum_3", "Einsum_4", "Einsum_dotprod"]
 
 
 def fixture_to_onnx(name, manifest, arrays):

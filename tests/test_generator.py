@@ -199,3 +199,19 @@ def test_trailing_dequantize_is_written_by_the_last_quantised_product():
     text = _emit(m, "c3_b64").read_text()
     assert text.count("sofie_cuda_qlinear_matmul(") == 2 and text.count("sofie_cuda_qlinear_matmul_f32(") == 1
     assert "sofie_cuda_dequantize_u8(" not in text and not re.search(r"\bdev_q3\b", text)   # the uint8 tensor has no slice
+
+
+def test_einsum_goes_to_the_gemm_or_to_the_general_kernel_and_refuses_the_rest():
+    def graph(eq, sa, sb, n_in=2):
+        names = ["a", "b", "c"][:n_in]
+        shapes = [sa, sb, sb][:n_in]
+        return onnx_wire.model("g", [onnx_wire.node("Einsum", names, ["y"], [onnx_wire.attr_str("equation", eq)])],
+                               [onnx_wire.value_info(n, 1, list(s)) for n, s in zip(names, shapes)], [onnx_wire.value_info("y", 1, [])], [])
+    plain = generated.emit(graph("ik,kj->ij", (4, 5), (5, 6)), "einsum_mm").read_text()
+    assert "sofie_cuda_gemm_f32(" in plain and "sofie_cuda_einsum_f32(" not in plain
+    general = generated.emit(graph("bij, bjk -> bik", (3, 4, 5), (3, 5, 2)), "einsum_bmm").read_text()
+    assert "const sofie_einsum_desc d = {3, 1, {3, 4, 2, 5, 0, 0, 0, 0}, {20, 5, 0, 1, 0, 0, 0, 0}, {10, 0, 1, 2, 0, 0, 0, 0}};" in general
+    for eq, sa, sb, n_in, what in (("...ij,...jk->...ik", (3, 4, 5), (3, 5, 2), 2, "ellipsis"), ("ii,ij->j", (4, 4), (4, 3), 2, "repeated"),
+                                   ("ij,jk,kl->il", (2, 3), (3, 4), 3, "operands"), ("ij,kk->i", (2, 3), (3, 4), 2, "repeated|extents")):
+        with pytest.raises(RuntimeError, match=what):
+            generated.emit(graph(eq, sa, sb, n_in), "einsum_bad")

@@ -187,6 +187,19 @@ def test_conv_transpose2d_empty_batch_and_bad_arguments():
     assert e.value.status == capi.ERR_INVALID
 
 
+@pytest.mark.parametrize("eq,sa,sb", [("abc,abd->ad", (2, 2, 3), (2, 2, 3)), ("abcd,abed->abce", (2, 1, 2, 3), (2, 1, 3, 3)), ("i,i->", (3,), (3,)),
+                                      ("bij,bjk->bik", (5, 33, 17), (5, 17, 9)), ("ij,kj->ik", (40, 50), (60, 50)), ("ab,cd->acbd", (2, 3), (4, 5)),
+                                      ("bhqd,bhkd->bhqk", (2, 3, 16, 8), (2, 3, 12, 8)), ("ij,ij", (7, 9), (7, 9))])
+def test_einsum_f32(eq, sa, sb):
+    rng = np.random.default_rng(len(eq))
+    A, B = rng.standard_normal(sa).astype(np.float32), rng.standard_normal(sb).astype(np.float32)
+    ref = o.einsum_f32(eq, A, B)
+    y = ops.einsum_f32(eq, dev(A), dev(B)).cpu().numpy()
+    assert y.shape == ref.shape and rel_err(y, ref) <= FP32_TOL
+    full = eq if "->" in eq else eq + "->"
+    assert rel_err(ref, np.einsum(full, A.astype(np.float64), B.astype(np.float64)).astype(np.float32)) <= FP32_TOL
+
+
 def test_relu_nan_negzero_and_ragged_sizes():
     for n in (0, 1, 3, 4, 5, 1023, 4099):
         x = np.random.default_rng(n).standard_normal(n).astype(np.float32)
