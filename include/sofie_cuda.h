@@ -96,8 +96,35 @@ int sofie_cuda_ctx_fetch(sofie_cuda_ctx *ctx, const void *src_device, size_t byt
  * reads; the memory is zero-initialised and owned by the context. */
 int sofie_cuda_ctx_host_output(sofie_cuda_ctx *ctx, size_t bytes, void **dptr);
 int sofie_cuda_ctx_sync(sofie_cuda_ctx *ctx);
-/* Read and clear the device-side status word that kernels with bounded waits set on give-up. */
+/* Waits for the context's stream, then reads and clears the context's status word, which a kernel whose
+ * bounded wait ran out has set (SOFIE_CUDA_ERR_DEVICE; the kernel itself ended normally and the context
+ * stays usable). The word lies in mapped pinned host memory and belongs to this context alone.
+ * sofie_cuda_ctx_fetch performs the same check after its own wait, so the emitted infer() never returns
+ * the output of a kernel that gave up (the reference has no counterpart: CPU code cannot time out). */
 int sofie_cuda_ctx_check(sofie_cuda_ctx *ctx);
+/* The same for launches made on streams that belong to no context (direct callers of the compute entry
+ * points): one word per device. Synchronises the whole device. */
+int sofie_cuda_device_check(int device);
+/* Self test of the bounded waits (no counterpart in the reference): launches one CTA that allocates
+ * tensor memory and waits on a barrier nothing arrives on, with a limit of `limit_cycles` SM clocks
+ * (at most 2e8, about 0.1 s) instead of the library's one second. The kernel gives up, records status
+ * 0x1ff with detail 0x7e57 in the status word of the stream's context, releases its tensor memory and,
+ * when `reached_exit_device` is not NULL, stores 1 there as its last action. Nothing faults or hangs;
+ * the following sofie_cuda_ctx_check / sofie_cuda_ctx_fetch reports SOFIE_CUDA_ERR_DEVICE once. */
+int sofie_cuda_selftest_wait_timeout(void *stream, int64_t limit_cycles, uint32_t *reached_exit_device);
+/* Per-operator device timers (no counterpart in the reference, whose only timing is the caller's clock).
+ * The emitted Launch() calls sofie_cuda_ctx_mark(ctx, i) before operator i and once more after the last
+ * one. With the timers off (the default) a mark does nothing; with them on -- the environment variable
+ * SOFIE_CUDA_TIMERS=1 when the context is created, or sofie_cuda_ctx_timers(ctx, 1) before the first
+ * inference -- every mark records a CUDA event on the context stream (as a node of the captured graph when
+ * a capture is running) and sofie_cuda_ctx_timers_read returns, after waiting for the stream, the
+ * milliseconds between consecutive marks of the last inference: one number per operator, in Launch() order.
+ * ms may be NULL to ask for the count only; *count is the number of intervals available. The event nodes
+ * serialise the kernels around them (no overlap of one kernel's prologue with the previous kernel's tail),
+ * so a timed Session is a little slower than an untimed one: use it to see where a step's time goes. */
+int sofie_cuda_ctx_timers(sofie_cuda_ctx *ctx, int on);
+int sofie_cuda_ctx_mark(sofie_cuda_ctx *ctx, int slot);
+int sofie_cuda_ctx_timers_read(sofie_cuda_ctx *ctx, float *ms, int n, int *count);
 /* Capture of the kernel sequence of one infer() into a CUDA graph: begin, run the launchers on
  * the context stream, end; then launch replays it. */
 int sofie_cuda_ctx_graph_begin(sofie_cuda_ctx *ctx);

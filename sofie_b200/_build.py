@@ -4,6 +4,7 @@ The library is the product's only compute back end; nothing here falls back to a
 """
 from __future__ import annotations
 
+import fcntl
 import hashlib
 import os
 import shutil
@@ -45,9 +46,24 @@ def _fingerprint() -> str:
 def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile every .cu under csrc/ into one shared library. Re-uses an up-to-date build."""
     fp = _fingerprint()
-    if not force and LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == fp:
+
+    def current():
+        return not force and LIB.exists() and STAMP.exists() and STAMP.read_text().strip() == fp
+    if current():
         return LIB
     LIBDIR.mkdir(parents=True, exist_ok=True)
+    # one builder at a time: the ranks of a multi-GPU job all arrive here; the first compiles, the rest wait
+    with open(LIBDIR / ".build.lock", "a+") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if current():
+                return LIB
+            return _compile_and_link(fp, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _compile_and_link(fp: str, verbose: bool) -> Path:
     objdir = LIBDIR / "obj"
     objdir.mkdir(exist_ok=True)
     nvcc = _nvcc()
@@ -66,10 +82,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src.name}:\n{out}")
-    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, "-o", str(LIB), "-lcudart"]
+    tmp = LIB.with_name(f".{LIB.name}.{os.getpid()}.tmp")
+    link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", *objs, "-o", str(tmp), "-lcudart"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
+        tmp.unlink(missing_ok=True)
         raise RuntimeError(f"link of {LIB.name} failed:\n{r.stdout}")
+    os.replace(tmp, LIB)
     STAMP.write_text(fp)
     return LIB
 

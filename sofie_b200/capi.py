@@ -91,6 +91,11 @@ SIGNATURES = {
     "sofie_cuda_ctx_fetch": [vp, vp, sz, C.POINTER(vp)],
     "sofie_cuda_ctx_sync": [vp],
     "sofie_cuda_ctx_check": [vp],
+    "sofie_cuda_device_check": [C.c_int],
+    "sofie_cuda_selftest_wait_timeout": [vp, C.c_int64, vp],
+    "sofie_cuda_ctx_timers": [vp, C.c_int],
+    "sofie_cuda_ctx_mark": [vp, C.c_int],
+    "sofie_cuda_ctx_timers_read": [vp, vp, C.c_int, C.POINTER(C.c_int)],
     "sofie_cuda_ctx_host_output": [vp, sz, C.POINTER(vp)],
     "sofie_cuda_ctx_h2d_part": [vp, vp, vp, sz, C.c_int],
     "sofie_cuda_ctx_wait_part": [vp, C.c_int],

@@ -17,10 +17,15 @@ int fail(int status, const char *fmt, ...);
 void set_last_engine(int engine);
 int forced_engine();
 
-// Device-side status word shared by all kernels that have bounded waits. A kernel that gives up
-// stores a non-zero code here and returns normally, so the context stays usable; the host reads
-// it with sofie_cuda_ctx_check().
-uint32_t *device_status_word(); // device pointer (per current device), nullptr on failure
+// Status word of the kernels that have bounded waits. A kernel that gives up stores a non-zero code
+// there and returns normally, so the context stays usable. A stream that belongs to a context reports
+// into that context's own word, which lies in mapped pinned host memory: sofie_cuda_ctx_fetch and
+// sofie_cuda_ctx_check read it with a plain host load after the stream synchronisation they do anyway,
+// and one Session never sees (or clears) another Session's failure. Launches on any other stream share
+// one word per device in device memory, read by sofie_cuda_device_check().
+uint32_t *device_status_word(cudaStream_t stream); // address the kernel writes to, nullptr on failure
+void register_stream_status(cudaStream_t stream, uint32_t *word);
+void unregister_stream_status(cudaStream_t stream);
 
 #define SOFIE_CUDA_TRY(expr)                                                                         \
    do {                                                                                              \

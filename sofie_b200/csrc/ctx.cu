@@ -44,15 +44,35 @@ bool pdl_enabled()
 }
 int forced_engine() { return g_forced_engine; }
 
-// One status word per device, allocated on first use with that device current.
+// Streams of contexts report into their context's word; every other stream into one word per device,
+// allocated on first use with that device current.
 static std::mutex g_status_mutex;
 static uint32_t *g_status_words[64] = {nullptr};
+static std::vector<std::pair<cudaStream_t, uint32_t *>> g_stream_status;
 
-uint32_t *device_status_word()
+void register_stream_status(cudaStream_t stream, uint32_t *word)
+{
+   std::lock_guard<std::mutex> lock(g_status_mutex);
+   g_stream_status.emplace_back(stream, word);
+}
+
+void unregister_stream_status(cudaStream_t stream)
+{
+   std::lock_guard<std::mutex> lock(g_status_mutex);
+   for (size_t i = 0; i < g_stream_status.size(); i++)
+      if (g_stream_status[i].first == stream) {
+         g_stream_status.erase(g_stream_status.begin() + i);
+         return;
+      }
+}
+
+uint32_t *device_status_word(cudaStream_t stream)
 {
    int dev = 0;
-   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
    std::lock_guard<std::mutex> lock(g_status_mutex);
+   for (auto &e : g_stream_status)
+      if (e.first == stream) return e.second;
+   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
    if (!g_status_words[dev]) {
       uint32_t *p = nullptr;
       if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
@@ -82,9 +102,29 @@ struct sofie_cuda_ctx {
    // pipelined input upload: parts of the input are copied on a stream of their own, one event per part
    cudaStream_t copy_stream = nullptr;
    cudaEvent_t part_event[SOFIE_CUDA_MAX_PARTS] = {};
+   // status word of this context's kernels (mapped pinned host memory, 256 bytes)
+   uint32_t *status = nullptr;
+   // per-operator device timers (off unless SOFIE_CUDA_TIMERS is set or sofie_cuda_ctx_timers says so)
+   bool timers_on = false;
+   std::vector<cudaEvent_t> marks;
+   std::vector<char> mark_seen;
 };
 
 using namespace sofie;
+
+// The context's status word, read after the stream has been synchronised: a plain host load.
+static int report_status(sofie_cuda_ctx *ctx)
+{
+   volatile uint32_t *w = ctx->status;
+   if (w && w[0]) {
+      const uint32_t code = w[0], d1 = w[1], d2 = w[2], d3 = w[3];
+      w[1] = w[2] = w[3] = 0;
+      w[0] = 0;
+      return fail(SOFIE_CUDA_ERR_DEVICE, "device status 0x%x (detail 0x%x 0x%x 0x%x)", code, d1, d2, d3);
+   }
+   return SOFIE_CUDA_OK;
+}
+
 
 namespace {
 struct DeviceGuard {
@@ -162,13 +202,27 @@ int sofie_cuda_ctx_create(sofie_cuda_ctx **out, int device, size_t arena_bytes)
       ctx->arena_bytes = (arena_bytes + 255) & ~size_t(255);
       err = cudaMalloc(&ctx->arena, ctx->arena_bytes);
    }
+   if (err == cudaSuccess) {
+      void *w = nullptr, *d = nullptr;
+      err = cudaHostAlloc(&w, 256, cudaHostAllocMapped);
+      if (err == cudaSuccess) {
+         std::memset(w, 0, 256);
+         err = cudaHostGetDevicePointer(&d, w, 0);
+         if (err == cudaSuccess && d != w) err = cudaErrorNotSupported; // needs unified addressing
+         ctx->status = static_cast<uint32_t *>(w);
+      }
+   }
    if (err != cudaSuccess) {
+      if (ctx->status) cudaFreeHost(ctx->status);
+      if (ctx->arena) cudaFree(ctx->arena);
       if (ctx->stream) cudaStreamDestroy(ctx->stream);
       delete ctx;
       cudaGetLastError();
       return fail(err == cudaErrorMemoryAllocation ? SOFIE_CUDA_ERR_NOMEM : SOFIE_CUDA_ERR_CUDA,
                   "context creation on device %d (arena %zu bytes): %s", device, arena_bytes, cudaGetErrorString(err));
    }
+   register_stream_status(ctx->stream, ctx->status);
+   if (const char *t = std::getenv("SOFIE_CUDA_TIMERS")) ctx->timers_on = std::atoi(t) != 0;
    *out = ctx;
    return SOFIE_CUDA_OK;
 }
@@ -177,7 +231,10 @@ int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx)
 {
    if (!ctx) return SOFIE_CUDA_OK;
    DeviceGuard guard(ctx->device);
+   // nothing of this context may still be running or copying when its memory goes away
    cudaStreamSynchronize(ctx->stream);
+   if (ctx->copy_stream) cudaStreamSynchronize(ctx->copy_stream);
+   unregister_stream_status(ctx->stream);
    if (ctx->graph_exec) cudaGraphExecDestroy(ctx->graph_exec);
    if (ctx->graph) cudaGraphDestroy(ctx->graph);
    for (void *p : ctx->owned) cudaFree(p);
@@ -186,10 +243,10 @@ int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx)
    if (ctx->staging) cudaFreeHost(ctx->staging);
    if (ctx->result) cudaFreeHost(ctx->result);
    splitk_scratch_release(ctx->device, ctx->stream);
-   if (ctx->copy_stream) {
-      cudaStreamSynchronize(ctx->copy_stream);
-      cudaStreamDestroy(ctx->copy_stream);
-   }
+   if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+   if (ctx->status) cudaFreeHost(ctx->status);
+   for (cudaEvent_t e : ctx->marks)
+      if (e) cudaEventDestroy(e);
    for (cudaEvent_t e : ctx->part_event)
       if (e) cudaEventDestroy(e);
    cudaStreamDestroy(ctx->stream);
@@ -273,6 +330,7 @@ static bool is_pinned(const void *p)
 int sofie_cuda_ctx_h2d(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t bytes)
 {
    SOFIE_REQUIRE(ctx && dst && src, "NULL argument");
+   SOFIE_REQUIRE(!ctx->capturing, "input copies are not part of the captured graph");
    DeviceGuard guard(ctx->device);
    if (is_pinned(src)) {
       SOFIE_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -327,6 +385,7 @@ int sofie_cuda_ctx_wait_part(sofie_cuda_ctx *ctx, int part)
 int sofie_cuda_ctx_d2h(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t bytes)
 {
    SOFIE_REQUIRE(ctx && dst && src, "NULL argument");
+   SOFIE_REQUIRE(!ctx->capturing, "result copies are not part of the captured graph");
    DeviceGuard guard(ctx->device);
    if (is_pinned(dst)) {
       SOFIE_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -373,6 +432,7 @@ int sofie_cuda_ctx_host_output(sofie_cuda_ctx *ctx, size_t bytes, void **dptr)
 int sofie_cuda_ctx_fetch(sofie_cuda_ctx *ctx, const void *src, size_t bytes, void **host)
 {
    SOFIE_REQUIRE(ctx && src && host, "NULL argument");
+   SOFIE_REQUIRE(!ctx->capturing, "result copies are not part of the captured graph");
    DeviceGuard guard(ctx->device);
    for (auto &h : ctx->host_outputs) {
       const char *s8 = static_cast<const char *>(src);
@@ -380,7 +440,7 @@ int sofie_cuda_ctx_fetch(sofie_cuda_ctx *ctx, const void *src, size_t bytes, voi
          // the kernels wrote the result into host memory themselves: wait for them, nothing to copy
          SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
          *host = const_cast<char *>(s8);
-         return SOFIE_CUDA_OK;
+         return report_status(ctx);
       }
    }
    if (bytes > ctx->result_bytes) {
@@ -393,7 +453,7 @@ int sofie_cuda_ctx_fetch(sofie_cuda_ctx *ctx, const void *src, size_t bytes, voi
    if (bytes) SOFIE_CUDA_TRY(cudaMemcpyAsync(ctx->result, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
    SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
    *host = ctx->result;
-   return SOFIE_CUDA_OK;
+   return report_status(ctx);
 }
 
 int sofie_cuda_ctx_sync(sofie_cuda_ctx *ctx)
@@ -407,11 +467,24 @@ int sofie_cuda_ctx_sync(sofie_cuda_ctx *ctx)
 int sofie_cuda_ctx_check(sofie_cuda_ctx *ctx)
 {
    SOFIE_REQUIRE(ctx, "NULL ctx");
+   SOFIE_REQUIRE(!ctx->capturing, "the stream cannot be synchronised during a graph capture");
    DeviceGuard guard(ctx->device);
-   uint32_t *word = device_status_word();
-   if (!word) return fail(SOFIE_CUDA_ERR_CUDA, "no device status word");
-   uint32_t host_word[4] = {0, 0, 0, 0};
    SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+   return report_status(ctx);
+}
+
+int sofie_cuda_device_check(int device)
+{
+   SOFIE_REQUIRE(device >= 0 && device < 64, "device index out of range");
+   uint32_t *word = nullptr;
+   {
+      std::lock_guard<std::mutex> lock(g_status_mutex);
+      word = g_status_words[device];
+   }
+   if (!word) return SOFIE_CUDA_OK; // no kernel with a bounded wait ran outside a context on this device
+   DeviceGuard guard(device);
+   uint32_t host_word[4] = {0, 0, 0, 0};
+   SOFIE_CUDA_TRY(cudaDeviceSynchronize());
    SOFIE_CUDA_TRY(cudaMemcpy(host_word, word, sizeof(host_word), cudaMemcpyDeviceToHost));
    if (host_word[0]) {
       SOFIE_CUDA_TRY(cudaMemset(word, 0, 256));
@@ -421,12 +494,56 @@ int sofie_cuda_ctx_check(sofie_cuda_ctx *ctx)
    return SOFIE_CUDA_OK;
 }
 
+int sofie_cuda_ctx_timers(sofie_cuda_ctx *ctx, int on)
+{
+   SOFIE_REQUIRE(ctx, "NULL ctx");
+   SOFIE_REQUIRE(!ctx->capturing && !ctx->graph_exec, "switch the timers before the first inference is captured");
+   ctx->timers_on = on != 0;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_mark(sofie_cuda_ctx *ctx, int slot)
+{
+   SOFIE_REQUIRE(ctx, "NULL ctx");
+   if (!ctx->timers_on) return SOFIE_CUDA_OK;
+   SOFIE_REQUIRE(slot >= 0 && slot < 4096, "timer slot out of range");
+   DeviceGuard guard(ctx->device);
+   if ((size_t)slot >= ctx->marks.size()) {
+      ctx->marks.resize(slot + 1, nullptr);
+      ctx->mark_seen.resize(slot + 1, 0);
+   }
+   if (!ctx->marks[slot]) SOFIE_CUDA_TRY(cudaEventCreate(&ctx->marks[slot]));
+   // inside a capture the record becomes a node of the graph that updates this very event on every replay
+   SOFIE_CUDA_TRY(cudaEventRecordWithFlags(ctx->marks[slot], ctx->stream, ctx->capturing ? cudaEventRecordExternal : cudaEventRecordDefault));
+   ctx->mark_seen[slot] = 1;
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_ctx_timers_read(sofie_cuda_ctx *ctx, float *ms, int n, int *count)
+{
+   SOFIE_REQUIRE(ctx && count, "NULL argument");
+   SOFIE_REQUIRE(!ctx->capturing, "the stream cannot be synchronised during a graph capture");
+   DeviceGuard guard(ctx->device);
+   SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+   // intervals between consecutive recorded marks, in slot order
+   int prev = -1, k = 0;
+   for (int i = 0; i < (int)ctx->marks.size(); i++) {
+      if (!ctx->mark_seen[i]) continue;
+      if (prev >= 0) {
+         if (ms && k < n) SOFIE_CUDA_TRY(cudaEventElapsedTime(&ms[k], ctx->marks[prev], ctx->marks[i]));
+         k++;
+      }
+      prev = i;
+   }
+   *count = k;
+   return SOFIE_CUDA_OK;
+}
+
 int sofie_cuda_ctx_graph_begin(sofie_cuda_ctx *ctx)
 {
    SOFIE_REQUIRE(ctx, "NULL ctx");
    SOFIE_REQUIRE(!ctx->capturing, "graph capture already in progress");
    DeviceGuard guard(ctx->device);
-   device_status_word(); // allocate outside of capture
    if (ctx->graph_exec) {
       cudaGraphExecDestroy(ctx->graph_exec);
       ctx->graph_exec = nullptr;

@@ -51,7 +51,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 // status word, raises the CTA's abort flag and returns false.
 constexpr long long kWaitLimitCycles = 2000000000LL;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          uint32_t *status, uint32_t code, uint32_t detail)
+                                          uint32_t *status, uint32_t code, uint32_t detail,
+                                          long long limit_cycles = kWaitLimitCycles)
 {
    if (mbar_try_wait(bar, parity)) return true;
    const long long start = clock64();
@@ -62,12 +63,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
       for (int spin = 0; spin < 16; spin++)
          if (mbar_try_wait(bar, parity)) return true;
       if (*abort_flag) return false;
-      if (clock64() - start > kWaitLimitCycles) {
+      if (clock64() - start > limit_cycles) {
          *abort_flag = 1;
-         if (status && atomicCAS(status, 0u, code) == 0u) {
-            status[1] = detail;
-            status[2] = blockIdx.x;
-            status[3] = blockIdx.y;
+         // The word may lie in mapped host memory, where a device atomic is not atomic for the host: plain
+         // volatile accesses, detail first, the code last. When several CTAs give up together any one of them
+         // may win; every one of them reports a real give-up.
+         volatile uint32_t *w = status;
+         if (w && w[0] == 0u) {
+            w[1] = detail;
+            w[2] = blockIdx.x;
+            w[3] = blockIdx.y;
+            __threadfence_system();
+            w[0] = code;
+            __threadfence_system();
          }
          return false;
       }

@@ -820,7 +820,7 @@ static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, c
    rc = make_tensor_map(&tmW, dt, 2, Wp, wdims, wstr, wbox, pl.cb);
    if (rc) return rc;
    const int smem = (int)(COPIES * pl.w_bytes + pl.stages * per_stage) + 1024;
-   uint32_t *status = device_status_word();
+   uint32_t *status = device_status_word(s);
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int grid = tg.num_tiles < kNumSMs ? tg.num_tiles : kNumSMs;
    auto kern = umma_conv3x3_patch_kernel<KIND, BN, KPS, G>;
@@ -875,7 +875,7 @@ static int launch_conv_tps(cudaStream_t s, const CUtensorMap &tmX, const CUtenso
    const int smem = stages * STAGE_BYTES + 1024;
    auto kern = umma_conv3x3_kernel<KIND, BN, CB, TPS>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-   uint32_t *status = device_status_word();
+   uint32_t *status = device_status_word(s);
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int grid = tg.num_tiles < kNumSMs ? tg.num_tiles : kNumSMs;
    SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8), smem, s, tmX, tmW, ep, tg, status));

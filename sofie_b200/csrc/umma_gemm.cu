@@ -688,7 +688,7 @@ static int launch_pair(cudaStream_t s, const CUtensorMap &tmA, const CUtensorMap
    const int smem = kPairStages * kPairStageBytes + 1024;
    auto kern = umma_gemm_pair_kernel<KIND>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-   uint32_t *status = device_status_word();
+   uint32_t *status = device_status_word(s);
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int tiles = ceil_div(N, kPairBN) * ceil_div(M, 2 * kBM);
    const int pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
@@ -715,7 +715,7 @@ static int launch_one(cudaStream_t s, const CUtensorMap &tmA, const CUtensorMap 
    const int smem = stages * L::kStageBytes + 1024;
    auto kern = umma_gemm_kernel<KIND, BN>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-   uint32_t *status = device_status_word();
+   uint32_t *status = device_status_word(s);
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int tiles = ceil_div(N, BN) * ceil_div(M, kBM);
    const int grid = tiles < kNumSMs ? tiles : kNumSMs;

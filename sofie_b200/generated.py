@@ -9,9 +9,14 @@ of the benchmark; nothing here computes anything itself.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
+import fcntl
 import hashlib
+import os
+import shutil
 import subprocess
+import tempfile
 from pathlib import Path
 
 import numpy as np
@@ -41,31 +46,93 @@ extern "C" long sofie_session_infer(void *s, {in_type} **xs, {out_type} *y, long
    }} catch (const std::exception &e) {{ set_err(err, errlen, e.what()); return -1; }}
 }}
 extern "C" void sofie_session_destroy(void *s) {{ delete static_cast<Session *>(s); }}
+extern "C" void *sofie_session_ctx(void *s) {{ return static_cast<Session *>(s)->fCtx; }}
+extern "C" int sofie_session_run_resident(void *s, char *err, int errlen) {{
+   try {{ static_cast<Session *>(s)->RunResident(); return 0; }} catch (const std::exception &e) {{ set_err(err, errlen, e.what()); return -1; }}
+}}
 """
 
 
+@contextlib.contextmanager
+def _locked(path: Path):
+    """Exclusive advisory lock on `path` (created on demand). Several processes of one job -- the ranks of a
+    multi-GPU run, test workers -- build the same generator, library and emitted Session; whoever holds the lock
+    builds, the others wait and find the finished files."""
+    path.parent.mkdir(parents=True, exist_ok=True)
+    with open(path, "a+") as fh:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(fh, fcntl.LOCK_UN)
+
+
+_generator_built = False
+
+
 def build_generator() -> Path:
-    """make the generator libraries (libSOFIE_core, libSOFIE_parsers) and the sofie_emit tool."""
-    r = subprocess.run(["make", "-C", str(HOST), f"OUT={LIBDIR}"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"building the SOFIE generator failed:\n{r.stdout}")
+    """make the generator libraries (libSOFIE_core, libSOFIE_parsers) and the sofie_emit tool (once per process,
+    one process at a time)."""
+    global _generator_built
+    if not _generator_built:
+        with _locked(LIBDIR / ".generator.lock"):
+            r = subprocess.run(["make", "-C", str(HOST), f"OUT={LIBDIR}"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"building the SOFIE generator failed:\n{r.stdout}")
+        _generator_built = True
     return LIBDIR / "sofie_emit"
 
 
-def emit(onnx_bytes: bytes, name: str, batch: int | None = None, workdir: Path | None = None, binary: bool = False,
-         pipelined: bool = False) -> Path:
-    """Parse -> Generate -> OutputGenerated. Returns the path of <name>.hxx (the .dat, or with binary=True the
-    .bin, lies next to it)."""
-    tool = build_generator()
-    work = Path(workdir) if workdir else WORK / (name + ("_bin_" if binary else "_") + ("pipe_" if pipelined else "") +
-                                                 hashlib.sha1(onnx_bytes).hexdigest()[:10])
+def _toolchain_fingerprint() -> str:
+    """Identifies everything an emitted Session depends on besides its ONNX bytes: the generator binaries, the
+    library sources and this file's trampoline text."""
+    h = hashlib.sha1()
+    for f in ("sofie_emit", "libSOFIE_core.so", "libSOFIE_parsers.so"):
+        h.update((LIBDIR / f).read_bytes())
+    h.update(_build._fingerprint().encode())
+    h.update(TRAMPOLINE.encode())
+    return h.hexdigest()
+
+
+def _run_emit(tool: Path, onnx_bytes: bytes, name: str, batch, binary: bool, pipelined, work: Path) -> Path:
     work.mkdir(parents=True, exist_ok=True)
     onnx_path, hxx = work / f"{name}.onnx", work / f"{name}.hxx"
     onnx_path.write_bytes(onnx_bytes)
-    cmd = [str(tool), str(onnx_path), str(hxx)] + ([str(batch)] if batch else []) + (["--binary"] if binary else []) + (["--pipelined-upload"] if pipelined else [])
+    cmd = [str(tool), str(onnx_path), str(hxx)] + ([str(batch)] if batch else []) + (["--binary"] if binary else []) + (["--pipelined-upload"] if pipelined is True else []) + (["--single-upload"] if pipelined is False else [])
     r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"sofie_emit failed: {r.stdout.strip()}")
+    return hxx
+
+
+def emit(onnx_bytes: bytes, name: str, batch: int | None = None, workdir: Path | None = None, binary: bool = False,
+         pipelined: bool | None = None) -> Path:
+    """Parse -> Generate -> OutputGenerated. Returns the path of <name>.hxx (the .dat, or with binary=True the
+    .bin, lies next to it). pipelined: None = the generator's size gate decides whether the input is uploaded in
+    parts, True = always (Options::kPipelinedUpload), False = never (Options::kSingleUpload).
+
+    Without `workdir` the files go to a cache directory keyed by the ONNX bytes, the options and the generator
+    build. The directory is filled under a temporary name and renamed into place, so a reader never sees a
+    half-written header or weight file, and an existing directory is reused as it is: concurrent processes that
+    ask for the same model (the ranks of a multi-GPU run) emit once."""
+    tool = build_generator()
+    if workdir:
+        return _run_emit(tool, onnx_bytes, name, batch, binary, pipelined, Path(workdir))
+    key = hashlib.sha1(onnx_bytes + f"|{name}|{batch}|{binary}|{pipelined}|{_toolchain_fingerprint()}".encode()).hexdigest()[:16]
+    final = WORK / f"{name}_{key}"
+    hxx = final / f"{name}.hxx"
+    if hxx.exists():
+        return hxx
+    with _locked(WORK / f".{name}_{key}.lock"):
+        if hxx.exists():
+            return hxx
+        tmp = Path(tempfile.mkdtemp(prefix=f".{name}_{key}.", dir=WORK))
+        try:
+            _run_emit(tool, onnx_bytes, name, batch, binary, pipelined, tmp)
+            os.replace(tmp, final)
+        except BaseException:
+            shutil.rmtree(tmp, ignore_errors=True)
+            raise
     return hxx
 
 
@@ -77,19 +144,29 @@ def count_inputs(hxx: Path) -> int:
 
 
 def compile_session(hxx: Path, name: str, in_type="float", out_type="float") -> Path:
-    """Compile the emitted header (plus the trampolines) and link it against libSOFIE_cuda."""
+    """Compile the emitted header (plus the trampolines) and link it against libSOFIE_cuda. The shared object is
+    written under a temporary name and renamed into place; an up-to-date one is reused."""
     lib = _build.build()
     so = hxx.with_suffix(".so")
-    if so.exists() and so.stat().st_mtime >= max(hxx.stat().st_mtime, lib.stat().st_mtime, Path(__file__).stat().st_mtime):
+
+    def fresh():
+        return so.exists() and so.stat().st_mtime >= max(hxx.stat().st_mtime, lib.stat().st_mtime)
+    if fresh():
         return so
-    src = hxx.with_name(hxx.stem + "_trampoline.cxx")
-    args = ", ".join(f"xs[{i}]" for i in range(count_inputs(hxx)))
-    src.write_text(TRAMPOLINE.format(header=hxx.name, name=name, in_type=in_type, out_type=out_type, args=args))
-    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I", str(ROOT / "include"), "-I", str(hxx.parent), str(src), "-o", str(so),
-           "-L", str(lib.parent), "-lSOFIE_cuda", f"-Wl,-rpath,{lib.parent}"]
-    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"compiling the emitted header failed:\n{r.stdout}")
+    with _locked(hxx.with_suffix(".lock")):
+        if fresh():
+            return so
+        src = hxx.with_name(hxx.stem + "_trampoline.cxx")
+        args = ", ".join(f"xs[{i}]" for i in range(count_inputs(hxx)))
+        src.write_text(TRAMPOLINE.format(header=hxx.name, name=name, in_type=in_type, out_type=out_type, args=args))
+        tmp = so.with_name(f".{so.name}.{os.getpid()}.tmp")
+        cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I", str(ROOT / "include"), "-I", str(hxx.parent), str(src), "-o", str(tmp),
+               "-L", str(lib.parent), "-lSOFIE_cuda", f"-Wl,-rpath,{lib.parent}"]
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            tmp.unlink(missing_ok=True)
+            raise RuntimeError(f"compiling the emitted header failed:\n{r.stdout}")
+        os.replace(tmp, so)
     return so
 
 
@@ -103,6 +180,9 @@ class GeneratedSession:
         self.lib.sofie_session_infer.restype = C.c_long
         self.lib.sofie_session_infer.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_long, C.c_char_p, C.c_int]
         self.lib.sofie_session_destroy.argtypes = [C.c_void_p]
+        self.lib.sofie_session_ctx.restype = C.c_void_p
+        self.lib.sofie_session_ctx.argtypes = [C.c_void_p]
+        self.lib.sofie_session_run_resident.argtypes = [C.c_void_p, C.c_char_p, C.c_int]
         self.err = C.create_string_buffer(1024)
         self.handle = self.lib.sofie_session_create(str(dat).encode(), self.err, 1024)
         if not self.handle:
@@ -126,6 +206,17 @@ class GeneratedSession:
         if n != self.out_elems:
             raise RuntimeError(f"infer failed ({n}): {self.err.value.decode()}")
 
+    @property
+    def ctx(self) -> int:
+        """The Session's sofie_cuda_ctx (its public member fCtx), for the ctx_* entry points of the C ABI."""
+        return self.lib.sofie_session_ctx(self.handle)
+
+    def run_resident(self) -> None:
+        """Session::RunResident(): the kernels of one inference on the inputs the last infer() left on the device;
+        enqueues only (no copies, no wait)."""
+        if self.lib.sofie_session_run_resident(self.handle, self.err, 1024) != 0:
+            raise RuntimeError(f"RunResident failed: {self.err.value.decode()}")
+
     def close(self):
         if self.handle:
             self.lib.sofie_session_destroy(self.handle)
@@ -139,7 +230,7 @@ class GeneratedSession:
 
 
 def session_from_model(model, name: str | None = None, batch: int | None = None, binary: bool = False,
-                       fp8_scales=None, pipelined: bool = False) -> GeneratedSession:
+                       fp8_scales=None, pipelined: bool | None = None) -> GeneratedSession:
     """configs.Model -> ONNX bytes -> generator -> compiled Session."""
     from . import onnx_wire
     name = name or model.name
@@ -153,4 +244,47 @@ def session_from_model(model, name: str | None = None, batch: int | None = None,
         out_elems = int(found.group(1))
     if out_elems is None:
         raise RuntimeError("cannot find the output size in the emitted header")
-    return GeneratedSession(so, hxx.with_suffix(".bin" if binary else ".dat"), out_elems)
+    sess = GeneratedSession(so, hxx.with_suffix(".bin" if binary else ".dat"), out_elems)
+    sess.hxx = hxx
+    return sess
+
+
+def launch_plan(hxx: Path) -> list[dict]:
+    """The operators of the emitted Launch() in execution order, read from the header text: for each the comment
+    line the generator wrote above it, the libSOFIE_cuda entry points it calls and the multiply-accumulate work
+    of its contraction descriptors (2 x M x N x K per product, 2 x N x oH x oW x Cout x C/g x kH x kW per convolution; 0 for
+    everything else). The intervals sofie_cuda_ctx_timers_read returns are in this order."""
+    import re
+    text = hxx.read_text()
+    body = text[text.index("void Launch() {"):]
+    body = body[:body.index("\n}\n")]
+    segs = re.split(r"\n\s*Check\(sofie_cuda_ctx_mark\(fCtx, \d+\), \"sofie_cuda_ctx_mark\"\);", "\n" + body)[1:]
+    plan = []
+    for seg in segs:
+        if not seg.strip():
+            continue
+        calls = re.findall(r"Check\((sofie_cuda_\w+)\(", seg)
+        if not calls:
+            continue
+        title = next((ln.strip(" /-") for ln in seg.splitlines() if ln.strip().startswith("//")), calls[0])
+        flops = 0
+        for kind, vals in re.findall(r"const (sofie_\w+_desc) \w+ = \{([^;]*)\};", seg):
+            nums = [float(v.rstrip("f")) for v in re.findall(r"-?\d+\.?\d*(?:e[-+]?\d+)?f?", vals)]
+            if kind in ("sofie_gemm_f32_desc", "sofie_qgemm_desc", "sofie_fp8_gemm_desc"):
+                flops += 2 * nums[0] * nums[1] * nums[2]
+            elif kind == "sofie_conv2d_desc":
+                n, c, h, w, co, kh, kw, ph, pw, sh, sw, dh, dw, grp = nums[:14]
+                oh = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
+                ow = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+                flops += 2 * n * oh * ow * co * (c / grp) * kh * kw
+            elif kind == "sofie_qconv2d_desc":
+                n, c, h, w, co, kh, kw, ph, pw, sh, sw = nums[:11]
+                oh = (h + 2 * ph - kh) // sh + 1
+                ow = (w + 2 * pw - kw) // sw + 1
+                flops += 2 * n * oh * ow * co * c * kh * kw
+            elif kind == "sofie_mlp_desc":
+                m, layers = int(nums[0]), int(nums[1])
+                dims = nums[2:3 + layers]
+                flops += 2 * m * sum(dims[i] * dims[i + 1] for i in range(layers))
+        plan.append(dict(title=title, calls=calls, flops=int(flops)))
+    return plan

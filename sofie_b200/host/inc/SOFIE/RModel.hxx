@@ -56,6 +56,7 @@ private:
    std::map<std::string, size_t> fArenaOffsets;      // tensors that own arena memory
    size_t fArenaBytes = 0;
    bool fForcePipelinedUpload = false;
+   bool fNeverPipelinedUpload = false;
    std::vector<std::string> fSessionMembers;         // data members of the emitted Session, in declaration order
    std::set<std::string> fDeviceWeights;             // initialised tensors the emitted code uploads
    struct DeviceBuffer {

@@ -24,6 +24,7 @@ enum class Options {
    kGNNComponent = 0x10,
    kBinaryWeightFile = 0x40,    // addition: weights in a raw little-endian side file <name>.bin read with one fread per tensor
    kPipelinedUpload = 0x80,     // addition: upload the input in parts under the first convolution whatever its size (default: from 32 MB)
+   kSingleUpload = 0x100,       // addition: never upload the input in parts (every operator is then part of Launch() and of the graph)
 };
 
 enum class WeightFileType { None, RootBinary, Text, Binary };

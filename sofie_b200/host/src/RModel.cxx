@@ -490,6 +490,7 @@ void RModel::Generate(std::underlying_type_t<Options> options, int batchSize, lo
       fWeightFile = WeightFileType::Binary;
    }
    fForcePipelinedUpload = has(Options::kPipelinedUpload);
+   fNeverPipelinedUpload = has(Options::kSingleUpload);
    Initialize(batchSize, verbose);
    std::string hgname;
    fGC.clear();
@@ -706,7 +707,7 @@ void RModel::GenerateInfer()
          break;
       }
    bool pipelined = false;
-   if (head < fOperators.size() && fInputTensorNames.size() == 1) {
+   if (head < fOperators.size() && fInputTensorNames.size() == 1 && !fNeverPipelinedUpload) {
       const std::string &in = fInputTensorNames[0];
       const auto &reads = fOperators[head]->GetOpInputTensors();
       size_t readers = 0;
@@ -727,11 +728,16 @@ void RModel::GenerateInfer()
    fGC += pipelined ? "// all other kernel launches of one inference, on the context stream\n"
                     : "// all kernel launches of one inference, on the context stream\n";
    fGC += "void Launch() {\n";
+   // a mark before every operator and one after the last: device timers when they are switched on, nothing otherwise
+   size_t lastMark = 0;
    for (size_t i = 0; i < fOperators.size(); i++) {
       if (fOperators[i]->IsFusedAway() || (pipelined && i == head)) continue;
       if (fVerbose) std::cout << "Generating code for operator .... " << i << std::endl;
+      fGC += "   Check(sofie_cuda_ctx_mark(fCtx, " + std::to_string(i) + "), \"sofie_cuda_ctx_mark\");\n";
       fGC += fOperators[i]->Generate(std::to_string(i));
+      lastMark = i + 1;
    }
+   fGC += "   Check(sofie_cuda_ctx_mark(fCtx, " + std::to_string(lastMark) + "), \"sofie_cuda_ctx_mark\");\n";
    fGC += "}\n\n";
 
    ETensorType t0 = GetTensorType(fOutputTensorNames[0]);
@@ -745,6 +751,27 @@ void RModel::GenerateInfer()
       for (size_t i = 0; i < nOut; i++) ret += "std::vector<" + ConvertTypeToString(GetTensorType(fOutputTensorNames[i])) + ">" + (i + 1 < nOut ? "," : "");
       ret += ">";
    }
+   // The kernels of one inference once the inputs are on the device (or, with the pipelined upload, while all but
+   // the first operator's share of them is): replay of the captured graph, or the first, capturing, pass.
+   fGC += "void Run() {\n";
+   fGC += "   if (fGraphReady) {\n";
+   fGC += "      Check(sofie_cuda_ctx_graph_launch(fCtx), \"sofie_cuda_ctx_graph_launch\");\n";
+   fGC += "   } else {\n";
+   fGC += "      Launch();\n";
+   fGC += "      if (fUseGraph) {\n";
+   fGC += "         Check(sofie_cuda_ctx_graph_begin(fCtx), \"sofie_cuda_ctx_graph_begin\");\n";
+   fGC += "         try { Launch(); } catch (...) { sofie_cuda_ctx_graph_end(fCtx); throw; }\n";
+   fGC += "         Check(sofie_cuda_ctx_graph_end(fCtx), \"sofie_cuda_ctx_graph_end\");\n";
+   fGC += "         fGraphReady = true;\n";
+   fGC += "      }\n";
+   fGC += "   }\n";
+   fGC += "}\n\n";
+   // Every kernel of one inference on the inputs of the previous infer() call, which are still on the device:
+   // no copy in either direction and no wait (for callers that time or pipeline the device work themselves).
+   fGC += "void RunResident() {\n";
+   if (pipelined) fGC += "   for (int part = 0; part < " + std::to_string(kUploadParts) + "; part++) LaunchHead(part);\n";
+   fGC += "   Run();\n";
+   fGC += "}\n\n";
    fGC += ret + " infer(" + GenerateInferSignature() + "){\n";
    if (pipelined) {
       const std::string &n = fInputTensorNames[0];
@@ -762,17 +789,7 @@ void RModel::GenerateInfer()
          fGC += "   Check(sofie_cuda_ctx_h2d(fCtx, " + EMIT::Dev(n) + ", tensor_" + n + ", " + ByteCount(GetTensorShape(n), GetTensorType(n)) +
                 "), \"sofie_cuda_ctx_h2d\");\n";
    }
-   fGC += "   if (fGraphReady) {\n";
-   fGC += "      Check(sofie_cuda_ctx_graph_launch(fCtx), \"sofie_cuda_ctx_graph_launch\");\n";
-   fGC += "   } else {\n";
-   fGC += "      Launch();\n";
-   fGC += "      if (fUseGraph) {\n";
-   fGC += "         Check(sofie_cuda_ctx_graph_begin(fCtx), \"sofie_cuda_ctx_graph_begin\");\n";
-   fGC += "         try { Launch(); } catch (...) { sofie_cuda_ctx_graph_end(fCtx); throw; }\n";
-   fGC += "         Check(sofie_cuda_ctx_graph_end(fCtx), \"sofie_cuda_ctx_graph_end\");\n";
-   fGC += "         fGraphReady = true;\n";
-   fGC += "      }\n";
-   fGC += "   }\n";
+   fGC += "   Run();\n";
    for (size_t i = 0; i < nOut; i++) {
       const std::string &o = fOutputTensorNames[i];
       std::string type = ConvertTypeToString(GetTensorType(o));

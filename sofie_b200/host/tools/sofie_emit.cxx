@@ -1,4 +1,4 @@
-// sofie_emit <model.onnx> <output.hxx> [batch] [--binary] [--pipelined-upload]
+// sofie_emit <model.onnx> <output.hxx> [batch] [--binary] [--pipelined-upload | --single-upload]
 // The reference's usage pattern (src/SOFIE_core/README.md:26-57, test/EmitFromONNX.cxx.in:13-22):
 // Parse -> Generate -> OutputGenerated, which writes the header and, next to it, the weight file.
 #include <cstdlib>
@@ -10,7 +10,7 @@
 int main(int argc, char **argv)
 {
    if (argc < 3) {
-      std::cerr << "usage: " << argv[0] << " <model.onnx> <output.hxx> [batch size for parametric inputs] [--binary] [--pipelined-upload]\n";
+      std::cerr << "usage: " << argv[0] << " <model.onnx> <output.hxx> [batch size for parametric inputs] [--binary] [--pipelined-upload | --single-upload]\n";
       return 2;
    }
    try {
@@ -21,6 +21,7 @@ int main(int argc, char **argv)
       for (int i = 3; i < argc; i++) {
          if (std::string(argv[i]) == "--binary") options = options | SOFIE::Options::kBinaryWeightFile;
          else if (std::string(argv[i]) == "--pipelined-upload") options = options | SOFIE::Options::kPipelinedUpload;
+         else if (std::string(argv[i]) == "--single-upload") options = options | SOFIE::Options::kSingleUpload;
          else batch = std::atoi(argv[i]);
       }
       model.Generate(options, batch);

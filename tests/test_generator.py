@@ -215,3 +215,41 @@ def test_einsum_goes_to_the_gemm_or_to_the_general_kernel_and_refuses_the_rest()
                                    ("ij,jk,kl->il", (2, 3), (3, 4), 3, "operands"), ("ij,kk->i", (2, 3), (3, 4), 2, "repeated|extents")):
         with pytest.raises(RuntimeError, match=what):
             generated.emit(graph(eq, sa, sb, n_in), "einsum_bad")
+
+
+def _emit_and_compile_worker(tag, out):
+    # what every rank of a multi-GPU run does at start-up: same model, same name, at the same moment
+    import ctypes
+    try:
+        m, _ = configs.cnn_f32(batch=6)
+        hxx = generated.emit(onnx_wire.model_to_onnx(m), "race_c2_b6")
+        so = generated.compile_session(hxx, "race_c2_b6")
+        lib = ctypes.CDLL(str(so))
+        ok = all(hasattr(lib, f) for f in ("sofie_session_create", "sofie_session_infer", "sofie_session_destroy"))
+        dat = hxx.with_suffix(".dat").read_text().split()
+        out.put((tag, str(so), ok and dat[0] == "tensor_cb0" and len(dat) > 1000, ""))
+    except BaseException as e:  # reported to the parent instead of lost with the child
+        out.put((tag, "", False, f"{type(e).__name__}: {e}"))
+
+
+def test_eight_processes_emit_and_compile_the_same_model_at_once():
+    """The generated-Session cache is shared by the ranks of one job: nobody may read a header, weight file or
+    shared object that another process is still writing, and the model is emitted and compiled once."""
+    import multiprocessing as mp
+    import shutil
+    for old in generated.WORK.glob("race_c2_b6_*"):
+        shutil.rmtree(old)
+    generated.build_generator()
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_emit_and_compile_worker, args=(i, out)) for i in range(8)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert all(r[2] for r in results), results
+    assert len({r[1] for r in results}) == 1                      # one cache entry serves all eight
+    assert len(list(generated.WORK.glob("race_c2_b6_*"))) == 1    # and no temporary directory is left behind
+    assert not list(generated.WORK.glob(".race_c2_b6_*.*/"))
