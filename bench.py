@@ -427,7 +427,7 @@ def memory_bound_ops(ops, model, pk):
     out = []
     x_elems = int(np.prod(model.input_shape))
     for o in ops:
-        if o["flops"] == 0 and o["ms"] > 0 and o["calls"][0] in ("sofie_cuda_quantize_u8", "sofie_cuda_quantize_e4m3_f32"):
+        if o["flops"] == 0 and o["ms"] > 0 and o["calls"] and o["calls"][0] in ("sofie_cuda_quantize_u8", "sofie_cuda_quantize_e4m3_f32"):
             nbytes = x_elems * 5  # float in, one byte out
             out.append(dict(kernel=o["title"], bytes=nbytes, ms=o["ms"], gbs=nbytes / (o["ms"] * 1e-3) / 1e9,
                             frac=nbytes / (o["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"]))

@@ -93,12 +93,15 @@ __host__ __device__ constexpr T ceil_div(T a, T b)
 // evaluating nearbyintf((float)acc * mult) under the default rounding mode gets the same bits.
 __device__ __forceinline__ int requant_u8(int acc, float mult, int y_zp, int relu)
 {
-   // round-to-nearest-even conversion that saturates at the int range, then the clamp in integers:
-   // the same value as clamping the rounded float first, in fewer instructions
-   int q = __float2int_rn(__fmul_rn(__int2float_rn(acc), mult));
-   q = min(max(q, 0 - y_zp), 255 - y_zp) + y_zp;
-   if (relu && q < y_zp) q = y_zp;
-   return q;
+   // The clamp runs on the float product, the rounding after it: clamp(rne(v), lo, hi) == rne(clamp(v, lo, hi)) for
+   // integer bounds because rounding is monotone. A clamped value lies in [-255, 255], where adding 1.5 * 2^23
+   // rounds it to the nearest integer, ties to even, in the adder (full rate) and leaves that integer in the low
+   // mantissa bits; the float-to-int conversion instruction this replaces runs at a fraction of that rate.
+   // Relu on a quantised value, max(q, y_zp), is the lower bound 0 before the zero point is added.
+   const float lo = relu ? 0.f : (float)(-y_zp), hi = (float)(255 - y_zp);
+   float v = __fmul_rn(__int2float_rn(acc), mult);
+   v = fminf(fmaxf(v, lo), hi);
+   return __float_as_int(__fadd_rn(v, 12582912.f)) - 0x4B400000 + y_zp;
 }
 
 __device__ __forceinline__ float relu_ref(float v)

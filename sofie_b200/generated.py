@@ -258,15 +258,12 @@ def launch_plan(hxx: Path) -> list[dict]:
     text = hxx.read_text()
     body = text[text.index("void Launch() {"):]
     body = body[:body.index("\n}\n")]
-    segs = re.split(r"\n\s*Check\(sofie_cuda_ctx_mark\(fCtx, \d+\), \"sofie_cuda_ctx_mark\"\);", "\n" + body)[1:]
+    # one segment per mark; the text behind the last mark is the end of the function
+    segs = re.split(r"\n\s*Check\(sofie_cuda_ctx_mark\(fCtx, \d+\), \"sofie_cuda_ctx_mark\"\);", "\n" + body)[1:-1]
     plan = []
     for seg in segs:
-        if not seg.strip():
-            continue
-        calls = re.findall(r"Check\((sofie_cuda_\w+)\(", seg)
-        if not calls:
-            continue
-        title = next((ln.strip(" /-") for ln in seg.splitlines() if ln.strip().startswith("//")), calls[0])
+        calls = re.findall(r"Check\((sofie_cuda_\w+)\(", seg)   # none for an operator that is an alias (Flatten, Reshape)
+        title = next((ln.strip(" /-") for ln in seg.splitlines() if ln.strip().startswith("//")), calls[0] if calls else "alias")
         flops = 0
         for kind, vals in re.findall(r"const (sofie_\w+_desc) \w+ = \{([^;]*)\};", seg):
             nums = [float(v.rstrip("f")) for v in re.findall(r"-?\d+\.?\d*(?:e[-+]?\d+)?f?", vals)]

@@ -99,13 +99,13 @@ def test_operator_timers_and_run_resident_of_the_emitted_session(cuda_device, mo
     timed = generated.session_from_model(m, "c2_b32_timers")
     monkeypatch.delenv("SOFIE_CUDA_TIMERS")
     plan = generated.launch_plan(timed.hxx)
-    assert [p["calls"][0] for p in plan] == ["sofie_cuda_conv2d_f32"] * 3 + ["sofie_cuda_gemm_f32"]
+    assert [p["calls"] for p in plan] == [["sofie_cuda_conv2d_f32"]] * 3 + [[], ["sofie_cuda_gemm_f32"]]   # Flatten is an alias
     assert sum(p["flops"] for p in plan) == m.flops_per_sample * 32
     ms = (C.c_float * len(plan))()
     for _ in range(3):                                      # eager pass, capturing pass, graph replay
         y = timed.infer(x)
         capi.call("sofie_cuda_ctx_timers_read", timed.ctx, ms, len(plan), C.byref(n))
-        assert n.value == len(plan) and all(0.0 < t < 50.0 for t in ms)
+        assert n.value == len(plan) and all(0.0 <= t < 50.0 for t in ms)
         assert np.array_equal(y, y0)
     assert np.abs(y0 - ref).max() <= 1e-5 * np.abs(ref).max()
     # RunResident: the kernels again on the input the last infer() left on the device, no copies
