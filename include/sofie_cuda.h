@@ -322,7 +322,11 @@ enum {
    SOFIE_UNARY_LOG = 7,
    SOFIE_UNARY_SQRT = 8,
    SOFIE_UNARY_RECIPROCAL = 9,
-   SOFIE_UNARY_ABS = 10
+   SOFIE_UNARY_ABS = 10,
+   SOFIE_UNARY_ERF = 11,   /* std::erf(x)              (ROperator_Erf.hxx:58)   */
+   SOFIE_UNARY_SWISH = 12, /* x / (1 + exp(-x))        (ROperator_Swish.hxx:59) */
+   SOFIE_UNARY_COS = 13,   /* ROperator_BasicUnary.hxx */
+   SOFIE_UNARY_SIN = 14
 };
 int sofie_cuda_unary_f32(void *stream, int32_t op, float alpha, const float *X, float *Y, size_t n);
 

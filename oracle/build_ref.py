@@ -161,9 +161,17 @@ def scipy_openblas() -> Path:
     return Path(libs[0])
 
 
-def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
-    if not ref.exists():
+def reference_dir(argv=None) -> Path:
+    """Where the reference checkout lies: the command line, else the environment variable SOFIE_REFERENCE_DIR, else a
+    directory `reference` next to this repository."""
+    if argv and len(argv) > 1:
+        return Path(argv[1])
+    return Path(os.environ.get("SOFIE_REFERENCE_DIR", HERE.parent.parent / "reference"))
+
+
+def main(argv=None):
+    ref = reference_dir(argv)
+    if not (ref / "src/SOFIE_core/src/RModel.cxx").exists():
         print(f"{ref} absent: keeping the prebuilt files in {REF_OUT}")
         return 0
     subprocess.run(["make", "-C", str(HERE), f"REFERENCE={ref}", "_ref/ref_emit"], check=True)
@@ -191,4 +199,4 @@ def main():
 
 
 if __name__ == "__main__":
-    sys.exit(main())
+    sys.exit(main(sys.argv))

@@ -128,7 +128,7 @@ def pool2d_f32(X, mode=0, kernel=(2, 2), stride=(2, 2), pads=(0, 0, 0, 0), count
 
 
 UNARY_OPS = {"Sigmoid": 0, "Tanh": 1, "LeakyRelu": 2, "Selu": 3, "Elu": 4, "Neg": 5, "Exp": 6, "Log": 7, "Sqrt": 8,
-             "Reciprocal": 9, "Abs": 10}
+             "Reciprocal": 9, "Abs": 10, "Erf": 11, "Swish": 12, "Cos": 13, "Sin": 14}
 BINARY_OPS = {"Add": 0, "Sub": 1, "Mul": 2, "Div": 3}
 
 

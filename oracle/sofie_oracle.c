@@ -362,7 +362,8 @@ ORACLE_API void oracle_softmax_f32(size_t outer, size_t axis_len, size_t inner, 
 /* Unary operators with the expressions of the emitted code (ROperator_Sigmoid.hxx:59,
  * ROperator_Tanh.hxx:60, ROperator_LeakyRelu.hxx:73, ROperator_Selu.hxx:59 -- double constants --,
  * ROperator_Elu.hxx:71 -- `alpha * exp(x) - 1` as written there --, ROperator_BasicUnary.hxx).
- * op: 0 Sigmoid, 1 Tanh, 2 LeakyRelu, 3 Selu, 4 Elu, 5 Neg, 6 Exp, 7 Log, 8 Sqrt, 9 Reciprocal, 10 Abs. */
+ * op: 0 Sigmoid, 1 Tanh, 2 LeakyRelu, 3 Selu, 4 Elu, 5 Neg, 6 Exp, 7 Log, 8 Sqrt, 9 Reciprocal, 10 Abs,
+ * 11 Erf (ROperator_Erf.hxx:58), 12 Swish (ROperator_Swish.hxx:59), 13 Cos, 14 Sin. */
 ORACLE_API void oracle_unary_f32(int op, float alpha, const float *X, float *Y, size_t n)
 {
    for (size_t i = 0; i < n; i++) {
@@ -384,6 +385,10 @@ ORACLE_API void oracle_unary_f32(int op, float alpha, const float *X, float *Y, 
       case 7: y = logf(x); break;
       case 8: y = sqrtf(x); break;
       case 9: y = 1 / x; break;
+      case 11: y = erff(x); break;
+      case 12: y = x / (1 + expf(-x)); break;
+      case 13: y = cosf(x); break;
+      case 14: y = sinf(x); break;
       default: y = fabsf(x); break;
       }
       Y[i] = y;

@@ -33,6 +33,10 @@ __device__ __forceinline__ float unary_apply(int op, float x, float alpha)
    case SOFIE_UNARY_LOG: return logf(x);
    case SOFIE_UNARY_SQRT: return sqrtf(x);
    case SOFIE_UNARY_RECIPROCAL: return __fdiv_rn(1.f, x);
+   case SOFIE_UNARY_ERF: return erff(x);                                               // ROperator_Erf.hxx:58
+   case SOFIE_UNARY_SWISH: return __fdiv_rn(x, __fadd_rn(1.f, expf(-x)));              // ROperator_Swish.hxx:59
+   case SOFIE_UNARY_COS: return cosf(x);
+   case SOFIE_UNARY_SIN: return sinf(x);
    default: return fabsf(x); // SOFIE_UNARY_ABS
    }
 }
@@ -113,7 +117,7 @@ using namespace sofie;
 
 extern "C" int sofie_cuda_unary_f32(void *stream, int32_t op, float alpha, const float *X, float *Y, size_t n)
 {
-   SOFIE_REQUIRE(op >= SOFIE_UNARY_SIGMOID && op <= SOFIE_UNARY_ABS, "unknown unary operator %d", op);
+   SOFIE_REQUIRE(op >= SOFIE_UNARY_SIGMOID && op <= SOFIE_UNARY_SIN, "unknown unary operator %d", op);
    if (n == 0) return SOFIE_CUDA_OK;
    SOFIE_REQUIRE(X && Y, "NULL tensor");
    const bool vec = aligned16(X) && aligned16(Y);

@@ -140,7 +140,7 @@ def count_inputs(hxx: Path) -> int:
     """Number of tensors the emitted infer() takes (one pointer argument each)."""
     import re
     m = re.search(r"std::vector<float>\s+infer\(([^)]*)\)", hxx.read_text())
-    return max(1, m.group(1).count("tensor_")) if m else 1
+    return m.group(1).count("tensor_") if m else 1   # 0 for a graph made of constants only
 
 
 def compile_session(hxx: Path, name: str, in_type="float", out_type="float") -> Path:
@@ -192,7 +192,7 @@ class GeneratedSession:
     def infer(self, x, out: np.ndarray | None = None) -> np.ndarray:
         """x: one array, or a list of arrays for a model with several inputs (in the order of infer())."""
         xs = [np.ascontiguousarray(a) for a in (x if isinstance(x, (list, tuple)) else [x])]
-        ptrs = (C.c_void_p * len(xs))(*[a.ctypes.data_as(C.c_void_p) for a in xs])
+        ptrs = (C.c_void_p * max(1, len(xs)))(*[a.ctypes.data_as(C.c_void_p) for a in xs])
         y = out if out is not None else np.empty(self.out_elems, self.out_dtype)
         n = self.lib.sofie_session_infer(self.handle, ptrs, y.ctypes.data_as(C.c_void_p), self.out_elems, self.err, 1024)
         if n != self.out_elems:

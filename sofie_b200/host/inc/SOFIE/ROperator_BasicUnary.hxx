@@ -1,7 +1,7 @@
 // Elementwise unary operators: the activations the reference has one class each for
 // (ROperator_Sigmoid.hxx, ROperator_Tanh.hxx, ROperator_LeakyRelu.hxx, ROperator_Selu.hxx,
-// ROperator_Elu.hxx) and its ROperator_BasicUnary<T, Op> family (Reciprocal, Sqrt, Neg, Exp, Log,
-// Abs). Each emits one call of sofie_cuda_unary_f32; the formulas live in the library and follow
+// ROperator_Elu.hxx, ROperator_Erf.hxx, ROperator_Swish.hxx) and its ROperator_BasicUnary<T, Op> family
+// (Reciprocal, Sqrt, Neg, Exp, Log, Abs, Sin, Cos). Each emits one call of sofie_cuda_unary_f32; the formulas live in the library and follow
 // the loops the reference emits (cited there).
 #ifndef SOFIE_ROPERATOR_BASICUNARY
 #define SOFIE_ROPERATOR_BASICUNARY
@@ -14,7 +14,7 @@
 
 namespace SOFIE {
 
-enum class EBasicUnaryOperator { kReciprocal, kSqrt, kNeg, kExp, kLog, kAbs };
+enum class EBasicUnaryOperator { kReciprocal, kSqrt, kNeg, kExp, kLog, kAbs, kSin, kCos };
 
 // Common body; `code` is the SOFIE_UNARY_* value of include/sofie_cuda.h.
 class ROperator_UnaryDevice : public ROperator {
@@ -84,6 +84,18 @@ public:
    ROperator_Elu(float alpha, std::string nameX, std::string nameY) : ROperator_UnaryDevice("Elu", 4, alpha, nameX, nameY) {}
 };
 
+// std::erf(x) (reference: ROperator_Erf.hxx:58) and x / (1 + exp(-x)) (reference: ROperator_Swish.hxx:59)
+template <typename T>
+class ROperator_Erf final : public ROperator_UnaryDevice {
+public:
+   ROperator_Erf(std::string nameX, std::string nameY) : ROperator_UnaryDevice("Erf", 11, 0.f, nameX, nameY) {}
+};
+template <typename T>
+class ROperator_Swish final : public ROperator_UnaryDevice {
+public:
+   ROperator_Swish(std::string nameX, std::string nameY) : ROperator_UnaryDevice("Swish", 12, 0.f, nameX, nameY) {}
+};
+
 template <typename T, EBasicUnaryOperator Op>
 class ROperator_BasicUnary final : public ROperator_UnaryDevice {
    static int Code()
@@ -94,6 +106,8 @@ class ROperator_BasicUnary final : public ROperator_UnaryDevice {
       case EBasicUnaryOperator::kLog: return 7;
       case EBasicUnaryOperator::kSqrt: return 8;
       case EBasicUnaryOperator::kReciprocal: return 9;
+      case EBasicUnaryOperator::kCos: return 13;
+      case EBasicUnaryOperator::kSin: return 14;
       default: return 10;
       }
    }
@@ -105,6 +119,8 @@ class ROperator_BasicUnary final : public ROperator_UnaryDevice {
       case EBasicUnaryOperator::kLog: return "Log";
       case EBasicUnaryOperator::kSqrt: return "Sqrt";
       case EBasicUnaryOperator::kReciprocal: return "Reciprocal";
+      case EBasicUnaryOperator::kCos: return "Cos";
+      case EBasicUnaryOperator::kSin: return "Sin";
       default: return "Abs";
       }
    }

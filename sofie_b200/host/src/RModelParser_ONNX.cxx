@@ -17,6 +17,7 @@
 #include "SOFIE/ROperator_Conv.hxx"
 #include "SOFIE/ROperator_Fp8.hxx"
 #include "SOFIE/ROperator_Gemm.hxx"
+#include "SOFIE/ROperator_Identity.hxx"
 #include "SOFIE/ROperator_ConvTranspose.hxx"
 #include "SOFIE/ROperator_Einsum.hxx"
 #include "SOFIE/ROperator_Pool.hxx"
@@ -206,6 +207,28 @@ std::unique_ptr<ROperator> ParseBasicUnary(RModelParser_ONNX &p, const onnx::Nod
 {
    return ParseUnaryWith(p, n, [&] { return new ROperator_BasicUnary<float, Op>(n.input(0), n.output(0)); });
 }
+std::unique_ptr<ROperator> ParseErf(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   return ParseUnaryWith(p, n, [&] { return new ROperator_Erf<float>(n.input(0), n.output(0)); });
+}
+std::unique_ptr<ROperator> ParseSwish(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   return ParseUnaryWith(p, n, [&] { return new ROperator_Swish<float>(n.input(0), n.output(0)); });
+}
+// Identity of a run-time tensor (reference: ParseIdentity.cxx:7-35, float only there; any type here since nothing is
+// computed). An Identity of a constant is resolved in ParseONNXGraph and never gets here.
+std::unique_ptr<ROperator> ParseIdentity(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   require_type(p, n.input(0), n.op_type());
+   p.RegisterTensorType(n.output(0), p.GetTensorType(n.input(0)));
+   return std::unique_ptr<ROperator>(new ROperator_Identity<float>(n.input(0), n.output(0)));
+}
+// Constant nodes become initialised tensors in ParseONNXGraph (the reference keeps an operator that copies the values
+// into the output at Session construction, ParseConstant.cxx:9-175 / ROperator_Constant.hxx); nothing is left to emit.
+std::unique_ptr<ROperator> ParseConstant(RModelParser_ONNX &, const onnx::NodeProto &n)
+{
+   throw std::runtime_error("SOFIE - Constant node " + n.output(0) + " reached the operator stage");
+}
 template <EBasicBinaryOperator Op>
 std::unique_ptr<ROperator> ParseBasicBinary(RModelParser_ONNX &p, const onnx::NodeProto &n)
 {
@@ -342,6 +365,12 @@ RModelParser_ONNX::RModelParser_ONNX() noexcept : fOperatorsMapImpl(std::make_un
    RegisterOperator("Sqrt", ParseBasicUnary<EBasicUnaryOperator::kSqrt>);
    RegisterOperator("Reciprocal", ParseBasicUnary<EBasicUnaryOperator::kReciprocal>);
    RegisterOperator("Abs", ParseBasicUnary<EBasicUnaryOperator::kAbs>);
+   RegisterOperator("Cos", ParseBasicUnary<EBasicUnaryOperator::kCos>);
+   RegisterOperator("Sin", ParseBasicUnary<EBasicUnaryOperator::kSin>);
+   RegisterOperator("Erf", ParseErf);
+   RegisterOperator("Swish", ParseSwish);
+   RegisterOperator("Identity", ParseIdentity);
+   RegisterOperator("Constant", ParseConstant);
    RegisterOperator("Add", ParseBasicBinary<Add>);
    RegisterOperator("Sub", ParseBasicBinary<Sub>);
    RegisterOperator("Mul", ParseBasicBinary<Mul>);
@@ -493,8 +522,7 @@ void RModelParser_ONNX::ParseONNXGraph(RModel &rmodel, const onnx::GraphProto &g
 
    // ---- initialisers (the reference accepts FLOAT / DOUBLE / INT32 / INT64 only,
    //      RModelParser_ONNX.cxx:560-591; UINT8 and INT8 are needed by the quantised operators)
-   for (int i = 0; i < graph.initializer_size(); i++) {
-      const auto &t = graph.initializer(i);
+   auto add_constant = [&](const onnx::TensorProto &t, const std::string &name) {
       std::vector<size_t> shape;
       size_t length = 1;
       for (int j = 0; j < t.dims_size(); j++) {
@@ -503,7 +531,7 @@ void RModelParser_ONNX::ParseONNXGraph(RModel &rmodel, const onnx::GraphProto &g
       }
       if (t.dims_size() == 0) shape = {1}; // scalar
       ETensorType type = static_cast<ETensorType>(t.data_type());
-      RegisterTensorType(t.name(), type);
+      RegisterTensorType(name, type);
       std::shared_ptr<void> data;
       switch (type) {
       case ETensorType::FLOAT: data = tensor_data<float>(t, length); break;
@@ -513,9 +541,45 @@ void RModelParser_ONNX::ParseONNXGraph(RModel &rmodel, const onnx::GraphProto &g
       case ETensorType::UINT8: data = tensor_data<uint8_t>(t, length); break;
       case ETensorType::INT8: data = tensor_data<int8_t>(t, length); break;
       case ETensorType::FLOAT8E4M3FN: data = tensor_data<uint8_t>(t, length); break; // raw bit patterns
-      default: throw std::runtime_error("SOFIE Data type in weight tensor " + t.name() + " not supported!\n");
+      default: throw std::runtime_error("SOFIE Data type in weight tensor " + name + " not supported!\n");
       }
-      rmodel.AddInitializedTensor(t.name(), type, shape, data);
+      rmodel.AddInitializedTensor(name, type, shape, data);
+   };
+   for (int i = 0; i < graph.initializer_size(); i++) add_constant(graph.initializer(i), graph.initializer(i).name());
+
+   // ---- Constant nodes, and Identity nodes of constants, are initialised tensors under another spelling
+   //      (reference: ParseConstant.cxx:46-165 reads the same attributes; exporters write the shape of a Reshape
+   //      and shared weights this way). They produce no operator.
+   std::vector<bool> folded(graph.node_size(), false);
+   for (bool again = true; again;) {
+      again = false;
+      for (int i = 0; i < graph.node_size(); i++) {
+         const auto &node = graph.node(i);
+         if (folded[i] || node.output_size() != 1) continue;
+         const std::string &out = node.output(0);
+         if (node.op_type() == "Constant" && node.input_size() == 0) {
+            if (node.attribute_size() != 1) throw std::runtime_error("SOFIE ONNX Parser Constant needs exactly one attribute");
+            const auto &a = node.attribute(0);
+            onnx::TensorProto t;
+            if (a.name() == "value") t = a.t();
+            else if (a.name() == "value_float") { t.fDataType = onnx::TensorProto::FLOAT; t.fDims = {1}; t.fFloatData = {a.f()}; }
+            else if (a.name() == "value_floats") { t.fDataType = onnx::TensorProto::FLOAT; t.fDims = {(int64_t)a.fFloats.size()}; t.fFloatData = a.fFloats; }
+            else if (a.name() == "value_int") { t.fDataType = onnx::TensorProto::INT64; t.fDims = {1}; t.fInt64Data = {a.i()}; }
+            else if (a.name() == "value_ints") { t.fDataType = onnx::TensorProto::INT64; t.fDims = {(int64_t)a.fInts.size()}; t.fInt64Data = a.fInts; }
+            else throw std::runtime_error("SOFIE ONNX Parser Constant op: not yet supporting attribute " + a.name());
+            add_constant(t, out);
+         } else if (node.op_type() == "Identity" && node.input_size() == 1 && initializer_names.count(node.input(0))) {
+            const std::string src = UTILITY::Clean_name(node.input(0));
+            const auto &t = rmodel.GetInitializedTensor(src);
+            RegisterTensorType(out, t.type());
+            rmodel.AddInitializedTensor(out, t.type(), t.shape(), t.sharedptr());
+         } else {
+            continue;
+         }
+         folded[i] = true;
+         initializer_names[out] = true;
+         again = true;
+      }
    }
 
    // ---- execution order: a node is ready when all its inputs exist
@@ -523,8 +587,9 @@ void RModelParser_ONNX::ParseONNXGraph(RModel &rmodel, const onnx::GraphProto &g
    for (auto &n : initializer_names) available[n.first] = true;
    for (int i = 0; i < graph.input_size(); i++) available[graph.input(i).name()] = true;
    std::vector<size_t> order;
-   std::vector<bool> placed(graph.node_size(), false);
-   while ((int)order.size() < graph.node_size()) {
+   std::vector<bool> placed = folded;
+   const size_t nLive = (size_t)std::count(folded.begin(), folded.end(), false);
+   while (order.size() < nLive) {
       bool progress = false;
       for (int i = 0; i < graph.node_size(); i++) {
          if (placed[i]) continue;

@@ -70,6 +70,11 @@ def attr_ints(name, vs):
     return _s(1, name) + b"".join(_vi(8, int(v)) for v in vs) + _vi(20, 7)
 
 
+def attr_tensor(name, tensor_name, arr):
+    """AttributeProto of type TENSOR (field 5 = t, type 4), as a Constant node's `value`."""
+    return _s(1, name) + _ld(5, tensor(tensor_name, np.asarray(arr))) + _vi(20, 4)
+
+
 def attr_str(name, v):
     return _s(1, name) + _ld(4, v.encode()) + _vi(20, 3)
 

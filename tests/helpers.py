@@ -182,6 +182,10 @@ def run_fixture(name, manifest, arrays, backend):
             y = backend.unary(t[ins[0]], op, a.get("alpha", 0.01 if op == "LeakyRelu" else 1.0))
         elif op in ("Add", "Sub", "Mul", "Div"):
             y = backend.binary(t[ins[0]], t[ins[1]], op)
+        elif op == "Constant":
+            y = arrays[a["value"]["tensor"]]
+        elif op == "Identity":
+            y = t[ins[0]]
         else:
             raise NotImplementedError(op)
         t[n["outputs"][0]] = y
@@ -189,7 +193,7 @@ def run_fixture(name, manifest, arrays, backend):
     return np.asarray(out).ravel()
 
 
-UNARY_FIXTURE_OPS = ("Sigmoid", "Tanh", "LeakyRelu", "Selu", "Elu", "Neg", "Exp", "Log", "Sqrt", "Reciprocal", "Abs")
+UNARY_FIXTURE_OPS = ("Sigmoid", "Tanh", "LeakyRelu", "Selu", "Elu", "Neg", "Exp", "Log", "Sqrt", "Reciprocal", "Abs", "Erf", "Swish", "Cos", "Sin")
 
 FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutPadding",
                  "ConvWithAutopadSameLower", "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "AvgPool",
@@ -198,12 +202,20 @@ FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "Conv
                  "Elu", "Tanh", "Sqrt", "Reciprocal",
                  "AddBroadcast1", "AddBroadcast2", "AddBroadcast3", "AddBroadcast4", "AddBroadcast5", "AddBroadcast7",
                  "ConvTranspose1d", "ConvTranspose2d", "ConvTransposeBias2d", "ConvTransposeBias2dBatched", "MaxPool1d",
-                 "Einsum_3", "Einsum_4", "Einsum_dotprod"]
+                 "Einsum_3", "Einsum_4", "Einsum_dotprod", "Erf", "Abs", "Cos", "Sin", "Constant"]
+# fixtures the test-side ONNX writer can re-encode (it has no tensor-valued attributes)
+REENCODABLE_CASES = [n for n in FIXTURE_CASES if n != "Constant"]
+
+
+def fixture_onnx_bytes(name):
+    """The fixture model exactly as the reference's tests hold it (tests/golden/onnx/<name>.onnx, copied byte for byte by
+    tests/golden/make_golden.py): what the C++ parser is tested on."""
+    return (GOLDEN / "onnx" / f"{name}.onnx").read_bytes()
 
 
 def fixture_to_onnx(name, manifest, arrays):
-    """Re-serialise one golden fixture (nodes, attributes, weights, input shapes) as ONNX bytes, so the
-    C++ front end can parse the same graphs the reference's tests parse."""
+    """Re-serialise one golden fixture (nodes, attributes, weights, input shapes) as ONNX bytes with this repository's
+    own writer: a test of the writer (the parser itself is tested on the reference's bytes, fixture_onnx_bytes)."""
     from sofie_b200 import onnx_wire as ow
     entry = manifest[name]
     nodes = []

@@ -7,7 +7,7 @@ import re
 import numpy as np
 import pytest
 
-from helpers import FIXTURE_CASES, build_functor_program, fixture_to_onnx, load_fixtures, tiny_regressor
+from helpers import FIXTURE_CASES, REENCODABLE_CASES, build_functor_program, fixture_onnx_bytes, fixture_to_onnx, load_fixtures, tiny_regressor
 from sofie_b200 import configs, generated, onnx_wire
 
 
@@ -83,10 +83,38 @@ def test_configurations_emit_and_compile(key, kw):
 
 
 @pytest.mark.parametrize("name", FIXTURE_CASES)
-def test_reference_fixture_graphs_parse_and_emit(name):
+def test_reference_fixture_files_parse_and_emit(name):
+    """The reference's own .onnx files, byte for byte, through RModelParser_ONNX::Parse and Generate."""
+    hxx = generated.emit(fixture_onnx_bytes(name), name)
+    text = hxx.read_text()
+    assert "infer(" in text and f"namespace SOFIE_{name}" in text
+
+
+@pytest.mark.parametrize("name", REENCODABLE_CASES)
+def test_reencoded_fixture_graphs_emit_the_same_launches(name):
+    """The test-side ONNX writer against the reference's files: both spellings of a graph give the same calls."""
     manifest, arrays = load_fixtures()
-    hxx = generated.emit(fixture_to_onnx(name, manifest, arrays), name)
-    assert "infer(" in hxx.read_text()
+    calls = lambda hxx: re.findall(r"Check\((sofie_cuda_(?!ctx_)\w+)\(", hxx.read_text())
+    assert calls(generated.emit(fixture_to_onnx(name, manifest, arrays), name + "_rewritten")) == calls(generated.emit(fixture_onnx_bytes(name), name))
+
+
+def test_constant_and_identity_nodes_become_initialised_tensors():
+    w = np.arange(6, dtype=np.float32).reshape(3, 2)
+    shape = np.array([2, 3], np.int64)
+    g = onnx_wire.model("g", [onnx_wire.node("Constant", [], ["shape"], [onnx_wire.attr_tensor("value", "s", shape)]),
+                              onnx_wire.node("Identity", ["w"], ["w2"]),
+                              onnx_wire.node("MatMul", ["x", "w2"], ["h"]),
+                              onnx_wire.node("Identity", ["h"], ["h2"]),
+                              onnx_wire.node("Reshape", ["h2", "shape"], ["y"])],
+                        [onnx_wire.value_info("x", 1, [3, 3])], [onnx_wire.value_info("y", 1, [])], [onnx_wire.tensor("w", w)])
+    text = generated.emit(g, "const_ident").read_text()
+    # the shared weight is uploaded under its second name, the run-time Identity and the Reshape are aliases, one GEMM runs
+    assert text.count("sofie_cuda_gemm_f32(") == 1 and "Identity op_" in text and "Reshape op_" in text
+    assert "tensor_w2" in text.replace("dev_", "tensor_") and "tensor_shape" not in text
+    with pytest.raises(RuntimeError, match="not yet supporting attribute"):
+        generated.emit(onnx_wire.model("g", [onnx_wire.node("Constant", [], ["c"], [onnx_wire.attr_str("value_string", "a")]),
+                                             onnx_wire.node("Relu", ["x"], ["y"])],
+                                       [onnx_wire.value_info("x", 1, [2])], [onnx_wire.value_info("y", 1, [])], []), "const_bad")
 
 
 def test_unsupported_operator_and_bad_file_raise():

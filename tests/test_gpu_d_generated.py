@@ -4,7 +4,7 @@ the reference's own golden vectors, with the reference's own emitted CPU code an
 import numpy as np
 import pytest
 
-from helpers import FIXTURE_CASES, GOLDEN, fixture_to_onnx, load_fixtures, rel_err
+from helpers import FIXTURE_CASES, GOLDEN, fixture_onnx_bytes, load_fixtures, rel_err
 from oracle import build_ref, run_model
 from sofie_b200 import configs, generated, onnx_wire
 
@@ -12,10 +12,12 @@ pytestmark = pytest.mark.gpu
 REF = np.load(GOLDEN / "ref_outputs.npz")
 
 
-@pytest.mark.parametrize("name", [n for n in FIXTURE_CASES if n != "Einsum_matmul"])
+@pytest.mark.parametrize("name", FIXTURE_CASES)
 def test_reference_golden_vectors_through_generated_session(name, cuda_device):
+    """The reference's own .onnx file (byte for byte) -> Parse -> Generate -> g++ -> Session::infer against the expected
+    output the reference's test holds for it."""
     manifest, arrays = load_fixtures()
-    hxx = generated.emit(fixture_to_onnx(name, manifest, arrays), name)
+    hxx = generated.emit(fixture_onnx_bytes(name), name)
     exp = arrays[f"{name}/expected"]
     s = generated.GeneratedSession(generated.compile_session(hxx, name), hxx.with_suffix(".dat"), exp.size)
     xs = [arrays[f"{name}/in/{i}"] for i in manifest[name]["inputs"]]  # Add, Sub, Mul, Div take two graph inputs
