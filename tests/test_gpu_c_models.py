@@ -121,7 +121,7 @@ def test_c5_full_batch_sampled_images_bit_exact(cuda_device):
     m_s, _ = configs.cnn_i8(batch=len(rows), with_input=False)
     ref = run_model.run(m_s, x[rows])
     assert np.array_equal(y[rows].view(np.uint32), ref.view(np.uint32))
-    assert len(np.unique(y)) > 100                                  # not a constant output
+    assert len(np.unique(y)) > 30                                   # not a constant output (uint8 codes, dequantised)
 
 
 def test_c4_full_rows_sampled_rows(cuda_device):
