@@ -983,6 +983,9 @@ int launch_qconv2d_umma(cudaStream_t s, const ConvGeom &g, const uint8_t *X, con
                         const int32_t *bias, int x_zp, int y_zp, uint8_t *Y)
 {
    if (x_zp != 0) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "tensor-core quantised convolution needs an input zero point of 0");
+   // fused 2x2 pooling on large enough images: the kernel whose TMEM lanes are pooling windows
+   const int prc = launch_qconv2d_umma_pooled(s, g, X, W, mult, bias, x_zp, y_zp, Y);
+   if (prc >= 0) return prc;
    umma::ConvEpilogue ep = {};
    ep.mult = mult;
    ep.qbias = bias;

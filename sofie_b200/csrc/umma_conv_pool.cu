@@ -1,0 +1,333 @@
+// Quantised 3x3 convolution with the 2x2 MaxPool taken inside tensor memory (sm_100a, tcgen05).
+//
+// The general tensor-core convolution (umma_conv.cu) maps the 128 TMEM lanes of a tile to 128 output
+// pixels, so the four pixels of a pooling window sit in four lanes and its epilogue has to bring them
+// together with shuffles before it can requantise: for the small channel counts of a CNN's first
+// layers that epilogue, not the MMAs, sets the kernel's time. Here a tile is 32 x 16 output pixels of
+// one image = 16 x 8 pooling windows, the TMEM lanes are the 128 WINDOWS, and the four pixels of a
+// window are four accumulators side by side in the columns of the same lane:
+//     accumulator(position (dy,dx)) [window (py,px)] [channel]  =  conv output at (2py+dy, 2px+dx)
+// Each position is an implicit GEMM of its own (M = 128 windows, N = Cout, K = 9 taps x Cin) into its
+// own BN columns; a thread of the epilogue reads its lane's four accumulators and the pooling is three
+// integer max instructions per channel in registers, followed by one requantisation per POOLED value.
+// Consecutive MMAs go to different accumulators (tap-major, position-minor order), so none waits for
+// the accumulator of the one before it.
+//
+// Operand A without im2col: the haloed input patch of a tile (34 rows x 18 columns) is fetched once per
+// tile and channel plane (16 bytes of channels) as two TMA boxes, one with the patch's even columns and
+// one with its odd columns (the image is addressed as [N][H][W/2][2][C], so a column parity is a
+// coordinate, not a stride). In shared memory a box is [patch row][9 columns][16 bytes]; the eight
+// windows of one tile row and one column parity are then eight consecutive 16-byte rows = one core
+// matrix of the no-swizzle K-major layout, the next tile row of windows is two patch rows further
+// (the stride between 8-row groups), and the next 16 bytes of K are the next plane (the leading byte
+// offset). For tap (r,s) and position (dy,dx) the operand is therefore the SAME bytes read from the
+// start address  box((dx+s) & 1) + ((dy+r) * 9 + ((dx+s) >> 1)) * 16 : 36 addresses, no copies.
+// Taps outside the image are the TMA zero fill (the input zero point must be 0, as in umma_conv.cu).
+// All 9 x Cin x Cout weights stay in shared memory. No load uses cluster multicast.
+//
+// Roles (19 warps, one persistent CTA per SM): warp 0 TMA producer, warps 1 and 18 MMA issuers (tiles
+// taken alternately into the two halves of tensor memory), warps 2..17 epilogue (four per lane quarter,
+// 16 channels each). Every wait is bounded (umma::mbar_wait).
+#include "umma.cuh"
+#include "contract.cuh"
+#include <cstdlib>
+
+namespace sofie {
+namespace umma {
+
+namespace {
+
+constexpr int kPoolTileH = 32, kPoolTileW = 16;          // output pixels per tile (one image region)
+constexpr int kPoolRows = kPoolTileH + 2;                // patch rows including the halo
+constexpr int kPoolCols = 9;                             // columns of one parity in the patch
+constexpr int kPoolRowPitch = kPoolCols * 16;            // bytes between patch rows inside a box
+constexpr int kPoolBox = kPoolRows * kPoolRowPitch;      // bytes one box delivers (4896)
+constexpr int kPoolBoxStride = (kPoolBox + 127) / 128 * 128; // TMA destinations are 128-byte aligned (4992)
+constexpr int kPoolPlaneStride = 2 * kPoolBoxStride;     // the two parities of one plane
+constexpr int kPoolMaxStages = 4;
+constexpr int kPoolThreads = 19 * 32;
+constexpr int kPoolIssuerB = 18;
+constexpr int kPoolEpiWarps = 16;
+
+struct PoolConvParams {
+   int N, H, W, C, Cout;
+   int tilesH, tilesW, num_tiles;
+   int stages;
+   uint32_t w_bytes;      // all weights
+   uint32_t stage_bytes;  // one patch: planes x kPoolPlaneStride
+   const float *mult;
+   const int32_t *qbias;
+   int y_zp, relu;
+   uint8_t *Y;            // [N][H/2][W/2][Cout]
+};
+
+// BN = accumulator columns per position (32 or 64 >= Cout), KPS = MMAs (32 bytes of K) per tap = Cin / 32.
+template <int BN, int KPS>
+__global__ void __launch_bounds__(kPoolThreads, 1)
+umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, PoolConvParams p,
+                          uint32_t *status)
+{
+   constexpr int PLANES = 2 * KPS;
+   constexpr int CBK = KPS * 32 >= 128 ? 128 : KPS * 32;    // bytes of one weight row chunk (selects the swizzle)
+   constexpr int CHUNKS = KPS * 32 / CBK;
+   constexpr uint32_t B_TILE = BN * CBK;
+   constexpr uint32_t TMEM_COLS = 8 * BN;                   // two buffers of four accumulators
+   constexpr int PIECES = BN / 16;                          // 16-channel pieces of a lane's row
+   extern __shared__ unsigned char smem_raw[];
+   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+   __shared__ uint64_t full_bar[kPoolMaxStages], empty_bar[kPoolMaxStages], tmem_full[2], tmem_empty[2], w_full;
+   __shared__ uint32_t tmem_base_holder;
+   __shared__ volatile uint32_t abort_flag;
+   __shared__ float s_mult[64];
+   __shared__ int s_qbias[64];
+
+   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+   griddep_launch_dependents();
+   int negative_mult = 0;
+   for (int c = threadIdx.x; c < 64; c += blockDim.x) {
+      const bool in = c < p.Cout;
+      s_mult[c] = in ? p.mult[c] : 0.f;
+      s_qbias[c] = (in && p.qbias) ? p.qbias[c] : 0;
+      if (in && !(p.mult[c] >= 0.f)) negative_mult = 1;
+   }
+   const int S = p.stages;
+   unsigned char *w_smem = smem;
+   unsigned char *slots = smem + p.w_bytes;
+
+   if (threadIdx.x == 0) {
+      for (int s = 0; s < kPoolMaxStages; s++) {
+         mbar_init(&full_bar[s], 1);
+         mbar_init(&empty_bar[s], 1);
+      }
+      for (int b = 0; b < 2; b++) {
+         mbar_init(&tmem_full[b], 1);
+         mbar_init(&tmem_empty[b], kPoolEpiWarps);
+      }
+      mbar_init(&w_full, 1);
+      abort_flag = 0;
+      fence_mbar_init();
+      prefetch_tensormap(&tmX);
+      prefetch_tensormap(&tmW);
+   }
+   if (warp == 1) {
+      tmem_alloc(&tmem_base_holder, TMEM_COLS);
+      tmem_relinquish();
+   }
+   tc_fence_before();
+   // Pooling the raw sums first is exact when every later step is non-decreasing in the sum: all multipliers >= 0.
+   const bool pool_first = __syncthreads_or(negative_mult) == 0;
+   tc_fence_after();
+   const uint32_t tmem_base = tmem_base_holder;
+   const int per_image = p.tilesH * p.tilesW;
+
+   if (warp == 0) {
+      // ---------------- TMA producer ----------------
+      if (lane == 0) mbar_expect_tx(&w_full, p.w_bytes);
+      __syncwarp();
+      for (int item = lane; item < 9 * CHUNKS; item += 32) {
+         const int tap = item / CHUNKS, ch = item - tap * CHUNKS;
+         tma_load_2d(w_smem + (size_t)item * B_TILE, &tmW, tap * p.C + ch * CBK, 0, &w_full);
+      }
+      griddep_wait(); // the activations are the previous kernel's output
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x, g = 0; tile < p.num_tiles && ok; tile += gridDim.x, g++, ring_next(s, ph, S)) {
+         const int n = tile / per_image, rem = tile - n * per_image;
+         const int h0 = (rem / p.tilesW) * kPoolTileH, w0 = (rem % p.tilesW) * kPoolTileW;
+         if (lane == 0) {
+            ok = mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g);
+            if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)(2 * PLANES) * kPoolBox);
+         }
+         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+         if (!ok) break;
+         if (lane < 2 * PLANES) {
+            // box b = 0: patch columns w0-1, w0+1, ... (odd image columns, from pair w0/2 - 1);
+            // box b = 1: patch columns w0, w0+2, ...   (even image columns, from pair w0/2).
+            const int plane = lane >> 1, b = lane & 1;
+            asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+                         ::"r"(smem_u32(slots + (size_t)s * p.stage_bytes + (size_t)plane * kPoolPlaneStride + (size_t)b * kPoolBoxStride)),
+                         "l"(&tmX), "r"(plane * 16), "r"(b ? 0 : 1), "r"(b ? w0 / 2 : w0 / 2 - 1), "r"(h0 - 1), "r"(n),
+                         "r"(smem_u32(&full_bar[s]))
+                         : "memory");
+         }
+         __syncwarp();
+      }
+   } else if (warp == 1 || warp == kPoolIssuerB) {
+      // ---------------- MMA issuers: even tiles of this CTA -> buffer 0 (warp 1), odd tiles -> buffer 1 ----------------
+      const int issuer = warp == 1 ? 0 : 1;
+      if (lane == 0) {
+         constexpr uint32_t idesc = make_idesc<kI8>(128, BN);
+         bool ok = mbar_wait(&w_full, 0, &abort_flag, status, kStatusWaitFull, 0x4000);
+         tc_fence_after();
+         const uint64_t db0 = make_smem_desc(smem_u32(w_smem), CBK);
+         const uint32_t b_hi_word = (uint32_t)(db0 >> 32), b_lo_word = (uint32_t)db0;
+         int s = 0, lt = 0;
+         uint32_t ph = 0;
+         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, lt++, ring_next(s, ph, S)) {
+            const int buf = lt & 1;
+            // every slot's arrival is observed by both issuers: a parity wait only tells the last two phases apart
+            ok = mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, lt);
+            if (!ok) break;
+            if (buf != issuer) continue;
+            if (!mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt)) break;
+            tc_fence_after();
+            const uint32_t d = tmem_base + (uint32_t)(buf * 4 * BN);
+            const uint64_t da0 = make_smem_desc_noswizzle(smem_u32(slots + (size_t)s * p.stage_bytes), kPoolPlaneStride, 2 * kPoolRowPitch);
+            const uint32_t a_hi_word = (uint32_t)(da0 >> 32), a_lo_word = (uint32_t)da0;
+#pragma unroll
+            for (int tap = 0; tap < 9; tap++) {
+#pragma unroll
+               for (int kk = 0; kk < KPS; kk++) {
+                  const int kb = kk * 32;
+                  const uint32_t b16 = (uint32_t)((tap * CHUNKS + kb / CBK) * B_TILE + kb % CBK) >> 4;
+                  const uint64_t bdesc = ((uint64_t)b_hi_word << 32) | (uint64_t)(b_lo_word + b16);
+#pragma unroll
+                  for (int pos = 0; pos < 4; pos++) {
+                     const int row = (pos >> 1) + tap / 3, e = (pos & 1) + tap % 3;
+                     const uint32_t a16 = (uint32_t)((e & 1) * kPoolBoxStride + (row * kPoolCols + (e >> 1)) * 16 + kk * 2 * kPoolPlaneStride) >> 4;
+                     const uint64_t adesc = ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + a16);
+                     tc_mma<kI8>(d + (uint32_t)(pos * BN), adesc, bdesc, idesc, (tap | kk) ? 1u : 0u);
+                  }
+               }
+            }
+            tc_commit(&empty_bar[s]);
+            tc_commit(&tmem_full[buf]);
+         }
+      }
+   } else if (warp < 2 + kPoolEpiWarps) {
+      // ---------------- epilogue: lane = pooling window, four accumulators per lane ----------------
+      const int e = warp - 2;
+      const int lane_base = (warp & 3) * 32;
+      const int piece = e >> 2;                       // which 16 channels of the lane's row
+      const int win = lane_base + lane;
+      const int px = win & 7, py = win >> 3;
+      const int c0 = piece * 16;
+      const bool active = piece < PIECES && c0 < p.Cout;
+      const int oH = p.H / 2, oW = p.W / 2;
+      int lt = 0;
+      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, lt++) {
+         const int buf = lt & 1;
+         if (!mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt)) break;
+         tc_fence_after();
+         if (active) {
+            const int n = tile / per_image, rem = tile - n * per_image;
+            const int oh = (rem / p.tilesW) * (kPoolTileH / 2) + py, ow = (rem % p.tilesW) * (kPoolTileW / 2) + px;
+            const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * 4 * BN + c0);
+            int q[16];
+            if (pool_first) {
+               uint32_t a[16], b[16];
+               tmem_ld_32x16(t_row, a);
+               tmem_ld_32x16(t_row + BN, b);
+               tmem_ld_wait();
+#pragma unroll
+               for (int j = 0; j < 16; j++) a[j] = (uint32_t)max((int)a[j], (int)b[j]);
+               uint32_t c[16];
+               tmem_ld_32x16(t_row + 2 * BN, b);
+               tmem_ld_32x16(t_row + 3 * BN, c);
+               tmem_ld_wait();
+#pragma unroll
+               for (int j = 0; j < 16; j++) {
+                  const int m = max((int)a[j], max((int)b[j], (int)c[j]));
+                  q[j] = requant_u8(m + s_qbias[c0 + j], s_mult[c0 + j], p.y_zp, p.relu);
+               }
+            } else {
+               // a negative multiplier reverses the order: requantise the four pixels, then take the maximum
+#pragma unroll
+               for (int pos = 0; pos < 4; pos++) {
+                  uint32_t a[16];
+                  tmem_ld_32x16(t_row + pos * BN, a);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int j = 0; j < 16; j++) {
+                     const int v = requant_u8((int)a[j] + s_qbias[c0 + j], s_mult[c0 + j], p.y_zp, p.relu);
+                     q[j] = pos ? max(q[j], v) : v;
+                  }
+               }
+            }
+            uint32_t w4[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+               w4[j] = (uint32_t)q[4 * j] | ((uint32_t)q[4 * j + 1] << 8) | ((uint32_t)q[4 * j + 2] << 16) | ((uint32_t)q[4 * j + 3] << 24);
+            uint8_t *y = p.Y + (((size_t)n * oH + oh) * oW + ow) * p.Cout + c0;
+            *reinterpret_cast<uint4 *>(y) = make_uint4(w4[0], w4[1], w4[2], w4[3]);   // Cout % 16 == 0: aligned
+         }
+         tc_fence_before();
+         __syncwarp();
+         if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+      }
+   }
+   tc_fence_before();
+   __syncthreads();
+   if (warp == 1) {
+      __syncwarp();
+      tc_fence_after();
+      tmem_dealloc(tmem_base, TMEM_COLS);
+   }
+}
+
+template <int BN, int KPS>
+int launch_pool_conv(cudaStream_t s, const ConvGeom &g, const uint8_t *X, const int8_t *Wp, const float *mult, const int32_t *bias,
+                     int y_zp, uint8_t *Y)
+{
+   constexpr int CBK = KPS * 32 >= 128 ? 128 : KPS * 32;
+   constexpr int CHUNKS = KPS * 32 / CBK;
+   PoolConvParams p = {};
+   p.N = g.N; p.H = g.H; p.W = g.W; p.C = g.C; p.Cout = g.Cout;
+   p.tilesH = g.H / kPoolTileH;
+   p.tilesW = g.W / kPoolTileW;
+   p.num_tiles = g.N * p.tilesH * p.tilesW;
+   p.w_bytes = (uint32_t)(9 * CHUNKS * BN * CBK);
+   p.stage_bytes = (uint32_t)(2 * KPS * kPoolPlaneStride);
+   p.stages = (int)((200 * 1024 - (long)p.w_bytes) / (long)p.stage_bytes);
+   if (p.stages > kPoolMaxStages) p.stages = kPoolMaxStages;
+   if (p.stages < 2) return -1;
+   p.mult = mult; p.qbias = bias; p.y_zp = y_zp; p.relu = g.relu; p.Y = Y;
+   CUtensorMap tmX, tmW;
+   // the image as [N][H][W/2][2][C]: the parity of a column is a coordinate of its own
+   uint64_t xdims[5] = {(uint64_t)g.C, 2u, (uint64_t)g.W / 2, (uint64_t)g.H, (uint64_t)g.N};
+   uint64_t xstr[4] = {(uint64_t)g.C, (uint64_t)2 * g.C, (uint64_t)g.W * g.C, (uint64_t)g.H * g.W * g.C};
+   uint32_t xbox[5] = {16u, 1u, (uint32_t)kPoolCols, (uint32_t)kPoolRows, 1u};
+   int rc = make_tensor_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, X, xdims, xstr, xbox, 0);
+   if (rc) return rc;
+   uint64_t wdims[2] = {(uint64_t)9 * g.C, (uint64_t)g.Cout};
+   uint64_t wstr[1] = {(uint64_t)9 * g.C};
+   uint32_t wbox[2] = {(uint32_t)CBK, (uint32_t)BN};
+   rc = make_tensor_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, Wp, wdims, wstr, wbox, CBK);
+   if (rc) return rc;
+   const int smem = (int)(p.w_bytes + p.stages * p.stage_bytes) + 1024;
+   uint32_t *status = device_status_word(s);
+   if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
+   const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+   auto kern = umma_qconv3x3_pool_kernel<BN, KPS>;
+   SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kPoolThreads), smem, s, tmX, tmW, p, status));
+   SOFIE_LAUNCH_CHECK("umma_qconv3x3_pool_kernel");
+   set_last_engine(SOFIE_ENGINE_TCGEN05);
+   return SOFIE_CUDA_OK;
+}
+
+} // namespace
+} // namespace umma
+
+// Quantised 3x3 / stride 1 / pad 1 convolution with fused Relu and MaxPool 2x2 on the pooled-window kernel.
+// Returns -1 when the shape is not this kernel's (the caller then takes the general tensor-core kernel).
+int launch_qconv2d_umma_pooled(cudaStream_t s, const ConvGeom &g, const uint8_t *X, const int8_t *W, const float *mult,
+                               const int32_t *bias, int x_zp, int y_zp, uint8_t *Y)
+{
+   static const bool enabled = [] { const char *e = getenv("SOFIE_CUDA_CONV_POOLED"); return !e || atoi(e) != 0; }();
+   if (!enabled || x_zp != 0 || g.pool != 2) return -1;
+   if (!(g.kH == 3 && g.kW == 3 && g.pad_h == 1 && g.pad_w == 1 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 && g.group == 1)) return -1;
+   if (!g.x_nhwc || !g.y_nhwc || !g.w_packed) return -1;
+   if (g.H % umma::kPoolTileH != 0 || g.W % umma::kPoolTileW != 0) return -1;
+   if (g.Cout % 16 != 0 || g.Cout > 64) return -1;
+   if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(Y) & 15)) return -1;
+   const bool wide = g.Cout > 32;
+   switch (g.C) {
+   case 32: return wide ? umma::launch_pool_conv<64, 1>(s, g, X, W, mult, bias, y_zp, Y) : umma::launch_pool_conv<32, 1>(s, g, X, W, mult, bias, y_zp, Y);
+   case 64: return wide ? umma::launch_pool_conv<64, 2>(s, g, X, W, mult, bias, y_zp, Y) : umma::launch_pool_conv<32, 2>(s, g, X, W, mult, bias, y_zp, Y);
+   default: return -1;
+   }
+}
+
+} // namespace sofie

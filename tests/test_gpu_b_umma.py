@@ -158,7 +158,10 @@ def test_conv3x3_f32_tcgen05(case):
 
 @pytest.mark.parametrize("case", [(3, 32, 32, 32, 64, 1, 2), (7, 64, 16, 16, 64, 1, 2), (9, 64, 8, 8, 128, 1, 2), (2, 32, 16, 16, 40, 0, 0),
                                   (130, 32, 32, 32, 64, 1, 2), (3, 128, 16, 16, 128, 1, 2), (2, 256, 16, 16, 32, 0, 0),
-                                  (2, 128, 32, 16, 64, 1, 0), (5, 32, 16, 16, 24, 1, 2)])
+                                  (2, 128, 32, 16, 64, 1, 0), (5, 32, 16, 16, 24, 1, 2),
+                                  # pooled-window kernel (32 x 16 tiles, pooling in tensor memory): two K steps per tap, 32 and 48
+                                  # output channels, no Relu, several tiles per image in both directions, more tiles than SMs
+                                  (2, 64, 32, 32, 64, 1, 2), (2, 32, 64, 48, 32, 0, 2), (3, 64, 32, 16, 48, 1, 2), (40, 32, 64, 32, 16, 1, 2)])
 def test_qlinear_conv3x3_tcgen05_bit_exact(case):
     N, C, H, W, Cout, relu, pool = case
     rng = np.random.default_rng(sum(case))
@@ -178,7 +181,7 @@ def test_qlinear_conv3x3_tcgen05_bit_exact(case):
     assert len(np.unique(ref)) > 20
 
 
-@pytest.mark.parametrize("case", [(3, 32, 32, 32, 64), (2, 64, 16, 16, 64), (4, 1, 32, 32, 16), (2, 64, 8, 8, 128)])
+@pytest.mark.parametrize("case", [(3, 32, 32, 32, 64), (2, 64, 16, 16, 64), (4, 1, 32, 32, 16), (2, 64, 8, 8, 128), (2, 64, 32, 32, 32)])
 def test_qconv_pool_with_negative_multipliers(case):
     """A negative requantisation multiplier makes the requantisation decreasing in the accumulator, so the
     kernels must not pool the raw accumulators first; they detect it and pool the finished values."""
