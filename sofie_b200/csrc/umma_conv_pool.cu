@@ -25,9 +25,13 @@
 // Taps outside the image are the TMA zero fill (the input zero point must be 0, as in umma_conv.cu).
 // All 9 x Cin x Cout weights stay in shared memory. No load uses cluster multicast.
 //
-// Roles (19 warps, one persistent CTA per SM): warp 0 TMA producer, warps 1 and 18 MMA issuers (tiles
-// taken alternately into the two halves of tensor memory), warps 2..17 epilogue (four per lane quarter,
-// 16 channels each). Every wait is bounded (umma::mbar_wait).
+// Roles (21 warps, one persistent CTA per SM): warp 0 TMA producer; warps 1, 18, 19, 20 MMA issuers, one per
+// window position (an MMA of 64 columns occupies the tensor core for 48 clocks, its 6 KB of operands at 128
+// bytes per clock, but costs the thread that issues it 80 to 90: four threads issuing side by side keep
+// the pipe full, and all four work on the same tile, so a tile finishes as early as it can); warps 2..17
+// epilogue in two groups of eight that take the tiles alternately (group 0 drains TMEM buffer 0 while group 1
+// drains buffer 1: the latency of one tile's TMEM reads hides behind the other's arithmetic), two warps per
+// lane quarter, 32 channels each. Every wait is bounded (umma::mbar_wait).
 #include "umma.cuh"
 #include "contract.cuh"
 #include <cstdlib>
@@ -45,9 +49,40 @@ constexpr int kPoolBox = kPoolRows * kPoolRowPitch;      // bytes one box delive
 constexpr int kPoolBoxStride = (kPoolBox + 127) / 128 * 128; // TMA destinations are 128-byte aligned (4992)
 constexpr int kPoolPlaneStride = 2 * kPoolBoxStride;     // the two parities of one plane
 constexpr int kPoolMaxStages = 4;
-constexpr int kPoolThreads = 19 * 32;
-constexpr int kPoolIssuerB = 18;
-constexpr int kPoolEpiWarps = 16;
+constexpr int kPoolThreads = 21 * 32;
+constexpr int kPoolEpiWarps = 16;              // warps 2..17, two groups of eight
+constexpr int kPoolFirstExtraIssuer = 18;      // warps 18, 19, 20 issue positions 1, 2, 3 (warp 1 issues position 0)
+
+// Tiles start, start + step, ... of an (images x tile rows x tile columns) grid, walked with adds and compares only.
+struct PoolTileWalker {
+   int n, th, tw, dn, dth, dtw, tilesH, tilesW;
+   __device__ __forceinline__ void init(int start, int step, int tiles_h, int tiles_w)
+   {
+      tilesH = tiles_h;
+      tilesW = tiles_w;
+      const int per_image = tiles_h * tiles_w;
+      n = start / per_image;
+      th = (start % per_image) / tiles_w;
+      tw = start % tiles_w;
+      dn = step / per_image;
+      dth = (step % per_image) / tiles_w;
+      dtw = step % tiles_w;
+   }
+   __device__ __forceinline__ void next()
+   {
+      tw += dtw;
+      if (tw >= tilesW) {
+         tw -= tilesW;
+         th++;
+      }
+      th += dth;
+      if (th >= tilesH) {
+         th -= tilesH;
+         n++;
+      }
+      n += dn;
+   }
+};
 
 struct PoolConvParams {
    int N, H, W, C, Cout;
@@ -72,7 +107,6 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
    constexpr int CHUNKS = KPS * 32 / CBK;
    constexpr uint32_t B_TILE = BN * CBK;
    constexpr uint32_t TMEM_COLS = 8 * BN;                   // two buffers of four accumulators
-   constexpr int PIECES = BN / 16;                          // 16-channel pieces of a lane's row
    extern __shared__ unsigned char smem_raw[];
    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
    __shared__ uint64_t full_bar[kPoolMaxStages], empty_bar[kPoolMaxStages], tmem_full[2], tmem_empty[2], w_full;
@@ -97,11 +131,11 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
    if (threadIdx.x == 0) {
       for (int s = 0; s < kPoolMaxStages; s++) {
          mbar_init(&full_bar[s], 1);
-         mbar_init(&empty_bar[s], 1);
+         mbar_init(&empty_bar[s], 4);   // one commit per issuer
       }
       for (int b = 0; b < 2; b++) {
-         mbar_init(&tmem_full[b], 1);
-         mbar_init(&tmem_empty[b], kPoolEpiWarps);
+         mbar_init(&tmem_full[b], 4);   // one commit per issuer
+         mbar_init(&tmem_empty[b], kPoolEpiWarps / 2);
       }
       mbar_init(&w_full, 1);
       abort_flag = 0;
@@ -153,26 +187,31 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          }
          __syncwarp();
       }
-   } else if (warp == 1 || warp == kPoolIssuerB) {
-      // ---------------- MMA issuers: even tiles of this CTA -> buffer 0 (warp 1), odd tiles -> buffer 1 ----------------
-      const int issuer = warp == 1 ? 0 : 1;
+   } else if (warp == 1 || warp >= kPoolFirstExtraIssuer) {
+      // ---------------- MMA issuers: thread `pos` issues the nine taps of window position pos of every tile ----------------
+      const int pos = warp == 1 ? 0 : warp - kPoolFirstExtraIssuer + 1;
       if (lane == 0) {
          constexpr uint32_t idesc = make_idesc<kI8>(128, BN);
          bool ok = mbar_wait(&w_full, 0, &abort_flag, status, kStatusWaitFull, 0x4000);
          tc_fence_after();
          const uint64_t db0 = make_smem_desc(smem_u32(w_smem), CBK);
          const uint32_t b_hi_word = (uint32_t)(db0 >> 32), b_lo_word = (uint32_t)db0;
+         // start of this position's operand for tap (r,s), in 16-byte units: box (dx+s) & 1, patch row dy+r, column (dx+s) >> 1
+         uint32_t a_off[9];
+#pragma unroll
+         for (int tap = 0; tap < 9; tap++) {
+            const int row = (pos >> 1) + tap / 3, e = (pos & 1) + tap % 3;
+            a_off[tap] = (uint32_t)((e & 1) * kPoolBoxStride + (row * kPoolCols + (e >> 1)) * 16) >> 4;
+         }
          int s = 0, lt = 0;
          uint32_t ph = 0;
          for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, lt++, ring_next(s, ph, S)) {
             const int buf = lt & 1;
-            // every slot's arrival is observed by both issuers: a parity wait only tells the last two phases apart
             ok = mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, lt);
             if (!ok) break;
-            if (buf != issuer) continue;
             if (!mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt)) break;
             tc_fence_after();
-            const uint32_t d = tmem_base + (uint32_t)(buf * 4 * BN);
+            const uint32_t d = tmem_base + (uint32_t)(buf * 4 * BN + pos * BN);
             const uint64_t da0 = make_smem_desc_noswizzle(smem_u32(slots + (size_t)s * p.stage_bytes), kPoolPlaneStride, 2 * kPoolRowPitch);
             const uint32_t a_hi_word = (uint32_t)(da0 >> 32), a_lo_word = (uint32_t)da0;
 #pragma unroll
@@ -182,13 +221,8 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                   const int kb = kk * 32;
                   const uint32_t b16 = (uint32_t)((tap * CHUNKS + kb / CBK) * B_TILE + kb % CBK) >> 4;
                   const uint64_t bdesc = ((uint64_t)b_hi_word << 32) | (uint64_t)(b_lo_word + b16);
-#pragma unroll
-                  for (int pos = 0; pos < 4; pos++) {
-                     const int row = (pos >> 1) + tap / 3, e = (pos & 1) + tap % 3;
-                     const uint32_t a16 = (uint32_t)((e & 1) * kPoolBoxStride + (row * kPoolCols + (e >> 1)) * 16 + kk * 2 * kPoolPlaneStride) >> 4;
-                     const uint64_t adesc = ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + a16);
-                     tc_mma<kI8>(d + (uint32_t)(pos * BN), adesc, bdesc, idesc, (tap | kk) ? 1u : 0u);
-                  }
+                  const uint64_t adesc = ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + a_off[tap] + (uint32_t)((kk * 2 * kPoolPlaneStride) >> 4));
+                  tc_mma<kI8>(d, adesc, bdesc, idesc, (tap | kk) ? 1u : 0u);
                }
             }
             tc_commit(&empty_bar[s]);
@@ -198,21 +232,25 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
    } else if (warp < 2 + kPoolEpiWarps) {
       // ---------------- epilogue: lane = pooling window, four accumulators per lane ----------------
       const int e = warp - 2;
+      const int group = e >> 3;                       // which tiles (and TMEM buffer) this warp drains
+      const int half = (e >> 2) & 1;                  // which 32 channels of the lane's row
       const int lane_base = (warp & 3) * 32;
-      const int piece = e >> 2;                       // which 16 channels of the lane's row
       const int win = lane_base + lane;
       const int px = win & 7, py = win >> 3;
-      const int c0 = piece * 16;
-      const bool active = piece < PIECES && c0 < p.Cout;
       const int oH = p.H / 2, oW = p.W / 2;
-      int lt = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, lt++) {
-         const int buf = lt & 1;
+      PoolTileWalker tw;
+      tw.init(blockIdx.x + group * gridDim.x, 2 * gridDim.x, p.tilesH, p.tilesW);
+      int lt = group;
+      for (int tile = blockIdx.x + group * gridDim.x; tile < p.num_tiles; tile += 2 * gridDim.x, lt += 2, tw.next()) {
+         const int buf = group;
          if (!mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt)) break;
          tc_fence_after();
-         if (active) {
-            const int n = tile / per_image, rem = tile - n * per_image;
-            const int oh = (rem / p.tilesW) * (kPoolTileH / 2) + py, ow = (rem % p.tilesW) * (kPoolTileW / 2) + px;
+         const int oh = tw.th * (kPoolTileH / 2) + py, ow = tw.tw * (kPoolTileW / 2) + px;
+         uint8_t *yrow = p.Y + (((size_t)tw.n * oH + oh) * oW + ow) * p.Cout;
+#pragma unroll
+         for (int piece = 0; piece < 2; piece++) {
+            const int c0 = half * 32 + piece * 16;
+            if (c0 >= BN || c0 >= p.Cout) break;
             const uint32_t t_row = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * 4 * BN + c0);
             int q[16];
             if (pool_first) {
@@ -228,7 +266,7 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                tmem_ld_wait();
 #pragma unroll
                for (int j = 0; j < 16; j++) {
-                  const int m = max((int)a[j], max((int)b[j], (int)c[j]));
+                  const int m = __vimax3_s32((int)a[j], (int)b[j], (int)c[j]);
                   q[j] = requant_u8(m + s_qbias[c0 + j], s_mult[c0 + j], p.y_zp, p.relu);
                }
             } else {
@@ -249,8 +287,7 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 #pragma unroll
             for (int j = 0; j < 4; j++)
                w4[j] = (uint32_t)q[4 * j] | ((uint32_t)q[4 * j + 1] << 8) | ((uint32_t)q[4 * j + 2] << 16) | ((uint32_t)q[4 * j + 3] << 24);
-            uint8_t *y = p.Y + (((size_t)n * oH + oh) * oW + ow) * p.Cout + c0;
-            *reinterpret_cast<uint4 *>(y) = make_uint4(w4[0], w4[1], w4[2], w4[3]);   // Cout % 16 == 0: aligned
+            *reinterpret_cast<uint4 *>(yrow + c0) = make_uint4(w4[0], w4[1], w4[2], w4[3]);   // Cout % 16 == 0: aligned
          }
          tc_fence_before();
          __syncwarp();
