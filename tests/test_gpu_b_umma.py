@@ -181,6 +181,29 @@ def test_qlinear_conv3x3_tcgen05_bit_exact(case):
     assert len(np.unique(ref)) > 20
 
 
+@pytest.mark.parametrize("case", [(3, 64, 64, 32, 1, 0), (2, 32, 48, 16, 0, 7), (5, 96, 32, 64, 1, 0), (150, 64, 64, 32, 1, 3), (1, 32, 16, 48, 1, 200)])
+def test_qlinear_first_layer_pooled_tcgen05_bit_exact(case):
+    """One input channel, 3x3 / pad 1, Relu or not, MaxPool 2x2 fused: the tensor-core first-layer kernel (operand rows built
+    from the staged image rows, pooling in tensor memory) against the oracle, NCHW input as the Session hands it over."""
+    N, H, W, Cout, relu, y_zp = case
+    ops.set_engine(0)
+    rng = np.random.default_rng(sum(case))
+    X = (rng.integers(0, 256, (N, 1, H, W)) * (rng.random((N, 1, H, W)) < 0.3)).astype(np.uint8)
+    X[0, 0, 0, :] = 255
+    X[0, 0, :, -1] = 255                       # bright borders next to the padding
+    Wt = rng.integers(-127, 128, (Cout, 1, 3, 3)).astype(np.int8)
+    ws = rng.uniform(0.001, 0.01, Cout).astype(np.float32)
+    bias = rng.integers(-300, 300, Cout).astype(np.int32)
+    y_scale = 0.03 * 0.005 * 127 * 6
+    ref = o.maxpool2d_u8(o.qlinear_conv2d(X, 0.03, 0, Wt, ws, y_scale, y_zp, bias=bias, pad=(1, 1), relu=bool(relu)))
+    mult = dev(o.requant_multiplier(0.03, ws, y_scale))
+    y = ops.qlinear_conv2d(dev(X), dev(Wt), mult, dev(bias), shape=X.shape, pad=(1, 1), x_zp=0, y_zp=y_zp, relu=bool(relu), pool=2,
+                           x_layout=0, y_layout=1, w_packed=False)
+    assert ops.last_engine() == capi.ENGINE_TCGEN05
+    assert np.array_equal(y.cpu().numpy().transpose(0, 3, 1, 2), ref)
+    assert len(np.unique(ref)) > 20
+
+
 @pytest.mark.parametrize("case", [(3, 32, 32, 32, 64), (2, 64, 16, 16, 64), (4, 1, 32, 32, 16), (2, 64, 8, 8, 128), (2, 64, 32, 32, 32)])
 def test_qconv_pool_with_negative_multipliers(case):
     """A negative requantisation multiplier makes the requantisation decreasing in the accumulator, so the
