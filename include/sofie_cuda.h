@@ -165,6 +165,18 @@ int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *desc, const flo
                         const float *C, float *Y);
 
 /*
+ * A stack of `batch` independent products with the same descriptor: matrix b of A, B and Y starts b * strideA,
+ * b * strideB, b * strideY elements after the first (strideA or strideB = 0: that operand is shared by the whole stack);
+ * C, when given, is a per-column bias (bias_kind 1) shared by all. ONNX MatMul of operands with leading "stack"
+ * dimensions and Einsum equations of the form "...ik,...kj->...ij". The reference emits one sgemm_ per stack index
+ * for both (ROperator_Gemm.hxx:353-387 -- where only the output offset advances, so every index multiplies the first
+ * matrices again --, ROperator_Einsum.hxx:275-332); here every index has its own operands, as ONNX defines, and each
+ * product takes the same kernels as sofie_cuda_gemm_f32.
+ */
+int sofie_cuda_gemm_f32_batched(void *stream, const sofie_gemm_f32_desc *desc, const float *A, const float *B, const float *C,
+                                float *Y, int32_t batch, int64_t strideA, int64_t strideB, int64_t strideY);
+
+/*
  * Allocation-free skinny GEMM (no counterpart in the reference).
  *
  * Same arithmetic and descriptor as sofie_cuda_gemm_f32, restricted to the split-K shape class

@@ -106,6 +106,7 @@ SIGNATURES = {
     "sofie_cuda_last_engine": [],
     "sofie_cuda_set_engine": [C.c_int],
     "sofie_cuda_gemm_f32": [vp, C.POINTER(GemmF32Desc), vp, vp, vp, vp],
+    "sofie_cuda_gemm_f32_batched": [vp, C.POINTER(GemmF32Desc), vp, vp, vp, vp, i32, C.c_int64, C.c_int64, C.c_int64],
     "sofie_cuda_gemm_f32_splitk_static": [vp, C.POINTER(GemmF32Desc), vp, vp, vp, vp],
     "sofie_cuda_transpose_f32": [vp, vp, vp, i32, i32],
     "sofie_cuda_conv2d_f32": [vp, C.POINTER(Conv2dDesc), vp, vp, vp, vp],

@@ -67,6 +67,20 @@ int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *d, const float 
                    [&] { return launch_gemm_f32_simt(s, *d, A, B, C, Y); });
 }
 
+int sofie_cuda_gemm_f32_batched(void *stream, const sofie_gemm_f32_desc *d, const float *A, const float *B, const float *C, float *Y,
+                                int32_t batch, int64_t strideA, int64_t strideB, int64_t strideY)
+{
+   SOFIE_REQUIRE(d != nullptr && batch >= 0, "NULL descriptor or negative batch");
+   SOFIE_REQUIRE(strideA >= 0 && strideB >= 0 && strideY > 0, "bad strides");
+   SOFIE_REQUIRE(d->bias_kind != 2, "a stacked product takes a bias per column only");
+   for (int32_t b = 0; b < batch; b++) {
+      // every matrix of the stack goes through the same dispatch as a single product: tensor cores where the shape allows
+      const int rc = sofie_cuda_gemm_f32(stream, d, A + (size_t)b * strideA, B + (size_t)b * strideB, C, Y + (size_t)b * strideY);
+      if (rc) return rc;
+   }
+   return SOFIE_CUDA_OK;
+}
+
 int sofie_cuda_conv2d_f32(void *stream, const sofie_conv2d_desc *d, const float *X, const float *W, const float *bias,
                           float *Y)
 {

@@ -91,7 +91,37 @@ def _toolchain_fingerprint() -> str:
         h.update((LIBDIR / f).read_bytes())
     h.update(_build._fingerprint().encode())
     h.update(TRAMPOLINE.encode())
+    h.update(TRAMPOLINE_DYN.encode())
     return h.hexdigest()
+
+
+# A Session generated with a run-time batch parameter: Session(file, size_t bs) / infer(size_t bs, float*).
+TRAMPOLINE_DYN = r"""
+#include "{header}"
+#include <cstring>
+#include <string>
+using Session = SOFIE_{name}::Session;
+static void set_err(char *err, int n, const char *msg) {{ if (err && n > 0) {{ std::strncpy(err, msg, n - 1); err[n - 1] = 0; }} }}
+extern "C" void *sofie_session_create_bs(const char *dat, long max_batch, char *err, int errlen) {{
+   try {{ return new Session(dat, (size_t)max_batch); }} catch (const std::exception &e) {{ set_err(err, errlen, e.what()); return nullptr; }}
+}}
+extern "C" long sofie_session_infer_bs(void *s, long bs, {in_type} **xs, {out_type} *y, long ny, char *err, int errlen) {{
+   try {{
+      auto out = static_cast<Session *>(s)->infer((size_t)bs, {args});
+      if ((long)out.size() > ny) {{ set_err(err, errlen, "output buffer too small"); return -(long)out.size(); }}
+      std::memcpy(y, out.data(), out.size() * sizeof({out_type}));
+      return (long)out.size();
+   }} catch (const std::exception &e) {{ set_err(err, errlen, e.what()); return -1; }}
+}}
+extern "C" void sofie_session_destroy(void *s) {{ delete static_cast<Session *>(s); }}
+extern "C" void *sofie_session_ctx(void *s) {{ return static_cast<Session *>(s)->fCtx; }}
+"""
+
+
+def is_dynamic(hxx: Path) -> bool:
+    """True when the emitted infer() takes the batch as its first argument."""
+    import re
+    return re.search(r"std::vector<float>\s+infer\(size_t \w+,", hxx.read_text()) is not None
 
 
 def _run_emit(tool: Path, onnx_bytes: bytes, name: str, batch, binary: bool, pipelined, work: Path) -> Path:
@@ -158,7 +188,8 @@ def compile_session(hxx: Path, name: str, in_type="float", out_type="float") -> 
             return so
         src = hxx.with_name(hxx.stem + "_trampoline.cxx")
         args = ", ".join(f"xs[{i}]" for i in range(count_inputs(hxx)))
-        src.write_text(TRAMPOLINE.format(header=hxx.name, name=name, in_type=in_type, out_type=out_type, args=args))
+        template = TRAMPOLINE_DYN if is_dynamic(hxx) else TRAMPOLINE
+        src.write_text(template.format(header=hxx.name, name=name, in_type=in_type, out_type=out_type, args=args))
         tmp = so.with_name(f".{so.name}.{os.getpid()}.tmp")
         cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I", str(ROOT / "include"), "-I", str(hxx.parent), str(src), "-o", str(tmp),
                "-L", str(lib.parent), "-lSOFIE_cuda", f"-Wl,-rpath,{lib.parent}"]
@@ -168,6 +199,69 @@ def compile_session(hxx: Path, name: str, in_type="float", out_type="float") -> 
             raise RuntimeError(f"compiling the emitted header failed:\n{r.stdout}")
         os.replace(tmp, so)
     return so
+
+
+class DynamicSession:
+    """An emitted Session with a run-time batch: built for `max_batch` samples, infer() takes any batch up to it."""
+
+    def __init__(self, so: Path, dat: Path, max_batch: int, out_per_sample: int):
+        self.lib = C.CDLL(str(so))
+        self.lib.sofie_session_create_bs.restype = C.c_void_p
+        self.lib.sofie_session_create_bs.argtypes = [C.c_char_p, C.c_long, C.c_char_p, C.c_int]
+        self.lib.sofie_session_infer_bs.restype = C.c_long
+        self.lib.sofie_session_infer_bs.argtypes = [C.c_void_p, C.c_long, C.c_void_p, C.c_void_p, C.c_long, C.c_char_p, C.c_int]
+        self.lib.sofie_session_destroy.argtypes = [C.c_void_p]
+        self.err = C.create_string_buffer(1024)
+        self.handle = self.lib.sofie_session_create_bs(str(dat).encode(), max_batch, self.err, 1024)
+        if not self.handle:
+            raise RuntimeError(self.err.value.decode())
+        self.max_batch, self.out_per_sample = max_batch, out_per_sample
+
+    def infer(self, x: np.ndarray) -> np.ndarray:
+        """x: [batch, ...] float32; returns batch * out_per_sample floats."""
+        x = np.ascontiguousarray(x, np.float32)
+        bs = x.shape[0]
+        y = np.empty(max(1, bs * self.out_per_sample), np.float32)
+        ptrs = (C.c_void_p * 1)(x.ctypes.data_as(C.c_void_p))
+        n = self.lib.sofie_session_infer_bs(self.handle, bs, ptrs, y.ctypes.data_as(C.c_void_p), y.size, self.err, 1024)
+        if n != bs * self.out_per_sample:
+            raise RuntimeError(f"infer failed ({n}): {self.err.value.decode()}")
+        return y[:n]
+
+    def close(self):
+        if self.handle:
+            self.lib.sofie_session_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def dynamic_session_from_model(model, name: str, max_batch: int, param: str = "bs") -> DynamicSession:
+    """configs.Model -> ONNX with the first input dimension written as the parameter `param` -> Generate() without a batch
+    size -> compiled Session(file, max_batch)."""
+    from . import onnx_wire
+    hxx = emit(onnx_wire.model_to_onnx(model, batch_param=param), name)
+    so = compile_session(hxx, name)
+    sess = DynamicSession(so, hxx.with_suffix(".dat"), max_batch, int(np.prod(model_output_shape(model)[1:])))
+    sess.hxx = hxx
+    return sess
+
+
+def model_output_shape(model):
+    """Shape of the model's output for its configured batch, from a dry run of the shapes through the layers' weights (Gemm /
+    QLinearMatMul chains end in [batch, N]); falls back to running nothing: only the per-sample size is needed."""
+    last = model.layers[-1]
+    w = model.weights
+    for L in reversed(model.layers):
+        if L["op"] in ("Gemm", "QLinearMatMul", "Fp8Gemm"):
+            B = w[L["B"]]
+            n = B.shape[0] if (L.get("transB") or L["op"] == "Fp8Gemm") else B.shape[1]
+            return (model.batch(), n)
+    raise ValueError(f"cannot tell the output width of a model ending in {last['op']}")
 
 
 class GeneratedSession:

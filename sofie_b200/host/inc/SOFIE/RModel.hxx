@@ -57,6 +57,14 @@ private:
    size_t fArenaBytes = 0;
    bool fForcePipelinedUpload = false;
    bool fNeverPipelinedUpload = false;
+   // Run-time batch: Generate() without a batch size on a model whose inputs carry a batch parameter in their first
+   // dimension keeps that parameter in the emitted Session (reference: RModel.cxx:680-713, 876-884). Shapes are then
+   // inferred with the batch set to a large prime; a number of the emitted text that is a multiple of it scales with the
+   // batch and is written as `k * fBatch`.
+   bool fDynamicBatch = false;
+   std::string fBatchParam;
+   static constexpr size_t kBatchSentinel = 1000003;
+   void MakeBatchSymbolic();
    std::vector<std::string> fSessionMembers;         // data members of the emitted Session, in declaration order
    std::set<std::string> fDeviceWeights;             // initialised tensors the emitted code uploads
    struct DeviceBuffer {

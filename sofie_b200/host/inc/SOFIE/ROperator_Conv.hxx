@@ -1,4 +1,4 @@
-// ONNX Conv (2-D), optional fused Relu and MaxPool 2x2.
+// ONNX Conv (1-D and 2-D), optional fused Relu and MaxPool 2x2.
 //
 // Constructor signatures as in the reference (src/SOFIE_core/inc/SOFIE/ROperator_Conv.hxx:52-92) and
 // the same attribute rules: no `pads` attribute means pad 1 (:136-139), SAME_UPPER / SAME_LOWER give
@@ -7,7 +7,8 @@
 // UTILITY::Im2col, sgemm_ and saxpy_ (:302-522); this emits ONE call of sofie_cuda_conv2d_f32 and
 // registers no `_f` / `_xcol` scratch tensors. When the model plan fuses a following Relu and
 // MaxPool(2x2, stride 2) the call's descriptor carries them and the output tensor is the pool's.
-// 1-D and 3-D convolutions are outside the CUDA path.
+// A 1-D convolution [N,C,L] * [Cout,C/g,k] (reference: fDim == 1, :95-201) is the 2-D one on an image of height 1
+// (kernel 1 x k, no padding in the added dimension): same call, same kernels. 3-D convolutions are outside the CUDA path.
 #ifndef SOFIE_ROPERATOR_CONV
 #define SOFIE_ROPERATOR_CONV
 
@@ -28,11 +29,39 @@ struct ConvAttributes {
    // resolved values
    size_t kH = 0, kW = 0, padH = 0, padW = 0, sH = 1, sW = 1, dH = 1, dW = 1;
 
+   bool oneD = false; // rank-3 tensors: the single spatial axis is treated as the width of an image of height 1
+
    void Resolve(const std::vector<size_t> &shapeX, const std::vector<size_t> &shapeW)
    {
-      if (shapeX.size() != 4 || shapeW.size() != 4)
-         throw std::runtime_error("SOFIE Conv Op: only 2-D convolutions (rank-4 tensors) are generated for the CUDA path");
+      oneD = shapeX.size() == 3 && shapeW.size() == 3;
+      if (!oneD && (shapeX.size() != 4 || shapeW.size() != 4))
+         throw std::runtime_error("SOFIE Conv Op: only 1-D and 2-D convolutions (rank-3 and rank-4 tensors) are generated for the CUDA path");
       if (group == 0) group = shapeX[1] / shapeW[1];
+      if (oneD) {
+         kH = 1;
+         kW = kernel_shape.empty() ? shapeW[2] : kernel_shape[0];
+         if (kW != shapeW[2]) throw std::runtime_error("SOFIE Conv Op: kernel_shape differs from the weight tensor");
+         dH = sH = 1;
+         dW = dilations.empty() ? 1 : dilations[0];
+         sW = strides.empty() ? 1 : strides[0];
+         const size_t eW = kW + (dW - 1) * (kW - 1);
+         std::vector<size_t> p; // {begin, end} of the one spatial axis
+         if (autopad == "NOTSET") {
+            p = pads.empty() ? std::vector<size_t>{1, 1} : pads; // the reference's default is 1, not 0 (:136-139)
+         } else if (autopad == "SAME_UPPER" || autopad == "SAME_LOWER") {
+            p = {eW / 2, eW / 2};
+            if (eW % 2 == 1) (autopad == "SAME_UPPER") ? p[0]++ : p[1]++;
+         } else if (autopad == "VALID") {
+            p = {0, 0};
+         } else {
+            throw std::runtime_error("SOFIE Conv Op invalid auto_pad " + autopad);
+         }
+         if (p.size() != 2) throw std::runtime_error("SOFIE Conv Op: pads of a 1-D convolution must have 2 values");
+         padH = 0;
+         padW = (p[0] == p[1]) ? p[0] : (p[0] + p[1]) / 2; // averaged like the 2-D case
+         pads = {0, p[0], 0, p[1]};
+         return;
+      }
       kH = kernel_shape.empty() ? shapeW[2] : kernel_shape[0];
       kW = kernel_shape.empty() ? shapeW[3] : kernel_shape[1];
       if (kH != shapeW[2] || kW != shapeW[3]) throw std::runtime_error("SOFIE Conv Op: kernel_shape differs from the weight tensor");
@@ -62,6 +91,7 @@ struct ConvAttributes {
    std::vector<size_t> OutputShape(const std::vector<size_t> &shapeX, const std::vector<size_t> &shapeW) const
    {
       const size_t eH = kH + (dH - 1) * (kH - 1), eW = kW + (dW - 1) * (kW - 1);
+      if (oneD) return {shapeX[0], shapeW[0], (shapeX[2] + pads[1] + pads[3] - eW) / sW + 1};
       // the reference sizes the output from the un-averaged pads (ROperator_Conv.hxx:178-189)
       size_t oH = (shapeX[2] + pads[0] + pads[2] - eH) / sH + 1;
       size_t oW = (shapeX[3] + pads[1] + pads[3] - eW) / sW + 1;
@@ -234,8 +264,10 @@ private:
          x += " + (size_t)part * " + std::to_string(ConvertShapeToLength(fShapeX) / parts);
          y += " + (size_t)part * " + std::to_string(ConvertShapeToLength(fShapeOut) / parts);
       }
-      out << SP << SP << "const sofie_conv2d_desc d = {" << fShapeX[0] / parts << ", " << fShapeX[1] << ", " << fShapeX[2] << ", "
-          << fShapeX[3] << ", " << fShapeW[0] << ", " << fAttr.kH << ", " << fAttr.kW << ", " << fAttr.padH << ", " << fAttr.padW
+      // a 1-D convolution runs as an image of height 1
+      const size_t H = fAttr.oneD ? 1 : fShapeX[2], W = fAttr.oneD ? fShapeX[2] : fShapeX[3];
+      out << SP << SP << "const sofie_conv2d_desc d = {" << fShapeX[0] / parts << ", " << fShapeX[1] << ", " << H << ", "
+          << W << ", " << fShapeW[0] << ", " << fAttr.kH << ", " << fAttr.kW << ", " << fAttr.padH << ", " << fAttr.padW
           << ", " << fAttr.sH << ", " << fAttr.sW << ", " << fAttr.dH << ", " << fAttr.dW << ", " << fAttr.group << ", "
           << (int)fLayoutX << ", " << (int)fLayoutY << ", " << (fPacked ? 1 : 0) << ", " << (fFusedRelu ? 1 : 0) << ", "
           << fFusedPool << "};\n";

@@ -2,8 +2,11 @@
 //
 // Constructor as in the reference (src/SOFIE_core/inc/SOFIE/ROperator_Einsum.hxx:40-60: equation, input names,
 // output name). The reference emits nested loops over the output and the summation labels, or one sgemm_ per stack
-// index when the equation is a (stacked) matrix product (:200-332); this emits ONE call of sofie_cuda_einsum_f32 with
-// the labels' extents and strides worked out here. "ik,kj->ij" never gets here: the parser hands it to the GEMM.
+// index when the equation is a (stacked) matrix product (:200-332). Here an equation of the form
+// "<stack>ik,<stack>kj-><stack>ij" (either operand possibly transposed in its last two labels) becomes one call of
+// sofie_cuda_gemm_f32_batched, i.e. the tensor-core GEMM per stack index; every other equation is ONE call of
+// sofie_cuda_einsum_f32 with the labels' extents and strides worked out here. "ik,kj->ij" never gets here: the parser
+// hands it to the GEMM operator.
 #ifndef SOFIE_ROPERATOR_EINSUM
 #define SOFIE_ROPERATOR_EINSUM
 
@@ -25,6 +28,32 @@ class ROperator_Einsum final : public ROperator {
    std::vector<char> fLabels;            // output labels in output order, then the summed ones
    std::vector<size_t> fExtent, fStrideA, fStrideB;
    size_t fNOut = 0;
+   // stacked matrix product form
+   bool fIsMatMul = false;
+   size_t fStack = 1, fM = 0, fN = 0, fK = 0;
+   int fTransA = 0, fTransB = 0;
+
+   // "<stack>ik,<stack>kj-><stack>ij": the same leading labels in the same order everywhere, then two labels each
+   void DetectMatMul(const std::map<char, size_t> &size)
+   {
+      fIsMatMul = false;
+      const size_t nb = fLabelsOut.size() < 2 ? std::string::npos : fLabelsOut.size() - 2;
+      if (nb == std::string::npos || fLabelsA.size() != nb + 2 || fLabelsB.size() != nb + 2) return;
+      if (fLabelsA.compare(0, nb, fLabelsOut, 0, nb) != 0 || fLabelsB.compare(0, nb, fLabelsOut, 0, nb) != 0) return;
+      const std::string ra = fLabelsA.substr(nb), rb = fLabelsB.substr(nb), ro = fLabelsOut.substr(nb);
+      const char i = ro[0], j = ro[1];
+      if (ra.find(i) == std::string::npos || rb.find(j) == std::string::npos || ra.find(j) != std::string::npos || rb.find(i) != std::string::npos) return;
+      const char ka = ra[0] == i ? ra[1] : ra[0], kb = rb[0] == j ? rb[1] : rb[0];
+      if (ka != kb || ka == i || ka == j) return;
+      fIsMatMul = true;
+      fTransA = ra[0] == ka;   // A stored [k][i]
+      fTransB = rb[0] == j;    // B stored [j][k]
+      fM = size.at(i);
+      fN = size.at(j);
+      fK = size.at(ka);
+      fStack = 1;
+      for (size_t b = 0; b < nb; b++) fStack *= size.at(fLabelsOut[b]);
+   }
 
    void ParseEquation()
    {
@@ -104,6 +133,7 @@ public:
       std::vector<size_t> y;
       for (char c : fLabelsOut) y.push_back(size[c]);
       if (y.empty()) y.push_back(1); // a scalar result is kept as one element
+      DetectMatMul(size);
       return {y};
    }
    void Initialize(RModel &model) override
@@ -135,6 +165,16 @@ public:
       };
       out << "\n" << SP << "//------ Einsum op_" << OpName << "  " << fEquation << " -> " << fNY << " " << ConvertShapeToString(fShapeY) << "\n";
       out << SP << "{\n";
+      if (fIsMatMul) {
+         // a (stacked) matrix product: the GEMM kernels, one product per stack index
+         out << SP << SP << "const sofie_gemm_f32_desc d = {" << fM << ", " << fN << ", " << fK << ", " << fTransA << ", " << fTransB
+             << ", 1.0f, 0.0f, 0, 0};\n";
+         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_f32_batched(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNB) + ", nullptr, " +
+                                       EMIT::Dev(fNY) + ", " + std::to_string(fStack) + ", " + std::to_string(fM * fK) + ", " +
+                                       std::to_string(fN * fK) + ", " + std::to_string(fM * fN) + ")");
+         out << SP << "}\n";
+         return out.str();
+      }
       out << SP << SP << "const sofie_einsum_desc d = {" << fNOut << ", " << fLabels.size() - fNOut << ", {" << list(fExtent) << "}, {"
           << list(fStrideA) << "}, {" << list(fStrideB) << "}};\n";
       out << EMIT::Call(SP + SP, "sofie_cuda_einsum_f32(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNB) + ", " + EMIT::Dev(fNY) + ")");

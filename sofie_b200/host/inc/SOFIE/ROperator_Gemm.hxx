@@ -32,6 +32,7 @@ private:
    EActivationType fActivation = EActivationType::UNDEFINED;
    std::vector<size_t> fShapeA, fShapeB, fShapeC, fShapeY;
    size_t fM = 0, fN = 0, fK = 0;
+   size_t fStack = 1; // matrices in a stacked MatMul (both operands carry the same leading dimensions)
    int fBiasKind = 0;
    int fEmitTransB = 0;
 
@@ -71,7 +72,7 @@ public:
    bool MlpFusable() const
    {
       return fPlainInput && fNBdev != fNB && fAttrAlpha == 1.f && !fAttrTransA && (fBiasKind == 0 || (fBiasKind == 1 && fAttrBeta == 1.f)) &&
-             fK <= 256 && fN <= 256 && fM <= kMlpFusedMaxRows && fShapeA.size() == 2;
+             fK <= 256 && fN <= 256 && fM <= kMlpFusedMaxRows && fShapeA.size() == 2 && fStack == 1;
    }
    void AbsorbChain(const std::vector<ROperator_Gemm<T> *> &tail)
    {
@@ -89,17 +90,29 @@ public:
    {
       if (input.size() < 2 || input.size() > 3) throw std::runtime_error("SOFIE Gemm Op Shape Inference needs 2 or 3 input tensors");
       auto a = input[0], b = input[1];
-      if (a.size() < 2 || b.size() != 2)
-         throw std::runtime_error("SOFIE Gemm Op: A must have at least 2 dimensions and B exactly 2 (stacked MatMul is not on the CUDA path yet)");
-      // leading dimensions of A fold into the row count
+      if (a.size() < 2 || b.size() < 2) throw std::runtime_error("SOFIE Gemm Op: A and B must have at least 2 dimensions");
+      // B with leading dimensions of extent 1 only is a plain matrix
+      while (b.size() > 2 && b[0] == 1) b.erase(b.begin());
+      fStack = 1;
+      if (b.size() > 2) {
+         // a stack of matrices on both sides (ONNX MatMul): the leading dimensions must agree; product s multiplies
+         // matrix s of A with matrix s of B
+         if (a.size() != b.size() || !std::equal(a.begin(), a.end() - 2, b.begin()))
+            throw std::runtime_error("SOFIE Gemm Op: stacked operands " + ConvertShapeToString(input[0]) + " and " + ConvertShapeToString(input[1]) +
+                                     " need the same leading dimensions");
+         if (fAttrTransA || fAttrTransB) throw std::runtime_error("SOFIE Gemm Op: transposed stacked operands are not supported");
+         for (size_t i = 0; i + 2 < a.size(); i++) fStack *= a[i];
+      }
+      // leading dimensions of A fold into the row count when B is one matrix
       size_t rows = 1;
-      for (size_t i = 0; i + 2 < a.size(); i++) rows *= a[i];
+      if (fStack == 1)
+         for (size_t i = 0; i + 2 < a.size(); i++) rows *= a[i];
       size_t am = a[a.size() - 2], ak = a[a.size() - 1];
       if (fAttrTransA) {
          if (a.size() != 2) throw std::runtime_error("SOFIE Gemm Op: transA with a stacked A is not supported");
          std::swap(am, ak);
       }
-      size_t bk = fAttrTransB ? b[1] : b[0], bn = fAttrTransB ? b[0] : b[1];
+      size_t bk = fAttrTransB ? b[b.size() - 1] : b[b.size() - 2], bn = fAttrTransB ? b[b.size() - 2] : b[b.size() - 1];
       if (ak != bk) throw std::runtime_error("SOFIE Gemm Op: inner dimensions differ: " + std::to_string(ak) + " vs " + std::to_string(bk));
       std::vector<size_t> y(a.begin(), a.end() - 2);
       y.push_back(am);
@@ -121,6 +134,8 @@ public:
       fShapeB = model.GetTensorShape(fNB);
       if (fShapeB.size() == 1) fShapeB.push_back(1);
       fShapeY = ShapeInference({fShapeA, fShapeB})[0];
+      if (fStack > 1 && !fNC.empty() && model.GetTensorShape(fNC).size() > 1 && ConvertShapeToLength(model.GetTensorShape(fNC)) != fN)
+         throw std::runtime_error("SOFIE Gemm Op: a stacked product takes a bias per column only");
       if (!fNC.empty()) {
          if (!model.IsInitializedTensor(fNC)) throw std::runtime_error("SOFIE Gemm Op: bias " + fNC + " must be a constant tensor");
          fShapeC = model.GetTensorShape(fNC);
@@ -139,7 +154,7 @@ public:
       if (model.IsInitializedTensor(fNB)) {
          const auto &w = model.GetInitializedTensor(fNB);
          const float *src = w.data<float>();
-         std::shared_ptr<void> buf(malloc(fN * fK * sizeof(float) + 1), free);
+         std::shared_ptr<void> buf(malloc(fStack * fN * fK * sizeof(float) + 1), free);
          float *dst = static_cast<float *>(buf.get());
          // K axis order of A on the device: (h,w,c) when A is the flattening of an NHWC activation
          std::vector<size_t> kperm(fK);
@@ -155,13 +170,14 @@ public:
                for (size_t x = 0; x < W; x++)
                   for (size_t c = 0; c < C; c++) kperm[(h * W + x) * C + c] = (c * H + h) * W + x;
          }
-         for (size_t n = 0; n < fN; n++)
-            for (size_t k = 0; k < fK; k++) {
-               size_t ks = kperm[k];
-               dst[n * fK + k] = fAttrTransB ? src[n * fK + ks] : src[ks * fN + n];
-            }
+         for (size_t st = 0; st < fStack; st++)
+            for (size_t n = 0; n < fN; n++)
+               for (size_t k = 0; k < fK; k++) {
+                  size_t ks = kperm[k];
+                  dst[(st * fN + n) * fK + k] = fAttrTransB ? src[(st * fN + n) * fK + ks] : src[(st * fK + ks) * fN + n];
+               }
          fNBdev = fNB + "_nk_" + fNY;
-         model.AddInitializedTensor(fNBdev, ETensorType::FLOAT, {fN, fK}, buf);
+         model.AddInitializedTensor(fNBdev, ETensorType::FLOAT, {fStack * fN, fK}, buf);
          model.UseOnDevice(fNBdev);
          fEmitTransB = 1;
       } else if (model.GetTensorLayout(model.ResolveAlias(fNA)) == ELayout::NHWC) {
@@ -224,6 +240,19 @@ public:
          out << SP << SP << "const float * const w[] = {" << w << "};\n";
          out << SP << SP << "const float * const b[] = {" << b << "};\n";
          out << EMIT::Call(SP + SP, "sofie_cuda_mlp_f32(fStream, &d, " + EMIT::Dev(fNA) + ", w, b, " + EMIT::Dev(fNYChain) + ")");
+         out << SP << "}\n";
+         return out.str();
+      }
+      if (fStack > 1) {
+         out << "\n" << SP << "//--------- stacked MatMul " << opName << ": " << fStack << " x ([" << fM << "," << fK << "] x [" << fK << "," << fN << "])\n";
+         out << SP << "{\n";
+         out << SP << SP << "const sofie_gemm_f32_desc d = {" << fM << ", " << fN << ", " << fK << ", 0, " << fEmitTransB << ", "
+             << EMIT::FloatLit(fAttrAlpha) << ", " << EMIT::FloatLit(fBiasKind ? fAttrBeta : 0.f) << ", " << fBiasKind << ", "
+             << (fActivation == EActivationType::RELU ? 1 : 0) << "};\n";
+         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_f32_batched(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNBdev) + ", " +
+                                       (fBiasKind ? EMIT::Dev(fNCdev) : std::string("nullptr")) + ", " + EMIT::Dev(fNY) + ", " +
+                                       std::to_string(fStack) + ", " + std::to_string(fM * fK) + ", " + std::to_string(fN * fK) + ", " +
+                                       std::to_string(fM * fN) + ")");
          out << SP << "}\n";
          return out.str();
       }

@@ -4,6 +4,7 @@
 #include "SOFIE/RModel.hxx"
 
 #include <algorithm>
+#include <cctype>
 #include <fstream>
 #include <iomanip>
 #include <iostream>
@@ -265,13 +266,33 @@ void RModel::Initialize(int batchSize, bool verbose)
    // shapes are fixed at generation time: parametric input dimensions take batchSize when given,
    // else their default value, else 1 (the reference substitutes batch parameters the same way,
    // src/SOFIE_core/src/RModel.cxx:399-440, and can leave others dynamic)
+   // Without a batch size the parameter stays a run-time value when it is the first dimension of every parametric
+   // input and the only parameter (what exporters write for a dynamic batch axis); any other parametric shape is
+   // fixed to its default as before.
+   fDynamicBatch = false;
+   if (batchSize <= 0 && !fInputTensorInfos.empty()) {
+      bool ok = true;
+      std::string param;
+      for (auto &input : fInputTensorInfos)
+         for (size_t i = 0; i < input.second.shape.size(); i++) {
+            const Dim &d = input.second.shape[i];
+            if (!d.isParam) continue;
+            if (i != 0 || (!param.empty() && param != d.param)) ok = false;
+            param = d.param;
+         }
+      // every input must carry it: a fully specified input next to a batched one cannot be scaled
+      if (ok && !param.empty() && fReadyInputTensorInfos.empty()) {
+         fDynamicBatch = true;
+         fBatchParam = param;
+      }
+   }
    for (auto &input : fInputTensorInfos) {
       std::vector<size_t> shape;
       for (auto &d : input.second.shape) {
          if (d.isParam) {
-            size_t v = batchSize > 0 ? (size_t)batchSize : (d.dim ? d.dim : 1);
-            fShapeParams[d.param] = std::to_string(v);
-            shape.push_back(v);
+            size_t v = batchSize > 0 ? (size_t)batchSize : ((d.dim && d.dim != static_cast<size_t>(-1)) ? d.dim : 1);
+            fShapeParams[d.param] = std::to_string(v);   // the constructor's default for the parameter
+            shape.push_back(fDynamicBatch ? kBatchSentinel : v);
          } else {
             shape.push_back(d.dim);
          }
@@ -408,6 +429,14 @@ void RModel::PlanArena()
    std::vector<Slot> slots;
    auto bytes_of = [&](const std::string &n) {
       size_t b = ConvertShapeToLength(GetTensorShape(n)) * GetTypeSize(GetTensorType(n));
+      if (fDynamicBatch) {
+         // slices scale with the batch: the bytes of ONE sample are rounded to 256, so that every offset is a multiple of
+         // 256 for every batch
+         if (b % kBatchSentinel != 0)
+            throw std::runtime_error("SOFIE: tensor " + n + " does not scale with the batch parameter " + fBatchParam +
+                                     "; generate this model with a fixed batch size");
+         return kBatchSentinel * ((std::max<size_t>(b / kBatchSentinel, 1) + 255) & ~size_t(255));
+      }
       return (std::max<size_t>(b, 1) + 255) & ~size_t(255);
    };
    for (auto &in : fInputTensorNames) slots.push_back({in, bytes_of(in), -1, -1, 0});
@@ -459,6 +488,7 @@ void RModel::PlanArena()
 std::string RModel::GenerateInferSignature(bool isdecl)
 {
    std::string s;
+   if (fDynamicBatch) s += std::string(isdecl ? "size_t " : "") + fBatchParam + ",";   // reference: RModel.cxx:688-702
    for (auto &name : fInputTensorNames) {
       if (isdecl) {
          std::string type = ConvertTypeToString(GetTensorType(name));
@@ -496,8 +526,51 @@ void RModel::Generate(std::underlying_type_t<Options> options, int batchSize, lo
    fGC.clear();
    GenerateHeaderInfo(hgname);
    GenerateSessionCode();
+   if (fDynamicBatch) MakeBatchSymbolic();
    fGC += ("} //SOFIE_" + fName + "\n");
    fGC += "\n#endif  // " + hgname + "\n";
+}
+
+// Rewrites every integer literal of the emitted Session that is a non-zero multiple of the batch sentinel as
+// `<multiple> * fBatch` (inside the braces of a descriptor, whose fields are 32-bit, with a cast). The sentinel is a
+// prime above a million, so a number that does not scale with the batch is not a multiple of it.
+void RModel::MakeBatchSymbolic()
+{
+   std::string out;
+   out.reserve(fGC.size() + 1024);
+   size_t line_start = 0;
+   while (line_start < fGC.size()) {
+      size_t line_end = fGC.find('\n', line_start);
+      if (line_end == std::string::npos) line_end = fGC.size();
+      const std::string line = fGC.substr(line_start, line_end - line_start);
+      const bool in_desc = line.find("_desc ") != std::string::npos && line.find("= {") != std::string::npos;
+      for (size_t i = 0; i < line.size();) {
+         const char c = line[i];
+         const bool starts_number = std::isdigit((unsigned char)c) && (i == 0 || !(std::isalnum((unsigned char)line[i - 1]) || line[i - 1] == '_' || line[i - 1] == '.'));
+         if (!starts_number) {
+            out += c;
+            i++;
+            continue;
+         }
+         size_t j = i;
+         while (j < line.size() && std::isdigit((unsigned char)line[j])) j++;
+         const bool plain = j == line.size() || !(std::isalnum((unsigned char)line[j]) || line[j] == '_' || line[j] == '.');
+         const std::string digits = line.substr(i, j - i);
+         unsigned long long v = 0;
+         bool fits = digits.size() <= 18;
+         if (fits) v = std::stoull(digits);
+         if (plain && fits && v != 0 && v % kBatchSentinel == 0) {
+            const std::string k = std::to_string(v / kBatchSentinel);
+            out += in_desc ? "static_cast<int32_t>(" + k + " * fBatch)" : "(size_t(" + k + ") * fBatch)";
+         } else {
+            out += digits;
+         }
+         i = j;
+      }
+      if (line_end < fGC.size()) out += '\n';
+      line_start = line_end + 1;
+   }
+   fGC.swap(out);
 }
 
 static std::string ByteCount(const std::vector<size_t> &shape, ETensorType t)
@@ -515,6 +588,12 @@ void RModel::GenerateSessionMembers()
    fGC += "void * fStream = nullptr;\n";
    fGC += "bool fGraphReady = false;\n";
    fGC += "bool fUseGraph = true;\n";
+   if (fDynamicBatch) {
+      fSessionMembers.push_back("fBatch");
+      fSessionMembers.push_back("fMaxBatch");
+      fGC += "size_t fBatch = 0;      // batch of the current / last infer(); the captured graph is the one of this batch\n";
+      fGC += "size_t fMaxBatch = 0;   // the batch the Session was constructed for: the arena holds that many samples\n";
+   }
    auto pointer = [this](ETensorType type, const std::string &name) {
       fGC += EMIT::CType(type) + " * " + EMIT::Dev(name) + " = nullptr;\n";
       fSessionMembers.push_back(EMIT::Dev(name));
@@ -605,9 +684,14 @@ void RModel::GenerateConstructor()
    else fGC += "Session(std::string = \"\"";
    for (auto &p : fShapeParams) fGC += ",\n        size_t " + p.first + " = " + p.second;
    fGC += ") {\n";
-   for (auto &p : fShapeParams)
-      fGC += "   if (" + p.first + " != " + p.second + ") throw std::runtime_error(\"SOFIE: this Session was generated for " + p.first +
-             " = " + p.second + "\");\n";
+   if (fDynamicBatch) {
+      fGC += "   if (" + fBatchParam + " == 0) throw std::runtime_error(\"SOFIE: a Session needs room for at least one sample\");\n";
+      fGC += "   fBatch = fMaxBatch = " + fBatchParam + ";\n";
+   } else {
+      for (auto &p : fShapeParams)
+         fGC += "   if (" + p.first + " != " + p.second + ") throw std::runtime_error(\"SOFIE: this Session was generated for " + p.first +
+                " = " + p.second + "\");\n";
+   }
    fGC += "   if (const char * g = std::getenv(\"SOFIE_CUDA_GRAPH\")) fUseGraph = (g[0] != '0');\n";
    fGC += "   Check(sofie_cuda_ctx_create(&fCtx, -1, " + std::to_string(fArenaBytes) + "), \"sofie_cuda_ctx_create\");\n";
    fGC += "   try {\n";
@@ -707,7 +791,7 @@ void RModel::GenerateInfer()
          break;
       }
    bool pipelined = false;
-   if (head < fOperators.size() && fInputTensorNames.size() == 1 && !fNeverPipelinedUpload) {
+   if (head < fOperators.size() && fInputTensorNames.size() == 1 && !fNeverPipelinedUpload && !fDynamicBatch) {
       const std::string &in = fInputTensorNames[0];
       const auto &reads = fOperators[head]->GetOpInputTensors();
       size_t readers = 0;
@@ -773,6 +857,13 @@ void RModel::GenerateInfer()
    fGC += "   Run();\n";
    fGC += "}\n\n";
    fGC += ret + " infer(" + GenerateInferSignature() + "){\n";
+   if (fDynamicBatch) {
+      // any batch up to the one the Session was built for; the graph is captured again when the batch changes
+      fGC += "   if (" + fBatchParam + " > fMaxBatch) throw std::runtime_error(\"SOFIE: infer() was called with " + fBatchParam +
+             " = \" + std::to_string(" + fBatchParam + ") + \", the Session was constructed for at most \" + std::to_string(fMaxBatch));\n";
+      fGC += "   if (" + fBatchParam + " == 0) return {};\n";
+      fGC += "   if (" + fBatchParam + " != fBatch) { fBatch = " + fBatchParam + "; fGraphReady = false; }\n";
+   }
    if (pipelined) {
       const std::string &n = fInputTensorNames[0];
       const size_t elems = ConvertShapeToLength(GetTensorShape(n)) / kUploadParts;

@@ -264,8 +264,9 @@ def e4m3_bytes(x: np.ndarray, scale: float) -> np.ndarray:
     return np.clip(q, -448.0, 448.0).astype(ml_dtypes.float8_e4m3fn).view(np.uint8)
 
 
-def model_to_onnx(m, fp8_scales=None) -> bytes:
-    """Serialise a sofie_b200.configs.Model as an ONNX file. The FP8 chain (Fp8Gemm layers) needs its calibrated
+def model_to_onnx(m, fp8_scales=None, batch_param=None) -> bytes:
+    """Serialise a sofie_b200.configs.Model as an ONNX file (batch_param: write the first input dimension as the named
+    parameter instead of a number, as exporters do for a dynamic batch axis). The FP8 chain (Fp8Gemm layers) needs its calibrated
     activation scales: it is written as QuantizeLinear to FLOAT8E4M3FN, one custom Fp8Gemm node per layer with
     E4M3 weights and static scales as attributes, and a final Cast from bfloat16 to float."""
     nodes, inits = [], []
@@ -374,6 +375,6 @@ def model_to_onnx(m, fp8_scales=None) -> bytes:
                 nodes.append(node("Relu", [out], [L["Y"]]))
         else:
             raise NotImplementedError(f"no ONNX serialisation for {op}")
-    inputs = [value_info(m.input_name, FLOAT, m.input_shape)]
+    inputs = [value_info(m.input_name, FLOAT, ([batch_param] + list(m.input_shape[1:])) if batch_param else m.input_shape)]
     outputs = [value_info(m.output_name, FLOAT, [])]
     return model(m.name, nodes, inputs, outputs, inits)

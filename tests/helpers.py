@@ -312,3 +312,22 @@ def tiny_regressor(nfeat=4):
     m.layers.append(dict(op="Gemm", A="h", B="w1", C="b1", Y="y", transB=1))
     m.output_name = "y"
     return m
+
+
+def conv1d_model_onnx(batch=3, length=10, seed=11):
+    """The shape of the reference's 1-D convolution test model (test/Conv1dModelGenerator.py, TestSofieModels.cxx Conv1d_B1):
+    Conv1d 2->4, kernel 2, pad 1, Relu; Conv1d 4->8, kernel 3, pad 1, two groups, Relu. Returns (onnx bytes, weights, input)."""
+    from sofie_b200 import onnx_wire as ow
+    rng = np.random.default_rng(seed)
+    w0 = (rng.standard_normal((4, 2, 2)) * 0.5).astype(np.float32)
+    b0 = rng.uniform(-0.1, 0.1, 4).astype(np.float32)
+    w1 = (rng.standard_normal((8, 2, 3)) * 0.4).astype(np.float32)
+    b1 = rng.uniform(-0.1, 0.1, 8).astype(np.float32)
+    x = rng.standard_normal((batch, 2, length)).astype(np.float32)
+    nodes = [ow.node("Conv", ["x", "w0", "b0"], ["c0"], [ow.attr_ints("kernel_shape", [2]), ow.attr_ints("pads", [1, 1]), ow.attr_ints("strides", [1])]),
+             ow.node("Relu", ["c0"], ["r0"]),
+             ow.node("Conv", ["r0", "w1", "b1"], ["c1"], [ow.attr_ints("kernel_shape", [3]), ow.attr_ints("pads", [1, 1]), ow.attr_int("group", 2)]),
+             ow.node("Relu", ["c1"], ["y"])]
+    g = ow.model("conv1d", nodes, [ow.value_info("x", ow.FLOAT, list(x.shape))], [ow.value_info("y", ow.FLOAT, [])],
+                 [ow.tensor("w0", w0), ow.tensor("b0", b0), ow.tensor("w1", w1), ow.tensor("b1", b1)])
+    return g, dict(w0=w0, b0=b0, w1=w1, b1=b1), x

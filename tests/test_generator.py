@@ -237,8 +237,15 @@ def test_einsum_goes_to_the_gemm_or_to_the_general_kernel_and_refuses_the_rest()
                                [onnx_wire.value_info(n, 1, list(s)) for n, s in zip(names, shapes)], [onnx_wire.value_info("y", 1, [])], [])
     plain = generated.emit(graph("ik,kj->ij", (4, 5), (5, 6)), "einsum_mm").read_text()
     assert "sofie_cuda_gemm_f32(" in plain and "sofie_cuda_einsum_f32(" not in plain
-    general = generated.emit(graph("bij, bjk -> bik", (3, 4, 5), (3, 5, 2)), "einsum_bmm").read_text()
-    assert "const sofie_einsum_desc d = {3, 1, {3, 4, 2, 5, 0, 0, 0, 0}, {20, 5, 0, 1, 0, 0, 0, 0}, {10, 0, 1, 2, 0, 0, 0, 0}};" in general
+    # a stacked matrix product reaches the GEMM kernels too, one product per stack index (either operand may be transposed)
+    bmm = generated.emit(graph("bij, bjk -> bik", (3, 4, 5), (3, 5, 2)), "einsum_bmm").read_text()
+    assert "const sofie_gemm_f32_desc d = {4, 2, 5, 0, 0, 1.0f, 0.0f, 0, 0};" in bmm
+    assert "sofie_cuda_gemm_f32_batched(fStream, &d, dev_a, dev_b, nullptr, dev_y, 3, 20, 10, 8)" in bmm and "sofie_cuda_einsum_f32(" not in bmm
+    bmm_t = generated.emit(graph("abki,abjk->abij", (2, 3, 5, 4), (2, 3, 6, 5)), "einsum_bmm_t").read_text()
+    assert "const sofie_gemm_f32_desc d = {4, 6, 5, 1, 1, 1.0f, 0.0f, 0, 0};" in bmm_t and ", 6, 20, 30, 24)" in bmm_t
+    # anything else (here the stack label sits in another position of the output) is the general kernel
+    general = generated.emit(graph("bij, bjk -> ibk", (3, 4, 5), (3, 5, 2)), "einsum_general").read_text()
+    assert "const sofie_einsum_desc d = {3, 1, {4, 3, 2, 5, 0, 0, 0, 0}, {5, 20, 0, 1, 0, 0, 0, 0}, {0, 10, 1, 2, 0, 0, 0, 0}};" in general
     for eq, sa, sb, n_in, what in (("...ij,...jk->...ik", (3, 4, 5), (3, 5, 2), 2, "ellipsis"), ("ii,ij->j", (4, 4), (4, 3), 2, "repeated"),
                                    ("ij,jk,kl->il", (2, 3), (3, 4), 3, "operands"), ("ij,kk->i", (2, 3), (3, 4), 2, "repeated|extents")):
         with pytest.raises(RuntimeError, match=what):
@@ -281,3 +288,60 @@ def test_eight_processes_emit_and_compile_the_same_model_at_once():
     assert len({r[1] for r in results}) == 1                      # one cache entry serves all eight
     assert len(list(generated.WORK.glob("race_c2_b6_*"))) == 1    # and no temporary directory is left behind
     assert not list(generated.WORK.glob(".race_c2_b6_*.*/"))
+
+
+def test_run_time_batch_parameter_keeps_the_reference_signatures():
+    """Generate() without a batch size on a model whose input has a batch parameter: the emitted Session takes the
+    parameter in its constructor (the largest batch, which sizes the arena) and in infer() (reference: RModel.cxx:680-713,
+    876-884); every number that scales with the batch is written in terms of it."""
+    m, _ = configs.cnn_f32(batch=4, with_input=False)
+    text = generated.emit(onnx_wire.model_to_onnx(m, batch_param="bs"), "c2_dynamic").read_text()
+    assert re.search(r'Session\(std::string filename ="c2_dynamic.dat",\s+size_t bs = 1\)', text)
+    assert "std::vector<float> infer(size_t bs,float* tensor_x){" in text
+    assert "1000003" not in text                                                    # no trace of the stand-in batch
+    assert "const sofie_conv2d_desc d = {static_cast<int32_t>(1 * fBatch), 3, 32, 32, 16," in text
+    assert "sofie_cuda_ctx_h2d(fCtx, dev_x, tensor_x, (size_t(12288) * fBatch))" in text
+    assert "if (bs != fBatch) { fBatch = bs; fGraphReady = false; }" in text and "if (bs > fMaxBatch) throw" in text
+    # slices scale with the batch and stay 256-byte aligned for every batch: one sample's bytes are rounded up
+    slices = re.findall(r"sofie_cuda_ctx_arena\(fCtx, (?:\(size_t\((\d+)\) \* fBatch\)|0), \(size_t\((\d+)\) \* fBatch\)", text)
+    assert len(slices) == 5 and all(int(o or 0) % 256 == 0 for o, _ in slices)
+    assert "LaunchHead" not in text                                                 # the upload is never split: a part is not a whole number of samples
+    generated.compile_session(generated.emit(onnx_wire.model_to_onnx(m, batch_param="bs"), "c2_dynamic"), "c2_dynamic")
+    # with a batch size given, the same file generates the fixed-batch Session as before
+    fixed = generated.emit(onnx_wire.model_to_onnx(m, batch_param="bs"), "c2_dynamic_fixed", batch=8).read_text()
+    assert "std::vector<float> infer(float* tensor_x){" in fixed and "size_t bs = 8" in fixed and "fBatch" not in fixed
+    assert "const sofie_conv2d_desc d = {8, 3, 32, 32, 16," in fixed
+
+
+def test_conv1d_is_emitted_as_an_image_of_height_one():
+    from helpers import conv1d_model_onnx
+    g, _, _ = conv1d_model_onnx(batch=3, length=10)
+    text = generated.emit(g, "conv1d_b3").read_text()
+    descs = [[int(v) for v in d.split(",")] for d in re.findall(r"sofie_conv2d_desc d = \{([^}]*)\}", text)]
+    # N, C, H, W, Cout, kH, kW, pad_h, pad_w, strides, dilations, group, layouts, packed, relu, pool
+    assert descs[0] == [3, 2, 1, 10, 4, 1, 2, 0, 1, 1, 1, 1, 1, 1, 0, 0, 0, 1, 0]
+    assert descs[1] == [3, 4, 1, 11, 8, 1, 3, 0, 1, 1, 1, 1, 1, 2, 0, 0, 0, 1, 0]     # kernel 2 with pad 1 lengthens the axis to 11
+    assert "sofie_cuda_relu_f32(" not in text                                          # both Relus are fused
+    with pytest.raises(RuntimeError, match="1-D and 2-D"):
+        w = np.zeros((2, 2, 3, 3, 3), np.float32)
+        generated.emit(onnx_wire.model("g", [onnx_wire.node("Conv", ["x", "w"], ["y"])], [onnx_wire.value_info("x", 1, [1, 2, 5, 5, 5])],
+                                       [onnx_wire.value_info("y", 1, [])], [onnx_wire.tensor("w", w)]), "conv3d_refused")
+
+
+def test_stacked_matmul_is_one_batched_gemm_call():
+    """MatMul of operands with the same leading dimensions: every stack index multiplies ITS matrices (the ONNX definition;
+    the reference's emitted loop advances only the output offset, ROperator_Gemm.hxx:353-387)."""
+    w = np.arange(2 * 3 * 5 * 4, dtype=np.float32).reshape(2, 3, 5, 4)
+    act = onnx_wire.model("g", [onnx_wire.node("MatMul", ["a", "b"], ["y"])], [onnx_wire.value_info("a", 1, [2, 3, 7, 5]), onnx_wire.value_info("b", 1, [2, 3, 5, 4])],
+                          [onnx_wire.value_info("y", 1, [])], [])
+    text = generated.emit(act, "stacked_mm").read_text()
+    assert "const sofie_gemm_f32_desc d = {7, 4, 5, 0, 0, 1.0f, 0.0f, 0, 0};" in text
+    assert "sofie_cuda_gemm_f32_batched(fStream, &d, dev_a, dev_b, nullptr, dev_y, 6, 35, 20, 28)" in text
+    const = onnx_wire.model("g", [onnx_wire.node("MatMul", ["a", "w"], ["y"])], [onnx_wire.value_info("a", 1, [2, 3, 7, 5])],
+                            [onnx_wire.value_info("y", 1, [])], [onnx_wire.tensor("w", w)])
+    text = generated.emit(const, "stacked_mm_const").read_text()
+    # constant stacked weights are stored [N,K] per matrix, the layout the tensor-core GEMM takes
+    assert "const sofie_gemm_f32_desc d = {7, 4, 5, 0, 1, 1.0f, 0.0f, 0, 0};" in text and "dev_w_nk_y" in text
+    with pytest.raises(RuntimeError, match="same leading dimensions"):
+        generated.emit(onnx_wire.model("g", [onnx_wire.node("MatMul", ["a", "b"], ["y"])], [onnx_wire.value_info("a", 1, [2, 7, 5]), onnx_wire.value_info("b", 1, [3, 5, 4])],
+                                       [onnx_wire.value_info("y", 1, [])], []), "stacked_mm_bad")

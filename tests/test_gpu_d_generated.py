@@ -127,3 +127,72 @@ def test_pipelined_upload_from_pinned_and_pageable_memory(cuda_device):
     xp.copy_(torch.from_numpy(x2))
     s.infer_ptr(xp.data_ptr(), yp.data_ptr())
     assert rel_err(yp.numpy().reshape(256, -1)[::-1], REF["ref_c2"].reshape(256, -1)) <= 1e-5
+
+
+@pytest.mark.parametrize("key,kw,bit_exact", [("C1", {}, False), ("C2", {}, False), ("C3", {}, True), ("C5", {}, True)])
+def test_run_time_batch_session(key, kw, bit_exact, cuda_device):
+    """One Session constructed for 48 samples serves batches of 48, 17, 1 and 48 again (the graph is captured anew when the
+    batch changes); each result equals the oracle's for those samples, and a larger batch is refused."""
+    m, x = configs.BUILDERS[key](batch=48, **kw)
+    s = generated.dynamic_session_from_model(m, f"{key.lower()}_dyn48", 48)
+    per = s.out_per_sample
+    for bs in (48, 17, 17, 1, 48):
+        mb, _ = configs.BUILDERS[key](batch=bs, with_input=False, **kw)
+        ref = run_model.run(mb, x[:bs]).ravel()
+        y = s.infer(x[:bs])
+        assert y.size == bs * per
+        if bit_exact:
+            assert np.array_equal(y.view(np.uint32), ref.view(np.uint32)), bs
+        else:
+            assert rel_err(y, ref) <= 1e-5, bs
+    with pytest.raises(RuntimeError, match="constructed for at most 48"):
+        s.infer(np.zeros((49,) + x.shape[1:], np.float32))
+    assert s.infer(x[:0]).size == 0
+
+
+def test_conv1d_model_through_generated_session(cuda_device):
+    """The reference's 1-D convolution test shape (two Conv1d layers, the second grouped) against the oracle's 2-D convolution on
+    the same data seen as images of height 1, and against torch's conv1d in float64."""
+    import torch
+    import torch.nn.functional as F
+    from helpers import conv1d_model_onnx
+    from oracle import cpu_oracle as o
+    for batch, length in ((1, 10), (5, 33)):
+        g, w, x = conv1d_model_onnx(batch, length)
+        name = f"conv1d_b{batch}_l{length}"
+        hxx = generated.emit(g, name)
+        t = F.relu(F.conv1d(torch.from_numpy(x).double(), torch.from_numpy(w["w0"]).double(), torch.from_numpy(w["b0"]).double(), padding=1))
+        t = F.relu(F.conv1d(t, torch.from_numpy(w["w1"]).double(), torch.from_numpy(w["b1"]).double(), padding=1, groups=2)).numpy()
+        r = o.conv2d_f32(x[:, :, None, :], w["w0"][:, :, None, :], w["b0"], pad=(0, 1), relu=True)
+        r = o.conv2d_f32(r, w["w1"][:, :, None, :], w["b1"], pad=(0, 1), group=2, relu=True)[:, :, 0, :]
+        assert r.shape == t.shape and rel_err(r, t) <= 1e-6
+        s = generated.GeneratedSession(generated.compile_session(hxx, name), hxx.with_suffix(".dat"), r.size)
+        assert rel_err(s.infer(x), r) <= 1e-5
+
+
+def test_stacked_matmul_and_stacked_einsum_through_generated_session(cuda_device):
+    rng = np.random.default_rng(8)
+    a = rng.standard_normal((2, 3, 70, 64)).astype(np.float32)
+    b = rng.standard_normal((2, 3, 64, 48)).astype(np.float32)
+    ref = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    # MatMul, both operands run-time tensors
+    g = onnx_wire.model("g", [onnx_wire.node("MatMul", ["a", "b"], ["y"])], [onnx_wire.value_info("a", 1, list(a.shape)), onnx_wire.value_info("b", 1, list(b.shape))],
+                        [onnx_wire.value_info("y", 1, [])], [])
+    hxx = generated.emit(g, "stacked_mm_run")
+    s = generated.GeneratedSession(generated.compile_session(hxx, "stacked_mm_run"), hxx.with_suffix(".dat"), ref.size)
+    assert rel_err(s.infer([a, b]), ref) <= 1e-5
+    # MatMul with constant stacked weights followed by a bias Add (fused into the product) 
+    bias = rng.standard_normal(48).astype(np.float32)
+    g = onnx_wire.model("g", [onnx_wire.node("MatMul", ["a", "w"], ["h"]), onnx_wire.node("Add", ["h", "c"], ["y"])], [onnx_wire.value_info("a", 1, list(a.shape))],
+                        [onnx_wire.value_info("y", 1, [])], [onnx_wire.tensor("w", b), onnx_wire.tensor("c", bias)])
+    hxx = generated.emit(g, "stacked_mm_const_run")
+    s = generated.GeneratedSession(generated.compile_session(hxx, "stacked_mm_const_run"), hxx.with_suffix(".dat"), ref.size)
+    assert rel_err(s.infer(a), ref + bias) <= 1e-5
+    # Einsum, stacked with a transposed second operand
+    bt = np.ascontiguousarray(b.transpose(0, 1, 3, 2))
+    g = onnx_wire.model("g", [onnx_wire.node("Einsum", ["a", "b"], ["y"], [onnx_wire.attr_str("equation", "pqik,pqjk->pqij")])],
+                        [onnx_wire.value_info("a", 1, list(a.shape)), onnx_wire.value_info("b", 1, list(bt.shape))], [onnx_wire.value_info("y", 1, [])], [])
+    hxx = generated.emit(g, "stacked_einsum_run")
+    assert "sofie_cuda_gemm_f32_batched(" in hxx.read_text()
+    s = generated.GeneratedSession(generated.compile_session(hxx, "stacked_einsum_run"), hxx.with_suffix(".dat"), ref.size)
+    assert rel_err(s.infer([a, bt]), ref) <= 1e-5
