@@ -456,6 +456,17 @@ int sofie_cuda_gemm_e4m3(void *stream, const sofie_fp8_gemm_desc *desc, const ui
 int sofie_cuda_gemm_e4m3_f32(void *stream, const sofie_fp8_gemm_desc *desc, const uint8_t *A, const uint8_t *W,
                              const float *bias, float *Yf32);
 
+/* Dynamic per-tensor scales ("scales computed from amax" at run time instead of calibrated ones). The first call computes
+ * max|x| over the n values, stores scale = amax / 448 (1 for an all-zero tensor) in *scale_device and writes
+ * Y = e4m3(x / scale) with the rounding of the static form; the second is sofie_cuda_gemm_e4m3 / _f32 with the
+ * activation scale read from device memory (desc->a_scale and desc->q_scale are ignored: the following layer's scale is
+ * only known once this product is complete, so its input is quantised by the next dynamic_quantize call). Everything
+ * stays on the stream: no value travels to the host. */
+int sofie_cuda_dynamic_quantize_e4m3_f32(void *stream, const float *X, uint8_t *Y, size_t n, float *scale_device);
+int sofie_cuda_dynamic_quantize_e4m3_bf16(void *stream, const uint16_t *X, uint8_t *Y, size_t n, float *scale_device);
+int sofie_cuda_gemm_e4m3_dynamic(void *stream, const sofie_fp8_gemm_desc *desc, const uint8_t *A, const float *a_scale_device,
+                                 const uint8_t *W, const float *bias, uint16_t *Ybf16, float *Yf32);
+
 #ifdef __cplusplus
 }
 #endif

@@ -65,9 +65,14 @@ def run(model, x, fp8_scales=None, return_all=False):
             t[L["Y"]] = o.qlinear_conv2d(t[L["X"]], L["x_scale"], L["x_zp"], w[L["W"]], w[L["w_scale"]], L["y_scale"],
                                          L["y_zp"], pad=(p[0], p[1]), stride=s, relu=L.get("relu", False))
         elif op == "Fp8Gemm":
-            a_scale = fp8_scales[fp8_i]
-            fp8_i += 1
             A = t[L["A"]]
+            if isinstance(fp8_scales, str) and fp8_scales == "dynamic":
+                # scale computed from the tensor itself: max|x| / 448 in float32, 1 for an all-zero tensor
+                amax = np.float32(np.abs(np.asarray(A, np.float32)).max()) if A.size else np.float32(0)
+                a_scale = float(amax / np.float32(448.0)) if amax > 0 else 1.0
+            else:
+                a_scale = fp8_scales[fp8_i]
+            fp8_i += 1
             Aq = o.quantize_e4m3(A, a_scale)
             Wq = o.quantize_e4m3(w[L["B"]], L["w_scale"])
             bits = o.gemm_e4m3(Aq, a_scale, Wq, L["w_scale"], w.get(L.get("C")), relu=L["relu"])

@@ -140,6 +140,9 @@ SIGNATURES = {
     "sofie_cuda_amax_f32": [vp, vp, sz, vp],
     "sofie_cuda_gemm_e4m3": [vp, C.POINTER(Fp8GemmDesc), vp, vp, vp, vp, vp],
     "sofie_cuda_gemm_e4m3_f32": [vp, C.POINTER(Fp8GemmDesc), vp, vp, vp, vp],
+    "sofie_cuda_dynamic_quantize_e4m3_f32": [vp, vp, vp, sz, vp],
+    "sofie_cuda_dynamic_quantize_e4m3_bf16": [vp, vp, vp, sz, vp],
+    "sofie_cuda_gemm_e4m3_dynamic": [vp, C.POINTER(Fp8GemmDesc), vp, vp, vp, vp, vp, vp],
 }
 STRING_GETTERS = {"sofie_cuda_strerror": [C.c_int], "sofie_cuda_last_error": []}
 SIZE_GETTERS = {"sofie_cuda_mlp_f32_smem": [C.POINTER(MlpDesc)]}

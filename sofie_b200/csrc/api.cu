@@ -201,4 +201,19 @@ int sofie_cuda_gemm_e4m3_f32(void *stream, const sofie_fp8_gemm_desc *d, const u
                    [&] { return launch_gemm_e4m3_simt(s, *d, A, W, bias, nullptr, nullptr, Yf32); });
 }
 
+int sofie_cuda_gemm_e4m3_dynamic(void *stream, const sofie_fp8_gemm_desc *d, const uint8_t *A, const float *a_scale_device, const uint8_t *W,
+                                 const float *bias, uint16_t *Ybf16, float *Yf32)
+{
+   SOFIE_REQUIRE(d != nullptr, "NULL descriptor");
+   SOFIE_REQUIRE(d->M >= 0 && d->N > 0 && d->K > 0, "bad GEMM shape");
+   SOFIE_REQUIRE(d->w_scale > 0.f, "w_scale must be positive");
+   if (d->M == 0) return SOFIE_CUDA_OK;
+   SOFIE_REQUIRE(A && W && a_scale_device && (Ybf16 || Yf32), "NULL tensor");
+   cudaStream_t s = as_stream(stream);
+   sofie_fp8_gemm_desc dd = *d;
+   dd.q_scale = 0.f; // the next layer's scale is not known before this product is complete: nothing is quantised here
+   return dispatch([&] { return launch_gemm_e4m3_umma(s, dd, A, W, bias, Ybf16, nullptr, Yf32, a_scale_device); },
+                   [&] { return launch_gemm_e4m3_simt(s, dd, A, W, bias, Ybf16, nullptr, Yf32, a_scale_device); });
+}
+
 } // extern "C"

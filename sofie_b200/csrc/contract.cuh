@@ -18,9 +18,9 @@ int launch_qgemm_simt(cudaStream_t, const sofie_qgemm_desc &, const uint8_t *, c
 int launch_qgemm_umma(cudaStream_t, const sofie_qgemm_desc &, const uint8_t *, const int8_t *, const float *,
                       const int32_t *, uint8_t *, float *Yf32, float dq_scale);
 int launch_gemm_e4m3_simt(cudaStream_t, const sofie_fp8_gemm_desc &, const uint8_t *, const uint8_t *, const float *,
-                          uint16_t *, uint8_t *, float *Yf32);
+                          uint16_t *, uint8_t *, float *Yf32, const float *a_scale_dev = nullptr);
 int launch_gemm_e4m3_umma(cudaStream_t, const sofie_fp8_gemm_desc &, const uint8_t *, const uint8_t *, const float *,
-                          uint16_t *, uint8_t *, float *Yf32);
+                          uint16_t *, uint8_t *, float *Yf32, const float *a_scale_dev = nullptr);
 int launch_conv2d_f32_simt(cudaStream_t, const ConvGeom &, const float *, const float *, const float *, float *);
 int launch_conv2d_f32_umma(cudaStream_t, const ConvGeom &, const float *, const float *, const float *, float *);
 int launch_qconv2d_simt(cudaStream_t, const ConvGeom &, const uint8_t *, const int8_t *, const float *, const int32_t *,

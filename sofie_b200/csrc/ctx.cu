@@ -90,8 +90,10 @@ struct sofie_cuda_ctx {
    char *arena = nullptr;
    size_t arena_bytes = 0;
    std::vector<void *> owned;
-   void *staging = nullptr; // pinned
+   void *staging = nullptr; // pinned: kStagingSlots slots of kStagingSlot bytes, used as a ring
    size_t staging_bytes = 0;
+   cudaEvent_t staging_event[4] = {}; // the copy out of (h2d) or into (d2h) a slot has completed
+   bool staging_busy[4] = {};         // a copy that read the slot may still be in flight
    void *result = nullptr;  // pinned, grown on demand: where sofie_cuda_ctx_fetch lands device results
    size_t result_bytes = 0;
    cudaGraph_t graph = nullptr;
@@ -140,7 +142,11 @@ struct DeviceGuard {
       if (prev >= 0) cudaSetDevice(prev);
    }
 };
-constexpr size_t kStagingBytes = size_t(64) << 20;
+// Pageable host memory crosses PCIe through pinned staging slots: while the copy engine drains one slot the CPU fills
+// the next, so the host memcpy and the DMA overlap instead of alternating.
+constexpr int kStagingSlots = 4;
+constexpr size_t kStagingSlot = size_t(8) << 20;
+constexpr size_t kStagingBytes = kStagingSlots * kStagingSlot;
 } // namespace
 
 extern "C" {
@@ -245,6 +251,8 @@ int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx)
    splitk_scratch_release(ctx->device, ctx->stream);
    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
    if (ctx->status) cudaFreeHost(ctx->status);
+   for (cudaEvent_t e : ctx->staging_event)
+      if (e) cudaEventDestroy(e);
    for (cudaEvent_t e : ctx->marks)
       if (e) cudaEventDestroy(e);
    for (cudaEvent_t e : ctx->part_event)
@@ -312,6 +320,7 @@ static int ensure_staging(sofie_cuda_ctx *ctx)
    if (ctx->staging) return SOFIE_CUDA_OK;
    SOFIE_CUDA_TRY(cudaMallocHost(&ctx->staging, kStagingBytes));
    ctx->staging_bytes = kStagingBytes;
+   for (auto &e : ctx->staging_event) SOFIE_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
    return SOFIE_CUDA_OK;
 }
 
@@ -339,13 +348,16 @@ int sofie_cuda_ctx_h2d(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t b
    int rc = ensure_staging(ctx);
    if (rc) return rc;
    size_t done = 0;
-   while (done < bytes) {
-      size_t chunk = bytes - done < ctx->staging_bytes ? bytes - done : ctx->staging_bytes;
-      // The staging buffer is reused: wait for the previous chunk's copy before overwriting it.
-      SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-      std::memcpy(ctx->staging, static_cast<const char *>(src) + done, chunk);
-      SOFIE_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(dst) + done, ctx->staging, chunk, cudaMemcpyHostToDevice,
-                                     ctx->stream));
+   bool used[kStagingSlots] = {};
+   for (int slot = 0; done < bytes; slot = (slot + 1) % kStagingSlots) {
+      const size_t chunk = bytes - done < kStagingSlot ? bytes - done : kStagingSlot;
+      char *stage = static_cast<char *>(ctx->staging) + (size_t)slot * kStagingSlot;
+      // a slot is refilled only after the copy that last read it has finished (also a copy of an earlier call)
+      if (used[slot] || ctx->staging_busy[slot]) SOFIE_CUDA_TRY(cudaEventSynchronize(ctx->staging_event[slot]));
+      std::memcpy(stage, static_cast<const char *>(src) + done, chunk);
+      SOFIE_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(dst) + done, stage, chunk, cudaMemcpyHostToDevice, ctx->stream));
+      SOFIE_CUDA_TRY(cudaEventRecord(ctx->staging_event[slot], ctx->stream));
+      used[slot] = ctx->staging_busy[slot] = true;
       done += chunk;
    }
    return SOFIE_CUDA_OK;
@@ -394,14 +406,27 @@ int sofie_cuda_ctx_d2h(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t b
    }
    int rc = ensure_staging(ctx);
    if (rc) return rc;
+   // every input copy that used the slots has to be over before results land in them
+   SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+   for (auto &b : ctx->staging_busy) b = false;
+   // the copies of all slots are queued first, then each is copied out as soon as it has arrived: the host memcpy of
+   // one slot overlaps the DMA into the next
    size_t done = 0;
    while (done < bytes) {
-      size_t chunk = bytes - done < ctx->staging_bytes ? bytes - done : ctx->staging_bytes;
-      SOFIE_CUDA_TRY(cudaMemcpyAsync(ctx->staging, static_cast<const char *>(src) + done, chunk, cudaMemcpyDeviceToHost,
-                                     ctx->stream));
-      SOFIE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-      std::memcpy(static_cast<char *>(dst) + done, ctx->staging, chunk);
-      done += chunk;
+      const size_t round = bytes - done < kStagingBytes ? bytes - done : kStagingBytes;
+      int slots = 0;
+      for (size_t off = 0; off < round; off += kStagingSlot, slots++) {
+         const size_t chunk = round - off < kStagingSlot ? round - off : kStagingSlot;
+         SOFIE_CUDA_TRY(cudaMemcpyAsync(static_cast<char *>(ctx->staging) + off, static_cast<const char *>(src) + done + off, chunk,
+                                        cudaMemcpyDeviceToHost, ctx->stream));
+         SOFIE_CUDA_TRY(cudaEventRecord(ctx->staging_event[slots], ctx->stream));
+      }
+      for (int slot = 0; slot < slots; slot++) {
+         const size_t off = (size_t)slot * kStagingSlot, chunk = round - off < kStagingSlot ? round - off : kStagingSlot;
+         SOFIE_CUDA_TRY(cudaEventSynchronize(ctx->staging_event[slot]));
+         std::memcpy(static_cast<char *>(dst) + done + off, static_cast<char *>(ctx->staging) + off, chunk);
+      }
+      done += round;
    }
    return SOFIE_CUDA_OK;
 }

@@ -273,8 +273,10 @@ __device__ __forceinline__ uint8_t to_e4m3(float x)
 
 // Scalar forms: the tail of a tensor and unaligned tensors.
 template <typename In>
-__global__ void quantize_e4m3_kernel(const In *__restrict__ X, uint8_t *__restrict__ Y, size_t begin, size_t n, float scale)
+__global__ void quantize_e4m3_kernel(const In *__restrict__ X, uint8_t *__restrict__ Y, size_t begin, size_t n, float scale_in,
+                                     const float *__restrict__ scale_dev)
 {
+   const float scale = scale_dev ? *scale_dev : scale_in; // a scale computed on the device by an earlier kernel of the stream
    for (size_t i = begin + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
       float x;
       if constexpr (sizeof(In) == 2) x = bf16_to_f32(X[i]);
@@ -285,8 +287,10 @@ __global__ void quantize_e4m3_kernel(const In *__restrict__ X, uint8_t *__restri
 
 // Eight elements per thread and step: 16- or 32-byte loads, one 8-byte store.
 template <typename In>
-__global__ void quantize_e4m3_vec8_kernel(const In *__restrict__ X, uint8_t *__restrict__ Y, size_t n8, float scale)
+__global__ void quantize_e4m3_vec8_kernel(const In *__restrict__ X, uint8_t *__restrict__ Y, size_t n8, float scale_in,
+                                          const float *__restrict__ scale_dev)
 {
+   const float scale = scale_dev ? *scale_dev : scale_in;
    const size_t nthreads = (size_t)gridDim.x * blockDim.x;
 #pragma unroll 2
    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += nthreads) {
@@ -354,23 +358,56 @@ __global__ void amax_f32_kernel(const float *__restrict__ X, size_t n, unsigned 
    if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
 }
 
+// max |x| of bfloat16 values (as float bit patterns, like amax_f32_kernel)
+__global__ void amax_bf16_kernel(const uint16_t *__restrict__ X, size_t n, unsigned *__restrict__ out)
+{
+   unsigned m = 0;
+   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+      unsigned u = ((unsigned)X[i] << 16) & 0x7FFFFFFFu;
+      if (u <= 0x7F800000u) m = max(m, u);
+   }
+   for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+   if ((threadIdx.x & 31) == 0 && m) atomicMax(out, m);
+}
+// scale = amax / 448 (the largest E4M3 value), 1 for an all-zero tensor: in place, one thread
+__global__ void e4m3_scale_from_amax_kernel(float *amax_to_scale)
+{
+   const float a = *amax_to_scale;
+   *amax_to_scale = a > 0.f ? __fdiv_rn(a, 448.f) : 1.f;
+}
+
 template <typename In>
-static int launch_quantize_e4m3(cudaStream_t s, const In *X, uint8_t *Y, size_t n, float scale)
+static int launch_quantize_e4m3(cudaStream_t s, const In *X, uint8_t *Y, size_t n, float scale, const float *scale_dev = nullptr)
 {
    size_t done = 0;
    if (aligned16(X) && (reinterpret_cast<uintptr_t>(Y) & 7) == 0 && n >= 8) {
       const size_t n8 = n / 8;
-      quantize_e4m3_vec8_kernel<In><<<grid_for(n8), kThreads, 0, s>>>(X, Y, n8, scale);
+      quantize_e4m3_vec8_kernel<In><<<grid_for(n8), kThreads, 0, s>>>(X, Y, n8, scale, scale_dev);
       SOFIE_LAUNCH_CHECK("quantize_e4m3_vec8_kernel");
       done = n8 * 8;
    }
    if (done < n) {
-      quantize_e4m3_kernel<In><<<grid_for(n - done), kThreads, 0, s>>>(X, Y, done, n, scale);
+      quantize_e4m3_kernel<In><<<grid_for(n - done), kThreads, 0, s>>>(X, Y, done, n, scale, scale_dev);
       SOFIE_LAUNCH_CHECK("quantize_e4m3_kernel");
    }
    return SOFIE_CUDA_OK;
 }
 
+// Dynamic per-tensor quantisation: scale = max|x| / 448 on the device, then the same rounding as the static form.
+template <typename In>
+static int dynamic_quantize_e4m3(cudaStream_t s, const In *X, uint8_t *Y, size_t n, float *scale_device)
+{
+   SOFIE_CUDA_TRY(cudaMemsetAsync(scale_device, 0, sizeof(float), s));
+   if (n) {
+      if constexpr (sizeof(In) == 2) amax_bf16_kernel<<<grid_for(n), kThreads, 0, s>>>(X, n, reinterpret_cast<unsigned *>(scale_device));
+      else amax_f32_kernel<<<grid_for(n), kThreads, 0, s>>>(X, n, reinterpret_cast<unsigned *>(scale_device));
+      SOFIE_LAUNCH_CHECK("amax kernel");
+   }
+   e4m3_scale_from_amax_kernel<<<1, 1, 0, s>>>(scale_device);
+   SOFIE_LAUNCH_CHECK("e4m3_scale_from_amax_kernel");
+   if (n == 0) return SOFIE_CUDA_OK;
+   return launch_quantize_e4m3<In>(s, X, Y, n, 1.f, scale_device);
+}
 } // namespace
 
 extern "C" {
@@ -518,6 +555,18 @@ int sofie_cuda_quantize_e4m3_bf16(void *stream, const uint16_t *X, uint8_t *Y, s
    SOFIE_REQUIRE(X && Y && scale > 0.f, "bad arguments");
    if (n == 0) return SOFIE_CUDA_OK;
    return launch_quantize_e4m3<uint16_t>(as_stream(stream), X, Y, n, scale);
+}
+int sofie_cuda_dynamic_quantize_e4m3_f32(void *stream, const float *X, uint8_t *Y, size_t n, float *scale_device)
+{
+   SOFIE_REQUIRE((X && Y) || n == 0, "NULL tensor");
+   SOFIE_REQUIRE(scale_device != nullptr, "NULL scale");
+   return dynamic_quantize_e4m3<float>(as_stream(stream), X, Y, n, scale_device);
+}
+int sofie_cuda_dynamic_quantize_e4m3_bf16(void *stream, const uint16_t *X, uint8_t *Y, size_t n, float *scale_device)
+{
+   SOFIE_REQUIRE((X && Y) || n == 0, "NULL tensor");
+   SOFIE_REQUIRE(scale_device != nullptr, "NULL scale");
+   return dynamic_quantize_e4m3<uint16_t>(as_stream(stream), X, Y, n, scale_device);
 }
 int sofie_cuda_cast_bf16_f32(void *stream, const uint16_t *X, float *Y, size_t n)
 {

@@ -327,7 +327,8 @@ __device__ __forceinline__ float e4m3_decode(unsigned v)
 
 __global__ void __launch_bounds__(256)
 gemm_e4m3_simt_kernel(sofie_fp8_gemm_desc d, const uint8_t *__restrict__ A, const uint8_t *__restrict__ W,
-                      const float *__restrict__ bias, uint16_t *__restrict__ Ybf16, uint8_t *__restrict__ Yq, float *__restrict__ Yf32)
+                      const float *__restrict__ bias, uint16_t *__restrict__ Ybf16, uint8_t *__restrict__ Yq, float *__restrict__ Yf32,
+                      const float *__restrict__ a_scale_dev)
 {
    constexpr int BM = 64, BN = 64, BK = 16;
    __shared__ float lut[256];
@@ -362,7 +363,7 @@ gemm_e4m3_simt_kernel(sofie_fp8_gemm_desc d, const uint8_t *__restrict__ A, cons
       }
       __syncthreads();
    }
-   const float scale = d.a_scale * d.w_scale;
+   const float scale = __fmul_rn(a_scale_dev ? *a_scale_dev : d.a_scale, d.w_scale);
 #pragma unroll
    for (int i = 0; i < 4; i++) {
       int gm = m0 + ty * 4 + i;
@@ -384,10 +385,10 @@ gemm_e4m3_simt_kernel(sofie_fp8_gemm_desc d, const uint8_t *__restrict__ A, cons
 }
 
 int launch_gemm_e4m3_simt(cudaStream_t s, const sofie_fp8_gemm_desc &d, const uint8_t *A, const uint8_t *W,
-                          const float *bias, uint16_t *Ybf16, uint8_t *Yq, float *Yf32)
+                          const float *bias, uint16_t *Ybf16, uint8_t *Yq, float *Yf32, const float *a_scale_dev)
 {
    dim3 grid(ceil_div(d.N, 64), ceil_div(d.M, 64));
-   gemm_e4m3_simt_kernel<<<grid, 256, 0, s>>>(d, A, W, bias, Ybf16, Yq, Yf32);
+   gemm_e4m3_simt_kernel<<<grid, 256, 0, s>>>(d, A, W, bias, Ybf16, Yq, Yf32, a_scale_dev);
    SOFIE_LAUNCH_CHECK("gemm_e4m3_simt_kernel");
    set_last_engine(SOFIE_ENGINE_SIMT);
    return SOFIE_CUDA_OK;

@@ -74,6 +74,8 @@ struct GemmEpilogue {
    uint8_t *Yu8;
    // kF8
    float scale, q_scale, q_inv; // q_inv = 1 / q_scale rounded to fp32
+   const float *a_scale_dev;    // kF8: the activation scale lies in device memory (dynamic quantisation); scale = *a_scale_dev * w_scale
+   float w_scale;
    const float *bias;
    uint16_t *Ybf16;
    uint8_t *Yq;
@@ -201,6 +203,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const ui
       // y = acc * scale (+ bias) (Relu) -> bf16 (round to nearest even) -> optional E4M3 of bf16(y) / q_scale.
       // Both conversions use the paired hardware instructions (two values per instruction).
       uint32_t hb[16], qb[8];
+      const float scale = ep.a_scale_dev ? __fmul_rn(__ldg(ep.a_scale_dev), ep.w_scale) : ep.scale;
 #pragma unroll
       for (int j4 = 0; j4 < 8; j4++) {
          const float4 c = cf4[j4];
@@ -208,7 +211,7 @@ __device__ __forceinline__ void store_row_chunk(const GemmEpilogue &ep, const ui
          float yv[4];
 #pragma unroll
          for (int t = 0; t < 4; t++) {
-            float y = __fmul_rn(__uint_as_float(r[4 * j4 + t]), ep.scale);
+            float y = __fmul_rn(__uint_as_float(r[4 * j4 + t]), scale);
             if (ep.bias) y = __fadd_rn(y, cc[t]);
             yv[t] = ep.relu ? relu_ref(y) : y;
          }
@@ -802,10 +805,12 @@ int launch_qgemm_umma(cudaStream_t s, const sofie_qgemm_desc &d, const uint8_t *
 }
 
 int launch_gemm_e4m3_umma(cudaStream_t s, const sofie_fp8_gemm_desc &d, const uint8_t *A, const uint8_t *W,
-                          const float *bias, uint16_t *Ybf16, uint8_t *Yq, float *Yf32)
+                          const float *bias, uint16_t *Ybf16, uint8_t *Yq, float *Yf32, const float *a_scale_dev)
 {
    umma::GemmEpilogue ep = {};
    ep.scale = d.a_scale * d.w_scale;
+   ep.a_scale_dev = a_scale_dev;
+   ep.w_scale = d.w_scale;
    ep.q_scale = d.q_scale;
    ep.q_inv = d.q_scale != 0.f ? (float)(1.0 / (double)d.q_scale) : 0.f;
    ep.bias = bias;

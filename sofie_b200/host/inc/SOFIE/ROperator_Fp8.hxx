@@ -6,7 +6,11 @@
 //                  out_scale > 0 the output is the E4M3 quantisation of that bfloat16 value for the
 //                  next layer (what a following QuantizeLinear would compute), else bfloat16
 //   Cast           bfloat16 <-> float
-// W_q is an initialiser of type FLOAT8E4M3FN stored [N, K]; scales are static attributes.
+// W_q is an initialiser of type FLOAT8E4M3FN stored [N, K]; scales are static attributes, or -- "scales computed from
+// amax" at run time -- come from
+//   DynamicQuantizeE4M3 (custom operator)  X -> (Y = e4m3(x / scale), scale = max|x| / 448 as a one-element float tensor)
+// whose second output is the fourth input of the Fp8Gemm that reads Y; such an Fp8Gemm writes bfloat16 (the next layer's
+// scale is not known before the product is complete) and the next DynamicQuantizeE4M3 quantises it.
 #ifndef SOFIE_ROPERATOR_FP8
 #define SOFIE_ROPERATOR_FP8
 
@@ -60,6 +64,42 @@ public:
    }
 };
 
+class ROperator_DynamicQuantizeE4M3 final : public ROperator {
+   std::string fNX, fNY, fNScale;
+   std::vector<size_t> fShape;
+   ETensorType fInType = ETensorType::FLOAT;
+
+public:
+   ROperator_DynamicQuantizeE4M3(std::string nameX, std::string nameY, std::string nameScale)
+      : fNX(UTILITY::Clean_name(nameX)), fNY(UTILITY::Clean_name(nameY)), fNScale(UTILITY::Clean_name(nameScale))
+   {
+      fInputTensorNames = {fNX};
+      fOutputTensorNames = {fNY, fNScale};
+   }
+   EOpKind Kind() const override { return EOpKind::Quantize; }
+   std::vector<ETensorType> TypeInference(std::vector<ETensorType>) override { return {ETensorType::FLOAT8E4M3FN, ETensorType::FLOAT}; }
+   std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override { return {input[0], {1}}; }
+   void Initialize(RModel &model) override
+   {
+      if (!model.CheckIfTensorAlreadyExist(fNX)) throw std::runtime_error("SOFIE DynamicQuantizeE4M3 Op Input Tensor " + fNX + " is not found in model");
+      fInType = model.GetTensorType(fNX);
+      if (fInType != ETensorType::FLOAT && fInType != ETensorType::BFLOAT16)
+         throw std::runtime_error("SOFIE DynamicQuantizeE4M3 Op: input must be float or bfloat16");
+      fShape = model.GetTensorShape(fNX);
+      model.AddIntermediateTensor(fNY, ETensorType::FLOAT8E4M3FN, fShape);
+      model.AddIntermediateTensor(fNScale, ETensorType::FLOAT, std::vector<size_t>{1});
+   }
+   std::string Generate(std::string OpName) override
+   {
+      std::stringstream out;
+      out << "\n" << SP << "//------ DynamicQuantizeE4M3 op_" << OpName << ": scale = max|x| / 448 on the device\n";
+      out << EMIT::Call(SP, std::string(fInType == ETensorType::FLOAT ? "sofie_cuda_dynamic_quantize_e4m3_f32" : "sofie_cuda_dynamic_quantize_e4m3_bf16") +
+                               "(fStream, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ", " + std::to_string(ConvertShapeToLength(fShape)) + ", " +
+                               EMIT::Dev(fNScale) + ")");
+      return out.str();
+   }
+};
+
 class ROperator_Cast final : public ROperator {
    std::string fNX, fNY;
    ETensorType fTo, fFrom = ETensorType::UNDEFINED;
@@ -103,14 +143,16 @@ class ROperator_Fp8Gemm final : public ROperator {
    bool fRelu;
    std::vector<size_t> fShapeA, fShapeW;
    std::string fNYFloat; // set when a Cast to float behind this layer is written by the same launch
+   std::string fNAScale; // run-time activation scale (second output of a DynamicQuantizeE4M3), empty for a static scale
 
 public:
    ROperator_Fp8Gemm(float aScale, float wScale, float outScale, bool relu, std::string nameA, std::string nameW, std::string nameB,
-                     std::string nameY)
+                     std::string nameY, std::string nameAScale = "")
       : fNA(UTILITY::Clean_name(nameA)), fNW(UTILITY::Clean_name(nameW)), fNB(UTILITY::Clean_name(nameB)), fNY(UTILITY::Clean_name(nameY)),
-        fAScale(aScale), fWScale(wScale), fOutScale(outScale), fRelu(relu)
+        fAScale(aScale), fWScale(wScale), fOutScale(outScale), fRelu(relu), fNAScale(nameAScale.empty() ? "" : UTILITY::Clean_name(nameAScale))
    {
       fInputTensorNames = {fNA};
+      if (!fNAScale.empty()) fInputTensorNames.push_back(fNAScale);
       fOutputTensorNames = {fNY};
    }
    EOpKind Kind() const override { return EOpKind::Fp8Gemm; }
@@ -136,6 +178,11 @@ public:
       if (!fNB.empty() && (!model.IsInitializedTensor(fNB) || model.GetTensorType(fNB) != ETensorType::FLOAT))
          throw std::runtime_error("SOFIE Fp8Gemm Op: bias " + fNB + " must be a float constant");
       if (!(fAScale > 0.f) || !(fWScale > 0.f) || fOutScale < 0.f) throw std::runtime_error("SOFIE Fp8Gemm Op: scales must be positive");
+      if (!fNAScale.empty()) {
+         if (!model.CheckIfTensorAlreadyExist(fNAScale) || model.GetTensorType(fNAScale) != ETensorType::FLOAT || ConvertShapeToLength(model.GetTensorShape(fNAScale)) != 1)
+            throw std::runtime_error("SOFIE Fp8Gemm Op: the run-time activation scale " + fNAScale + " must be a one-element float tensor");
+         if (fOutScale > 0.f) throw std::runtime_error("SOFIE Fp8Gemm Op: with a run-time activation scale the output is bfloat16 (out_scale must be 0)");
+      }
       fShapeA = model.GetTensorShape(fNA);
       fShapeW = model.GetTensorShape(fNW);
       if (fShapeA.size() != 2 || fShapeW.size() != 2 || fShapeA[1] != fShapeW[1])
@@ -159,7 +206,12 @@ public:
       out << SP << SP << "const sofie_fp8_gemm_desc d = {" << fShapeA[0] << ", " << fShapeW[0] << ", " << fShapeA[1] << ", "
           << EMIT::FloatLit(fAScale) << ", " << EMIT::FloatLit(fWScale) << ", " << (fRelu ? 1 : 0) << ", " << EMIT::FloatLit(fOutScale) << "};\n";
       const std::string bias = fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB);
-      if (!fNYFloat.empty()) {
+      if (!fNAScale.empty()) {
+         // activation scale from device memory, written by the DynamicQuantizeE4M3 in front of this layer
+         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3_dynamic(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNAScale) + ", " + EMIT::Dev(fNW) + ", " + bias +
+                                       ", " + (fNYFloat.empty() ? EMIT::Dev(fNY) : std::string("nullptr")) + ", " +
+                                       (fNYFloat.empty() ? std::string("nullptr") : EMIT::Dev(fNYFloat)) + ")");
+      } else if (!fNYFloat.empty()) {
          out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3_f32(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNW) + ", " + bias + ", " +
                                        EMIT::Dev(fNYFloat) + ")");
       } else {

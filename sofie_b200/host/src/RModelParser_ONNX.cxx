@@ -282,9 +282,19 @@ std::unique_ptr<ROperator> ParseFp8Gemm(RModelParser_ONNX &p, const onnx::NodePr
    if (n.input_size() < 2) throw std::runtime_error("SOFIE - Fp8Gemm needs A and W");
    float out_scale = attr_float(n, "out_scale", 0.f);
    p.RegisterTensorType(n.output(0), out_scale > 0.f ? ETensorType::FLOAT8E4M3FN : ETensorType::BFLOAT16);
+   // optional fourth input: the activation scale as a run-time tensor (second output of DynamicQuantizeE4M3)
    return std::unique_ptr<ROperator>(new ROperator_Fp8Gemm(attr_float(n, "a_scale", 1.f), attr_float(n, "w_scale", 1.f), out_scale,
                                                            attr_int(n, "relu", 0) != 0, n.input(0), n.input(1),
-                                                           n.input_size() > 2 ? n.input(2) : "", n.output(0)));
+                                                           n.input_size() > 2 ? n.input(2) : "", n.output(0), n.input_size() > 3 ? n.input(3) : ""));
+}
+
+std::unique_ptr<ROperator> ParseDynamicQuantizeE4M3(RModelParser_ONNX &p, const onnx::NodeProto &n)
+{
+   require_type(p, n.input(0), "DynamicQuantizeE4M3");
+   if (n.output_size() != 2) throw std::runtime_error("SOFIE - DynamicQuantizeE4M3 has two outputs: the E4M3 tensor and its scale");
+   p.RegisterTensorType(n.output(0), ETensorType::FLOAT8E4M3FN);
+   p.RegisterTensorType(n.output(1), ETensorType::FLOAT);
+   return std::unique_ptr<ROperator>(new ROperator_DynamicQuantizeE4M3(n.input(0), n.output(0), n.output(1)));
 }
 
 std::unique_ptr<ROperator> ParseDequantizeLinear(RModelParser_ONNX &p, const onnx::NodeProto &n)
@@ -378,6 +388,7 @@ RModelParser_ONNX::RModelParser_ONNX() noexcept : fOperatorsMapImpl(std::make_un
    RegisterOperator("BatchNormalization", ParseBatchNormalization);
    RegisterOperator("Cast", ParseCast);
    RegisterOperator("Fp8Gemm", ParseFp8Gemm);
+   RegisterOperator("DynamicQuantizeE4M3", ParseDynamicQuantizeE4M3);
    RegisterOperator("QuantizeLinear", ParseQuantizeLinear);
    RegisterOperator("DequantizeLinear", ParseDequantizeLinear);
    RegisterOperator("QLinearMatMul", ParseQLinearMatMul);

@@ -273,8 +273,9 @@ def model_to_onnx(m, fp8_scales=None, batch_param=None) -> bytes:
     w = m.weights
     used = set()
     fp8_layers = [L for L in m.layers if L["op"] == "Fp8Gemm"]
-    if fp8_layers and (fp8_scales is None or len(fp8_scales) != len(fp8_layers)):
-        raise ValueError("the FP8 chain needs one calibrated activation scale per Fp8Gemm layer")
+    fp8_dynamic = isinstance(fp8_scales, str) and fp8_scales == "dynamic"   # scales from amax at run time
+    if fp8_layers and not fp8_dynamic and (fp8_scales is None or len(fp8_scales) != len(fp8_layers)):
+        raise ValueError("the FP8 chain needs one calibrated activation scale per Fp8Gemm layer (or fp8_scales='dynamic')")
     fp8_i = 0
 
     def init(name, arr=None):
@@ -342,6 +343,20 @@ def model_to_onnx(m, fp8_scales=None, batch_param=None) -> bytes:
                                                           attr_ints("strides", L["strides"])]))
             if L.get("relu"):
                 nodes.append(node("Relu", [out], [L["Y"]]))
+        elif op == "Fp8Gemm" and fp8_dynamic:
+            # DynamicQuantizeE4M3 in front of every layer; the layer reads its scale as a fourth input and writes bfloat16
+            last = fp8_i + 1 == len(fp8_layers)
+            src, sc = L["A"] + "_q", L["A"] + "_scale"
+            prev = L["A"] if fp8_i == 0 else L["A"] + "_bf16"
+            nodes.append(node("DynamicQuantizeE4M3", [prev], [src, sc]))
+            wq = L["B"] + "_e4m3"
+            inits.append(tensor(wq, e4m3_bytes(w[L["B"]], L["w_scale"]), FLOAT8E4M3FN))
+            ins = [src, wq, init(L["C"]) if L.get("C") else "", sc]
+            out = L["Y"] + "_bf16"
+            nodes.append(node("Fp8Gemm", ins, [out], [attr_float("w_scale", L["w_scale"]), attr_int("relu", int(bool(L.get("relu"))))]))
+            if last:
+                nodes.append(node("Cast", [out], [L["Y"]], [attr_int("to", FLOAT)]))
+            fp8_i += 1
         elif op == "Fp8Gemm":
             a_scale = float(fp8_scales[fp8_i])
             last = fp8_i + 1 == len(fp8_layers)

@@ -345,3 +345,13 @@ def test_stacked_matmul_is_one_batched_gemm_call():
     with pytest.raises(RuntimeError, match="same leading dimensions"):
         generated.emit(onnx_wire.model("g", [onnx_wire.node("MatMul", ["a", "b"], ["y"])], [onnx_wire.value_info("a", 1, [2, 7, 5]), onnx_wire.value_info("b", 1, [3, 5, 4])],
                                        [onnx_wire.value_info("y", 1, [])], []), "stacked_mm_bad")
+
+
+def test_fp8_chain_with_run_time_scales_emits_the_dynamic_calls():
+    m, x = configs.gemm_chain_fp8(rows=128, width=256, layers=3)
+    text = generated.emit(onnx_wire.model_to_onnx(m, "dynamic"), "c4_dyn_emit", binary=True).read_text()
+    assert text.count("sofie_cuda_dynamic_quantize_e4m3_f32(") == 1 and text.count("sofie_cuda_dynamic_quantize_e4m3_bf16(") == 2
+    assert text.count("sofie_cuda_gemm_e4m3_dynamic(") == 3 and "sofie_cuda_gemm_e4m3(" not in text
+    # the scale is a device tensor handed from the quantiser to the product; the last product writes the floats itself
+    assert "sofie_cuda_gemm_e4m3_dynamic(fStream, &d, dev_x_q, dev_x_scale, dev_W0_e4m3, dev_b0, dev_y0_bf16, nullptr)" in text
+    assert re.search(r"sofie_cuda_gemm_e4m3_dynamic\(fStream, &d, dev_y1_q, dev_y1_scale, dev_W2_e4m3, dev_b2, nullptr, dev_y2\)", text)

@@ -196,3 +196,33 @@ def test_stacked_matmul_and_stacked_einsum_through_generated_session(cuda_device
     assert "sofie_cuda_gemm_f32_batched(" in hxx.read_text()
     s = generated.GeneratedSession(generated.compile_session(hxx, "stacked_einsum_run"), hxx.with_suffix(".dat"), ref.size)
     assert rel_err(s.infer([a, bt]), ref) <= 1e-5
+
+
+def test_fp8_chain_with_scales_from_amax_at_run_time(cuda_device):
+    """The FP8 chain with every activation scale computed on the device from the tensor's own max|x| (DynamicQuantizeE4M3 in front of each
+    layer, the layer reading the scale from device memory) against the oracle doing the same in float32; and the scale the device
+    computed for the input is bit for bit max|x| / 448."""
+    import ctypes as C
+    import torch
+    from sofie_b200 import capi
+    m, x = configs.gemm_chain_fp8(rows=512, width=1024)
+    ref = run_model.run(m, x, fp8_scales="dynamic")
+    s = generated.session_from_model(m, "c4_dynamic_scales", binary=True, fp8_scales="dynamic")
+    y = s.infer(x)
+    assert rel_err(y, ref.ravel()) <= 2e-2
+    # other data through the same Session: the scales follow the data (a static calibration would saturate here)
+    x2 = (x * 37.0).astype(np.float32)
+    assert rel_err(s.infer(x2), run_model.run(m, x2, fp8_scales="dynamic").ravel()) <= 2e-2
+    # the entry point alone: scale and codes against the oracle's quantiser
+    xd = torch.from_numpy(x).to(cuda_device)
+    q = torch.empty(x.shape, dtype=torch.uint8, device=cuda_device)
+    sc = torch.full((1,), -1.0, device=cuda_device)
+    capi.call("sofie_cuda_dynamic_quantize_e4m3_f32", None, C.c_void_p(xd.data_ptr()), C.c_void_p(q.data_ptr()), xd.numel(), C.c_void_p(sc.data_ptr()))
+    torch.cuda.synchronize()
+    scale = np.float32(np.abs(x).max()) / np.float32(448.0)
+    assert sc.cpu().numpy()[0].view(np.uint32) == np.float32(scale).view(np.uint32)
+    from oracle import cpu_oracle as o
+    assert np.array_equal(q.cpu().numpy(), o.quantize_e4m3(x, float(scale)))
+    z = torch.zeros(64, device=cuda_device)
+    capi.call("sofie_cuda_dynamic_quantize_e4m3_f32", None, C.c_void_p(z.data_ptr()), C.c_void_p(q.data_ptr()), 64, C.c_void_p(sc.data_ptr()))
+    assert float(sc.cpu()[0]) == 1.0                      # an all-zero tensor keeps a usable scale
