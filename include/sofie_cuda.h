@@ -58,8 +58,14 @@ int sofie_cuda_device_count(int *count);
  */
 typedef struct sofie_cuda_ctx sofie_cuda_ctx;
 
-/* device < 0: take the device from the environment variable SOFIE_CUDA_DEVICE, else device 0. */
+/* device < 0: the calling thread's default device when one is set (sofie_cuda_set_default_device), else the
+ * environment variable SOFIE_CUDA_DEVICE, else device 0. */
 int sofie_cuda_ctx_create(sofie_cuda_ctx **ctx, int device, size_t arena_bytes);
+/* Device of the contexts this THREAD creates with device < 0 -- which is how an emitted Session, whose constructor has no
+ * device argument (the reference's has none: src/SOFIE_core/src/RModel.cxx:876-884), is placed on a chosen GPU; a
+ * negative value returns to the environment variable. One Session per GPU, each constructed after this call, is the
+ * reference's one-Session-per-slot idiom (SOFIEHelpers.hxx:23-49) applied to devices. */
+int sofie_cuda_set_default_device(int device);
 int sofie_cuda_ctx_destroy(sofie_cuda_ctx *ctx);
 int sofie_cuda_ctx_stream(sofie_cuda_ctx *ctx, void **stream);
 int sofie_cuda_ctx_device(sofie_cuda_ctx *ctx, int *device);

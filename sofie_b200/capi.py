@@ -79,6 +79,7 @@ class Fp8GemmDesc(C.Structure):
 SIGNATURES = {
     "sofie_cuda_abi_version": [],
     "sofie_cuda_device_count": [C.POINTER(C.c_int)],
+    "sofie_cuda_set_default_device": [C.c_int],
     "sofie_cuda_ctx_create": [C.POINTER(vp), C.c_int, sz],
     "sofie_cuda_ctx_destroy": [vp],
     "sofie_cuda_ctx_stream": [vp, C.POINTER(vp)],

@@ -16,6 +16,7 @@ namespace sofie {
 
 static thread_local char g_last_error[512] = "";
 static thread_local int g_last_engine = SOFIE_ENGINE_NONE;
+static thread_local int g_default_device = -1; // device of contexts created with device < 0 on this thread (-1: environment)
 // Initial kernel-family choice from the environment (SOFIE_CUDA_ENGINE = 0, 1 or 2), for A/B runs.
 static int initial_engine()
 {
@@ -175,6 +176,12 @@ int sofie_cuda_set_engine(int engine)
    return SOFIE_CUDA_OK;
 }
 
+int sofie_cuda_set_default_device(int device)
+{
+   g_default_device = device < 0 ? -1 : device;
+   return SOFIE_CUDA_OK;
+}
+
 int sofie_cuda_device_count(int *count)
 {
    SOFIE_REQUIRE(count != nullptr, "count is NULL");
@@ -192,6 +199,7 @@ int sofie_cuda_ctx_create(sofie_cuda_ctx **out, int device, size_t arena_bytes)
 {
    SOFIE_REQUIRE(out != nullptr, "ctx output pointer is NULL");
    *out = nullptr;
+   if (device < 0 && g_default_device >= 0) device = g_default_device;
    if (device < 0) {
       const char *env = std::getenv("SOFIE_CUDA_DEVICE");
       device = env ? std::atoi(env) : 0;

@@ -331,3 +331,54 @@ def conv1d_model_onnx(batch=3, length=10, seed=11):
     g = ow.model("conv1d", nodes, [ow.value_info("x", ow.FLOAT, list(x.shape))], [ow.value_info("y", ow.FLOAT, [])],
                  [ow.tensor("w0", w0), ow.tensor("b0", b0), ow.tensor("w1", w1), ow.tensor("b1", b1)])
     return g, dict(w0=w0, b0=b0, w1=w1, b1=b1), x
+
+
+SHARDED_MAIN = r"""
+#include "{header}"
+#include "SOFIE/SOFIEHelpers.hxx"
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+// usage: prog <weights> <input file> <batch> <floats per sample> <device> [<device> ...]; prints one output value per line
+int main(int argc, char **argv)
+{{
+   if (argc < 6) return 2;
+   try {{
+      const long batch = std::atol(argv[3]), per = std::atol(argv[4]);
+      std::vector<int> devices;
+      for (int i = 5; i < argc; i++) devices.push_back(std::atoi(argv[i]));
+      SofieSharded<SOFIE_{name}::Session> net(argv[1], devices, (size_t)batch, (size_t)per);
+      std::vector<float> x(batch * per);
+      std::FILE *fp = std::fopen(argv[2], "rb");
+      if (!fp || std::fread(x.data(), sizeof(float), x.size(), fp) != x.size()) return 3;
+      std::fclose(fp);
+      std::vector<float> y = net.infer((size_t)batch, x.data());
+      std::vector<float> y7 = net.infer(7, x.data());                      // a batch smaller than the number of shards' worth
+      for (float v : y) std::printf("%.9g\\n", v);
+      std::printf("#\\n");
+      for (float v : y7) std::printf("%.9g\\n", v);
+      try {{ net.infer((size_t)batch + devices.size(), x.data()); return 5; }} catch (const std::runtime_error &) {{ }}
+   }} catch (const std::exception &e) {{
+      std::fprintf(stderr, "%s\\n", e.what());
+      return 4;
+   }}
+   return 0;
+}}
+"""
+
+
+def build_sharded_program(model, name):
+    """Emits `model` with a run-time batch parameter and builds a program that runs it through SofieSharded."""
+    import subprocess
+    from sofie_b200 import _build, generated, onnx_wire
+    hxx = generated.emit(onnx_wire.model_to_onnx(model, batch_param="bs"), name)
+    lib = _build.build()
+    src = hxx.with_name(name + "_sharded.cxx")
+    src.write_text(SHARDED_MAIN.format(header=hxx.name, name=name))
+    exe = hxx.with_name(name + "_sharded")
+    cmd = ["g++", "-std=c++17", "-O2", "-pthread", "-I", str(generated.ROOT / "include"), "-I", str(generated.HOST / "inc"),
+           "-I", str(hxx.parent), str(src), "-o", str(exe), "-L", str(lib.parent), "-lSOFIE_cuda", f"-Wl,-rpath,{lib.parent}"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compiling the sharded program failed:\n{r.stdout}")
+    return exe, hxx.with_suffix(".dat")

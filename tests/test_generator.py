@@ -355,3 +355,10 @@ def test_fp8_chain_with_run_time_scales_emits_the_dynamic_calls():
     # the scale is a device tensor handed from the quantiser to the product; the last product writes the floats itself
     assert "sofie_cuda_gemm_e4m3_dynamic(fStream, &d, dev_x_q, dev_x_scale, dev_W0_e4m3, dev_b0, dev_y0_bf16, nullptr)" in text
     assert re.search(r"sofie_cuda_gemm_e4m3_dynamic\(fStream, &d, dev_y1_q, dev_y1_scale, dev_W2_e4m3, dev_b2, nullptr, dev_y2\)", text)
+
+
+def test_sharded_helper_compiles_against_a_run_time_batch_session():
+    from helpers import build_sharded_program
+    m, _ = configs.cnn_i8(batch=8, with_input=False)
+    exe, dat = build_sharded_program(m, "c5_sharded")
+    assert exe.exists() and dat.exists()

@@ -226,3 +226,25 @@ def test_fp8_chain_with_scales_from_amax_at_run_time(cuda_device):
     z = torch.zeros(64, device=cuda_device)
     capi.call("sofie_cuda_dynamic_quantize_e4m3_f32", None, C.c_void_p(z.data_ptr()), C.c_void_p(q.data_ptr()), 64, C.c_void_p(sc.data_ptr()))
     assert float(sc.cpu()[0]) == 1.0                      # an all-zero tensor keeps a usable scale
+
+
+def test_batch_sharded_over_sessions_with_the_helper(cuda_device, tmp_path):
+    """SofieSharded: one batch cut into contiguous shards, one Session per shard (here three Sessions; on a box with several GPUs
+    each on its own device, on one GPU all on device 0), rows back in batch order, bit-identical to the whole batch on the oracle."""
+    import subprocess
+    import torch
+    from helpers import build_sharded_program
+    m, x = configs.cnn_i8(batch=50)
+    exe, dat = build_sharded_program(m, "c5_sharded")
+    xin = tmp_path / "x.f32"
+    x.tofile(xin)
+    ngpu = torch.cuda.device_count()
+    devices = [str(i % ngpu) for i in range(3)]
+    r = subprocess.run([str(exe), str(dat), str(xin), "50", str(64 * 64)] + devices, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    full, small = r.stdout.split("#")
+    y = np.array([float(v) for v in full.split()], np.float32)
+    y7 = np.array([float(v) for v in small.split()], np.float32)
+    ref = run_model.run(m, x).ravel()
+    assert np.array_equal(y.view(np.uint32), ref.view(np.uint32))
+    assert np.array_equal(y7.view(np.uint32), ref[:14].view(np.uint32))
