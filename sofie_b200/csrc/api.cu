@@ -61,7 +61,10 @@ int sofie_cuda_gemm_f32(void *stream, const sofie_gemm_f32_desc *d, const float 
    // few rows, few columns, long K: split K over the grid instead of running on two or three SMs
    if (forced_engine() != SOFIE_ENGINE_TCGEN05 && splitk_shape_ok(*d) && ceil_div(d->M, 128) < 32) {
       if (rowblock_shape_ok(*d, A, B)) return launch_gemm_f32_rowblock(s, *d, A, B, C, Y); // small batch: one launch, no scratch
-      return launch_gemm_f32_splitk_auto(s, *d, A, B, C, Y);
+      const int rc = launch_gemm_f32_splitk_auto(s, *d, A, B, C, Y);
+      // no scratch buffer to be had (every slot of the pool belongs to another live stream, or the first call on this
+      // stream came during a capture, where nothing can be allocated): the general kernels below take the shape too
+      if (rc != SOFIE_CUDA_ERR_NOMEM) return rc;
    }
    return dispatch([&] { return launch_gemm_f32_umma(s, *d, A, B, C, Y); },
                    [&] { return launch_gemm_f32_simt(s, *d, A, B, C, Y); });

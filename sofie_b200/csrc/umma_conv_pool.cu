@@ -96,6 +96,16 @@ struct PoolConvParams {
    uint8_t *Y;            // [N][H/2][W/2][Cout]
 };
 
+// Requantisation to a zero point of 0: q = clamp(rne(acc * mult), 0, 255) is ONE conversion with round-to-nearest-even and
+// saturation to the uint8 range (the lower bound 0 is also the Relu of a quantised value, so `relu` changes nothing here).
+// Same value as requant_u8(acc, mult, 0, relu), three instructions instead of seven.
+__device__ __forceinline__ uint32_t requant_u8_zp0(int acc, float mult)
+{
+   uint32_t q;
+   asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(__fmul_rn(__int2float_rn(acc), mult)));
+   return q;
+}
+
 // The epilogue of both kernels of this file: the sixteen epilogue warps form NBUF groups that take the tiles in turn,
 // group g draining TMEM buffer g (NBUF = 2: eight warps per group, two per lane quarter, BN / 2 channels each; NBUF = 4,
 // possible when a tile's four accumulators are 128 columns: four warps per group, one per lane quarter, all BN
@@ -142,10 +152,23 @@ __device__ __forceinline__ void pool_epilogue_warp(const PoolConvParams &p, cons
             tmem_ld_32x16(t_row + 2 * BN, b);
             tmem_ld_32x16(t_row + 3 * BN, c);
             tmem_ld_wait();
+            // four channels at a time: their multipliers (and biases) are one 16-byte shared load each (c0 is a multiple of 16)
+            const bool has_bias = p.qbias != nullptr, zp0 = p.y_zp == 0;
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-               const int m = __vimax3_s32((int)a[j], (int)b[j], (int)c[j]);
-               q[j] = requant_u8(m + s_qbias[c0 + j], s_mult[c0 + j], p.y_zp, p.relu);
+            for (int j4 = 0; j4 < 4; j4++) {
+               const float4 m4 = reinterpret_cast<const float4 *>(s_mult + c0)[j4];
+               const float mu[4] = {m4.x, m4.y, m4.z, m4.w};
+               int bi[4] = {0, 0, 0, 0};
+               if (has_bias) {
+                  const int4 b4 = reinterpret_cast<const int4 *>(s_qbias + c0)[j4];
+                  bi[0] = b4.x; bi[1] = b4.y; bi[2] = b4.z; bi[3] = b4.w;
+               }
+#pragma unroll
+               for (int t = 0; t < 4; t++) {
+                  const int j = 4 * j4 + t;
+                  const int m = __vimax3_s32((int)a[j], (int)b[j], (int)c[j]) + bi[t];
+                  q[j] = zp0 ? (int)requant_u8_zp0(m, mu[t]) : requant_u8(m, mu[t], p.y_zp, p.relu);
+               }
             }
          } else {
             // a negative multiplier reverses the order: requantise the four pixels, then take the maximum
@@ -189,8 +212,8 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
    __shared__ uint64_t full_bar[kPoolMaxStages], empty_bar[kPoolMaxStages], tmem_full[2], tmem_empty[2], w_full;
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
-   __shared__ float s_mult[64];
-   __shared__ int s_qbias[64];
+   __shared__ __align__(16) float s_mult[64];
+   __shared__ __align__(16) int s_qbias[64];
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    griddep_launch_dependents();
@@ -357,8 +380,8 @@ umma_qconv3x3_first_pool_kernel(const __grid_constant__ CUtensorMap tmX, const i
    __shared__ uint64_t raw_full[kFirstStages], raw_empty[kFirstStages], a_full[kFirstStages], a_empty[kFirstStages], tmem_full[4], tmem_empty[4];
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
-   __shared__ float s_mult[64];
-   __shared__ int s_qbias[64];
+   __shared__ __align__(16) float s_mult[64];
+   __shared__ __align__(16) int s_qbias[64];
 
    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
    griddep_launch_dependents();

@@ -354,12 +354,12 @@ int main(int argc, char **argv)
       std::fclose(fp);
       std::vector<float> y = net.infer((size_t)batch, x.data());
       std::vector<float> y7 = net.infer(7, x.data());                      // a batch smaller than the number of shards' worth
-      for (float v : y) std::printf("%.9g\\n", v);
-      std::printf("#\\n");
-      for (float v : y7) std::printf("%.9g\\n", v);
+      for (float v : y) std::printf("%.9g\n", v);
+      std::printf("#\n");
+      for (float v : y7) std::printf("%.9g\n", v);
       try {{ net.infer((size_t)batch + devices.size(), x.data()); return 5; }} catch (const std::runtime_error &) {{ }}
    }} catch (const std::exception &e) {{
-      std::fprintf(stderr, "%s\\n", e.what());
+      std::fprintf(stderr, "%s\n", e.what());
       return 4;
    }}
    return 0;

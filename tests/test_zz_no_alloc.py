@@ -44,6 +44,34 @@ def test_static_scratch_gemm_matches_regular_entry_point_twice(cuda_device):
         assert rel_err(y_static.cpu().numpy(), ref) <= 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,transB", [(37, 10, 4098, 1), (256, 16, 2048, 0), (101, 3, 1030, 0)])
+def test_static_scratch_gemm_other_staging_paths_and_no_allocation(M, N, K, transB, cuda_device):
+    """Weights stored [K,N], a K that is not a multiple of 4 and a row count that is not a multiple of 8 take the entry point's
+    other staging paths; and the property it is named for: once the first call on the device has looked up the array's
+    address, a call leaves the amount of free device memory exactly as it found it."""
+    capi.call("sofie_cuda_set_engine", 0)
+    rng = np.random.default_rng(M + K)
+    A = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).cuda()
+    Bh = rng.standard_normal((N, K) if transB else (K, N)).astype(np.float32)
+    B = torch.from_numpy(Bh).cuda()
+    Cb = torch.from_numpy(rng.standard_normal(N).astype(np.float32)).cuda()
+    d = capi.GemmF32Desc(M, N, K, 0, transB, 1.0, 1.0, 1, 0)
+    y = [torch.full((M, N), float("nan"), device="cuda") for _ in range(2)]
+    y_regular = torch.full((M, N), float("nan"), device="cuda")
+    _run("sofie_cuda_gemm_f32_splitk_static", d, A, B, Cb, y[0])      # may be the first call on this device: it takes the symbol's address
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    _run("sofie_cuda_gemm_f32_splitk_static", d, A, B, Cb, y[1])
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before                # nothing was allocated (or freed) by the call
+    _run("sofie_cuda_gemm_f32", d, A, B, Cb, y_regular)
+    torch.cuda.synchronize()
+    ref = o.gemm_f32(A.cpu().numpy(), Bh, Cb.cpu().numpy(), transB=transB)
+    for out in y:
+        assert rel_err(out.cpu().numpy(), y_regular.cpu().numpy()) <= 1e-5
+        assert rel_err(out.cpu().numpy(), ref) <= 1e-5
+
+
 def test_static_scratch_gemm_rejects_what_it_cannot_hold(cuda_device):
     lib = capi.load()
     x = torch.zeros(16, device="cuda")
