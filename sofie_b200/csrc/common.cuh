@@ -98,8 +98,15 @@ __device__ __forceinline__ int requant_u8(int acc, float mult, int y_zp, int rel
    // rounds it to the nearest integer, ties to even, in the adder (full rate) and leaves that integer in the low
    // mantissa bits; the float-to-int conversion instruction this replaces runs at a fraction of that rate.
    // Relu on a quantised value, max(q, y_zp), is the lower bound 0 before the zero point is added.
-   const float lo = relu ? 0.f : (float)(-y_zp), hi = (float)(255 - y_zp);
    float v = __fmul_rn(__int2float_rn(acc), mult);
+   if (y_zp == 0) {
+      // zero point 0: the clamp to [0, 255] (whose lower bound is also the Relu) and the rounding are ONE conversion with
+      // round-to-nearest-even and saturation to the uint8 range
+      uint32_t q;
+      asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(q) : "f"(v));
+      return (int)q;
+   }
+   const float lo = relu ? 0.f : (float)(-y_zp), hi = (float)(255 - y_zp);
    v = fminf(fmaxf(v, lo), hi);
    return __float_as_int(__fadd_rn(v, 12582912.f)) - 0x4B400000 + y_zp;
 }
