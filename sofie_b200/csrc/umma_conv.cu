@@ -40,9 +40,11 @@ struct ConvTiling {
 };
 
 constexpr int kConvMaxStages = 8;
-constexpr int kConvEpilogueWarps = 8;                          // warps 2..9
+constexpr int kConvEpilogueWarps = 8;                          // fp32: warps 2..9
+constexpr int kConvEpilogueWarpsI8 = 16;                       // int8: warps 2..17 (no converters; requantisation and pooling are the longer epilogue)
 constexpr int kConvConverterWarps = 8;                         // fp32 only: warps 10..17
-constexpr int kConvThreadsI8 = (2 + kConvEpilogueWarps) * 32;
+constexpr int kConvIssuerB = 2 + kConvEpilogueWarpsI8;           // int8: warp of the second MMA issuer
+constexpr int kConvThreadsI8 = (3 + kConvEpilogueWarpsI8) * 32;
 constexpr int kConvThreadsTF32 = (2 + kConvEpilogueWarps + kConvConverterWarps) * 32;
 
 // Walks the tiles start, start + step, ... of an (image groups x tile rows x tile columns) grid with
@@ -249,7 +251,7 @@ __device__ __forceinline__ void conv_tile_epilogue(const ConvEpilogue &ep, const
    }
 }
 
-template <int KIND, int BN, int CB, int TPS>
+template <int KIND, int BN, int CB, int TPS, bool RW>
 __global__ void __launch_bounds__(KIND == kTF32 ? kConvThreadsTF32 : kConvThreadsI8, 1)
 umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, ConvEpilogue ep,
                     ConvTiling tg, uint32_t *status)
@@ -258,18 +260,24 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
    constexpr int CBE = CB / ES;                         // channels per chunk
    constexpr int A_TILE = 128 * CB, B_TILE = BN * CB;
    constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
-   constexpr int SUB_BYTES = COPIES * (A_TILE + B_TILE); // one (tap, channel chunk): A and B tiles (+ lo copies)
+   // RW (int8 only): the packed weights of all nine taps stay in shared memory for the life of the CTA and a
+   // pipeline stage carries activations alone. Without it every tile fetches the weights again, which for
+   // small images (many tiles, few pixels each) is half of all the bytes the kernel moves.
+   static_assert(!RW || KIND == kI8, "resident weights: int8 only (the fp32 path would need their lo copies as well)");
+   constexpr int SUB_BYTES = RW ? A_TILE : COPIES * (A_TILE + B_TILE); // one (tap, channel chunk): A and B tiles (+ lo copies)
    // A pipeline stage holds TPS such sub-blocks (TPS = 3: the three taps of one kernel row), so the
    // fixed cost of a stage hand-over (barrier round trip, commit) is paid once per TPS taps.
-   // Back-to-back MMAs into the same accumulator serialise on the accumulator (about 130 cycles
-   // each, whatever N is), so the MMAs of a tile rotate over NACC accumulators, which the epilogue
-   // adds up. Two such sets of accumulators double-buffer the tiles.
-   constexpr int NACC = 256 / BN > 6 ? 6 : 256 / BN;
-   constexpr uint32_t TMEM_COLS = 512;
-   constexpr int EPI_WARPS = kConvEpilogueWarps;
+   // fp32: the three MMAs of a K step (lo x hi, hi x lo, hi x hi) rotate over NACC accumulators, which the
+   // epilogue adds up, and two such sets double-buffer the tiles. int8: one accumulator per tile and up to
+   // four tiles in flight, so a tile's trip through the epilogue and its barriers is hidden behind the MMAs
+   // of the next ones.
+   constexpr int NACC = KIND == kI8 ? 1 : (256 / BN > 6 ? 6 : 256 / BN);
+   constexpr int NBUF = KIND == kI8 ? 4 : 2;
+   constexpr uint32_t TMEM_COLS = KIND == kI8 ? NBUF * BN : 512;
+   constexpr int EPI_WARPS = KIND == kI8 ? kConvEpilogueWarpsI8 : kConvEpilogueWarps;
    extern __shared__ unsigned char smem_raw[];
    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-   __shared__ uint64_t full_bar[kConvMaxStages], conv_bar[kConvMaxStages], empty_bar[kConvMaxStages], tmem_full[2], tmem_empty[2];
+   __shared__ uint64_t full_bar[kConvMaxStages], conv_bar[kConvMaxStages], empty_bar[kConvMaxStages], tmem_full[NBUF], tmem_empty[NBUF], w_full;
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
    __shared__ float s_bias[128], s_mult[128]; // per output channel, zero / one beyond Cout
@@ -289,10 +297,12 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
    const int S = tg.stages;
    const int stages_per_tile = 9 * tg.chunks / TPS; // TPS > 1 only when chunks == 1
 
-   auto a_hi = [&](int s, int k) { return smem + (size_t)(s * TPS + k) * SUB_BYTES; };
-   auto b_hi = [&](int s, int k) { return smem + (size_t)(s * TPS + k) * SUB_BYTES + A_TILE; };
-   auto a_lo = [&](int s, int k) { return smem + (size_t)(s * TPS + k) * SUB_BYTES + A_TILE + B_TILE; };
-   auto b_lo = [&](int s, int k) { return smem + (size_t)(s * TPS + k) * SUB_BYTES + 2 * A_TILE + B_TILE; };
+   unsigned char *w_smem = smem;                                             // RW: 9 * chunks weight tiles
+   unsigned char *ring = smem + (RW ? (size_t)9 * tg.chunks * B_TILE : 0);
+   auto a_hi = [&](int s, int k) { return ring + (size_t)(s * TPS + k) * SUB_BYTES; };
+   auto b_hi = [&](int s, int k) { return ring + (size_t)(s * TPS + k) * SUB_BYTES + A_TILE; };
+   auto a_lo = [&](int s, int k) { return ring + (size_t)(s * TPS + k) * SUB_BYTES + A_TILE + B_TILE; };
+   auto b_lo = [&](int s, int k) { return ring + (size_t)(s * TPS + k) * SUB_BYTES + 2 * A_TILE + B_TILE; };
 
    if (threadIdx.x == 0) {
       for (int s = 0; s < kConvMaxStages; s++) {
@@ -300,10 +310,11 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          mbar_init(&conv_bar[s], kConvConverterWarps * 32);
          mbar_init(&empty_bar[s], 1);
       }
-      for (int b = 0; b < 2; b++) {
+      for (int b = 0; b < NBUF; b++) {
          mbar_init(&tmem_full[b], 1);
          mbar_init(&tmem_empty[b], EPI_WARPS);
       }
+      mbar_init(&w_full, 1);
       abort_flag = 0;
       fence_mbar_init();
       prefetch_tensormap(&tmX);
@@ -324,7 +335,16 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       // Issuing a tensor copy costs the issuing thread a few hundred cycles, so the 2 x TPS copies of
       // a stage are issued by 2 x TPS lanes in parallel; lane 0 waits for the free slot and posts the
       // expected byte count (the phase cannot complete before that arrive, whatever the order).
-      griddep_wait(); // the activations (and, in this variant, every stage) come after the previous kernel
+      if constexpr (RW) {
+         // the weights are constants: fetched before the previous kernel's output is waited for
+         if (lane == 0) mbar_expect_tx(&w_full, (uint32_t)(9 * tg.chunks * B_TILE));
+         __syncwarp();
+         for (int item = lane; item < 9 * tg.chunks; item += 32) {
+            const int tap = item / tg.chunks, ch = item - tap * tg.chunks;
+            tma_load_2d(w_smem + (size_t)item * B_TILE, &tmW, tap * tg.C + ch * CBE, 0, &w_full);
+         }
+      }
+      griddep_wait(); // the activations come after the previous kernel
       int g = 0, s = 0; // stage counter, continuous over the tiles of this CTA, and its ring slot
       uint32_t ph = 0;
       bool ok = true;
@@ -335,33 +355,44 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          for (int st = 0; st < stages_per_tile; st++, g++, ring_next(s, ph, S)) {
             if (lane == 0) {
                ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
-               if (ok) mbar_expect_tx(&full_bar[s], TPS * (A_TILE + B_TILE));
+               if (ok) mbar_expect_tx(&full_bar[s], TPS * (RW ? A_TILE : A_TILE + B_TILE));
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
-            if (lane < 2 * TPS) {
-               const int k = lane >> 1;
+            if (RW ? lane < TPS : lane < 2 * TPS) {
+               const int k = RW ? lane : lane >> 1;
                const int item = st * TPS + k;
                const int tap = tg.chunks == 1 ? item : item / tg.chunks, ch = tg.chunks == 1 ? 0 : item % tg.chunks;
                const int r = tap / 3, sx = tap - 3 * r;
                // x coordinate (channels) is a multiple of CBE, i.e. of 16 bytes; the spatial
                // coordinates may be -1 or reach H / W: those elements read as zero
-               if (lane & 1) tma_load_2d(b_hi(s, k), &tmW, tap * tg.C + ch * CBE, 0, &full_bar[s]);
+               if (!RW && (lane & 1)) tma_load_2d(b_hi(s, k), &tmW, tap * tg.C + ch * CBE, 0, &full_bar[s]);
                else tma_load_4d(a_hi(s, k), &tmX, ch * CBE, w0 + sx - 1, h0 + r - 1, n0, &full_bar[s]);
             }
             __syncwarp();
          }
       }
-   } else if (warp == 1) {
-      // ---------------- MMA issuer ----------------
+   } else if (warp == 1 || (KIND == kI8 && warp == kConvIssuerB)) {
+      // ---------------- MMA issuers ----------------
+      // int8: two threads of different warps take the tiles alternately (an MMA costs the thread that issues
+      // it more clocks than it occupies the tensor pipe); fp32: one thread.
+      const int issuer = warp == 1 ? 0 : 1;
       if (lane == 0) {
          constexpr uint32_t idesc = make_idesc<KIND>(128, BN);
          int g = 0, lt = 0, s = 0;
          uint32_t ph = 0;
          bool ok = true;
+         if constexpr (RW) ok = SOFIE_PROF_WAIT(mbar_wait(&w_full, 0, &abort_flag, status, kStatusWaitFull, 0x4000));
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, lt++) {
-            const int buf = lt & 1;
-            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt))) break;
+            const int buf = lt & (NBUF - 1);
+            if (KIND == kI8 && (lt & 1) != issuer) {
+               // the other issuer's tile: step over its stages, still seeing each of them become ready (a parity
+               // wait tells only the last two phases of a barrier apart, so no phase of a shared slot is skipped)
+               for (int st = 0; st < stages_per_tile && ok; st++, g++, ring_next(s, ph, S))
+                  ok = SOFIE_PROF_WAIT(mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
+               continue;
+            }
+            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((lt / NBUF) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt))) break;
             tc_fence_after();
             const uint32_t d_base = tmem_base + (uint32_t)(buf * NACC * BN);
             int mma_idx = 0; // MMAs issued for this tile
@@ -373,7 +404,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 #pragma unroll
                for (int sub = 0; sub < TPS; sub++) {
                   const uint64_t da = make_smem_desc(smem_u32(a_hi(s, sub)), CB);
-                  const uint64_t db = make_smem_desc(smem_u32(b_hi(s, sub)), CB);
+                  const uint64_t db = make_smem_desc(smem_u32(RW ? w_smem + (size_t)(st * TPS + sub) * B_TILE : b_hi(s, sub)), CB);
 #pragma unroll
                   for (int k = 0; k < CB / 32; k++) {
                      const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K = 2 units of 16 bytes
@@ -398,7 +429,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
             if (ok) tc_commit(&tmem_full[buf]);
          }
       }
-   } else if (warp >= 2 + EPI_WARPS) {
+   } else if (KIND == kTF32 && warp >= 2 + EPI_WARPS) {
       // ---------------- converter warps (kTF32): hi/lo split of each stage ----------------
       if constexpr (KIND == kTF32) {
          constexpr int NT = kConvConverterWarps * 32;
@@ -442,9 +473,9 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
             }
          }
       }
-   } else {
-      // ---------------- epilogue warps 2..9 ----------------
-      // A warp reads the 32 TMEM lanes (pixels) its id modulo 4 selects; the two warps of a lane
+   } else if (warp < 2 + EPI_WARPS) {
+      // ---------------- epilogue warps, from warp 2 on ----------------
+      // A warp reads the 32 TMEM lanes (pixels) its id modulo 4 selects; the warps of a lane
       // quarter split the output channels.
       const int e = warp - 2;
       const int lane_base = (warp & 3) * 32;
@@ -454,9 +485,9 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
       tw.init(blockIdx.x, gridDim.x, tg.tilesH, tg.tilesW);
       int lt = 0;
       for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, lt++, tw.next()) {
-         const int buf = lt & 1;
+         const int buf = lt & (NBUF - 1);
          const int n0 = tw.n * tg.tileN, h0 = tw.th * tg.tileH, w0 = tw.tw * tg.tileW;
-         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
+         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt / NBUF) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
          tc_fence_after();
          conv_tile_epilogue<KIND, BN, NACC, EPI_WARPS>(ep, tg, s_bias, s_mult, s_qbias, pool_first, tmem_base, buf, e, lane_base, lane, nn, hh, ww, n0, h0, w0);
          // this warp is done with the TMEM buffer: the MMA warp may overwrite it
@@ -465,7 +496,7 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       }
    }
-   SOFIE_PROF_REPORT(warp == 0 ? "producer" : (warp == 1 ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
+   SOFIE_PROF_REPORT(warp == 0 ? "producer" : ((warp == 1 || (KIND == kI8 && warp == kConvIssuerB)) ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
    // A wait gives up only after about a second, long after every copy and MMA of this CTA landed.
    tc_fence_before();
    __syncthreads();
@@ -497,10 +528,13 @@ constexpr int kPatchTileH = 16, kPatchTileW = 8;
 constexpr int kPatchH = kPatchTileH + 2, kPatchW = kPatchTileW + 2;
 constexpr int kPlaneBox = kPatchH * kPatchW * 16;                 // bytes one plane copy delivers
 constexpr int kPlaneStride = (kPlaneBox + 127) / 128 * 128;       // TMA destinations are 128-byte aligned
-constexpr int kPatchMaxStages = 4;
+constexpr int kPatchMaxStages = 8;
 
-constexpr int kPatchThreads = 19 * 32; // producer, MMA issuer, 8 epilogue + 8 converter warps (fp32) or 16 epilogue warps (int8), second MMA issuer
-constexpr int kPatchIssuerB = 18;      // warp of the second issuer
+// warps: producer, MMA issuer, 8 epilogue + 8 converter warps (fp32) or 16 epilogue warps (int8), then the further
+// MMA issuers from warp 18 on: one for fp32, three for int8 (whose MMAs are shorter than one thread can issue them)
+constexpr int kPatchIssuerB = 18;
+template <int KIND> constexpr int kPatchIssuers = KIND == kI8 ? 4 : 2;
+template <int KIND> constexpr int kPatchThreads = (18 + kPatchIssuers<KIND> - 1) * 32;
 
 struct PatchPlan {
    int chunks;   // weight sub-tiles per tap (rows of cb bytes)
@@ -508,7 +542,7 @@ struct PatchPlan {
    int stages;   // pipeline slots
    uint32_t stage_bytes; // one copy (hi) of the planes of a stage
    uint32_t w_bytes;     // one copy (hi) of all weights
-   int issuers;          // 1 or 2 threads issuing the MMAs (2: tiles taken alternately)
+   int issuers;          // 1, 2 or (int8) 4 threads issuing the MMAs, taking the tiles in turn
    int conv_groups;      // fp32: 1 or 2 groups of converter warps (2: slots taken alternately)
 };
 
@@ -521,7 +555,7 @@ struct PatchPlan {
 // patch, the larger operand, is read once for two of the three products); a second MMA of width BN
 // adds lo(patch) x hi(weights). The two halves of the wide accumulator are added in the epilogue.
 template <int KIND, int BN, int KPS, int G>
-__global__ void __launch_bounds__(kPatchThreads, 1)
+__global__ void __launch_bounds__(kPatchThreads<KIND>, 1)
 umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, ConvEpilogue ep,
                           ConvTiling tg, PatchPlan pl, uint32_t *status)
 {
@@ -533,12 +567,16 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
    constexpr int CBK = KSTEPS * 32 >= 128 ? 128 : KSTEPS * 32; // bytes per weight row chunk (== pl.cb)
    constexpr int CHUNKS = KSTEPS * 32 / CBK;
    constexpr uint32_t B_TILE = BN * CBK;                     // one copy of a (tap, chunk) weight sub-tile
-   constexpr uint32_t TMEM_COLS = 2 * NACC * BN;             // two buffers: 64 ... 512 columns
+   // Accumulator buffers in tensor memory: as many tiles as fit in 512 columns, four at most. A tile's trip
+   // from its last MMA through the epilogue and back to the issuer is several barrier hand-overs long; with
+   // small tiles (few MMAs each) two buffers leave the tensor core waiting for that trip.
+   constexpr int NBUF = (512 / (NACC * BN)) >= 4 ? 4 : 2;
+   constexpr uint32_t TMEM_COLS = NBUF * NACC * BN;          // 128 ... 512 columns
    constexpr int EPI_WARPS = (KIND == kTF32) ? 8 : 16;
    constexpr int CONV_WARPS = 8;
    extern __shared__ unsigned char smem_raw[];
    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-   __shared__ uint64_t full_bar[kPatchMaxStages], conv_bar[kPatchMaxStages], empty_bar[kPatchMaxStages], tmem_full[2], tmem_empty[2];
+   __shared__ uint64_t full_bar[kPatchMaxStages], conv_bar[kPatchMaxStages], empty_bar[kPatchMaxStages], tmem_full[NBUF], tmem_empty[NBUF];
    __shared__ uint64_t w_full, w_conv;
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
@@ -567,7 +605,7 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          mbar_init(&conv_bar[s], CONV_WARPS * 32 / pl.conv_groups); // the converter threads that split one slot
          mbar_init(&empty_bar[s], 1);
       }
-      for (int b = 0; b < 2; b++) {
+      for (int b = 0; b < NBUF; b++) {
          mbar_init(&tmem_full[b], 1);
          mbar_init(&tmem_empty[b], EPI_WARPS);
       }
@@ -599,7 +637,9 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       }
       // everything above touched constants only; the activations are the previous kernel's output
       griddep_wait();
-      // patches: one box per plane, issued by as many lanes
+      // patches: one box per plane, issued by as many lanes. (A box of 16-byte rows costs the copy engine about
+      // as much per row as one of long rows -- some 1.5 clocks --, which bounds this role at int8; copying the
+      // pieces with cp.async from four warps instead was slower still: too few copies in flight.)
       int g = 0, s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -620,15 +660,15 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             __syncwarp();
          }
       }
-   } else if (warp == 1 || warp == kPatchIssuerB) {
+   } else if (warp == 1 || warp >= kPatchIssuerB) {
       // ---------------- MMA issuers ----------------
-      // Two threads of different warps take the tiles of this CTA alternately (issuer 0 the even
-      // ones into TMEM buffer 0, issuer 1 the odd ones into buffer 1): while one waits for its
-      // barriers and commits, the other keeps the tensor pipe fed, which a single thread cannot --
-      // issuing blocks it whenever the pipe's short queue is full, so its own hand-over work
-      // between two tiles leaves the pipe idle.
-      const int issuer = warp == 1 ? 0 : 1;
-      if (lane == 0) {
+      // Threads of different warps take the tiles of this CTA in turn (the accumulator buffers go round
+      // with the tile count): while one waits for its barriers and commits, the others keep the tensor
+      // pipe fed, which a single thread cannot -- an MMA costs the thread that issues it more clocks than
+      // it occupies the pipe, and its hand-over work between two tiles leaves the pipe idle.
+      const int issuer = warp == 1 ? 0 : warp - kPatchIssuerB + 1;
+      const int ni = pl.issuers < NBUF ? pl.issuers : NBUF; // a buffer is never shared by two issuers
+      if (lane == 0 && issuer < ni) {
          constexpr uint32_t idesc = make_idesc<KIND>(128, BN);
          constexpr uint32_t idesc_wide = make_idesc<KIND>(128, NACC * BN);
          bool ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&w_conv, 0, &abort_flag, status, kStatusWaitConv, 0x4000)
@@ -643,20 +683,18 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          int g = 0, lt = 0, s = 0;
          uint32_t ph = 0;
          for (int tile = blockIdx.x; tile < tg.num_tiles && ok; tile += gridDim.x, lt++) {
-            const int buf = lt & 1;
-            if (pl.issuers == 2 ? buf != issuer : issuer != 0) {
+            const int buf = lt & (NBUF - 1);
+            if ((lt & (ni - 1)) != issuer) {
                // The other issuer's tile: step over its stages of the ring, but still see each of them
                // become ready. A parity wait only tells the last two phases of a barrier apart, so a
                // thread that skipped a phase of a slot it shares with the other issuer could take an
                // old completion for the one it waits for.
-               if (pl.issuers == 2) {
-                  for (int grp = 0; grp < G && ok; grp++, g++, ring_next(s, ph, S))
-                     ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
-                                                          : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
-               }
+               for (int grp = 0; grp < G && ok; grp++, g++, ring_next(s, ph, S))
+                  ok = SOFIE_PROF_WAIT((KIND == kTF32) ? mbar_wait(&conv_bar[s], ph, &abort_flag, status, kStatusWaitConv, g)
+                                                       : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
                continue;
             }
-            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt))) break;
+            if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_empty[buf], ((lt / NBUF) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt))) break;
             const uint32_t d = tmem_base + (uint32_t)(buf * NACC * BN);
 #pragma unroll
             for (int grp = 0; grp < G; grp++, g++, ring_next(s, ph, S)) {
@@ -757,9 +795,9 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
       tw.init(blockIdx.x, gridDim.x, tg.tilesH, tg.tilesW);
       int lt = 0;
       for (int tile = blockIdx.x; tile < tg.num_tiles; tile += gridDim.x, lt++, tw.next()) {
-         const int buf = lt & 1;
+         const int buf = lt & (NBUF - 1);
          const int n0 = tw.n * tg.tileN, h0 = tw.th * tg.tileH, w0 = tw.tw * tg.tileW;
-         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt >> 1) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
+         if (!SOFIE_PROF_WAIT(mbar_wait(&tmem_full[buf], (lt / NBUF) & 1, &abort_flag, status, kStatusWaitAccum, 0x3000 + lt))) break;
          tc_fence_after();
          conv_tile_epilogue<KIND, BN, NACC, EPI_WARPS>(ep, tg, s_bias, s_mult, s_qbias, pool_first, tmem_base, buf, e, lane_base, lane, nn, hh, ww, n0, h0, w0);
          tc_fence_before();
@@ -767,7 +805,7 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          if (lane == 0) mbar_arrive(&tmem_empty[buf]);
       }
    }
-   SOFIE_PROF_REPORT(warp == 0 ? "producer" : ((warp == 1 || warp == kPatchIssuerB) ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
+   SOFIE_PROF_REPORT(warp == 0 ? "producer" : ((warp == 1 || warp >= kPatchIssuerB) ? "mma" : (warp < 2 + EPI_WARPS ? "epilogue" : "converter")));
    tc_fence_before();
    __syncthreads();
    if (warp == 1) {
@@ -790,9 +828,9 @@ static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, c
    pl.chunks = row_bytes / pl.cb;
    pl.w_bytes = (uint32_t)(9 * pl.chunks * BN * pl.cb);
    pl.stage_bytes = (uint32_t)(2 * KPS * kPlaneStride);
-   static const int issuers = [] { const char *e = getenv("SOFIE_CUDA_CONV_ISSUERS"); return e && atoi(e) == 1 ? 1 : 2; }();
+   static const int issuers = [] { const char *e = getenv("SOFIE_CUDA_CONV_ISSUERS"); const int v = e ? atoi(e) : 0; return v == 1 || v == 2 || v == 4 ? v : 4; }();
    static const int groups = [] { const char *e = getenv("SOFIE_CUDA_CONV_GROUPS"); return e && atoi(e) == 1 ? 1 : 2; }();
-   pl.issuers = issuers;
+   pl.issuers = issuers < kPatchIssuers<KIND> ? issuers : kPatchIssuers<KIND>;
    pl.conv_groups = groups;
    const long budget = 200 * 1024 - (long)COPIES * pl.w_bytes;
    const long per_stage = (long)COPIES * pl.stage_bytes;
@@ -825,7 +863,7 @@ static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, c
    const int grid = tg.num_tiles < kNumSMs ? tg.num_tiles : kNumSMs;
    auto kern = umma_conv3x3_patch_kernel<KIND, BN, KPS, G>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kPatchThreads), smem, s, tmX, tmW, ep, tg, pl, status));
+   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kPatchThreads<KIND>), smem, s, tmX, tmW, ep, tg, pl, status));
    SOFIE_LAUNCH_CHECK("umma_conv3x3_patch_kernel");
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;
@@ -863,17 +901,26 @@ static int try_launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *
 }
 
 // ------------------------------------------------------------------------------------------------
-template <int KIND, int BN, int CB, int TPS>
-static int launch_conv_tps(cudaStream_t s, const CUtensorMap &tmX, const CUtensorMap &tmW, const ConvEpilogue &ep, ConvTiling tg)
+// Weights resident in shared memory (int8, when the nine taps of all channel chunks take at most half
+// of it): SOFIE_CUDA_CONV_RESIDENT_W=0 keeps the streamed form (used to compare the two).
+static bool conv_resident_weights()
+{
+   static const bool on = [] { const char *e = getenv("SOFIE_CUDA_CONV_RESIDENT_W"); return !(e && atoi(e) == 0); }();
+   return on;
+}
+
+template <int KIND, int BN, int CB, int TPS, bool RW>
+static int launch_conv_tps_rw(cudaStream_t s, const CUtensorMap &tmX, const CUtensorMap &tmW, const ConvEpilogue &ep, ConvTiling tg)
 {
    constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
-   constexpr int STAGE_BYTES = TPS * COPIES * (128 + BN) * CB;
-   int stages = (200 * 1024) / STAGE_BYTES;
+   constexpr int STAGE_BYTES = RW ? TPS * 128 * CB : TPS * COPIES * (128 + BN) * CB;
+   const int w_bytes = RW ? 9 * tg.chunks * BN * CB : 0;
+   int stages = (200 * 1024 - w_bytes) / STAGE_BYTES;
    if (stages > kConvMaxStages) stages = kConvMaxStages;
    if (stages < 2) return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "convolution tile does not fit in shared memory");
    tg.stages = stages;
-   const int smem = stages * STAGE_BYTES + 1024;
-   auto kern = umma_conv3x3_kernel<KIND, BN, CB, TPS>;
+   const int smem = w_bytes + stages * STAGE_BYTES + 1024;
+   auto kern = umma_conv3x3_kernel<KIND, BN, CB, TPS, RW>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
    uint32_t *status = device_status_word(s);
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
@@ -882,6 +929,16 @@ static int launch_conv_tps(cudaStream_t s, const CUtensorMap &tmX, const CUtenso
    SOFIE_LAUNCH_CHECK("umma_conv3x3_kernel");
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;
+}
+
+template <int KIND, int BN, int CB, int TPS>
+static int launch_conv_tps(cudaStream_t s, const CUtensorMap &tmX, const CUtensorMap &tmW, const ConvEpilogue &ep, const ConvTiling &tg)
+{
+   if constexpr (KIND == kI8) {
+      if (conv_resident_weights() && 9 * tg.chunks * BN * CB <= 100 * 1024 && tg.num_tiles > kNumSMs)
+         return launch_conv_tps_rw<KIND, BN, CB, TPS, true>(s, tmX, tmW, ep, tg);
+   }
+   return launch_conv_tps_rw<KIND, BN, CB, TPS, false>(s, tmX, tmW, ep, tg);
 }
 
 template <int KIND, int BN, int CB>
