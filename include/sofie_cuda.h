@@ -324,6 +324,22 @@ static inline size_t sofie_mlp_smem_bytes(const sofie_mlp_desc *d)
    return floats * sizeof(float);
 }
 size_t sofie_cuda_mlp_f32_smem(const sofie_mlp_desc *desc); /* the same value, as an exported symbol */
+/* Chains that sofie_cuda_mlp_f32 can also run on the tensor cores (tcgen05, 3xTF32, 128 rows per CTA, activations
+ * handed from layer to layer through tensor memory and shared memory) when sofie_cuda_set_engine forces that engine:
+ * up to four layers, every layer's input width a multiple of 8 and at most 128, outputs at most 128 wide,
+ * intermediate widths multiples of 16. Not the default (it is slower than the FMA kernel on small batches and than one
+ * tensor-core GEMM per layer on large ones). Host arithmetic only. */
+static inline int sofie_mlp_tensor_core_shape(const sofie_mlp_desc *d)
+{
+   int32_t l;
+   if (d->layers < 1 || d->layers > 4) return 0;
+   for (l = 0; l < d->layers; l++) {
+      const int32_t k = d->dims[l], n = d->dims[l + 1];
+      if (k < 8 || k % 8 != 0 || k > 128 || n < 1 || n > 128) return 0;
+      if (l + 1 < d->layers && n % 16 != 0) return 0;
+   }
+   return 1;
+}
 
 /* Unary operators, y[i] = f(x[i]). The formulas are the ones the reference emits
  * (ROperator_Sigmoid.hxx:59, ROperator_Tanh.hxx:60, ROperator_LeakyRelu.hxx:73, ROperator_Selu.hxx:59,

@@ -16,6 +16,7 @@
 // tile of the next batch rows is fetched while the layers after the first run.
 // fp32 FMA throughout (K <= 256 per layer, accumulation in order of k).
 #include "common.cuh"
+#include "contract.cuh"
 
 namespace sofie {
 namespace {
@@ -300,10 +301,19 @@ extern "C" int sofie_cuda_mlp_f32(void *stream, const sofie_mlp_desc *d, const f
       return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "the fused MLP needs %zu bytes of shared memory for these layers (limit %d)", worst, SOFIE_MLP_MAX_SMEM);
    if (d->M == 0) return SOFIE_CUDA_OK;
    SOFIE_REQUIRE(X && Y, "NULL tensor");
+   cudaStream_t s = as_stream(stream);
+   // The tensor-core chain (umma_mlp.cu) runs when the caller forces that engine. It is not the default: measured on
+   // B200 for 64 -> 128 -> 128 -> 10 it takes 42 us at 1024 rows (this file's FMA kernel: 17 us, on 128 SMs instead of 8)
+   // and 311 us at 2^18 rows (one tensor-core GEMM launch per layer: 193 us) -- every CTA re-reads and re-splits all the
+   // weights for each 128-row slab, and those reads from L2 and their shared-memory writes, not the MMAs, set its time.
+   if (forced_engine() == SOFIE_ENGINE_TCGEN05) {
+      const int rc = launch_mlp_f32_umma(s, d, X, W, B, Y);
+      if (rc >= 0) return rc;
+      return fail(SOFIE_CUDA_ERR_UNSUPPORTED, "these layer widths are not served by the tensor-core chain");
+   }
    int rows = 32;
    while (rows > 8 && (d->M + rows - 1) / rows < kNumSMs) rows >>= 1;
    set_last_engine(SOFIE_ENGINE_SIMT);
-   cudaStream_t s = as_stream(stream);
    if (rows == 32) return launch_mlp<32>(s, p, floats, maxact, X, Y);
    if (rows == 16) return launch_mlp<16>(s, p, floats, maxact, X, Y);
    return launch_mlp<8>(s, p, floats, maxact, X, Y);

@@ -69,8 +69,20 @@ def _mlp_reference(x, Ws, Bs, relu, nk):
     (20000, (64, 128, 128, 10), (1, 1, 0), (1, 1, 1), (1, 1, 1)),     # several tiles per block: the input prefetch
     (5000, (32, 64, 32, 64, 32, 64, 32, 64, 8), (1, 0, 1, 0, 1, 0, 1, 1), (1, 0, 1, 0, 1, 0, 1, 0), (1,) * 8),  # eight layers, more tiles than SMs
     (96, (100, 33, 200), (1, 0), (0, 0), (0, 1)),
+    # widths the tensor-core chain takes: weights stored [K,N], a K that ends in a partial stage (40 = 32 + 8), four layers,
+    # a last slab of one row, an output narrower than its 16-column chunk, no bias
+    (300, (40, 48, 16), (1, 0), (0, 1), (1, 1)),
+    (129, (8, 16, 128, 32, 3), (1, 1, 0, 1), (1, 0, 1, 0), (0, 1, 0, 1)),
+    (1, (128, 128), (1,), (1,), (0,)),
+    (19000, (24, 112, 5), (1, 0), (1, 1), (1, 1)),                     # more slabs than SMs
 ])
-def test_mlp_f32_fused_chain(M, dims, relu, nk, bias):
+@pytest.mark.parametrize("engine", ["auto", "tcgen05"])
+def test_mlp_f32_fused_chain(M, dims, relu, nk, bias, engine):
+    tensor_shape = (len(dims) <= 5 and all(k % 8 == 0 and k <= 128 for k in dims[:-1]) and all(n <= 128 for n in dims[1:])
+                    and all(n % 16 == 0 for n in dims[1:-1]))
+    if engine == "tcgen05" and not tensor_shape:
+        pytest.skip("widths outside the tensor-core chain")
+    capi.call("sofie_cuda_set_engine", capi.ENGINE_TCGEN05 if engine == "tcgen05" else 0)
     rng = np.random.default_rng(M + len(dims))
     x = rng.standard_normal((M, dims[0])).astype(np.float32)
     Ws, Bs = [], []
@@ -79,7 +91,12 @@ def test_mlp_f32_fused_chain(M, dims, relu, nk, bias):
         Ws.append((rng.standard_normal((N, K) if nk[l] else (K, N)) / np.sqrt(K)).astype(np.float32))
         Bs.append(rng.standard_normal(N).astype(np.float32) if bias[l] else None)
     ref = _mlp_reference(x, Ws, Bs, relu, nk)
-    y = ops.mlp_f32(dev(x), [dev(W) for W in Ws], [None if b is None else dev(b) for b in Bs], relu, nk).cpu().numpy()
+    try:
+        y = ops.mlp_f32(dev(x), [dev(W) for W in Ws], [None if b is None else dev(b) for b in Bs], relu, nk).cpu().numpy()
+        used = ops.last_engine()
+    finally:
+        capi.call("sofie_cuda_set_engine", 0)
+    assert used == (capi.ENGINE_TCGEN05 if engine == "tcgen05" else capi.ENGINE_SIMT)
     assert y.shape == ref.shape and rel_err(y, ref) <= FP32_TOL
 
 
