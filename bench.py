@@ -18,7 +18,8 @@ path, and the job's throughput is the whole batch over the slowest rank's time: 
 With one GPU the line also carries `per_config` (C1..C5 at their BASELINE sizes) and `large_batch` (C3 at 2^18
 rows, C2 at 8192 images), each with value, e2e from pinned and from pageable memory, the dominant contraction's
 roofline fraction and -- where the CPU baseline leg ran -- the comparison of the GPU result with the CPU result
-on the baseline's sample.
+on the baseline's sample, and `hbm_ops`: the memory-bound operators of the path (Relu, Softmax, MaxPool, (de)quantise,
+layout change ...) called alone on tensors larger than L2, in GB/s against the measured copy bandwidth.
 
 `--impl reference` times the CPU side on the same workload: the reference's own emitted C++ (oracle/_ref,
 -O3 + OpenBLAS, all host threads) for the fp32 configurations C1/C2; for the quantised configurations, which
@@ -434,6 +435,50 @@ def memory_bound_ops(ops, model, pk):
     return out
 
 
+def standalone_hbm_ops(torch, pk, reps=5):
+    """Achieved GB/s of the memory-bound operators of the path, each called alone through the C ABI on tensors larger than
+    L2 (256-512 MB of traffic per call), CUDA events on the launching stream, median of `reps` after one warm-up call.
+    bytes = what the operator has to read plus what it has to write."""
+    from sofie_b200 import ops
+    dev = "cuda"
+    n = 1 << 26                                                   # 64 Mi elements: 256 MB of floats
+    x = torch.randn(n, device=dev)
+    y = torch.randn(n, device=dev)
+    img = x.view(1024, 16, 64, 64)
+    q = ops.quantize_u8(x, 0.02, 128)
+    cases = [
+        ("Relu (sofie_cuda_relu_f32)", lambda: ops.relu_f32(x), 8 * n),
+        ("Sigmoid (sofie_cuda_unary_f32)", lambda: ops.unary_f32(x, "Sigmoid"), 8 * n),
+        ("Add (sofie_cuda_binary_f32)", lambda: ops.binary_f32(x, y, "Add"), 12 * n),
+        ("Softmax over 1000 classes (sofie_cuda_softmax_f32)", lambda: ops.softmax_f32(x[: 65536 * 1000].view(65536, 1000)), 8 * 65536 * 1000),
+        ("Softmax over 10 classes (sofie_cuda_softmax_f32)", lambda: ops.softmax_f32(x[: (1 << 22) * 10].view(1 << 22, 10)), 8 * (1 << 22) * 10),
+        ("MaxPool 2x2 fp32 NCHW (sofie_cuda_pool2d_f32)", lambda: ops.pool2d_f32(img), 5 * n),
+        ("QuantizeLinear to uint8 (sofie_cuda_quantize_u8)", lambda: ops.quantize_u8(x, 0.02, 128), 5 * n),
+        ("DequantizeLinear from uint8 (sofie_cuda_dequantize_u8)", lambda: ops.dequantize_u8(q, 0.02, 128), 5 * n),
+        ("Quantize to E4M3 (sofie_cuda_quantize_e4m3_f32)", lambda: ops.quantize_e4m3(x, 0.01), 5 * n),
+        ("NCHW -> NHWC (sofie_cuda_nchw_to_nhwc)", lambda: ops.nchw_to_nhwc(img), 8 * n),
+    ]
+    out = []
+    for title, call, nbytes in cases:
+        try:
+            call()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(reps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                call()
+                e1.record()
+                e1.synchronize()
+                times.append(e0.elapsed_time(e1))
+            ms = float(np.median(times))
+            out.append(dict(kernel=title, bytes=int(nbytes), ms=round(ms, 4), gbs=round(nbytes / (ms * 1e-3) / 1e9, 1),
+                            frac=round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)))
+        except Exception as e:  # a kernel that refuses a shape must not take the line with it
+            out.append(dict(kernel=title, error=f"{type(e).__name__}: {e}"))
+    return out
+
+
 def side_config(workload, batch, steps, warmup, flush, pk, with_cpu, tag):
     """One entry of per_config / large_batch at one GPU."""
     t0 = time.time()
@@ -554,6 +599,9 @@ def run(args, rank, world, local_rank):
                     line["large_batch"][f"{w}@{b}"] = side_config(w, b, 5, 3, flush, pk, False, "_large")
                 except Exception as e:
                     line["large_batch"][f"{w}@{b}"] = dict(error=f"{type(e).__name__}: {e}")
+        if (not args.no_per_config and not args.batch) or args.hbm_ops:
+            torch.cuda.empty_cache()
+            line["hbm_ops"] = dict(peak_gbs=pk["hbm_gbs"], peak_basis=f"{pk['source']} copy bandwidth", ops=standalone_hbm_ops(torch, pk))
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -570,6 +618,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="C5", choices=sorted(WORKLOAD_DESC))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--hbm-ops", action="store_true", help="also time the stand-alone memory-bound operators (always on in the default run)")
     ap.add_argument("--no-per-config", action="store_true", help="only the headline workload (the other configurations are skipped)")
     ap.add_argument("--batch", type=int, default=None, help="another batch / row count than the configuration's (large-batch runs, ncu captures)")
     args = ap.parse_args()

@@ -83,6 +83,65 @@ __global__ void pool2d_f32_kernel(sofie_pool2d_desc d, int oH, int oW, const flo
    }
 }
 
+// The common window: 2 x 2, stride 2, no padding (what every configuration of this path pools with). NCHW: a thread
+// reads 16 bytes of two input rows and writes two outputs; NHWC: a thread reads four channels of the four pixels of a
+// window as 16-byte loads and writes 16 bytes. 32-bit index arithmetic (the launcher checks the sizes).
+template <bool AVG>
+__global__ void pool2x2_f32_nchw_kernel(const float *__restrict__ X, float *__restrict__ Y, unsigned planes_rows /* N*C*oH */, int W)
+{
+   const unsigned qw = (unsigned)W >> 2; // float4 per input row = pairs of outputs per output row
+   const unsigned total = planes_rows * qw;
+   for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+      const unsigned row = idx / qw, q = idx - row * qw;
+      const float4 a = __ldg(reinterpret_cast<const float4 *>(X + (size_t)row * 2 * W) + q);
+      const float4 b = __ldg(reinterpret_cast<const float4 *>(X + ((size_t)row * 2 + 1) * W) + q);
+      float2 o;
+      if (AVG) {
+         o.x = (((a.x + a.y) + b.x) + b.y) / 4.f; // the window's elements in the order the reference adds them
+         o.y = (((a.z + a.w) + b.z) + b.w) / 4.f;
+      } else {
+         o.x = -INFINITY;
+         if (a.x > o.x) o.x = a.x;
+         if (a.y > o.x) o.x = a.y;
+         if (b.x > o.x) o.x = b.x;
+         if (b.y > o.x) o.x = b.y;
+         o.y = -INFINITY;
+         if (a.z > o.y) o.y = a.z;
+         if (a.w > o.y) o.y = a.w;
+         if (b.z > o.y) o.y = b.z;
+         if (b.w > o.y) o.y = b.w;
+      }
+      reinterpret_cast<float2 *>(Y + (size_t)row * (W >> 1))[q] = o;
+   }
+}
+template <bool AVG>
+__global__ void pool2x2_f32_nhwc_kernel(const float *__restrict__ X, float *__restrict__ Y, unsigned rows /* N*oH */, int oW, int C)
+{
+   const unsigned c4 = (unsigned)C >> 2;
+   const unsigned total = rows * (unsigned)oW * c4;
+   for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+      const unsigned pix = idx / c4, c = idx - pix * c4;
+      const unsigned row = pix / (unsigned)oW, ow = pix - row * (unsigned)oW;
+      const float4 *p = reinterpret_cast<const float4 *>(X + ((size_t)row * 2 * (2 * oW) + 2 * ow) * C) + c;
+      const float4 v00 = __ldg(p), v01 = __ldg(p + c4), v10 = __ldg(p + (size_t)2 * oW * c4), v11 = __ldg(p + (size_t)2 * oW * c4 + c4);
+      float4 o;
+      auto one = [](float a, float b, float c, float d) {
+         if (AVG) return (((a + b) + c) + d) / 4.f;
+         float m = -INFINITY;
+         if (a > m) m = a;
+         if (b > m) m = b;
+         if (c > m) m = c;
+         if (d > m) m = d;
+         return m;
+      };
+      o.x = one(v00.x, v01.x, v10.x, v11.x);
+      o.y = one(v00.y, v01.y, v10.y, v11.y);
+      o.z = one(v00.z, v01.z, v10.z, v11.z);
+      o.w = one(v00.w, v01.w, v10.w, v11.w);
+      reinterpret_cast<float4 *>(Y + (size_t)pix * C)[c] = o;
+   }
+}
+
 template <bool NHWC>
 __global__ void maxpool2d_u8_kernel(int N, int C, int H, int W, int kH, int kW, int sh, int sw, int oH, int oW,
                                     const uint8_t *__restrict__ X, uint8_t *__restrict__ Y)
@@ -134,6 +193,101 @@ __global__ void softmax_rows_kernel(const float *__restrict__ X, float *__restri
       for (size_t i = lane; i < len; i += 32) y[i] = y[i] / sum;
    }
 }
+// inner == 1, rows of up to 32 * 4 * V4 values that are multiples of 4 long and 16-byte aligned: one warp per row, the
+// row read ONCE into registers (16-byte loads), written once.
+template <int V4>
+__global__ void softmax_rows_reg_kernel(const float *__restrict__ X, float *__restrict__ Y, size_t rows, int len4)
+{
+   const int lane = threadIdx.x & 31;
+   const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+   const size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+   for (size_t r = warp; r < rows; r += nwarps) {
+      const float4 *x = reinterpret_cast<const float4 *>(X) + r * len4;
+      float4 *y = reinterpret_cast<float4 *>(Y) + r * len4;
+      float4 v[V4];
+      float vmax = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < V4; i++) {
+         const int k = lane + 32 * i;
+         if (k < len4) {
+            v[i] = __ldg(x + k);
+            vmax = fmaxf(vmax, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+         }
+      }
+      for (int o = 16; o; o >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < V4; i++) {
+         if (lane + 32 * i < len4) {
+            v[i].x = expf(v[i].x - vmax);
+            v[i].y = expf(v[i].y - vmax);
+            v[i].z = expf(v[i].z - vmax);
+            v[i].w = expf(v[i].w - vmax);
+            sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+         }
+      }
+      for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+      for (int i = 0; i < V4; i++) {
+         const int k = lane + 32 * i;
+         if (k < len4) y[k] = make_float4(v[i].x / sum, v[i].y / sum, v[i].z / sum, v[i].w / sum);
+      }
+   }
+}
+// inner == 1, rows of at most 32 values (class scores): a block takes 256 consecutive rows, copies them into shared memory
+// with coalesced loads (row pitch padded to an odd number of words), one thread works on one row, and the block copies
+// the results out coalesced. No division in the copy loops: row and column advance incrementally.
+constexpr int kSoftmaxShortRows = 256, kSoftmaxShortMax = 32;
+__global__ void __launch_bounds__(kSoftmaxShortRows) softmax_rows_short_kernel(const float *__restrict__ X, float *__restrict__ Y, size_t rows, int len)
+{
+   __shared__ float s_v[kSoftmaxShortRows * (kSoftmaxShortMax + 1)];
+   const int pitch = len | 1;
+   const int t = threadIdx.x;
+   const int step_row = kSoftmaxShortRows / len, step_col = kSoftmaxShortRows - step_row * len;
+   for (size_t r0 = (size_t)blockIdx.x * kSoftmaxShortRows; r0 < rows; r0 += (size_t)gridDim.x * kSoftmaxShortRows) {
+      const int nrows = rows - r0 < (size_t)kSoftmaxShortRows ? (int)(rows - r0) : kSoftmaxShortRows;
+      const int total = nrows * len;
+      const float *x = X + r0 * len;
+      float *y = Y + r0 * len;
+      int row = t / len, col = t - row * len;
+      for (int i = t; i < total; i += kSoftmaxShortRows) {
+         s_v[row * pitch + col] = __ldg(x + i);
+         row += step_row;
+         col += step_col;
+         if (col >= len) {
+            col -= len;
+            row++;
+         }
+      }
+      __syncthreads();
+      if (t < nrows) {
+         float *v = s_v + t * pitch;
+         float vmax = -INFINITY;
+         for (int i = 0; i < len; i++) vmax = fmaxf(vmax, v[i]);
+         float sum = 0.f;
+         for (int i = 0; i < len; i++) {
+            const float e = expf(v[i] - vmax);
+            v[i] = e;
+            sum += e;
+         }
+         for (int i = 0; i < len; i++) v[i] = v[i] / sum;
+      }
+      __syncthreads();
+      row = t / len;
+      col = t - row * len;
+      for (int i = t; i < total; i += kSoftmaxShortRows) {
+         y[i] = s_v[row * pitch + col];
+         row += step_row;
+         col += step_col;
+         if (col >= len) {
+            col -= len;
+            row++;
+         }
+      }
+      __syncthreads();
+   }
+}
+
 // inner > 1: one thread per (outer, inner) line, strided walk; neighbouring threads touch
 // neighbouring addresses, so the accesses stay coalesced.
 __global__ void softmax_strided_kernel(const float *__restrict__ X, float *__restrict__ Y, size_t outer, size_t len,
@@ -176,6 +330,42 @@ __global__ void transpose_batched_kernel(const T *__restrict__ in, T *__restrict
       int c = c0 + j, r = r0 + threadIdx.x;
       if (r < rows && c < cols) dst[(size_t)c * rows + r] = tile[threadIdx.x][j];
    }
+}
+
+// NCHW <-> NHWC for float images with few channels (a multiple of 4, at most 64): a thread owns a pixel; its reads (NCHW
+// side) are coalesced across the warp plane by plane, its NHWC side is C contiguous floats moved as 16-byte words. The
+// tiled transpose above wastes half of each 32 x 32 tile when C = 16.
+template <bool TO_NHWC>
+__global__ void layout_few_channels_f32_kernel(const float *__restrict__ in, float *__restrict__ out, unsigned images, unsigned P, int C)
+{
+   const size_t total = (size_t)images * P;
+   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+      const size_t n = idx / P, p = idx - n * P;
+      if (TO_NHWC) {
+         const float *src = in + n * (size_t)C * P + p;
+         float4 *dst = reinterpret_cast<float4 *>(out + idx * C);
+         for (int c = 0; c < C; c += 4)
+            dst[c >> 2] = make_float4(__ldg(src + (size_t)c * P), __ldg(src + (size_t)(c + 1) * P), __ldg(src + (size_t)(c + 2) * P),
+                                      __ldg(src + (size_t)(c + 3) * P));
+      } else {
+         const float4 *src = reinterpret_cast<const float4 *>(in + idx * C);
+         float *dst = out + n * (size_t)C * P + p;
+         for (int c = 0; c < C; c += 4) {
+            const float4 v = __ldg(src + (c >> 2));
+            dst[(size_t)c * P] = v.x;
+            dst[(size_t)(c + 1) * P] = v.y;
+            dst[(size_t)(c + 2) * P] = v.z;
+            dst[(size_t)(c + 3) * P] = v.w;
+         }
+      }
+   }
+}
+template <bool TO_NHWC>
+static bool launch_layout_few_channels(cudaStream_t s, const float *in, float *out, int N, int C, int P)
+{
+   if (C % 4 != 0 || C > 64 || !aligned16(in) || !aligned16(out)) return false;
+   layout_few_channels_f32_kernel<TO_NHWC><<<grid_for((size_t)N * P), kThreads, 0, s>>>(in, out, (unsigned)N, (unsigned)P, C);
+   return true;
 }
 
 template <typename T>
@@ -443,7 +633,17 @@ int sofie_cuda_pool2d_f32(void *stream, const sofie_pool2d_desc *d, const float 
    size_t total = (size_t)d->N * d->C * oH * oW;
    if (total == 0) return SOFIE_CUDA_OK;
    cudaStream_t s = as_stream(stream);
-   if (d->layout == SOFIE_LAYOUT_NHWC)
+   const bool window2x2 = d->kH == 2 && d->kW == 2 && d->stride_h == 2 && d->stride_w == 2 && !d->pads[0] && !d->pads[1] && !d->pads[2] &&
+                          !d->pads[3] && d->H % 2 == 0 && d->W % 2 == 0 && aligned16(X) && aligned16(Y) && total < (1u << 31);
+   if (window2x2 && d->layout != SOFIE_LAYOUT_NHWC && d->W % 4 == 0) {
+      const unsigned rows = (unsigned)((size_t)d->N * d->C * oH);
+      if (d->mode == 0) pool2x2_f32_nchw_kernel<false><<<grid_for(total / 2), kThreads, 0, s>>>(X, Y, rows, d->W);
+      else pool2x2_f32_nchw_kernel<true><<<grid_for(total / 2), kThreads, 0, s>>>(X, Y, rows, d->W);
+   } else if (window2x2 && d->layout == SOFIE_LAYOUT_NHWC && d->C % 4 == 0) {
+      const unsigned rows = (unsigned)((size_t)d->N * oH);
+      if (d->mode == 0) pool2x2_f32_nhwc_kernel<false><<<grid_for(total / 4), kThreads, 0, s>>>(X, Y, rows, oW, d->C);
+      else pool2x2_f32_nhwc_kernel<true><<<grid_for(total / 4), kThreads, 0, s>>>(X, Y, rows, oW, d->C);
+   } else if (d->layout == SOFIE_LAYOUT_NHWC)
       pool2d_f32_kernel<true><<<grid_for(total), kThreads, 0, s>>>(*d, oH, oW, X, Y);
    else
       pool2d_f32_kernel<false><<<grid_for(total), kThreads, 0, s>>>(*d, oH, oW, X, Y);
@@ -474,7 +674,16 @@ int sofie_cuda_softmax_f32(void *stream, const float *X, float *Y, size_t outer,
    SOFIE_REQUIRE(axis_len > 0, "softmax along an axis with zero elements");
    if (outer == 0 || inner == 0) return SOFIE_CUDA_OK;
    cudaStream_t s = as_stream(stream);
-   if (inner == 1)
+   const bool vec = axis_len % 4 == 0 && aligned16(X) && aligned16(Y);
+   if (inner == 1 && axis_len <= (size_t)kSoftmaxShortMax)
+      softmax_rows_short_kernel<<<grid_for(outer), kSoftmaxShortRows, 0, s>>>(X, Y, outer, (int)axis_len);
+   else if (inner == 1 && vec && axis_len <= 32 * 4 * 2)
+      softmax_rows_reg_kernel<2><<<grid_for(outer * 32), kThreads, 0, s>>>(X, Y, outer, (int)(axis_len / 4));
+   else if (inner == 1 && vec && axis_len <= 32 * 4 * 8)
+      softmax_rows_reg_kernel<8><<<grid_for(outer * 32), kThreads, 0, s>>>(X, Y, outer, (int)(axis_len / 4));
+   else if (inner == 1 && vec && axis_len <= 32 * 4 * 16)
+      softmax_rows_reg_kernel<16><<<grid_for(outer * 32), kThreads, 0, s>>>(X, Y, outer, (int)(axis_len / 4));
+   else if (inner == 1)
       softmax_rows_kernel<<<grid_for(outer * 32), kThreads, 0, s>>>(X, Y, outer, axis_len);
    else
       softmax_strided_kernel<<<grid_for(outer * inner), kThreads, 0, s>>>(X, Y, outer, axis_len, inner);
@@ -495,11 +704,19 @@ int sofie_cuda_transpose_i8(void *stream, const int8_t *in, int8_t *out, int32_t
 int sofie_cuda_nchw_to_nhwc_f32(void *stream, const float *X, float *Y, int32_t N, int32_t C, int32_t H, int32_t W)
 {
    SOFIE_REQUIRE(X && Y && N >= 0 && C > 0 && H > 0 && W > 0, "bad layout-change arguments");
+   if (N > 0 && launch_layout_few_channels<true>(as_stream(stream), X, Y, N, C, H * W)) {
+      SOFIE_LAUNCH_CHECK("layout_few_channels_f32_kernel");
+      return SOFIE_CUDA_OK;
+   }
    return launch_transpose<float>(as_stream(stream), X, Y, N, C, H * W);
 }
 int sofie_cuda_nhwc_to_nchw_f32(void *stream, const float *X, float *Y, int32_t N, int32_t C, int32_t H, int32_t W)
 {
    SOFIE_REQUIRE(X && Y && N >= 0 && C > 0 && H > 0 && W > 0, "bad layout-change arguments");
+   if (N > 0 && launch_layout_few_channels<false>(as_stream(stream), X, Y, N, C, H * W)) {
+      SOFIE_LAUNCH_CHECK("layout_few_channels_f32_kernel");
+      return SOFIE_CUDA_OK;
+   }
    return launch_transpose<float>(as_stream(stream), X, Y, N, H * W, C);
 }
 int sofie_cuda_nchw_to_nhwc_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W)

@@ -244,12 +244,35 @@ def test_pool2d_f32(mode, k, s, pads, cip):
     assert rel_err(y2, ref) <= 1e-6
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("shape", [(3, 5, 8, 12), (2, 16, 64, 64), (1, 4, 2, 4), (2, 3, 6, 10)])
+def test_pool2d_f32_window_2x2_stride_2(mode, shape):
+    """The window every configuration pools with has kernels of its own (16-byte accesses) in both layouts; the last shape
+    (W not a multiple of 4, C not a multiple of 4) stays on the general kernel."""
+    X = np.random.default_rng(sum(shape)).standard_normal(shape).astype(np.float32)
+    X[0, 0, 0, 0] = np.nan                                           # a NaN never wins a maximum (v > m is false), as in the reference
+    ref = o.pool2d_f32(X, mode, (2, 2), (2, 2), (0, 0, 0, 0), 0)
+    y = ops.pool2d_f32(dev(X), mode=mode).cpu().numpy()
+    np.testing.assert_array_equal(y, ref)                            # exact; a NaN average is a NaN on both sides
+    y2 = ops.pool2d_f32(dev(X.transpose(0, 2, 3, 1)), mode=mode, layout=1, shape=X.shape).cpu().numpy().transpose(0, 3, 1, 2)
+    np.testing.assert_array_equal(y2, ref)
+
+
 @pytest.mark.parametrize("shape,axis", [((3,), 0), ((1, 3), 1), ((2, 3, 4), 1), ((2, 3, 4, 2), -2), ((64, 10), -1),
-                                        ((5, 1000), 1), ((4, 7, 33), 0)])
+                                        ((5, 1000), 1), ((4, 7, 33), 0),
+                                        ((1000, 10), 1), ((257, 32), 1), ((300, 1), 1),      # short rows: 256 rows per block, a ragged last block
+                                        ((9, 36), 1), ((70, 256), 1), ((33, 1024), 1), ((5, 2048), 1),  # rows kept in registers
+                                        ((3, 2052), 1), ((6, 1001), 1), ((4, 4096), 1)])     # longer or not a multiple of 4: re-read
 def test_softmax_f32(shape, axis):
     X = np.random.default_rng(1).standard_normal(shape).astype(np.float32) * 3
     y = ops.softmax_f32(dev(X), axis).cpu().numpy()
     assert np.abs(y - o.softmax_f32(X, axis)).max() <= 1e-6
+    # a view that starts 4 bytes into its buffer (not 16-byte aligned) takes the element-wise kernels
+    if len(shape) == 2 and axis == 1:
+        buf = torch.zeros(X.size + 1, device="cuda")
+        buf[1:] = dev(X).flatten()
+        y = ops.softmax_f32(buf[1:].view(shape), axis).cpu().numpy()
+        assert np.abs(y - o.softmax_f32(X, axis)).max() <= 1e-6
 
 
 def test_layout_round_trips():
@@ -257,6 +280,11 @@ def test_layout_round_trips():
     nhwc = ops.nchw_to_nhwc(dev(X))
     assert np.array_equal(nhwc.cpu().numpy(), X.transpose(0, 2, 3, 1))
     assert np.array_equal(ops.nhwc_to_nchw(nhwc).cpu().numpy(), X)
+    for shape in ((2, 4, 3, 5), (3, 16, 8, 8), (1, 64, 5, 7), (2, 68, 4, 4)):   # few channels, a multiple of 4: one thread per pixel
+        X = np.random.default_rng(4).standard_normal(shape).astype(np.float32)
+        nhwc = ops.nchw_to_nhwc(dev(X))
+        assert np.array_equal(nhwc.cpu().numpy(), X.transpose(0, 2, 3, 1))
+        assert np.array_equal(ops.nhwc_to_nchw(nhwc).cpu().numpy(), X)
     U = np.random.default_rng(2).integers(0, 256, (2, 33, 6, 5)).astype(np.uint8)
     assert np.array_equal(ops.nhwc_to_nchw(ops.nchw_to_nhwc(dev(U))).cpu().numpy(), U)
     Wm = np.random.default_rng(2).standard_normal((45, 70)).astype(np.float32)
