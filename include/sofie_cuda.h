@@ -249,6 +249,26 @@ typedef struct sofie_conv_transpose2d_desc {
 } sofie_conv_transpose2d_desc;
 int sofie_cuda_conv_transpose2d_f32(void *stream, const sofie_conv_transpose2d_desc *desc, const float *X, const float *W,
                                     const float *bias, float *Y);
+/* The same operator as the reference lowers it (ROperator_ConvTranspose.icc:364-474: filter GEMM, then col2im), with the
+ * GEMM on the tensor cores: the images are made channel-last, ONE product [N*H*W, C] x [C, kH*kW*Cout] covers all of
+ * them (sofie_cuda_gemm_f32), and every output pixel gathers its taps' products, adds the bias and applies Relu.
+ * `scratch` is device memory of sofie_conv_transpose2d_gemm_scratch_bytes(desc) bytes, 256-byte aligned, that the call
+ * overwrites (channel-last input, re-ordered filters, the products); 0 bytes = this shape is not served (fewer than 16
+ * input channels or a count that is not a multiple of 4: use sofie_cuda_conv_transpose2d_f32). Host arithmetic only, so
+ * that a code generator can plan the buffer without a GPU. */
+static inline size_t sofie_round_up_floats(size_t n) { return (n + 63) & ~(size_t)63; } /* 256-byte steps */
+static inline size_t sofie_conv_transpose2d_gemm_scratch_bytes(const sofie_conv_transpose2d_desc *d)
+{
+   size_t pixels, taps;
+   if (d->C < 16 || d->C % 4 != 0 || d->N < 1 || d->H < 1 || d->W < 1 || d->Cout < 1 || d->kH < 1 || d->kW < 1) return 0;
+   pixels = (size_t)d->N * (size_t)d->H * (size_t)d->W;
+   taps = (size_t)d->kH * (size_t)d->kW;
+   return 4 * (sofie_round_up_floats(pixels * (size_t)d->C) + sofie_round_up_floats(taps * (size_t)d->Cout * (size_t)d->C) +
+               sofie_round_up_floats(pixels * taps * (size_t)d->Cout));
+}
+size_t sofie_cuda_conv_transpose2d_f32_gemm_scratch(const sofie_conv_transpose2d_desc *desc); /* the same value, as an exported symbol */
+int sofie_cuda_conv_transpose2d_f32_gemm(void *stream, const sofie_conv_transpose2d_desc *desc, const float *X, const float *W,
+                                         const float *bias, float *Y, void *scratch, size_t scratch_bytes);
 
 /* Einsum of two operands, general form (reference: ROperator_Einsum.hxx:200-332, nested loops or one sgemm_ per
  * stack index): Y[out labels] = sum over all other labels of A[...] * B[...]. The labels are listed by extent, first

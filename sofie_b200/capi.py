@@ -113,6 +113,7 @@ SIGNATURES = {
     "sofie_cuda_conv2d_f32": [vp, C.POINTER(Conv2dDesc), vp, vp, vp, vp],
     "sofie_cuda_conv2d_pack_f32": [vp, C.POINTER(Conv2dDesc), vp, vp],
     "sofie_cuda_conv_transpose2d_f32": [vp, C.POINTER(ConvTranspose2dDesc), vp, vp, vp, vp],
+    "sofie_cuda_conv_transpose2d_f32_gemm": [vp, C.POINTER(ConvTranspose2dDesc), vp, vp, vp, vp, vp, C.c_size_t],
     "sofie_cuda_einsum_f32": [vp, C.POINTER(EinsumDesc), vp, vp, vp],
     "sofie_cuda_relu_f32": [vp, vp, vp, sz],
     "sofie_cuda_pool2d_f32": [vp, C.POINTER(Pool2dDesc), vp, vp],
@@ -146,7 +147,8 @@ SIGNATURES = {
     "sofie_cuda_gemm_e4m3_dynamic": [vp, C.POINTER(Fp8GemmDesc), vp, vp, vp, vp, vp, vp],
 }
 STRING_GETTERS = {"sofie_cuda_strerror": [C.c_int], "sofie_cuda_last_error": []}
-SIZE_GETTERS = {"sofie_cuda_mlp_f32_smem": [C.POINTER(MlpDesc)]}
+SIZE_GETTERS = {"sofie_cuda_mlp_f32_smem": [C.POINTER(MlpDesc)],
+                "sofie_cuda_conv_transpose2d_f32_gemm_scratch": [C.POINTER(ConvTranspose2dDesc)]}
 MLP_MAX_LAYERS, MLP_MAX_WIDTH, MLP_MAX_SMEM = 8, 256, 200 * 1024
 
 _lib = None

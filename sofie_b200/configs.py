@@ -188,15 +188,16 @@ def resblock_f32(batch=8, chans=16, hw=16, key="C2", with_input=True):
     return m, x
 
 
-def upsample_f32(batch=4, hw=12, key="C2", with_input=True):
+def upsample_f32(batch=4, hw=12, key="C2", with_input=True, channels=(8, 6)):
     """Decoder-style stack: Conv 3->8 + Relu; ConvTranspose 8->6, 2x2 stride 2; Relu; ConvTranspose 6->3, 3x3 stride 2 pad 1
-    output_padding 1, with bias; Tanh. Seeded like C2."""
+    output_padding 1, with bias; Tanh. Seeded like C2. `channels` widens the two hidden layers (8 and 6 by default)."""
     rng = np.random.Generator(np.random.PCG64(SEEDS[key] + 79))
-    m = Model(f"upsample_b{batch}", "x", (batch, 3, hw, hw), [])
-    m.weights["w0"] = (rng.standard_normal((8, 3, 3, 3)) * np.sqrt(2.0 / 27)).astype(np.float32)
-    m.weights["b0"] = rng.uniform(-0.1, 0.1, 8).astype(np.float32)
-    m.weights["t1"] = (rng.standard_normal((8, 6, 2, 2)) * np.sqrt(2.0 / 8)).astype(np.float32)
-    m.weights["t2"] = (rng.standard_normal((6, 3, 3, 3)) * np.sqrt(2.0 / 14)).astype(np.float32)
+    c0, c1 = channels
+    m = Model(f"upsample_b{batch}" + ("" if channels == (8, 6) else f"_c{c0}_{c1}"), "x", (batch, 3, hw, hw), [])
+    m.weights["w0"] = (rng.standard_normal((c0, 3, 3, 3)) * np.sqrt(2.0 / 27)).astype(np.float32)
+    m.weights["b0"] = rng.uniform(-0.1, 0.1, c0).astype(np.float32)
+    m.weights["t1"] = (rng.standard_normal((c0, c1, 2, 2)) * np.sqrt(2.0 / c0)).astype(np.float32)
+    m.weights["t2"] = (rng.standard_normal((c1, 3, 3, 3)) * np.sqrt(2.0 / (14 if c1 == 6 else 2.25 * c1))).astype(np.float32)
     m.weights["tb2"] = rng.uniform(-0.1, 0.1, 3).astype(np.float32)
     m.layers.append(dict(op="Conv", X="x", W="w0", B="b0", Y="c0", pads=(1, 1, 1, 1), strides=(1, 1), kernel=(3, 3)))
     m.layers.append(dict(op="Relu", X="c0", Y="r0"))
@@ -207,7 +208,7 @@ def upsample_f32(batch=4, hw=12, key="C2", with_input=True):
                          output_padding=(1, 1)))
     m.layers.append(dict(op="Tanh", X="u2", Y="y"))
     m.output_name = "y"
-    m.flops_per_sample = 2 * hw * hw * (8 * 27 + 8 * 6 * 4 + 4 * 6 * 3 * 9)
+    m.flops_per_sample = 2 * hw * hw * (c0 * 27 + c0 * c1 * 4 + 4 * c1 * 3 * 9)
     x = rng.standard_normal((batch, 3, hw, hw)).astype(np.float32) if with_input else None
     return m, x
 

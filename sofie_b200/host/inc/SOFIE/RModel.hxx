@@ -148,6 +148,7 @@ public:
    void PrintDynamicTensors() {}
    void HeadInitializedTensors(std::string name, int n_print = 50);
    bool UseSession() const { return fUseSession; }
+   bool RunTimeBatch() const { return fDynamicBatch; } // the batch is a parameter of the emitted Session
 
    // ---- device plan interface used by the operators ----
    ELayout GetTensorLayout(const std::string &name) const;

@@ -17,6 +17,7 @@
 #include "SOFIE/Emit.hxx"
 #include "SOFIE/RModel.hxx"
 #include "SOFIE/ROperator.hxx"
+#include "sofie_cuda.h" // sofie_conv_transpose2d_gemm_scratch_bytes: host arithmetic only
 
 namespace SOFIE {
 
@@ -28,6 +29,8 @@ private:
    size_t fAttrGroup;
    std::vector<size_t> fAttrKernelShape, fAttrOutputPadding, fAttrOutputShape, fAttrPads, fAttrStrides;
    std::string fNX, fNW, fNB, fNY;
+   std::string fNProducts;   // arena slice of the product form (channel-last input, re-ordered filters, products), when it is used
+   size_t fProductsBytes = 0;
    std::vector<size_t> fShapeX, fShapeW, fShapeB, fShapeY;
    size_t fDim = 0;
    // resolved 2-D values (a 1-D operator is the 2-D one with height 1)
@@ -112,11 +115,31 @@ public:
       model.AddIntermediateTensor(fNY, model.GetTensorType(fNX), fShapeY);
    }
 
+   sofie_conv_transpose2d_desc Desc() const
+   {
+      sofie_conv_transpose2d_desc d = {};
+      d.N = (int32_t)fShapeX[0], d.C = (int32_t)fShapeX[1], d.H = (int32_t)fH, d.W = (int32_t)fW, d.Cout = (int32_t)fShapeW[1];
+      d.kH = (int32_t)fKH, d.kW = (int32_t)fKW, d.pad_h = (int32_t)fPadH, d.pad_w = (int32_t)fPadW, d.stride_h = (int32_t)fSH,
+      d.stride_w = (int32_t)fSW, d.dil_h = (int32_t)fDH, d.dil_w = (int32_t)fDW, d.out_pad_h = (int32_t)fOPH, d.out_pad_w = (int32_t)fOPW;
+      return d;
+   }
+
    void PlanDevice(RModel &model) override
    {
       model.SetTensorLayout(fNY, ELayout::NCHW);
       model.UseOnDevice(fNW);
       if (!fNB.empty()) model.UseOnDevice(fNB);
+      // With 16 or more input channels the operator is lowered as the reference lowers it -- a filter GEMM, here one for
+      // all images and on the tensor cores, followed by the gather form of col2im -- and needs a slice of the arena for
+      // the products (alive during this operator only). Not with a run-time batch: part of the slice (the re-ordered
+      // filters) does not scale with the batch.
+      const sofie_conv_transpose2d_desc d = Desc();
+      fProductsBytes = model.RunTimeBatch() ? 0 : sofie_conv_transpose2d_gemm_scratch_bytes(&d);
+      if (fProductsBytes) {
+         fNProducts = fNY + "_products";
+         model.AddIntermediateTensor(fNProducts, ETensorType::FLOAT, std::vector<size_t>{fProductsBytes / sizeof(float)});
+         fOutputTensorNames = {fNY, fNProducts};
+      }
    }
 
    std::string Generate(std::string OpName) override
@@ -130,8 +153,13 @@ public:
       out << SP << SP << "const sofie_conv_transpose2d_desc d = {" << fShapeX[0] << ", " << fShapeX[1] << ", " << fH << ", " << fW << ", "
           << fShapeW[1] << ", " << fKH << ", " << fKW << ", " << fPadH << ", " << fPadW << ", " << fSH << ", " << fSW << ", " << fDH << ", "
           << fDW << ", " << fOPH << ", " << fOPW << ", 0};\n";
-      out << EMIT::Call(SP + SP, "sofie_cuda_conv_transpose2d_f32(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNW) + ", " +
-                                    (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB)) + ", " + EMIT::Dev(fNY) + ")");
+      const std::string args = EMIT::Dev(fNX) + ", " + EMIT::Dev(fNW) + ", " + (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB)) + ", " +
+                               EMIT::Dev(fNY);
+      if (fProductsBytes)
+         out << EMIT::Call(SP + SP, "sofie_cuda_conv_transpose2d_f32_gemm(fStream, &d, " + args + ", " + EMIT::Dev(fNProducts) + ", " +
+                                       std::to_string(fProductsBytes) + ")");
+      else
+         out << EMIT::Call(SP + SP, "sofie_cuda_conv_transpose2d_f32(fStream, &d, " + args + ")");
       out << SP << "}\n";
       return out.str();
    }

@@ -111,8 +111,9 @@ def softmax_f32(X, axis=-1):
     return Y
 
 
-def conv_transpose2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0), relu=False):
-    """ONNX ConvTranspose, group 1: X [N, C, H, W], W [C, Cout, kH, kW] -> [N, Cout, oH, oW]."""
+def conv_transpose2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0), relu=False, product_form=False):
+    """ONNX ConvTranspose, group 1: X [N, C, H, W], W [C, Cout, kH, kW] -> [N, Cout, oH, oW]. product_form: the entry
+    point that lowers to one tensor-core GEMM plus a gather (shapes with at least 16 input channels, a multiple of 4)."""
     N, Cin, H, Wd = X.shape
     _, Cout, kH, kW = W.shape
     oH = stride[0] * (H - 1) + dil[0] * (kH - 1) + 1 + out_pad[0] - 2 * pad[0]
@@ -120,7 +121,13 @@ def conv_transpose2d_f32(X, W, bias=None, pad=(0, 0), stride=(1, 1), dil=(1, 1),
     Y = torch.empty((N, Cout, max(oH, 0), max(oW, 0)), dtype=torch.float32, device=X.device)
     d = capi.ConvTranspose2dDesc(N, Cin, H, Wd, Cout, kH, kW, pad[0], pad[1], stride[0], stride[1], dil[0], dil[1], out_pad[0],
                                  out_pad[1], int(relu))
-    capi.call("sofie_cuda_conv_transpose2d_f32", _stream(), C.byref(d), _p(X), _p(W), _p(bias) if bias is not None else None, _p(Y))
+    b = _p(bias) if bias is not None else None
+    if product_form:
+        nbytes = capi.load().sofie_cuda_conv_transpose2d_f32_gemm_scratch(C.byref(d))
+        scratch = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=X.device)
+        capi.call("sofie_cuda_conv_transpose2d_f32_gemm", _stream(), C.byref(d), _p(X), _p(W), b, _p(Y), _p(scratch), nbytes)
+    else:
+        capi.call("sofie_cuda_conv_transpose2d_f32", _stream(), C.byref(d), _p(X), _p(W), b, _p(Y))
     return Y
 
 

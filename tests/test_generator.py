@@ -188,6 +188,15 @@ def test_conv_transpose_emits_one_call_and_refuses_what_the_reference_refuses():
     assert [int(v) for v in descs[0].split(",")] == [2, 8, 12, 12, 6, 2, 2, 0, 0, 2, 2, 1, 1, 0, 0, 0]
     assert [int(v) for v in descs[1].split(",")] == [2, 6, 24, 24, 3, 3, 3, 1, 1, 2, 2, 1, 1, 1, 1, 0]
     generated.compile_session(_emit(m, "upsample_b2"), "upsample_b2")
+    # 16 or more input channels: the product form (one GEMM for all images, then a gather) with its slice of the arena,
+    # which lives only during the operator; with a run-time batch the direct kernel is kept
+    m, _ = configs.upsample_f32(batch=2, channels=(32, 16))
+    text = _emit(m, "upsample_wide_b2").read_text()
+    assert text.count("sofie_cuda_conv_transpose2d_f32_gemm(") == 2 and "sofie_cuda_conv_transpose2d_f32(" not in text
+    assert "dev_u1_products" in text and "dev_u2_products" in text
+    generated.compile_session(_emit(m, "upsample_wide_b2"), "upsample_wide_b2")
+    dyn = generated.emit(onnx_wire.model_to_onnx(m, batch_param="bs"), "upsample_wide_dyn").read_text()
+    assert "sofie_cuda_conv_transpose2d_f32_gemm(" not in dyn and dyn.count("sofie_cuda_conv_transpose2d_f32(") == 2
 
     def graph(attrs):
         w = np.zeros((3, 2, 3, 3), np.float32)

@@ -2,6 +2,8 @@
 oracle and the reference's golden vectors. The contractions run here on the CUDA-core kernels
 (engine forced); the tcgen05 kernels have their own file.
 Tolerances: fp32 1e-5 (tensor-relative, helpers.rel_err), int8 bit-exact, FP8 2e-2."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -191,6 +193,46 @@ def test_conv_transpose2d_f32(case):
     y = ops.conv_transpose2d_f32(dev(X), dev(Wt), None if b is None else dev(b), pad=pad, stride=stride, dil=dil, out_pad=out_pad,
                                  relu=relu).cpu().numpy()
     assert y.shape == ref.shape and rel_err(y, ref) <= FP32_TOL
+
+
+@pytest.mark.parametrize("case", [
+    # N, C, H, W, Cout, k, pad, stride, dil, out_pad, bias, relu
+    (4, 32, 16, 16, 16, (4, 4), (1, 1), (2, 2), (1, 1), (0, 0), True, True),       # the usual 2x upsampling layer of a decoder
+    (2, 16, 7, 5, 6, (3, 2), (1, 0), (3, 2), (2, 1), (2, 1), False, False),        # dilation, output_padding, Cout not a multiple of 4
+    (3, 64, 8, 8, 32, (2, 2), (0, 0), (2, 2), (1, 1), (0, 0), True, False),        # stride = kernel: every output has one tap
+    (1, 20, 1, 33, 8, (1, 5), (0, 2), (1, 3), (1, 1), (0, 0), True, True),         # 1-D, C not a multiple of 8 (the GEMM's own fallback)
+    (5, 128, 12, 12, 64, (3, 3), (1, 1), (1, 1), (1, 1), (0, 0), True, False),     # stride 1: nine taps per output
+])
+def test_conv_transpose2d_f32_product_form(case):
+    """The entry point that lowers to one GEMM over all images plus a gather (the reference's own lowering, on the tensor cores)."""
+    N, Cin, H, W, Cout, k, pad, stride, dil, out_pad, bias, relu = case
+    rng = np.random.default_rng(N * 100 + Cin)
+    X = rng.standard_normal((N, Cin, H, W)).astype(np.float32)
+    Wt = (rng.standard_normal((Cin, Cout) + k) / np.sqrt(Cin * k[0] * k[1])).astype(np.float32)
+    b = rng.standard_normal(Cout).astype(np.float32) if bias else None
+    ref = o.conv_transpose2d_f32(X, Wt, b, pad=pad, stride=stride, dil=dil, out_pad=out_pad)
+    if relu:
+        ref = o.relu_f32(ref)
+    capi.call("sofie_cuda_set_engine", 0)
+    y = ops.conv_transpose2d_f32(dev(X), dev(Wt), None if b is None else dev(b), pad=pad, stride=stride, dil=dil, out_pad=out_pad,
+                                 relu=relu, product_form=True).cpu().numpy()
+    assert y.shape == ref.shape and rel_err(y, ref) <= FP32_TOL
+    if Cin % 8 == 0 and N * H * W >= 128:
+        assert ops.last_engine() == capi.ENGINE_TCGEN05
+
+
+def test_conv_transpose2d_product_form_limits():
+    lib = capi.load()
+    small = capi.ConvTranspose2dDesc(1, 8, 4, 4, 4, 3, 3, 0, 0, 1, 1, 1, 1, 0, 0, 0)       # fewer than 16 input channels
+    assert lib.sofie_cuda_conv_transpose2d_f32_gemm_scratch(C.byref(small)) == 0
+    x = torch.zeros(4096, device="cuda")
+    p = C.c_void_p(x.data_ptr())
+    assert lib.sofie_cuda_conv_transpose2d_f32_gemm(None, C.byref(small), p, p, None, p, p, 16384) == capi.ERR_UNSUPPORTED
+    d = capi.ConvTranspose2dDesc(1, 16, 4, 4, 4, 3, 3, 0, 0, 1, 1, 1, 1, 0, 0, 0)
+    need = lib.sofie_cuda_conv_transpose2d_f32_gemm_scratch(C.byref(d))
+    assert need == 4 * (256 + 576 + 576)                                           # 16*16 input, 9*4*16 filter, 16*36 product floats
+    assert lib.sofie_cuda_conv_transpose2d_f32_gemm(None, C.byref(d), p, p, None, p, p, need - 1) == capi.ERR_INVALID
+    assert b"needed" in lib.sofie_cuda_last_error()
 
 
 def test_conv_transpose2d_empty_batch_and_bad_arguments():

@@ -35,6 +35,16 @@ def test_generated_session_matches_reference_emitted_code(case, cuda_device):
     assert rel_err(y1, REF[case]) <= 1e-5
 
 
+def test_generated_decoder_with_product_form_conv_transpose(cuda_device):
+    """ConvTranspose layers with 32 and 16 input channels: emitted as the filter GEMM (tensor cores) plus gather, against the oracle."""
+    m, x = configs.upsample_f32(batch=6, hw=16, channels=(32, 16))
+    s = generated.session_from_model(m, "upsample_wide_b6")
+    assert "sofie_cuda_conv_transpose2d_f32_gemm(" in s.hxx.read_text()
+    y1 = s.infer(x)
+    assert np.array_equal(y1, s.infer(x))
+    assert rel_err(y1, run_model.run(m, x).ravel()) <= 1e-5
+
+
 def test_generated_int8_sessions_bit_exact(cuda_device):
     m, x = configs.mlp_i8(batch=512)
     y = generated.session_from_model(m, "c3_b512").infer(x)
