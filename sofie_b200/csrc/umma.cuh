@@ -301,6 +301,23 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, int row_b
    return desc;
 }
 
+// The same swizzled K-major rows with the 8-row groups `sbo_bytes` apart instead of densely packed. The swizzle is applied
+// to the absolute shared-memory address (bits 4-6 xor bits 7-9 for 128-byte rows, fewer bits for shorter rows), both by TMA
+// when it writes and by the MMA when it reads, so the start address may be any row of a TMA-written region and the group
+// stride any multiple of 16 bytes; the descriptor's base-offset field stays 0 (measured on B200: every row offset and group
+// stride tried reads the right bytes with base offset 0, and the wrong ones with the offset the address suggests).
+__device__ __forceinline__ uint64_t make_smem_desc_rows(uint32_t smem_addr, int row_bytes, uint32_t sbo_bytes)
+{
+   const uint64_t layout = row_bytes == 128 ? 2 : (row_bytes == 64 ? 4 : 6);
+   uint64_t desc = 0;
+   desc |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+   desc |= (uint64_t)1 << 16;
+   desc |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+   desc |= (uint64_t)1 << 46;
+   desc |= layout << 61;
+   return desc;
+}
+
 // K-major operand without swizzle: the tile is made of 8-row x 16-byte core matrices, each 128
 // contiguous bytes (8 rows at a 16-byte pitch). sbo_bytes is the distance between consecutive 8-row
 // groups, lbo_bytes the distance between the two 16-byte K columns one MMA (32 bytes of K) reads.

@@ -513,21 +513,24 @@ umma_conv3x3_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_consta
 // The kernel above fetches the input tile once per tap (nine overlapping boxes per channel chunk)
 // and the weight tile again for every output tile; the TMA issue cost and, for fp32, the hi/lo split
 // of all those bytes bound it. Here a tile is 16 rows x 8 columns of one image and its input is
-// fetched ONCE, as the 18 x 10 patch including the halo (zero fill outside the image), in a layout
-// that lets every tap address it in place:
-//    patch[plane p][patch row][patch column][16 bytes]     plane = 16 bytes of channels
-// For tap (r,s) the 128 x K operand starts at patch row r, column s: pixel (h, w) of the tile is at
-//    (r + h) * 10 + (s + w)  pixels of 16 bytes,
-// so the 8 pixels of one tile row are 128 contiguous bytes (one core matrix of the no-swizzle
-// K-major layout), consecutive tile rows are 160 bytes apart (the stride between 8-row groups) and
-// consecutive 16-byte K columns are one plane apart (the leading-dimension byte offset). A tap is
-// therefore only a different start address of the same shared-memory bytes.
+// fetched ONCE, as the 18 x 10 patch including the halo (zero fill outside the image), by one TMA box per
+// stage whose rows are the pixels (up to 128 bytes of channels each, the swizzle span; wider pixels are
+// streamed in groups of 128 bytes):
+//    patch[patch row][patch column][PB bytes of channels]      written with the swizzle of PB-byte rows
+// For tap (r,s) the 128 x K operand starts at patch row r, column s: pixel (h, w) of the tile is row
+//    (r + h) * 10 + (s + w)
+// of that region, so the 8 pixels of one tile row are one 8-row group of the K-major swizzled layout,
+// consecutive tile rows are one PATCH row (10 pixels) apart (the stride between 8-row groups), and the
+// next 32 bytes of K are 32 bytes further in the row. A tap is therefore only a different start address
+// of the same shared-memory bytes. This relies on the swizzle being a function of the absolute
+// shared-memory address on both sides (TMA write, MMA read), which holds on B200: a descriptor may start
+// at any row and step by any group stride (make_smem_desc_rows). An earlier form kept 16-byte channel
+// planes in the no-swizzle layout; its boxes had 16-byte rows, and the copy engine's cost is per row.
 // All 9 x C x Cout weights (and their lo parts for fp32) are loaded and split once per CTA and stay
 // in shared memory; the launcher falls back to the kernel above when they do not fit.
 constexpr int kPatchTileH = 16, kPatchTileW = 8;
 constexpr int kPatchH = kPatchTileH + 2, kPatchW = kPatchTileW + 2;
-constexpr int kPlaneBox = kPatchH * kPatchW * 16;                 // bytes one plane copy delivers
-constexpr int kPlaneStride = (kPlaneBox + 127) / 128 * 128;       // TMA destinations are 128-byte aligned
+constexpr int kPatchPixels = kPatchH * kPatchW;
 constexpr int kPatchMaxStages = 8;
 
 // warps: producer, MMA issuer, 8 epilogue + 8 converter warps (fp32) or 16 epilogue warps (int8), then the further
@@ -540,7 +543,7 @@ struct PatchPlan {
    int chunks;   // weight sub-tiles per tap (rows of cb bytes)
    int cb;       // bytes per weight row chunk: 32, 64 or 128 (selects the swizzle)
    int stages;   // pipeline slots
-   uint32_t stage_bytes; // one copy (hi) of the planes of a stage
+   uint32_t stage_bytes; // one copy (hi) of a stage: the patch's pixels x the stage's bytes of channels
    uint32_t w_bytes;     // one copy (hi) of all weights
    int issuers;          // 1, 2 or (int8) 4 threads issuing the MMAs, taking the tiles in turn
    int conv_groups;      // fp32: 1 or 2 groups of converter warps (2: slots taken alternately)
@@ -562,7 +565,8 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
    constexpr int ES = (KIND == kTF32) ? 4 : 1;
    constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
    constexpr int NACC = (KIND == kTF32) ? 2 : 1;
-   constexpr int PGP = 2 * KPS;                              // planes per stage
+   constexpr int PB = 32 * KPS;                              // bytes of channels per pixel and stage: 32, 64 or 128 = the swizzle span
+   static_assert(PB == 32 || PB == 64 || PB == 128, "a stage row is one swizzle span");
    constexpr int KSTEPS = KPS * G;                           // MMAs per tap
    constexpr int CBK = KSTEPS * 32 >= 128 ? 128 : KSTEPS * 32; // bytes per weight row chunk (== pl.cb)
    constexpr int CHUNKS = KSTEPS * 32 / CBK;
@@ -650,13 +654,13 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          for (int grp = 0; grp < G; grp++, g++, ring_next(s, ph, S)) {
             if (lane == 0) {
                ok = SOFIE_PROF_WAIT(mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g));
-               if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)PGP * kPlaneBox);
+               if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)(kPatchPixels * PB));
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
-            // channel coordinate = a multiple of 16 bytes; rows and columns start at -1 (zero fill)
-            if (lane < PGP)
-               tma_load_4d(slot_hi(s) + (size_t)lane * kPlaneStride, &tmX, (grp * PGP + lane) * (16 / ES), w0 - 1, h0 - 1, n0, &full_bar[s]);
+            // ONE box per stage: PB bytes of channels of every pixel of the haloed patch (channel coordinate = a multiple of
+            // PB bytes; rows and columns start at -1: zero fill), written with the swizzle of its row length
+            if (lane == 0) tma_load_4d(slot_hi(s), &tmX, grp * (PB / ES), w0 - 1, h0 - 1, n0, &full_bar[s]);
             __syncwarp();
          }
       }
@@ -702,7 +706,10 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                                                     : mbar_wait(&full_bar[s], ph, &abort_flag, status, kStatusWaitFull, g));
                if (!ok) break;
                tc_fence_after();
-               const uint64_t da0 = make_smem_desc_noswizzle(smem_u32(slot_hi(s)), kPlaneStride, kPatchW * 16);
+               // K-major rows of PB bytes in the swizzle TMA wrote them with; the eight pixels of a tile row are one 8-row
+               // group, the next group is one PATCH row further (not 8 rows: the swizzle is a function of the absolute
+               // shared-memory address, so a descriptor may start at any row and step by any number of rows)
+               const uint64_t da0 = make_smem_desc_rows(smem_u32(slot_hi(s)), PB, kPatchW * PB);
                const uint32_t a_hi_word = (uint32_t)(da0 >> 32), a_lo_word = (uint32_t)da0;
                auto adesc = [&](uint32_t off16) { return ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + off16); };
                auto bdesc = [&](uint32_t off16) { return ((uint64_t)b_hi_word << 32) | (uint64_t)(b_lo_word + off16); };
@@ -711,7 +718,7 @@ umma_conv3x3_patch_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 #pragma unroll
                   for (int kk = 0; kk < KPS; kk++) {
                      const int kb = (grp * KPS + kk) * 32; // byte offset in the K row of this tap
-                     const uint32_t a16 = (uint32_t)(((tap / 3) * kPatchW + (tap % 3)) * 16 + kk * 2 * kPlaneStride) >> 4;
+                     const uint32_t a16 = (uint32_t)(((tap / 3) * kPatchW + (tap % 3)) * PB + kk * 32) >> 4;
                      const uint32_t b16 = (uint32_t)((tap * CHUNKS + kb / CBK) * (COPIES * B_TILE) + kb % CBK) >> 4;
                      const uint32_t acc = (grp | tap | kk) ? 1u : 0u;
                      if constexpr (KIND == kTF32) {
@@ -827,7 +834,9 @@ static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, c
    pl.cb = row_bytes >= 128 ? 128 : row_bytes;
    pl.chunks = row_bytes / pl.cb;
    pl.w_bytes = (uint32_t)(9 * pl.chunks * BN * pl.cb);
-   pl.stage_bytes = (uint32_t)(2 * KPS * kPlaneStride);
+   // a multiple of 1024, so that every slot (and the lo copy of a slot, which the converters write at the same offset
+   // from it) starts on a boundary of the widest swizzle pattern
+   pl.stage_bytes = (uint32_t)((kPatchPixels * 32 * KPS + 1023) & ~1023);
    static const int issuers = [] { const char *e = getenv("SOFIE_CUDA_CONV_ISSUERS"); const int v = e ? atoi(e) : 0; return v == 1 || v == 2 || v == 4 ? v : 4; }();
    static const int groups = [] { const char *e = getenv("SOFIE_CUDA_CONV_GROUPS"); return e && atoi(e) == 1 ? 1 : 2; }();
    pl.issuers = issuers < kPatchIssuers<KIND> ? issuers : kPatchIssuers<KIND>;
@@ -849,8 +858,8 @@ static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, c
    CUtensorMap tmX, tmW;
    uint64_t xdims[4] = {(uint64_t)g.C, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N};
    uint64_t xstr[3] = {(uint64_t)g.C * ES, (uint64_t)g.W * g.C * ES, (uint64_t)g.H * g.W * g.C * ES};
-   uint32_t xbox[4] = {(uint32_t)(16 / ES), (uint32_t)kPatchW, (uint32_t)kPatchH, 1u};
-   int rc = make_tensor_map(&tmX, dt, 4, X, xdims, xstr, xbox, 0);
+   uint32_t xbox[4] = {(uint32_t)(32 * KPS / ES), (uint32_t)kPatchW, (uint32_t)kPatchH, 1u};
+   int rc = make_tensor_map(&tmX, dt, 4, X, xdims, xstr, xbox, 32 * KPS);
    if (rc) return rc;
    uint64_t wdims[2] = {(uint64_t)9 * g.C, (uint64_t)g.Cout};
    uint64_t wstr[1] = {(uint64_t)9 * g.C * ES};
@@ -869,22 +878,23 @@ static int launch_conv_patch(cudaStream_t s, const ConvGeom &g, const void *X, c
    return SOFIE_CUDA_OK;
 }
 
-// Plane grouping by channel bytes per pixel: the whole patch in one stage while that leaves room for
-// a deep pipeline, otherwise streamed in groups of 4 planes (2 MMAs per tap and stage).
+// A stage carries up to 128 bytes of channels per pixel (one swizzle span); wider pixels are streamed in groups of 128.
 template <int KIND, int BN>
 static int try_launch_conv_patch_bn(cudaStream_t s, const ConvGeom &g, const void *X, const void *Wp, const ConvEpilogue &ep)
 {
    constexpr int ES = (KIND == kTF32) ? 4 : 1;
-   constexpr int COPIES = (KIND == kTF32) ? 2 : 1;
-   const int row_bytes = g.C * ES;
-   const long w_all = (long)COPIES * 9 * row_bytes * BN;
-   // whole patch per stage if at least three such stages fit
-   const bool whole = 200 * 1024 - w_all >= 3L * COPIES * (row_bytes / 16) * kPlaneStride;
-   switch (row_bytes) {
+   switch (g.C * ES) {
    case 32: return launch_conv_patch<KIND, BN, 1, 1>(s, g, X, Wp, ep);
    case 64: return launch_conv_patch<KIND, BN, 2, 1>(s, g, X, Wp, ep);
-   case 128: return whole ? launch_conv_patch<KIND, BN, 4, 1>(s, g, X, Wp, ep) : launch_conv_patch<KIND, BN, 2, 2>(s, g, X, Wp, ep);
-   case 256: return whole ? launch_conv_patch<KIND, BN, 8, 1>(s, g, X, Wp, ep) : launch_conv_patch<KIND, BN, 2, 4>(s, g, X, Wp, ep);
+   case 128: {
+      // narrower stages when the resident weights leave room for fewer than two of the wide ones
+      const int rc = launch_conv_patch<KIND, BN, 4, 1>(s, g, X, Wp, ep);
+      return rc != -1 ? rc : launch_conv_patch<KIND, BN, 2, 2>(s, g, X, Wp, ep);
+   }
+   case 256: {
+      const int rc = launch_conv_patch<KIND, BN, 4, 2>(s, g, X, Wp, ep);
+      return rc != -1 ? rc : launch_conv_patch<KIND, BN, 2, 4>(s, g, X, Wp, ep);
+   }
    default: return -1;
    }
 }
