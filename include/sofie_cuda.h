@@ -270,6 +270,29 @@ size_t sofie_cuda_conv_transpose2d_f32_gemm_scratch(const sofie_conv_transpose2d
 int sofie_cuda_conv_transpose2d_f32_gemm(void *stream, const sofie_conv_transpose2d_desc *desc, const float *X, const float *W,
                                          const float *bias, float *Y, void *scratch, size_t scratch_bytes);
 
+/* 3-D convolution (reference: ROperator_Conv.hxx with fDim == 3, :95-201 and UTILITY::Im2col_3d, SOFIE_common.hxx:521-573):
+ * X [N, C, D, H, W], W [Cout, C/group, kD, kH, kW], Y [N, Cout, oD, oH, oW] with o = (i + 2*pad - (dil*(k-1)+1)) / stride + 1
+ * per axis; asymmetric ONNX pads are averaged by the caller as for the 2-D operator. Direct kernel on CUDA cores. */
+typedef struct sofie_conv3d_desc {
+   int32_t N, C, D, H, W;
+   int32_t Cout;
+   int32_t kD, kH, kW, pad_d, pad_h, pad_w, stride_d, stride_h, stride_w, dil_d, dil_h, dil_w;
+   int32_t group;
+   int32_t relu;            /* fused y = max(y, 0)                                          */
+} sofie_conv3d_desc;
+int sofie_cuda_conv3d_f32(void *stream, const sofie_conv3d_desc *desc, const float *X, const float *W, const float *bias, float *Y);
+
+/* MaxPool / AveragePool 3-D (reference: the fDim == 3 loops of ROperator_Pool.hxx:266-476) on [N, C, D, H, W];
+ * pads = (d_begin, h_begin, w_begin, d_end, h_end, w_end) as in ONNX. */
+typedef struct sofie_pool3d_desc {
+   int32_t mode;            /* 0: max, 1: average                                           */
+   int32_t N, C, D, H, W;
+   int32_t kD, kH, kW, stride_d, stride_h, stride_w;
+   int32_t pads[6];
+   int32_t count_include_pad;
+} sofie_pool3d_desc;
+int sofie_cuda_pool3d_f32(void *stream, const sofie_pool3d_desc *desc, const float *X, float *Y);
+
 /* Einsum of two operands, general form (reference: ROperator_Einsum.hxx:200-332, nested loops or one sgemm_ per
  * stack index): Y[out labels] = sum over all other labels of A[...] * B[...]. The labels are listed by extent, first
  * the n_out output labels in output order, then the n_sum summed ones; a_stride / b_stride give the element stride

@@ -127,6 +127,70 @@ def pool2d_f32(X, mode=0, kernel=(2, 2), stride=(2, 2), pads=(0, 0, 0, 0), count
     return Y
 
 
+def conv3d_f32(X, W, bias=None, pad=(0, 0, 0), stride=(1, 1, 1), dil=(1, 1, 1), group=1, relu=False):
+    """3-D convolution as the reference computes it (ROperator_Conv.hxx with fDim == 3: UTILITY::Im2col_3d, SOFIE_common.hxx:521-573,
+    then one sgemm_ per image and group; bias added afterwards): X [N, C, D, H, W], W [Cout, C/group, kD, kH, kW].
+    numpy restatement: for every filter tap the shifted, strided view of the zero-padded input times that tap's weights, summed in
+    (ic, kd, kh, kw) order in float32."""
+    X, W = _f(X), _f(W)
+    N, Cin, D, H, Wd = X.shape
+    Cout, cin_g, kD, kH, kW = W.shape
+    assert cin_g * group == Cin and Cout % group == 0
+    o = [(e + 2 * pad[i] - (dil[i] * (k - 1) + 1)) // stride[i] + 1 for i, (e, k) in enumerate(((D, kD), (H, kH), (Wd, kW)))]
+    Xp = np.zeros((N, Cin, D + 2 * pad[0], H + 2 * pad[1], Wd + 2 * pad[2]), np.float32)
+    Xp[:, :, pad[0]:pad[0] + D, pad[1]:pad[1] + H, pad[2]:pad[2] + Wd] = X
+    Y = np.zeros((N, Cout, *o), np.float32)
+    cout_g = Cout // group
+    for g in range(group):
+        for ic in range(cin_g):
+            for a in range(kD):
+                for b in range(kH):
+                    for c in range(kW):
+                        v = Xp[:, g * cin_g + ic,
+                               a * dil[0]:a * dil[0] + (o[0] - 1) * stride[0] + 1:stride[0],
+                               b * dil[1]:b * dil[1] + (o[1] - 1) * stride[1] + 1:stride[1],
+                               c * dil[2]:c * dil[2] + (o[2] - 1) * stride[2] + 1:stride[2]]
+                        w = W[g * cout_g:(g + 1) * cout_g, ic, a, b, c]
+                        Y[:, g * cout_g:(g + 1) * cout_g] += v[:, None] * w[None, :, None, None, None]
+    if bias is not None:
+        Y += _f(bias)[None, :, None, None, None]
+    if relu:
+        Y = np.where(Y > 0, Y, np.float32(0)).astype(np.float32)
+    return Y
+
+
+def pool3d_f32(X, mode=0, kernel=(2, 2, 2), stride=(2, 2, 2), pads=(0, 0, 0, 0, 0, 0), count_include_pad=0):
+    """MaxPool (mode 0) / AveragePool (mode 1) of [N, C, D, H, W] (reference: the fDim == 3 loops of ROperator_Pool.hxx:266-476, output
+    extent :172-197); pads = (d, h, w begin, d, h, w end). A maximum starts at -inf and takes v only when v > max (a NaN never wins);
+    an average adds the window's values in (d, h, w) order and divides by the number of values inside the tensor, or by the window
+    size with count_include_pad (or without padding)."""
+    X = _f(X)
+    N, Cc, D, H, W = X.shape
+    o = [-(-(e + pads[i] + pads[i + 3] - kernel[i] + 1) // stride[i]) for i, e in enumerate((D, H, W))]
+    Y = np.empty((N, Cc, *o), np.float32)
+    padded = any(pads)
+    for od in range(o[0]):
+        for oh in range(o[1]):
+            for ow in range(o[2]):
+                d0, h0, w0 = od * stride[0] - pads[0], oh * stride[1] - pads[1], ow * stride[2] - pads[2]
+                val = np.full((N, Cc), -np.inf if mode == 0 else 0.0, np.float32)
+                count = 0
+                for a in range(max(d0, 0), min(d0 + kernel[0], D)):
+                    for b in range(max(h0, 0), min(h0 + kernel[1], H)):
+                        for c in range(max(w0, 0), min(w0 + kernel[2], W)):
+                            v = X[:, :, a, b, c]
+                            if mode == 0:
+                                val = np.where(v > val, v, val)
+                            else:
+                                val = (val + v).astype(np.float32)
+                                count += 1
+                if mode == 1:
+                    n = kernel[0] * kernel[1] * kernel[2] if (count_include_pad or not padded) else count
+                    val = (val / np.float32(n)).astype(np.float32)
+                Y[:, :, od, oh, ow] = val
+    return Y
+
+
 UNARY_OPS = {"Sigmoid": 0, "Tanh": 1, "LeakyRelu": 2, "Selu": 3, "Elu": 4, "Neg": 5, "Exp": 6, "Log": 7, "Sqrt": 8,
              "Reciprocal": 9, "Abs": 10, "Erf": 11, "Swish": 12, "Cos": 13, "Sin": 14}
 BINARY_OPS = {"Add": 0, "Sub": 1, "Mul": 2, "Div": 3}

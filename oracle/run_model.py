@@ -23,6 +23,10 @@ def run(model, x, fp8_scales=None, return_all=False):
         if op == "Gemm":
             t[L["Y"]] = o.gemm_f32(t[L["A"]], w[L["B"]], w.get(L.get("C")), transB=L.get("transB", 0),
                                    alpha=L.get("alpha", 1.0), beta=L.get("beta", 1.0), relu=L.get("relu", False))
+        elif op == "Conv" and len(L["kernel"]) == 3:
+            p = L["pads"]
+            t[L["Y"]] = o.conv3d_f32(t[L["X"]], w[L["W"]], w.get(L.get("B")), pad=(p[0], p[1], p[2]), stride=L["strides"],
+                                     dil=L.get("dilations", (1, 1, 1)), group=L.get("group", 1))
         elif op == "Conv":
             p, s = L["pads"], L["strides"]
             t[L["Y"]] = o.conv2d_f32(t[L["X"]], w[L["W"]], w.get(L.get("B")), pad=(p[0], p[1]), stride=s,
@@ -35,7 +39,9 @@ def run(model, x, fp8_scales=None, return_all=False):
             t[L["Y"]] = o.relu_f32(t[L["X"]])
         elif op == "MaxPool":
             X = t[L["X"]]
-            if X.dtype == np.uint8:
+            if X.ndim == 5:
+                t[L["Y"]] = o.pool3d_f32(X, 0, L["kernel"], L["strides"], L["pads"])
+            elif X.dtype == np.uint8:
                 t[L["Y"]] = o.maxpool2d_u8(X, L["kernel"], L["strides"])
             else:
                 t[L["Y"]] = o.pool2d_f32(X, 0, L["kernel"], L["strides"], L["pads"])

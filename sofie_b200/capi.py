@@ -39,6 +39,16 @@ class Pool2dDesc(C.Structure):
                [("pads", i32 * 4), ("count_include_pad", i32), ("layout", i32)]
 
 
+class Pool3dDesc(C.Structure):
+    _fields_ = [(n, i32) for n in ("mode", "N", "C", "D", "H", "W", "kD", "kH", "kW", "stride_d", "stride_h", "stride_w")] + \
+               [("pads", i32 * 6), ("count_include_pad", i32)]
+
+
+class Conv3dDesc(C.Structure):
+    _fields_ = [(n, i32) for n in ("N", "C", "D", "H", "W", "Cout", "kD", "kH", "kW", "pad_d", "pad_h", "pad_w", "stride_d", "stride_h",
+                                   "stride_w", "dil_d", "dil_h", "dil_w", "group", "relu")]
+
+
 class QGemmDesc(C.Structure):
     _fields_ = [(n, i32) for n in ("M", "N", "K", "w_is_nk", "y_zp", "relu")]
 
@@ -117,6 +127,8 @@ SIGNATURES = {
     "sofie_cuda_einsum_f32": [vp, C.POINTER(EinsumDesc), vp, vp, vp],
     "sofie_cuda_relu_f32": [vp, vp, vp, sz],
     "sofie_cuda_pool2d_f32": [vp, C.POINTER(Pool2dDesc), vp, vp],
+    "sofie_cuda_pool3d_f32": [vp, C.POINTER(Pool3dDesc), vp, vp],
+    "sofie_cuda_conv3d_f32": [vp, C.POINTER(Conv3dDesc), vp, vp, vp, vp],
     "sofie_cuda_softmax_f32": [vp, vp, vp, sz, sz, sz],
     "sofie_cuda_mlp_f32": [vp, C.POINTER(MlpDesc), vp, C.POINTER(vp), C.POINTER(vp), vp],
     "sofie_cuda_unary_f32": [vp, i32, f32, vp, vp, sz],

@@ -213,6 +213,25 @@ def upsample_f32(batch=4, hw=12, key="C2", with_input=True, channels=(8, 6)):
     return m, x
 
 
+def volume_f32(batch=3, dhw=(6, 8, 10), key="C2", with_input=True):
+    """A small 3-D network: Conv3d 2->8 (3x3x3, pad 1) + Relu; MaxPool3d 2x2x2; Conv3d 8->4 (2x3x1, stride (1,2,1), group 2) with bias."""
+    rng = np.random.Generator(np.random.PCG64(SEEDS[key] + 131))
+    D, H, W = dhw
+    m = Model(f"volume_b{batch}", "x", (batch, 2, D, H, W), [])
+    m.weights["w0"] = (rng.standard_normal((8, 2, 3, 3, 3)) * np.sqrt(2.0 / 54)).astype(np.float32)
+    m.weights["b0"] = rng.uniform(-0.1, 0.1, 8).astype(np.float32)
+    m.weights["w1"] = (rng.standard_normal((4, 4, 2, 3, 1)) * np.sqrt(2.0 / 24)).astype(np.float32)
+    m.weights["b1"] = rng.uniform(-0.1, 0.1, 4).astype(np.float32)
+    m.layers.append(dict(op="Conv", X="x", W="w0", B="b0", Y="c0", pads=(1, 1, 1, 1, 1, 1), strides=(1, 1, 1), kernel=(3, 3, 3)))
+    m.layers.append(dict(op="Relu", X="c0", Y="r0"))
+    m.layers.append(dict(op="MaxPool", X="r0", Y="p0", pads=(0, 0, 0, 0, 0, 0), strides=(2, 2, 2), kernel=(2, 2, 2)))
+    m.layers.append(dict(op="Conv", X="p0", W="w1", B="b1", Y="y", pads=(0, 0, 0, 0, 0, 0), strides=(1, 2, 1), kernel=(2, 3, 1), group=2))
+    m.output_name = "y"
+    m.flops_per_sample = 2 * D * H * W * 8 * 54
+    x = rng.standard_normal((batch, 2, D, H, W)).astype(np.float32) if with_input else None
+    return m, x
+
+
 def mlp_activations_f32(batch=64, key="C1", with_input=True):
     """Gemm 32->48 + Selu; Gemm 48->48 + Tanh; Sub of a constant row; Gemm 48->24 + Elu; Div by a constant; Sigmoid."""
     rng = np.random.Generator(np.random.PCG64(SEEDS[key] + 78))

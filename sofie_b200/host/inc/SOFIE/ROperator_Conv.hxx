@@ -30,13 +30,45 @@ struct ConvAttributes {
    size_t kH = 0, kW = 0, padH = 0, padW = 0, sH = 1, sW = 1, dH = 1, dW = 1;
 
    bool oneD = false; // rank-3 tensors: the single spatial axis is treated as the width of an image of height 1
+   // rank-5 tensors [N, C, D, H, W] (reference: fDim == 3): kernel, averaged pads, strides and dilations of the three axes
+   bool volume = false;
+   size_t k3[3] = {0, 0, 0}, pad3[3] = {0, 0, 0}, s3[3] = {1, 1, 1}, d3[3] = {1, 1, 1};
 
    void Resolve(const std::vector<size_t> &shapeX, const std::vector<size_t> &shapeW)
    {
       oneD = shapeX.size() == 3 && shapeW.size() == 3;
-      if (!oneD && (shapeX.size() != 4 || shapeW.size() != 4))
-         throw std::runtime_error("SOFIE Conv Op: only 1-D and 2-D convolutions (rank-3 and rank-4 tensors) are generated for the CUDA path");
+      volume = shapeX.size() == 5 && shapeW.size() == 5;
+      if (!oneD && !volume && (shapeX.size() != 4 || shapeW.size() != 4))
+         throw std::runtime_error("SOFIE Conv Op: convolutions are generated for rank-3, rank-4 and rank-5 tensors");
       if (group == 0) group = shapeX[1] / shapeW[1];
+      if (volume) {
+         std::vector<size_t> p;
+         for (size_t a = 0; a < 3; a++) {
+            k3[a] = kernel_shape.empty() ? shapeW[2 + a] : kernel_shape.at(a);
+            if (k3[a] != shapeW[2 + a]) throw std::runtime_error("SOFIE Conv Op: kernel_shape differs from the weight tensor");
+            d3[a] = dilations.empty() ? 1 : dilations.at(a);
+            s3[a] = strides.empty() ? 1 : strides.at(a);
+         }
+         if (autopad == "NOTSET") {
+            p = pads.empty() ? std::vector<size_t>(6, 1) : pads; // the reference's default is 1, not 0
+         } else if (autopad == "SAME_UPPER" || autopad == "SAME_LOWER") {
+            p.assign(6, 0);
+            for (size_t a = 0; a < 3; a++) {
+               const size_t e = k3[a] + (d3[a] - 1) * (k3[a] - 1);
+               p[a] = p[a + 3] = e / 2;
+               if (e % 2 == 1) (autopad == "SAME_UPPER") ? p[a]++ : p[a + 3]++;
+            }
+         } else if (autopad == "VALID") {
+            p.assign(6, 0);
+         } else {
+            throw std::runtime_error("SOFIE Conv Op invalid auto_pad " + autopad);
+         }
+         if (p.size() != 6) throw std::runtime_error("SOFIE Conv Op: pads of a 3-D convolution must have 6 values");
+         // asymmetric padding is averaged, as for the 2-D operator
+         for (size_t a = 0; a < 3; a++) pad3[a] = (p[a] == p[a + 3]) ? p[a] : (p[a] + p[a + 3]) / 2;
+         pads = p;
+         return;
+      }
       if (oneD) {
          kH = 1;
          kW = kernel_shape.empty() ? shapeW[2] : kernel_shape[0];
@@ -92,6 +124,11 @@ struct ConvAttributes {
    {
       const size_t eH = kH + (dH - 1) * (kH - 1), eW = kW + (dW - 1) * (kW - 1);
       if (oneD) return {shapeX[0], shapeW[0], (shapeX[2] + pads[1] + pads[3] - eW) / sW + 1};
+      if (volume) {
+         std::vector<size_t> y = {shapeX[0], shapeW[0]};
+         for (size_t a = 0; a < 3; a++) y.push_back((shapeX[2 + a] + pads[a] + pads[a + 3] - (k3[a] + (d3[a] - 1) * (k3[a] - 1))) / s3[a] + 1);
+         return y;
+      }
       // the reference sizes the output from the un-averaged pads (ROperator_Conv.hxx:178-189)
       size_t oH = (shapeX[2] + pads[0] + pads[2] - eH) / sH + 1;
       size_t oW = (shapeX[3] + pads[1] + pads[3] - eW) / sW + 1;
@@ -140,7 +177,7 @@ public:
    }
 
    EOpKind Kind() const override { return EOpKind::Conv; }
-   bool AcceptsNHWC(const std::string &input) const override { return input == fNX && fAttr.group == 1; }
+   bool AcceptsNHWC(const std::string &input) const override { return input == fNX && fAttr.group == 1 && !fAttr.volume; }
    // fusion interface used by the model plan
    const std::string &OutputName() const { return fNOut; }
    void FuseRelu(const std::string &reluOutput)
@@ -219,7 +256,9 @@ public:
    {
       fLayoutX = model.GetTensorLayout(model.ResolveAlias(fNX));
       fShapeOut = model.GetTensorShape(fNOut);
-      fLayoutY = (fAttr.group == 1 && model.CanStayNHWC(fNOut)) ? ELayout::NHWC : ELayout::NCHW;
+      fLayoutY = (fAttr.group == 1 && !fAttr.volume && model.CanStayNHWC(fNOut)) ? ELayout::NHWC : ELayout::NCHW;
+      if (fAttr.volume && (fLayoutX != ELayout::NCHW || fFusedPool))
+         throw std::runtime_error("SOFIE Conv op: a 3-D convolution reads and writes the ONNX layout and fuses no pooling");
       model.SetTensorLayout(fNOut, fLayoutY);
       // NHWC input: weights packed [Cout][kH][kW][Cin], the operand layout of the tensor-core kernel
       fPacked = (fLayoutX == ELayout::NHWC && fAttr.group == 1);
@@ -263,6 +302,17 @@ private:
          // the batch axis is outermost in NCHW and in NHWC: a slice is a contiguous range of both tensors
          x += " + (size_t)part * " + std::to_string(ConvertShapeToLength(fShapeX) / parts);
          y += " + (size_t)part * " + std::to_string(ConvertShapeToLength(fShapeOut) / parts);
+      }
+      if (fAttr.volume) {
+         out << SP << SP << "const sofie_conv3d_desc d = {" << fShapeX[0] / parts << ", " << fShapeX[1] << ", " << fShapeX[2] << ", " << fShapeX[3]
+             << ", " << fShapeX[4] << ", " << fShapeW[0] << ", " << fAttr.k3[0] << ", " << fAttr.k3[1] << ", " << fAttr.k3[2] << ", "
+             << fAttr.pad3[0] << ", " << fAttr.pad3[1] << ", " << fAttr.pad3[2] << ", " << fAttr.s3[0] << ", " << fAttr.s3[1] << ", "
+             << fAttr.s3[2] << ", " << fAttr.d3[0] << ", " << fAttr.d3[1] << ", " << fAttr.d3[2] << ", " << fAttr.group << ", "
+             << (fFusedRelu ? 1 : 0) << "};\n";
+         out << EMIT::Call(SP + SP, "sofie_cuda_conv3d_f32(fStream, &d, " + x + ", " + EMIT::Dev(fNWdev) + ", " +
+                                       (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB)) + ", " + y + ")");
+         out << SP << "}\n";
+         return out.str();
       }
       // a 1-D convolution runs as an image of height 1
       const size_t H = fAttr.oneD ? 1 : fShapeX[2], W = fAttr.oneD ? fShapeX[2] : fShapeX[3];

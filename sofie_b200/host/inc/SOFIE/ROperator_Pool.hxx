@@ -1,9 +1,10 @@
-// ONNX MaxPool / AveragePool / GlobalAveragePool, 2-D.
+// ONNX MaxPool / AveragePool / GlobalAveragePool, 1-D, 2-D and 3-D.
 // Constructor and attribute struct as in the reference (src/SOFIE_core/inc/SOFIE/ROperator_Pool.hxx:17-83).
 // The reference emits scalar nested loops (:266-476); this emits one call of sofie_cuda_pool2d_f32
 // (or sofie_cuda_maxpool2d_u8 on a quantised tensor), unless the model plan folded a 2x2 stride-2
 // MaxPool into the preceding convolution. `pads` follow ONNX (h_begin, w_begin, h_end, w_end), the
-// reading of the reference's shape inference (:172-189).
+// reading of the reference's shape inference (:172-189). A 3-D pooling of [N, C, D, H, W] (reference: fDim == 3)
+// emits one call of sofie_cuda_pool3d_f32.
 #ifndef SOFIE_ROPERATOR_POOL
 #define SOFIE_ROPERATOR_POOL
 
@@ -38,6 +39,8 @@ private:
    std::vector<size_t> fShape4; // the input viewed as [N, C, H, W] (H = 1 for a 1-D pooling)
    size_t fKH = 0, fKW = 0, fSH = 1, fSW = 1;
    std::vector<size_t> fPads;
+   bool fVolume = false;        // rank-5 input: 3-D pooling
+   std::vector<size_t> fK3, fS3, fP3; // its window, strides and six pads
    ELayout fLayout = ELayout::NCHW;
    ETensorType fType = ETensorType::FLOAT;
 
@@ -56,20 +59,21 @@ public:
       return "Invalid";
    }
    EOpKind Kind() const override { return EOpKind::Pool; }
-   bool AcceptsNHWC(const std::string &) const override { return true; }
+   bool AcceptsNHWC(const std::string &) const override { return !fVolume; }
    const std::string &InputName() const { return fNX; }
    const std::string &OutputName() const { return fNY; }
    // 2x2 window, stride 2, no padding: the form a convolution epilogue can absorb
    bool IsMax2x2Stride2() const
    {
-      return fPoolMode == MaxPool && fKH == 2 && fKW == 2 && fSH == 2 && fSW == 2 && fPads[0] + fPads[1] + fPads[2] + fPads[3] == 0;
+      return !fVolume && fPoolMode == MaxPool && fKH == 2 && fKW == 2 && fSH == 2 && fSW == 2 && fPads[0] + fPads[1] + fPads[2] + fPads[3] == 0;
    }
 
    std::vector<ETensorType> TypeInference(std::vector<ETensorType> input) override { return input; }
    std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override
    {
+      if (input.size() == 1 && input[0].size() == 5) return {ShapeInference3d(input[0])};
       if (input.size() != 1 || (input[0].size() != 4 && input[0].size() != 3))
-         throw std::runtime_error("SOFIE " + Name() + " Op: only 1-D and 2-D pooling (rank-3 and rank-4 tensors) is generated for the CUDA path");
+         throw std::runtime_error("SOFIE " + Name() + " Op: pooling is generated for rank-3, rank-4 and rank-5 tensors");
       // a 1-D pooling of [N, C, W] is the 2-D one of [N, C, 1, W] with a window of height 1
       const bool oneD = input[0].size() == 3;
       std::vector<size_t> x = input[0];
@@ -103,6 +107,31 @@ public:
       return {{x[0], x[1], oH, oW}};
    }
 
+   // [N, C, D, H, W]: window, strides and pads per axis, output extent as the reference's shape inference (:172-197)
+   std::vector<size_t> ShapeInference3d(const std::vector<size_t> &x)
+   {
+      fVolume = true;
+      fK3 = fAttr.kernel_shape.empty() ? std::vector<size_t>{x[2], x[3], x[4]} : fAttr.kernel_shape;
+      fS3 = fAttr.strides.empty() ? std::vector<size_t>{1, 1, 1} : fAttr.strides;
+      if (fK3.size() != 3 || fS3.size() != 3) throw std::runtime_error("SOFIE " + Name() + " Op: a 3-D pooling needs 3 kernel and stride values");
+      if (fAttr.auto_pad == "NOTSET") {
+         fP3 = fAttr.pads.empty() ? std::vector<size_t>(6, 0) : fAttr.pads;
+      } else if (fAttr.auto_pad == "SAME_UPPER" || fAttr.auto_pad == "SAME_LOWER") {
+         fP3 = {fK3[0] / 2, fK3[1] / 2, fK3[2] / 2, fK3[0] / 2, fK3[1] / 2, fK3[2] / 2};
+         for (size_t a = 0; a < 3; a++)
+            if (fK3[a] % 2 == 1) (fAttr.auto_pad == "SAME_UPPER") ? fP3[a]++ : fP3[a + 3]++;
+      } else if (fAttr.auto_pad == "VALID") {
+         fP3 = std::vector<size_t>(6, 0);
+      } else {
+         throw std::runtime_error("SOFIE " + Name() + " Op invalid auto_pad value : " + fAttr.auto_pad);
+      }
+      if (fP3.size() != 6) throw std::runtime_error("SOFIE " + Name() + " Op: pads of a 3-D pooling must have 6 values");
+      fPads = {0, 0, 0, 0};
+      std::vector<size_t> y = {x[0], x[1]};
+      for (size_t a = 0; a < 3; a++) y.push_back((x[2 + a] + fP3[a] + fP3[a + 3] - fK3[a]) / fS3[a] + 1);
+      return y;
+   }
+
    void Initialize(RModel &model) override
    {
       fUseSession = model.UseSession();
@@ -110,10 +139,10 @@ public:
       fShapeX = model.GetTensorShape(fNX);
       if (fPoolMode == GlobalAveragePool) {
          fPoolMode = AveragePool;
-         fAttr.kernel_shape = {fShapeX.at(2), fShapeX.at(3)};
+         fAttr.kernel_shape.assign(fShapeX.begin() + 2, fShapeX.end());
          fAttr.auto_pad = "VALID";
-         fAttr.pads = {0, 0, 0, 0};
-         fAttr.strides = {1, 1};
+         fAttr.pads.assign(2 * (fShapeX.size() - 2), 0);
+         fAttr.strides.assign(fShapeX.size() - 2, 1);
       }
       fShapeY = ShapeInference({fShapeX})[0];
       fType = model.GetTensorType(fNX);
@@ -123,6 +152,8 @@ public:
    {
       fLayout = model.GetTensorLayout(model.ResolveAlias(fNX));
       model.SetTensorLayout(fNY, fLayout);
+      if (fVolume && (fType != ETensorType::FLOAT || fLayout != ELayout::NCHW))
+         throw std::runtime_error("SOFIE Pool op: 3-D pooling is generated for float tensors in the ONNX layout");
       if (fType == ETensorType::UINT8 && (fPoolMode != MaxPool || fPads[0] + fPads[1] + fPads[2] + fPads[3] != 0))
          throw std::runtime_error("SOFIE Pool op: only un-padded MaxPool is generated for quantised tensors");
       if (fType != ETensorType::UINT8 && fType != ETensorType::FLOAT)
@@ -134,6 +165,16 @@ public:
       if (fShapeX.empty() || fShapeY.empty()) throw std::runtime_error("SOFIE Pool Op called to Generate without being initialized first");
       std::stringstream out;
       out << "\n" << SP << "//----  operator " << Name() << "  " << OpName << "\n";
+      if (fVolume) {
+         out << SP << "{\n";
+         out << SP << SP << "const sofie_pool3d_desc d = {" << (fPoolMode == MaxPool ? 0 : 1) << ", " << fShapeX[0] << ", " << fShapeX[1] << ", "
+             << fShapeX[2] << ", " << fShapeX[3] << ", " << fShapeX[4] << ", " << fK3[0] << ", " << fK3[1] << ", " << fK3[2] << ", " << fS3[0]
+             << ", " << fS3[1] << ", " << fS3[2] << ", {" << fP3[0] << ", " << fP3[1] << ", " << fP3[2] << ", " << fP3[3] << ", " << fP3[4]
+             << ", " << fP3[5] << "}, " << fAttr.count_include_pad << "};\n";
+         out << EMIT::Call(SP + SP, "sofie_cuda_pool3d_f32(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ")");
+         out << SP << "}\n";
+         return out.str();
+      }
       if (fType == ETensorType::UINT8) {
          out << EMIT::Call(SP, "sofie_cuda_maxpool2d_u8(fStream, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ", " +
                                   std::to_string(fShape4[0]) + ", " + std::to_string(fShape4[1]) + ", " + std::to_string(fShape4[2]) +

@@ -314,6 +314,7 @@ public:
    std::vector<std::vector<size_t>> ShapeInference(std::vector<std::vector<size_t>> input) override
    {
       fAttr.Resolve(input[0], input[1]);
+      if (fAttr.volume) throw std::runtime_error("SOFIE QLinearConv Op: 3-D quantised convolutions are not generated");
       return {fAttr.OutputShape(input[0], input[1])};
    }
    void Initialize(RModel &model) override

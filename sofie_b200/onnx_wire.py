@@ -304,7 +304,7 @@ def model_to_onnx(m, fp8_scales=None, batch_param=None) -> bytes:
             ins = [L["X"], init(L["W"])] + ([init(L["B"])] if L.get("B") else [])
             nodes.append(node("Conv", ins, [L["Y"]], [attr_ints("kernel_shape", L["kernel"]), attr_ints("pads", L["pads"]),
                                                       attr_ints("strides", L["strides"]), attr_int("group", L.get("group", 1)),
-                                                      attr_ints("dilations", (1, 1))]))
+                                                      attr_ints("dilations", L.get("dilations", (1,) * len(L["kernel"])))]))
         elif op == "ConvTranspose":
             ins = [L["X"], init(L["W"])] + ([init(L["B"])] if L.get("B") else [])
             nodes.append(node("ConvTranspose", ins, [L["Y"]],

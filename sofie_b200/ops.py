@@ -102,6 +102,27 @@ def pool2d_f32(X, *, mode=0, kernel=(2, 2), stride=(2, 2), pads=(0, 0, 0, 0), co
     return Y
 
 
+def pool3d_f32(X, *, mode=0, kernel=(2, 2, 2), stride=(2, 2, 2), pads=(0, 0, 0, 0, 0, 0), count_include_pad=0):
+    """MaxPool (mode 0) / AveragePool (mode 1) of [N, C, D, H, W]; pads = (d, h, w begin, d, h, w end)."""
+    N, Cc, D, H, W = X.shape
+    o = [-(-(e + pads[i] + pads[i + 3] - kernel[i] + 1) // stride[i]) for i, e in enumerate((D, H, W))]
+    Y = torch.empty((N, Cc, *o), dtype=torch.float32, device=X.device)
+    d = capi.Pool3dDesc(mode, N, Cc, D, H, W, *kernel, *stride, (capi.i32 * 6)(*pads), count_include_pad)
+    capi.call("sofie_cuda_pool3d_f32", _stream(), C.byref(d), _p(X), _p(Y))
+    return Y
+
+
+def conv3d_f32(X, W, bias=None, *, pad=(0, 0, 0), stride=(1, 1, 1), dil=(1, 1, 1), group=1, relu=False):
+    """X [N, C, D, H, W], W [Cout, C/group, kD, kH, kW] -> [N, Cout, oD, oH, oW]."""
+    N, Cin, D, H, Wd = X.shape
+    Cout, _, kD, kH, kW = W.shape
+    o = [(e + 2 * pad[i] - (dil[i] * (k - 1) + 1)) // stride[i] + 1 for i, (e, k) in enumerate(((D, kD), (H, kH), (Wd, kW)))]
+    Y = torch.empty((N, Cout, *[max(v, 0) for v in o]), dtype=torch.float32, device=X.device)
+    d = capi.Conv3dDesc(N, Cin, D, H, Wd, Cout, kD, kH, kW, *pad, *stride, *dil, group, int(relu))
+    capi.call("sofie_cuda_conv3d_f32", _stream(), C.byref(d), _p(X), _p(W), _p(bias) if bias is not None else None, _p(Y))
+    return Y
+
+
 def softmax_f32(X, axis=-1):
     axis = axis % X.dim()
     outer = int(np.prod(X.shape[:axis], dtype=np.int64))

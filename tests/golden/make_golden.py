@@ -27,7 +27,7 @@ sys.path.insert(0, str(ROOT))
 from sofie_b200 import onnx_wire as ow  # noqa: E402
 
 CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutPadding", "ConvWithAutopadSameLower",
-         "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "AvgPool", "Softmax1d", "Softmax2d",
+         "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "MaxPool3d", "AvgPool", "Softmax1d", "Softmax2d",
          "Softmax3d", "Softmax4d", "Einsum_matmul",
          # elementwise family
          "LinearWithSelu", "LinearWithSigmoid", "LinearWithLeakyRelu", "Add", "Sub", "Mul", "Div", "Neg", "Exp", "Log", "Elu",

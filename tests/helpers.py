@@ -54,6 +54,9 @@ class OracleBackend:
     def pool(self, X, mode, kernel, stride, pads, count_include_pad=0):
         return self.o.pool2d_f32(X, mode, kernel, stride, pads, count_include_pad)
 
+    def pool3d(self, X, mode, kernel, stride, pads, count_include_pad=0):
+        return self.o.pool3d_f32(X, mode, kernel, stride, pads, count_include_pad)
+
     def softmax(self, X, axis):
         return self.o.softmax_f32(X, axis)
 
@@ -94,6 +97,10 @@ class CudaBackend:
 
     def pool(self, X, mode, kernel, stride, pads, count_include_pad=0):
         return self.ops.pool2d_f32(self._d(X), mode=mode, kernel=kernel, stride=stride, pads=pads,
+                                   count_include_pad=count_include_pad).cpu().numpy()
+
+    def pool3d(self, X, mode, kernel, stride, pads, count_include_pad=0):
+        return self.ops.pool3d_f32(self._d(X), mode=mode, kernel=kernel, stride=stride, pads=pads,
                                    count_include_pad=count_include_pad).cpu().numpy()
 
     def softmax(self, X, axis):
@@ -168,7 +175,10 @@ def run_fixture(name, manifest, arrays, backend):
                 y = y[:, :, 0, :]
         elif op in ("MaxPool", "AveragePool"):
             X = t[ins[0]]
-            if X.ndim == 3:   # a 1-D pooling is the 2-D one with a height of 1
+            if X.ndim == 5:
+                y = backend.pool3d(X, 0 if op == "MaxPool" else 1, tuple(a["kernel_shape"]), tuple(a.get("strides", [1, 1, 1])),
+                                   tuple(a.get("pads", [0] * 6)), a.get("count_include_pad", 0))
+            elif X.ndim == 3:   # a 1-D pooling is the 2-D one with a height of 1
                 p1 = a.get("pads", [0, 0])
                 y = backend.pool(X[:, :, None, :], 0 if op == "MaxPool" else 1, (1, a["kernel_shape"][0]), (1, a.get("strides", [1])[0]),
                                  (0, p1[0], 0, p1[1]), a.get("count_include_pad", 0))[:, :, 0, :]
@@ -196,7 +206,7 @@ def run_fixture(name, manifest, arrays, backend):
 UNARY_FIXTURE_OPS = ("Sigmoid", "Tanh", "LeakyRelu", "Selu", "Elu", "Neg", "Exp", "Log", "Sqrt", "Reciprocal", "Abs", "Erf", "Swish", "Cos", "Sin")
 
 FIXTURE_CASES = ["Linear_16", "Linear_32", "Linear_64", "ConvWithPadding", "ConvWithoutPadding",
-                 "ConvWithAutopadSameLower", "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "AvgPool",
+                 "ConvWithAutopadSameLower", "ConvWithStridesPadding", "ConvWithStridesNoPadding", "MaxPool2d", "MaxPool3d", "AvgPool",
                  "Softmax1d", "Softmax2d", "Softmax3d", "Softmax4d", "Einsum_matmul",
                  "LinearWithSelu", "LinearWithSigmoid", "LinearWithLeakyRelu", "Add", "Sub", "Mul", "Div", "Neg", "Exp", "Log",
                  "Elu", "Tanh", "Sqrt", "Reciprocal",

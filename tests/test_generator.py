@@ -331,10 +331,10 @@ def test_conv1d_is_emitted_as_an_image_of_height_one():
     assert descs[0] == [3, 2, 1, 10, 4, 1, 2, 0, 1, 1, 1, 1, 1, 1, 0, 0, 0, 1, 0]
     assert descs[1] == [3, 4, 1, 11, 8, 1, 3, 0, 1, 1, 1, 1, 1, 2, 0, 0, 0, 1, 0]     # kernel 2 with pad 1 lengthens the axis to 11
     assert "sofie_cuda_relu_f32(" not in text                                          # both Relus are fused
-    with pytest.raises(RuntimeError, match="1-D and 2-D"):
-        w = np.zeros((2, 2, 3, 3, 3), np.float32)
-        generated.emit(onnx_wire.model("g", [onnx_wire.node("Conv", ["x", "w"], ["y"])], [onnx_wire.value_info("x", 1, [1, 2, 5, 5, 5])],
-                                       [onnx_wire.value_info("y", 1, [])], [onnx_wire.tensor("w", w)]), "conv3d_refused")
+    with pytest.raises(RuntimeError, match="rank-3, rank-4 and rank-5"):               # a 4-D convolution has no operator
+        w = np.zeros((2, 2, 3, 3, 3, 3), np.float32)
+        generated.emit(onnx_wire.model("g", [onnx_wire.node("Conv", ["x", "w"], ["y"])], [onnx_wire.value_info("x", 1, [1, 2, 5, 5, 5, 5])],
+                                       [onnx_wire.value_info("y", 1, [])], [onnx_wire.tensor("w", w)]), "conv4d_refused")
 
 
 def test_stacked_matmul_is_one_batched_gemm_call():
@@ -371,3 +371,17 @@ def test_sharded_helper_compiles_against_a_run_time_batch_session():
     m, _ = configs.cnn_i8(batch=8, with_input=False)
     exe, dat = build_sharded_program(m, "c5_sharded")
     assert exe.exists() and dat.exists()
+
+
+def test_volume_operators_emit_3d_calls():
+    """Rank-5 tensors: Conv (+ fused Relu) and MaxPool emit the 3-D entry points; nothing is folded into a 2-D call."""
+    m, _ = configs.volume_f32(batch=2)
+    text = _emit(m, "volume_b2").read_text()
+    assert text.count("sofie_cuda_conv3d_f32(") == 2 and text.count("sofie_cuda_pool3d_f32(") == 1
+    assert "sofie_cuda_conv2d_f32(" not in text and "sofie_cuda_relu_f32(" not in text
+    descs = re.findall(r"sofie_conv3d_desc d = \{([^}]*)\}", text)
+    assert [int(v) for v in descs[0].split(",")] == [2, 2, 6, 8, 10, 8, 3, 3, 3, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1]
+    assert [int(v) for v in descs[1].split(",")] == [2, 8, 3, 4, 5, 4, 2, 3, 1, 0, 0, 0, 1, 2, 1, 1, 1, 1, 2, 0]
+    pool = re.search(r"sofie_pool3d_desc d = \{([^;]*)\};", text).group(1)
+    assert [int(v) for v in re.findall(r"-?\d+", pool)] == [0, 2, 8, 6, 8, 10, 2, 2, 2, 2, 2, 2, 0, 0, 0, 0, 0, 0, 0]
+    generated.compile_session(_emit(m, "volume_b2"), "volume_b2")

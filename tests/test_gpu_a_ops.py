@@ -300,6 +300,32 @@ def test_pool2d_f32_window_2x2_stride_2(mode, shape):
     np.testing.assert_array_equal(y2, ref)
 
 
+@pytest.mark.parametrize("stride,pad,dil,group,relu,bias", [((1, 1, 1), (1, 1, 1), (1, 1, 1), 1, True, True),
+                                                            ((2, 1, 1), (1, 0, 2), (1, 2, 1), 2, False, True),
+                                                            ((1, 2, 3), (0, 0, 0), (1, 1, 1), 4, False, False)])
+def test_conv3d_f32(stride, pad, dil, group, relu, bias):
+    rng = np.random.default_rng(21)
+    X = rng.standard_normal((3, 4, 5, 6, 7)).astype(np.float32)
+    W = (rng.standard_normal((8, 4 // group, 3, 2, 3)) / 6).astype(np.float32)
+    b = rng.standard_normal(8).astype(np.float32) if bias else None
+    ref = o.conv3d_f32(X, W, b, pad=pad, stride=stride, dil=dil, group=group, relu=relu)
+    y = ops.conv3d_f32(dev(X), dev(W), None if b is None else dev(b), pad=pad, stride=stride, dil=dil, group=group, relu=relu).cpu().numpy()
+    assert y.shape == ref.shape and rel_err(y, ref) <= FP32_TOL
+    assert ops.conv3d_f32(torch.zeros((0, 4, 5, 6, 7), device="cuda"), dev(W), group=group).shape[0] == 0
+    with pytest.raises(capi.SofieCudaError):                                        # kernel larger than the padded input
+        ops.conv3d_f32(torch.zeros((1, 4, 1, 1, 1), device="cuda"), dev(W), group=group)
+
+
+@pytest.mark.parametrize("mode,k,s,pads,cip", [(0, (2, 2, 2), (2, 2, 2), (0,) * 6, 0), (0, (3, 2, 2), (1, 2, 1), (1, 0, 1, 0, 1, 0), 0),
+                                               (1, (2, 2, 2), (2, 2, 2), (0,) * 6, 0), (1, (3, 3, 3), (2, 2, 2), (1,) * 6, 0),
+                                               (1, (3, 3, 3), (2, 2, 2), (1,) * 6, 1)])
+def test_pool3d_f32(mode, k, s, pads, cip):
+    X = np.random.default_rng(22).standard_normal((2, 3, 6, 5, 7)).astype(np.float32)
+    ref = o.pool3d_f32(X, mode, k, s, pads, cip)
+    y = ops.pool3d_f32(dev(X), mode=mode, kernel=k, stride=s, pads=pads, count_include_pad=cip).cpu().numpy()
+    assert y.shape == ref.shape and rel_err(y, ref) <= 1e-6
+
+
 @pytest.mark.parametrize("shape,axis", [((3,), 0), ((1, 3), 1), ((2, 3, 4), 1), ((2, 3, 4, 2), -2), ((64, 10), -1),
                                         ((5, 1000), 1), ((4, 7, 33), 0),
                                         ((1000, 10), 1), ((257, 32), 1), ((300, 1), 1),      # short rows: 256 rows per block, a ragged last block

@@ -45,6 +45,15 @@ def test_generated_decoder_with_product_form_conv_transpose(cuda_device):
     assert rel_err(y1, run_model.run(m, x).ravel()) <= 1e-5
 
 
+def test_generated_volume_network(cuda_device):
+    """Conv3d + Relu, MaxPool3d, grouped strided Conv3d through the emitted Session, against the oracle."""
+    m, x = configs.volume_f32(batch=3)
+    s = generated.session_from_model(m, "volume_b3")
+    y1 = s.infer(x)
+    assert np.array_equal(y1, s.infer(x))
+    assert rel_err(y1, run_model.run(m, x).ravel()) <= 1e-5
+
+
 def test_generated_int8_sessions_bit_exact(cuda_device):
     m, x = configs.mlp_i8(batch=512)
     y = generated.session_from_model(m, "c3_b512").infer(x)
