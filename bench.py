@@ -15,7 +15,7 @@ Multi-GPU (torchrun, one process per GPU): the batch of 16384 images is split in
 rank; every rank builds its own Session for its shard (weights replicated), there is no collective on the data
 path, and the job's throughput is the whole batch over the slowest rank's time: strong scaling.
 
-With one GPU the line also carries `per_config` (C1..C5 at their BASELINE sizes) and `large_batch` (C3 at 2^18
+With one GPU the line also carries `per_config` (C1..C5 at their BASELINE sizes) and `large_batch` (C1 and C3 at 2^18
 rows, C2 at 8192 images), each with value, e2e from pinned and from pageable memory, the dominant contraction's
 roofline fraction and -- where the CPU baseline leg ran -- the comparison of the GPU result with the CPU result
 on the baseline's sample, and `hbm_ops`: the memory-bound operators of the path (Relu, Softmax, MaxPool, (de)quantise,
@@ -412,12 +412,17 @@ class Measured:
         self.gen.close()
 
 
+NOMINAL_BF16_TFLOPS = 2250.0  # B200 dense bf16, datasheet; the other dtypes scale from it as they do from the measured number
+
+
 def roofline_of(workload, ops, shard_batch, pk):
     dom = max(ops, key=lambda o: o["flops"])
     tpeak = tensor_peak_tflops(workload, pk)
     achieved = dom["flops"] / (dom["ms"] * 1e-3) / 1e12
     traffic, source = dram_traffic(workload, dom["title"], shard_batch)
+    nominal = tpeak / pk["bf16_tflops"] * NOMINAL_BF16_TFLOPS
     return dict(bound="tensor", kernel=dom["title"], achieved=achieved, peak=tpeak, unit="TFLOP/s", frac=achieved / tpeak,
+                peak_nominal=nominal, frac_nominal=achieved / nominal,
                 traffic=traffic, traffic_source=source, kernel_ms=dom["ms"], flops_per_launch=dom["flops"],
                 peak_basis=f"{pk['source']} bf16 {pk['bf16_tflops']} TFLOP/s (burst) scaled to the dtype: fp32 as 3xTF32 = bf16/6, int8 and FP8 = 2 x bf16",
                 timing="the library's device timers (CUDA events around every operator of the emitted Launch(), in a captured graph), mean of the repetitions, each after an L2 flush")
@@ -495,7 +500,7 @@ def side_config(workload, batch, steps, warmup, flush, pk, with_cpu, tag):
         tflops=me.model.flops_per_sample * B * steps / (dev_ms * 1e-3) / 1e12,
         e2e=B * steps / (e2e_ms * 1e-3), e2e_pageable=B * max(2, steps // 2) / (e2e_pg_ms * 1e-3),
         h2d_bytes_per_step=int(me.x_pinned.numel() * 4), d2h_bytes_per_step=int(me.gen.out_elems * 4),
-        roofline={k: v for k, v in roofline_of(workload, ops, B, pk).items() if k in ("kernel", "kernel_ms", "frac", "achieved", "peak", "unit", "traffic")},
+        roofline={k: v for k, v in roofline_of(workload, ops, B, pk).items() if k in ("kernel", "kernel_ms", "frac", "frac_nominal", "achieved", "peak", "unit", "traffic")},
         layer_ms={o["title"]: round(o["ms"], 5) for o in ops}, gpu_launches_per_step=me.kernel_launches(),
     )
     mem = memory_bound_ops(ops, me.model, pk)
@@ -594,7 +599,7 @@ def run(args, rank, world, local_rank):
                     line["per_config"][w] = side_config(w, None, k if w != "C4" else 3, 3, flush, pk, not args.no_cpu_baseline, "")
                 except Exception as e:  # one configuration failing must not take the headline with it
                     line["per_config"][w] = dict(error=f"{type(e).__name__}: {e}")
-            for w, b in (("C3", 1 << 18), ("C2", 8192)):
+            for w, b in (("C1", 1 << 18), ("C3", 1 << 18), ("C2", 8192)):
                 try:
                     line["large_batch"][f"{w}@{b}"] = side_config(w, b, 5, 3, flush, pk, False, "_large")
                 except Exception as e:
