@@ -2,8 +2,9 @@
 
 csrc/        hand-written sm_100a kernels and the C ABI (include/sofie_cuda.h)
 capi, ops    ctypes binding of the C ABI, operator calls on torch CUDA tensors
-runner       Python mirror of the emitted Session (plan, upload, graph, infer)
+generated    emits, compiles and loads the C++ Session the generator writes for a model
+host/        the C++ generator (RModelParser_ONNX, RModel, ROperator_*): the planner of this package
 configs      the five seeded benchmark configurations
 onnx_wire    protobuf-free ONNX reader / writer
 """
-__all__ = ["capi", "ops", "runner", "configs", "onnx_wire"]
+__all__ = ["capi", "ops", "generated", "configs", "onnx_wire"]

@@ -5,7 +5,7 @@ has a fixed seed; one numpy PCG64 generator per configuration draws, in this ord
 layer by layer (weight then bias / scales of a layer), then the input. A model is a list of
 layer records using ONNX operator vocabulary (Gemm, Conv, Relu, MaxPool, Flatten, QuantizeLinear,
 QLinearMatMul, QLinearConv, DequantizeLinear, plus the FP8 Gemm chain) and a dict of numpy
-weights. The same records feed the ONNX writer, the C-ABI model runner and the CPU oracle.
+weights. The same records feed the ONNX writer (and through it the C++ generator) and the CPU oracle.
 """
 from __future__ import annotations
 

@@ -1,9 +1,10 @@
-"""Python mirror of the emitted Session for models described by sofie_b200.configs.Model.
+"""Test infrastructure: a Python mirror of the emitted Session for models described by sofie_b200.configs.Model.
 
 It does what the generated C++ Session does -- plan once (operator fusion, NHWC layout between
 convolutions, weight repacking, requantisation tables), upload weights once, then run infer() as
-a fixed sequence of libSOFIE_cuda calls that is captured into a CUDA graph -- but drives the C ABI
-from Python so that tests and the benchmark can build models without a C++ compile step.
+a fixed sequence of libSOFIE_cuda calls -- but drives the C ABI from Python, so that tests can reach
+the intermediate tensors of a model and force layouts the generator would not choose. The product's
+planner is the C++ generator (sofie_b200/host); nothing outside tests/ imports this file.
 torch supplies device memory, streams and graph capture only.
 
 Reference behaviour mirrored: Session construction loads weights, infer(float*) returns a new
@@ -14,9 +15,8 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from . import ops
-from . import capi
-from .capi import LAYOUT_NCHW, LAYOUT_NHWC
+from sofie_b200 import capi, ops
+from sofie_b200.capi import LAYOUT_NCHW, LAYOUT_NHWC
 
 # Largest batch that goes to the fused MLP kernel: it computes with fp32 FMA out of shared memory, which beats one
 # tensor-core GEMM launch per layer only while those launches are latency bound (measured cross-over between 2048
@@ -34,7 +34,7 @@ class Step:
 class Session:
     def __init__(self, model, device=0, fp8_scales=None, use_graph=True, nhwc=True):
         if not torch.cuda.is_available():
-            raise RuntimeError("sofie_b200.runner.Session needs a CUDA device: there is no CPU path")
+            raise RuntimeError("the mirror Session needs a CUDA device: there is no CPU path")
         self.model = model
         self.dev = torch.device("cuda", device)
         self.use_graph = use_graph

@@ -74,7 +74,8 @@ def test_no_gpu_means_loud_failure_not_cpu_fallback():
     ctx = C.c_void_p()
     rc = lib.sofie_cuda_ctx_create(C.byref(ctx), 0, 1 << 20)
     assert rc != capi.OK and not ctx.value
-    from sofie_b200 import configs, runner
+    import mirror_session as runner
+    from sofie_b200 import configs
     m, _ = configs.mlp_f32(batch=4)
     with pytest.raises(RuntimeError):
         runner.Session(m)

@@ -1,5 +1,5 @@
 """Whole-configuration parity on the GPU: the five seeded configurations run through the C ABI
-(sofie_b200.runner.Session = the Python mirror of the emitted Session) against
+(tests/mirror_session.py = a Python mirror of the emitted Session) against
   - the reference's own emitted CPU code (stored outputs, tests/golden/ref_outputs.npz) for the fp32
     configurations at their full sizes,
   - the CPU oracle at sizes it finishes in seconds for the int8 / FP8 configurations, and
@@ -10,7 +10,8 @@ import torch
 
 from helpers import GOLDEN, rel_err
 from oracle import build_ref, run_model
-from sofie_b200 import configs, runner
+import mirror_session as runner
+from sofie_b200 import configs
 
 pytestmark = pytest.mark.gpu
 REF = np.load(GOLDEN / "ref_outputs.npz")

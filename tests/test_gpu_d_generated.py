@@ -99,7 +99,7 @@ def test_binary_weight_file_gives_the_same_session(cuda_device, tmp_path):
 
 
 def test_fp8_chain_through_generated_session(cuda_device):
-    from sofie_b200 import runner
+    import mirror_session as runner
     m, x = configs.gemm_chain_fp8(rows=512, width=512, layers=3)
     scales = configs.calibrate_fp8_scales(m, x)
     y = generated.session_from_model(m, "c4_r512", binary=True, fp8_scales=scales).infer(x)
