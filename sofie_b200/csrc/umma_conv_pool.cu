@@ -14,14 +14,16 @@
 // the accumulator of the one before it.
 //
 // Operand A without im2col: the haloed input patch of a tile (34 rows x 18 columns) is fetched once per
-// tile and channel plane (16 bytes of channels) as two TMA boxes, one with the patch's even columns and
-// one with its odd columns (the image is addressed as [N][H][W/2][2][C], so a column parity is a
-// coordinate, not a stride). In shared memory a box is [patch row][9 columns][16 bytes]; the eight
-// windows of one tile row and one column parity are then eight consecutive 16-byte rows = one core
-// matrix of the no-swizzle K-major layout, the next tile row of windows is two patch rows further
-// (the stride between 8-row groups), and the next 16 bytes of K are the next plane (the leading byte
-// offset). For tap (r,s) and position (dy,dx) the operand is therefore the SAME bytes read from the
-// start address  box((dx+s) & 1) + ((dy+r) * 9 + ((dx+s) >> 1)) * 16 : 36 addresses, no copies.
+// tile as two TMA boxes, one with the patch's even columns and one with its odd columns (the image is
+// addressed as [N][H][W/2][2][C], so a column parity is a coordinate, not a stride). In shared memory a box
+// is [patch row][9 columns][C bytes], written with the swizzle of C-byte rows (C = 32 or 64); the eight
+// windows of one tile row and one column parity are then eight consecutive rows = one 8-row group of the
+// K-major swizzled layout, the next tile row of windows is two patch rows further (the stride between
+// 8-row groups), and the next 32 bytes of K are 32 bytes further in the row. For tap (r,s) and position
+// (dy,dx) the operand is therefore the SAME bytes read from the start address
+//     box((dx+s) & 1) + ((dy+r) * 9 + ((dx+s) >> 1)) * C : 36 addresses, no copies
+// (a descriptor may start at any row of a swizzled region: the swizzle is a function of the absolute
+// shared-memory address on TMA's side and on the MMA's, see make_smem_desc_rows).
 // Taps outside the image are the TMA zero fill (the input zero point must be 0, as in umma_conv.cu).
 // All 9 x Cin x Cout weights stay in shared memory. No load uses cluster multicast.
 //
@@ -44,10 +46,9 @@ namespace {
 constexpr int kPoolTileH = 32, kPoolTileW = 16;          // output pixels per tile (one image region)
 constexpr int kPoolRows = kPoolTileH + 2;                // patch rows including the halo
 constexpr int kPoolCols = 9;                             // columns of one parity in the patch
-constexpr int kPoolRowPitch = kPoolCols * 16;            // bytes between patch rows inside a box
-constexpr int kPoolBox = kPoolRows * kPoolRowPitch;      // bytes one box delivers (4896)
-constexpr int kPoolBoxStride = (kPoolBox + 127) / 128 * 128; // TMA destinations are 128-byte aligned (4992)
-constexpr int kPoolPlaneStride = 2 * kPoolBoxStride;     // the two parities of one plane
+constexpr int kPoolBoxPixels = kPoolRows * kPoolCols;    // pixels one box (one column parity of the patch) delivers
+// bytes between the two boxes of a stage: a multiple of 1024, the period of the widest swizzle pattern
+__host__ __device__ constexpr int pool_box_stride(int pixel_bytes) { return (kPoolBoxPixels * pixel_bytes + 1023) / 1024 * 1024; }
 constexpr int kPoolMaxStages = 4;
 constexpr int kPoolThreads = 21 * 32;
 constexpr int kPoolEpiWarps = 16;              // warps 2..17, two groups of eight
@@ -89,7 +90,7 @@ struct PoolConvParams {
    int tilesH, tilesW, num_tiles;
    int stages;
    uint32_t w_bytes;      // all weights
-   uint32_t stage_bytes;  // one patch: planes x kPoolPlaneStride
+   uint32_t stage_bytes;  // one patch: the boxes of its two column parities
    const float *mult;
    const int32_t *qbias;
    int y_zp, relu;
@@ -202,7 +203,9 @@ __global__ void __launch_bounds__(kPoolThreads, 1)
 umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, PoolConvParams p,
                           uint32_t *status)
 {
-   constexpr int PLANES = 2 * KPS;
+   constexpr int PB = 32 * KPS;                             // bytes of channels per pixel (C of int8): a box row, one swizzle span
+   static_assert(PB == 32 || PB == 64 || PB == 128, "a pixel is one swizzle span");
+   constexpr uint32_t BOX_STRIDE = pool_box_stride(PB);
    constexpr int CBK = KPS * 32 >= 128 ? 128 : KPS * 32;    // bytes of one weight row chunk (selects the swizzle)
    constexpr int CHUNKS = KPS * 32 / CBK;
    constexpr uint32_t B_TILE = BN * CBK;
@@ -271,17 +274,18 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
          const int h0 = (rem / p.tilesW) * kPoolTileH, w0 = (rem % p.tilesW) * kPoolTileW;
          if (lane == 0) {
             ok = mbar_wait(&empty_bar[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g);
-            if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)(2 * PLANES) * kPoolBox);
+            if (ok) mbar_expect_tx(&full_bar[s], (uint32_t)(2 * kPoolBoxPixels * PB));
          }
          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
          if (!ok) break;
-         if (lane < 2 * PLANES) {
+         if (lane < 2) {
             // box b = 0: patch columns w0-1, w0+1, ... (odd image columns, from pair w0/2 - 1);
             // box b = 1: patch columns w0, w0+2, ...   (even image columns, from pair w0/2).
-            const int plane = lane >> 1, b = lane & 1;
+            // A box row is one pixel with all its PB bytes of channels, written with the swizzle of that row length.
+            const int b = lane;
             asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-                         ::"r"(smem_u32(slots + (size_t)s * p.stage_bytes + (size_t)plane * kPoolPlaneStride + (size_t)b * kPoolBoxStride)),
-                         "l"(&tmX), "r"(plane * 16), "r"(b ? 0 : 1), "r"(b ? w0 / 2 : w0 / 2 - 1), "r"(h0 - 1), "r"(n),
+                         ::"r"(smem_u32(slots + (size_t)s * p.stage_bytes + (size_t)b * BOX_STRIDE)),
+                         "l"(&tmX), "r"(0), "r"(b ? 0 : 1), "r"(b ? w0 / 2 : w0 / 2 - 1), "r"(h0 - 1), "r"(n),
                          "r"(smem_u32(&full_bar[s]))
                          : "memory");
          }
@@ -301,7 +305,7 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 #pragma unroll
          for (int tap = 0; tap < 9; tap++) {
             const int row = (pos >> 1) + tap / 3, e = (pos & 1) + tap % 3;
-            a_off[tap] = (uint32_t)((e & 1) * kPoolBoxStride + (row * kPoolCols + (e >> 1)) * 16) >> 4;
+            a_off[tap] = (uint32_t)((e & 1) * BOX_STRIDE + (row * kPoolCols + (e >> 1)) * PB) >> 4;
          }
          int s = 0, lt = 0;
          uint32_t ph = 0;
@@ -312,7 +316,9 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
             if (!mbar_wait(&tmem_empty[buf], ((lt >> 1) & 1) ^ 1, &abort_flag, status, kStatusWaitAccum, 0x2000 + lt)) break;
             tc_fence_after();
             const uint32_t d = tmem_base + (uint32_t)(buf * 4 * BN + pos * BN);
-            const uint64_t da0 = make_smem_desc_noswizzle(smem_u32(slots + (size_t)s * p.stage_bytes), kPoolPlaneStride, 2 * kPoolRowPitch);
+            // swizzled K-major rows of PB bytes; the eight windows of a tile row are eight consecutive pixels of a box row, the
+            // next tile row of windows is two patch rows further (make_smem_desc_rows: any start row, any group stride)
+            const uint64_t da0 = make_smem_desc_rows(smem_u32(slots + (size_t)s * p.stage_bytes), PB, 2 * kPoolCols * PB);
             const uint32_t a_hi_word = (uint32_t)(da0 >> 32), a_lo_word = (uint32_t)da0;
 #pragma unroll
             for (int tap = 0; tap < 9; tap++) {
@@ -321,7 +327,7 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
                   const int kb = kk * 32;
                   const uint32_t b16 = (uint32_t)((tap * CHUNKS + kb / CBK) * B_TILE + kb % CBK) >> 4;
                   const uint64_t bdesc = ((uint64_t)b_hi_word << 32) | (uint64_t)(b_lo_word + b16);
-                  const uint64_t adesc = ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + a_off[tap] + (uint32_t)((kk * 2 * kPoolPlaneStride) >> 4));
+                  const uint64_t adesc = ((uint64_t)a_hi_word << 32) | (uint64_t)(a_lo_word + a_off[tap] + (uint32_t)(kk * 2));
                   tc_mma<kI8>(d, adesc, bdesc, idesc, (tap | kk) ? 1u : 0u);
                }
             }
@@ -560,7 +566,7 @@ int launch_pool_conv(cudaStream_t s, const ConvGeom &g, const uint8_t *X, const 
    p.tilesW = g.W / kPoolTileW;
    p.num_tiles = g.N * p.tilesH * p.tilesW;
    p.w_bytes = (uint32_t)(9 * CHUNKS * BN * CBK);
-   p.stage_bytes = (uint32_t)(2 * KPS * kPoolPlaneStride);
+   p.stage_bytes = (uint32_t)(2 * pool_box_stride(32 * KPS));
    p.stages = (int)((200 * 1024 - (long)p.w_bytes) / (long)p.stage_bytes);
    if (p.stages > kPoolMaxStages) p.stages = kPoolMaxStages;
    if (p.stages < 2) return -1;
@@ -569,8 +575,8 @@ int launch_pool_conv(cudaStream_t s, const ConvGeom &g, const uint8_t *X, const 
    // the image as [N][H][W/2][2][C]: the parity of a column is a coordinate of its own
    uint64_t xdims[5] = {(uint64_t)g.C, 2u, (uint64_t)g.W / 2, (uint64_t)g.H, (uint64_t)g.N};
    uint64_t xstr[4] = {(uint64_t)g.C, (uint64_t)2 * g.C, (uint64_t)g.W * g.C, (uint64_t)g.H * g.W * g.C};
-   uint32_t xbox[5] = {16u, 1u, (uint32_t)kPoolCols, (uint32_t)kPoolRows, 1u};
-   int rc = make_tensor_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, X, xdims, xstr, xbox, 0);
+   uint32_t xbox[5] = {(uint32_t)(32 * KPS), 1u, (uint32_t)kPoolCols, (uint32_t)kPoolRows, 1u};
+   int rc = make_tensor_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, X, xdims, xstr, xbox, 32 * KPS);
    if (rc) return rc;
    uint64_t wdims[2] = {(uint64_t)9 * g.C, (uint64_t)g.Cout};
    uint64_t wstr[1] = {(uint64_t)9 * g.C};
