@@ -10,6 +10,8 @@
 // have 16 epilogue warps (warps 2-17: each owns the 32 TMEM lanes its warp id modulo 4 selects and
 // every fourth 32-column chunk); kTF32 has 4 epilogue warps (2-5) and 8 converter warps (6-13) that split
 // every stage into hi / lo. Two TMEM accumulator buffers overlap epilogue and MMAs.
+#include <cstring>
+
 #include "umma.cuh"
 #include <cstdlib>
 #include "contract.cuh"
@@ -36,11 +38,47 @@ EncodeTiledFn encode_tiled_fn()
    return fn;
 }
 
+// A tensor map is a pure function of these arguments, and the launchers ask for the same few maps over and over (every
+// eager launch of a layer: the input parts of a pipelined upload, Sessions with a run-time batch, calls from Python). A
+// small per-thread table keyed by the arguments saves the driver call; a captured graph never comes back here.
+namespace {
+struct TensorMapKey {
+   uint64_t base, dims[5], strides[4];
+   uint32_t box[5];
+   int32_t dtype, rank, swizzle;
+   bool operator==(const TensorMapKey &o) const { return std::memcmp(this, &o, sizeof(*this)) == 0; }
+};
+struct TensorMapSlot {
+   bool used = false;
+   TensorMapKey key;
+   CUtensorMap map;
+};
+constexpr int kTensorMapSlots = 128;
+} // namespace
+
 int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank, const void *base, const uint64_t *dims,
                     const uint64_t *strides_bytes, const uint32_t *box, int swizzle_bytes)
 {
    EncodeTiledFn fn = encode_tiled_fn();
    if (!fn) return fail(SOFIE_CUDA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+   if (rank < 1 || rank > 5) return fail(SOFIE_CUDA_ERR_INVALID, "tensor map of rank %d", rank);
+   TensorMapKey key;
+   std::memset(&key, 0, sizeof(key)); // padding included: the key is compared bytewise
+   key.base = reinterpret_cast<uint64_t>(base);
+   key.dtype = (int32_t)dtype, key.rank = rank, key.swizzle = swizzle_bytes;
+   uint64_t h = key.base * 0x9E3779B97F4A7C15ull + (uint64_t)dtype * 31 + (uint64_t)swizzle_bytes;
+   for (int i = 0; i < rank; i++) {
+      key.dims[i] = dims[i];
+      key.box[i] = box[i];
+      if (i > 0) key.strides[i - 1] = strides_bytes[i - 1];
+      h = (h ^ (dims[i] + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2))) * 1099511628211ull + box[i];
+   }
+   thread_local TensorMapSlot table[kTensorMapSlots];
+   TensorMapSlot &slot = table[(h >> 17) % kTensorMapSlots];
+   if (slot.used && slot.key == key) {
+      *map = slot.map;
+      return SOFIE_CUDA_OK;
+   }
    cuuint64_t gdims[5], gstrides[5];
    cuuint32_t gbox[5], estrides[5];
    for (int i = 0; i < rank; i++) {
@@ -57,6 +95,9 @@ int make_tensor_map(CUtensorMap *map, CUtensorMapDataType dtype, int rank, const
                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
    if (r != CUDA_SUCCESS) return fail(SOFIE_CUDA_ERR_INVALID, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+   slot.used = true;
+   slot.key = key;
+   slot.map = *map;
    return SOFIE_CUDA_OK;
 }
 
