@@ -484,14 +484,6 @@ typedef struct sofie_qconv2d_desc {
 } sofie_qconv2d_desc;
 int sofie_cuda_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *desc, const uint8_t *X, const int8_t *W,
                               const float *mult, const int32_t *bias, uint8_t *Y);
-/* QuantizeLinear of a float tensor (scale x_scale, zero point desc->x_zp; the tensor in desc->x_layout) followed by the
- * QLinearConv that reads it, as one call (no counterpart in the reference). Xq is a buffer for the quantised tensor
- * (N*C*H*W bytes): a first layer of the pooled tensor-core kernel's class (one input channel, zero point 0, 3x3 / stride 1 /
- * pad 1 with fused Relu + MaxPool 2x2, H % 32 == 0, W % 16 == 0, Cout a multiple of 16 up to 64) quantises inside the
- * kernel, value by value with the function of sofie_cuda_quantize_u8, and leaves Xq untouched; every other shape runs the
- * two operators one after the other through Xq. Results are identical to the two separate calls. */
-int sofie_cuda_quantize_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *desc, const float *X, float x_scale, uint8_t *Xq,
-                                       const int8_t *W, const float *mult, const int32_t *bias, uint8_t *Y);
 int sofie_cuda_qconv2d_pack_i8(void *stream, const sofie_qconv2d_desc *desc, const int8_t *W, int8_t *Wpacked);
 /* MaxPool 2-D on uint8 (integer max), no padding. */
 int sofie_cuda_maxpool2d_u8(void *stream, const uint8_t *X, uint8_t *Y, int32_t N, int32_t C, int32_t H, int32_t W,

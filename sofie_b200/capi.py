@@ -143,7 +143,6 @@ SIGNATURES = {
     "sofie_cuda_qlinear_matmul_f32": [vp, C.POINTER(QGemmDesc), vp, vp, vp, vp, f32, vp],
     "sofie_cuda_transpose_i8": [vp, vp, vp, i32, i32],
     "sofie_cuda_qlinear_conv2d": [vp, C.POINTER(QConv2dDesc), vp, vp, vp, vp, vp],
-    "sofie_cuda_quantize_qlinear_conv2d": [vp, C.POINTER(QConv2dDesc), vp, C.c_float, vp, vp, vp, vp, vp],
     "sofie_cuda_qconv2d_pack_i8": [vp, C.POINTER(QConv2dDesc), vp, vp],
     "sofie_cuda_maxpool2d_u8": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32],
     "sofie_cuda_nchw_to_nhwc_u8": [vp, vp, vp, i32, i32, i32, i32],

@@ -179,29 +179,6 @@ int sofie_cuda_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *d, const u
                    [&] { return launch_qconv2d_simt(s, g, X, W, mult, bias, d->x_zp, d->y_zp, Y); });
 }
 
-int sofie_cuda_quantize_qlinear_conv2d(void *stream, const sofie_qconv2d_desc *d, const float *X, float x_scale, uint8_t *Xq, const int8_t *W,
-                                       const float *mult, const int32_t *bias, uint8_t *Y)
-{
-   SOFIE_REQUIRE(d && X && Xq && W && mult && Y, "NULL argument");
-   SOFIE_REQUIRE(x_scale > 0.f, "bad quantisation scale");
-   SOFIE_REQUIRE(d->x_zp >= 0 && d->x_zp <= 255 && d->y_zp >= 0 && d->y_zp <= 255, "zero point out of range");
-   ConvGeom g;
-   int rc = conv_geometry(g, d->N, d->C, d->H, d->W, d->Cout, d->kH, d->kW, d->pad_h, d->pad_w, d->stride_h, d->stride_w, 1,
-                          1, 1, d->x_layout, d->y_layout, d->w_packed, d->relu, d->pool);
-   if (rc) return rc;
-   if (d->N == 0) return SOFIE_CUDA_OK;
-   cudaStream_t s = as_stream(stream);
-   // one kernel when the layer is the pooled first-layer kernel's (one input channel, input zero point 0) ...
-   if (d->x_zp == 0 && forced_engine() != SOFIE_ENGINE_SIMT) {
-      rc = launch_qconv2d_umma_first_from_f32(s, g, X, x_scale, W, mult, bias, d->y_zp, Y);
-      if (rc >= 0) return rc;
-   }
-   // ... otherwise the two operators one after the other, through the caller's buffer for the quantised image
-   rc = sofie_cuda_quantize_u8(stream, X, Xq, (size_t)d->N * d->C * d->H * d->W, x_scale, d->x_zp);
-   if (rc) return rc;
-   return sofie_cuda_qlinear_conv2d(stream, d, Xq, W, mult, bias, Y);
-}
-
 int sofie_cuda_gemm_e4m3(void *stream, const sofie_fp8_gemm_desc *d, const uint8_t *A, const uint8_t *W,
                          const float *bias, uint16_t *Ybf16, uint8_t *Yq)
 {

@@ -32,9 +32,6 @@ int launch_qconv2d_umma_pooled(cudaStream_t, const ConvGeom &, const uint8_t *, 
                                int x_zp, int y_zp, uint8_t *);
 // fused chain of small Gemm layers on the tensor cores (umma_mlp.cu): -1 when the widths are not its own
 int launch_mlp_f32_umma(cudaStream_t, const sofie_mlp_desc *, const float *, const float *const *, const float *const *, float *);
-// QuantizeLinear (zero point 0) of a one-channel float image fused into the pooled first-layer kernel: -1 when the shape is not its own
-int launch_qconv2d_umma_first_from_f32(cudaStream_t, const ConvGeom &, const float *, float x_scale, const int8_t *, const float *,
-                                       const int32_t *, int y_zp, uint8_t *);
 // first-layer kernels (conv_first.cu): -1 when the shape is not theirs
 int launch_conv2d_f32_first(cudaStream_t, const ConvGeom &, const float *, const float *, const float *, float *);
 int launch_qconv2d_first(cudaStream_t, const ConvGeom &, const uint8_t *, const int8_t *, const float *, const int32_t *,

@@ -385,6 +385,21 @@ int launch_transpose(cudaStream_t s, const T *in, T *out, int batch, int rows, i
 }
 
 // ---------------------------------------------------------------- (de)quantise, casts ------------
+// q = clamp(rint(x / scale)) + zp with the correctly rounded quotient of the ONNX definition. The IEEE division
+// costs about 25 instructions and made this kernel arithmetic bound at a third of the HBM bandwidth, so the
+// quotient is first taken as x * (1 / scale): that product is within 2 ulp of the true quotient, hence rounds
+// to the same integer unless it lies within a few ulp of a half-integer, and only then (about one element in
+// ten thousand, and every value too large to have a fraction) the exact division decides.
+__device__ __forceinline__ uint8_t quant_u8(float x, float scale, float inv_scale, int zp)
+{
+   const float t = __fmul_rn(x, inv_scale);
+   float r = rintf(t);
+   const float to_half = fabsf(fabsf(t - r) - 0.5f); // distance of t from the nearest half-integer
+   if (!(to_half > fabsf(t) * 1e-6f)) r = rintf(__fdiv_rn(x, scale)); // also taken for NaN and for an infinite 1 / scale
+   r = fminf(fmaxf(r, (float)(0 - zp)), (float)(255 - zp));
+   return (uint8_t)(__float2int_rn(r) + zp);
+}
+
 // Sixteen elements per thread and step: four 16-byte loads in flight, one 16-byte store.
 __global__ void quantize_u8_vec16_kernel(const float *__restrict__ X, uint8_t *__restrict__ Y, size_t n16, float scale, float inv_scale,
                                          int zp)

@@ -361,42 +361,28 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 // Two threads issue (even and odd tiles): a tile's two waits, four MMAs and two commits cost one thread about as long as
 // the tile's epilogue takes, and the thread that issues is the pacemaker of everything behind it.
 //   warp 0 producer | warps 1 and 22 MMA issuers | warps 2..17 epilogue | warps 18..21 operand builders
-// F32IN: the layer reads the FLOAT image and the QuantizeLinear in front of it happens here: the staged rows are floats
-// (box of 24 floats from column w0 - 4), the builders first quantise them (the same function, value by value, as the
-// stand-alone QuantizeLinear kernel) into a small uint8 copy of the patch rows and then build from that copy; the
-// quantised image never exists in device memory.
 constexpr int kFirstRawPitch = 48;                                  // bytes per staged input row
 constexpr int kFirstRawBytes = kPoolRows * kFirstRawPitch;          // 1632
 constexpr int kFirstRawStride = (kFirstRawBytes + 127) / 128 * 128; // 1664
-constexpr int kFirstF32Cols = 24;                                   // floats per staged row of a float image: columns w0-4 .. w0+19
-constexpr int kFirstF32Bytes = kPoolRows * kFirstF32Cols * 4;       // 3264
-constexpr int kFirstF32Stride = (kFirstF32Bytes + 127) / 128 * 128; // 3328
-constexpr int kFirstQBytes = kPoolRows * kFirstF32Cols;             // the quantised copy of those rows: 816 bytes
 constexpr int kFirstABytes = 4 * 2048;                              // four positions x 128 rows x 16 bytes
 constexpr int kFirstStages = 4;
 constexpr int kFirstThreads = 23 * 32;
 constexpr int kFirstBuilderWarp0 = 18;
 constexpr int kFirstIssuerB = 22;
 
-template <int BN, bool F32IN>
+template <int BN>
 __global__ void __launch_bounds__(kFirstThreads, 1)
-umma_qconv3x3_first_pool_kernel(const __grid_constant__ CUtensorMap tmX, const int8_t *__restrict__ W, PoolConvParams p, float x_scale,
-                                float x_inv_scale, uint32_t *status)
+umma_qconv3x3_first_pool_kernel(const __grid_constant__ CUtensorMap tmX, const int8_t *__restrict__ W, PoolConvParams p, uint32_t *status)
 {
-   constexpr int RAW_STRIDE = F32IN ? kFirstF32Stride : kFirstRawStride;
-   constexpr int RAW_BYTES = F32IN ? kFirstF32Bytes : kFirstRawBytes;
-   constexpr int Q_PITCH = F32IN ? kFirstF32Cols : kFirstRawPitch; // bytes per row of what the builders read
-   constexpr int Q_BYTE0 = F32IN ? 3 : 15;                         // byte of patch column 0 in such a row
    constexpr int NBUF = 512 / (4 * BN);                // tiles in flight in tensor memory: 4 (BN = 32) or 2 (BN = 64)
    constexpr uint32_t TMEM_COLS = 512;
    extern __shared__ unsigned char smem_raw[];
    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-   // layout: [A slots: S x 8 KB][raw slots: S x 1664 (3328 for floats)][weights: BN x 16][zeros: 2 KB][F32IN: quantised rows, S x 1 KB]
+   // layout: [A slots: S x 8 KB][raw slots: S x 1664][weights: BN x 16][zeros: 2 KB]
    unsigned char *a_slots = smem;
    unsigned char *raw_slots = a_slots + kFirstStages * kFirstABytes;
-   unsigned char *w_smem = raw_slots + kFirstStages * RAW_STRIDE;
+   unsigned char *w_smem = raw_slots + kFirstStages * kFirstRawStride;
    unsigned char *zeros = w_smem + 1024;
-   unsigned char *q_slots = zeros + 2048;
    __shared__ uint64_t raw_full[kFirstStages], raw_empty[kFirstStages], a_full[kFirstStages], a_empty[kFirstStages], tmem_full[4], tmem_empty[4];
    __shared__ uint32_t tmem_base_holder;
    __shared__ volatile uint32_t abort_flag;
@@ -454,10 +440,10 @@ umma_qconv3x3_first_pool_kernel(const __grid_constant__ CUtensorMap tmX, const i
          uint32_t ph = 0;
          for (int tile = blockIdx.x, g = 0; tile < p.num_tiles; tile += gridDim.x, g++, ring_next(s, ph, S), tw.next()) {
             if (!mbar_wait(&raw_empty[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, g)) break;
-            mbar_expect_tx(&raw_full[s], RAW_BYTES);
-            // box {48 bytes, 34 rows, 1 image} from column w0 - 16 (a 16-byte boundary), row h0 - 1; floats: 24 from column w0 - 4
+            mbar_expect_tx(&raw_full[s], kFirstRawBytes);
+            // box {48 bytes, 34 rows, 1 image} from column w0 - 16 (a 16-byte boundary), row h0 - 1
             asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                         ::"r"(smem_u32(raw_slots + (size_t)s * RAW_STRIDE)), "l"(&tmX), "r"(tw.tw * kPoolTileW - (F32IN ? 4 : 16)),
+                         ::"r"(smem_u32(raw_slots + (size_t)s * kFirstRawStride)), "l"(&tmX), "r"(tw.tw * kPoolTileW - 16),
                          "r"(tw.th * kPoolTileH - 1), "r"(tw.n), "r"(smem_u32(&raw_full[s]))
                          : "memory");
          }
@@ -495,38 +481,22 @@ umma_qconv3x3_first_pool_kernel(const __grid_constant__ CUtensorMap tmX, const i
       // ---------------- operand builders: thread = pooling window (py, px) of the tile ----------------
       const int t = threadIdx.x - kFirstBuilderWarp0 * 32;
       const int px = t & 7, py = t >> 3;
-      // the window's 4 x 4 input bytes: patch rows 2py .. 2py+3, patch columns 2px .. 2px+3; patch column c is byte 15 + c of a staged
-      // row (byte 3 + c of a quantised row when the staged rows are floats)
-      const int byte0 = Q_BYTE0 + 2 * px, word0 = byte0 >> 2, shift = byte0 & 3;   // shift is 1 or 3
+      // the window's 4 x 4 input bytes: patch rows 2py .. 2py+3, patch columns 2px .. 2px+3; patch column c is byte 15 + c of a staged row
+      const int byte0 = 15 + 2 * px, word0 = byte0 >> 2, shift = byte0 & 3;   // shift is 1 or 3
       const uint32_t sel_row = shift == 1 ? 0x4321u : 0x6543u;                 // four bytes starting at byte `shift` of a word pair
       int s = 0;
       uint32_t ph = 0;
       for (int tile = blockIdx.x, g = 0; tile < p.num_tiles; tile += gridDim.x, g++, ring_next(s, ph, S)) {
          if (!mbar_wait(&raw_full[s], ph, &abort_flag, status, kStatusWaitFull, 0x6000 + g)) break;
-         const uint32_t *raw = reinterpret_cast<const uint32_t *>(raw_slots + (size_t)s * RAW_STRIDE);
-         if constexpr (F32IN) {
-            // QuantizeLinear of the staged float rows: 204 groups of four values, one or two per thread
-            uint32_t *q = reinterpret_cast<uint32_t *>(q_slots + (size_t)s * 1024);
-            for (int i = t; i < kFirstQBytes / 4; i += 128) {
-               const float4 v = reinterpret_cast<const float4 *>(raw)[i];
-               q[i] = (uint32_t)quant_u8(v.x, x_scale, x_inv_scale, 0) | ((uint32_t)quant_u8(v.y, x_scale, x_inv_scale, 0) << 8) |
-                      ((uint32_t)quant_u8(v.z, x_scale, x_inv_scale, 0) << 16) | ((uint32_t)quant_u8(v.w, x_scale, x_inv_scale, 0) << 24);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&raw_empty[s]);   // the float rows have been read
-            asm volatile("bar.sync 1, 128;" ::: "memory"); // the four builder warps: every quantised row is written before any is read
-            raw = q;
-         }
+         const uint32_t *raw = reinterpret_cast<const uint32_t *>(raw_slots + (size_t)s * kFirstRawStride);
          uint32_t r[4];
 #pragma unroll
          for (int i = 0; i < 4; i++) {
-            const uint32_t *row = raw + (2 * py + i) * (Q_PITCH / 4) + word0;
+            const uint32_t *row = raw + (2 * py + i) * (kFirstRawPitch / 4) + word0;
             r[i] = __byte_perm(row[0], row[1], sel_row);
          }
          __syncwarp();
-         if constexpr (!F32IN) {
-            if (lane == 0) mbar_arrive(&raw_empty[s]);   // the staged rows are in registers
-         }
+         if (lane == 0) mbar_arrive(&raw_empty[s]);   // the staged rows are in registers
          if (!mbar_wait(&a_empty[s], ph ^ 1, &abort_flag, status, kStatusWaitEmpty, 0x7000 + g)) break;
          unsigned char *a_slot = a_slots + (size_t)s * kFirstABytes + t * 16;
 #pragma unroll
@@ -555,9 +525,8 @@ umma_qconv3x3_first_pool_kernel(const __grid_constant__ CUtensorMap tmX, const i
    }
 }
 
-// F32IN: X is the float image and x_scale the scale of the QuantizeLinear (zero point 0) fused in front of the layer
-template <int BN, bool F32IN>
-int launch_first_pool_conv(cudaStream_t s, const ConvGeom &g, const void *X, float x_scale, const int8_t *W, const float *mult, const int32_t *bias,
+template <int BN>
+int launch_first_pool_conv(cudaStream_t s, const ConvGeom &g, const uint8_t *X, const int8_t *W, const float *mult, const int32_t *bias,
                            int y_zp, uint8_t *Y)
 {
    PoolConvParams p = {};
@@ -568,19 +537,18 @@ int launch_first_pool_conv(cudaStream_t s, const ConvGeom &g, const void *X, flo
    p.stages = kFirstStages;
    p.mult = mult; p.qbias = bias; p.y_zp = y_zp; p.relu = g.relu; p.Y = Y;
    CUtensorMap tmX;
-   constexpr int ES = F32IN ? 4 : 1;
    uint64_t xdims[3] = {(uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.N};
-   uint64_t xstr[2] = {(uint64_t)g.W * ES, (uint64_t)g.H * g.W * ES};
-   uint32_t xbox[3] = {(uint32_t)(F32IN ? kFirstF32Cols : kFirstRawPitch), (uint32_t)kPoolRows, 1u};
-   int rc = make_tensor_map(&tmX, F32IN ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, X, xdims, xstr, xbox, 0);
+   uint64_t xstr[2] = {(uint64_t)g.W, (uint64_t)g.H * g.W};
+   uint32_t xbox[3] = {(uint32_t)kFirstRawPitch, (uint32_t)kPoolRows, 1u};
+   int rc = make_tensor_map(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, X, xdims, xstr, xbox, 0);
    if (rc) return rc;
-   const int smem = kFirstStages * (kFirstABytes + (F32IN ? kFirstF32Stride : kFirstRawStride)) + 1024 + 2048 + (F32IN ? kFirstStages * 1024 : 0) + 1024;
+   const int smem = kFirstStages * (kFirstABytes + kFirstRawStride) + 1024 + 2048 + 1024;
    uint32_t *status = device_status_word(s);
    if (!status) return fail(SOFIE_CUDA_ERR_CUDA, "cannot allocate the device status word");
    const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
-   auto kern = umma_qconv3x3_first_pool_kernel<BN, F32IN>;
+   auto kern = umma_qconv3x3_first_pool_kernel<BN>;
    SOFIE_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kFirstThreads), smem, s, tmX, W, p, x_scale, 1.0f / x_scale, status));
+   SOFIE_CUDA_TRY(launch_dependent(kern, dim3(grid), dim3(kFirstThreads), smem, s, tmX, W, p, status));
    SOFIE_LAUNCH_CHECK("umma_qconv3x3_first_pool_kernel");
    set_last_engine(SOFIE_ENGINE_TCGEN05);
    return SOFIE_CUDA_OK;
@@ -647,32 +615,13 @@ int launch_qconv2d_umma_pooled(cudaStream_t s, const ConvGeom &g, const uint8_t 
       // one input channel: NCHW and NHWC are the same bytes, ONNX and packed weights too; rows must be TMA-addressable
       static const bool first = [] { const char *e = getenv("SOFIE_CUDA_FIRST_TC"); return !e || atoi(e) != 0; }();
       if (!first) return -1;
-      return wide ? umma::launch_first_pool_conv<64, false>(s, g, X, 1.f, W, mult, bias, y_zp, Y)
-                  : umma::launch_first_pool_conv<32, false>(s, g, X, 1.f, W, mult, bias, y_zp, Y);
+      return wide ? umma::launch_first_pool_conv<64>(s, g, X, W, mult, bias, y_zp, Y) : umma::launch_first_pool_conv<32>(s, g, X, W, mult, bias, y_zp, Y);
    }
    switch (g.C) {
    case 32: return wide ? umma::launch_pool_conv<64, 1>(s, g, X, W, mult, bias, y_zp, Y) : umma::launch_pool_conv<32, 1>(s, g, X, W, mult, bias, y_zp, Y);
    case 64: return wide ? umma::launch_pool_conv<64, 2>(s, g, X, W, mult, bias, y_zp, Y) : umma::launch_pool_conv<32, 2>(s, g, X, W, mult, bias, y_zp, Y);
    default: return -1;
    }
-}
-
-// QuantizeLinear (zero point 0, scale x_scale) of a float image with ONE channel fused into the pooled first-layer kernel.
-// Returns -1 when the shape is not that kernel's: the caller then quantises into a buffer and runs the convolution on it.
-int launch_qconv2d_umma_first_from_f32(cudaStream_t s, const ConvGeom &g, const float *X, float x_scale, const int8_t *W, const float *mult,
-                                       const int32_t *bias, int y_zp, uint8_t *Y)
-{
-   static const bool enabled = [] {
-      const char *e = getenv("SOFIE_CUDA_CONV_POOLED"), *f = getenv("SOFIE_CUDA_FIRST_TC"), *q = getenv("SOFIE_CUDA_FIRST_FUSED_QUANT");
-      return (!e || atoi(e) != 0) && (!f || atoi(f) != 0) && (!q || atoi(q) != 0);
-   }();
-   if (!enabled || g.C != 1 || g.pool != 2 || !g.y_nhwc) return -1;
-   if (!(g.kH == 3 && g.kW == 3 && g.pad_h == 1 && g.pad_w == 1 && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1 && g.group == 1)) return -1;
-   if (g.H % umma::kPoolTileH != 0 || g.W % umma::kPoolTileW != 0) return -1;
-   if (g.Cout % 16 != 0 || g.Cout > 64) return -1;
-   if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(Y) & 15)) return -1;
-   return g.Cout > 32 ? umma::launch_first_pool_conv<64, true>(s, g, X, x_scale, W, mult, bias, y_zp, Y)
-                      : umma::launch_first_pool_conv<32, true>(s, g, X, x_scale, W, mult, bias, y_zp, Y);
 }
 
 } // namespace sofie

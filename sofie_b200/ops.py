@@ -341,7 +341,7 @@ def qlinear_matmul_f32(A, W, mult, corr, y_scale, *, w_is_nk=True, y_zp=0, relu=
 
 
 def qlinear_conv2d(X, W, mult, bias=None, *, shape=None, pad=(0, 0), stride=(1, 1), x_zp=0, y_zp=0, relu=False,
-                   pool=0, x_layout=LAYOUT_NCHW, y_layout=LAYOUT_NCHW, w_packed=False, kernel=None, x_scale=None):
+                   pool=0, x_layout=LAYOUT_NCHW, y_layout=LAYOUT_NCHW, w_packed=False, kernel=None):
     N, Cin, H, Wd = shape if shape is not None else X.shape
     if w_packed:
         Cout, kH, kW = W.shape[0], kernel[0], kernel[1]
@@ -354,10 +354,6 @@ def qlinear_conv2d(X, W, mult, bias=None, *, shape=None, pad=(0, 0), stride=(1, 
     Y = torch.empty(yshape, dtype=torch.uint8, device=X.device)
     d = capi.QConv2dDesc(N, Cin, H, Wd, Cout, kH, kW, pad[0], pad[1], stride[0], stride[1], x_layout, y_layout,
                          int(w_packed), int(x_zp), int(y_zp), int(relu), pool)
-    if x_scale is not None:   # X is the float tensor: QuantizeLinear(x_scale, x_zp) happens inside the call
-        Xq = torch.full((N * Cin * H * Wd,), 0xEE, dtype=torch.uint8, device=X.device)
-        capi.call("sofie_cuda_quantize_qlinear_conv2d", _stream(), C.byref(d), _p(X), float(x_scale), _p(Xq), _p(W), _p(mult), _p(bias), _p(Y))
-        return Y
     capi.call("sofie_cuda_qlinear_conv2d", _stream(), C.byref(d), _p(X), _p(W), _p(mult), _p(bias), _p(Y))
     return Y
 

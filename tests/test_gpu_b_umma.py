@@ -204,37 +204,6 @@ def test_qlinear_first_layer_pooled_tcgen05_bit_exact(case):
     assert len(np.unique(ref)) > 20
 
 
-@pytest.mark.parametrize("case", [(3, 64, 64, 32, 1, 0), (2, 32, 48, 16, 0, 7), (150, 64, 64, 32, 1, 3), (5, 96, 32, 64, 1, 0),
-                                  (2, 30, 48, 16, 1, 0), (2, 32, 32, 24, 1, 0)])
-def test_quantize_fused_into_the_first_layer_bit_exact(case):
-    """sofie_cuda_quantize_qlinear_conv2d on a float image: QuantizeLinear inside the pooled first-layer kernel (the first four
-    cases) or, for shapes that kernel does not take (H = 30, Cout = 24), the two operators one after the other through the
-    caller's buffer. Either way bit for bit the oracle's QuantizeLinear followed by its QLinearConv + MaxPool, on values that
-    sit on and around the rounding ties of the quantisation."""
-    N, H, W, Cout, relu, y_zp = case
-    ops.set_engine(0)
-    rng = np.random.default_rng(sum(case) + 1)
-    x_scale = 0.0371
-    Xf = (rng.exponential(1.0, (N, 1, H, W)) * (rng.random((N, 1, H, W)) < 0.3)).astype(np.float32)
-    ties = ((np.arange(H * W) % 300) + 0.5).astype(np.float32) * np.float32(x_scale)      # x / scale within an ulp of k + 0.5
-    Xf[0, 0] = ties.reshape(H, W)
-    Xf[-1, 0, 0, :] = 1e9                                                                  # saturates to 255 next to the padding
-    Xf[-1, 0, 1, :] = -3.0                                                                 # clamps to 0
-    Xq = o.quantize_u8(Xf, x_scale, 0)
-    Wt = rng.integers(-127, 128, (Cout, 1, 3, 3)).astype(np.int8)
-    ws = rng.uniform(0.001, 0.01, Cout).astype(np.float32)
-    bias = rng.integers(-300, 300, Cout).astype(np.int32)
-    y_scale = x_scale * 0.005 * 127 * 6
-    ref = o.maxpool2d_u8(o.qlinear_conv2d(Xq, x_scale, 0, Wt, ws, y_scale, y_zp, bias=bias, pad=(1, 1), relu=bool(relu)))
-    mult = dev(o.requant_multiplier(x_scale, ws, y_scale))
-    y = ops.qlinear_conv2d(dev(Xf), dev(Wt), mult, dev(bias), shape=Xf.shape, pad=(1, 1), x_zp=0, y_zp=y_zp, relu=bool(relu), pool=2,
-                           x_layout=0, y_layout=1, w_packed=False, x_scale=x_scale)
-    assert np.array_equal(y.cpu().numpy().transpose(0, 3, 1, 2), ref)
-    if H % 32 == 0 and Cout % 16 == 0:
-        assert ops.last_engine() == capi.ENGINE_TCGEN05
-    assert len(np.unique(ref)) > 20
-
-
 @pytest.mark.parametrize("case", [(3, 32, 32, 32, 64), (2, 64, 16, 16, 64), (4, 1, 32, 32, 16), (2, 64, 8, 8, 128), (2, 64, 32, 32, 32)])
 def test_qconv_pool_with_negative_multipliers(case):
     """A negative requantisation multiplier makes the requantisation decreasing in the accumulator, so the
