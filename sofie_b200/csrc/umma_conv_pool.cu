@@ -360,15 +360,16 @@ umma_qconv3x3_pool_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_
 // arrive by one TMA box per tile; out-of-image bytes are the zero fill = the padding value (input zero point 0).
 // Two threads issue (even and odd tiles): a tile's two waits, four MMAs and two commits cost one thread about as long as
 // the tile's epilogue takes, and the thread that issues is the pacemaker of everything behind it.
-//   warp 0 producer | warps 1 and 22 MMA issuers | warps 2..17 epilogue | warps 18..21 operand builders
+//   warp 0 producer | warps 1 and 26 MMA issuers | warps 2..17 epilogue | warps 18..25 operand builders (two groups of four)
 constexpr int kFirstRawPitch = 48;                                  // bytes per staged input row
 constexpr int kFirstRawBytes = kPoolRows * kFirstRawPitch;          // 1632
 constexpr int kFirstRawStride = (kFirstRawBytes + 127) / 128 * 128; // 1664
 constexpr int kFirstABytes = 4 * 2048;                              // four positions x 128 rows x 16 bytes
 constexpr int kFirstStages = 4;
-constexpr int kFirstThreads = 23 * 32;
+constexpr int kFirstBuilderGroups = 2;   // groups of four builder warps that take the tiles alternately
+constexpr int kFirstThreads = (19 + 4 * kFirstBuilderGroups) * 32;
 constexpr int kFirstBuilderWarp0 = 18;
-constexpr int kFirstIssuerB = 22;
+constexpr int kFirstIssuerB = 18 + 4 * kFirstBuilderGroups;
 
 template <int BN>
 __global__ void __launch_bounds__(kFirstThreads, 1)
@@ -479,14 +480,19 @@ umma_qconv3x3_first_pool_kernel(const __grid_constant__ CUtensorMap tmX, const i
       pool_epilogue_warp<BN, NBUF>(p, s_mult, s_qbias, pool_first, tmem_base, tmem_full, tmem_empty, &abort_flag, status, warp, lane);
    } else {
       // ---------------- operand builders: thread = pooling window (py, px) of the tile ----------------
-      const int t = threadIdx.x - kFirstBuilderWarp0 * 32;
+      // Two groups of four warps take the tiles alternately (the number of slots is even: a slot always meets the same group):
+      // a group's chain of wait, load, permute, store, proxy fence and arrive is the one serial stage of a tile's way through
+      // this kernel, and two tiles are in it at any time.
+      const int bt = threadIdx.x - kFirstBuilderWarp0 * 32;
+      const int group = bt >> 7, t = bt & 127;
       const int px = t & 7, py = t >> 3;
       // the window's 4 x 4 input bytes: patch rows 2py .. 2py+3, patch columns 2px .. 2px+3; patch column c is byte 15 + c of a staged row
       const int byte0 = 15 + 2 * px, word0 = byte0 >> 2, shift = byte0 & 3;   // shift is 1 or 3
       const uint32_t sel_row = shift == 1 ? 0x4321u : 0x6543u;                 // four bytes starting at byte `shift` of a word pair
-      int s = 0;
-      uint32_t ph = 0;
-      for (int tile = blockIdx.x, g = 0; tile < p.num_tiles; tile += gridDim.x, g++, ring_next(s, ph, S)) {
+      static_assert(kFirstStages % kFirstBuilderGroups == 0, "a slot always meets the same builder group");
+      for (int g = group; blockIdx.x + (long long)g * gridDim.x < p.num_tiles; g += kFirstBuilderGroups) {
+         const int s = g % S;
+         const uint32_t ph = (uint32_t)(g / S) & 1u;
          if (!mbar_wait(&raw_full[s], ph, &abort_flag, status, kStatusWaitFull, 0x6000 + g)) break;
          const uint32_t *raw = reinterpret_cast<const uint32_t *>(raw_slots + (size_t)s * kFirstRawStride);
          uint32_t r[4];
