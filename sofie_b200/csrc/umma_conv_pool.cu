@@ -34,6 +34,8 @@
 // epilogue in two groups of eight that take the tiles alternately (group 0 drains TMEM buffer 0 while group 1
 // drains buffer 1: the latency of one tile's TMEM reads hides behind the other's arithmetic), two warps per
 // lane quarter, 32 channels each. Every wait is bounded (umma::mbar_wait).
+#include <type_traits>
+
 #include "umma.cuh"
 #include "contract.cuh"
 #include <cstdlib>
@@ -154,23 +156,29 @@ __device__ __forceinline__ void pool_epilogue_warp(const PoolConvParams &p, cons
             tmem_ld_32x16(t_row + 3 * BN, c);
             tmem_ld_wait();
             // four channels at a time: their multipliers (and biases) are one 16-byte shared load each (c0 is a multiple of 16)
-            const bool has_bias = p.qbias != nullptr, zp0 = p.y_zp == 0;
+            const bool zp0 = p.y_zp == 0;
+            // two copies of the loop: a layer without bias does not pay an addition per value for it
+            auto finish = [&](auto with_bias) {
 #pragma unroll
-            for (int j4 = 0; j4 < 4; j4++) {
-               const float4 m4 = reinterpret_cast<const float4 *>(s_mult + c0)[j4];
-               const float mu[4] = {m4.x, m4.y, m4.z, m4.w};
-               int bi[4] = {0, 0, 0, 0};
-               if (has_bias) {
-                  const int4 b4 = reinterpret_cast<const int4 *>(s_qbias + c0)[j4];
-                  bi[0] = b4.x; bi[1] = b4.y; bi[2] = b4.z; bi[3] = b4.w;
-               }
+               for (int j4 = 0; j4 < 4; j4++) {
+                  const float4 m4 = reinterpret_cast<const float4 *>(s_mult + c0)[j4];
+                  const float mu[4] = {m4.x, m4.y, m4.z, m4.w};
+                  int bi[4] = {0, 0, 0, 0};
+                  if constexpr (decltype(with_bias)::value) {
+                     const int4 b4 = reinterpret_cast<const int4 *>(s_qbias + c0)[j4];
+                     bi[0] = b4.x; bi[1] = b4.y; bi[2] = b4.z; bi[3] = b4.w;
+                  }
 #pragma unroll
-               for (int t = 0; t < 4; t++) {
-                  const int j = 4 * j4 + t;
-                  const int m = __vimax3_s32((int)a[j], (int)b[j], (int)c[j]) + bi[t];
-                  q[j] = zp0 ? (int)requant_u8_zp0(m, mu[t]) : requant_u8(m, mu[t], p.y_zp, p.relu);
+                  for (int t = 0; t < 4; t++) {
+                     const int j = 4 * j4 + t;
+                     int m = __vimax3_s32((int)a[j], (int)b[j], (int)c[j]);
+                     if constexpr (decltype(with_bias)::value) m += bi[t];
+                     q[j] = zp0 ? (int)requant_u8_zp0(m, mu[t]) : requant_u8(m, mu[t], p.y_zp, p.relu);
+                  }
                }
-            }
+            };
+            if (p.qbias != nullptr) finish(std::true_type{});
+            else finish(std::false_type{});
          } else {
             // a negative multiplier reverses the order: requantise the four pixels, then take the maximum
 #pragma unroll
