@@ -156,9 +156,9 @@ __device__ __forceinline__ void pool_epilogue_warp(const PoolConvParams &p, cons
             tmem_ld_32x16(t_row + 3 * BN, c);
             tmem_ld_wait();
             // four channels at a time: their multipliers (and biases) are one 16-byte shared load each (c0 is a multiple of 16)
-            const bool zp0 = p.y_zp == 0;
-            // two copies of the loop: a layer without bias does not pay an addition per value for it
-            auto finish = [&](auto with_bias) {
+            // four copies of the loop, chosen by two uniform branches outside it: a layer without bias does not pay an addition
+            // per value, and the choice between the two requantisation forms is not made (or both computed) per value
+            auto finish = [&](auto with_bias, auto zero_point_0) {
 #pragma unroll
                for (int j4 = 0; j4 < 4; j4++) {
                   const float4 m4 = reinterpret_cast<const float4 *>(s_mult + c0)[j4];
@@ -173,12 +173,18 @@ __device__ __forceinline__ void pool_epilogue_warp(const PoolConvParams &p, cons
                      const int j = 4 * j4 + t;
                      int m = __vimax3_s32((int)a[j], (int)b[j], (int)c[j]);
                      if constexpr (decltype(with_bias)::value) m += bi[t];
-                     q[j] = zp0 ? (int)requant_u8_zp0(m, mu[t]) : requant_u8(m, mu[t], p.y_zp, p.relu);
+                     if constexpr (decltype(zero_point_0)::value) q[j] = (int)requant_u8_zp0(m, mu[t]);
+                     else q[j] = requant_u8(m, mu[t], p.y_zp, p.relu);
                   }
                }
             };
-            if (p.qbias != nullptr) finish(std::true_type{});
-            else finish(std::false_type{});
+            if (p.y_zp == 0) {
+               if (p.qbias != nullptr) finish(std::true_type{}, std::true_type{});
+               else finish(std::false_type{}, std::true_type{});
+            } else {
+               if (p.qbias != nullptr) finish(std::true_type{}, std::false_type{});
+               else finish(std::false_type{}, std::false_type{});
+            }
          } else {
             // a negative multiplier reverses the order: requantise the four pixels, then take the maximum
 #pragma unroll
