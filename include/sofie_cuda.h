@@ -81,7 +81,7 @@ int sofie_cuda_ctx_upload(sofie_cuda_ctx *ctx, const void *host, size_t bytes, v
 int sofie_cuda_ctx_h2d(sofie_cuda_ctx *ctx, void *dst_device, const void *src_host, size_t bytes);
 /* Pipelined input upload: the input is copied in up to SOFIE_CUDA_MAX_PARTS parts (slices of the batch) on a
  * copy stream of the context, and the launches that read part p are issued after sofie_cuda_ctx_wait_part(p),
- * which makes the context stream wait for that copy only: the first layer of the model works on part p while
+ * which makes the context stream wait for that copy only: the model's leading operators work on part p while
  * part p+1 is still crossing PCIe. Copies from pageable host memory fall back to sofie_cuda_ctx_h2d. The
  * caller must not issue the parts of a new inference before the previous one has been fetched
  * (the emitted infer() ends with sofie_cuda_ctx_fetch, which waits). */

@@ -18,6 +18,11 @@ namespace EMIT {
 
 inline std::string Dev(const std::string &name) { return "dev_" + name; }
 inline std::string Host(const std::string &name) { return "host_" + name; }
+// slice `part` (a variable of the emitted code) of `parts` equal, contiguous slices of a tensor of `elems` elements
+inline std::string DevSlice(const std::string &name, size_t elems, size_t parts)
+{
+   return parts > 1 ? "(" + Dev(name) + " + (size_t)part * " + std::to_string(elems / parts) + ")" : Dev(name);
+}
 
 inline std::string CType(ETensorType t)
 {

@@ -57,6 +57,8 @@ private:
    size_t fArenaBytes = 0;
    bool fForcePipelinedUpload = false;
    bool fNeverPipelinedUpload = false;
+   size_t fUploadParts = 4;                  // parts of a pipelined input upload (at most SOFIE_CUDA_MAX_PARTS)
+   std::vector<size_t> fSlicedOps;           // operators launched once per uploaded part, in execution order
    // Run-time batch: Generate() without a batch size on a model whose inputs carry a batch parameter in their first
    // dimension keeps that parameter in the emitted Session (reference: RModel.cxx:680-713, 876-884). Shapes are then
    // inferred with the batch set to a large prime; a number of the emitted text that is a multiple of it scales with the
@@ -169,6 +171,7 @@ public:
 
 protected:
    void PlanDevice();
+   void PlanSlices();
    void PlanArena();
    void GenerateSessionCode();
    void GenerateSessionMembers();

@@ -44,9 +44,10 @@ public:
    // true when the operator can read a rank-4 input stored NHWC on the device
    virtual bool AcceptsNHWC(const std::string & /*input*/) const { return false; }
 
-   // Pipelined input upload: an operator that reads the model input and treats the samples of a batch
-   // independently can be launched on slice `part` of `parts` equal slices of the batch (`part` is a
-   // variable of the emitted code), so that it works on one slice while the next is still being copied.
+   // Pipelined input upload: an operator that treats the samples of a batch independently can be launched
+   // on slice `part` of `parts` equal, contiguous slices of its batch-shaped inputs and outputs (`part` is a
+   // variable of the emitted code), so that the model works on one slice while the next is still being copied.
+   // Constant inputs (weights, tables) are read whole by every slice.
    virtual bool CanSliceBatch(size_t /*parts*/) const { return false; }
    virtual std::string GenerateBatchSlice(std::string /*OpName*/, size_t /*parts*/) { return ""; }
 

@@ -53,12 +53,18 @@ public:
       fShape = model.GetTensorShape(fNX);
       model.AddIntermediateTensor(fNY, ETensorType::FLOAT8E4M3FN, fShape);
    }
-   std::string Generate(std::string OpName) override
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && !fShape.empty() && fShape[0] % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       std::stringstream out;
-      out << "\n" << SP << "//------ QuantizeLinear (E4M3) op_" << OpName << "\n";
+      const size_t n = ConvertShapeToLength(fShape);
+      out << "\n" << SP << "//------ QuantizeLinear (E4M3) op_" << OpName << (parts > 1 ? ", one slice of the batch" : "") << "\n";
       out << EMIT::Call(SP, std::string(fInType == ETensorType::FLOAT ? "sofie_cuda_quantize_e4m3_f32" : "sofie_cuda_quantize_e4m3_bf16") +
-                               "(fStream, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ", " + std::to_string(ConvertShapeToLength(fShape)) + ", " +
+                               "(fStream, " + EMIT::DevSlice(fNX, n, parts) + ", " + EMIT::DevSlice(fNY, n, parts) + ", " + std::to_string(n / parts) + ", " +
                                EMIT::FloatLit(fScale) + ")");
       return out.str();
    }
@@ -197,27 +203,35 @@ public:
       model.UseOnDevice(fNW);
       if (!fNB.empty()) model.UseOnDevice(fNB);
    }
-   std::string Generate(std::string OpName) override
+   // rows are independent once the activation scale is a constant (a run-time scale is the maximum over ALL rows)
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && fNAScale.empty() && !fShapeA.empty() && fShapeA[0] % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       std::stringstream out;
       out << "\n" << SP << "//------ Fp8Gemm op_" << OpName << (fRelu ? " + Relu" : "")
-          << (fOutScale > 0.f ? " -> E4M3" : (fNYFloat.empty() ? " -> bfloat16" : " -> bfloat16 -> float (Cast fused)")) << "\n";
+          << (fOutScale > 0.f ? " -> E4M3" : (fNYFloat.empty() ? " -> bfloat16" : " -> bfloat16 -> float (Cast fused)"))
+          << (parts > 1 ? ", one slice of the rows" : "") << "\n";
       out << SP << "{\n";
-      out << SP << SP << "const sofie_fp8_gemm_desc d = {" << fShapeA[0] << ", " << fShapeW[0] << ", " << fShapeA[1] << ", "
+      out << SP << SP << "const sofie_fp8_gemm_desc d = {" << fShapeA[0] / parts << ", " << fShapeW[0] << ", " << fShapeA[1] << ", "
           << EMIT::FloatLit(fAScale) << ", " << EMIT::FloatLit(fWScale) << ", " << (fRelu ? 1 : 0) << ", " << EMIT::FloatLit(fOutScale) << "};\n";
       const std::string bias = fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNB);
+      const size_t lenA = fShapeA[0] * fShapeA[1], lenY = fShapeA[0] * fShapeW[0];
       if (!fNAScale.empty()) {
          // activation scale from device memory, written by the DynamicQuantizeE4M3 in front of this layer
          out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3_dynamic(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNAScale) + ", " + EMIT::Dev(fNW) + ", " + bias +
                                        ", " + (fNYFloat.empty() ? EMIT::Dev(fNY) : std::string("nullptr")) + ", " +
                                        (fNYFloat.empty() ? std::string("nullptr") : EMIT::Dev(fNYFloat)) + ")");
       } else if (!fNYFloat.empty()) {
-         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3_f32(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNW) + ", " + bias + ", " +
-                                       EMIT::Dev(fNYFloat) + ")");
+         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3_f32(fStream, &d, " + EMIT::DevSlice(fNA, lenA, parts) + ", " + EMIT::Dev(fNW) + ", " + bias + ", " +
+                                       EMIT::DevSlice(fNYFloat, lenY, parts) + ")");
       } else {
-         const std::string ybf = fOutScale > 0.f ? std::string("nullptr") : EMIT::Dev(fNY);
-         const std::string yq = fOutScale > 0.f ? EMIT::Dev(fNY) : std::string("nullptr");
-         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNW) + ", " + bias + ", " + ybf + ", " + yq + ")");
+         const std::string ybf = fOutScale > 0.f ? std::string("nullptr") : EMIT::DevSlice(fNY, lenY, parts);
+         const std::string yq = fOutScale > 0.f ? EMIT::DevSlice(fNY, lenY, parts) : std::string("nullptr");
+         out << EMIT::Call(SP + SP, "sofie_cuda_gemm_e4m3(fStream, &d, " + EMIT::DevSlice(fNA, lenA, parts) + ", " + EMIT::Dev(fNW) + ", " + bias + ", " + ybf + ", " + yq + ")");
       }
       out << SP << "}\n";
       return out.str();

@@ -215,9 +215,17 @@ public:
       }
    }
 
-   std::string Generate(std::string opName) override
+   // rows of A are independent: any equal split of the rows is a valid launch (not for a transposed A, a stack of products
+   // or a bias with one value per row)
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && fStack <= 1 && !fAttrTransA && fBiasKind != 2 && fM > 0 && fM % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string opName, size_t parts)
    {
       opName = "op_" + opName;
+      const size_t M = fM / parts;
       if (fShapeA.empty() || fShapeB.empty() || fShapeY.empty())
          throw std::runtime_error("SOFIE Gemm Op called to Generate without being initialized first");
       std::stringstream out;
@@ -225,8 +233,8 @@ public:
          // one launch for the whole chain: widths, Relu flags and the device pointers of every layer
          std::vector<const ROperator_Gemm<T> *> layers{this};
          layers.insert(layers.end(), fChain.begin(), fChain.end());
-         out << "\n" << SP << "//--------- fused MLP " << opName << ": " << layers.size() << " Gemm layers, [" << fM << "," << fK << "] -> ["
-             << fM << "," << layers.back()->fN << "]\n";
+         out << "\n" << SP << "//--------- fused MLP " << opName << ": " << layers.size() << " Gemm layers, [" << M << "," << fK << "] -> ["
+             << M << "," << layers.back()->fN << "]" << (parts > 1 ? ", one slice of the rows" : "") << "\n";
          out << SP << "{\n";
          std::string dims = std::to_string(fK), relu, nk, w, b;
          for (size_t l = 0; l < layers.size(); l++) {
@@ -236,10 +244,11 @@ public:
             w += (l ? ", " : "") + EMIT::Dev(layers[l]->fNBdev);
             b += (l ? ", " : "") + (layers[l]->fBiasKind ? EMIT::Dev(layers[l]->fNCdev) : std::string("nullptr"));
          }
-         out << SP << SP << "const sofie_mlp_desc d = {" << fM << ", " << layers.size() << ", {" << dims << "}, {" << relu << "}, {" << nk << "}};\n";
+         out << SP << SP << "const sofie_mlp_desc d = {" << M << ", " << layers.size() << ", {" << dims << "}, {" << relu << "}, {" << nk << "}};\n";
          out << SP << SP << "const float * const w[] = {" << w << "};\n";
          out << SP << SP << "const float * const b[] = {" << b << "};\n";
-         out << EMIT::Call(SP + SP, "sofie_cuda_mlp_f32(fStream, &d, " + EMIT::Dev(fNA) + ", w, b, " + EMIT::Dev(fNYChain) + ")");
+         out << EMIT::Call(SP + SP, "sofie_cuda_mlp_f32(fStream, &d, " + EMIT::DevSlice(fNA, fM * fK, parts) + ", w, b, " +
+                                       EMIT::DevSlice(fNYChain, fM * layers.back()->fN, parts) + ")");
          out << SP << "}\n";
          return out.str();
       }
@@ -256,17 +265,19 @@ public:
          out << SP << "}\n";
          return out.str();
       }
-      out << "\n" << SP << "//--------- Gemm " << opName << ": [" << fM << "," << fK << "] x [" << fK << "," << fN << "]\n";
+      out << "\n" << SP << "//--------- Gemm " << opName << ": [" << M << "," << fK << "] x [" << fK << "," << fN << "]"
+          << (parts > 1 ? ", one slice of the rows" : "") << "\n";
       out << SP << "{\n";
-      out << SP << SP << "const sofie_gemm_f32_desc d = {" << fM << ", " << fN << ", " << fK << ", " << fAttrTransA << ", "
+      out << SP << SP << "const sofie_gemm_f32_desc d = {" << M << ", " << fN << ", " << fK << ", " << fAttrTransA << ", "
           << fEmitTransB << ", " << EMIT::FloatLit(fAttrAlpha) << ", " << EMIT::FloatLit(fBiasKind ? fAttrBeta : 0.f) << ", "
           << fBiasKind << ", " << (fActivation == EActivationType::RELU ? 1 : 0) << "};\n";
-      out << EMIT::Call(SP + SP, "sofie_cuda_gemm_f32(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNBdev) + ", " +
-                                    (fBiasKind ? EMIT::Dev(fNCdev) : std::string("nullptr")) + ", " + EMIT::Dev(fNY) + ")");
+      out << EMIT::Call(SP + SP, "sofie_cuda_gemm_f32(fStream, &d, " + EMIT::DevSlice(fNA, fM * fK, parts) + ", " + EMIT::Dev(fNBdev) + ", " +
+                                    (fBiasKind ? EMIT::Dev(fNCdev) : std::string("nullptr")) + ", " + EMIT::DevSlice(fNY, fM * fN, parts) + ")");
       out << SP << "}\n";
       return out.str();
    }
 
+public:
    std::vector<std::string> GetBlasRoutines() override { return {}; }
 };
 

@@ -72,12 +72,18 @@ public:
       model.AddIntermediateTensor(fNY, ETensorType::UINT8, fShape);
    }
    void PlanDevice(RModel &model) override { model.SetTensorLayout(fNY, model.GetTensorLayout(model.ResolveAlias(fNX))); }
-   std::string Generate(std::string OpName) override
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && !fShape.empty() && fShape[0] % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       std::stringstream out;
-      out << "\n" << SP << "//------ QuantizeLinear op_" << OpName << "\n";
-      out << EMIT::Call(SP, "sofie_cuda_quantize_u8(fStream, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ", " +
-                               std::to_string(ConvertShapeToLength(fShape)) + ", " + EMIT::FloatLit(fScale) + ", " + std::to_string(fZp) + ")");
+      const size_t n = ConvertShapeToLength(fShape);
+      out << "\n" << SP << "//------ QuantizeLinear op_" << OpName << (parts > 1 ? ", one slice of the batch" : "") << "\n";
+      out << EMIT::Call(SP, "sofie_cuda_quantize_u8(fStream, " + EMIT::DevSlice(fNX, n, parts) + ", " + EMIT::DevSlice(fNY, n, parts) + ", " +
+                               std::to_string(n / parts) + ", " + EMIT::FloatLit(fScale) + ", " + std::to_string(fZp) + ")");
       return out.str();
    }
 };
@@ -245,20 +251,28 @@ public:
                                EMIT::Dev(fNCorr) + ")");
       return out.str();
    }
-   std::string Generate(std::string OpName) override
+   // rows are independent: any equal split of the rows is a valid launch
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && fM > 0 && fM % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       std::stringstream out;
-      out << "\n" << SP << "//--------- QLinearMatMul op_" << OpName << (fRelu ? " + Relu" : "") << ": [" << fM << "," << fK << "] x [" << fK
-          << "," << fN << "]\n";
+      const size_t m = fM / parts;
+      out << "\n" << SP << "//--------- QLinearMatMul op_" << OpName << (fRelu ? " + Relu" : "") << ": [" << m << "," << fK << "] x [" << fK
+          << "," << fN << "]" << (parts > 1 ? ", one slice of the rows" : "") << "\n";
       out << SP << "{\n";
-      out << SP << SP << "const sofie_qgemm_desc d = {" << fM << ", " << fN << ", " << fK << ", 1, " << fYZp << ", " << (fRelu ? 1 : 0) << "};\n";
+      out << SP << SP << "const sofie_qgemm_desc d = {" << m << ", " << fN << ", " << fK << ", 1, " << fYZp << ", " << (fRelu ? 1 : 0) << "};\n";
+      const std::string a = EMIT::DevSlice(fNA, fM * fK, parts);
       if (!fNYFloat.empty())
-         out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_matmul_f32(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNBdev) + ", " +
+         out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_matmul_f32(fStream, &d, " + a + ", " + EMIT::Dev(fNBdev) + ", " +
                                        EMIT::Dev(fNMult) + ", " + EMIT::Dev(fNCorr) + ", " + EMIT::FloatLit(fDequantScale) + ", " +
-                                       EMIT::Dev(fNYFloat) + ")  /* + DequantizeLinear */");
+                                       EMIT::DevSlice(fNYFloat, fM * fN, parts) + ")  /* + DequantizeLinear */");
       else
-         out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_matmul(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNBdev) + ", " +
-                                       EMIT::Dev(fNMult) + ", " + EMIT::Dev(fNCorr) + ", " + EMIT::Dev(fNY) + ")");
+         out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_matmul(fStream, &d, " + a + ", " + EMIT::Dev(fNBdev) + ", " +
+                                       EMIT::Dev(fNMult) + ", " + EMIT::Dev(fNCorr) + ", " + EMIT::DevSlice(fNY, fM * fN, parts) + ")");
       out << SP << "}\n";
       return out.str();
    }
@@ -386,19 +400,27 @@ public:
                                EMIT::Dev(fNMult) + ", " + EMIT::Dev(fNCorr) + ")");
       return out.str();
    }
-   std::string Generate(std::string OpName) override
+   // the samples of a batch are independent: any equal split of the batch axis is a valid launch
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && !fShapeX.empty() && fShapeX[0] % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       std::stringstream out;
       out << "\n" << SP << "//----  operator QLinearConv op_" << OpName << (fRelu ? " + Relu" : "") << (fPool ? " + MaxPool2x2" : "") << " -> "
-          << fNOut << " " << ConvertShapeToString(fShapeOut) << (fLayoutY == ELayout::NHWC ? " (NHWC)" : "") << "\n";
+          << fNOut << " " << ConvertShapeToString(fShapeOut) << (fLayoutY == ELayout::NHWC ? " (NHWC)" : "")
+          << (parts > 1 ? ", one slice of the batch" : "") << "\n";
       out << SP << "{\n";
-      out << SP << SP << "const sofie_qconv2d_desc d = {" << fShapeX[0] << ", " << fShapeX[1] << ", " << fShapeX[2] << ", " << fShapeX[3]
+      out << SP << SP << "const sofie_qconv2d_desc d = {" << fShapeX[0] / parts << ", " << fShapeX[1] << ", " << fShapeX[2] << ", " << fShapeX[3]
           << ", " << fShapeW[0] << ", " << fAttr.kH << ", " << fAttr.kW << ", " << fAttr.padH << ", " << fAttr.padW << ", " << fAttr.sH
           << ", " << fAttr.sW << ", " << (int)fLayoutX << ", " << (int)fLayoutY << ", " << (fPacked ? 1 : 0) << ", " << fXZp << ", "
           << fYZp << ", " << (fRelu ? 1 : 0) << ", " << fPool << "};\n";
-      out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_conv2d(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNWdev) + ", " +
-                                    EMIT::Dev(fNMult) + ", " + (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNCorr)) + ", " +
-                                    EMIT::Dev(fNOut) + ")");
+      out << EMIT::Call(SP + SP, "sofie_cuda_qlinear_conv2d(fStream, &d, " + EMIT::DevSlice(fNX, ConvertShapeToLength(fShapeX), parts) + ", " +
+                                    EMIT::Dev(fNWdev) + ", " + EMIT::Dev(fNMult) + ", " +
+                                    (fNB.empty() ? std::string("nullptr") : EMIT::Dev(fNCorr)) + ", " +
+                                    EMIT::DevSlice(fNOut, ConvertShapeToLength(fShapeOut), parts) + ")");
       out << SP << "}\n";
       return out.str();
    }

@@ -128,6 +128,9 @@ public:
          throw std::runtime_error("SOFIE " + Name() + " Op: cannot reinterpret an NHWC tensor");
       model.AddAlias(fNOutput, owner);
    }
+   // an alias: slice `part` of the output IS slice `part` of the input
+   bool CanSliceBatch(size_t parts) const override { return parts > 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t) override { return Generate(OpName); }
    std::string Generate(std::string OpName) override
    {
       if (fShapeInput.empty()) throw std::runtime_error("SOFIE Reshape Op called to Generate without being initialized first");

@@ -9,6 +9,7 @@
 #include <iomanip>
 #include <iostream>
 #include <limits>
+#include <set>
 
 #include "SOFIE/Emit.hxx"
 #include "sofie_cuda.h" // sofie_mlp_smem_bytes: host arithmetic only, nothing of the library is linked
@@ -309,6 +310,7 @@ void RModel::Initialize(int batchSize, bool verbose)
       op->Initialize(*this);
    }
    PlanDevice();
+   PlanSlices();
    PlanArena();
    fIsInitialized = true;
 }
@@ -416,7 +418,71 @@ void RModel::PlanDevice()
    }
 }
 
-// Step 4: liveness-based first-fit placement in one arena (256-byte aligned slices).
+// Step 4: which operators run once per uploaded part of the input.
+void RModel::PlanSlices()
+{
+   // Pipelined input upload: when the model has one large input and its leading operators treat the samples of a
+   // batch independently, the input is copied in fUploadParts parts on the copy stream and those operators are
+   // launched once per part as soon as the part has arrived (slice `part` of every tensor they read and write);
+   // the operators behind the first one that cannot be sliced are the captured graph and run when all parts are done.
+   // Every copy carries about 10 us of fixed cost on top of its bytes at ~55 GB/s, so splitting only pays when a part
+   // is several megabytes: measured on B200, a 3 MB input in four parts is 12% slower end to end than in one piece.
+   // What is left after the last copy is one part's share of the kernels: eight parts from 128 MB on, four below.
+   fSlicedOps.clear();
+   fUploadParts = 4;
+   size_t head = fOperators.size();
+   for (size_t i = 0; i < fOperators.size(); i++)
+      if (!fOperators[i]->IsFusedAway()) {
+         head = i;
+         break;
+      }
+   if (head >= fOperators.size() || fInputTensorNames.size() != 1 || fNeverPipelinedUpload || fDynamicBatch) return;
+   const std::string &in = fInputTensorNames[0];
+   const size_t inBytes = ConvertShapeToLength(GetTensorShape(in)) * GetTypeSize(GetTensorType(in));
+   if (inBytes < (fForcePipelinedUpload ? 0 : size_t(32) << 20)) return;
+   auto prefix = [&](size_t parts) {
+      std::vector<size_t> sliced;
+      // every slice of a tensor starts on a 256-byte boundary, like the tensor itself
+      auto slices = [&](const std::string &n) {
+         return (ConvertShapeToLength(GetTensorShape(n)) * GetTypeSize(GetTensorType(n))) % (parts * 256) == 0;
+      };
+      if (!slices(in)) return sliced;
+      std::set<std::string> parted{in}; // tensors that come into being slice by slice
+      for (size_t i = head; i < fOperators.size(); i++) {
+         auto &op = fOperators[i];
+         if (op->IsFusedAway()) continue;
+         bool ok = op->CanSliceBatch(parts);
+         size_t batchInputs = 0;
+         for (auto &n : op->GetOpInputTensors()) {
+            if (IsInitializedTensor(n)) continue; // constants are read whole by every slice
+            ok = ok && parted.count(n) != 0 && slices(n);
+            batchInputs++;
+         }
+         ok = ok && batchInputs > 0;
+         for (auto &w : op->GetOpOutputTensors()) ok = ok && slices(w);
+         if (!ok) break;
+         for (auto &w : op->GetOpOutputTensors()) parted.insert(w);
+         sliced.push_back(i);
+      }
+      // the first sliced operator has to be the one that reads the input: otherwise nothing overlaps the copy
+      if (!sliced.empty()) {
+         bool readsInput = false;
+         for (auto &n : fOperators[sliced[0]]->GetOpInputTensors()) readsInput = readsInput || n == in;
+         if (!readsInput) sliced.clear();
+      }
+      return sliced;
+   };
+   fSlicedOps = prefix(4);
+   if (inBytes >= (size_t(128) << 20)) {
+      std::vector<size_t> eight = prefix(8);
+      if (!eight.empty() && eight.size() >= fSlicedOps.size()) {
+         fSlicedOps = eight;
+         fUploadParts = 8;
+      }
+   }
+}
+
+// Step 5: liveness-based first-fit placement in one arena (256-byte aligned slices).
 void RModel::PlanArena()
 {
    struct Slot {
@@ -460,6 +526,20 @@ void RModel::PlanArena()
       Slot *s = slot_of(o);
       if (!s) throw std::runtime_error("SOFIE: output tensor " + o + " is not produced by any operator");
       s->last = nOps;
+   }
+   // Operators launched per uploaded part run part after part: slice 1 of their first tensor is written after slice 0 of
+   // their last one (and the input's later parts arrive meanwhile), so everything they touch is alive together.
+   if (!fSlicedOps.empty()) {
+      const int lo = (int)fSlicedOps.front(), hi = (int)fSlicedOps.back();
+      auto together = [&](const std::string &n) {
+         if (Slot *s = slot_of(n)) {
+            s->first = std::min(s->first, lo);
+            s->last = std::max(s->last, hi);
+         }
+      };
+      for (auto &in : fInputTensorNames) together(in);
+      for (size_t i : fSlicedOps)
+         for (auto &out : fOperators[i]->GetOpOutputTensors()) together(out);
    }
    fArenaBytes = 0;
    for (size_t i = 0; i < slots.size(); i++) {
@@ -777,36 +857,15 @@ void RModel::GenerateInfer()
    size_t nOut = fOutputTensorNames.size();
    if (nOut == 0) throw std::runtime_error("SOFIE: output size=0 are not supported");
    // the launches of one infer(), in execution order; captured into a CUDA graph on the first call
-   // Pipelined input upload: when the first operator reads the (single, large) model input and can work on
-   // slices of the batch, the input is copied in kUploadParts parts on the copy stream and that operator is
-   // launched once per part as soon as its part has arrived; the rest of the model is the captured graph.
-   // Every copy carries about 10 us of fixed cost on top of its bytes at ~55 GB/s, so splitting only pays when a part
-   // is several megabytes: measured on B200, a 3 MB input in four parts is 12% slower end to end than in one piece.
-   constexpr size_t kUploadParts = 4;
-   const size_t kPipelineMinBytes = fForcePipelinedUpload ? 0 : size_t(32) << 20;
-   size_t head = fOperators.size();
-   for (size_t i = 0; i < fOperators.size(); i++)
-      if (!fOperators[i]->IsFusedAway()) {
-         head = i;
-         break;
-      }
-   bool pipelined = false;
-   if (head < fOperators.size() && fInputTensorNames.size() == 1 && !fNeverPipelinedUpload && !fDynamicBatch) {
-      const std::string &in = fInputTensorNames[0];
-      const auto &reads = fOperators[head]->GetOpInputTensors();
-      size_t readers = 0;
-      for (auto &op : fOperators)
-         if (!op->IsFusedAway())
-            for (auto &n : op->GetOpInputTensors()) readers += (n == in);
-      pipelined = !reads.empty() && reads[0] == in && readers == 1 && fOperators[head]->CanSliceBatch(kUploadParts) &&
-                  ConvertShapeToLength(GetTensorShape(in)) * GetTypeSize(GetTensorType(in)) >= kPipelineMinBytes;
-      for (auto &o : fOutputTensorNames) // a model output written slice by slice outside the graph is not worth a special case
-         for (auto &w : fOperators[head]->GetOpOutputTensors()) pipelined = pipelined && o != w;
-   }
+   const std::vector<size_t> &sliced = fSlicedOps; // the operators launched per uploaded part (PlanSlices)
+   const bool pipelined = !sliced.empty();
+   auto isSliced = [&](size_t i) { return std::find(sliced.begin(), sliced.end(), i) != sliced.end(); };
+   size_t tailOps = 0;
+   for (size_t i = 0; i < fOperators.size(); i++) tailOps += (!fOperators[i]->IsFusedAway() && !isSliced(i));
    if (pipelined) {
-      fGC += "// the first operator, on one slice of the batch: launched as soon as that slice of the input has arrived\n";
+      fGC += "// the leading operators on one slice of the batch: launched as soon as that slice of the input has arrived\n";
       fGC += "void LaunchHead(int part) {\n";
-      fGC += fOperators[head]->GenerateBatchSlice(std::to_string(head), kUploadParts);
+      for (size_t i : sliced) fGC += fOperators[i]->GenerateBatchSlice(std::to_string(i), fUploadParts);
       fGC += "}\n\n";
    }
    fGC += pipelined ? "// all other kernel launches of one inference, on the context stream\n"
@@ -815,7 +874,7 @@ void RModel::GenerateInfer()
    // a mark before every operator and one after the last: device timers when they are switched on, nothing otherwise
    size_t lastMark = 0;
    for (size_t i = 0; i < fOperators.size(); i++) {
-      if (fOperators[i]->IsFusedAway() || (pipelined && i == head)) continue;
+      if (fOperators[i]->IsFusedAway() || isSliced(i)) continue;
       if (fVerbose) std::cout << "Generating code for operator .... " << i << std::endl;
       fGC += "   Check(sofie_cuda_ctx_mark(fCtx, " + std::to_string(i) + "), \"sofie_cuda_ctx_mark\");\n";
       fGC += fOperators[i]->Generate(std::to_string(i));
@@ -838,6 +897,10 @@ void RModel::GenerateInfer()
    // The kernels of one inference once the inputs are on the device (or, with the pipelined upload, while all but
    // the first operator's share of them is): replay of the captured graph, or the first, capturing, pass.
    fGC += "void Run() {\n";
+   if (pipelined && tailOps == 0) {
+      // every operator runs per slice: nothing is left to capture
+      fGC += "}\n\n";
+   } else {
    fGC += "   if (fGraphReady) {\n";
    fGC += "      Check(sofie_cuda_ctx_graph_launch(fCtx), \"sofie_cuda_ctx_graph_launch\");\n";
    fGC += "   } else {\n";
@@ -850,10 +913,11 @@ void RModel::GenerateInfer()
    fGC += "      }\n";
    fGC += "   }\n";
    fGC += "}\n\n";
+   }
    // Every kernel of one inference on the inputs of the previous infer() call, which are still on the device:
    // no copy in either direction and no wait (for callers that time or pipeline the device work themselves).
    fGC += "void RunResident() {\n";
-   if (pipelined) fGC += "   for (int part = 0; part < " + std::to_string(kUploadParts) + "; part++) LaunchHead(part);\n";
+   if (pipelined) fGC += "   for (int part = 0; part < " + std::to_string(fUploadParts) + "; part++) LaunchHead(part);\n";
    fGC += "   Run();\n";
    fGC += "}\n\n";
    fGC += ret + " infer(" + GenerateInferSignature() + "){\n";
@@ -866,8 +930,8 @@ void RModel::GenerateInfer()
    }
    if (pipelined) {
       const std::string &n = fInputTensorNames[0];
-      const size_t elems = ConvertShapeToLength(GetTensorShape(n)) / kUploadParts;
-      const std::string parts = std::to_string(kUploadParts), slice = std::to_string(elems);
+      const size_t elems = ConvertShapeToLength(GetTensorShape(n)) / fUploadParts;
+      const std::string parts = std::to_string(fUploadParts), slice = std::to_string(elems);
       fGC += "   for (int part = 0; part < " + parts + "; part++)\n";
       fGC += "      Check(sofie_cuda_ctx_h2d_part(fCtx, " + EMIT::Dev(n) + " + (size_t)part * " + slice + ", tensor_" + n + " + (size_t)part * " + slice +
              ", " + std::to_string(elems * GetTypeSize(GetTensorType(n))) + ", part), \"sofie_cuda_ctx_h2d_part\");\n";

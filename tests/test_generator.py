@@ -231,6 +231,47 @@ def test_large_input_is_uploaded_in_parts_under_the_first_convolution():
     assert "void LaunchHead(int part)" in big and "const sofie_conv2d_desc d = {1024, 3, 32, 32, 16," in big
 
 
+def test_every_leading_operator_that_can_be_sliced_runs_per_uploaded_part():
+    """C5 with the pipelined upload: QuantizeLinear, the four convolutions, Flatten and both products are launched per quarter of the
+    batch, nothing is left for the graph. At a batch whose last tensor does not split into 256-byte aligned quarters the last product
+    stays behind, in Launch()."""
+    m, _ = configs.cnn_i8(batch=512, with_input=False)
+    text = generated.emit(onnx_wire.model_to_onnx(m), "c5_b512_pipe", pipelined=True).read_text()
+    head = text[text.index("void LaunchHead(int part)"):text.index("void Launch() {")]
+    assert head.count("sofie_cuda_quantize_u8(") == 1 and head.count("sofie_cuda_qlinear_conv2d(") == 4
+    assert head.count("sofie_cuda_qlinear_matmul(") == 1 and head.count("sofie_cuda_qlinear_matmul_f32(") == 1
+    assert "const sofie_qconv2d_desc d = {128, 1, 64, 64, 32," in head and "const sofie_qgemm_desc d = {128, 2, 256," in head
+    assert "(dev_x + (size_t)part * 524288)" in head and "(dev_y + (size_t)part * 256)" in head
+    assert "void Run() {\n}" in text and "sofie_cuda_ctx_graph_begin" not in text
+    small = generated.emit(onnx_wire.model_to_onnx(configs.cnn_i8(batch=8, with_input=False)[0]), "c5_b8_pipe", pipelined=True).read_text()
+    head = small[small.index("void LaunchHead(int part)"):small.index("void Launch() {")]
+    tail = small[small.index("void Launch() {"):small.index("void Run() {")]
+    assert head.count("sofie_cuda_qlinear_matmul(") == 1 and "sofie_cuda_qlinear_matmul_f32(" not in head
+    assert "sofie_cuda_qlinear_matmul_f32(fStream, &d, dev_f0," in tail and "sofie_cuda_ctx_graph_begin" in small
+
+
+def test_tensors_of_sliced_operators_share_no_arena_bytes():
+    """Slice 1 of a model's first tensor is written after slice 0 of its last one, and the input's later parts arrive in between:
+    the tensors of the operators launched per part must not reuse each other's bytes, as tensors of a whole-batch plan do."""
+    import re
+
+    def slices(text):
+        return {n: (int(o), int(b)) for o, b, n in re.findall(r"sofie_cuda_ctx_arena\(fCtx, (\d+), (\d+), reinterpret_cast<void\*\*>\(&dev_(\w+)\)\)", text)}
+
+    def overlaps(sl):
+        names = sorted(sl)
+        return [(a, b) for i, a in enumerate(names) for b in names[i + 1:]
+                if sl[a][0] < sl[b][0] + sl[b][1] and sl[b][0] < sl[a][0] + sl[a][1]]
+
+    for m, tag in ((configs.cnn_f32(batch=256, with_input=False)[0], "c2_b256"), (configs.cnn_i8(batch=512, with_input=False)[0], "c5_b512")):
+        onnx = onnx_wire.model_to_onnx(m)
+        piped = slices(generated.emit(onnx, tag + "_pipe", pipelined=True).read_text())
+        whole = slices(generated.emit(onnx, tag + "_whole", pipelined=False).read_text())
+        assert piped.keys() == whole.keys() and len(piped) >= 4
+        assert overlaps(piped) == []
+        assert overlaps(whole) != []         # the whole-batch plan does reuse dead tensors' bytes
+
+
 def test_trailing_dequantize_is_written_by_the_last_quantised_product():
     m, _ = configs.mlp_i8(batch=64)
     text = _emit(m, "c3_b64").read_text()

@@ -148,6 +148,28 @@ def test_pipelined_upload_from_pinned_and_pageable_memory(cuda_device):
     assert rel_err(yp.numpy().reshape(256, -1)[::-1], REF["ref_c2"].reshape(256, -1)) <= 1e-5
 
 
+@pytest.mark.parametrize("key,batch", [("C5", 512), ("C5", 8), ("C3", 1024), ("C4", 512)])
+def test_whole_model_per_uploaded_part(key, batch, cuda_device):
+    """The pipelined upload with every sliceable operator launched per quarter of the batch (C5 at 512: all of them; at 8: the last
+    product stays in the graph): the results are the oracle's, from pinned and from pageable memory, call after call."""
+    import torch
+    m, x = configs.gemm_chain_fp8(rows=batch, width=256, layers=2) if key == "C4" else configs.BUILDERS[key](batch=batch)
+    scales = configs.calibrate_fp8_scales(m, x[:64]) if key == "C4" else None
+    s = generated.session_from_model(m, f"{key.lower()}_b{batch}_pipe", pipelined=True, fp8_scales=scales)
+    assert "void LaunchHead(int part)" in s.hxx.read_text()
+    ref = run_model.run(m, x, fp8_scales=scales).ravel() if key == "C4" else run_model.run(m, x).ravel()
+    xp = torch.from_numpy(x).pin_memory()
+    yp = torch.empty(s.out_elems, dtype=torch.float32).pin_memory()
+    for _ in range(3):
+        yp.zero_()
+        s.infer_ptr(xp.data_ptr(), yp.data_ptr())
+        if key == "C4":
+            assert rel_err(yp.numpy(), ref) <= 2e-2
+        else:
+            assert np.array_equal(yp.numpy().view(np.uint32), ref.view(np.uint32))
+    assert np.array_equal(s.infer(x), yp.numpy())
+
+
 @pytest.mark.parametrize("key,kw,bit_exact", [("C1", {}, False), ("C2", {}, False), ("C3", {}, True), ("C5", {}, True)])
 def test_run_time_batch_session(key, kw, bit_exact, cuda_device):
     """One Session constructed for 48 samples serves batches of 48, 17, 1 and 48 again (the graph is captured anew when the
