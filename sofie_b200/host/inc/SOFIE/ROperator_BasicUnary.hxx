@@ -46,14 +46,21 @@ public:
       model.AddIntermediateTensor(fNY, model.GetTensorType(fNX), fShape);
    }
    void PlanDevice(RModel &model) override { model.SetTensorLayout(fNY, model.GetTensorLayout(model.ResolveAlias(fNX))); }
-   std::string Generate(std::string OpName) override
+   // elementwise: any equal split of the elements is a valid launch
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && !fShape.empty() && ConvertShapeToLength(fShape) % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       OpName = "op_" + OpName;
       if (fShape.empty()) throw std::runtime_error("SOFIE Operator " + fOpLabel + " called to Generate without being initialized first");
       std::stringstream out;
-      out << "\n" << SP << "//------ " << fOpLabel << " " << OpName << "\n";
-      out << EMIT::Call(SP, "sofie_cuda_unary_f32(fStream, " + std::to_string(fCode) + ", " + EMIT::FloatLit(fAlpha) + ", " + EMIT::Dev(fNX) +
-                               ", " + EMIT::Dev(fNY) + ", " + std::to_string(ConvertShapeToLength(fShape)) + ")");
+      const size_t n = ConvertShapeToLength(fShape);
+      out << "\n" << SP << "//------ " << fOpLabel << " " << OpName << (parts > 1 ? ", one slice of the batch" : "") << "\n";
+      out << EMIT::Call(SP, "sofie_cuda_unary_f32(fStream, " + std::to_string(fCode) + ", " + EMIT::FloatLit(fAlpha) + ", " +
+                               EMIT::DevSlice(fNX, n, parts) + ", " + EMIT::DevSlice(fNY, n, parts) + ", " + std::to_string(n / parts) + ")");
       return out.str();
    }
 };

@@ -159,12 +159,19 @@ public:
       if (fType != ETensorType::UINT8 && fType != ETensorType::FLOAT)
          throw std::runtime_error("SOFIE Pool op: unsupported tensor type");
    }
-   std::string Generate(std::string OpName) override
+   // the samples of a batch are independent: any equal split of the batch axis is a valid launch (2-D and 1-D pooling)
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && !fVolume && !fShapeX.empty() && fShapeX[0] % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       OpName = "op_" + OpName;
       if (fShapeX.empty() || fShapeY.empty()) throw std::runtime_error("SOFIE Pool Op called to Generate without being initialized first");
       std::stringstream out;
-      out << "\n" << SP << "//----  operator " << Name() << "  " << OpName << "\n";
+      out << "\n" << SP << "//----  operator " << Name() << "  " << OpName << (parts > 1 ? ", one slice of the batch" : "") << "\n";
+      const std::string x = EMIT::DevSlice(fNX, ConvertShapeToLength(fShapeX), parts), y = EMIT::DevSlice(fNY, ConvertShapeToLength(fShapeY), parts);
       if (fVolume) {
          out << SP << "{\n";
          out << SP << SP << "const sofie_pool3d_desc d = {" << (fPoolMode == MaxPool ? 0 : 1) << ", " << fShapeX[0] << ", " << fShapeX[1] << ", "
@@ -176,17 +183,17 @@ public:
          return out.str();
       }
       if (fType == ETensorType::UINT8) {
-         out << EMIT::Call(SP, "sofie_cuda_maxpool2d_u8(fStream, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ", " +
-                                  std::to_string(fShape4[0]) + ", " + std::to_string(fShape4[1]) + ", " + std::to_string(fShape4[2]) +
+         out << EMIT::Call(SP, "sofie_cuda_maxpool2d_u8(fStream, " + x + ", " + y + ", " +
+                                  std::to_string(fShape4[0] / parts) + ", " + std::to_string(fShape4[1]) + ", " + std::to_string(fShape4[2]) +
                                   ", " + std::to_string(fShape4[3]) + ", " + std::to_string(fKH) + ", " + std::to_string(fKW) + ", " +
                                   std::to_string(fSH) + ", " + std::to_string(fSW) + ", " + std::to_string((int)fLayout) + ")");
          return out.str();
       }
       out << SP << "{\n";
-      out << SP << SP << "const sofie_pool2d_desc d = {" << (fPoolMode == MaxPool ? 0 : 1) << ", " << fShape4[0] << ", " << fShape4[1]
+      out << SP << SP << "const sofie_pool2d_desc d = {" << (fPoolMode == MaxPool ? 0 : 1) << ", " << fShape4[0] / parts << ", " << fShape4[1]
           << ", " << fShape4[2] << ", " << fShape4[3] << ", " << fKH << ", " << fKW << ", " << fSH << ", " << fSW << ", {" << fPads[0]
           << ", " << fPads[1] << ", " << fPads[2] << ", " << fPads[3] << "}, " << fAttr.count_include_pad << ", " << (int)fLayout << "};\n";
-      out << EMIT::Call(SP + SP, "sofie_cuda_pool2d_f32(fStream, &d, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ")");
+      out << EMIT::Call(SP + SP, "sofie_cuda_pool2d_f32(fStream, &d, " + x + ", " + y + ")");
       out << SP << "}\n";
       return out.str();
    }

@@ -45,14 +45,21 @@ public:
          throw std::runtime_error("SOFIE Relu Op: a stand-alone Relu on a quantised tensor is not generated; it is fused into QLinear operators");
       model.SetTensorLayout(fNY, model.GetTensorLayout(model.ResolveAlias(fNX)));
    }
-   std::string Generate(std::string OpName) override
+   // elementwise: any equal split of the elements is a valid launch
+   bool CanSliceBatch(size_t parts) const override { return parts > 0 && !fShape.empty() && ConvertShapeToLength(fShape) % parts == 0; }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       OpName = "op_" + OpName;
       if (fShape.empty()) throw std::runtime_error("SOFIE Operator Relu called to Generate without being initialized first");
       std::stringstream out;
-      out << "\n" << SP << "//------ RELU " << OpName << "\n";
-      out << EMIT::Call(SP, "sofie_cuda_relu_f32(fStream, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ", " +
-                               std::to_string(ConvertShapeToLength(fShape)) + ")");
+      const size_t n = ConvertShapeToLength(fShape);
+      out << "\n" << SP << "//------ RELU " << OpName << (parts > 1 ? ", one slice of the batch" : "") << "\n";
+      out << EMIT::Call(SP, "sofie_cuda_relu_f32(fStream, " + EMIT::DevSlice(fNX, n, parts) + ", " + EMIT::DevSlice(fNY, n, parts) + ", " +
+                               std::to_string(n / parts) + ")");
       return out.str();
    }
 };

@@ -37,7 +37,19 @@ public:
       if (model.GetTensorType(fNX) != ETensorType::FLOAT) throw std::runtime_error("SOFIE Softmax Op: float tensors only");
       model.AddIntermediateTensor(fNY, model.GetTensorType(fNX), fShape);
    }
-   std::string Generate(std::string OpName) override
+   // rows in front of the normalised axis are independent: a split of the leading dimension is a valid launch unless that
+   // dimension is the axis itself
+   bool CanSliceBatch(size_t parts) const override
+   {
+      if (parts == 0 || fShape.empty() || fShape[0] % parts != 0) return false;
+      const int64_t axis = fAttrAxis < 0 ? fAttrAxis + (int64_t)fShape.size() : fAttrAxis;
+      return axis > 0 && axis < (int64_t)fShape.size();
+   }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       OpName = "op_" + OpName;
       if (fShape.empty()) throw std::runtime_error("SOFIE Operator Softmax called to Generate without being initialized first");
@@ -49,8 +61,9 @@ public:
       for (size_t i = axis + 1; i < rank; i++) inner *= fShape[i];
       if (fShape[axis] == 0) throw std::runtime_error("SOFIE - Softmax operator is along axis with zero elements");
       std::stringstream out;
-      out << "\n" << SP << "//------ SOFTMAX - " << rank << "  " << ConvertShapeToLength(fShape) << "  " << axis << "\n";
-      out << EMIT::Call(SP, "sofie_cuda_softmax_f32(fStream, " + EMIT::Dev(fNX) + ", " + EMIT::Dev(fNY) + ", " + std::to_string(outer) +
+      const size_t n = ConvertShapeToLength(fShape);
+      out << "\n" << SP << "//------ SOFTMAX - " << rank << "  " << n << "  " << axis << (parts > 1 ? ", one slice of the batch" : "") << "\n";
+      out << EMIT::Call(SP, "sofie_cuda_softmax_f32(fStream, " + EMIT::DevSlice(fNX, n, parts) + ", " + EMIT::DevSlice(fNY, n, parts) + ", " + std::to_string(outer / parts) +
                                ", " + std::to_string(fShape[axis]) + ", " + std::to_string(inner) + ")");
       return out.str();
    }

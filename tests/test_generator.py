@@ -250,6 +250,18 @@ def test_every_leading_operator_that_can_be_sliced_runs_per_uploaded_part():
     assert "sofie_cuda_qlinear_matmul_f32(fStream, &d, dev_f0," in tail and "sofie_cuda_ctx_graph_begin" in small
 
 
+def test_sliced_operators_end_at_the_first_one_that_cannot_be_sliced():
+    """Gemm, Selu, Gemm, Tanh run per uploaded part; the Sub of a constant row behind them (a binary operator, which has no sliced form)
+    and everything after it stay in the graph."""
+    m, _ = configs.mlp_activations_f32(batch=256, with_input=False)
+    text = generated.emit(onnx_wire.model_to_onnx(m), "mlp_act_b256_pipe", pipelined=True).read_text()
+    head = text[text.index("void LaunchHead(int part)"):text.index("void Launch() {")]
+    tail = text[text.index("void Launch() {"):text.index("void Run() {")]
+    assert head.count("sofie_cuda_gemm_f32(") == 2 and head.count("sofie_cuda_unary_f32(") == 2 and "one slice of the batch" in head
+    assert "const sofie_gemm_f32_desc d = {64, 48, 32," in head
+    assert tail.count("sofie_cuda_gemm_f32(") == 1 and tail.count("sofie_cuda_unary_f32(") == 2 and "part" not in tail.replace("sofie_cuda_ctx_mark", "")
+
+
 def test_tensors_of_sliced_operators_share_no_arena_bytes():
     """Slice 1 of a model's first tensor is written after slice 0 of its last one, and the input's later parts arrive in between:
     the tensors of the operators launched per part must not reuse each other's bytes, as tensors of a whole-batch plan do."""

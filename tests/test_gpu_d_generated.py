@@ -148,12 +148,17 @@ def test_pipelined_upload_from_pinned_and_pageable_memory(cuda_device):
     assert rel_err(yp.numpy().reshape(256, -1)[::-1], REF["ref_c2"].reshape(256, -1)) <= 1e-5
 
 
-@pytest.mark.parametrize("key,batch", [("C5", 512), ("C5", 8), ("C3", 1024), ("C4", 512)])
+@pytest.mark.parametrize("key,batch", [("C5", 512), ("C5", 8), ("C3", 1024), ("C4", 512), ("ACT", 256), ("C2", 64)])
 def test_whole_model_per_uploaded_part(key, batch, cuda_device):
     """The pipelined upload with every sliceable operator launched per quarter of the batch (C5 at 512: all of them; at 8: the last
     product stays in the graph): the results are the oracle's, from pinned and from pageable memory, call after call."""
     import torch
-    m, x = configs.gemm_chain_fp8(rows=batch, width=256, layers=2) if key == "C4" else configs.BUILDERS[key](batch=batch)
+    if key == "C4":
+        m, x = configs.gemm_chain_fp8(rows=batch, width=256, layers=2)
+    elif key == "ACT":
+        m, x = configs.mlp_activations_f32(batch=batch)      # Gemm, Selu, Gemm, Tanh per part; Sub ... Sigmoid in the graph
+    else:
+        m, x = configs.BUILDERS[key](batch=batch)
     scales = configs.calibrate_fp8_scales(m, x[:64]) if key == "C4" else None
     s = generated.session_from_model(m, f"{key.lower()}_b{batch}_pipe", pipelined=True, fp8_scales=scales)
     assert "void LaunchHead(int part)" in s.hxx.read_text()
@@ -165,6 +170,8 @@ def test_whole_model_per_uploaded_part(key, batch, cuda_device):
         s.infer_ptr(xp.data_ptr(), yp.data_ptr())
         if key == "C4":
             assert rel_err(yp.numpy(), ref) <= 2e-2
+        elif key in ("ACT", "C2"):
+            assert rel_err(yp.numpy(), ref) <= 1e-5
         else:
             assert np.array_equal(yp.numpy().view(np.uint32), ref.view(np.uint32))
     assert np.array_equal(s.infer(x), yp.numpy())
