@@ -250,6 +250,18 @@ def test_every_leading_operator_that_can_be_sliced_runs_per_uploaded_part():
     assert "sofie_cuda_qlinear_matmul_f32(fStream, &d, dev_f0," in tail and "sofie_cuda_ctx_graph_begin" in small
 
 
+def test_inputs_of_128_mb_and_more_are_uploaded_in_eight_parts():
+    """C5 at its full batch (268 MB of floats) without any option: eight parts of 2048 images, every operator launched per part;
+    half the batch (134 MB) still eight parts, a quarter (67 MB) four."""
+    for batch, parts in ((16384, 8), (8192, 8), (4096, 4)):
+        m, _ = configs.cnn_i8(batch=batch, with_input=False)
+        text = _emit(m, f"c5_b{batch}").read_text()
+        assert f"for (int part = 0; part < {parts}; part++) LaunchHead(part);" in text
+        per = batch // parts
+        assert f"const sofie_qconv2d_desc d = {{{per}, 1, 64, 64, 32," in text and f"(dev_x + (size_t)part * {per * 4096})" in text
+        assert f"sofie_cuda_ctx_h2d_part(fCtx, dev_x + (size_t)part * {per * 4096}, tensor_x + (size_t)part * {per * 4096}, {per * 4096 * 4}, part)" in text
+
+
 def test_sliced_operators_end_at_the_first_one_that_cannot_be_sliced():
     """Gemm, Selu, Gemm, Tanh run per uploaded part; the Sub of a constant row behind them (a binary operator, which has no sliced form)
     and everything after it stay in the graph."""
