@@ -193,6 +193,48 @@ def pin_to_gpu_numa_node(local_rank):
         return dict(numa_node=None, pinned=False, why=f"{type(e).__name__}")
 
 
+def place_host_memory_near_gpu(local_rank, record):
+    """Where sysfs names no NUMA node for the GPU (a container), asks NVML which host cores and which memory node are
+    nearest to it and (a) restricts this process to those of them it is allowed to run on, (b) makes that node the preferred
+    one for this process's page allocations (set_mempolicy, MPOL_PREFERRED: a hint, allocation elsewhere still succeeds), so
+    that the pinned input buffer allocated next lies on the GPU's side of the host. Process-local; nothing outlasts the process.
+    Adds what it did to `record`."""
+    try:
+        import ctypes
+        import platform
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
+        h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        allowed = os.sched_getaffinity(0)
+        try:
+            words = (max(allowed) // 64) + 1
+            mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+            cpus = {64 * w + b for w in range(words) for b in range(64) if (int(mask[w]) >> b) & 1}
+            use = cpus & allowed
+            record["nvml_cpus"] = len(cpus)
+            if use and use != allowed:
+                os.sched_setaffinity(0, use)
+                record.update(pinned=True, cores=len(use))
+        except Exception as e:
+            record["nvml_cpu_affinity"] = type(e).__name__
+        try:
+            nodes = pynvml.nvmlDeviceGetMemoryAffinity(h, 1, pynvml.NVML_AFFINITY_SCOPE_NODE)
+            node_mask = int(nodes[0])
+            record["nvml_mem_nodes"] = node_mask
+            if node_mask and platform.machine() == "x86_64":
+                libc = ctypes.CDLL(None, use_errno=True)
+                m = ctypes.c_ulong(node_mask)
+                rc = libc.syscall(238, 1, ctypes.byref(m), 65)   # set_mempolicy(MPOL_PREFERRED, &mask, maxnode)
+                record["mempolicy"] = "preferred" if rc == 0 else f"errno {ctypes.get_errno()}"
+        except Exception as e:
+            record["nvml_mem_affinity"] = type(e).__name__
+    except Exception as e:
+        record["nvml"] = type(e).__name__
+    return record
+
+
 # ------------------------------------------------------------------------------------ workloads
 def build_workload(workload, batch=None, with_input=True):
     """The configuration at its full size, or at another batch / row count (large-batch entries, shards, captures)."""
@@ -547,6 +589,8 @@ def run(args, rank, world, local_rank):
 
     os.environ["SOFIE_CUDA_DEVICE"] = str(local_rank)  # the emitted Session reads its device from here
     affinity = pin_to_gpu_numa_node(local_rank)
+    if not affinity.get("pinned"):
+        affinity = place_host_memory_near_gpu(local_rank, affinity)
     capi.load()
     clocks = ClockSampler(local_rank)
     pk = peaks()
