@@ -161,7 +161,10 @@ def test_conv3x3_f32_tcgen05(case):
                                   (2, 128, 32, 16, 64, 1, 0), (5, 32, 16, 16, 24, 1, 2),
                                   # pooled-window kernel (32 x 16 tiles, pooling in tensor memory): two K steps per tap, 32 and 48
                                   # output channels, no Relu, several tiles per image in both directions, more tiles than SMs
-                                  (2, 64, 32, 32, 64, 1, 2), (2, 32, 64, 48, 32, 0, 2), (3, 64, 32, 16, 48, 1, 2), (40, 32, 64, 32, 16, 1, 2)])
+                                  (2, 64, 32, 32, 64, 1, 2), (2, 32, 64, 48, 32, 0, 2), (3, 64, 32, 16, 48, 1, 2), (40, 32, 64, 32, 16, 1, 2),
+                                  # lines of eight pixels with more tiles than SMs (per-tap kernel with resident weights): two images per
+                                  # tile, one image per tile, 32-byte pixels
+                                  (301, 64, 8, 8, 128, 1, 2), (310, 64, 8, 8, 72, 0, 0), (160, 64, 16, 8, 64, 1, 2), (300, 32, 8, 8, 32, 1, 0)])
 def test_qlinear_conv3x3_tcgen05_bit_exact(case):
     N, C, H, W, Cout, relu, pool = case
     rng = np.random.default_rng(sum(case))
