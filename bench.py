@@ -3,19 +3,21 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C1..C5] [--batch B]
 
-Headline workload (default): configuration C5 of BASELINE.json, the int8 calorimeter CNN on
-[16384,1,64,64] -- the configuration the benchmark definition shards across 1/2/4/8 GPUs. One step = one
+Headline workload (default): configuration C5 of the benchmark definition, the int8 calorimeter CNN on
+[16384,1,64,64] -- the configuration that is sharded across 1/2/4/8 GPUs. One step = one
 Session::infer over the whole batch. Everything timed runs through the C++ Session the generator emits
 (ONNX bytes -> RModelParser_ONNX::Parse -> RModel::Generate -> g++ -> Session): `value` replays the Session's own
 captured CUDA graph with the input resident on the device (Session::RunResident, device-timed with CUDA events
 on the Session's stream, L2 flushed between steps); `e2e` calls Session::infer(float*) with a pinned host buffer,
-so every step holds the host->device copy of the input and the read-back of the result.
+so every step holds the host->device copy of the input and the read-back of the result. A large input is uploaded
+in parts with the model's leading operators launched per part (what infer() does by itself); `value` then uses the
+Session of the same model emitted with Options::kSingleUpload, whose graph runs every operator once over the batch.
 
 Multi-GPU (torchrun, one process per GPU): the batch of 16384 images is split into contiguous shards, one per
 rank; every rank builds its own Session for its shard (weights replicated), there is no collective on the data
 path, and the job's throughput is the whole batch over the slowest rank's time: strong scaling.
 
-With one GPU the line also carries `per_config` (C1..C5 at their BASELINE sizes) and `large_batch` (C1 and C3 at 2^18
+With one GPU the line also carries `per_config` (C1..C5 at the sizes of the benchmark definition) and `large_batch` (C1 and C3 at 2^18
 rows, C2 at 8192 images), each with value, e2e from pinned and from pageable memory, the dominant contraction's
 roofline fraction and -- where the CPU baseline leg ran -- the comparison of the GPU result with the CPU result
 on the baseline's sample, and `hbm_ops`: the memory-bound operators of the path (Relu, Softmax, MaxPool, (de)quantise,
