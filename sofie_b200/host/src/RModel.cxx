@@ -932,10 +932,12 @@ void RModel::GenerateInfer()
       const std::string &n = fInputTensorNames[0];
       const size_t elems = ConvertShapeToLength(GetTensorShape(n)) / fUploadParts;
       const std::string parts = std::to_string(fUploadParts), slice = std::to_string(elems);
-      fGC += "   for (int part = 0; part < " + parts + "; part++)\n";
+      // one loop: from pinned memory every call only enqueues (the copy of a part takes far longer than enqueueing the launches
+      // behind it, so the copy stream never runs dry); from pageable memory the copy call returns when the part has been staged,
+      // and the kernels of that part run while the host stages the next one
+      fGC += "   for (int part = 0; part < " + parts + "; part++) {\n";
       fGC += "      Check(sofie_cuda_ctx_h2d_part(fCtx, " + EMIT::Dev(n) + " + (size_t)part * " + slice + ", tensor_" + n + " + (size_t)part * " + slice +
              ", " + std::to_string(elems * GetTypeSize(GetTensorType(n))) + ", part), \"sofie_cuda_ctx_h2d_part\");\n";
-      fGC += "   for (int part = 0; part < " + parts + "; part++) {\n";
       fGC += "      Check(sofie_cuda_ctx_wait_part(fCtx, part), \"sofie_cuda_ctx_wait_part\");\n";
       fGC += "      LaunchHead(part);\n";
       fGC += "   }\n";
