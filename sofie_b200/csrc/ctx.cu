@@ -7,6 +7,8 @@
 #include "common.cuh"
 #include "contract.cuh"
 
+#include <atomic>
+#include <chrono>
 #include <condition_variable>
 #include <cstdlib>
 #include <cstring>
@@ -90,7 +92,9 @@ uint32_t *device_status_word(cudaStream_t stream)
 // Copies between pageable host memory and the pinned staging slots with several threads: one core copies about 12 GB/s,
 // a fifth of what the PCIe link takes. The caller and the helper threads each copy an equal, page-aligned piece of a
 // chunk; copy() returns when all pieces are done. SOFIE_CUDA_COPY_THREADS sets the number of threads (default 4, 1 = the
-// caller alone). The helpers sleep on a condition variable between chunks and end with the context.
+// caller alone). A helper spins for a fraction of a millisecond after a chunk (the next chunk of the same transfer comes
+// within that time, and waking a sleeping thread costs as much as its piece of the copy), then sleeps on a condition
+// variable; chunks below 4 MB are copied by the caller alone. The helpers end with the context.
 class HostCopyPool {
 public:
    explicit HostCopyPool(int helpers) : jobs_(helpers > 0 ? helpers : 0)
@@ -101,7 +105,7 @@ public:
    {
       {
          std::lock_guard<std::mutex> lock(mu_);
-         stop_ = true;
+         stop_.store(true);
       }
       wake_.notify_all();
       for (auto &t : threads_) t.join();
@@ -112,31 +116,27 @@ public:
    void copy(void *dst, const void *src, size_t bytes)
    {
       const size_t parts = jobs_.size() + 1;
-      if (parts == 1 || bytes < (size_t(1) << 20)) {
+      if (parts == 1 || bytes < (size_t(4) << 20)) {
          std::memcpy(dst, src, bytes);
          return;
       }
       const size_t piece = ((bytes / parts) + 4095) & ~size_t(4095);
-      size_t mine = 0;
+      const size_t mine = piece < bytes ? piece : bytes; // the caller takes the first piece
+      size_t off = mine;
+      for (auto &j : jobs_) {
+         const size_t n = off >= bytes ? 0 : (bytes - off < piece ? bytes - off : piece);
+         j = {static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, n};
+         off += n;
+      }
+      pending_.store((int)jobs_.size(), std::memory_order_relaxed);
+      generation_.fetch_add(1, std::memory_order_release); // publishes the jobs to the helpers that are still spinning
       {
-         std::lock_guard<std::mutex> lock(mu_);
-         size_t off = 0;
-         mine = piece < bytes ? piece : bytes; // the caller takes the first piece
-         off = mine;
-         for (auto &j : jobs_) {
-            const size_t n = off >= bytes ? 0 : (bytes - off < piece ? bytes - off : piece);
-            j = {static_cast<char *>(dst) + off, static_cast<const char *>(src) + off, n};
-            off += n;
-         }
-         // the last helper takes what rounding left over
-         if (off < bytes) jobs_.back().bytes += bytes - off;
-         pending_ = (int)jobs_.size();
-         generation_++;
+         std::lock_guard<std::mutex> lock(mu_);           // ... and to the sleeping ones: no wake-up is lost
       }
       wake_.notify_all();
       std::memcpy(dst, src, mine);
-      std::unique_lock<std::mutex> lock(mu_);
-      done_.wait(lock, [this] { return pending_ == 0; });
+      // the helpers' pieces are as long as the caller's: they finish at about the same time
+      while (pending_.load(std::memory_order_acquire) != 0) std::this_thread::yield();
    }
 
 private:
@@ -149,29 +149,29 @@ private:
    {
       unsigned long long seen = 0;
       for (;;) {
-         Job job;
-         {
-            std::unique_lock<std::mutex> lock(mu_);
-            wake_.wait(lock, [&] { return stop_ || generation_ != seen; });
-            if (stop_) return;
-            seen = generation_;
-            job = jobs_[index];
+         const auto t0 = std::chrono::steady_clock::now();
+         while (generation_.load(std::memory_order_acquire) == seen && !stop_.load(std::memory_order_relaxed)) {
+            if (std::chrono::steady_clock::now() - t0 > std::chrono::microseconds(500)) {
+               std::unique_lock<std::mutex> lock(mu_);
+               wake_.wait(lock, [&] { return stop_.load() || generation_.load(std::memory_order_acquire) != seen; });
+               break;
+            }
+            std::this_thread::yield();
          }
+         if (stop_.load()) return;
+         seen = generation_.load(std::memory_order_acquire);
+         const Job job = jobs_[index];
          if (job.bytes) std::memcpy(job.dst, job.src, job.bytes);
-         {
-            std::lock_guard<std::mutex> lock(mu_);
-            pending_--;
-         }
-         done_.notify_one();
+         pending_.fetch_sub(1, std::memory_order_release);
       }
    }
    std::vector<Job> jobs_;
    std::vector<std::thread> threads_;
    std::mutex mu_;
-   std::condition_variable wake_, done_;
-   unsigned long long generation_ = 0;
-   int pending_ = 0;
-   bool stop_ = false;
+   std::condition_variable wake_;
+   std::atomic<unsigned long long> generation_{0};
+   std::atomic<int> pending_{0};
+   std::atomic<bool> stop_{false};
 };
 
 } // namespace sofie
