@@ -69,6 +69,8 @@ public:
       fShapeA = model.GetTensorShape(fNA);
       fShapeB = model.GetTensorShape(fNB);
       fShapeY = UTILITY::MultidirectionalBroadcastShape(fShapeA, fShapeB);
+      fConstA = model.IsInitializedTensor(fNA);
+      fConstB = model.IsInitializedTensor(fNB);
       if (fShapeY.size() > 4) throw std::runtime_error(std::string("SOFIE Binary Op ") + Name() + ": rank above 4 is not supported on the device");
       model.AddIntermediateTensor(fNY, ETensorType::FLOAT, fShapeY);
    }
@@ -78,7 +80,22 @@ public:
       if (model.IsInitializedTensor(fNB)) model.UseOnDevice(fNB);
       model.SetTensorLayout(fNY, ELayout::NCHW);
    }
-   std::string Generate(std::string OpName) override
+   // elementwise over the output: an equal split of its leading dimension is a valid launch when every operand either has that
+   // dimension too (its slice is read) or is a constant broadcast along it (read whole by every slice)
+   bool CanSliceBatch(size_t parts) const override
+   {
+      if (parts == 0 || fShapeY.empty() || fShapeY[0] % parts != 0) return false;
+      const size_t lead = 4 - fShapeY.size();
+      const auto sa = Strides(fShapeA, fShapeY), sb = Strides(fShapeB, fShapeY);
+      if (fShapeY[0] > 1 && ((sa[lead] == 0 && !fConstA) || (sb[lead] == 0 && !fConstB))) return false;
+      return true;
+   }
+   std::string GenerateBatchSlice(std::string OpName, size_t parts) override { return GenerateCall(OpName, parts); }
+   std::string Generate(std::string OpName) override { return GenerateCall(OpName, 1); }
+
+private:
+   bool fConstA = false, fConstB = false;
+   std::string GenerateCall(std::string OpName, size_t parts)
    {
       OpName = "op_" + OpName;
       if (fShapeY.empty() && ConvertShapeToLength(fShapeY) != 1)
@@ -86,13 +103,22 @@ public:
       std::vector<size_t> out4(4 - fShapeY.size(), 1);
       out4.insert(out4.end(), fShapeY.begin(), fShapeY.end());
       auto sa = Strides(fShapeA, fShapeY), sb = Strides(fShapeB, fShapeY);
+      std::string a = EMIT::Dev(fNA), b = EMIT::Dev(fNB), y = EMIT::Dev(fNY);
+      if (parts > 1) {
+         const size_t lead = 4 - fShapeY.size(), rows = fShapeY[0] / parts;
+         out4[lead] = rows;
+         if (sa[lead]) a = "(" + a + " + (size_t)part * " + std::to_string((size_t)sa[lead] * rows) + ")";
+         if (sb[lead]) b = "(" + b + " + (size_t)part * " + std::to_string((size_t)sb[lead] * rows) + ")";
+         y = EMIT::DevSlice(fNY, ConvertShapeToLength(fShapeY), parts);
+      }
       std::stringstream out;
-      out << "\n" << SP << "//------ " << Name() << " " << OpName << " -> " << fNY << " " << ConvertShapeToString(fShapeY) << "\n";
+      out << "\n" << SP << "//------ " << Name() << " " << OpName << " -> " << fNY << " " << ConvertShapeToString(fShapeY)
+          << (parts > 1 ? ", one slice of the batch" : "") << "\n";
       out << SP << "{\n";
       out << SP << SP << "const sofie_binary_desc d = {" << (int)Op << ", {" << out4[0] << ", " << out4[1] << ", " << out4[2] << ", " << out4[3]
           << "}, {" << sa[0] << ", " << sa[1] << ", " << sa[2] << ", " << sa[3] << "}, {" << sb[0] << ", " << sb[1] << ", " << sb[2] << ", "
           << sb[3] << "}};\n";
-      out << EMIT::Call(SP + SP, "sofie_cuda_binary_f32(fStream, &d, " + EMIT::Dev(fNA) + ", " + EMIT::Dev(fNB) + ", " + EMIT::Dev(fNY) + ")");
+      out << EMIT::Call(SP + SP, "sofie_cuda_binary_f32(fStream, &d, " + a + ", " + b + ", " + y + ")");
       out << SP << "}\n";
       return out.str();
    }

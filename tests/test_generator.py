@@ -263,15 +263,22 @@ def test_inputs_of_128_mb_and_more_are_uploaded_in_eight_parts():
 
 
 def test_sliced_operators_end_at_the_first_one_that_cannot_be_sliced():
-    """Gemm, Selu, Gemm, Tanh run per uploaded part; the Sub of a constant row behind them (a binary operator, which has no sliced form)
-    and everything after it stay in the graph."""
+    """The decoder stack: the convolution (Relu fused) runs per uploaded part; the ConvTranspose behind it has no sliced form, so it
+    and everything after it stay in the graph. The MLP with Sub / Div of constant rows between its layers is sliced throughout:
+    a binary operator reads its batch-shaped operand slice by slice and the constant one whole."""
+    m, _ = configs.upsample_f32(batch=64, with_input=False)
+    text = generated.emit(onnx_wire.model_to_onnx(m), "upsample_b64_pipe", pipelined=True).read_text()
+    head = text[text.index("void LaunchHead(int part)"):text.index("void Launch() {")]
+    tail = text[text.index("void Launch() {"):text.index("void Run() {")]
+    assert head.count("sofie_cuda_conv2d_f32(") == 1 and "sofie_cuda_conv_transpose2d" not in head and "one of 4 slices of the batch" in head
+    assert tail.count("sofie_cuda_conv_transpose2d_f32") >= 2 and "part" not in tail.replace("sofie_cuda_ctx_mark", "")
     m, _ = configs.mlp_activations_f32(batch=256, with_input=False)
     text = generated.emit(onnx_wire.model_to_onnx(m), "mlp_act_b256_pipe", pipelined=True).read_text()
     head = text[text.index("void LaunchHead(int part)"):text.index("void Launch() {")]
-    tail = text[text.index("void Launch() {"):text.index("void Run() {")]
-    assert head.count("sofie_cuda_gemm_f32(") == 2 and head.count("sofie_cuda_unary_f32(") == 2 and "one slice of the batch" in head
-    assert "const sofie_gemm_f32_desc d = {64, 48, 32," in head
-    assert tail.count("sofie_cuda_gemm_f32(") == 1 and tail.count("sofie_cuda_unary_f32(") == 2 and "part" not in tail.replace("sofie_cuda_ctx_mark", "")
+    assert head.count("sofie_cuda_gemm_f32(") == 3 and head.count("sofie_cuda_unary_f32(") == 4 and head.count("sofie_cuda_binary_f32(") == 2
+    assert "const sofie_gemm_f32_desc d = {64, 48, 32," in head and "void Run() {\n}" in text
+    # Sub of a constant row [48] from [256, 48]: 64 rows per launch, the activation sliced, the row whole
+    assert "{1, 1, 64, 48}, {0, 0, 48, 1}, {0, 0, 0, 1}" in head and "(dev_a1 + (size_t)part * 3072), dev_shift, (dev_sh + (size_t)part * 3072)" in head
 
 
 def test_tensors_of_sliced_operators_share_no_arena_bytes():

@@ -148,7 +148,7 @@ def test_pipelined_upload_from_pinned_and_pageable_memory(cuda_device):
     assert rel_err(yp.numpy().reshape(256, -1)[::-1], REF["ref_c2"].reshape(256, -1)) <= 1e-5
 
 
-@pytest.mark.parametrize("key,batch", [("C5", 512), ("C5", 8), ("C3", 1024), ("C4", 512), ("ACT", 256), ("C2", 64)])
+@pytest.mark.parametrize("key,batch", [("C5", 512), ("C5", 8), ("C3", 1024), ("C4", 512), ("ACT", 256), ("C2", 64), ("RES", 64)])
 def test_whole_model_per_uploaded_part(key, batch, cuda_device):
     """The pipelined upload with every sliceable operator launched per quarter of the batch (C5 at 512: all of them; at 8: the last
     product stays in the graph): the results are the oracle's, from pinned and from pageable memory, call after call."""
@@ -156,7 +156,9 @@ def test_whole_model_per_uploaded_part(key, batch, cuda_device):
     if key == "C4":
         m, x = configs.gemm_chain_fp8(rows=batch, width=256, layers=2)
     elif key == "ACT":
-        m, x = configs.mlp_activations_f32(batch=batch)      # Gemm, Selu, Gemm, Tanh per part; Sub ... Sigmoid in the graph
+        m, x = configs.mlp_activations_f32(batch=batch)      # Gemm, unary and binary operators (one operand a constant row): all per part
+    elif key == "RES":
+        m, x = configs.resblock_f32(batch=batch)             # Add of two batch-shaped tensors, both read slice by slice
     else:
         m, x = configs.BUILDERS[key](batch=batch)
     scales = configs.calibrate_fp8_scales(m, x[:64]) if key == "C4" else None
@@ -170,7 +172,7 @@ def test_whole_model_per_uploaded_part(key, batch, cuda_device):
         s.infer_ptr(xp.data_ptr(), yp.data_ptr())
         if key == "C4":
             assert rel_err(yp.numpy(), ref) <= 2e-2
-        elif key in ("ACT", "C2"):
+        elif key in ("ACT", "C2", "RES"):
             assert rel_err(yp.numpy(), ref) <= 1e-5
         else:
             assert np.array_equal(yp.numpy().view(np.uint32), ref.view(np.uint32))
