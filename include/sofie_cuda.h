@@ -118,6 +118,11 @@ int sofie_cuda_device_check(int device);
  * when `reached_exit_device` is not NULL, stores 1 there as its last action. Nothing faults or hangs;
  * the following sofie_cuda_ctx_check / sofie_cuda_ctx_fetch reports SOFIE_CUDA_ERR_DEVICE once. */
 int sofie_cuda_selftest_wait_timeout(void *stream, int64_t limit_cycles, uint32_t *reached_exit_device);
+/* Self test of the threaded host copy that carries pageable inputs into the pinned staging ring (no
+ * counterpart in the reference; needs no GPU): copies `bytes` bytes from src to dst `repeats` times in
+ * chunks of `chunk` bytes with `threads` threads (the caller and threads - 1 helpers), exactly as
+ * sofie_cuda_ctx_h2d does per staging slot. Returns SOFIE_CUDA_OK, or SOFIE_CUDA_ERR_INVALID for bad arguments. */
+int sofie_cuda_selftest_host_copy(void *dst, const void *src, size_t bytes, size_t chunk, int threads, int repeats);
 /* Per-operator device timers (no counterpart in the reference, whose only timing is the caller's clock).
  * The emitted Launch() calls sofie_cuda_ctx_mark(ctx, i) before operator i and once more after the last
  * one. With the timers off (the default) a mark does nothing; with them on -- the environment variable

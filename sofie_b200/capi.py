@@ -104,6 +104,7 @@ SIGNATURES = {
     "sofie_cuda_ctx_check": [vp],
     "sofie_cuda_device_check": [C.c_int],
     "sofie_cuda_selftest_wait_timeout": [vp, C.c_int64, vp],
+    "sofie_cuda_selftest_host_copy": [vp, vp, C.c_size_t, C.c_size_t, C.c_int, C.c_int],
     "sofie_cuda_ctx_timers": [vp, C.c_int],
     "sofie_cuda_ctx_mark": [vp, C.c_int],
     "sofie_cuda_ctx_timers_read": [vp, vp, C.c_int, C.POINTER(C.c_int)],

@@ -120,7 +120,7 @@ public:
          std::memcpy(dst, src, bytes);
          return;
       }
-      const size_t piece = ((bytes / parts) + 4095) & ~size_t(4095);
+      const size_t piece = (((bytes + parts - 1) / parts) + 4095) & ~size_t(4095); // parts x piece >= bytes
       const size_t mine = piece < bytes ? piece : bytes; // the caller takes the first piece
       size_t off = mine;
       for (auto &j : jobs_) {
@@ -467,6 +467,17 @@ int sofie_cuda_ctx_h2d(sofie_cuda_ctx *ctx, void *dst, const void *src, size_t b
       used[slot] = ctx->staging_busy[slot] = true;
       done += chunk;
    }
+   return SOFIE_CUDA_OK;
+}
+
+int sofie_cuda_selftest_host_copy(void *dst, const void *src, size_t bytes, size_t chunk, int threads, int repeats)
+{
+   SOFIE_REQUIRE((dst && src) || bytes == 0, "NULL buffer");
+   SOFIE_REQUIRE(chunk > 0 && threads >= 1 && threads <= 16 && repeats >= 1, "bad chunk size, thread count or repeat count");
+   HostCopyPool pool(threads - 1);
+   for (int r = 0; r < repeats; r++)
+      for (size_t done = 0; done < bytes; done += chunk)
+         pool.copy(static_cast<char *>(dst) + done, static_cast<const char *>(src) + done, bytes - done < chunk ? bytes - done : chunk);
    return SOFIE_CUDA_OK;
 }
 

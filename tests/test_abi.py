@@ -79,3 +79,25 @@ def test_no_gpu_means_loud_failure_not_cpu_fallback():
     m, _ = configs.mlp_f32(batch=4)
     with pytest.raises(RuntimeError):
         runner.Session(m)
+
+
+@pytest.mark.parametrize("threads", [1, 2, 4, 7])
+def test_threaded_host_copy_moves_every_byte(threads):
+    """The copy that carries pageable inputs into the staging ring, run on plain host memory: chunk sizes below and above the 4 MB
+    from which the helper threads join in, lengths that are no multiple of a page or of the thread count, many chunks in a row
+    (the helpers spin between chunks, then sleep), and a pool that is created and destroyed per call."""
+    import numpy as np
+    capi.load()
+    rng = np.random.default_rng(threads)
+    for nbytes, chunk, repeats in ((0, 1 << 20, 1), (1, 8 << 20, 1), (4095, 8 << 20, 2), ((4 << 20) - 1, 8 << 20, 1), (4 << 20, 8 << 20, 1),
+                                   ((4 << 20) + 1, 8 << 20, 3), ((33 << 20) + 7, 8 << 20, 2), ((24 << 20) + 4097, (5 << 20) + 13, 1)):
+        src = rng.integers(0, 256, nbytes, dtype=np.uint8)
+        dst = np.zeros(nbytes + 64, np.uint8)
+        dst[nbytes:] = 0xA5                                     # canary behind the destination
+        capi.call("sofie_cuda_selftest_host_copy", dst.ctypes.data, src.ctypes.data, nbytes, chunk, threads, repeats)
+        assert np.array_equal(dst[:nbytes], src), (nbytes, chunk)
+        assert (dst[nbytes:] == 0xA5).all()
+    with pytest.raises(RuntimeError):
+        capi.call("sofie_cuda_selftest_host_copy", 0, 0, 16, 1 << 20, 1, 1)
+    with pytest.raises(RuntimeError):
+        capi.call("sofie_cuda_selftest_host_copy", dst.ctypes.data, src.ctypes.data, 16, 1 << 20, 0, 1)
