@@ -179,6 +179,32 @@ def test_whole_model_per_uploaded_part(key, batch, cuda_device):
     assert np.array_equal(s.infer(x), yp.numpy())
 
 
+def test_relu_pool_softmax_per_uploaded_part(cuda_device):
+    """A model of stand-alone Relu, 3x3 MaxPool, Flatten and Softmax with the pipelined upload: all four are launched per quarter of
+    the batch (slices of the elementwise count, of the images, of the rows) and give the oracle's numbers."""
+    import torch
+    rng = np.random.default_rng(11)
+    m = configs.Model("relu_pool_softmax_b256", "x", (256, 4, 16, 16), [])
+    m.layers.append(dict(op="Relu", X="x", Y="r"))
+    m.layers.append(dict(op="MaxPool", X="r", Y="p", kernel=(3, 3), strides=(1, 1), pads=(1, 1, 1, 1)))
+    m.layers.append(dict(op="Flatten", X="p", Y="f"))
+    m.layers.append(dict(op="Softmax", X="f", Y="y", axis=1))
+    m.output_name = "y"
+    x = rng.standard_normal((256, 4, 16, 16)).astype(np.float32)
+    s = generated.session_from_model(m, "relu_pool_softmax_b256_pipe", pipelined=True)
+    text = s.hxx.read_text()
+    head = text[text.index("void LaunchHead(int part)"):text.index("void Launch() {")]
+    assert "sofie_cuda_relu_f32(" in head and "sofie_cuda_pool2d_f32(" in head and "sofie_cuda_softmax_f32(" in head and "void Run() {\n}" in text
+    ref = run_model.run(m, x).ravel()
+    xp = torch.from_numpy(x).pin_memory()
+    yp = torch.empty(s.out_elems, dtype=torch.float32).pin_memory()
+    for _ in range(2):
+        yp.zero_()
+        s.infer_ptr(xp.data_ptr(), yp.data_ptr())
+        assert rel_err(yp.numpy(), ref) <= 1e-5
+    assert np.array_equal(s.infer(x), yp.numpy())
+
+
 @pytest.mark.parametrize("key,kw,bit_exact", [("C1", {}, False), ("C2", {}, False), ("C3", {}, True), ("C5", {}, True)])
 def test_run_time_batch_session(key, kw, bit_exact, cuda_device):
     """One Session constructed for 48 samples serves batches of 48, 17, 1 and 48 again (the graph is captured anew when the
